@@ -1,0 +1,282 @@
+#!/usr/bin/env python
+"""Benchmark of the per-token MoE decode path on the gpt-oss-20b architecture.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl ours|reference]
+
+Workload (the reference's headline measurement): gpt-oss-20b architecture, seeded synthetic
+weights (MXFP4 experts, bf16 attention/embedding/unembedding quantised to Q8 at load), a 73-token
+random-id prompt, then K greedy decode steps from position 73 (K = 128 reproduces pos 73 -> 201).
+One "step" is one decoded token.  Every step streams ~2.66 GB of weights, far more than the
+126 MB L2, so no explicit L2 flush is needed between steps.
+
+`value` is tokens/s with the token id chained on the device (inputs resident in HBM), timed with
+CUDA events on the engine's stream; `e2e` drives every step through Engine.run(tok, pos) with a
+host token in and a host token out.  With --gpus N > 1 (launched by torchrun) every rank decodes
+its own sequence on its own GPU (independent replicas, no data-path collective); the time is the
+maximum over ranks.
+
+--impl reference times the CPU restatement of the reference's algorithm (oracle/, kind "port":
+the reference itself is Rust + aarch64 NEON and cannot be built here) on the host cores.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import tempfile
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+PROMPT_LEN = 73
+SEED = 2
+WORKLOAD = "gpt-oss-20b decode, 73-token prompt, batch 1, greedy"
+METRIC = "batch-1 decode tok/s (gpt-oss-20b shape, MXFP4)"
+
+
+def measured_peaks():
+    p = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(p):
+        try:
+            return float(json.load(open(p))["hbm_gbs"]), "measured"
+        except Exception:
+            pass
+    return 6650.0, "fallback"
+
+
+class ClockSampler:
+    """nvidia-smi clocks and throttle reasons sampled every 200 ms while the timed region runs."""
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, gpu_index):
+        self.idx = gpu_index
+        self.f = tempfile.NamedTemporaryFile("w+", suffix=".csv", delete=False)
+        self.p = None
+
+    def start(self):
+        try:
+            self.p = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "200", "-i", str(self.idx)],
+                                      stdout=self.f, stderr=subprocess.DEVNULL)
+        except Exception:
+            self.p = None
+
+    def stop(self):
+        if self.p is None:
+            return None
+        time.sleep(0.25)
+        self.p.terminate()
+        try:
+            self.p.wait(timeout=5)
+        except Exception:
+            self.p.kill()
+        self.f.flush()
+        rows = [l.strip().split(", ") for l in open(self.f.name) if l.strip()]
+        os.unlink(self.f.name)
+        sm, smax, reasons = [], [], set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for r in rows:
+            if len(r) < 9:
+                continue
+            try:
+                sm.append(float(r[1])); smax.append(float(r[2]))
+            except ValueError:
+                continue
+            for n, v in zip(names, r[5:9]):
+                if v.strip().lower() == "active":
+                    reasons.add(n)
+        if not sm:
+            return None
+        return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(smax), "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def run_reference(args, rank, world):
+    """CPU arm: the oracle (a port of the reference's algorithm) on all host threads."""
+    if rank != 0:
+        return
+    from oracle import oracle as O
+    O.build()
+    cores = os.cpu_count() or 1
+    cfg = O.make_cfg(d=2880, nh=64, nkv=8, hd=64, nl=24, ne=32, topk=4, nvocab=201088)
+    m = O.Model.synth(cfg, SEED)
+    prompt = O.synth_prompt(SEED, PROMPT_LEN, 199999)
+    tok = 0
+    for i, t in enumerate(prompt):
+        tok = m.run(int(t), i, i == len(prompt) - 1)
+    pos = PROMPT_LEN
+    # bounded sample: each call is one decode token; cap the total so the run ends within minutes
+    steps = min(args.steps, 64)
+    warm = min(args.warmup, 3)
+    for _ in range(warm):
+        tok = m.run(tok, pos, True); pos += 1
+    t0 = time.perf_counter()
+    for _ in range(steps):
+        tok = m.run(tok, pos, True); pos += 1
+    dt = time.perf_counter() - t0
+    v = steps / dt
+    sample = f"{steps} decode steps from position {PROMPT_LEN + warm} after a {PROMPT_LEN}-token prompt (full model)"
+    print(json.dumps({
+        "impl": "reference", "metric": METRIC, "value": v, "unit": "tok/s", "n_gpus": args.gpus, "steps": steps, "warmup": warm,
+        "ms_per_step": 1000.0 * dt / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8xfp4->int32,f32",
+        "data": "synthetic", "config": {"workload": WORKLOAD, "l2": "inputs larger than L2"},
+        "cpu_baseline": {"value": v, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
+        "e2e": {"value": v, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }), flush=True)
+
+
+def cpu_baseline_and_parity(eng_tokens, first_tok, nsteps):
+    """Rank 0, N = 1: time the oracle on a bounded sample of the same workload and use it as the
+    checker of the GPU's first decoded tokens."""
+    from oracle import oracle as O
+    O.build()
+    cfg = O.make_cfg(d=2880, nh=64, nkv=8, hd=64, nl=24, ne=32, topk=4, nvocab=201088)
+    m = O.Model.synth(cfg, SEED)
+    prompt = O.synth_prompt(SEED, PROMPT_LEN, 199999)
+    tok = 0
+    for i, t in enumerate(prompt):
+        tok = m.run(int(t), i, i == len(prompt) - 1)
+    ok = tok == first_tok
+    pos = PROMPT_LEN
+    t0 = time.perf_counter()
+    got = []
+    for _ in range(nsteps):
+        tok = m.run(tok, pos, True); pos += 1
+        got.append(tok)
+    dt = time.perf_counter() - t0
+    ok = ok and got == [int(t) for t in eng_tokens[:nsteps]]
+    m.close()
+    return {"value": nsteps / dt, "unit": "tok/s", "cores": os.cpu_count() or 1, "kind": "port",
+            "sample": f"{nsteps} decode steps from position {PROMPT_LEN} after the {PROMPT_LEN}-token prompt (full model)"}, \
+           {"tokens_checked": nsteps + 1, "identical": bool(ok)}
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline / parity leg")
+    ap.add_argument("--no-stages", action="store_true", help="skip the per-kernel-class timing")
+    args = ap.parse_args()
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if args.impl == "reference":
+        run_reference(args, rank, world)
+        return
+    args.warmup = max(args.warmup, 3)
+    K = max(1, min(args.steps, 4096 - PROMPT_LEN - 1))
+
+    import numpy as np
+    import torch
+    import cpubrrr_b200 as B
+    from cpubrrr_b200 import synth as S
+
+    torch.cuda.set_device(local_rank)
+    dist = None
+    if world > 1:
+        import torch.distributed as dist
+        dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
+
+    eng = B.Engine.synth(B.gptoss_20b_cfg(), SEED, device=local_rank)
+    prompt = S.synth_prompt(SEED + rank, PROMPT_LEN, 199999)   # every replica decodes its own sequence
+    first = eng.prefill(prompt)
+    stream = torch.cuda.ExternalStream(eng.stream, device=torch.device("cuda", local_rank))
+
+    def barrier():
+        torch.cuda.synchronize()
+        if dist is not None:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    # ---- device-chained decode: W warm-up steps, then exactly K timed steps
+    eng.decode(first, PROMPT_LEN, args.warmup)
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    if sampler:
+        sampler.start()
+    e0.record(stream)
+    eng.decode_enqueue(first, PROMPT_LEN, K)
+    e1.record(stream)
+    toks = eng.decode_wait(K)
+    barrier()
+    ms = e0.elapsed_time(e1)
+    # keep the GPU busy long enough for the clock sampler on short runs
+    if sampler:
+        t_end = time.time() + max(0.0, 1.0 - ms / 1000.0)
+        while time.time() < t_end:
+            eng.decode(first, PROMPT_LEN, 16)
+    clocks = sampler.stop() if sampler else None
+    if dist is not None:
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+
+    # ---- end to end through the public API: host token in, host token out, every step
+    tok, pos = first, PROMPT_LEN
+    for _ in range(args.warmup):
+        tok = eng.run(tok, pos, True); pos += 1
+    tok, pos = first, PROMPT_LEN
+    barrier()
+    t0 = time.perf_counter()
+    for _ in range(K):
+        tok = eng.run(tok, pos, True); pos += 1
+    torch.cuda.synchronize()
+    e2e_s = time.perf_counter() - t0
+    if dist is not None:
+        t = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        e2e_s = float(t.item())
+
+    if rank != 0:
+        eng.close()
+        if dist is not None:
+            dist.barrier()
+            dist.destroy_process_group()
+        return
+
+    peak, peak_kind = measured_peaks()
+    mid = PROMPT_LEN + K // 2
+    step_bytes = sum(eng.bytes_per_step(PROMPT_LEN + i) for i in range(K)) / K
+    value = world * K / (ms / 1000.0)
+    out = {
+        "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": args.warmup,
+        "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "int8xfp4->int32,f32", "data": "synthetic",
+        "config": {"workload": WORKLOAD, "arch": "24 layers, d 2880, 64/8 heads x 64, 32 experts top-4, vocab 201088",
+                   "positions": [PROMPT_LEN, PROMPT_LEN + K], "parallelism": f"replicas x{world}" if world > 1 else "single GPU",
+                   "l2": "inputs larger than L2 (2.66 GB of weights streamed per step)"},
+        "e2e": {"value": world * K / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 4},
+        "gpu_launches": K * eng.launches_per_step(True),
+        "clocks": clocks,
+        "step_roofline": {"bound": "hbm", "bytes_per_step": step_bytes, "achieved": step_bytes / (ms / K) / 1e6, "peak": peak,
+                          "unit": "GB/s", "frac": step_bytes / (ms / K) / 1e6 / peak, "peak_kind": peak_kind,
+                          "frac_of_8TBs": step_bytes / (ms / K) / 1e6 / 8000.0},
+    }
+    if not args.no_stages:
+        st = eng.stage_times(mid, reps=10)
+        tot = sum(t * n for _, t, _, n in st)
+        stages = [{"kernel": nm, "launches_per_step": n, "us_per_launch": 1000 * t, "share": t * n / tot,
+                   "bytes_per_launch": by, "gbs": by / t / 1e6 if t > 0 else 0.0} for nm, t, by, n in st]
+        out["stages"] = stages
+        top = max(stages, key=lambda s: s["share"])
+        out["roofline"] = {"bound": "hbm", "kernel": top["kernel"], "achieved": top["gbs"], "peak": peak, "unit": "GB/s",
+                           "frac": top["gbs"] / peak, "traffic": None, "peak_kind": peak_kind,
+                           "bytes_per_launch": top["bytes_per_launch"], "us_per_launch": top["us_per_launch"]}
+    if world == 1 and not args.no_cpu:
+        cpu, parity = cpu_baseline_and_parity(toks, first, 16)
+        out["cpu_baseline"] = cpu
+        out["parity"] = parity
+    eng.close()
+    print(json.dumps(out), flush=True)
+    if dist is not None:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()

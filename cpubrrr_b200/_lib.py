@@ -1,0 +1,86 @@
+"""ctypes binding of libbrrr.so — every symbol declared in include/brrr.h."""
+import ctypes as C
+import os
+
+HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(HERE, "libbrrr.so")
+
+
+class BrrrError(RuntimeError):
+    pass
+
+
+class Cfg(C.Structure):
+    """brrr_cfg: the keys of the data directory's config.txt."""
+    _fields_ = [(n, C.c_int32) for n in ("n_embd", "n_layer", "n_head", "n_head_kv", "head_dim", "n_expert",
+                                         "n_expert_used", "n_ff_exp", "sliding_window", "n_vocab")] + [
+        ("rope_freq_base", C.c_float), ("rms_eps", C.c_float)]
+
+
+_P = C.c_void_p
+_I = C.c_int
+# name -> (restype, argtypes); the authoritative list of exported entry points
+SIGNATURES = {
+    "brrr_strerror": (C.c_char_p, [_I]),
+    "brrr_last_cuda_error": (C.c_char_p, []),
+    "brrr_model_open": (_I, [C.c_char_p, C.c_char_p, _I, C.POINTER(_P)]),
+    "brrr_model_open_synth": (_I, [C.POINTER(Cfg), C.c_uint64, _I, C.POINTER(_P)]),
+    "brrr_model_cfg": (_I, [_P, C.POINTER(Cfg)]),
+    "brrr_model_close": (None, [_P]),
+    "brrr_forward": (_I, [_P, C.c_uint32, C.c_uint32, _I, C.POINTER(C.c_uint32)]),
+    "brrr_forward_tile": (_I, [_P, _P, C.c_uint32, C.c_uint32, _I, C.POINTER(C.c_uint32)]),
+    "brrr_decode": (_I, [_P, C.c_uint32, C.c_uint32, C.c_uint32, _P]),
+    "brrr_decode_enqueue": (_I, [_P, C.c_uint32, C.c_uint32, C.c_uint32]),
+    "brrr_decode_wait": (_I, [_P, C.c_uint32, _P]),
+    "brrr_logits": (_I, [_P, _P]),
+    "brrr_hidden": (_I, [_P, _P]),
+    "brrr_forward_trace": (_I, [_P, C.c_uint32, C.c_uint32, _P]),
+    "brrr_model_stream": (_P, [_P]),
+    "brrr_model_launches_per_step": (_I, [_P, _I]),
+    "brrr_model_bytes_per_step": (C.c_uint64, [_P, C.c_uint32]),
+    "brrr_stage_count": (_I, []),
+    "brrr_stage_name": (C.c_char_p, [_I]),
+    "brrr_stage_time": (_I, [_P, _I, C.c_uint32, _I, C.POINTER(C.c_float), C.POINTER(C.c_uint64), C.POINTER(_I)]),
+    "brrr_quant_q8": (_I, [_P, _I, _P, _P, _P]),
+    "brrr_rmsnorm_quant": (_I, [_P, _P, C.c_float, _I, _P, _P, _P, _P]),
+    "brrr_q8mat_from_bf16": (_I, [_P, _I, _I, C.POINTER(_P), _P]),
+    "brrr_q8mat_export": (_I, [_P, _P, _P, _P]),
+    "brrr_q8mat_free": (None, [_P]),
+    "brrr_q8_matvec": (_I, [_P, _P, _P, _P, _P]),
+    "brrr_mxmat_from_gguf": (_I, [_P, _I, _I, C.POINTER(_P), _P]),
+    "brrr_mxmat_free": (None, [_P]),
+    "brrr_mx_matvec": (_I, [_P, _I, _I, _P, _P, _P, _P, _P]),
+    "brrr_router_topk": (_I, [_P, _P, _P, _I, _I, _I, _P, _P, _P, _P]),
+    "brrr_swiglu_quant": (_I, [_P, _I, _I, _P, _P, _P]),
+    "brrr_attn_decode": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P, _P]),
+    "brrr_rope_table": (_I, [C.POINTER(Cfg), _P]),
+    "brrr_moe_ffn_step": (_I, [_P, _I, _P, _P, _P, _P]),
+    "brrr_synth_tensor": (_I, [C.c_uint64, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint64, _P, _P]),
+    "brrr_expf": (_I, [_P, _I, _P, _P]),
+}
+
+_lib = None
+
+
+def lib():
+    """Load libbrrr.so (built by `python -m cpubrrr_b200.build`). Raises if it is missing: the
+    engine has no other execution path."""
+    global _lib
+    if _lib is None:
+        if not os.path.exists(LIB_PATH):
+            raise BrrrError(f"{LIB_PATH} is missing: build it with `python -m cpubrrr_b200.build`")
+        L = C.CDLL(LIB_PATH)
+        for name, (res, args) in SIGNATURES.items():
+            fn = getattr(L, name)      # AttributeError if the library does not export it
+            fn.restype = res
+            fn.argtypes = args
+        _lib = L
+    return _lib
+
+
+def check(status, what=""):
+    if status != 0:
+        L = lib()
+        msg = L.brrr_strerror(status).decode()
+        detail = L.brrr_last_cuda_error().decode()
+        raise BrrrError(f"{what}: {msg}" + (f" ({detail})" if detail else ""))

@@ -1,0 +1,45 @@
+// Host-callable launchers of the decode kernels.  Every launcher only enqueues work on the given
+// stream (capturable into a CUDA graph) and reports launch-configuration errors through
+// cudaGetLastError at the call site.
+#pragma once
+#include "brrr_dev.cuh"
+
+namespace brrr {
+
+// ---- elementwise / small stages (kernels_small.cu)
+void launch_quant_q8(const float *x, int n, int8_t *q, float *s, cudaStream_t st);
+void launch_rmsnorm_quant(const float *x, const float *w, float eps, int n, float *xn, int8_t *q, float *s, cudaStream_t st);
+void launch_embed(const uint16_t *embd, int d, const DevState *state, float *x, cudaStream_t st);
+void launch_swiglu_quant(const float *gu, int topk, int d, int8_t *hq, float *hs, cudaStream_t st);
+void launch_finish_token(DevState *state, cudaStream_t st);
+void launch_expf(const float *x, int n, float *y, cudaStream_t st);
+void launch_synth(uint64_t seed, uint32_t layer, uint32_t kind, uint32_t type, uint64_t nelems, void *out, cudaStream_t st);
+
+// ---- Q8 matrices (kernels_q8.cu)
+void launch_q8_pack(const uint16_t *w_bf16, int rows_src, int row0_dst, Q8Dev m, cudaStream_t st);
+void launch_q8_export(Q8Dev m, int8_t *q, float *s, cudaStream_t st);
+enum { Q8_EPI_PLAIN = 0, Q8_EPI_BIAS = 1, Q8_EPI_RESID_BIAS = 2, Q8_EPI_HEAD = 3 };
+void launch_q8_gemv(Q8Dev m, const int8_t *xq, const float *xs, const float *bias, float *y, int epi, DevState *state, cudaStream_t st);
+
+// ---- MXFP4 matrices (kernels_mx.cu)
+void launch_mx_pack(const uint8_t *raw, MxDev m, cudaStream_t st);
+void launch_mx_gemv(MxDev m, int row0, int nrows, const int8_t *xq, const float *xs, float *y, int32_t *blockdots, cudaStream_t st);
+void launch_gate_up(MxDev gate, MxDev up, const float *gate_b, const float *up_b, const int32_t *top, int topk, int d,
+                    const int8_t *xq, const float *xs, float *gu, cudaStream_t st);
+void launch_down_combine(MxDev down, const float *down_b, const int32_t *top, const float *wts, int topk, int d,
+                         const int8_t *hq, const float *hs, float *x, cudaStream_t st);
+
+// ---- router (kernels_router.cu)
+// x_in is the residual stream when norm_w != nullptr (RMSNorm applied first) or an already
+// normalised vector otherwise.  xq_out/xs_out nullable.
+void launch_ffn_in(const float *x_in, const float *norm_w, float eps, int d, int8_t *xq_out, float *xs_out,
+                   const float *W, const float *b, int ne, int topk, float *logits, int32_t *top, float *wts,
+                   unsigned int *counter, cudaStream_t st);
+int ffn_in_init();   // one-time kernel attribute set-up; returns cudaError_t
+
+// ---- attention (kernels_attn.cu)
+// pos is read from state when state != nullptr, else pos_val.  window = 0 means full attention.
+void launch_attn_decode(const float *qkv, float *kc, float *vc, const float *rope, const float *sinks, int nh, int nkv,
+                        const DevState *state, int pos_val, int window, float *ao, int8_t *aq, float *as, cudaStream_t st);
+
+}  // namespace brrr

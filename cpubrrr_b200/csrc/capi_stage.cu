@@ -1,0 +1,119 @@
+// Stage-level C ABI (include/brrr.h): device pointers in, device pointers out.  Each function
+// launches the same kernel the forward pass uses for that stage.
+#include "../../include/brrr.h"
+#include "brrr_kernels.h"
+
+#include <cstdio>
+
+using namespace brrr;
+
+namespace {
+int check_launch() { return cudaGetLastError() == cudaSuccess ? BRRR_OK : BRRR_ERR_CUDA; }
+}  // namespace
+
+struct brrr_q8mat { Q8Dev m; };
+struct brrr_mxmat { MxDev m; };
+
+extern "C" int brrr_quant_q8(const float *d_x, int n, int8_t *d_q, float *d_s, void *stream) {
+    if (!d_x || !d_q || !d_s || n <= 0 || n % 32) return BRRR_ERR_ARG;
+    launch_quant_q8(d_x, n, d_q, d_s, (cudaStream_t)stream);
+    return check_launch();
+}
+
+extern "C" int brrr_rmsnorm_quant(const float *d_x, const float *d_w, float eps, int n, float *d_xn, int8_t *d_q, float *d_s, void *stream) {
+    if (!d_x || !d_w || !d_q || !d_s || n <= 0 || n % 32 || n > 8192) return BRRR_ERR_ARG;
+    launch_rmsnorm_quant(d_x, d_w, eps, n, d_xn, d_q, d_s, (cudaStream_t)stream);
+    return check_launch();
+}
+
+extern "C" int brrr_q8mat_from_bf16(const uint16_t *d_w, int rows, int cols, brrr_q8mat **out, void *stream) {
+    if (!d_w || !out || rows <= 0 || rows % 4 || cols <= 0 || cols % 64) return BRRR_ERR_ARG;
+    brrr_q8mat *q = new brrr_q8mat();
+    q->m.rows = rows; q->m.cols = cols;
+    if (cudaMalloc(&q->m.wq, (size_t)rows * cols) != cudaSuccess) { delete q; return BRRR_ERR_NOMEM; }
+    if (cudaMalloc(&q->m.ws, (size_t)rows * (cols / 32) * 4) != cudaSuccess) { cudaFree(q->m.wq); delete q; return BRRR_ERR_NOMEM; }
+    launch_q8_pack(d_w, rows, 0, q->m, (cudaStream_t)stream);
+    *out = q;
+    return check_launch();
+}
+
+extern "C" int brrr_q8mat_export(const brrr_q8mat *m, int8_t *d_q, float *d_s, void *stream) {
+    if (!m || !d_q || !d_s) return BRRR_ERR_ARG;
+    launch_q8_export(m->m, d_q, d_s, (cudaStream_t)stream);
+    return check_launch();
+}
+
+extern "C" void brrr_q8mat_free(brrr_q8mat *m) {
+    if (!m) return;
+    cudaFree(m->m.wq); cudaFree(m->m.ws);
+    delete m;
+}
+
+extern "C" int brrr_q8_matvec(const brrr_q8mat *w, const int8_t *d_xq, const float *d_xs, float *d_y, void *stream) {
+    if (!w || !d_xq || !d_xs || !d_y) return BRRR_ERR_ARG;
+    launch_q8_gemv(w->m, d_xq, d_xs, nullptr, d_y, Q8_EPI_PLAIN, nullptr, (cudaStream_t)stream);
+    return check_launch();
+}
+
+extern "C" int brrr_mxmat_from_gguf(const uint8_t *d_raw, int rows, int blocks, brrr_mxmat **out, void *stream) {
+    if (!d_raw || !out || rows <= 0 || rows % 8 || blocks <= 0 || blocks % 2) return BRRR_ERR_ARG;
+    brrr_mxmat *x = new brrr_mxmat();
+    x->m.rows = rows; x->m.blocks = blocks;
+    if (cudaMalloc(&x->m.nib, (size_t)rows * blocks * 16) != cudaSuccess) { delete x; return BRRR_ERR_NOMEM; }
+    if (cudaMalloc(&x->m.exps, (size_t)rows * blocks) != cudaSuccess) { cudaFree(x->m.nib); delete x; return BRRR_ERR_NOMEM; }
+    launch_mx_pack(d_raw, x->m, (cudaStream_t)stream);
+    *out = x;
+    return check_launch();
+}
+
+extern "C" void brrr_mxmat_free(brrr_mxmat *m) {
+    if (!m) return;
+    cudaFree(m->m.nib); cudaFree(m->m.exps);
+    delete m;
+}
+
+extern "C" int brrr_mx_matvec(const brrr_mxmat *w, int row0, int nrows, const int8_t *d_xq, const float *d_xs, float *d_y, int32_t *d_blockdots, void *stream) {
+    if (!w || !d_xq || !d_xs || !d_y || row0 < 0 || nrows <= 0 || row0 + nrows > w->m.rows) return BRRR_ERR_ARG;
+    launch_mx_gemv(w->m, row0, nrows, d_xq, d_xs, d_y, d_blockdots, (cudaStream_t)stream);
+    return check_launch();
+}
+
+extern "C" int brrr_router_topk(const float *d_w, const float *d_b, const float *d_xn, int ne, int d, int topk,
+                                float *d_logits, int32_t *d_top, float *d_wts, void *stream) {
+    if (!d_w || !d_xn || !d_logits || !d_top || !d_wts || ne <= 0 || d <= 0 || d > 8192 || topk <= 0 || topk > 8 || topk > ne) return BRRR_ERR_ARG;
+    static unsigned int *counter = nullptr;   // arrival counter of the router CTAs (self-resetting)
+    if (!counter) {
+        if (ffn_in_init() != 0) return BRRR_ERR_CUDA;
+        if (cudaMalloc(&counter, sizeof(unsigned int)) != cudaSuccess) return BRRR_ERR_NOMEM;
+        if (cudaMemset(counter, 0, sizeof(unsigned int)) != cudaSuccess) return BRRR_ERR_CUDA;
+    }
+    launch_ffn_in(d_xn, nullptr, 0.0f, d, nullptr, nullptr, d_w, d_b, ne, topk, d_logits, d_top, d_wts, counter, (cudaStream_t)stream);
+    return check_launch();
+}
+
+extern "C" int brrr_swiglu_quant(const float *d_gu, int topk, int d, int8_t *d_hq, float *d_hs, void *stream) {
+    if (!d_gu || !d_hq || !d_hs || topk <= 0 || d <= 0 || d % 32) return BRRR_ERR_ARG;
+    launch_swiglu_quant(d_gu, topk, d, d_hq, d_hs, (cudaStream_t)stream);
+    return check_launch();
+}
+
+extern "C" int brrr_attn_decode(const float *d_qkv, float *d_kc, float *d_vc, const float *d_rope, const float *d_sinks,
+                                int n_head, int n_head_kv, int pos, int start, float *d_ao, int8_t *d_aq, float *d_as, void *stream) {
+    if (!d_qkv || !d_kc || !d_vc || !d_rope || !d_sinks || !d_ao || !d_aq || !d_as) return BRRR_ERR_ARG;
+    if (n_head <= 0 || n_head_kv <= 0 || n_head % n_head_kv || pos < 0 || pos >= BRRR_MAXSEQ || start < 0 || start > pos) return BRRR_ERR_ARG;
+    int window = start > 0 ? pos - start + 1 : 0;
+    launch_attn_decode(d_qkv, d_kc, d_vc, d_rope, d_sinks, n_head, n_head_kv, nullptr, pos, window, d_ao, d_aq, d_as, (cudaStream_t)stream);
+    return check_launch();
+}
+
+extern "C" int brrr_synth_tensor(uint64_t seed, uint32_t layer, uint32_t kind, uint32_t type, uint64_t nelems, void *d_out, void *stream) {
+    if (!d_out || (type != 0 && type != 30 && type != 39) || (type == 39 && nelems % 32)) return BRRR_ERR_ARG;
+    launch_synth(seed, layer, kind, type, nelems, d_out, (cudaStream_t)stream);
+    return check_launch();
+}
+
+extern "C" int brrr_expf(const float *d_x, int n, float *d_y, void *stream) {
+    if (!d_x || !d_y || n <= 0) return BRRR_ERR_ARG;
+    launch_expf(d_x, n, d_y, (cudaStream_t)stream);
+    return check_launch();
+}

@@ -1,0 +1,642 @@
+// Host side of the engine: data-directory loader, synthetic-model builder, the decode step as a
+// CUDA graph, and the model-level C ABI (include/brrr.h).
+//
+// It mirrors the reference's host program for this path (src/bin/engine_gpt2.rs): load_cfg
+// (64-80), the manifest/mmap loader (1276-1285), the per-layer weight preparation (1290-1315),
+// the activation buffers (1340-1347) and run() (1379-1385) — with the 12-worker barrier
+// scheduler (619-687, 1354-1378) replaced by one CUDA graph launch per token.
+#include "../../include/brrr.h"
+#include "brrr_kernels.h"
+#include "brrr_synth.h"
+
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <algorithm>
+#include <fcntl.h>
+#include <map>
+#include <string>
+#include <sys/mman.h>
+#include <sys/stat.h>
+#include <unistd.h>
+#include <vector>
+
+using namespace brrr;
+
+static thread_local char g_cuda_err[512] = "";
+
+#define CU(call)                                                                                         \
+    do {                                                                                                 \
+        cudaError_t _e = (call);                                                                         \
+        if (_e != cudaSuccess) {                                                                         \
+            snprintf(g_cuda_err, sizeof g_cuda_err, "%s:%d %s: %s", __FILE__, __LINE__, #call, cudaGetErrorString(_e)); \
+            return BRRR_ERR_CUDA;                                                                        \
+        }                                                                                                \
+    } while (0)
+
+extern "C" const char *brrr_last_cuda_error(void) { return g_cuda_err; }
+extern "C" const char *brrr_strerror(int s) {
+    switch (s) {
+    case BRRR_OK: return "ok";
+    case BRRR_ERR_ARG: return "bad argument or unsupported shape";
+    case BRRR_ERR_IO: return "data directory or blob unreadable or malformed";
+    case BRRR_ERR_CUDA: return "CUDA call failed";
+    case BRRR_ERR_NOMEM: return "out of memory";
+    case BRRR_ERR_RANGE: return "position, token or count out of range";
+    case BRRR_ERR_STATE: return "call not valid in the current state";
+    }
+    return "unknown status";
+}
+
+namespace {
+
+struct Layer {
+    float *attn_norm = nullptr, *ffn_norm = nullptr;
+    Q8Dev wqkv{}, wo{};
+    float *bqkv = nullptr, *bo = nullptr, *sinks = nullptr, *ginp = nullptr, *ginp_b = nullptr;
+    MxDev gate{}, up{}, down{};
+    float *gate_b = nullptr, *up_b = nullptr, *down_b = nullptr;
+    float *kc = nullptr, *vc = nullptr;
+};
+
+// Where raw GGUF-format tensor bytes come from: a mapped blob or the synthetic generator.
+struct Source {
+    bool synth = false;
+    uint64_t seed = 0;
+    const uint8_t *blob = nullptr;
+    size_t blob_len = 0;
+    struct Ent { uint32_t type; size_t off, nel; };
+    std::map<std::string, Ent> idx;
+};
+
+const char *kind_name(int kind) {
+    switch (kind) {
+    case BRRR_T_ATTN_NORM: return "attn_norm.weight"; case BRRR_T_FFN_NORM: return "ffn_norm.weight";
+    case BRRR_T_WQ: return "attn_q.weight"; case BRRR_T_WK: return "attn_k.weight";
+    case BRRR_T_WV: return "attn_v.weight"; case BRRR_T_WO: return "attn_out.weight";
+    case BRRR_T_BQ: return "attn_q.bias"; case BRRR_T_BK: return "attn_k.bias";
+    case BRRR_T_BV: return "attn_v.bias"; case BRRR_T_BO: return "attn_out.bias";
+    case BRRR_T_SINKS: return "attn_sinks"; case BRRR_T_ROUTER_W: return "ffn_gate_inp.weight";
+    case BRRR_T_ROUTER_B: return "ffn_gate_inp.bias"; case BRRR_T_GATE: return "ffn_gate_exps.weight";
+    case BRRR_T_UP: return "ffn_up_exps.weight"; case BRRR_T_DOWN: return "ffn_down_exps.weight";
+    case BRRR_T_GATE_B: return "ffn_gate_exps.bias"; case BRRR_T_UP_B: return "ffn_up_exps.bias";
+    case BRRR_T_DOWN_B: return "ffn_down_exps.bias";
+    case BRRR_T_TOK_EMBD: return "token_embd.weight"; case BRRR_T_OUT_NORM: return "output_norm.weight";
+    case BRRR_T_OUTPUT: return "output.weight";
+    }
+    return "?";
+}
+
+size_t type_bytes(uint32_t type, size_t nel) {
+    switch (type) {
+    case 0: return nel * 4;
+    case 30: return nel * 2;
+    case 39: return nel / 32 * 17;
+    }
+    return 0;
+}
+
+}  // namespace
+
+struct brrr_model {
+    brrr_cfg cfg{};
+    int device = 0;
+    cudaStream_t stream = nullptr;
+    std::vector<Layer> L;
+    float *out_norm = nullptr;
+    Q8Dev head{};
+    uint16_t *tok_embd = nullptr;
+    float *rope = nullptr;
+    // activations
+    float *x = nullptr, *qkv = nullptr, *ao = nullptr, *gu = nullptr, *rlogits = nullptr, *logits = nullptr;
+    float *xs = nullptr, *as = nullptr, *hs = nullptr, *wts = nullptr;
+    int8_t *xq = nullptr, *aq = nullptr, *hq = nullptr;
+    int32_t *top = nullptr;
+    DevState *st = nullptr;
+    // host staging (pinned)
+    uint32_t *h_in = nullptr, *h_out = nullptr;
+    cudaGraphExec_t g_head = nullptr, g_nohead = nullptr;
+    int launches_head = 0, launches_nohead = 0;
+    uint32_t pending_base = 0;   // n_out at the start of the enqueued decode run
+    std::vector<void *> allocs;
+
+    template <typename T> int alloc(T **p, size_t n) {
+        void *v = nullptr;
+        if (cudaMalloc(&v, n ? n * sizeof(T) : 16) != cudaSuccess) {
+            snprintf(g_cuda_err, sizeof g_cuda_err, "cudaMalloc of %zu bytes failed", n * sizeof(T));
+            return BRRR_ERR_NOMEM;
+        }
+        allocs.push_back(v);
+        *p = (T *)v;
+        return BRRR_OK;
+    }
+};
+
+namespace {
+
+#define TRY(expr) do { int _s = (expr); if (_s != BRRR_OK) return _s; } while (0)
+
+// Fetch one tensor's raw bytes into device scratch.
+int fetch(brrr_model *m, const Source &s, uint32_t layer, int kind, uint32_t type, size_t nel, void *scratch) {
+    if (s.synth) {
+        launch_synth(s.seed, layer, kind, type, nel, scratch, m->stream);
+        CU(cudaGetLastError());
+        return BRRR_OK;
+    }
+    char name[160];
+    if (layer == BRRR_L_GLOBAL) snprintf(name, sizeof name, "%s", kind_name(kind));
+    else snprintf(name, sizeof name, "blk.%u.%s", layer, kind_name(kind));
+    auto it = s.idx.find(name);
+    if (it == s.idx.end()) { snprintf(g_cuda_err, sizeof g_cuda_err, "missing tensor %s", name); return BRRR_ERR_IO; }
+    if (it->second.type != type || it->second.nel != nel) { snprintf(g_cuda_err, sizeof g_cuda_err, "tensor %s: type/size mismatch", name); return BRRR_ERR_IO; }
+    size_t bytes = type_bytes(type, nel);
+    if (it->second.off + bytes > s.blob_len) { snprintf(g_cuda_err, sizeof g_cuda_err, "tensor %s exceeds blob", name); return BRRR_ERR_IO; }
+    CU(cudaMemcpyAsync(scratch, s.blob + it->second.off, bytes, cudaMemcpyHostToDevice, m->stream));
+    CU(cudaStreamSynchronize(m->stream));
+    return BRRR_OK;
+}
+
+int load_f32(brrr_model *m, const Source &s, uint32_t layer, int kind, size_t n, float **out) {
+    TRY(m->alloc(out, n));
+    return fetch(m, s, layer, kind, 0, n, *out);
+}
+
+int alloc_q8(brrr_model *m, int rows, int cols, Q8Dev *q) {
+    q->rows = rows; q->cols = cols;
+    TRY(m->alloc(&q->wq, (size_t)rows * cols));
+    TRY(m->alloc(&q->ws, (size_t)rows * (cols / 32)));
+    return BRRR_OK;
+}
+
+int load_q8_part(brrr_model *m, const Source &s, uint32_t layer, int kind, int rows, int row0, Q8Dev q, void *scratch) {
+    TRY(fetch(m, s, layer, kind, 30, (size_t)rows * q.cols, scratch));
+    launch_q8_pack((const uint16_t *)scratch, rows, row0, q, m->stream);
+    CU(cudaGetLastError());
+    return BRRR_OK;
+}
+
+int load_mx(brrr_model *m, const Source &s, uint32_t layer, int kind, int rows, int blocks, MxDev *x, void *scratch) {
+    x->rows = rows; x->blocks = blocks;
+    TRY(m->alloc(&x->nib, (size_t)rows * blocks * 16));
+    TRY(m->alloc(&x->exps, (size_t)rows * blocks));
+    TRY(fetch(m, s, layer, kind, 39, (size_t)rows * blocks * 32, scratch));
+    launch_mx_pack((const uint8_t *)scratch, *x, m->stream);
+    CU(cudaGetLastError());
+    return BRRR_OK;
+}
+
+void rope_table_host(const brrr_cfg &c, float *tab) {
+    // YaRN table (src/bin/engine_gpt2.rs:536-572): factor 32, original context 4096, beta 32 / 1,
+    // mscale 1 + 0.1 ln 32; entries are the rotation of (1, 0), i.e. (cos*mscale, sin*mscale).
+    int hd = c.head_dim, half = hd / 2;
+    float base = c.rope_freq_base;
+    const float PI = 3.14159265358979323846f;
+    float lb = logf(base);
+    float fd32 = (float)hd * logf(4096.0f / (32.0f * 2.0f * PI)) / (2.0f * lb);
+    float fd1 = (float)hd * logf(4096.0f / (1.0f * 2.0f * PI)) / (2.0f * lb);
+    float low = floorf(fd32); if (low < 0.0f) low = 0.0f;
+    float high = ceilf(fd1); if (high > (float)hd - 1.0f) high = (float)hd - 1.0f;
+    float mscale = 1.0f + 0.1f * logf(32.0f);
+    float den = high - low; if (den < 0.001f) den = 0.001f;
+    for (int pos = 0; pos < BRRR_MAXSEQ; pos++)
+        for (int i = 0; i < half; i++) {
+            float theta_ex = (float)pos * powf(base, -(2.0f * (float)i) / (float)hd);
+            float theta_in = theta_ex / 32.0f;
+            float y = ((float)i - low) / den;
+            if (y < 0.0f) y = 0.0f;
+            if (y > 1.0f) y = 1.0f;
+            float mix = 1.0f - y;
+            float theta = theta_in * (1.0f - mix) + theta_ex * mix;
+            tab[((size_t)pos * half + i) * 2] = cosf(theta) * mscale;
+            tab[((size_t)pos * half + i) * 2 + 1] = sinf(theta) * mscale;
+        }
+}
+
+int check_cfg(const brrr_cfg &c) {
+    if (c.n_embd <= 0 || c.n_embd % 64 || c.n_embd > 8192) return BRRR_ERR_ARG;
+    if (c.n_ff_exp != c.n_embd) return BRRR_ERR_ARG;                     // engine_gpt2.rs:73
+    if (c.head_dim != 64) return BRRR_ERR_ARG;                           // engine_gpt2.rs:74
+    if (c.n_head <= 0 || c.n_head_kv <= 0 || c.n_head % c.n_head_kv) return BRRR_ERR_ARG;
+    if (c.n_expert <= 0 || c.n_expert_used <= 0 || c.n_expert_used > 8 || c.n_expert_used > c.n_expert) return BRRR_ERR_ARG;
+    if (c.n_vocab <= 0 || c.n_vocab % 4 || c.n_layer <= 0) return BRRR_ERR_ARG;
+    if (c.sliding_window <= 0) return BRRR_ERR_ARG;
+    return BRRR_OK;
+}
+
+// The decode step, enqueued kernel by kernel (captured into a graph, or run directly by the
+// trace path).  Stage order and data flow follow forward_worker (engine_gpt2.rs:751-934).
+enum { ST_EMBED = 0, ST_ATTN_NORM, ST_QKV, ST_ATTN, ST_OPROJ, ST_FFN_IN, ST_GATE_UP, ST_SWIGLU, ST_DOWN, ST_HEAD_NORM, ST_HEAD, ST_FINISH, ST_COUNT };
+const char *const kStageNames[ST_COUNT] = {"embed", "attn_norm_quant", "qkv_gemv", "attention", "oproj_gemv", "ffn_norm_router",
+                                           "gate_up_mxfp4", "swiglu_quant", "down_combine_mxfp4", "head_norm_quant", "head_gemv_argmax", "finish_token"};
+
+int enqueue_step(brrr_model *m, bool want, float *trace_dev, int *nlaunch, unsigned mask = ~0u) {
+    const brrr_cfg &c = m->cfg;
+    const int d = c.n_embd, nh = c.n_head, nkv = c.n_head_kv, topk = c.n_expert_used;
+    cudaStream_t s = m->stream;
+    int n = 0;
+    auto on = [&](int st) { if (mask & (1u << st)) { n++; return true; } return false; };
+    if (on(ST_EMBED)) launch_embed(m->tok_embd, d, m->st, m->x, s);
+    if (trace_dev) CU(cudaMemcpyAsync(trace_dev, m->x, d * sizeof(float), cudaMemcpyDeviceToDevice, s));
+    for (int il = 0; il < c.n_layer; il++) {
+        Layer &ly = m->L[il];
+        if (on(ST_ATTN_NORM)) launch_rmsnorm_quant(m->x, ly.attn_norm, c.rms_eps, d, nullptr, m->xq, m->xs, s);
+        if (on(ST_QKV)) launch_q8_gemv(ly.wqkv, m->xq, m->xs, ly.bqkv, m->qkv, Q8_EPI_BIAS, m->st, s);
+        int window = ((il + 1) % 2 != 0) ? c.sliding_window : 0;         // even layer index: sliding window
+        if (window >= BRRR_MAXSEQ) window = 0;
+        if (on(ST_ATTN)) launch_attn_decode(m->qkv, ly.kc, ly.vc, m->rope, ly.sinks, nh, nkv, m->st, 0, window, m->ao, m->aq, m->as, s);
+        if (on(ST_OPROJ)) launch_q8_gemv(ly.wo, m->aq, m->as, ly.bo, m->x, Q8_EPI_RESID_BIAS, m->st, s);
+        if (on(ST_FFN_IN)) launch_ffn_in(m->x, ly.ffn_norm, c.rms_eps, d, m->xq, m->xs, ly.ginp, ly.ginp_b, c.n_expert, topk, m->rlogits, m->top, m->wts,
+                                         &m->st->router_done, s);
+        if (on(ST_GATE_UP)) launch_gate_up(ly.gate, ly.up, ly.gate_b, ly.up_b, m->top, topk, d, m->xq, m->xs, m->gu, s);
+        if (on(ST_SWIGLU)) launch_swiglu_quant(m->gu, topk, d, m->hq, m->hs, s);
+        if (on(ST_DOWN)) launch_down_combine(ly.down, ly.down_b, m->top, m->wts, topk, d, m->hq, m->hs, m->x, s);
+        if (trace_dev) CU(cudaMemcpyAsync(trace_dev + (size_t)(il + 1) * d, m->x, d * sizeof(float), cudaMemcpyDeviceToDevice, s));
+    }
+    if (want) {
+        if (on(ST_HEAD_NORM)) launch_rmsnorm_quant(m->x, m->out_norm, c.rms_eps, d, nullptr, m->xq, m->xs, s);
+        if (on(ST_HEAD)) launch_q8_gemv(m->head, m->xq, m->xs, nullptr, m->logits, Q8_EPI_HEAD, m->st, s);
+        if (on(ST_FINISH)) launch_finish_token(m->st, s);
+    }
+    CU(cudaGetLastError());
+    if (nlaunch) *nlaunch = n;
+    return BRRR_OK;
+}
+
+int capture(brrr_model *m, bool want, cudaGraphExec_t *out, int *nlaunch, unsigned mask = ~0u) {
+    cudaGraph_t g = nullptr;
+    CU(cudaStreamBeginCapture(m->stream, cudaStreamCaptureModeThreadLocal));
+    int s = enqueue_step(m, want, nullptr, nlaunch, mask);
+    cudaError_t e = cudaStreamEndCapture(m->stream, &g);
+    if (s != BRRR_OK) { if (g) cudaGraphDestroy(g); return s; }
+    CU(e);
+    CU(cudaGraphInstantiate(out, g, 0));
+    CU(cudaGraphDestroy(g));
+    return BRRR_OK;
+}
+
+int build_model(brrr_model *m, const Source &src) {
+    const brrr_cfg &c = m->cfg;
+    const int d = c.n_embd, nh = c.n_head, nkv = c.n_head_kv, hd = c.head_dim, nb = d / 32, ne = c.n_expert, topk = c.n_expert_used;
+    CU(cudaSetDevice(m->device));
+    CU(cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking));
+    { int e = ffn_in_init(); if (e) { snprintf(g_cuda_err, sizeof g_cuda_err, "ffn_in_init: %s", cudaGetErrorString((cudaError_t)e)); return BRRR_ERR_CUDA; } }
+
+    // scratch for one raw tensor: the largest of the bf16 matrices and one MXFP4 expert tensor
+    size_t scratch_bytes = std::max({(size_t)c.n_vocab * d * 2, (size_t)ne * d * nb * 17, (size_t)nh * hd * d * 2});
+    void *scratch = nullptr;
+    if (cudaMalloc(&scratch, scratch_bytes) != cudaSuccess) return BRRR_ERR_NOMEM;
+    struct Guard { void *p; ~Guard() { cudaFree(p); } } guard{scratch};
+
+    m->L.resize(c.n_layer);
+    const int qkv_rows = (nh + 2 * nkv) * hd;
+    for (int il = 0; il < c.n_layer; il++) {
+        Layer &ly = m->L[il];
+        TRY(load_f32(m, src, il, BRRR_T_ATTN_NORM, d, &ly.attn_norm));
+        TRY(load_f32(m, src, il, BRRR_T_FFN_NORM, d, &ly.ffn_norm));
+        TRY(alloc_q8(m, qkv_rows, d, &ly.wqkv));
+        TRY(load_q8_part(m, src, il, BRRR_T_WQ, nh * hd, 0, ly.wqkv, scratch));
+        TRY(load_q8_part(m, src, il, BRRR_T_WK, nkv * hd, nh * hd, ly.wqkv, scratch));
+        TRY(load_q8_part(m, src, il, BRRR_T_WV, nkv * hd, (nh + nkv) * hd, ly.wqkv, scratch));
+        TRY(alloc_q8(m, d, nh * hd, &ly.wo));
+        TRY(load_q8_part(m, src, il, BRRR_T_WO, d, 0, ly.wo, scratch));
+        TRY(m->alloc(&ly.bqkv, (size_t)qkv_rows));
+        TRY(fetch(m, src, il, BRRR_T_BQ, 0, nh * hd, ly.bqkv));
+        TRY(fetch(m, src, il, BRRR_T_BK, 0, nkv * hd, ly.bqkv + nh * hd));
+        TRY(fetch(m, src, il, BRRR_T_BV, 0, nkv * hd, ly.bqkv + (nh + nkv) * hd));
+        TRY(load_f32(m, src, il, BRRR_T_BO, d, &ly.bo));
+        TRY(load_f32(m, src, il, BRRR_T_SINKS, nh, &ly.sinks));
+        TRY(load_f32(m, src, il, BRRR_T_ROUTER_W, (size_t)ne * d, &ly.ginp));
+        TRY(load_f32(m, src, il, BRRR_T_ROUTER_B, ne, &ly.ginp_b));
+        TRY(load_mx(m, src, il, BRRR_T_GATE, ne * d, nb, &ly.gate, scratch));
+        TRY(load_mx(m, src, il, BRRR_T_UP, ne * d, nb, &ly.up, scratch));
+        TRY(load_mx(m, src, il, BRRR_T_DOWN, ne * d, nb, &ly.down, scratch));
+        TRY(load_f32(m, src, il, BRRR_T_GATE_B, (size_t)ne * d, &ly.gate_b));
+        TRY(load_f32(m, src, il, BRRR_T_UP_B, (size_t)ne * d, &ly.up_b));
+        TRY(load_f32(m, src, il, BRRR_T_DOWN_B, (size_t)ne * d, &ly.down_b));
+        TRY(m->alloc(&ly.kc, (size_t)BRRR_MAXSEQ * nkv * hd));
+        TRY(m->alloc(&ly.vc, (size_t)BRRR_MAXSEQ * nkv * hd));
+        CU(cudaMemsetAsync(ly.kc, 0, (size_t)BRRR_MAXSEQ * nkv * hd * 4, m->stream));
+        CU(cudaMemsetAsync(ly.vc, 0, (size_t)BRRR_MAXSEQ * nkv * hd * 4, m->stream));
+    }
+    TRY(m->alloc(&m->tok_embd, (size_t)c.n_vocab * d));
+    TRY(fetch(m, src, BRRR_L_GLOBAL, BRRR_T_TOK_EMBD, 30, (size_t)c.n_vocab * d, m->tok_embd));
+    TRY(load_f32(m, src, BRRR_L_GLOBAL, BRRR_T_OUT_NORM, d, &m->out_norm));
+    TRY(alloc_q8(m, c.n_vocab, d, &m->head));
+    TRY(load_q8_part(m, src, BRRR_L_GLOBAL, BRRR_T_OUTPUT, c.n_vocab, 0, m->head, scratch));
+
+    std::vector<float> tab((size_t)BRRR_MAXSEQ * hd);
+    rope_table_host(c, tab.data());
+    TRY(m->alloc(&m->rope, tab.size()));
+    CU(cudaMemcpyAsync(m->rope, tab.data(), tab.size() * 4, cudaMemcpyHostToDevice, m->stream));
+
+    TRY(m->alloc(&m->x, d)); TRY(m->alloc(&m->qkv, qkv_rows)); TRY(m->alloc(&m->ao, nh * hd));
+    TRY(m->alloc(&m->gu, (size_t)topk * 2 * d)); TRY(m->alloc(&m->rlogits, ne)); TRY(m->alloc(&m->logits, c.n_vocab));
+    TRY(m->alloc(&m->xs, nb)); TRY(m->alloc(&m->as, nh * hd / 32)); TRY(m->alloc(&m->hs, (size_t)topk * nb)); TRY(m->alloc(&m->wts, 8));
+    TRY(m->alloc(&m->xq, d)); TRY(m->alloc(&m->aq, nh * hd)); TRY(m->alloc(&m->hq, (size_t)topk * d));
+    TRY(m->alloc(&m->top, 8)); TRY(m->alloc(&m->st, 1));
+    CU(cudaMemsetAsync(m->st, 0, sizeof(DevState), m->stream));
+    CU(cudaMemsetAsync(m->x, 0, d * 4, m->stream));
+    CU(cudaMallocHost(&m->h_in, 16));
+    CU(cudaMallocHost(&m->h_out, BRRR_MAXSEQ * sizeof(uint32_t)));
+    CU(cudaStreamSynchronize(m->stream));
+    TRY(capture(m, true, &m->g_head, &m->launches_head));
+    TRY(capture(m, false, &m->g_nohead, &m->launches_nohead));
+    CU(cudaStreamSynchronize(m->stream));
+    return BRRR_OK;
+}
+
+int parse_dir(const char *dir, brrr_cfg *c, Source *src) {
+    std::string p = std::string(dir) + "/config.txt";
+    FILE *f = fopen(p.c_str(), "r");
+    if (!f) { snprintf(g_cuda_err, sizeof g_cuda_err, "cannot open %s", p.c_str()); return BRRR_ERR_IO; }
+    memset(c, 0, sizeof *c);
+    c->sliding_window = 1 << 30;                                         // engine_gpt2.rs:78
+    char line[512], key[128], val[128];
+    std::map<std::string, std::string> kv;
+    while (fgets(line, sizeof line, f))
+        if (sscanf(line, "%127s %127s", key, val) == 2) kv[key] = val;
+    fclose(f);
+    const char *need_i[] = {"n_embd", "n_layer", "n_head", "n_head_kv", "head_dim", "n_expert", "n_expert_used", "n_ff_exp", "n_vocab"};
+    for (const char *k : need_i)
+        if (!kv.count(k)) { snprintf(g_cuda_err, sizeof g_cuda_err, "config missing %s", k); return BRRR_ERR_IO; }
+    if (!kv.count("rope_freq_base") || !kv.count("rms_eps")) { snprintf(g_cuda_err, sizeof g_cuda_err, "config missing rope_freq_base/rms_eps"); return BRRR_ERR_IO; }
+    c->n_embd = atoi(kv["n_embd"].c_str()); c->n_layer = atoi(kv["n_layer"].c_str());
+    c->n_head = atoi(kv["n_head"].c_str()); c->n_head_kv = atoi(kv["n_head_kv"].c_str());
+    c->head_dim = atoi(kv["head_dim"].c_str()); c->n_expert = atoi(kv["n_expert"].c_str());
+    c->n_expert_used = atoi(kv["n_expert_used"].c_str()); c->n_ff_exp = atoi(kv["n_ff_exp"].c_str());
+    c->n_vocab = atoi(kv["n_vocab"].c_str());
+    if (kv.count("sliding_window")) c->sliding_window = atoi(kv["sliding_window"].c_str());
+    c->rope_freq_base = strtof(kv["rope_freq_base"].c_str(), nullptr);
+    c->rms_eps = strtof(kv["rms_eps"].c_str(), nullptr);
+
+    p = std::string(dir) + "/manifest.txt";
+    f = fopen(p.c_str(), "r");
+    if (!f) { snprintf(g_cuda_err, sizeof g_cuda_err, "cannot open %s", p.c_str()); return BRRR_ERR_IO; }
+    size_t data_start = 0;
+    if (fscanf(f, "%127s %zu", key, &data_start) != 2 || strcmp(key, "data_start")) { fclose(f); snprintf(g_cuda_err, sizeof g_cuda_err, "bad manifest header"); return BRRR_ERR_IO; }
+    char nm[256]; unsigned ty; size_t off, nel;
+    while (fscanf(f, "%255s %u %zu %zu", nm, &ty, &off, &nel) == 4) src->idx[nm] = Source::Ent{ty, data_start + off, nel};
+    fclose(f);
+    return BRRR_OK;
+}
+
+}  // namespace
+
+extern "C" int brrr_model_open(const char *data_dir, const char *blob_path, int device, brrr_model **out) {
+    if (!data_dir || !blob_path || !out) return BRRR_ERR_ARG;
+    *out = nullptr;
+    brrr_model *m = new brrr_model();
+    m->device = device;
+    Source src;
+    int s = parse_dir(data_dir, &m->cfg, &src);
+    if (s == BRRR_OK) s = check_cfg(m->cfg);
+    void *map = MAP_FAILED;
+    if (s == BRRR_OK) {
+        int fd = open(blob_path, O_RDONLY);
+        struct stat stt;
+        if (fd < 0 || fstat(fd, &stt) != 0) { snprintf(g_cuda_err, sizeof g_cuda_err, "cannot open blob %s", blob_path); s = BRRR_ERR_IO; }
+        else {
+            src.blob_len = stt.st_size;
+            map = mmap(nullptr, src.blob_len, PROT_READ, MAP_PRIVATE, fd, 0);
+            if (map == MAP_FAILED) { snprintf(g_cuda_err, sizeof g_cuda_err, "mmap of %s failed", blob_path); s = BRRR_ERR_IO; }
+            src.blob = (const uint8_t *)map;
+        }
+        if (fd >= 0) close(fd);
+    }
+    if (s == BRRR_OK) s = build_model(m, src);
+    if (map != MAP_FAILED) munmap(map, src.blob_len);
+    if (s != BRRR_OK) { brrr_model_close(m); return s; }
+    *out = m;
+    return BRRR_OK;
+}
+
+extern "C" int brrr_model_open_synth(const brrr_cfg *cfg, uint64_t seed, int device, brrr_model **out) {
+    if (!cfg || !out) return BRRR_ERR_ARG;
+    *out = nullptr;
+    int s = check_cfg(*cfg);
+    if (s != BRRR_OK) return s;
+    brrr_model *m = new brrr_model();
+    m->cfg = *cfg;
+    m->device = device;
+    Source src;
+    src.synth = true; src.seed = seed;
+    s = build_model(m, src);
+    if (s != BRRR_OK) { brrr_model_close(m); return s; }
+    *out = m;
+    return BRRR_OK;
+}
+
+extern "C" void brrr_model_close(brrr_model *m) {
+    if (!m) return;
+    cudaSetDevice(m->device);
+    if (m->stream) cudaStreamSynchronize(m->stream);
+    if (m->g_head) cudaGraphExecDestroy(m->g_head);
+    if (m->g_nohead) cudaGraphExecDestroy(m->g_nohead);
+    for (void *p : m->allocs) cudaFree(p);
+    if (m->h_in) cudaFreeHost(m->h_in);
+    if (m->h_out) cudaFreeHost(m->h_out);
+    if (m->stream) cudaStreamDestroy(m->stream);
+    delete m;
+}
+
+extern "C" int brrr_model_cfg(const brrr_model *m, brrr_cfg *out) {
+    if (!m || !out) return BRRR_ERR_ARG;
+    *out = m->cfg;
+    return BRRR_OK;
+}
+
+extern "C" void *brrr_model_stream(brrr_model *m) { return m ? (void *)m->stream : nullptr; }
+extern "C" int brrr_model_launches_per_step(const brrr_model *m, int want) { return m ? (want ? m->launches_head : m->launches_nohead) : 0; }
+
+extern "C" uint64_t brrr_model_bytes_per_step(const brrr_model *m, uint32_t pos) {
+    if (!m) return 0;
+    const brrr_cfg &c = m->cfg;
+    const uint64_t d = c.n_embd, nh = c.n_head, nkv = c.n_head_kv, hd = c.head_dim, nb = d / 32, ne = c.n_expert, k = c.n_expert_used;
+    auto q8 = [](uint64_t rows, uint64_t cols) { return rows * cols + rows * (cols / 32) * 4; };
+    uint64_t per_layer = 0;
+    per_layer += k * 3 * d * nb * 17;                       // MXFP4 gate, up, down of the k selected experts
+    per_layer += q8((nh + 2 * nkv) * hd, d) + q8(d, nh * hd);
+    per_layer += ne * d * 4 + ne * 4;                       // router
+    per_layer += ((nh + 2 * nkv) * hd + d) * 4 + k * 3 * d * 4;   // biases
+    per_layer += 2 * d * 4 + nh * 4;                        // norms, sinks
+    uint64_t total = per_layer * c.n_layer;
+    for (int il = 0; il < c.n_layer; il++) {
+        uint64_t start = ((il + 1) % 2 != 0 && (uint64_t)c.sliding_window < BRRR_MAXSEQ) ? (pos + 1 > (uint64_t)c.sliding_window ? pos + 1 - c.sliding_window : 0) : 0;
+        total += (pos - start + 1) * nkv * hd * 4 * 2;      // f32 K and V
+    }
+    total += q8(c.n_vocab, d) + d * 4 + d * 2;              // head, output norm, embedding row
+    return total;
+}
+
+static int run_graph(brrr_model *m, bool want) {
+    CU(cudaGraphLaunch(want ? m->g_head : m->g_nohead, m->stream));
+    return BRRR_OK;
+}
+
+extern "C" int brrr_forward(brrr_model *m, uint32_t tok, uint32_t pos, int want, uint32_t *out_tok) {
+    if (!m) return BRRR_ERR_ARG;
+    if (tok >= (uint32_t)m->cfg.n_vocab || pos >= BRRR_MAXSEQ) return BRRR_ERR_RANGE;
+    CU(cudaSetDevice(m->device));
+    m->h_in[0] = tok; m->h_in[1] = pos;
+    CU(cudaMemcpyAsync(m->st, m->h_in, 8, cudaMemcpyHostToDevice, m->stream));   // DevState.tok, .pos
+    TRY(run_graph(m, want != 0));
+    if (want) CU(cudaMemcpyAsync(m->h_out, &m->st->tok, 4, cudaMemcpyDeviceToHost, m->stream));
+    CU(cudaStreamSynchronize(m->stream));
+    if (want && out_tok) *out_tok = m->h_out[0];
+    return BRRR_OK;
+}
+
+extern "C" int brrr_forward_tile(brrr_model *m, const uint32_t *toks, uint32_t n, uint32_t pos0, int want, uint32_t *out_tok) {
+    if (!m || !toks || n == 0) return BRRR_ERR_ARG;
+    if (pos0 + n > BRRR_MAXSEQ) return BRRR_ERR_RANGE;
+    // Token-serial schedule: bit-identical to the batched tile by the reference's own guarantee.
+    for (uint32_t i = 0; i < n; i++) {
+        int s = brrr_forward(m, toks[i], pos0 + i, want && i == n - 1, out_tok);
+        if (s != BRRR_OK) return s;
+    }
+    return BRRR_OK;
+}
+
+extern "C" int brrr_decode_enqueue(brrr_model *m, uint32_t first_tok, uint32_t pos, uint32_t n) {
+    if (!m) return BRRR_ERR_ARG;
+    if (first_tok >= (uint32_t)m->cfg.n_vocab || n == 0 || n > BRRR_MAXSEQ || pos + n > BRRR_MAXSEQ) return BRRR_ERR_RANGE;
+    CU(cudaSetDevice(m->device));
+    m->h_in[0] = first_tok; m->h_in[1] = pos; m->h_in[2] = 0;
+    CU(cudaMemcpyAsync(m->st, m->h_in, 12, cudaMemcpyHostToDevice, m->stream));  // tok, pos, n_out = 0
+    for (uint32_t i = 0; i < n; i++) TRY(run_graph(m, true));
+    return BRRR_OK;
+}
+
+extern "C" int brrr_decode_wait(brrr_model *m, uint32_t n, uint32_t *out_toks) {
+    if (!m || !out_toks || n == 0 || n > BRRR_MAXSEQ) return BRRR_ERR_ARG;
+    CU(cudaSetDevice(m->device));
+    CU(cudaMemcpyAsync(m->h_out, m->st->out, n * sizeof(uint32_t), cudaMemcpyDeviceToHost, m->stream));
+    CU(cudaStreamSynchronize(m->stream));
+    memcpy(out_toks, m->h_out, n * sizeof(uint32_t));
+    return BRRR_OK;
+}
+
+extern "C" int brrr_decode(brrr_model *m, uint32_t first_tok, uint32_t pos, uint32_t n, uint32_t *out_toks) {
+    if (!out_toks) return BRRR_ERR_ARG;
+    int s = brrr_decode_enqueue(m, first_tok, pos, n);
+    if (s != BRRR_OK) return s;
+    return brrr_decode_wait(m, n, out_toks);
+}
+
+extern "C" int brrr_logits(brrr_model *m, float *out) {
+    if (!m || !out) return BRRR_ERR_ARG;
+    CU(cudaSetDevice(m->device));
+    CU(cudaMemcpyAsync(out, m->logits, (size_t)m->cfg.n_vocab * 4, cudaMemcpyDeviceToHost, m->stream));
+    CU(cudaStreamSynchronize(m->stream));
+    return BRRR_OK;
+}
+
+extern "C" int brrr_hidden(brrr_model *m, float *out) {
+    if (!m || !out) return BRRR_ERR_ARG;
+    CU(cudaSetDevice(m->device));
+    CU(cudaMemcpyAsync(out, m->x, (size_t)m->cfg.n_embd * 4, cudaMemcpyDeviceToHost, m->stream));
+    CU(cudaStreamSynchronize(m->stream));
+    return BRRR_OK;
+}
+
+extern "C" int brrr_forward_trace(brrr_model *m, uint32_t tok, uint32_t pos, float *trace) {
+    if (!m || !trace) return BRRR_ERR_ARG;
+    if (tok >= (uint32_t)m->cfg.n_vocab || pos >= BRRR_MAXSEQ) return BRRR_ERR_RANGE;
+    CU(cudaSetDevice(m->device));
+    size_t n = (size_t)(m->cfg.n_layer + 1) * m->cfg.n_embd;
+    float *dev = nullptr;
+    CU(cudaMalloc(&dev, n * 4));
+    m->h_in[0] = tok; m->h_in[1] = pos;
+    cudaMemcpyAsync(m->st, m->h_in, 8, cudaMemcpyHostToDevice, m->stream);
+    int s = enqueue_step(m, true, dev, nullptr);
+    if (s == BRRR_OK && cudaMemcpyAsync(trace, dev, n * 4, cudaMemcpyDeviceToHost, m->stream) != cudaSuccess) s = BRRR_ERR_CUDA;
+    if (cudaStreamSynchronize(m->stream) != cudaSuccess) s = BRRR_ERR_CUDA;
+    cudaFree(dev);
+    return s;
+}
+
+extern "C" int brrr_rope_table(const brrr_cfg *cfg, float *out) {
+    if (!cfg || !out || cfg->head_dim <= 0 || cfg->head_dim % 2) return BRRR_ERR_ARG;
+    rope_table_host(*cfg, out);
+    return BRRR_OK;
+}
+
+extern "C" int brrr_moe_ffn_step(brrr_model *m, int il, const float *d_xn, float *d_x, int32_t *d_top, float *d_wts) {
+    if (!m || !d_xn || !d_x || il < 0 || il >= m->cfg.n_layer) return BRRR_ERR_ARG;
+    CU(cudaSetDevice(m->device));
+    const brrr_cfg &c = m->cfg;
+    const int d = c.n_embd, topk = c.n_expert_used;
+    Layer &ly = m->L[il];
+    cudaStream_t s = m->stream;
+    launch_ffn_in(d_xn, nullptr, c.rms_eps, d, m->xq, m->xs, ly.ginp, ly.ginp_b, c.n_expert, topk, m->rlogits, m->top, m->wts, &m->st->router_done, s);
+    launch_gate_up(ly.gate, ly.up, ly.gate_b, ly.up_b, m->top, topk, d, m->xq, m->xs, m->gu, s);
+    launch_swiglu_quant(m->gu, topk, d, m->hq, m->hs, s);
+    launch_down_combine(ly.down, ly.down_b, m->top, m->wts, topk, d, m->hq, m->hs, d_x, s);
+    CU(cudaGetLastError());
+    if (d_top) CU(cudaMemcpyAsync(d_top, m->top, topk * sizeof(int32_t), cudaMemcpyDeviceToDevice, s));
+    if (d_wts) CU(cudaMemcpyAsync(d_wts, m->wts, topk * sizeof(float), cudaMemcpyDeviceToDevice, s));
+    CU(cudaStreamSynchronize(s));
+    return BRRR_OK;
+}
+
+// Algorithmic bytes one launch of a stage class reads (weights in run-time format + f32 KV).
+static uint64_t stage_bytes_per_launch(const brrr_model *m, int stage, uint32_t pos) {
+    const brrr_cfg &c = m->cfg;
+    const uint64_t d = c.n_embd, nh = c.n_head, nkv = c.n_head_kv, hd = c.head_dim, nb = d / 32, ne = c.n_expert, k = c.n_expert_used;
+    auto q8 = [](uint64_t rows, uint64_t cols) { return rows * cols + rows * (cols / 32) * 4; };
+    switch (stage) {
+    case ST_EMBED: return d * 2;
+    case ST_ATTN_NORM: case ST_HEAD_NORM: return d * 8;
+    case ST_QKV: return q8((nh + 2 * nkv) * hd, d) + (nh + 2 * nkv) * hd * 4;
+    case ST_ATTN: {
+        uint64_t tot = 0;
+        for (int il = 0; il < c.n_layer; il++) {
+            uint64_t start = ((il + 1) % 2 != 0 && (uint64_t)c.sliding_window < BRRR_MAXSEQ) ? (pos + 1 > (uint64_t)c.sliding_window ? pos + 1 - c.sliding_window : 0) : 0;
+            tot += (pos - start + 1) * nkv * hd * 8;
+        }
+        return tot / c.n_layer;
+    }
+    case ST_OPROJ: return q8(d, nh * hd) + d * 4;
+    case ST_FFN_IN: return ne * d * 4 + ne * 4 + d * 8;
+    case ST_GATE_UP: return k * 2 * d * nb * 17 + k * 2 * d * 4;
+    case ST_SWIGLU: return k * 2 * d * 4;
+    case ST_DOWN: return k * d * nb * 17 + k * d * 4;
+    case ST_HEAD: return q8(c.n_vocab, d);
+    }
+    return 0;
+}
+
+extern "C" int brrr_stage_count(void) { return ST_COUNT; }
+extern "C" const char *brrr_stage_name(int stage) { return stage >= 0 && stage < ST_COUNT ? kStageNames[stage] : ""; }
+
+extern "C" int brrr_stage_time(brrr_model *m, int stage, uint32_t pos, int reps, float *ms_per_launch, uint64_t *bytes_per_launch, int *launches_per_step) {
+    if (!m || stage < 0 || stage >= ST_COUNT || stage == ST_FINISH || reps <= 0 || pos >= BRRR_MAXSEQ) return BRRR_ERR_ARG;
+    CU(cudaSetDevice(m->device));
+    cudaGraphExec_t g = nullptr;
+    int n = 0;
+    TRY(capture(m, true, &g, &n, 1u << stage));
+    uint32_t saved[2];
+    CU(cudaMemcpyAsync(saved, m->st, 8, cudaMemcpyDeviceToHost, m->stream));
+    CU(cudaStreamSynchronize(m->stream));
+    m->h_in[0] = saved[0]; m->h_in[1] = pos;
+    CU(cudaMemcpyAsync(m->st, m->h_in, 8, cudaMemcpyHostToDevice, m->stream));
+    cudaEvent_t e0, e1;
+    CU(cudaEventCreate(&e0)); CU(cudaEventCreate(&e1));
+    for (int i = 0; i < 3; i++) CU(cudaGraphLaunch(g, m->stream));
+    CU(cudaEventRecord(e0, m->stream));
+    for (int i = 0; i < reps; i++) CU(cudaGraphLaunch(g, m->stream));
+    CU(cudaEventRecord(e1, m->stream));
+    CU(cudaStreamSynchronize(m->stream));
+    float ms = 0.0f;
+    CU(cudaEventElapsedTime(&ms, e0, e1));
+    cudaEventDestroy(e0); cudaEventDestroy(e1);
+    cudaGraphExecDestroy(g);
+    m->h_in[0] = saved[0]; m->h_in[1] = saved[1];
+    CU(cudaMemcpyAsync(m->st, m->h_in, 8, cudaMemcpyHostToDevice, m->stream));
+    CU(cudaStreamSynchronize(m->stream));
+    if (ms_per_launch) *ms_per_launch = n ? ms / ((float)reps * n) : 0.0f;
+    if (bytes_per_launch) *bytes_per_launch = stage_bytes_per_launch(m, stage, pos);
+    if (launches_per_step) *launches_per_step = n;
+    return BRRR_OK;
+}

@@ -1,0 +1,327 @@
+"""numpy port of the counter-based synthetic tensor generator (csrc/brrr_synth.h) and a writer
+that lays a synthetic model out as the reference's data directory: a GGUF blob plus
+config.txt / manifest.txt / tokens.bin in the formats scripts/setup_model.sh,
+scripts/gguf_index.py and scripts/dump_tokenizer.py of the reference emit.
+
+Used to exercise the file-loading path (brrr_model_open) with models whose bytes equal what
+brrr_model_open_synth generates on the device for the same seed.
+"""
+import json
+import os
+import struct
+
+import numpy as np
+
+PHI = np.uint64(0x9E3779B97F4A7C15)
+L_GLOBAL = 0xFFFF
+T = dict(ATTN_NORM=0, FFN_NORM=1, WQ=2, WK=3, WV=4, WO=5, BQ=6, BK=7, BV=8, BO=9, SINKS=10, ROUTER_W=11,
+         ROUTER_B=12, GATE=13, UP=14, DOWN=15, GATE_B=16, UP_B=17, DOWN_B=18, TOK_EMBD=32, OUT_NORM=33,
+         OUTPUT=34, PROMPT=40, INPUT=41)
+
+_old = np.seterr(over="ignore")
+
+
+def mix64(z):
+    z = np.asarray(z, dtype=np.uint64)
+    z = (z ^ (z >> np.uint64(30))) * np.uint64(0xBF58476D1CE4E5B9)
+    z = (z ^ (z >> np.uint64(27))) * np.uint64(0x94D049BB133111EB)
+    return z ^ (z >> np.uint64(31))
+
+
+def tensor_key(seed, layer, kind):
+    a = mix64(np.uint64(seed) + PHI)
+    b = np.uint64((layer << 8) | kind) * PHI
+    return mix64(a ^ b)
+
+
+def draw(key, idx):
+    idx = np.asarray(idx, dtype=np.uint64)
+    return mix64(key + (idx + np.uint64(1)) * PHI)
+
+
+def bytesum64(x):
+    m1 = np.uint64(0x00FF00FF00FF00FF)
+    m2 = np.uint64(0x0000FFFF0000FFFF)
+    x = (x & m1) + ((x >> np.uint64(8)) & m1)
+    x = (x & m2) + ((x >> np.uint64(16)) & m2)
+    return ((x + (x >> np.uint64(32))) & np.uint64(0xFFFF)).astype(np.int32)
+
+
+def normal(key, n):
+    idx = np.arange(n, dtype=np.uint64)
+    s = bytesum64(draw(key, idx * np.uint64(2))) + bytesum64(draw(key, idx * np.uint64(2) + np.uint64(1))) - 2040
+    return s.astype(np.float32) * np.float32(0.0033829376)
+
+
+def synth_f32(seed, layer, kind, n):
+    mean = np.float32(1.0 if kind in (T["ATTN_NORM"], T["FFN_NORM"], T["OUT_NORM"]) else 0.0)
+    sigma = np.float32(1.0 if kind == T["SINKS"] else 0.02)
+    z = normal(tensor_key(seed, layer, kind), n)
+    return (z * sigma).astype(np.float32) + mean
+
+
+def f32_to_bf16(v):
+    b = np.asarray(v, dtype=np.float32).view(np.uint32).astype(np.uint64)
+    return (((b + np.uint64(0x7FFF) + ((b >> np.uint64(16)) & np.uint64(1))) >> np.uint64(16)) & np.uint64(0xFFFF)).astype(np.uint16)
+
+
+def synth_bf16(seed, layer, kind, n):
+    z = normal(tensor_key(seed, layer, kind), n)
+    return f32_to_bf16((z * np.float32(0.02)).astype(np.float32))
+
+
+def synth_mxfp4(seed, layer, kind, nblocks):
+    key = tensor_key(seed, layer, kind)
+    b = np.arange(nblocks, dtype=np.uint64)
+    d0, d1, d2 = draw(key, b * np.uint64(3)), draw(key, b * np.uint64(3) + np.uint64(1)), draw(key, b * np.uint64(3) + np.uint64(2))
+    out = np.empty((nblocks, 17), np.uint8)
+    out[:, 0] = (np.uint64(117) + d2 % np.uint64(7)).astype(np.uint8)
+    out[:, 1:9] = d0.view(np.uint8).reshape(nblocks, 8)      # little-endian bytes
+    out[:, 9:17] = d1.view(np.uint8).reshape(nblocks, 8)
+    return out.reshape(-1)
+
+
+def synth_prompt(seed, n, bound):
+    key = tensor_key(seed, L_GLOBAL, T["PROMPT"])
+    return (draw(key, np.arange(n, dtype=np.uint64)) % np.uint64(bound)).astype(np.uint32)
+
+
+def synth_input(seed, n):
+    """N(0,1)-like activation vector for stage tests."""
+    return normal(tensor_key(seed, L_GLOBAL, T["INPUT"]), n)
+
+
+# ---------------------------------------------------------------- data directory
+_KIND_NAMES = {
+    "ATTN_NORM": "attn_norm.weight", "FFN_NORM": "ffn_norm.weight", "WQ": "attn_q.weight", "WK": "attn_k.weight",
+    "WV": "attn_v.weight", "WO": "attn_out.weight", "BQ": "attn_q.bias", "BK": "attn_k.bias", "BV": "attn_v.bias",
+    "BO": "attn_out.bias", "SINKS": "attn_sinks", "ROUTER_W": "ffn_gate_inp.weight", "ROUTER_B": "ffn_gate_inp.bias",
+    "GATE": "ffn_gate_exps.weight", "UP": "ffn_up_exps.weight", "DOWN": "ffn_down_exps.weight",
+    "GATE_B": "ffn_gate_exps.bias", "UP_B": "ffn_up_exps.bias", "DOWN_B": "ffn_down_exps.bias",
+}
+GGML_F32, GGML_BF16, GGML_MXFP4 = 0, 30, 39
+
+
+def model_tensors(cfg, seed):
+    """Yield (name, ggml_type, ggml_dims, raw bytes) for every tensor of a synthetic gpt-oss model.
+    ggml dims are innermost-first, as GGUF stores them."""
+    d, nh, nkv, hd, ne, nl, nv = cfg.n_embd, cfg.n_head, cfg.n_head_kv, cfg.head_dim, cfg.n_expert, cfg.n_layer, cfg.n_vocab
+    for il in range(nl):
+        def f32(kind, n, dims):
+            return (f"blk.{il}.{_KIND_NAMES[kind]}", GGML_F32, dims, synth_f32(seed, il, T[kind], n).tobytes())
+
+        def bf16(kind, rows, cols):
+            return (f"blk.{il}.{_KIND_NAMES[kind]}", GGML_BF16, [cols, rows], synth_bf16(seed, il, T[kind], rows * cols).tobytes())
+
+        def mx(kind):
+            return (f"blk.{il}.{_KIND_NAMES[kind]}", GGML_MXFP4, [d, d, ne], synth_mxfp4(seed, il, T[kind], ne * d * (d // 32)).tobytes())
+
+        yield f32("ATTN_NORM", d, [d]); yield f32("FFN_NORM", d, [d])
+        yield bf16("WQ", nh * hd, d); yield bf16("WK", nkv * hd, d); yield bf16("WV", nkv * hd, d); yield bf16("WO", d, nh * hd)
+        yield f32("BQ", nh * hd, [nh * hd]); yield f32("BK", nkv * hd, [nkv * hd]); yield f32("BV", nkv * hd, [nkv * hd]); yield f32("BO", d, [d])
+        yield f32("SINKS", nh, [nh])
+        yield f32("ROUTER_W", ne * d, [d, ne]); yield f32("ROUTER_B", ne, [ne])
+        yield mx("GATE"); yield mx("UP"); yield mx("DOWN")
+        yield f32("GATE_B", ne * d, [d, ne]); yield f32("UP_B", ne * d, [d, ne]); yield f32("DOWN_B", ne * d, [d, ne])
+    yield ("token_embd.weight", GGML_BF16, [d, nv], synth_bf16(seed, L_GLOBAL, T["TOK_EMBD"], nv * d).tobytes())
+    yield ("output_norm.weight", GGML_F32, [d], synth_f32(seed, L_GLOBAL, T["OUT_NORM"], d).tobytes())
+    yield ("output.weight", GGML_BF16, [d, nv], synth_bf16(seed, L_GLOBAL, T["OUTPUT"], nv * d).tobytes())
+
+
+def _gguf_str(s):
+    b = s.encode() if isinstance(s, str) else s
+    return struct.pack("<Q", len(b)) + b
+
+
+def write_gguf(path, cfg, seed, tokens=None, arch="gpt-oss"):
+    """Write a GGUF v3 file by hand (little-endian, alignment 32): header, metadata key/values
+    (the hyper-parameters setup_model.sh looks up, and the token list), tensor infos, data."""
+    kv = []
+
+    def kv_u32(k, v): kv.append(_gguf_str(k) + struct.pack("<II", 4, v))
+    def kv_f32(k, v): kv.append(_gguf_str(k) + struct.pack("<If", 6, v))
+    def kv_str(k, v): kv.append(_gguf_str(k) + struct.pack("<I", 8) + _gguf_str(v))
+
+    kv_str("general.architecture", arch)
+    kv_u32("general.alignment", 32)
+    kv_u32(f"{arch}.embedding_length", cfg.n_embd)
+    kv_u32(f"{arch}.block_count", cfg.n_layer)
+    kv_u32(f"{arch}.attention.head_count", cfg.n_head)
+    kv_u32(f"{arch}.attention.head_count_kv", cfg.n_head_kv)
+    kv_u32(f"{arch}.attention.key_length", cfg.head_dim)
+    kv_u32(f"{arch}.expert_count", cfg.n_expert)
+    kv_u32(f"{arch}.expert_used_count", cfg.n_expert_used)
+    kv_u32(f"{arch}.expert_feed_forward_length", cfg.n_ff_exp)
+    kv_u32(f"{arch}.attention.sliding_window", cfg.sliding_window)
+    kv_f32(f"{arch}.rope.freq_base", cfg.rope_freq_base)
+    kv_f32(f"{arch}.attention.layer_norm_rms_epsilon", cfg.rms_eps)
+    kv_u32(f"{arch}.vocab_size", cfg.n_vocab)
+    kv_u32(f"{arch}.context_length", 4096)
+    if tokens is None:
+        tokens = default_tokens(cfg.n_vocab)
+    arr = struct.pack("<IQ", 8, len(tokens)) + b"".join(_gguf_str(t) for t in tokens)
+    kv.append(_gguf_str("tokenizer.ggml.tokens") + struct.pack("<I", 9) + arr)
+
+    tensors = list(model_tensors(cfg, seed))
+    infos, off = [], 0
+    for name, ty, dims, raw in tensors:
+        infos.append(_gguf_str(name) + struct.pack("<I", len(dims)) + struct.pack(f"<{len(dims)}Q", *dims) + struct.pack("<IQ", ty, off))
+        off = (off + len(raw) + 31) // 32 * 32
+    head = b"GGUF" + struct.pack("<I", 3) + struct.pack("<QQ", len(tensors), len(kv)) + b"".join(kv) + b"".join(infos)
+    with open(path, "wb") as f:
+        f.write(head)
+        f.write(b"\0" * ((len(head) + 31) // 32 * 32 - len(head)))
+        for name, ty, dims, raw in tensors:
+            f.write(raw)
+            f.write(b"\0" * ((len(raw) + 31) // 32 * 32 - len(raw)))
+
+
+def default_tokens(n_vocab):
+    """Byte-level toy vocabulary: 256 single bytes (GPT-2 byte-to-unicode spelling), then short
+    words; special tokens spelled with '<|' so the engine's lookup skips them."""
+    bs = list(range(33, 127)) + list(range(161, 173)) + list(range(174, 256))
+    cs = bs[:]
+    n = 0
+    for b in range(256):
+        if b not in bs:
+            bs.append(b); cs.append(256 + n); n += 1
+    b2u = dict(zip(bs, [chr(c) for c in cs]))
+    toks = [b2u[b].encode("utf-8") for b in range(256)]
+    i = 0
+    while len(toks) < n_vocab - 4:
+        toks.append(("".join(b2u[ord(ch)] for ch in f"w{i}")).encode("utf-8"))
+        i += 1
+    for s in ("<|start|>", "<|end|>", "<|message|>", "<|return|>"):
+        if len(toks) < n_vocab:
+            toks.append(s.encode())
+    return toks[:n_vocab]
+
+
+# ---- index / manifest / config / tokenizer dump: the behaviour of the reference's
+# scripts/gguf_index.py, scripts/dump_tokenizer.py and the inline generator of
+# scripts/setup_model.sh:41-93, restated.
+def _rd_str(f):
+    (n,) = struct.unpack("<Q", f.read(8))
+    return f.read(n)
+
+
+_SCALAR = {0: "<B", 1: "<b", 2: "<H", 3: "<h", 4: "<I", 5: "<i", 6: "<f", 7: "<?", 10: "<Q", 11: "<q", 12: "<d"}
+
+
+def _rd_val(f, t):
+    if t in _SCALAR:
+        return struct.unpack(_SCALAR[t], f.read(struct.calcsize(_SCALAR[t])))[0]
+    if t == 8:
+        return _rd_str(f)
+    if t == 9:
+        (et,) = struct.unpack("<I", f.read(4))
+        (n,) = struct.unpack("<Q", f.read(8))
+        return [_rd_val(f, et) for _ in range(n)]
+    raise ValueError(f"bad kv type {t}")
+
+
+def gguf_index(path):
+    with open(path, "rb") as f:
+        assert f.read(4) == b"GGUF"
+        (ver,) = struct.unpack("<I", f.read(4))
+        n_tensors, n_kv = struct.unpack("<QQ", f.read(16))
+        meta, tokens = {}, None
+        for _ in range(n_kv):
+            k = _rd_str(f).decode()
+            (t,) = struct.unpack("<I", f.read(4))
+            v = _rd_val(f, t)
+            if k == "tokenizer.ggml.tokens":
+                tokens = v
+            if isinstance(v, bytes):
+                v = v.decode("utf-8", "replace")
+            if not isinstance(v, list):
+                meta[k] = v
+        infos = []
+        for _ in range(n_tensors):
+            name = _rd_str(f).decode()
+            (nd,) = struct.unpack("<I", f.read(4))
+            dims = struct.unpack(f"<{nd}Q", f.read(8 * nd))
+            ttype, off = struct.unpack("<IQ", f.read(12))
+            infos.append({"name": name, "dims": list(dims), "type": ttype, "offset": off})
+        align = meta.get("general.alignment", 32)
+        data_start = (f.tell() + align - 1) // align * align
+    return {"version": ver, "data_start": data_start, "meta": meta, "tensors": infos, "tokens": tokens}
+
+
+def _bytes_to_unicode():
+    bs = list(range(33, 127)) + list(range(161, 173)) + list(range(174, 256))
+    cs = bs[:]
+    n = 0
+    for b in range(256):
+        if b not in bs:
+            bs.append(b); cs.append(256 + n); n += 1
+    return dict(zip([chr(c) for c in cs], bs))
+
+
+def write_data_dir(out_dir, blob_path):
+    """Emit config.txt, manifest.txt, tokens.bin, blob_path.txt for a GGUF blob."""
+    os.makedirs(out_dir, exist_ok=True)
+    d = gguf_index(blob_path)
+    m = d["meta"]
+    with open(os.path.join(out_dir, "manifest.txt"), "w") as w:
+        w.write(f"data_start {d['data_start']}\n")
+        for t in d["tensors"]:
+            n = 1
+            for x in t["dims"]:
+                n *= x
+            w.write(f"{t['name']} {t['type']} {t['offset']} {n}\n")
+    arch = m.get("general.architecture", "?")
+
+    def g(*suffixes):
+        for k, v in m.items():
+            for s in suffixes:
+                if k == f"{arch}.{s}" or k.endswith("." + s):
+                    return v
+        return None
+
+    n_vocab = g("vocab_size")
+    if n_vocab is None:
+        for t in d["tensors"]:
+            if t["name"] in ("token_embd.weight", "output.weight"):
+                n_vocab = max(t["dims"]); break
+    n_ff_exp = g("expert_feed_forward_length")
+    if n_ff_exp is None:
+        for t in d["tensors"]:
+            if t["name"].endswith("ffn_gate_exps.weight"):
+                n_ff_exp = t["dims"][1]; break
+    cfg = {"arch": arch, "n_embd": g("embedding_length"), "n_layer": g("block_count"), "n_head": g("attention.head_count"),
+           "n_head_kv": g("attention.head_count_kv"), "head_dim": g("attention.key_length"), "n_expert": g("expert_count"),
+           "n_expert_used": g("expert_used_count"), "n_ff_exp": n_ff_exp, "sliding_window": g("attention.sliding_window"),
+           "rope_freq_base": g("rope.freq_base"), "rms_eps": g("attention.layer_norm_rms_epsilon"), "n_vocab": n_vocab,
+           "context_length": g("context_length")}
+    with open(os.path.join(out_dir, "config.txt"), "w") as w:
+        for k, v in cfg.items():
+            if v is not None:
+                w.write(f"{k} {v}\n")
+    u2b = _bytes_to_unicode()
+    with open(os.path.join(out_dir, "tokens.bin"), "wb") as w:
+        toks = d["tokens"] or []
+        w.write(struct.pack("<I", len(toks)))
+        for s in toks:
+            try:
+                t = s.decode("utf-8")
+                b = bytes(u2b[ch] for ch in t) if all(ch in u2b for ch in t) else s
+            except UnicodeDecodeError:
+                b = s
+            w.write(struct.pack("<H", len(b)))
+            w.write(b)
+    with open(os.path.join(out_dir, "blob_path.txt"), "w") as w:
+        w.write(str(blob_path) + "\n")
+    with open(os.path.join(out_dir, "index.json"), "w") as w:
+        json.dump({"version": d["version"], "data_start": d["data_start"],
+                   "meta": {k: v for k, v in m.items() if isinstance(v, (int, float, str))}, "tensors": d["tensors"]}, w, indent=1)
+    return cfg
+
+
+def write_synth_model(out_dir, cfg, seed):
+    """GGUF blob + data directory for a synthetic model; returns (data_dir, blob_path)."""
+    os.makedirs(out_dir, exist_ok=True)
+    blob = os.path.join(out_dir, "model.gguf")
+    write_gguf(blob, cfg, seed)
+    write_data_dir(out_dir, blob)
+    return out_dir, blob

@@ -1,0 +1,185 @@
+/* brrr.h — C ABI of the B200 decode engine.
+ *
+ * This is the boundary a host program links against (the reference host is Rust: an
+ * `unsafe extern "C"` block binds these symbols unchanged).  Plain pointers and sizes only; every
+ * function returns an int status (0 = BRRR_OK), never aborts and never throws.  A model handle
+ * owns all of its device memory; use one host thread per handle.
+ *
+ * The reference (arizqi/cpubrrr) has no FFI: its engines are monolithic binaries.  Each entry
+ * point below names the reference function or code region it replaces, by file:line within the
+ * reference project.
+ *
+ * Pointers named d_* are CUDA device pointers; everything else is host memory.
+ * `stream` arguments are a cudaStream_t passed as void* (NULL = the default stream).
+ */
+#ifndef BRRR_H
+#define BRRR_H
+
+#include <stdint.h>
+#include <stddef.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+enum {
+    BRRR_OK = 0,
+    BRRR_ERR_ARG = 1,        /* bad argument / unsupported shape */
+    BRRR_ERR_IO = 2,         /* data directory or blob unreadable / malformed */
+    BRRR_ERR_CUDA = 3,       /* a CUDA call failed; brrr_last_cuda_error() has the text */
+    BRRR_ERR_NOMEM = 4,
+    BRRR_ERR_RANGE = 5,      /* position / token / count out of range */
+    BRRR_ERR_STATE = 6       /* call not valid in the handle's current state */
+};
+
+#define BRRR_MAXSEQ 4096     /* src/bin/engine_gpt2.rs:16 */
+
+/* Model hyper-parameters: the keys of the data directory's config.txt
+ * (scripts/setup_model.sh:71-89, parsed at src/bin/engine_gpt2.rs:58-80). */
+typedef struct brrr_cfg {
+    int32_t n_embd, n_layer, n_head, n_head_kv, head_dim;
+    int32_t n_expert, n_expert_used, n_ff_exp, sliding_window, n_vocab;
+    float rope_freq_base, rms_eps;
+} brrr_cfg;
+
+typedef struct brrr_model brrr_model;
+
+const char *brrr_strerror(int status);
+const char *brrr_last_cuda_error(void);
+
+/* ---------------------------------------------------------------- model lifetime */
+
+/* Load a model from a data directory (config.txt, manifest.txt) and its GGUF blob: mmap, upload,
+ * quantise attention/head weights from bf16 to Q8 and re-lay the MXFP4 experts, all on `device`.
+ * Replaces load_cfg + the loader in main (src/bin/engine_gpt2.rs:64-80, 1276-1352):
+ * Q8Mat::from_bf16 (464-494), repack_mx (439-461), rope_init (536-550). */
+int brrr_model_open(const char *data_dir, const char *blob_path, int device, brrr_model **out);
+
+/* Same model container filled with seeded synthetic tensors generated on the device in the GGUF
+ * tensor formats (no file involved), then converted exactly as brrr_model_open converts a blob.
+ * No counterpart in the reference: it stands in for a checkpoint where none is available. */
+int brrr_model_open_synth(const brrr_cfg *cfg, uint64_t seed, int device, brrr_model **out);
+
+int brrr_model_cfg(const brrr_model *m, brrr_cfg *out);
+void brrr_model_close(brrr_model *m);
+
+/* ---------------------------------------------------------------- forward pass */
+
+/* One token through the whole network at position `pos`; with want_logits != 0 the vocabulary
+ * projection runs and *out_tok receives the greedy token (first strict maximum).  Host token in,
+ * host token out.  Replaces the closure `run(tok, pos, want) -> u32` and the worker dispatch
+ * behind it (src/bin/engine_gpt2.rs:1373-1385; forward_worker 751-934; head 936-1002).  The
+ * whole step is one CUDA graph launch. */
+int brrr_forward(brrr_model *m, uint32_t tok, uint32_t pos, int want_logits, uint32_t *out_tok);
+
+/* A tile of tokens at positions pos0.. (prefill); the result equals feeding them one by one, as
+ * the reference guarantees for run_tile (src/bin/engine_gpt2.rs:1004-1010, 1387-1393). */
+int brrr_forward_tile(brrr_model *m, const uint32_t *toks, uint32_t n, uint32_t pos0, int want_logits, uint32_t *out_tok);
+
+/* n greedy decode steps starting from `first_tok` at position `pos`, the token id staying on the
+ * device between steps (one graph launch per step, no host round trip); out_toks[i] is the token
+ * produced by step i.  Replaces the decode loop of generate (src/bin/engine_gpt2.rs:1431-1438)
+ * without its stop-token test, which the caller applies to out_toks. */
+int brrr_decode(brrr_model *m, uint32_t first_tok, uint32_t pos, uint32_t n, uint32_t *out_toks);
+
+/* Same loop, asynchronous: enqueue n steps on the model's stream and return; the tokens are
+ * collected by brrr_decode_wait.  Lets a caller time the device work with its own events. */
+int brrr_decode_enqueue(brrr_model *m, uint32_t first_tok, uint32_t pos, uint32_t n);
+int brrr_decode_wait(brrr_model *m, uint32_t n, uint32_t *out_toks);
+
+/* Full-vocabulary Q8 logits of the last want_logits step (host buffer of n_vocab floats); the
+ * values `CPBRR_HEADCHK` materialises at src/bin/engine_gpt2.rs:973-976. */
+int brrr_logits(brrr_model *m, float *out);
+/* Residual stream x after the last step (host buffer of n_embd floats); the vector the
+ * reference's DUMP / CPBRR_DBG taps summarise (src/bin/engine_gpt2.rs:924-928). */
+int brrr_hidden(brrr_model *m, float *out);
+/* Debug forward that runs the same kernels un-graphed and copies x after the embedding and after
+ * every layer into trace[(n_layer+1)][n_embd] (host). */
+int brrr_forward_trace(brrr_model *m, uint32_t tok, uint32_t pos, float *trace);
+/* The model's CUDA stream (cudaStream_t as void*), for callers that record their own events. */
+void *brrr_model_stream(brrr_model *m);
+/* Number of kernel launches one decode step performs (graph kernel nodes). */
+int brrr_model_launches_per_step(const brrr_model *m, int want_logits);
+/* Weight + KV bytes one decode step at position `pos` must read in the run-time formats. */
+uint64_t brrr_model_bytes_per_step(const brrr_model *m, uint32_t pos);
+
+/* Stage timing for roofline reports.  The decode step is made of brrr_stage_count() kernel
+ * classes (brrr_stage_name(i)); brrr_stage_time replays, as one CUDA graph, every launch of one
+ * class that a step at position `pos` performs (all layers, real weights, so the working set
+ * exceeds L2 for the streaming classes), `reps` times between two events on the model's stream,
+ * and returns the mean duration of one launch, the algorithmic bytes one launch reads and the
+ * launches per step.  Counterpart of the reference's per-stage timers TM[5]
+ * (src/bin/engine_gpt2.rs:56, 843-929, 1496-1497). */
+int brrr_stage_count(void);
+const char *brrr_stage_name(int stage);
+int brrr_stage_time(brrr_model *m, int stage, uint32_t pos, int reps, float *ms_per_launch, uint64_t *bytes_per_launch, int *launches_per_step);
+
+/* ---------------------------------------------------------------- stage-level entry points
+ * Device pointers in, device pointers out.  They launch the same kernels the forward pass uses. */
+
+/* Per-32-block int8 quantiser: q[i] = round_half_away(x[i] / s[b]), s[b] = max(1e-12, amax)/127.
+ * Replaces qblock32 / quant_i8 (src/bin/engine_gpt2.rs:689-699; src/bin/engine.rs:264-279). */
+int brrr_quant_q8(const float *d_x, int n, int8_t *d_q, float *d_s, void *stream);
+
+/* RMSNorm then the quantiser above; d_xn (nullable) receives the normalised floats.
+ * Replaces ssq + rmsnorm_quant_par (src/bin/engine_gpt2.rs:709-738). */
+int brrr_rmsnorm_quant(const float *d_x, const float *d_w, float eps, int n, float *d_xn, int8_t *d_q, float *d_s, void *stream);
+
+/* Opaque device matrices in the engine's streaming layouts. */
+typedef struct brrr_q8mat brrr_q8mat;
+typedef struct brrr_mxmat brrr_mxmat;
+
+/* bf16 [rows][cols] (device) -> Q8 matrix, quantised per 32-block as Q8Mat::from_bf16
+ * (src/bin/engine_gpt2.rs:464-494). rows % 4 == 0, cols % 64 == 0. */
+int brrr_q8mat_from_bf16(const uint16_t *d_w, int rows, int cols, brrr_q8mat **out, void *stream);
+/* copies back the quantised values in natural order: q[rows][cols], s[rows][cols/32] (device) */
+int brrr_q8mat_export(const brrr_q8mat *m, int8_t *d_q, float *d_s, void *stream);
+void brrr_q8mat_free(brrr_q8mat *m);
+/* y[r] = row r . Q8 activation.  Replaces dot_q8_i8 / Q8Mat::dot (src/bin/engine_gpt2.rs:165-191, 495-500). */
+int brrr_q8_matvec(const brrr_q8mat *w, const int8_t *d_xq, const float *d_xs, float *d_y, void *stream);
+
+/* GGUF MXFP4 rows (17-byte blocks, device) -> engine layout.  Replaces repack_mx
+ * (src/bin/engine_gpt2.rs:439-461). rows % 8 == 0, blocks % 2 == 0. */
+int brrr_mxmat_from_gguf(const uint8_t *d_raw, int rows, int blocks, brrr_mxmat **out, void *stream);
+void brrr_mxmat_free(brrr_mxmat *m);
+/* y[i] = row (row0 + i) . Q8 activation for i < nrows.  d_blockdots (nullable) receives the exact
+ * int32 block accumulators as [nrows][blocks][4 lanes].  Replaces dot4_mx_i8
+ * (src/bin/engine_gpt2.rs:193-228). */
+int brrr_mx_matvec(const brrr_mxmat *w, int row0, int nrows, const int8_t *d_xq, const float *d_xs, float *d_y, int32_t *d_blockdots, void *stream);
+
+/* Router GEMV + top-k + softmax over the selected k.  d_b nullable.  d_logits [ne], d_top [k],
+ * d_wts [k].  Replaces src/bin/engine_gpt2.rs:848-867. */
+int brrr_router_topk(const float *d_w, const float *d_b, const float *d_xn, int ne, int d, int topk,
+                     float *d_logits, int32_t *d_top, float *d_wts, void *stream);
+
+/* Clamped SwiGLU on gu[topk][2d] (gate | up) then the per-32 quantiser.  Replaces
+ * src/bin/engine_gpt2.rs:886-907. */
+int brrr_swiglu_quant(const float *d_gu, int topk, int d, int8_t *d_hq, float *d_hs, void *stream);
+
+/* Decode attention for all heads at position pos.  d_qkv holds this token's projected q | k | v
+ * (bias added, not rotated); the kernel rotates q and k, appends k/v to the cache
+ * [pos][n_head_kv][64] and attends over start..pos, then quantises the output.  d_rope is the
+ * [BRRR_MAXSEQ][32][2] cos/sin table.  Replaces rope_yarn + the cache write + the attention stage
+ * (src/bin/engine_gpt2.rs:575-587, 783-837). head_dim is 64. */
+int brrr_attn_decode(const float *d_qkv, float *d_kc, float *d_vc, const float *d_rope, const float *d_sinks,
+                     int n_head, int n_head_kv, int pos, int start, float *d_ao, int8_t *d_aq, float *d_as, void *stream);
+
+/* YaRN cos/sin table [BRRR_MAXSEQ][head_dim/2][2] built on the host (src/bin/engine_gpt2.rs:531-572). */
+int brrr_rope_table(const brrr_cfg *cfg, float *out);
+
+/* One MoE FFN step of layer `il` on a normalised token: quantise d_xn, route, gate/up, SwiGLU,
+ * down + weighted combine added onto d_x.  d_top/d_wts (nullable) receive the routing.
+ * Replaces src/bin/engine_gpt2.rs:847-923. */
+int brrr_moe_ffn_step(brrr_model *m, int il, const float *d_xn, float *d_x, int32_t *d_top, float *d_wts);
+
+/* Fill a device buffer with a synthetic tensor in its GGUF format (type 0 = f32, 30 = bf16,
+ * 39 = MXFP4; nelems counts values). Same generator brrr_model_open_synth uses. */
+int brrr_synth_tensor(uint64_t seed, uint32_t layer, uint32_t kind, uint32_t type, uint64_t nelems, void *d_out, void *stream);
+
+/* exp as the engine defines it (fixed IEEE sequence); d_y[i] = exp(d_x[i]). */
+int brrr_expf(const float *d_x, int n, float *d_y, void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BRRR_H */

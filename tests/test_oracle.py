@@ -1,0 +1,278 @@
+"""Pins the CPU oracle (the checker of the CUDA path) against independent statements of the same
+formats and arithmetic: the gguf package's MXFP4 dequantiser, float64 dequantise-then-dot with
+the reference's own verifier thresholds, numpy restatements of the quantiser, and the
+reference's invariants and constants.  No GPU needed."""
+import ctypes as C
+import json
+import os
+
+import numpy as np
+import pytest
+
+from cpubrrr_b200 import synth as S
+
+KVI = np.array([0, 1, 2, 3, 4, 6, 8, 12, 0, -1, -2, -3, -4, -6, -8, -12], np.int32)
+GOLD = os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden")
+
+
+def np_quant_q8(x):
+    """Independent numpy statement of the per-32 quantiser (f32 ops, round half away from zero)."""
+    x = np.asarray(x, np.float32).reshape(-1, 32)
+    amax = np.maximum(np.abs(x).max(axis=1), np.float32(1e-12)).astype(np.float32)
+    sc = (amax / np.float32(127.0)).astype(np.float32)
+    q = (x / sc[:, None]).astype(np.float32)
+    r = np.sign(q) * np.floor(np.abs(q) + np.float32(0.5))
+    return np.clip(r, -127, 127).astype(np.int8).reshape(-1), sc
+
+
+def mx_dequant_np(raw, rows, blocks):
+    raw = np.asarray(raw, np.uint8).reshape(rows, blocks, 17)
+    e = raw[:, :, 0].astype(np.int32)
+    nb = raw[:, :, 1:]
+    lo, hi = KVI[nb & 0xF], KVI[nb >> 4]
+    vals = np.concatenate([lo, hi], axis=2).astype(np.float64)
+    return (vals * np.exp2(e[:, :, None].astype(np.float64) - 128)).reshape(rows, blocks * 32)
+
+
+def test_expf_close_to_libm_and_edges(orc):
+    x = np.concatenate([np.linspace(-103.9, 88.7, 40001), np.linspace(-2, 2, 20001)]).astype(np.float32)
+    got = orc.expf(x).astype(np.float64)
+    ref = np.exp(x.astype(np.float64))
+    ok = ref > 1.2e-38
+    ulp = np.abs(got[ok] - ref[ok]) / np.spacing(ref[ok].astype(np.float32)).astype(np.float64)
+    assert ulp.max() <= 2.0
+    assert orc.expf(np.float32(0.0)) == 1.0
+    assert orc.expf(np.float32(-200.0)) == 0.0
+    assert np.isinf(orc.expf(np.float32(89.0)))
+    assert 0 < orc.expf(np.float32(-100.0)) < 1e-40          # subnormal result is produced, not flushed
+
+
+def test_mxfp4_format_matches_gguf_package(orc):
+    """value = KVI[nibble] * 2^(e-128); byte j low nibble = element j, high nibble = element j+16
+    (src/bin/engine.rs:178-182) — pinned by the gguf package's own dequantiser."""
+    gguf = pytest.importorskip("gguf")
+    rng = np.random.default_rng(0)
+    rows, blocks = 8, 6
+    raw = rng.integers(0, 256, rows * blocks * 17, dtype=np.uint8).reshape(rows, blocks * 17)
+    raw.reshape(rows, blocks, 17)[:, :, 0] = rng.integers(100, 140, (rows, blocks))
+    ref = gguf.quants.dequantize(raw, gguf.GGMLQuantizationType.MXFP4)
+    got = orc.mx_dequant_rows(raw, rows, blocks)
+    assert np.array_equal(got, ref.astype(np.float32))
+    assert np.array_equal(got.astype(np.float64), mx_dequant_np(raw, rows, blocks))
+
+
+def test_mxfp4_known_block(orc):
+    """e = 128 with codes 0..15 dequantises to the doubled e2m1 table itself."""
+    blk = np.zeros(17, np.uint8)
+    blk[0] = 128
+    blk[1:17] = np.arange(16) | (np.arange(16)[::-1] << 4)
+    got = orc.mx_dequant_rows(blk, 1, 1)[0]
+    assert list(got[:16]) == [0, 1, 2, 3, 4, 6, 8, 12, 0, -1, -2, -3, -4, -6, -8, -12]
+    assert list(got[16:]) == [0, 1, 2, 3, 4, 6, 8, 12, 0, -1, -2, -3, -4, -6, -8, -12][::-1]
+
+
+def test_quantiser_matches_numpy_statement(orc):
+    rng = np.random.default_rng(1)
+    x = rng.standard_normal(2880).astype(np.float32)
+    x[64:96] = 0.0                      # all-zero block: scale 1e-12/127, q = 0
+    x[100] = 0.5 * 127 / 127            # exercise .5 ties
+    q, s = orc.quant_q8(x)
+    qn, sn = np_quant_q8(x)
+    assert np.array_equal(q, qn) and np.array_equal(s, sn)
+    assert s[2] == np.float32(1e-12) / np.float32(127.0) and not q[64:96].any()
+    # ties round away from zero (Rust f32::round), not to even
+    t = np.zeros(32, np.float32); t[0] = 127.0; t[1] = 2.5; t[2] = -2.5; t[3] = 3.5
+    q, s = orc.quant_q8(t)
+    assert s[0] == 1.0 and list(q[:4]) == [127, 3, -3, 4]
+
+
+def test_mx_dot_exact_integers_and_f64_threshold(orc):
+    """Integer block accumulators equal an independent numpy integer dot; float result within the
+    reference's bench_real threshold (rel 1e-4) of a float64 dequantise-then-dot, on the
+    reference's deterministic activation x[i] = ((7i+3) mod 11) - 5 (scripts/extract_experts.py:40)."""
+    rows, blocks = 64, 90
+    raw = S.synth_mxfp4(11, 0, S.T["GATE"], rows * blocks)
+    nib, exps = orc.repack_mx(raw, rows, blocks)
+    xi = ((7 * np.arange(blocks * 32) + 3) % 11 - 5).astype(np.float32)
+    xq, xs = orc.quant_q8(xi)
+    y, dbg = orc.mx_matvec(nib, exps, rows, blocks, xq, xs, want_dbg=True)
+    r = raw.reshape(rows, blocks, 17)[:, :, 1:]
+    lo, hi = KVI[r & 0xF], KVI[r >> 4]                       # [rows][blocks][16]
+    x3 = xq.astype(np.int32).reshape(blocks, 2, 16)
+    prod = lo * x3[None, :, 0, :] + hi * x3[None, :, 1, :]   # byte i: lo*x0[i] + hi*x1[i]
+    lanes = prod.reshape(rows, blocks, 4, 4).sum(axis=3)     # lane j = bytes 4j..4j+3
+    want = lanes.reshape(rows // 4, 4, blocks, 4).transpose(0, 2, 1, 3)
+    assert np.array_equal(dbg, want)
+    w = mx_dequant_np(raw, rows, blocks)
+    xd = xq.astype(np.float64) * np.repeat(xs.astype(np.float64), 32)
+    ref = w @ xd
+    assert np.abs(y - ref).max() / np.abs(ref).max() < 1e-4
+
+
+def test_q8_matrix_quantisation_and_dot(orc):
+    rows, cols = 32, 2880
+    wb = S.synth_bf16(5, 0, S.T["WQ"], rows * cols)
+    q, s = orc.q8_from_bf16(wb, rows, cols)
+    wf = (wb.astype(np.uint32) << 16).view(np.float32).reshape(rows, cols)
+    qn, sn = np_quant_q8(wf)
+    assert np.array_equal(q.reshape(-1), qn) and np.array_equal(s.reshape(-1), sn)
+    x = S.synth_input(3, cols)
+    xq, xs = orc.quant_q8(x)
+    y = orc.q8_matvec(q, s, xq, xs)
+    ref = (q.astype(np.float64) * np.repeat(s.astype(np.float64), 32, axis=1)) @ (xq.astype(np.float64) * np.repeat(xs.astype(np.float64), 32))
+    assert np.abs(y - ref).max() / np.abs(ref).max() < 1e-5
+
+
+def test_rmsnorm_and_ssq(orc):
+    x = S.synth_input(4, 2880) * np.float32(3.0)
+    w = S.synth_f32(4, 0, S.T["ATTN_NORM"], 2880)
+    out = orc.rmsnorm(x, w, 1e-5)
+    x64 = x.astype(np.float64)
+    ref = x64 / np.sqrt((x64 ** 2).mean() + 1e-5) * w
+    assert np.abs(out - ref).max() < 1e-5
+    assert abs(float(orc.ssq(x)) - (x64 ** 2).sum()) / (x64 ** 2).sum() < 1e-6
+    # n % 16 != 0 exercises the scalar tail
+    assert abs(float(orc.ssq(x[:37])) - (x64[:37] ** 2).sum()) < 1e-3
+
+
+def test_rope_table_against_float64(orc):
+    cfg = orc.make_cfg(d=2880, nh=64, nkv=8, hd=64, nl=1, ne=32, topk=4, nvocab=1024)
+    tab = orc.rope_table(cfg)
+    hd, base = 64, 150000.0
+    fd = lambda beta: hd * np.log(4096.0 / (beta * 2 * np.pi)) / (2 * np.log(base))
+    low, high = max(np.floor(fd(32.0)), 0), min(np.ceil(fd(1.0)), hd - 1)
+    i = np.arange(32)
+    mix = 1 - np.clip((i - low) / max(high - low, 0.001), 0, 1)
+    for pos in (0, 1, 73, 200, 4095):
+        th_ex = pos * base ** (-(2.0 * i) / hd)
+        th = th_ex / 32 * (1 - mix) + th_ex * mix
+        ms = 1 + 0.1 * np.log(32.0)
+        # f32 angles at large pos carry ~pos*6e-8 absolute error
+        assert np.abs(tab[pos, :, 0] - np.cos(th) * ms).max() < 2e-3
+        assert np.abs(tab[pos, :, 1] - np.sin(th) * ms).max() < 2e-3
+    assert np.array_equal(tab[0, :, 1], np.zeros(32, np.float32))
+
+
+def test_router_topk_rank_order_and_ties(orc):
+    ne, d, k = 32, 64, 4
+    w = np.zeros((ne, d), np.float32)
+    b = np.linspace(-1, 1, ne).astype(np.float32)
+    b[5] = b[31]                     # tie with the maximum: lower index must rank first
+    xn = np.ones(d, np.float32)
+    logits, top, wts = orc.router_topk(w, b, xn, k)
+    assert list(top) == [5, 31, 30, 29]
+    assert abs(wts.sum() - 1) < 1e-6 and wts[0] == wts[1] and np.all(np.diff(wts) <= 0)
+    # serial unfused accumulation order
+    rng = np.random.default_rng(3)
+    w = rng.standard_normal((ne, d)).astype(np.float32)
+    xn = rng.standard_normal(d).astype(np.float32)
+    logits, top, wts = orc.router_topk(w, b, xn, k)
+    acc = b.copy()
+    for j in range(d):
+        acc = (acc + (w[:, j] * xn[j]).astype(np.float32)).astype(np.float32)
+    assert np.array_equal(logits, acc)
+    order = np.argsort(-logits, kind="stable")[:k]
+    assert list(top) == list(order)
+
+
+def test_swiglu_clamps(orc):
+    d = 64
+    gu = np.zeros((1, 2 * d), np.float32)
+    gu[0, :d] = np.linspace(-20, 20, d)
+    gu[0, d:] = np.linspace(-10, 10, d)
+    hq, hs, h = orc.swiglu_quant(gu, 1, d)
+    g, u = gu[0, :d].astype(np.float64), gu[0, d:].astype(np.float64)
+    xg, yu = np.minimum(g, 7.0), np.clip(u, -7.0, 7.0)
+    ref = xg / (1 + np.exp(-1.702 * xg)) * (yu + 1)
+    assert np.abs(h[0] - ref).max() < 1e-5 * max(1, np.abs(ref).max())
+    qn, sn = np_quant_q8(h[0])
+    assert np.array_equal(hq[0], qn) and np.array_equal(hs[0], sn)
+
+
+def test_attention_head_sink_and_window(orc):
+    """cosine > 0.99999 vs float64 (the reference's attn_forward threshold); the sink only enters
+    the denominator; the window start is pos - (swa-1)."""
+    rng = np.random.default_rng(5)
+    nkv, hd, pos = 2, 64, 150
+    kc = rng.standard_normal((pos + 1, nkv, hd)).astype(np.float32)
+    vc = rng.standard_normal((pos + 1, nkv, hd)).astype(np.float32)
+    q = rng.standard_normal(hd).astype(np.float32)
+    for start in (0, pos - 127):
+        ao = orc.attn_head(q, kc, vc, nkv, hd, 1, start, pos, 0.3)
+        s = (kc[start:pos + 1, 1].astype(np.float64) @ q.astype(np.float64)) / 8.0
+        mx = max(s.max(), 0.3)
+        e = np.exp(s - mx)
+        ref = (e[:, None] * vc[start:pos + 1, 1]).sum(0) / (np.exp(0.3 - mx) + e.sum())
+        cos = ao @ ref / np.linalg.norm(ao) / np.linalg.norm(ref)
+        assert cos > 0.99999 and np.abs(ao - ref).max() < 1e-5
+
+
+def test_synth_generator_numpy_equals_c(orc):
+    """The numpy port of the generator and the C header the oracle compiles produce equal bytes
+    (checked through a synthetic model the oracle builds)."""
+    cfg = orc.make_cfg(d=128, nh=4, nkv=2, hd=64, nl=2, ne=8, topk=4, nvocab=512)
+    m = orc.Model.synth(cfg, 9)
+    assert np.array_equal(m.layer_f32(1, S.T["BQ"], 256), S.synth_f32(9, 1, S.T["BQ"], 256))
+    assert np.array_equal(m.layer_f32(0, S.T["ATTN_NORM"], 128), S.synth_f32(9, 0, S.T["ATTN_NORM"], 128))
+    assert np.array_equal(m.layer_f32(1, S.T["SINKS"], 4), S.synth_f32(9, 1, S.T["SINKS"], 4))
+    nib, exps, rows, blocks = m.layer_mx(1, 2)
+    n2, e2 = orc.repack_mx(S.synth_mxfp4(9, 1, S.T["DOWN"], rows * blocks), rows, blocks)
+    assert np.array_equal(nib, n2) and np.array_equal(exps, e2)
+    q, s = m.layer_q8(0, 3)
+    q2, s2 = orc.q8_from_bf16(S.synth_bf16(9, 0, S.T["WO"], 128 * 256), 128, 256)
+    assert np.array_equal(q, q2) and np.array_equal(s, s2)
+    assert np.array_equal(orc.synth_prompt(9, 16, 500), S.synth_prompt(9, 16, 500))
+    z = S.synth_input(1, 200000)
+    assert abs(z.mean()) < 0.01 and abs(z.std() - 1) < 0.01
+    e = S.synth_mxfp4(1, 0, S.T["GATE"], 7000).reshape(-1, 17)[:, 0]
+    assert e.min() == 117 and e.max() == 123
+
+
+def test_data_dir_route_equals_synth_route(orc, tmp_path):
+    """A model written as GGUF + config/manifest and loaded through the data-directory contract
+    gives the same tokens and logits as the in-memory synthetic model of the same seed."""
+    from cpubrrr_b200.engine import make_cfg
+    d, blob = S.write_synth_model(str(tmp_path), make_cfg(128, 2, 4, 2, 8, 4, 512), 7)
+    m1 = orc.Model.open(d, blob)
+    m2 = orc.Model.synth(orc.make_cfg(d=128, nh=4, nkv=2, hd=64, nl=2, ne=8, topk=4, nvocab=512), 7)
+    p = S.synth_prompt(7, 6, 500)
+    for i, t in enumerate(p):
+        assert m1.run(t, i, True) == m2.run(t, i, True)
+    assert np.array_equal(m1.logits(), m2.logits())
+
+
+def test_forward_invariants(orc):
+    """Same position recomputed gives the same result (KV overwrite is idempotent); want=False
+    leaves the same hidden state; sliding window changes results only past the window."""
+    cfg = orc.make_cfg(d=128, nh=4, nkv=2, hd=64, nl=2, ne=8, topk=4, nvocab=512, swa=4)
+    m = orc.Model.synth(cfg, 3)
+    p = S.synth_prompt(3, 12, 500)
+    toks = [m.run(t, i, True) for i, t in enumerate(p)]
+    h = m.hidden()
+    assert m.run(p[-1], len(p) - 1, True) == toks[-1] and np.array_equal(m.hidden(), h)
+    m.run(p[-1], len(p) - 1, False)
+    assert np.array_equal(m.hidden(), h)
+    full = orc.Model.synth(orc.make_cfg(d=128, nh=4, nkv=2, hd=64, nl=2, ne=8, topk=4, nvocab=512, swa=4096), 3)
+    t2 = [full.run(t, i, True) for i, t in enumerate(p)]
+    assert toks[:4] == t2[:4]        # positions 0..3 fit in the window of 4
+    assert not np.array_equal(full.hidden(), h)
+
+
+def test_golden_tokens(orc):
+    """Committed fixture (tests/golden/gptoss_tiny_tokens.json, made by tests/golden/make_golden.py
+    with this oracle): guards the oracle itself against silent drift."""
+    path = os.path.join(GOLD, "gptoss_tiny_tokens.json")
+    g = json.load(open(path))
+    c = g["cfg"]
+    m = orc.Model.synth(orc.make_cfg(d=c["d"], nh=c["nh"], nkv=c["nkv"], hd=64, nl=c["nl"], ne=c["ne"], topk=c["topk"],
+                                     nvocab=c["nvocab"], swa=c["swa"]), g["seed"])
+    tok = 0
+    for i, t in enumerate(g["prompt"]):
+        tok = m.run(t, i, i == len(g["prompt"]) - 1)
+    out, pos = [], len(g["prompt"])
+    for _ in range(len(g["tokens"])):
+        out.append(tok)
+        tok = m.run(tok, pos, True)
+        pos += 1
+    assert out == g["tokens"]
+    assert [int(b) for b in m.logits()[:8].view(np.uint32)] == g["last_logit_bits"]
