@@ -79,7 +79,8 @@ def test_q8_pack_and_matvec(L, orc, dev, rows, cols):
     x = S.synth_input(cols, cols)
     xq, xs = orc.quant_q8(x)
     dy = torch.empty(rows, dtype=torch.float32, device=dev)
-    ok(L.brrr_q8_matvec(h, P(to_dev(xq, dev)), P(to_dev(xs, dev)), P(dy), None))
+    dxq, dxs = to_dev(xq, dev), to_dev(xs, dev)      # keep the inputs alive across the call
+    ok(L.brrr_q8_matvec(h, P(dxq), P(dxs), P(dy), None))
     torch.cuda.synchronize()
     assert np.array_equal(bits(dy.cpu().numpy()), bits(orc.q8_matvec(q, s, xq, xs)))
     L.brrr_q8mat_free(h)
@@ -94,7 +95,8 @@ def test_mx_pack_and_matvec_int_exact(L, orc, dev, rows, blocks):
     r = raw.reshape(rows * blocks, 17)
     r[::7, 0] = np.arange(len(r[::7])) % 200     # 2^(e-128) up to 2^71: no overflow to inf
     h = C.c_void_p()
-    ok(L.brrr_mxmat_from_gguf(P(to_dev(raw, dev)), rows, blocks, C.byref(h), None))
+    draw = to_dev(raw, dev)
+    ok(L.brrr_mxmat_from_gguf(P(draw), rows, blocks, C.byref(h), None))
     x = S.synth_input(blocks, blocks * 32) * np.float32(1e-3 if blocks == 4 else 1.0)
     xq, xs = orc.quant_q8(x)
     nib, exps = orc.repack_mx(raw, rows, blocks)
@@ -129,10 +131,12 @@ def test_mx_all_nibble_codes(L, orc, dev):
     x = np.resize(np.array([127, -127, 1, -1, 64, -3, 0, 5], np.float32), blocks * 32)
     xq, xs = orc.quant_q8(x)
     h = C.c_void_p()
-    ok(L.brrr_mxmat_from_gguf(P(to_dev(raw, dev)), rows, blocks, C.byref(h), None))
+    draw = to_dev(raw, dev)
+    ok(L.brrr_mxmat_from_gguf(P(draw), rows, blocks, C.byref(h), None))
     dy = torch.empty(rows, dtype=torch.float32, device=dev)
     dd = torch.empty((rows, blocks, 4), dtype=torch.int32, device=dev)
-    ok(L.brrr_mx_matvec(h, 0, rows, P(to_dev(xq, dev)), P(to_dev(xs, dev)), P(dy), P(dd), None))
+    dxq, dxs = to_dev(xq, dev), to_dev(xs, dev)
+    ok(L.brrr_mx_matvec(h, 0, rows, P(dxq), P(dxs), P(dy), P(dd), None))
     nib, exps = orc.repack_mx(raw, rows, blocks)
     y, dbg = orc.mx_matvec(nib, exps, rows, blocks, xq, xs, want_dbg=True)
     assert np.array_equal(dd.cpu().numpy(), dbg.transpose(0, 2, 1, 3).reshape(rows, blocks, 4))
@@ -152,8 +156,9 @@ def test_router_topk(L, orc, dev, ne, d, topk, bias):
     dt = torch.empty(topk, dtype=torch.int32, device=dev)
     dwt = torch.empty(topk, dtype=torch.float32, device=dev)
     db = to_dev(b, dev) if bias else None
+    dw, dxn = to_dev(w, dev), to_dev(xn, dev)
     for _ in range(2):   # second call checks the self-resetting arrival counter
-        ok(L.brrr_router_topk(P(to_dev(w, dev)), P(db) if bias else None, P(to_dev(xn, dev)), ne, d, topk, P(dl), P(dt), P(dwt), None))
+        ok(L.brrr_router_topk(P(dw), P(db) if bias else None, P(dxn), ne, d, topk, P(dl), P(dt), P(dwt), None))
         torch.cuda.synchronize()
     logits, top, wts = orc.router_topk(w, b, xn, topk)
     assert np.array_equal(bits(dl.cpu().numpy()), bits(logits))
@@ -168,7 +173,8 @@ def test_swiglu_quant(L, orc, dev):
     gu[:8] = [7.0, 7.5, -7.0, -30.0, 0.0, 100.0, -100.0, 6.999]
     dq = torch.empty((topk, d), dtype=torch.int8, device=dev)
     ds = torch.empty((topk, d // 32), dtype=torch.float32, device=dev)
-    ok(L.brrr_swiglu_quant(P(to_dev(gu, dev)), topk, d, P(dq), P(ds), None))
+    dgu = to_dev(gu, dev)
+    ok(L.brrr_swiglu_quant(P(dgu), topk, d, P(dq), P(ds), None))
     hq, hs, _ = orc.swiglu_quant(gu, topk, d)
     assert np.array_equal(dq.cpu().numpy(), hq) and np.array_equal(bits(ds.cpu().numpy()), bits(hs))
 
@@ -192,8 +198,8 @@ def test_attention_decode(L, orc, brrr, dev, pos, start):
     dao = torch.empty(nh * hd, dtype=torch.float32, device=dev)
     daq = torch.empty(nh * hd, dtype=torch.int8, device=dev)
     das = torch.empty(nh * hd // 32, dtype=torch.float32, device=dev)
-    ok(L.brrr_attn_decode(P(to_dev(qkv, dev)), P(dkc), P(dvc), P(to_dev(tab, dev)), P(to_dev(sinks, dev)), nh, nkv, pos, start,
-                          P(dao), P(daq), P(das), None))
+    dqkv, dtab, dsinks = to_dev(qkv, dev), to_dev(tab, dev), to_dev(sinks, dev)
+    ok(L.brrr_attn_decode(P(dqkv), P(dkc), P(dvc), P(dtab), P(dsinks), nh, nkv, pos, start, P(dao), P(daq), P(das), None))
     # oracle: rotate q and k, append, attend
     q = qkv[:nh * hd].reshape(nh, hd).copy(); k = qkv[nh * hd:(nh + nkv) * hd].reshape(nkv, hd).copy()
     v = qkv[(nh + nkv) * hd:].reshape(nkv, hd)

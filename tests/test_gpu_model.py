@@ -152,7 +152,9 @@ def test_moe_ffn_step_config1_shape(brrr, orc, dev):
                         vp(y), vp(top), vp(wts))
     dy = torch.zeros(2880, dtype=torch.float32, device=dev)
     dt = torch.zeros(4, dtype=torch.int32, device=dev); dw = torch.zeros(4, dtype=torch.float32, device=dev)
-    eng.moe_ffn_step(0, C.c_void_p(to_dev(xn, dev).data_ptr()), C.c_void_p(dy.data_ptr()), C.c_void_p(dt.data_ptr()), C.c_void_p(dw.data_ptr()))
+    dxn = to_dev(xn, dev)
+    torch.cuda.synchronize()
+    eng.moe_ffn_step(0, C.c_void_p(dxn.data_ptr()), C.c_void_p(dy.data_ptr()), C.c_void_p(dt.data_ptr()), C.c_void_p(dw.data_ptr()))
     assert np.array_equal(dt.cpu().numpy(), top)
     assert np.array_equal(bits(dw.cpu().numpy()), bits(wts))
     assert np.array_equal(bits(dy.cpu().numpy()), bits(y))
