@@ -160,6 +160,8 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline / parity leg")
     ap.add_argument("--no-stages", action="store_true", help="skip the per-kernel-class timing")
+    ap.add_argument("--layers", type=int, default=24, help="profiling aid: fewer layers (not the benchmark workload)")
+    ap.add_argument("--vocab", type=int, default=201088, help="profiling aid: smaller vocabulary (not the benchmark workload)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -181,8 +183,13 @@ def main():
         import torch.distributed as dist
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
 
-    eng = B.Engine.synth(B.gptoss_20b_cfg(), SEED, device=local_rank)
-    prompt = S.synth_prompt(SEED + rank, PROMPT_LEN, 199999)   # every replica decodes its own sequence
+    cfg = B.gptoss_20b_cfg()
+    reduced = args.layers != 24 or args.vocab != 201088
+    if reduced:                                                 # small case for profiler captures only
+        cfg = B.make_cfg(2880, args.layers, 64, 8, 32, 4, args.vocab)
+        args.no_cpu = True
+    eng = B.Engine.synth(cfg, SEED, device=local_rank)
+    prompt = S.synth_prompt(SEED + rank, PROMPT_LEN, min(199999, args.vocab))   # every replica decodes its own sequence
     first = eng.prefill(prompt)
     stream = torch.cuda.ExternalStream(eng.stream, device=torch.device("cuda", local_rank))
 
@@ -247,7 +254,7 @@ def main():
         "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": args.warmup,
         "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "int8xfp4->int32,f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD, "arch": "24 layers, d 2880, 64/8 heads x 64, 32 experts top-4, vocab 201088",
+        "config": {"workload": WORKLOAD if not reduced else f"PROFILING CASE ({args.layers} layers, vocab {args.vocab}) - not the benchmark workload", "arch": "24 layers, d 2880, 64/8 heads x 64, 32 experts top-4, vocab 201088",
                    "positions": [PROMPT_LEN, PROMPT_LEN + K], "parallelism": f"replicas x{world}" if world > 1 else "single GPU",
                    "l2": "inputs larger than L2 (2.66 GB of weights streamed per step)"},
         "e2e": {"value": world * K / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 4},

@@ -41,6 +41,7 @@ SIGNATURES = {
     "brrr_stage_count": (_I, []),
     "brrr_stage_name": (C.c_char_p, [_I]),
     "brrr_stage_time": (_I, [_P, _I, C.c_uint32, _I, C.POINTER(C.c_float), C.POINTER(C.c_uint64), C.POINTER(_I)]),
+    "brrr_debug_stamps": (_I, [_P, _P]),
     "brrr_quant_q8": (_I, [_P, _I, _P, _P, _P]),
     "brrr_rmsnorm_quant": (_I, [_P, _P, C.c_float, _I, _P, _P, _P, _P]),
     "brrr_q8mat_from_bf16": (_I, [_P, _I, _I, C.POINTER(_P), _P]),

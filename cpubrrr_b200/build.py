@@ -49,6 +49,8 @@ def build(force=False, verbose=False):
     nvcc = _nvcc()
     os.makedirs(OBJ, exist_ok=True)
     extra = ["-Xptxas", "-v"] if verbose else []
+    if os.environ.get("BRRR_TIMELINE"):
+        extra.append("-DBRRR_TIMELINE")
 
     def compile_one(src):
         obj = os.path.join(OBJ, src.replace(".cu", ".o"))

@@ -45,6 +45,56 @@ __device__ __forceinline__ float block_rms_inv(const float *x, int n, float eps,
     return *sh_out;
 }
 
+// Block-wide RMSNorm + per-32 Q8 quantisation of x[0..n) into a staged activation image.
+// Each thread owns 4 consecutive elements (one 32-bit word of quants), 8 consecutive threads own
+// a 32-block, so a block's amax needs three shuffles.  norm_w == nullptr: quantise x as it is.
+//   NQ_Q8:      xp[b*4+j] = {elements 4j..4j+3, elements 16+4j..16+4j+3}   (Q8 GEMV image)
+//   NQ_MX:      xp[b*4+j] = the same two words byte-interleaved for the MXFP4 lane dot
+//   NQ_NATURAL: quants in element order to (int8_t*)xp, scales to xsc       (global buffers)
+// xf: n floats of shared scratch.  Must be called by all threads; nthreads % 32 == 0, n % 32 == 0,
+// x 16-byte aligned.  Ends with the image complete but NOT yet synchronised.
+enum { NQ_Q8 = 0, NQ_MX = 1, NQ_NATURAL = 2 };
+template <int LAYOUT>
+__device__ __forceinline__ void block_norm_quant(const float *__restrict__ x, const float *__restrict__ norm_w, float eps, int n,
+                                                 float *xf, int2 *xp, float *xsc, float *inv_sh, int tid, int nthreads) {
+    const int groups = n >> 2;
+    const float4 *x4 = reinterpret_cast<const float4 *>(x);
+    float4 *xf4 = reinterpret_cast<float4 *>(xf);
+    for (int g = tid; g < groups; g += nthreads) xf4[g] = x4[g];
+    __syncthreads();
+    float inv = 1.0f;
+    if (norm_w) inv = block_rms_inv(xf, n, eps, inv_sh);
+    const int npass = (groups + nthreads - 1) / nthreads;
+    for (int p = 0; p < npass; p++) {
+        const int g = tid + p * nthreads;
+        const bool live = g < groups;
+        float4 v = live ? xf4[g] : make_float4(0.f, 0.f, 0.f, 0.f);
+        if (norm_w && live) {
+            float4 w = reinterpret_cast<const float4 *>(norm_w)[g];
+            v.x = __fmul_rn(__fmul_rn(v.x, inv), w.x); v.y = __fmul_rn(__fmul_rn(v.y, inv), w.y);
+            v.z = __fmul_rn(__fmul_rn(v.z, inv), w.z); v.w = __fmul_rn(__fmul_rn(v.w, inv), w.w);
+        }
+        float amax = fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w)));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 2));
+        amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 4));
+        const float sc = __fdiv_rn(fmaxf(amax, 1e-12f), 127.0f);
+        uint32_t word = (uint32_t)(brrr_q8_round(v.x, sc) & 0xFF) | ((uint32_t)(brrr_q8_round(v.y, sc) & 0xFF) << 8) |
+                        ((uint32_t)(brrr_q8_round(v.z, sc) & 0xFF) << 16) | ((uint32_t)(brrr_q8_round(v.w, sc) & 0xFF) << 24);
+        const int t = g & 7, b = g >> 3;
+        if (LAYOUT == NQ_MX) {
+            uint32_t other = __shfl_xor_sync(0xffffffffu, word, 4);
+            if (live && t < 4)
+                xp[b * 4 + t] = make_int2((int)brrr_prmt(word, other, 0x5140u), (int)brrr_prmt(word, other, 0x7362u));
+        } else if (LAYOUT == NQ_Q8) {
+            if (live) reinterpret_cast<int *>(&xp[b * 4 + (t & 3)])[t >> 2] = (int)word;
+        } else {
+            if (live) reinterpret_cast<uint32_t *>(xp)[g] = word;
+        }
+        if (live && t == 0) xsc[b] = sc;
+    }
+}
+
 // gpt-oss clamped SwiGLU: xg = min(g, 7), yu = clamp(u, -7, 7), (xg / (1 + exp(-1.702 xg))) (yu + 1)
 __device__ __forceinline__ float swiglu_oai(float g, float u) {
     float xg = fminf(g, 7.0f);

@@ -90,47 +90,56 @@ __device__ __forceinline__ int brrr_mx_lane_dot(uint32_t w, int xa, int xb) {
 }
 
 // ---------------------------------------------------------------- layouts
-// Q8 matrix, rows % 4 == 0, cols % 64 == 0, np = cols / 64 block pairs.
-//   wq: [rows/4][np][4 rows][2 parity][4 lanes][8 B]; the 8 bytes of (row, block b = 2i+p, lane j)
-//       are w[32b+4j .. +3] then w[32b+16+4j .. +3]
-//   ws: [rows/4][np][4 rows][2 parity] f32 block scales
+// Both weight formats are stored as fixed-size *units* that hold everything 16 rows need for two
+// consecutive 32-blocks (a block pair): quants and scales together, so one contiguous stream
+// feeds a CTA and any run of units is a valid bulk-copy source (unit sizes are multiples of 16).
+// Units are ordered [row / 16][pair]; a CTA that owns consecutive 16-row groups owns one
+// contiguous byte range.
+//
+// Q8 unit (1152 B), rows padded to a multiple of 16, cols % 64 == 0, np = cols / 64:
+//   bytes [0, 1024):    [16 rows][2 parity][4 lanes][8 B]; the 8 bytes of (row, block b = 2i+p,
+//                       lane j) are w[32b+4j .. +3] then w[32b+16+4j .. +3]
+//   bytes [1024, 1152): [16 rows][2 parity] f32 block scales
 // A warp (4 rows x 8 chains) reads 256 contiguous bytes per step.
+constexpr int Q8_UNIT = 1152;
+constexpr int Q8_UNIT_SCALES = 1024;
 struct Q8Dev {
-    int8_t *wq;
-    float *ws;
-    int rows, cols;
+    uint8_t *data;
+    int rows, cols;      // logical shape; storage holds ceil(rows / 16) * 16 rows
 };
-__host__ __device__ __forceinline__ size_t q8_woff(int row, int pair, int np) {
-    return ((size_t)(row >> 2) * np + pair) * 256 + (size_t)(row & 3) * 64;
-}
-__host__ __device__ __forceinline__ size_t q8_soff(int row, int pair, int np) {
-    return ((size_t)(row >> 2) * np + pair) * 8 + (size_t)(row & 3) * 2;
-}
+__host__ __device__ __forceinline__ int q8_urows(int rows) { return (rows + 15) >> 4; }
+__host__ __device__ __forceinline__ size_t q8_bytes(int rows, int cols) { return (size_t)q8_urows(rows) * (cols / 64) * Q8_UNIT; }
+__host__ __device__ __forceinline__ size_t q8_unit_off(int urow, int pair, int np) { return ((size_t)urow * np + pair) * Q8_UNIT; }
 
-// MXFP4 matrix, rows % 8 == 0, blocks % 2 == 0, np = blocks / 2.
-//   nib:  [rows/8][np][8 rows][4 lanes][8 B]; the 8 bytes of (row, pair i, lane j) are the lane
-//         word of block 2i then of block 2i+1
-//   exps: [rows/8][np][8 rows][2] e8m0 bytes
+// MXFP4 unit (544 B), rows % 16 == 0, blocks % 2 == 0, np = blocks / 2:
+//   bytes [0, 512):   [16 rows][4 lanes][8 B]; the 8 bytes of (row, pair i, lane j) are the lane
+//                     word (bytes 4j..4j+3 of the 16 nibble bytes) of block 2i then of block 2i+1
+//   bytes [512, 544): [16 rows][2] e8m0 bytes
 // A warp (8 rows x 4 lanes) reads 256 contiguous bytes per step.
+constexpr int MX_UNIT = 544;
+constexpr int MX_UNIT_EXPS = 512;
 struct MxDev {
-    uint8_t *nib;
-    uint8_t *exps;
+    uint8_t *data;
     int rows, blocks;
 };
-__host__ __device__ __forceinline__ size_t mx_noff(int row, int pair, int np) {
-    return ((size_t)(row >> 3) * np + pair) * 256 + (size_t)(row & 7) * 32;
-}
-__host__ __device__ __forceinline__ size_t mx_eoff(int row, int pair, int np) {
-    return ((size_t)(row >> 3) * np + pair) * 16 + (size_t)(row & 7) * 2;
-}
+__host__ __device__ __forceinline__ size_t mx_bytes(int rows, int blocks) { return (size_t)(rows / 16) * (blocks / 2) * MX_UNIT; }
+__host__ __device__ __forceinline__ size_t mx_unit_off(int urow, int pair, int np) { return ((size_t)urow * np + pair) * MX_UNIT; }
 
 // Device-resident decode state: the token and position of the step being run, the running
-// argmax of the vocabulary projection and the ring of emitted tokens.
+// argmax of the vocabulary projection, the ring of emitted tokens and a sticky error word.
 struct DevState {
     uint32_t tok;
     uint32_t pos;
     uint32_t n_out;
     uint32_t router_done;          // CTA arrival counter of the router kernel
     unsigned long long best;       // (orderable logit << 32) | ~index
+    uint32_t err;                  // DEV_ERR_* (0 = none); set by a kernel whose bounded wait ran out
+    uint32_t pad;
     uint32_t out[BRRR_MAXSEQ];
+    long long stamps[32];          // optional in-kernel clock stamps (timeline builds only)
 };
+#ifdef BRRR_TIMELINE
+#define BRRR_STAMP(state, i) do { if ((state) && threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0) (state)->stamps[i] = clock64(); } while (0)
+#else
+#define BRRR_STAMP(state, i) do { } while (0)
+#endif

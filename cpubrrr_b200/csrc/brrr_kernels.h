@@ -8,7 +8,7 @@ namespace brrr {
 
 // ---- elementwise / small stages (kernels_small.cu)
 void launch_quant_q8(const float *x, int n, int8_t *q, float *s, cudaStream_t st);
-void launch_rmsnorm_quant(const float *x, const float *w, float eps, int n, float *xn, int8_t *q, float *s, cudaStream_t st);
+cudaError_t launch_rmsnorm_quant(const float *x, const float *w, float eps, int n, float *xn, int8_t *q, float *s, bool pdl, cudaStream_t st);
 void launch_embed(const uint16_t *embd, int d, const DevState *state, float *x, cudaStream_t st);
 void launch_swiglu_quant(const float *gu, int topk, int d, int8_t *hq, float *hs, cudaStream_t st);
 void launch_finish_token(DevState *state, cudaStream_t st);
@@ -19,27 +19,42 @@ void launch_synth(uint64_t seed, uint32_t layer, uint32_t kind, uint32_t type, u
 void launch_q8_pack(const uint16_t *w_bf16, int rows_src, int row0_dst, Q8Dev m, cudaStream_t st);
 void launch_q8_export(Q8Dev m, int8_t *q, float *s, cudaStream_t st);
 enum { Q8_EPI_PLAIN = 0, Q8_EPI_BIAS = 1, Q8_EPI_RESID_BIAS = 2, Q8_EPI_HEAD = 3 };
-void launch_q8_gemv(Q8Dev m, const int8_t *xq, const float *xs, const float *bias, float *y, int epi, DevState *state, cudaStream_t st);
+// Streaming GEMV.  x_f32 != nullptr: RMSNorm(x_f32, norm_w, eps) + Q8 quantisation in the prologue;
+// otherwise the Q8 activation (xq, xs) is used.  pdl: launch with programmatic stream serialization.
+cudaError_t launch_q8_stream(Q8Dev m, const float *x_f32, const float *norm_w, float eps, const int8_t *xq, const float *xs,
+                             const float *bias, float *y, int epi, DevState *state, bool pdl, cudaStream_t st);
+
+// Direct-from-global GEMV for very large matrices (the vocabulary head); activation pre-quantised.
+cudaError_t launch_q8_direct(Q8Dev m, const int8_t *xq, const float *xs, const float *bias, float *y, int epi, DevState *state, bool pdl, cudaStream_t st);
 
 // ---- MXFP4 matrices (kernels_mx.cu)
 void launch_mx_pack(const uint8_t *raw, MxDev m, cudaStream_t st);
 void launch_mx_gemv(MxDev m, int row0, int nrows, const int8_t *xq, const float *xs, float *y, int32_t *blockdots, cudaStream_t st);
-void launch_gate_up(MxDev gate, MxDev up, const float *gate_b, const float *up_b, const int32_t *top, int topk, int d,
-                    const int8_t *xq, const float *xs, float *gu, cudaStream_t st);
-void launch_down_combine(MxDev down, const float *down_b, const int32_t *top, const float *wts, int topk, int d,
-                         const int8_t *hq, const float *hs, float *x, cudaStream_t st);
+// gate/up of the selected experts + clamped SwiGLU + Q8 of h.  Activation: x_f32 with norm_w
+// (RMSNorm + quantise), x_f32 without norm_w (quantise only), or (xq, xs).  gu nullable.
+cudaError_t launch_gate_up(MxDev gate, MxDev up, const float *gate_b, const float *up_b, const int32_t *top, int topk, int d,
+                           const float *x_f32, const float *norm_w, float eps, const int8_t *xq, const float *xs,
+                           int8_t *hq, float *hs, float *gu, DevState *state, bool pdl, cudaStream_t st);
+cudaError_t launch_down_combine(MxDev down, const float *down_b, const int32_t *top, const float *wts, int topk, int d,
+                                const int8_t *hq, const float *hs, float *x, DevState *state, bool pdl, cudaStream_t st);
 
 // ---- router (kernels_router.cu)
+// The router matrix is used in a tiled layout: [32-expert group][tile][32][RT_STRIDE] floats.
+constexpr int RT_TJ = 128;                       // tile width (elements of d)
+constexpr int RT_STRIDE = RT_TJ + 4;             // padded row stride in floats
+constexpr int RT_TILE_FLOATS = 32 * RT_STRIDE;
+size_t router_packed_floats(int ne, int d);
+void launch_router_pack(const float *W, int ne, int d, float *out, cudaStream_t st);
 // x_in is the residual stream when norm_w != nullptr (RMSNorm applied first) or an already
-// normalised vector otherwise.  xq_out/xs_out nullable.
-void launch_ffn_in(const float *x_in, const float *norm_w, float eps, int d, int8_t *xq_out, float *xs_out,
-                   const float *W, const float *b, int ne, int topk, float *logits, int32_t *top, float *wts,
-                   unsigned int *counter, cudaStream_t st);
-int ffn_in_init();   // one-time kernel attribute set-up; returns cudaError_t
+// normalised vector otherwise.
+cudaError_t launch_ffn_in(const float *x_in, const float *norm_w, float eps, int d, const float *Wt, const float *b, int ne, int topk,
+                          float *logits, int32_t *top, float *wts, unsigned int *counter, DevState *state, bool pdl, cudaStream_t st);
 
 // ---- attention (kernels_attn.cu)
-// pos is read from state when state != nullptr, else pos_val.  window = 0 means full attention.
-void launch_attn_decode(const float *qkv, float *kc, float *vc, const float *rope, const float *sinks, int nh, int nkv,
-                        const DevState *state, int pos_val, int window, float *ao, int8_t *aq, float *as, cudaStream_t st);
+// KV cache layout [n_head_kv][BRRR_MAXSEQ][64].  pos is read from state when state != nullptr,
+// else pos_val.  window = 0 means full attention.
+cudaError_t launch_attn_decode(const float *qkv, float *kc, float *vc, const float *rope, const float *sinks, int nh, int nkv,
+                               const DevState *state, int pos_val, int window, float *ao, int8_t *aq, float *as,
+                               DevState *err_state, bool pdl, cudaStream_t st);
 
 }  // namespace brrr

@@ -1,7 +1,7 @@
 // Bulk asynchronous copies (TMA, untiled cp.async.bulk) with mbarrier completion, programmatic
 // dependent launch, and the launch helper shared by the streaming kernels.
 //
-// Every wait is bounded: after WAIT_LIMIT failed polls the waiter records an error code in the
+// Every wait is bounded (Waiter): when a wait runs out the waiter records an error code in the
 // device state and carries on (results are then garbage, but the kernel terminates and the host
 // reports the failure).  No copy here uses cluster multicast.
 #pragma once
@@ -38,16 +38,33 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     return ok != 0;
 }
 
-constexpr uint32_t WAIT_LIMIT = 1u << 22;
+constexpr long long WAIT_CYCLES = 2000000000ll;      // about one second of SM clock
 enum { DEV_ERR_NONE = 0, DEV_ERR_COPY_TIMEOUT = 1 };
 
-// Bounded wait for phase `parity` of `bar`; on timeout records the error once and returns false.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, uint32_t *err_word) {
-    for (uint32_t it = 0; it < WAIT_LIMIT; it++)
+// Bounded waiting on copy barriers.  A wait that exceeds WAIT_CYCLES records the error once in
+// the device state and marks the thread dead: every later wait returns at once, so a lost copy
+// costs about a second, not a hang.  A kernel that starts with the error word already set skips
+// its waits altogether (poison_if_failed).
+struct Waiter {
+    uint32_t *err;
+    bool dead;
+    __device__ __forceinline__ explicit Waiter(uint32_t *e) : err(e), dead(false) {}
+    __device__ __forceinline__ void poison_if_failed() {
+        if (err && *reinterpret_cast<volatile uint32_t *>(err) != 0u) dead = true;
+    }
+    __device__ __forceinline__ bool wait(uint64_t *bar, uint32_t parity) {
+        if (dead) return false;
         if (mbar_try_wait(bar, parity)) return true;
-    if (err_word) atomicCAS(err_word, (uint32_t)DEV_ERR_NONE, (uint32_t)DEV_ERR_COPY_TIMEOUT);
-    return false;
-}
+        const long long t0 = clock64();
+        do {
+            for (int i = 0; i < 128; i++)
+                if (mbar_try_wait(bar, parity)) return true;
+        } while (clock64() - t0 < WAIT_CYCLES);
+        dead = true;
+        if (err) atomicCAS(err, (uint32_t)DEV_ERR_NONE, (uint32_t)DEV_ERR_COPY_TIMEOUT);
+        return false;
+    }
+};
 
 // Programmatic dependent launch.  pdl_wait(): block until the preceding kernel in the stream has
 // completed and its writes are visible.  pdl_trigger(): allow the next kernel's CTAs to be

@@ -22,16 +22,16 @@ extern "C" int brrr_quant_q8(const float *d_x, int n, int8_t *d_q, float *d_s, v
 
 extern "C" int brrr_rmsnorm_quant(const float *d_x, const float *d_w, float eps, int n, float *d_xn, int8_t *d_q, float *d_s, void *stream) {
     if (!d_x || !d_w || !d_q || !d_s || n <= 0 || n % 32 || n > 8192) return BRRR_ERR_ARG;
-    launch_rmsnorm_quant(d_x, d_w, eps, n, d_xn, d_q, d_s, (cudaStream_t)stream);
+    if (launch_rmsnorm_quant(d_x, d_w, eps, n, d_xn, d_q, d_s, false, (cudaStream_t)stream) != cudaSuccess) return BRRR_ERR_CUDA;
     return check_launch();
 }
 
 extern "C" int brrr_q8mat_from_bf16(const uint16_t *d_w, int rows, int cols, brrr_q8mat **out, void *stream) {
-    if (!d_w || !out || rows <= 0 || rows % 4 || cols <= 0 || cols % 64) return BRRR_ERR_ARG;
+    if (!d_w || !out || rows <= 0 || cols <= 0 || cols % 64 || cols > 8192) return BRRR_ERR_ARG;
     brrr_q8mat *q = new brrr_q8mat();
     q->m.rows = rows; q->m.cols = cols;
-    if (cudaMalloc(&q->m.wq, (size_t)rows * cols) != cudaSuccess) { delete q; return BRRR_ERR_NOMEM; }
-    if (cudaMalloc(&q->m.ws, (size_t)rows * (cols / 32) * 4) != cudaSuccess) { cudaFree(q->m.wq); delete q; return BRRR_ERR_NOMEM; }
+    if (cudaMalloc(&q->m.data, q8_bytes(rows, cols)) != cudaSuccess) { delete q; return BRRR_ERR_NOMEM; }
+    if (cudaMemsetAsync(q->m.data, 0, q8_bytes(rows, cols), (cudaStream_t)stream) != cudaSuccess) { cudaFree(q->m.data); delete q; return BRRR_ERR_CUDA; }
     launch_q8_pack(d_w, rows, 0, q->m, (cudaStream_t)stream);
     *out = q;
     return check_launch();
@@ -45,22 +45,21 @@ extern "C" int brrr_q8mat_export(const brrr_q8mat *m, int8_t *d_q, float *d_s, v
 
 extern "C" void brrr_q8mat_free(brrr_q8mat *m) {
     if (!m) return;
-    cudaFree(m->m.wq); cudaFree(m->m.ws);
+    cudaFree(m->m.data);
     delete m;
 }
 
 extern "C" int brrr_q8_matvec(const brrr_q8mat *w, const int8_t *d_xq, const float *d_xs, float *d_y, void *stream) {
     if (!w || !d_xq || !d_xs || !d_y) return BRRR_ERR_ARG;
-    launch_q8_gemv(w->m, d_xq, d_xs, nullptr, d_y, Q8_EPI_PLAIN, nullptr, (cudaStream_t)stream);
+    if (launch_q8_stream(w->m, nullptr, nullptr, 0.0f, d_xq, d_xs, nullptr, d_y, Q8_EPI_PLAIN, nullptr, false, (cudaStream_t)stream) != cudaSuccess) return BRRR_ERR_CUDA;
     return check_launch();
 }
 
 extern "C" int brrr_mxmat_from_gguf(const uint8_t *d_raw, int rows, int blocks, brrr_mxmat **out, void *stream) {
-    if (!d_raw || !out || rows <= 0 || rows % 8 || blocks <= 0 || blocks % 2) return BRRR_ERR_ARG;
+    if (!d_raw || !out || rows <= 0 || rows % 16 || blocks <= 0 || blocks % 2) return BRRR_ERR_ARG;
     brrr_mxmat *x = new brrr_mxmat();
     x->m.rows = rows; x->m.blocks = blocks;
-    if (cudaMalloc(&x->m.nib, (size_t)rows * blocks * 16) != cudaSuccess) { delete x; return BRRR_ERR_NOMEM; }
-    if (cudaMalloc(&x->m.exps, (size_t)rows * blocks) != cudaSuccess) { cudaFree(x->m.nib); delete x; return BRRR_ERR_NOMEM; }
+    if (cudaMalloc(&x->m.data, mx_bytes(rows, blocks)) != cudaSuccess) { delete x; return BRRR_ERR_NOMEM; }
     launch_mx_pack(d_raw, x->m, (cudaStream_t)stream);
     *out = x;
     return check_launch();
@@ -68,7 +67,7 @@ extern "C" int brrr_mxmat_from_gguf(const uint8_t *d_raw, int rows, int blocks, 
 
 extern "C" void brrr_mxmat_free(brrr_mxmat *m) {
     if (!m) return;
-    cudaFree(m->m.nib); cudaFree(m->m.exps);
+    cudaFree(m->m.data);
     delete m;
 }
 
@@ -83,12 +82,18 @@ extern "C" int brrr_router_topk(const float *d_w, const float *d_b, const float 
     if (!d_w || !d_xn || !d_logits || !d_top || !d_wts || ne <= 0 || d <= 0 || d > 8192 || topk <= 0 || topk > 8 || topk > ne) return BRRR_ERR_ARG;
     static unsigned int *counter = nullptr;   // arrival counter of the router CTAs (self-resetting)
     if (!counter) {
-        if (ffn_in_init() != 0) return BRRR_ERR_CUDA;
         if (cudaMalloc(&counter, sizeof(unsigned int)) != cudaSuccess) return BRRR_ERR_NOMEM;
         if (cudaMemset(counter, 0, sizeof(unsigned int)) != cudaSuccess) return BRRR_ERR_CUDA;
     }
-    launch_ffn_in(d_xn, nullptr, 0.0f, d, nullptr, nullptr, d_w, d_b, ne, topk, d_logits, d_top, d_wts, counter, (cudaStream_t)stream);
-    return check_launch();
+    if (d % 64) return BRRR_ERR_ARG;
+    // stage-level call: re-lay the natural [ne][d] matrix into the tiled form first
+    float *wt = nullptr;
+    if (cudaMalloc(&wt, router_packed_floats(ne, d) * sizeof(float)) != cudaSuccess) return BRRR_ERR_NOMEM;
+    launch_router_pack(d_w, ne, d, wt, (cudaStream_t)stream);
+    cudaError_t e = launch_ffn_in(d_xn, nullptr, 0.0f, d, wt, d_b, ne, topk, d_logits, d_top, d_wts, counter, nullptr, false, (cudaStream_t)stream);
+    if (e == cudaSuccess) e = cudaStreamSynchronize((cudaStream_t)stream);
+    cudaFree(wt);
+    return e == cudaSuccess ? check_launch() : BRRR_ERR_CUDA;
 }
 
 extern "C" int brrr_swiglu_quant(const float *d_gu, int topk, int d, int8_t *d_hq, float *d_hs, void *stream) {
@@ -102,7 +107,7 @@ extern "C" int brrr_attn_decode(const float *d_qkv, float *d_kc, float *d_vc, co
     if (!d_qkv || !d_kc || !d_vc || !d_rope || !d_sinks || !d_ao || !d_aq || !d_as) return BRRR_ERR_ARG;
     if (n_head <= 0 || n_head_kv <= 0 || n_head % n_head_kv || pos < 0 || pos >= BRRR_MAXSEQ || start < 0 || start > pos) return BRRR_ERR_ARG;
     int window = start > 0 ? pos - start + 1 : 0;
-    launch_attn_decode(d_qkv, d_kc, d_vc, d_rope, d_sinks, n_head, n_head_kv, nullptr, pos, window, d_ao, d_aq, d_as, (cudaStream_t)stream);
+    if (launch_attn_decode(d_qkv, d_kc, d_vc, d_rope, d_sinks, n_head, n_head_kv, nullptr, pos, window, d_ao, d_aq, d_as, nullptr, false, (cudaStream_t)stream) != cudaSuccess) return BRRR_ERR_CUDA;
     return check_launch();
 }
 

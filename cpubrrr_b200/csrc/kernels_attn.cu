@@ -7,69 +7,138 @@
 //   mx = max(sink, scores); den = exp(sink-mx) + sum_t exp(s_t-mx), t ascending, serial
 //   out[u] = (sum_t fma(v[t][u], p_t, .), t ascending, serial) * (1/den)
 // The serial sums are one thread each (64 output dims + 1 denominator).
+//
+// The cache is laid out [kv head][position][64] so the window of one head is one contiguous
+// range; it is brought into shared memory in tiles of 128 positions by bulk asynchronous copies
+// issued before the kernel waits on its predecessor (the cached positions are older than this
+// token).  The current position's k and v never come from the cache: every head recomputes them.
 #include "brrr_kernels.h"
 #include "brrr_block.cuh"
+#include "brrr_tma.cuh"
 
 namespace brrr {
 
 constexpr int HD = 64;
 constexpr int AT_THREADS = 256;
+constexpr int AT_TILE = 128;                       // positions per tile
+constexpr int AT_SLOTS = 2;                        // ring depth per tensor
+constexpr size_t AT_TILE_BYTES = (size_t)AT_TILE * HD * sizeof(float);
 
-__global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(const float *__restrict__ qkv, float *__restrict__ kc, float *__restrict__ vc,
-                                                                 const float *__restrict__ rope, const float *__restrict__ sinks, int nh, int nkv,
-                                                                 const DevState *__restrict__ state, int pos_val, int window,
-                                                                 float *__restrict__ ao, int8_t *__restrict__ aq, float *__restrict__ as) {
+struct AttnArgs {
+    const float *qkv;
+    float *kc, *vc;          // [nkv][MAXSEQ][64]
+    const float *rope, *sinks;
+    int nh, nkv;
+    const DevState *state;
+    int pos_val, window;
+    float *ao;
+    int8_t *aq;
+    float *as;
+    DevState *err_state;
+};
+
+__global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(AttnArgs a) {
+    extern __shared__ __align__(128) unsigned char smraw[];
+    float *ktiles = reinterpret_cast<float *>(smraw);                                   // [AT_SLOTS][128][64]
+    float *vtiles = reinterpret_cast<float *>(smraw + AT_TILE_BYTES * AT_SLOTS);
+    float *sc = reinterpret_cast<float *>(smraw + AT_TILE_BYTES * AT_SLOTS * 2);         // [MAXSEQ]
+    uint64_t *kbar = reinterpret_cast<uint64_t *>(sc + BRRR_MAXSEQ);
+    uint64_t *vbar = kbar + AT_SLOTS;
     __shared__ float q[HD], kcur[HD], vcur[HD];
-    __shared__ float sc[BRRR_MAXSEQ];
     __shared__ float red[AT_THREADS / 32];
     __shared__ float den_sh;
     const int h = blockIdx.x, tid = threadIdx.x;
-    const int group = nh / nkv, kvh = h / group;
-    const int pos = state ? (int)state->pos : pos_val;
-    const int start = window > 0 ? max(pos - (window - 1), 0) : 0;
-    const int n = pos - start + 1;
-    const float sink = sinks[h];
+    const int group = a.nh / a.nkv, kvh = h / group;
+    uint32_t *err = a.err_state ? &a.err_state->err : nullptr;
+    Waiter waiter(err);
+
+    // The position is an input of this step (written before the graph launch or by the previous
+    // step's last kernel), never by the immediate predecessor, so it may be read before the wait.
+    const int pos = a.state ? (int)a.state->pos : a.pos_val;
+    const int start = a.window > 0 ? max(pos - (a.window - 1), 0) : 0;
+    const int n = pos - start + 1;                  // keys including the current one
+    const int ncached = n - 1;                      // keys that come from the cache
+    const int ntiles = (ncached + AT_TILE - 1) / AT_TILE;
+    const float *kbase = a.kc + ((size_t)kvh * BRRR_MAXSEQ + start) * HD;
+    const float *vbase = a.vc + ((size_t)kvh * BRRR_MAXSEQ + start) * HD;
+
+    auto issue = [&](const float *base, float *tiles, uint64_t *bars, int t) {     // thread 0 only
+        int slot = t % AT_SLOTS, cnt = min(AT_TILE, ncached - t * AT_TILE);
+        mbar_expect_tx(&bars[slot], (uint32_t)cnt * HD * 4);
+        bulk_g2s(tiles + (size_t)slot * AT_TILE * HD, base + (size_t)t * AT_TILE * HD, (uint32_t)cnt * HD * 4, &bars[slot]);
+    };
+    if (tid == 0) {
+        for (int s = 0; s < AT_SLOTS; s++) { mbar_init(&kbar[s], 1); mbar_init(&vbar[s], 1); }
+        mbar_fence_init();
+        for (int t = 0; t < min(AT_SLOTS, ntiles); t++) { issue(kbase, ktiles, kbar, t); issue(vbase, vtiles, vbar, t); }
+    }
+    pdl_wait();          // qkv projection done
+    pdl_trigger();
+    waiter.poison_if_failed();
 
     // ---- RoPE (NeoX halves, table holds cos*mscale / sin*mscale) on q and k; v passes through
+    const float sink = a.sinks[h];
     if (tid < 64) {
-        const float *src = tid < 32 ? qkv + h * HD : qkv + (nh + kvh) * HD;
+        const float *src = tid < 32 ? a.qkv + h * HD : a.qkv + (a.nh + kvh) * HD;
         float *dst = tid < 32 ? q : kcur;
         int i = tid & 31;
-        float c = rope[((size_t)pos * 32 + i) * 2], s = rope[((size_t)pos * 32 + i) * 2 + 1];
-        float a = src[i], b = src[32 + i];
-        dst[i] = __fsub_rn(__fmul_rn(a, c), __fmul_rn(b, s));
-        dst[32 + i] = __fadd_rn(__fmul_rn(b, c), __fmul_rn(a, s));
+        float c = a.rope[((size_t)pos * 32 + i) * 2], s = a.rope[((size_t)pos * 32 + i) * 2 + 1];
+        float x0 = src[i], x1 = src[32 + i];
+        dst[i] = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
+        dst[32 + i] = __fadd_rn(__fmul_rn(x1, c), __fmul_rn(x0, s));
     } else if (tid < 128) {
-        vcur[tid - 64] = qkv[(nh + nkv + kvh) * HD + (tid - 64)];
+        vcur[tid - 64] = a.qkv[(a.nh + a.nkv + kvh) * HD + (tid - 64)];
     }
     __syncthreads();
     // the first head of each KV group appends this position to the cache
     if (h % group == 0 && tid < 128) {
-        size_t o = ((size_t)pos * nkv + kvh) * HD + (tid & 63);
-        if (tid < 64) kc[o] = kcur[tid]; else vc[o] = vcur[tid - 64];
+        size_t o = ((size_t)kvh * BRRR_MAXSEQ + pos) * HD + (tid & 63);
+        if (tid < 64) a.kc[o] = kcur[tid]; else a.vc[o] = vcur[tid - 64];
     }
 
     // ---- scores: 16 threads per key
     {
         const int g = tid >> 4, c = tid & 15;
         const float q0 = q[c], q1 = q[16 + c], q2 = q[32 + c], q3 = q[48 + c];
-        for (int t0 = 0; t0 < n; t0 += AT_THREADS / 16) {
-            int t = t0 + g;
-            bool live = t < n;
-            float a = 0.0f;
-            if (live) {
-                int tp = start + t;
-                const float *kp = tp == pos ? kcur : kc + ((size_t)tp * nkv + kvh) * HD;
-                a = __fmaf_rn(kp[c], q0, a);
-                a = __fmaf_rn(kp[16 + c], q1, a);
-                a = __fmaf_rn(kp[32 + c], q2, a);
-                a = __fmaf_rn(kp[48 + c], q3, a);
+        for (int t = 0; t < ntiles; t++) {
+            const int slot = t % AT_SLOTS, cnt = min(AT_TILE, ncached - t * AT_TILE);
+            waiter.wait(&kbar[slot], (uint32_t)(t / AT_SLOTS) & 1u);
+            const float *kt = ktiles + (size_t)slot * AT_TILE * HD;
+#pragma unroll 2
+            for (int k0 = 0; k0 < cnt; k0 += AT_THREADS / 16) {
+                int kk = k0 + g;
+                bool live = kk < cnt;
+                float s = 0.0f;
+                if (live) {
+                    const float *kp = kt + kk * HD;
+                    s = __fmaf_rn(kp[c], q0, s);
+                    s = __fmaf_rn(kp[16 + c], q1, s);
+                    s = __fmaf_rn(kp[32 + c], q2, s);
+                    s = __fmaf_rn(kp[48 + c], q3, s);
+                }
+                s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, 4));
+                s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, 8));
+                s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, 1));
+                s = __fadd_rn(s, __shfl_xor_sync(0xffffffffu, s, 2));
+                if (live && c == 0) sc[t * AT_TILE + kk] = __fmul_rn(s, 0.125f);
             }
-            a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 4));
-            a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 8));
-            a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 1));
-            a = __fadd_rn(a, __shfl_xor_sync(0xffffffffu, a, 2));
-            if (live && c == 0) sc[t] = __fmul_rn(a, 0.125f);
+            if (t + AT_SLOTS < ntiles) {
+                __syncthreads();
+                if (tid == 0) { fence_proxy_async(); issue(kbase, ktiles, kbar, t + AT_SLOTS); }
+            }
+        }
+        // the current position, from this CTA's own rotated k
+        if (g == 0) {
+            float s = 0.0f;
+            s = __fmaf_rn(kcur[c], q0, s);
+            s = __fmaf_rn(kcur[16 + c], q1, s);
+            s = __fmaf_rn(kcur[32 + c], q2, s);
+            s = __fmaf_rn(kcur[48 + c], q3, s);
+            s = __fadd_rn(s, __shfl_xor_sync(0xffffu, s, 4));
+            s = __fadd_rn(s, __shfl_xor_sync(0xffffu, s, 8));
+            s = __fadd_rn(s, __shfl_xor_sync(0xffffu, s, 1));
+            s = __fadd_rn(s, __shfl_xor_sync(0xffffu, s, 2));
+            if (c == 0) sc[ncached] = __fmul_rn(s, 0.125f);
         }
     }
     __syncthreads();
@@ -88,31 +157,50 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(const float *__
 
     // ---- serial sums: thread u < 64 owns output dim u, thread 64 the denominator
     float acc = 0.0f;
-    if (tid < 64) {
-        const float *vbase = vc + ((size_t)start * nkv + kvh) * HD + tid;
-        const size_t vstride = (size_t)nkv * HD;
-#pragma unroll 8
-        for (int t = 0; t < n - 1; t++) acc = __fmaf_rn(__ldcg(vbase + (size_t)t * vstride), sc[t], acc);
-        acc = __fmaf_rn(vcur[tid], sc[n - 1], acc);          // t = pos: this token's own v
-    } else if (tid == 64) {
+    if (tid == 64) {
         float den = brrr_expf_dev(__fsub_rn(sink, mx));
 #pragma unroll 8
         for (int t = 0; t < n; t++) den = __fadd_rn(den, sc[t]);
         den_sh = den;
     }
+    for (int t = 0; t < ntiles; t++) {
+        const int slot = t % AT_SLOTS, cnt = min(AT_TILE, ncached - t * AT_TILE);
+        if (tid < 64) {
+            waiter.wait(&vbar[slot], (uint32_t)(t / AT_SLOTS) & 1u);
+            const float *vt = vtiles + (size_t)slot * AT_TILE * HD + tid;
+            const float *pt = sc + t * AT_TILE;
+#pragma unroll 8
+            for (int kk = 0; kk < cnt; kk++) acc = __fmaf_rn(vt[kk * HD], pt[kk], acc);
+        }
+        if (t + AT_SLOTS < ntiles) {
+            __syncthreads();
+            if (tid == 0) { fence_proxy_async(); issue(vbase, vtiles, vbar, t + AT_SLOTS); }
+        }
+    }
+    if (tid < 64) acc = __fmaf_rn(vcur[tid], sc[ncached], acc);          // t = pos: this token's own v
     __syncthreads();
     if (tid < 64) {
         float inv = __fdiv_rn(1.0f, den_sh);
         float o = __fmul_rn(acc, inv);
-        ao[h * HD + tid] = o;
+        a.ao[h * HD + tid] = o;
         // this head owns Q8 blocks 2h and 2h+1 of the attention output
-        warp_quant_block(o, tid & 31, aq + h * HD + (tid >> 5) * 32, as + h * 2 + (tid >> 5));
+        warp_quant_block(o, tid & 31, a.aq + h * HD + (tid >> 5) * 32, a.as + h * 2 + (tid >> 5));
     }
 }
 
-void launch_attn_decode(const float *qkv, float *kc, float *vc, const float *rope, const float *sinks, int nh, int nkv,
-                        const DevState *state, int pos_val, int window, float *ao, int8_t *aq, float *as, cudaStream_t st) {
-    attn_decode_kernel<<<nh, AT_THREADS, 0, st>>>(qkv, kc, vc, rope, sinks, nh, nkv, state, pos_val, window, ao, aq, as);
+static size_t attn_smem() { return AT_TILE_BYTES * AT_SLOTS * 2 + (size_t)BRRR_MAXSEQ * 4 + AT_SLOTS * 2 * 8; }
+
+cudaError_t launch_attn_decode(const float *qkv, float *kc, float *vc, const float *rope, const float *sinks, int nh, int nkv,
+                               const DevState *state, int pos_val, int window, float *ao, int8_t *aq, float *as,
+                               DevState *err_state, bool pdl, cudaStream_t st) {
+    AttnArgs a{qkv, kc, vc, rope, sinks, nh, nkv, state, pos_val, window, ao, aq, as, err_state};
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_smem());
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    return launch_k(attn_decode_kernel, dim3(nh), dim3(AT_THREADS), attn_smem(), st, pdl, a);
 }
 
 }  // namespace brrr

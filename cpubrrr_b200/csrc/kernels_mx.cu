@@ -2,11 +2,14 @@
 //
 // Float order of one row (fixed): 4 lane chains.  Chain j walks the blocks b = 0, 1, ...
 // accumulating fma(float(t_j(b)), 2^(e_b - 128) * xs[b], acc), t_j(b) being the exact int32
-// lane dot (brrr_mx_lane_dot); the row result is (a0+a1)+(a2+a3).  One thread owns one chain;
-// 8 rows x 4 lanes make a warp and every step of the warp is one contiguous 256-byte read
-// covering two blocks.
+// lane dot (brrr_mx_lane_dot); the row result is (a0+a1)+(a2+a3).  One thread owns one chain.
+//
+// Data movement: 64 threads (16 rows x 4 lanes) consume one 16-row unit row of one expert matrix,
+// a contiguous byte stream; a CTA runs 4 (or top-k) such streams side by side.  Thread 0 feeds
+// all of them through a shared-memory ring with bulk asynchronous copies, one mbarrier per stage.
 #include "brrr_kernels.h"
 #include "brrr_block.cuh"
+#include "brrr_tma.cuh"
 
 namespace brrr {
 
@@ -22,8 +25,10 @@ __global__ void mx_pack_kernel(const uint8_t *__restrict__ raw, MxDev m) {
     const uint8_t *src = raw + rb * 17;
     int np = m.blocks / 2;
     uint32_t w = (uint32_t)src[1 + 4 * j] | ((uint32_t)src[2 + 4 * j] << 8) | ((uint32_t)src[3 + 4 * j] << 16) | ((uint32_t)src[4 + 4 * j] << 24);
-    *reinterpret_cast<uint32_t *>(m.nib + mx_noff(row, b >> 1, np) + j * 8 + (b & 1) * 4) = w;
-    if (j == 0) m.exps[mx_eoff(row, b >> 1, np) + (b & 1)] = src[0];
+    uint8_t *unit = m.data + mx_unit_off(row >> 4, b >> 1, np);
+    int rl = row & 15;
+    *reinterpret_cast<uint32_t *>(unit + rl * 32 + j * 8 + (b & 1) * 4) = w;
+    if (j == 0) unit[MX_UNIT_EXPS + rl * 2 + (b & 1)] = src[0];
 }
 
 void launch_mx_pack(const uint8_t *raw, MxDev m, cudaStream_t st) {
@@ -35,57 +40,68 @@ void launch_mx_pack(const uint8_t *raw, MxDev m, cudaStream_t st) {
 // ---------------------------------------------------------------- activation staging
 // Shared-memory image of a Q8 activation for the MXFP4 lane dot: one int2 {xa, xb} per
 // (block, lane), bytes interleaved to the prmt output order (see brrr_mx_lane_dot).
+__device__ __forceinline__ int2 mx_interleave(uint32_t lo, uint32_t hi) {
+    return make_int2((int)brrr_prmt(lo, hi, 0x5140u), (int)brrr_prmt(lo, hi, 0x7362u));
+}
+
 __device__ __forceinline__ void mx_stage_x(const int8_t *__restrict__ xq, const float *__restrict__ xs, int nb, int2 *xp, float *xsc, int tid, int nthreads) {
     for (int idx = tid; idx < nb * 4; idx += nthreads) {
         int b = idx >> 2, j = idx & 3;
         const uint32_t *xw = reinterpret_cast<const uint32_t *>(xq + b * 32);
-        uint32_t lo = xw[j], hi = xw[4 + j];
-        xp[idx] = make_int2((int)brrr_prmt(lo, hi, 0x5140u), (int)brrr_prmt(lo, hi, 0x7362u));
+        xp[idx] = mx_interleave(xw[j], xw[4 + j]);
     }
     for (int b = tid; b < nb; b += nthreads) xsc[b] = xs[b];
 }
 
-// One lane chain over all blocks of a row.  nibp / expp point at the thread's first 8 / 2 bytes.
+// Quantise one 32-block held one value per lane straight into the staged layout.
+__device__ __forceinline__ void mx_quant_stage_block(float v, int lane, int b, int2 *xp, float *xsc) {
+    float amax = fmaxf(warp_max(fabsf(v)), 1e-12f);
+    float sc = __fdiv_rn(amax, 127.0f);
+    uint32_t q = (uint32_t)(brrr_q8_round(v, sc) & 0xFF);
+    uint32_t word = q << (8 * (lane & 3));
+    word |= __shfl_xor_sync(0xffffffffu, word, 1);
+    word |= __shfl_xor_sync(0xffffffffu, word, 2);           // lanes 4j..4j+3 hold lo word j, lanes 16+4j.. hi word j
+    uint32_t other = __shfl_xor_sync(0xffffffffu, word, 16);
+    if (lane < 16 && (lane & 3) == 0) xp[b * 4 + (lane >> 2)] = mx_interleave(word, other);
+    if (lane == 0) xsc[b] = sc;
+}
+
+// Two blocks (one pair) of one lane chain from a unit in shared memory.
 template <bool DBG>
-__device__ __forceinline__ float mx_chain(const uint8_t *__restrict__ nibp, const uint8_t *__restrict__ expp, const int2 *xpj, const float *xsc,
-                                          int np, int32_t *dbg /* [blocks][4], this lane's column */) {
-    float acc = 0.0f;
-#pragma unroll 8
-    for (int i = 0; i < np; i++) {
-        uint2 w = __ldg(reinterpret_cast<const uint2 *>(nibp + (size_t)i * 256));
-        uint32_t e2 = __ldg(reinterpret_cast<const unsigned short *>(expp + (size_t)i * 16));
-        int2 x0 = xpj[i * 8], x1 = xpj[i * 8 + 4];
-        int t0 = brrr_mx_lane_dot(w.x, x0.x, x0.y);
-        int t1 = brrr_mx_lane_dot(w.y, x1.x, x1.y);
-        if (DBG) { dbg[(2 * i) * 4] = t0; dbg[(2 * i + 1) * 4] = t1; }
-        float sv0 = __fmul_rn(brrr_e8m0_scale(e2 & 0xFFu), xsc[2 * i]);
-        float sv1 = __fmul_rn(brrr_e8m0_scale(e2 >> 8), xsc[2 * i + 1]);
-        acc = __fmaf_rn((float)t0, sv0, acc);
-        acc = __fmaf_rn((float)t1, sv1, acc);
-    }
+__device__ __forceinline__ float mx_pair_step(const unsigned char *unit, int rl, int j, const int2 *xpj, const float *xsc, int pair, float acc, int32_t *dbg) {
+    uint2 w = *reinterpret_cast<const uint2 *>(unit + rl * 32 + j * 8);
+    uint32_t e2 = *reinterpret_cast<const unsigned short *>(unit + MX_UNIT_EXPS + rl * 2);
+    int2 x0 = xpj[pair * 8], x1 = xpj[pair * 8 + 4];
+    int t0 = brrr_mx_lane_dot(w.x, x0.x, x0.y);
+    int t1 = brrr_mx_lane_dot(w.y, x1.x, x1.y);
+    if (DBG) { dbg[(2 * pair) * 4] = t0; dbg[(2 * pair + 1) * 4] = t1; }
+    acc = __fmaf_rn((float)t0, __fmul_rn(brrr_e8m0_scale(e2 & 0xFFu), xsc[2 * pair]), acc);
+    acc = __fmaf_rn((float)t1, __fmul_rn(brrr_e8m0_scale(e2 >> 8), xsc[2 * pair + 1]), acc);
     return acc;
 }
 
 // ---------------------------------------------------------------- plain matvec (stage-level / tests)
+// Reads units straight from global memory; optionally dumps the int32 block accumulators.
 template <bool DBG>
 __global__ void __launch_bounds__(256) mx_gemv_kernel(MxDev m, int row0, int nrows, const int8_t *__restrict__ xq, const float *__restrict__ xs,
                                                       float *__restrict__ y, int32_t *__restrict__ blockdots) {
-    extern __shared__ __align__(16) unsigned char smraw[];
+    extern __shared__ __align__(128) unsigned char smraw[];
     const int nb = m.blocks, np = nb / 2;
     int2 *xp = reinterpret_cast<int2 *>(smraw);
     float *xsc = reinterpret_cast<float *>(smraw + (size_t)nb * 4 * sizeof(int2));
     mx_stage_x(xq, xs, nb, xp, xsc, threadIdx.x, 256);
     __syncthreads();
-    int rl = blockIdx.x * 64 + (threadIdx.x >> 2), j = threadIdx.x & 3;
-    bool live = rl < nrows;
+    int rl_out = blockIdx.x * 64 + (threadIdx.x >> 2), j = threadIdx.x & 3;
+    bool live = rl_out < nrows;
     float acc = 0.0f;
     if (live) {
-        int row = row0 + rl;
-        acc = mx_chain<DBG>(m.nib + mx_noff(row, 0, np) + j * 8, m.exps + mx_eoff(row, 0, np), xp + j, xsc, np,
-                            DBG ? blockdots + (size_t)rl * nb * 4 + j : nullptr);
+        int row = row0 + rl_out;
+        for (int i = 0; i < np; i++)
+            acc = mx_pair_step<DBG>(m.data + mx_unit_off(row >> 4, i, np), row & 15, j, xp + j, xsc, i, acc,
+                                    DBG ? blockdots + (size_t)rl_out * nb * 4 + j : nullptr);
     }
     acc = brrr_hsum4(acc);
-    if (live && j == 0) y[rl] = acc;
+    if (live && j == 0) y[rl_out] = acc;
 }
 
 void launch_mx_gemv(MxDev m, int row0, int nrows, const int8_t *xq, const float *xs, float *y, int32_t *blockdots, cudaStream_t st) {
@@ -95,86 +111,237 @@ void launch_mx_gemv(MxDev m, int row0, int nrows, const int8_t *xq, const float 
     else mx_gemv_kernel<false><<<grid, 256, smem, st>>>(m, row0, nrows, xq, xs, y, blockdots);
 }
 
-// ---------------------------------------------------------------- gate / up of the selected experts
-// grid (ceil(d/64), 2, topk): 64 rows of expert top[z]'s gate (y = 0) or up (y = 1) matrix.
-// gu[ei][2d] = gate | up, bias added.
-__global__ void __launch_bounds__(256) gate_up_kernel(MxDev gate, MxDev up, const float *__restrict__ gate_b, const float *__restrict__ up_b,
-                                                      const int32_t *__restrict__ top, int d, const int8_t *__restrict__ xq,
-                                                      const float *__restrict__ xs, float *__restrict__ gu) {
-    extern __shared__ __align__(16) unsigned char smraw[];
-    const int nb = gate.blocks, np = nb / 2;
-    int2 *xp = reinterpret_cast<int2 *>(smraw);
-    float *xsc = reinterpret_cast<float *>(smraw + (size_t)nb * 4 * sizeof(int2));
-    mx_stage_x(xq, xs, nb, xp, xsc, threadIdx.x, 256);
-    __syncthreads();
-    const int ei = blockIdx.z, isup = blockIdx.y;
-    const int e = top[ei];
-    const MxDev &m = isup ? up : gate;
-    const float *bias = isup ? up_b : gate_b;
-    int r = blockIdx.x * 64 + (threadIdx.x >> 2), j = threadIdx.x & 3;
-    bool live = r < d;
-    float acc = 0.0f;
-    if (live) {
-        int row = e * d + r;
-        acc = mx_chain<false>(m.nib + mx_noff(row, 0, np) + j * 8, m.exps + mx_eoff(row, 0, np), xp + j, xsc, np, nullptr);
+// ---------------------------------------------------------------- multi-stream ring
+// NS streams of np units each; chunk c covers pairs [c*ch, ...) of every stream.  Stage layout:
+// [stream][ch][MX_UNIT].
+struct MxRing {
+    unsigned char *ring;
+    uint64_t *bars;
+    int ch, stages, np, ns;
+    size_t stream_bytes, stage_bytes;
+    __device__ __forceinline__ void issue(int c, const uint8_t *const *src) const {   // thread 0 only
+        int cnt = min(ch, np - c * ch), slot = c % stages;
+        mbar_expect_tx(&bars[slot], (uint32_t)cnt * MX_UNIT * ns);
+        for (int s = 0; s < ns; s++)
+            bulk_g2s(ring + stage_bytes * slot + stream_bytes * s, src[s] + (size_t)c * ch * MX_UNIT, (uint32_t)cnt * MX_UNIT, &bars[slot]);
     }
-    acc = brrr_hsum4(acc);
-    if (live && j == 0) gu[(size_t)ei * 2 * d + (size_t)isup * d + r] = __fadd_rn(acc, bias[(size_t)e * d + r]);
+};
+
+struct MxLaunchShape { int ch, stages; };
+static MxLaunchShape mx_shape(int np, int ns, size_t budget) {
+    MxLaunchShape s;
+    s.ch = np;
+    for (int c = 9; c <= 12; c++) if (np % c == 0) { s.ch = c; break; }
+    if (s.ch == np) for (int c = 8; c >= 5; c--) if (np % c == 0) { s.ch = c; break; }
+    if (s.ch == np && np > 12) s.ch = 8;
+    int nchunks = (np + s.ch - 1) / s.ch;
+    int maxs = (int)(budget / ((size_t)ns * s.ch * MX_UNIT));
+    if (maxs < 2) maxs = 2;
+    s.stages = nchunks < maxs ? nchunks : maxs;
+    return s;
 }
 
-void launch_gate_up(MxDev gate, MxDev up, const float *gate_b, const float *up_b, const int32_t *top, int topk, int d,
-                    const int8_t *xq, const float *xs, float *gu, cudaStream_t st) {
-    size_t smem = (size_t)gate.blocks * 4 * sizeof(int2) + gate.blocks * sizeof(float);
-    dim3 grid((d + 63) / 64, 2, topk);
-    gate_up_kernel<<<grid, 256, smem, st>>>(gate, up, gate_b, up_b, top, d, xq, xs, gu);
+// ---------------------------------------------------------------- gate / up + SwiGLU + quantiser
+// One CTA per (expert slot ei, 32-row block): streams 0,1 = the two gate unit rows, 2,3 = the two
+// up unit rows of expert top[ei].  The 32 gate and 32 up results (bias added) pass through the
+// clamped SwiGLU and are quantised as one Q8 block of h.
+struct GateUpArgs {
+    MxDev gate, up;
+    const float *gate_b, *up_b;
+    const int32_t *top;
+    int d;
+    const float *x_f32;      // residual stream (norm_w != null) or normalised vector (norm_w == null); null: use xq/xs
+    const float *norm_w;
+    float eps;
+    const int8_t *xq;
+    const float *xs;
+    int8_t *hq;
+    float *hs;
+    float *gu;               // nullable: [topk][2d] gate | up (bias added), for inspection
+    DevState *state;
+    int ch, stages;
+};
+
+__global__ void __launch_bounds__(256) gate_up_kernel(GateUpArgs a) {
+    extern __shared__ __align__(128) unsigned char smraw[];
+    const int nb = a.gate.blocks, np = nb / 2, tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    MxRing r;
+    r.ch = a.ch; r.stages = a.stages; r.np = np; r.ns = 4;
+    r.stream_bytes = (size_t)a.ch * MX_UNIT; r.stage_bytes = r.stream_bytes * 4;
+    r.ring = smraw;
+    float *xf = reinterpret_cast<float *>(smraw + r.stage_bytes * a.stages);   // d floats when x_f32 is given (16-byte aligned)
+    int2 *xp = reinterpret_cast<int2 *>(xf + (a.x_f32 ? a.d : 0));
+    float *xsc = reinterpret_cast<float *>(xp + nb * 4);
+    r.bars = reinterpret_cast<uint64_t *>(xsc + nb + (nb & 1));
+    __shared__ float inv_sh;
+    __shared__ float gu_s[2][32];
+    __shared__ const uint8_t *src[4];
+    uint32_t *err = a.state ? &a.state->err : nullptr;
+    Waiter waiter(err);
+    const int ei = blockIdx.y, blk32 = blockIdx.x;
+
+    if (tid == 0) {
+        for (int s = 0; s < a.stages; s++) mbar_init(&r.bars[s], 1);
+        mbar_fence_init();
+    }
+    // The activation comes from two kernels back (complete by the launch protocol), so it is
+    // normalised and quantised here, before waiting for the router that runs alongside.
+    if (a.x_f32) block_norm_quant<NQ_MX>(a.x_f32, a.norm_w, a.eps, a.d, xf, xp, xsc, &inv_sh, tid, 256);
+    pdl_wait();          // router done: top[] valid
+    pdl_trigger();
+    waiter.poison_if_failed();
+    if (!a.x_f32) mx_stage_x(a.xq, a.xs, nb, xp, xsc, tid, 256);
+    const int e = a.top[ei];
+    const int nchunks = (np + a.ch - 1) / a.ch;
+    if (tid == 0) {
+        int urow = (e * a.d + blk32 * 32) >> 4;
+        src[0] = a.gate.data + mx_unit_off(urow, 0, np);
+        src[1] = a.gate.data + mx_unit_off(urow + 1, 0, np);
+        src[2] = a.up.data + mx_unit_off(urow, 0, np);
+        src[3] = a.up.data + mx_unit_off(urow + 1, 0, np);
+        for (int c = 0; c < min(a.stages, nchunks); c++) r.issue(c, src);
+    }
+    __syncthreads();
+
+    const int sidx = tid >> 6, rl = (tid & 63) >> 2, j = tid & 3;
+    float acc = 0.0f;
+    for (int c = 0; c < nchunks; c++) {
+        const int cnt = min(a.ch, np - c * a.ch), slot = c % a.stages;
+        waiter.wait(&r.bars[slot], (uint32_t)(c / a.stages) & 1u);
+        const unsigned char *base = r.ring + r.stage_bytes * slot + r.stream_bytes * sidx;
+#pragma unroll 3
+        for (int i = 0; i < cnt; i++) acc = mx_pair_step<false>(base + (size_t)i * MX_UNIT, rl, j, xp + j, xsc, c * a.ch + i, acc, nullptr);
+        if (c + a.stages < nchunks) {
+            __syncthreads();
+            if (tid == 0) { fence_proxy_async(); r.issue(c + a.stages, src); }
+        }
+    }
+    acc = brrr_hsum4(acc);
+    const int isup = sidx >> 1, r32 = (sidx & 1) * 16 + rl;
+    if (j == 0) {
+        const float *bias = isup ? a.up_b : a.gate_b;
+        float v = __fadd_rn(acc, bias[(size_t)e * a.d + blk32 * 32 + r32]);
+        gu_s[isup][r32] = v;
+        if (a.gu) a.gu[(size_t)ei * 2 * a.d + (size_t)isup * a.d + blk32 * 32 + r32] = v;
+    }
+    __syncthreads();
+    if (warp == 0) {
+        float h = swiglu_oai(gu_s[0][lane], gu_s[1][lane]);
+        warp_quant_block(h, lane, a.hq + (size_t)ei * a.d + blk32 * 32, a.hs + ei * nb + blk32);
+    }
+}
+
+cudaError_t launch_gate_up(MxDev gate, MxDev up, const float *gate_b, const float *up_b, const int32_t *top, int topk, int d,
+                           const float *x_f32, const float *norm_w, float eps, const int8_t *xq, const float *xs,
+                           int8_t *hq, float *hs, float *gu, DevState *state, bool pdl, cudaStream_t st) {
+    GateUpArgs a{};
+    a.gate = gate; a.up = up; a.gate_b = gate_b; a.up_b = up_b; a.top = top; a.d = d;
+    a.x_f32 = x_f32; a.norm_w = norm_w; a.eps = eps; a.xq = xq; a.xs = xs; a.hq = hq; a.hs = hs; a.gu = gu; a.state = state;
+    const int nb = gate.blocks, np = nb / 2;
+    MxLaunchShape s = mx_shape(np, 4, 60 * 1024);
+    a.ch = s.ch; a.stages = s.stages;
+    size_t smem = (size_t)4 * a.ch * MX_UNIT * a.stages + (size_t)nb * 4 * 8 + (size_t)nb * 4 + (x_f32 ? (size_t)d * 4 : 0) + 8 + (size_t)a.stages * 8;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gate_up_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    return launch_k(gate_up_kernel, dim3(d / 32, topk), dim3(256), smem, st, pdl, a);
 }
 
 // ---------------------------------------------------------------- down + weighted combine
-// 16 output rows per CTA; warp (ei, half) computes 8 rows of expert top[ei]; then one thread per
-// row folds s = x; s += wts[ei] * (acc_ei + bias) for ei ascending (multiply then add).
-__global__ void down_combine_kernel(MxDev down, const float *__restrict__ down_b, const int32_t *__restrict__ top, const float *__restrict__ wts,
-                                    int topk, int d, const int8_t *__restrict__ hq, const float *__restrict__ hs, float *__restrict__ x) {
-    extern __shared__ __align__(16) unsigned char smraw[];
-    const int nb = down.blocks, np = nb / 2;
-    const size_t per = (size_t)nb * 4 * sizeof(int2) + nb * sizeof(float);
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int ei = warp >> 1, half = warp & 1;
-    // each pair of warps stages its own expert slot's activation
-    int2 *xp = reinterpret_cast<int2 *>(smraw + per * ei);
-    float *xsc = reinterpret_cast<float *>(smraw + per * ei + (size_t)nb * 4 * sizeof(int2));
-    float *part = reinterpret_cast<float *>(smraw + per * topk);   // [topk][16]
-    mx_stage_x(hq + (size_t)ei * d, hs + (size_t)ei * nb, nb, xp, xsc, half * 32 + lane, 64);
+// One CTA per 16 output rows; stream ei = that unit row of expert top[ei]'s down matrix, consumed
+// by 64 threads against the slot's own activation hq[ei].  One thread per row then folds
+// s = x; s += wts[ei] * (acc_ei + bias) for ei ascending (multiply then add).
+struct DownArgs {
+    MxDev down;
+    const float *down_b;
+    const int32_t *top;
+    const float *wts;
+    int topk, d;
+    const int8_t *hq;
+    const float *hs;
+    float *x;
+    DevState *state;
+    int ch, stages;
+};
+
+__global__ void __launch_bounds__(512) down_combine_kernel(DownArgs a) {
+    extern __shared__ __align__(128) unsigned char smraw[];
+    const int nb = a.down.blocks, np = nb / 2, tid = threadIdx.x, nthreads = a.topk * 64;
+    MxRing r;
+    r.ch = a.ch; r.stages = a.stages; r.np = np; r.ns = a.topk;
+    r.stream_bytes = (size_t)a.ch * MX_UNIT; r.stage_bytes = r.stream_bytes * a.topk;
+    r.ring = smraw;
+    const size_t per = (size_t)nb * 4 * sizeof(int2) + (size_t)nb * sizeof(float);   // one slot's staged activation
+    unsigned char *xbase = smraw + r.stage_bytes * a.stages;
+    float *part = reinterpret_cast<float *>(xbase + per * a.topk);                    // [topk][16]
+    r.bars = reinterpret_cast<uint64_t *>(part + a.topk * 16);
+    __shared__ const uint8_t *src[8];
+    uint32_t *err = a.state ? &a.state->err : nullptr;
+    Waiter waiter(err);
+    const int nchunks = (np + a.ch - 1) / a.ch;
+
+    if (tid == 0) {
+        for (int s = 0; s < a.stages; s++) mbar_init(&r.bars[s], 1);
+        mbar_fence_init();
+        // expert ids come from the router, two kernels back: complete by the launch protocol,
+        // so the weight stream starts before this kernel waits for gate/up
+        for (int s = 0; s < a.topk; s++) src[s] = a.down.data + mx_unit_off(((a.top[s] * a.d) >> 4) + blockIdx.x, 0, np);
+        for (int c = 0; c < min(a.stages, nchunks); c++) r.issue(c, src);
+    }
+    pdl_wait();          // gate/up done: hq, hs valid
+    pdl_trigger();
+    waiter.poison_if_failed();
+    const int ei = tid >> 6, t64 = tid & 63;
+    int2 *xp = reinterpret_cast<int2 *>(xbase + per * ei);
+    float *xsc = reinterpret_cast<float *>(xbase + per * ei + (size_t)nb * 4 * sizeof(int2));
+    mx_stage_x(a.hq + (size_t)ei * a.d, a.hs + (size_t)ei * nb, nb, xp, xsc, t64, 64);
     __syncthreads();
-    const int e = top[ei];
-    int rl = half * 8 + (lane >> 2), j = lane & 3;
-    int r = blockIdx.x * 16 + rl;
-    bool live = r < d;
+
+    const int rl = t64 >> 2, j = t64 & 3;
     float acc = 0.0f;
-    if (live) {
-        int row = e * d + r;
-        acc = mx_chain<false>(down.nib + mx_noff(row, 0, np) + j * 8, down.exps + mx_eoff(row, 0, np), xp + j, xsc, np, nullptr);
+    for (int c = 0; c < nchunks; c++) {
+        const int cnt = min(a.ch, np - c * a.ch), slot = c % a.stages;
+        waiter.wait(&r.bars[slot], (uint32_t)(c / a.stages) & 1u);
+        const unsigned char *base = r.ring + r.stage_bytes * slot + r.stream_bytes * ei;
+#pragma unroll 3
+        for (int i = 0; i < cnt; i++) acc = mx_pair_step<false>(base + (size_t)i * MX_UNIT, rl, j, xp + j, xsc, c * a.ch + i, acc, nullptr);
+        if (c + a.stages < nchunks) {
+            __syncthreads();
+            if (tid == 0) { fence_proxy_async(); r.issue(c + a.stages, src); }
+        }
     }
     acc = brrr_hsum4(acc);
     if (j == 0) part[ei * 16 + rl] = acc;
     __syncthreads();
-    if (threadIdx.x < 16) {
-        int rr = blockIdx.x * 16 + threadIdx.x;
-        if (rr < d) {
-            float s = x[rr];
-            for (int k = 0; k < topk; k++) {
-                int ek = top[k];
-                s = __fadd_rn(s, __fmul_rn(wts[k], __fadd_rn(part[k * 16 + threadIdx.x], down_b[(size_t)ek * d + rr])));
-            }
-            x[rr] = s;
-        }
+    if (tid < 16) {
+        int rr = blockIdx.x * 16 + tid;
+        float s = a.x[rr];
+        for (int k = 0; k < a.topk; k++)
+            s = __fadd_rn(s, __fmul_rn(a.wts[k], __fadd_rn(part[k * 16 + tid], a.down_b[(size_t)a.top[k] * a.d + rr])));
+        a.x[rr] = s;
     }
+    (void)nthreads;
 }
 
-void launch_down_combine(MxDev down, const float *down_b, const int32_t *top, const float *wts, int topk, int d,
-                         const int8_t *hq, const float *hs, float *x, cudaStream_t st) {
-    size_t per = (size_t)down.blocks * 4 * sizeof(int2) + down.blocks * sizeof(float);
-    size_t smem = per * topk + (size_t)topk * 16 * sizeof(float);
-    down_combine_kernel<<<(d + 15) / 16, topk * 64, smem, st>>>(down, down_b, top, wts, topk, d, hq, hs, x);
+cudaError_t launch_down_combine(MxDev down, const float *down_b, const int32_t *top, const float *wts, int topk, int d,
+                                const int8_t *hq, const float *hs, float *x, DevState *state, bool pdl, cudaStream_t st) {
+    DownArgs a{};
+    a.down = down; a.down_b = down_b; a.top = top; a.wts = wts; a.topk = topk; a.d = d; a.hq = hq; a.hs = hs; a.x = x; a.state = state;
+    const int nb = down.blocks, np = nb / 2;
+    MxLaunchShape s = mx_shape(np, topk, 80 * 1024);
+    a.ch = s.ch; a.stages = s.stages;
+    size_t per = (size_t)nb * 4 * 8 + (size_t)nb * 4;
+    size_t smem = (size_t)topk * a.ch * MX_UNIT * a.stages + per * topk + (size_t)topk * 16 * 4 + (size_t)a.stages * 8 + 8;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(down_combine_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    return launch_k(down_combine_kernel, dim3(d / 16), dim3(topk * 64), smem, st, pdl, a);
 }
 
 }  // namespace brrr

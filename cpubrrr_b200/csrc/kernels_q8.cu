@@ -1,12 +1,19 @@
-// Q8 weight matrices: load-time quantisation from bf16 and the row . Q8-activation GEMV.
+// Q8 weight matrices: load-time quantisation from bf16 and the streaming row . Q8-activation GEMV
+// (qkv projection, output projection, vocabulary projection).
 //
 // Float order of one row (fixed): 8 chains = 2 block parities x 4 lanes.  Chain (p, j) walks the
 // blocks b = p, p+2, ... accumulating fma(float(t_j(b)), ws[b]*xs[b], acc) where t_j(b) is the
 // exact int32 dot of bytes 4j..4j+3 of both 16-byte halves of the block.  The row result is
-// hsum4(acc_even + acc_odd).  One thread owns one chain; the chains of 4 rows make a warp and
-// every step of the warp is one contiguous 256-byte read.
+// hsum4(acc_even + acc_odd).  One thread owns one chain, so the order never depends on the grid.
+//
+// Data movement: a CTA (128 threads = 16 rows x 8 chains) owns a run of consecutive 16-row unit
+// rows, i.e. one contiguous byte range of the matrix.  Thread 0 streams it into a shared-memory
+// ring with bulk asynchronous copies (one mbarrier per stage); the copies are issued before the
+// kernel waits on its predecessor (programmatic dependent launch), so weight traffic overlaps
+// the previous kernel's tail.  Compute threads read quants and scales from shared memory.
 #include "brrr_kernels.h"
 #include "brrr_block.cuh"
+#include "brrr_tma.cuh"
 
 namespace brrr {
 
@@ -23,8 +30,10 @@ __global__ void q8_pack_kernel(const uint16_t *__restrict__ w, int rows_src, int
     float sc = __fdiv_rn(amax, 127.0f);
     int row = row0_dst + r, pair = b >> 1, p = b & 1;
     int j = (lane & 15) >> 2, byte = (lane & 3) + (lane >= 16 ? 4 : 0);
-    m.wq[q8_woff(row, pair, np) + p * 32 + j * 8 + byte] = (int8_t)brrr_q8_round(v, sc);
-    if (lane == 0) m.ws[q8_soff(row, pair, np) + p] = sc;
+    uint8_t *unit = m.data + q8_unit_off(row >> 4, pair, np);
+    int rl = row & 15;
+    unit[rl * 64 + p * 32 + j * 8 + byte] = (uint8_t)(int8_t)brrr_q8_round(v, sc);
+    if (lane == 0) reinterpret_cast<float *>(unit + Q8_UNIT_SCALES)[rl * 2 + p] = sc;
 }
 
 void launch_q8_pack(const uint16_t *w, int rows_src, int row0_dst, Q8Dev m, cudaStream_t st) {
@@ -41,8 +50,10 @@ __global__ void q8_export_kernel(Q8Dev m, int8_t *__restrict__ q, float *__restr
     int r = (int)(warp / nb), b = (int)(warp % nb);
     int pair = b >> 1, p = b & 1;
     int j = (lane & 15) >> 2, byte = (lane & 3) + (lane >= 16 ? 4 : 0);
-    q[(size_t)r * m.cols + b * 32 + lane] = m.wq[q8_woff(r, pair, np) + p * 32 + j * 8 + byte];
-    if (lane == 0) s[(size_t)r * nb + b] = m.ws[q8_soff(r, pair, np) + p];
+    const uint8_t *unit = m.data + q8_unit_off(r >> 4, pair, np);
+    int rl = r & 15;
+    q[(size_t)r * m.cols + b * 32 + lane] = (int8_t)unit[rl * 64 + p * 32 + j * 8 + byte];
+    if (lane == 0) s[(size_t)r * nb + b] = reinterpret_cast<const float *>(unit + Q8_UNIT_SCALES)[rl * 2 + p];
 }
 
 void launch_q8_export(Q8Dev m, int8_t *q, float *s, cudaStream_t st) {
@@ -50,49 +61,180 @@ void launch_q8_export(Q8Dev m, int8_t *q, float *s, cudaStream_t st) {
     q8_export_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, st>>>(m, q, s);
 }
 
-// ---------------------------------------------------------------- GEMV
-// ROWS rows per CTA, 8 threads per row.  Shared memory: the activation re-laid as one int2 per
-// (block, lane) = {x[32b+4j..+3], x[32b+16+4j..+3]} and the block scales.
-template <int ROWS, int EPI>
-__global__ void __launch_bounds__(ROWS * 8) q8_gemv_kernel(Q8Dev m, const int8_t *__restrict__ xq, const float *__restrict__ xs,
-                                                           const float *__restrict__ bias, float *__restrict__ y, DevState *state) {
+// ---------------------------------------------------------------- streaming GEMV
+struct Q8Args {
+    Q8Dev m;
+    const float *x_f32;     // NORM: residual stream (RMSNorm + quantise in the prologue)
+    const float *norm_w;
+    float eps;
+    const int8_t *xq;       // !NORM: already quantised activation
+    const float *xs;
+    const float *bias;
+    float *y;
+    DevState *state;
+    int ch;                 // pairs per chunk
+    int stages;             // ring depth
+};
+
+constexpr int Q8_THREADS = 128;
+
+template <int EPI, bool NORM>
+__global__ void __launch_bounds__(Q8_THREADS) q8_stream_kernel(Q8Args a) {
+    extern __shared__ __align__(128) unsigned char smraw[];
+    const int nb = a.m.cols / 32, np = a.m.cols / 64;
+    const int tid = threadIdx.x;
+    const size_t stage_bytes = (size_t)a.ch * Q8_UNIT;
+    unsigned char *ring = smraw;
+    float *xf = reinterpret_cast<float *>(smraw + stage_bytes * a.stages);   // NORM only: cols floats (16-byte aligned)
+    int2 *xp = reinterpret_cast<int2 *>(xf + (NORM ? a.m.cols : 0));
+    float *xsc = reinterpret_cast<float *>(xp + nb * 4);
+    uint64_t *bars = reinterpret_cast<uint64_t *>(xsc + nb + (nb & 1));
+    __shared__ float inv_sh;
+    __shared__ unsigned long long wbest[Q8_THREADS / 32];
+    uint32_t *err = a.state ? &a.state->err : nullptr;
+    Waiter waiter(err);
+
+    // unit rows [u0, u1) of this CTA, balanced over the grid
+    const int urows = q8_urows(a.m.rows);
+    const int u0 = (int)((long long)urows * blockIdx.x / gridDim.x);
+    const int u1 = (int)((long long)urows * (blockIdx.x + 1) / gridDim.x);
+    const int cpr = (np + a.ch - 1) / a.ch;                          // chunks per unit row
+    const int nchunks = (u1 - u0) * cpr;
+
+    auto issue = [&](int c) {                                        // thread 0 only
+        int u = u0 + c / cpr, k = c % cpr;
+        int cnt = min(a.ch, np - k * a.ch);
+        int slot = c % a.stages;
+        mbar_expect_tx(&bars[slot], (uint32_t)cnt * Q8_UNIT);
+        bulk_g2s(ring + stage_bytes * slot, a.m.data + q8_unit_off(u, k * a.ch, np), (uint32_t)cnt * Q8_UNIT, &bars[slot]);
+    };
+
+    if (tid == 0) {
+        for (int s = 0; s < a.stages; s++) mbar_init(&bars[s], 1);
+        mbar_fence_init();
+    }
+    __syncthreads();
+    if (tid == 0)
+        for (int c = 0; c < min(a.stages, nchunks); c++) issue(c);
+
+    pdl_wait();          // predecessor's outputs (activation, residual) are now visible
+    pdl_trigger();
+    waiter.poison_if_failed();
+
+    // ---- activation: normalise + quantise, or stage the given Q8 vector
+    if (NORM) {
+        block_norm_quant<NQ_Q8>(a.x_f32, a.norm_w, a.eps, a.m.cols, xf, xp, xsc, &inv_sh, tid, Q8_THREADS);
+    } else {
+        for (int idx = tid; idx < nb * 4; idx += Q8_THREADS) {
+            int b = idx >> 2, j = idx & 3;
+            const int *xw = reinterpret_cast<const int *>(a.xq + b * 32);
+            xp[idx] = make_int2(xw[j], xw[4 + j]);
+        }
+        for (int b = tid; b < nb; b += Q8_THREADS) xsc[b] = a.xs[b];
+    }
+    __syncthreads();
+
+    const int rl = tid >> 3, c8 = tid & 7, p = c8 >> 2;
+    float acc = 0.0f;
+    unsigned long long best = 0ull;
+    for (int c = 0; c < nchunks; c++) {
+        const int u = u0 + c / cpr, k = c % cpr;
+        const int cnt = min(a.ch, np - k * a.ch);
+        const int slot = c % a.stages;
+        waiter.wait(&bars[slot], (uint32_t)(c / a.stages) & 1u);
+        const unsigned char *base = ring + stage_bytes * slot;
+        const int pair0 = k * a.ch;
+#pragma unroll 4
+        for (int i = 0; i < cnt; i++) {
+            const unsigned char *unit = base + (size_t)i * Q8_UNIT;
+            int2 w = *reinterpret_cast<const int2 *>(unit + rl * 64 + c8 * 8);
+            float s = *reinterpret_cast<const float *>(unit + Q8_UNIT_SCALES + rl * 8 + p * 4);
+            int2 xv = xp[(pair0 + i) * 8 + c8];
+            int t = __dp4a(w.y, xv.y, __dp4a(w.x, xv.x, 0));
+            acc = __fmaf_rn((float)t, __fmul_rn(s, xsc[(pair0 + i) * 2 + p]), acc);
+        }
+        if (k == cpr - 1) {
+            // row finished: acc_even + acc_odd per lane, then (l0+l1)+(l2+l3)
+            float r = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 4));
+            r = brrr_hsum4(r);
+            const int row = u * 16 + rl;
+            if (c8 == 0 && row < a.m.rows) {
+                if (EPI == Q8_EPI_PLAIN) a.y[row] = r;
+                else if (EPI == Q8_EPI_BIAS) a.y[row] = __fadd_rn(r, a.bias[row]);
+                else if (EPI == Q8_EPI_RESID_BIAS) a.y[row] = __fadd_rn(a.y[row], __fadd_rn(r, a.bias[row]));   // x += dot + bias
+                else {
+                    a.y[row] = r;
+                    unsigned long long key = ((unsigned long long)float_orderable(r) << 32) | (0xFFFFFFFFu - (uint32_t)row);
+                    best = key > best ? key : best;
+                }
+            }
+            acc = 0.0f;
+        }
+        if (c + a.stages < nchunks) {
+            __syncthreads();                       // everyone is done with this slot
+            if (tid == 0) { fence_proxy_async(); issue(c + a.stages); }
+        }
+    }
+    if (EPI == Q8_EPI_HEAD) {
+        // running argmax: first strict maximum = lowest index among equal values
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+            best = other > best ? other : best;
+        }
+        if ((tid & 31) == 0) wbest[tid >> 5] = best;
+        __syncthreads();
+        if (tid == 0) {
+            for (int w = 1; w < Q8_THREADS / 32; w++) best = wbest[w] > best ? wbest[w] : best;
+            if (best) atomicMax(&a.state->best, best);
+        }
+    }
+}
+
+// ---------------------------------------------------------------- direct-load GEMV (vocabulary head)
+// For a matrix far larger than what the SMs can hold in flight, staging through shared memory
+// only adds traffic: 32 rows per CTA, 8 chains per row, weights read straight from global memory
+// (a warp's step is one contiguous 256-byte read of a unit), thousands of CTAs in flight.
+template <int EPI>
+__global__ void __launch_bounds__(256) q8_direct_kernel(Q8Dev m, const int8_t *__restrict__ xq, const float *__restrict__ xs,
+                                                        const float *__restrict__ bias, float *__restrict__ y, DevState *state) {
     extern __shared__ __align__(16) unsigned char smraw[];
     const int nb = m.cols / 32, np = m.cols / 64;
     int2 *xp = reinterpret_cast<int2 *>(smraw);
     float *xsc = reinterpret_cast<float *>(smraw + (size_t)nb * 4 * sizeof(int2));
-    for (int idx = threadIdx.x; idx < nb * 4; idx += ROWS * 8) {
+    __shared__ unsigned long long wbest[8];
+    pdl_wait();
+    pdl_trigger();
+    for (int idx = threadIdx.x; idx < nb * 4; idx += 256) {
         int b = idx >> 2, j = idx & 3;
         const int *xw = reinterpret_cast<const int *>(xq + b * 32);
         xp[idx] = make_int2(xw[j], xw[4 + j]);
     }
-    for (int b = threadIdx.x; b < nb; b += ROWS * 8) xsc[b] = xs[b];
+    for (int b = threadIdx.x; b < nb; b += 256) xsc[b] = xs[b];
     __syncthreads();
-
-    const int row = blockIdx.x * ROWS + (threadIdx.x >> 3);
-    const int c = threadIdx.x & 7, p = c >> 2, j = c & 3;
-    const bool live = row < m.rows;
+    const int row = blockIdx.x * 32 + (threadIdx.x >> 3);
+    const int c8 = threadIdx.x & 7, p = c8 >> 2;
+    const bool live = row < q8_urows(m.rows) * 16;            // padding rows exist in storage (zeros)
     float acc = 0.0f;
     if (live) {
-        const int2 *wp = reinterpret_cast<const int2 *>(m.wq + q8_woff(row, 0, np) + p * 32 + j * 8);
-        const float *sp = m.ws + q8_soff(row, 0, np) + p;
-        const int2 *xpp = xp + p * 4 + j;
-        const float *xsp = xsc + p;
+        const uint8_t *u0 = m.data + q8_unit_off(row >> 4, 0, np);
+        const int2 *wp = reinterpret_cast<const int2 *>(u0 + (row & 15) * 64 + c8 * 8);
+        const float *sp = reinterpret_cast<const float *>(u0 + Q8_UNIT_SCALES + (row & 15) * 8 + p * 4);
 #pragma unroll 8
         for (int i = 0; i < np; i++) {
-            int2 w = __ldg(wp + (size_t)i * 32);
-            float s = __ldg(sp + (size_t)i * 8);
-            int2 xv = xpp[i * 8];
+            int2 w = __ldg(wp + (size_t)i * (Q8_UNIT / 8));
+            float s = __ldg(sp + (size_t)i * (Q8_UNIT / 4));
+            int2 xv = xp[i * 8 + c8];
             int t = __dp4a(w.y, xv.y, __dp4a(w.x, xv.x, 0));
-            acc = __fmaf_rn((float)t, __fmul_rn(s, xsp[i * 2]), acc);
+            acc = __fmaf_rn((float)t, __fmul_rn(s, xsc[i * 2 + p]), acc);
         }
     }
     acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 4));   // acc_even + acc_odd, per lane
     acc = brrr_hsum4(acc);
-
+    const bool out = live && c8 == 0 && row < m.rows;
     if (EPI == Q8_EPI_HEAD) {
-        // logits + running argmax: first strict maximum = lowest index among equal values
         unsigned long long key = 0ull;
-        if (live && c == 0) {
+        if (out) {
             y[row] = acc;
             key = ((unsigned long long)float_orderable(acc) << 32) | (0xFFFFFFFFu - (uint32_t)row);
         }
@@ -101,37 +243,79 @@ __global__ void __launch_bounds__(ROWS * 8) q8_gemv_kernel(Q8Dev m, const int8_t
             unsigned long long other = __shfl_xor_sync(0xffffffffu, key, o);
             key = other > key ? other : key;
         }
-        __shared__ unsigned long long wbest[ROWS * 8 / 32];
         if ((threadIdx.x & 31) == 0) wbest[threadIdx.x >> 5] = key;
         __syncthreads();
         if (threadIdx.x == 0) {
-            for (int w = 1; w < ROWS * 8 / 32; w++) key = wbest[w] > key ? wbest[w] : key;
-            atomicMax(&state->best, key);
+            for (int w = 1; w < 8; w++) key = wbest[w] > key ? wbest[w] : key;
+            if (key) atomicMax(&state->best, key);
         }
-    } else if (live && c == 0) {
+    } else if (out) {
         if (EPI == Q8_EPI_PLAIN) y[row] = acc;
         else if (EPI == Q8_EPI_BIAS) y[row] = __fadd_rn(acc, bias[row]);
-        else y[row] = __fadd_rn(y[row], __fadd_rn(acc, bias[row]));   // x += dot + bias
+        else y[row] = __fadd_rn(y[row], __fadd_rn(acc, bias[row]));
     }
 }
 
-template <int ROWS>
-static void q8_gemv_dispatch(Q8Dev m, const int8_t *xq, const float *xs, const float *bias, float *y, int epi, DevState *state, cudaStream_t st) {
-    int nb = m.cols / 32;
-    size_t smem = (size_t)nb * 4 * sizeof(int2) + nb * sizeof(float);
-    unsigned grid = (m.rows + ROWS - 1) / ROWS;
+cudaError_t launch_q8_direct(Q8Dev m, const int8_t *xq, const float *xs, const float *bias, float *y, int epi, DevState *state, bool pdl, cudaStream_t st) {
+    const int nb = m.cols / 32;
+    size_t smem = (size_t)nb * 4 * sizeof(int2) + (size_t)nb * sizeof(float);
+    dim3 grid((q8_urows(m.rows) * 16 + 31) / 32), block(256);
     switch (epi) {
-    case Q8_EPI_PLAIN: q8_gemv_kernel<ROWS, Q8_EPI_PLAIN><<<grid, ROWS * 8, smem, st>>>(m, xq, xs, bias, y, state); break;
-    case Q8_EPI_BIAS: q8_gemv_kernel<ROWS, Q8_EPI_BIAS><<<grid, ROWS * 8, smem, st>>>(m, xq, xs, bias, y, state); break;
-    case Q8_EPI_RESID_BIAS: q8_gemv_kernel<ROWS, Q8_EPI_RESID_BIAS><<<grid, ROWS * 8, smem, st>>>(m, xq, xs, bias, y, state); break;
-    case Q8_EPI_HEAD: q8_gemv_kernel<ROWS, Q8_EPI_HEAD><<<grid, ROWS * 8, smem, st>>>(m, xq, xs, bias, y, state); break;
+    case Q8_EPI_PLAIN: return launch_k(q8_direct_kernel<Q8_EPI_PLAIN>, grid, block, smem, st, pdl, m, xq, xs, bias, y, state);
+    case Q8_EPI_BIAS: return launch_k(q8_direct_kernel<Q8_EPI_BIAS>, grid, block, smem, st, pdl, m, xq, xs, bias, y, state);
+    case Q8_EPI_RESID_BIAS: return launch_k(q8_direct_kernel<Q8_EPI_RESID_BIAS>, grid, block, smem, st, pdl, m, xq, xs, bias, y, state);
+    case Q8_EPI_HEAD: return launch_k(q8_direct_kernel<Q8_EPI_HEAD>, grid, block, smem, st, pdl, m, xq, xs, bias, y, state);
     }
+    return cudaErrorInvalidValue;
 }
 
-void launch_q8_gemv(Q8Dev m, const int8_t *xq, const float *xs, const float *bias, float *y, int epi, DevState *state, cudaStream_t st) {
-    // Small matrices use 16 rows per CTA so the grid still covers the SMs.
-    if (m.rows <= 148 * 32) q8_gemv_dispatch<16>(m, xq, xs, bias, y, epi, state, st);
-    else q8_gemv_dispatch<32>(m, xq, xs, bias, y, epi, state, st);
+// chunk size: a divisor of np between 6 and 12 pairs when there is one (no ragged tail), else 8
+static int pick_chunk(int np) {
+    for (int c = 9; c <= 12; c++) if (np % c == 0) return c;
+    for (int c = 8; c >= 6; c--) if (np % c == 0) return c;
+    return np < 8 ? np : 8;
+}
+
+static size_t q8_smem(const Q8Args &a, bool norm) {
+    int nb = a.m.cols / 32;
+    size_t s = (size_t)a.ch * Q8_UNIT * a.stages + (size_t)nb * 4 * 8 + (size_t)nb * 4 + (norm ? (size_t)a.m.cols * 4 : 0) + 8 + (size_t)a.stages * 8;
+    return s;
+}
+
+template <int EPI, bool NORM>
+static cudaError_t q8_launch_t(const Q8Args &a, unsigned grid, bool pdl, cudaStream_t st) {
+    static size_t configured = 0;
+    size_t smem = q8_smem(a, NORM);
+    if (smem > configured) {
+        cudaError_t e = cudaFuncSetAttribute(q8_stream_kernel<EPI, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return e;
+        configured = 200 * 1024;
+    }
+    return launch_k(q8_stream_kernel<EPI, NORM>, dim3(grid), dim3(Q8_THREADS), smem, st, pdl, a);
+}
+
+cudaError_t launch_q8_stream(Q8Dev m, const float *x_f32, const float *norm_w, float eps, const int8_t *xq, const float *xs,
+                             const float *bias, float *y, int epi, DevState *state, bool pdl, cudaStream_t st) {
+    Q8Args a{};
+    a.m = m; a.x_f32 = x_f32; a.norm_w = norm_w; a.eps = eps; a.xq = xq; a.xs = xs; a.bias = bias; a.y = y; a.state = state;
+    const int np = m.cols / 64, urows = q8_urows(m.rows);
+    a.ch = pick_chunk(np);
+    const int cpr = (np + a.ch - 1) / a.ch;
+    // Small matrices: one unit row per CTA, whole row resident.  Large ones: a persistent grid.
+    unsigned grid = urows <= 148 * 4 ? urows : 148 * 4;
+    int per_cta = (urows + grid - 1) / grid * cpr;
+    int max_stages = (int)((96 * 1024) / ((size_t)a.ch * Q8_UNIT));
+    if (max_stages < 2) max_stages = 2;
+    a.stages = per_cta < max_stages ? per_cta : max_stages;
+    if (epi == Q8_EPI_HEAD && a.stages > 5) a.stages = 5;
+    const bool norm = x_f32 != nullptr;
+    switch (epi) {
+    case Q8_EPI_PLAIN: return norm ? q8_launch_t<Q8_EPI_PLAIN, true>(a, grid, pdl, st) : q8_launch_t<Q8_EPI_PLAIN, false>(a, grid, pdl, st);
+    case Q8_EPI_BIAS: return norm ? q8_launch_t<Q8_EPI_BIAS, true>(a, grid, pdl, st) : q8_launch_t<Q8_EPI_BIAS, false>(a, grid, pdl, st);
+    case Q8_EPI_RESID_BIAS: return norm ? q8_launch_t<Q8_EPI_RESID_BIAS, true>(a, grid, pdl, st) : q8_launch_t<Q8_EPI_RESID_BIAS, false>(a, grid, pdl, st);
+    case Q8_EPI_HEAD: return norm ? q8_launch_t<Q8_EPI_HEAD, true>(a, grid, pdl, st) : q8_launch_t<Q8_EPI_HEAD, false>(a, grid, pdl, st);
+    }
+    return cudaErrorInvalidValue;
 }
 
 }  // namespace brrr

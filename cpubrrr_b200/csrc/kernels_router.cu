@@ -1,114 +1,197 @@
-// FFN entry stage: RMSNorm of the residual stream, Q8 quantisation of the result, router GEMV
-// and top-k softmax.
+// FFN entry stage: RMSNorm of the residual stream, router GEMV and top-k softmax.
 //
 // The router logit of expert e is the *serial* f32 sum  acc = b[e]; acc += W[e][j] * xn[j]
 // for j ascending, multiply and add rounded separately.  That chain cannot be split without
-// changing bits, so one lane owns one expert and walks the whole row; the other warps of the CTA
-// stream W from memory and pre-multiply the products into shared-memory tiles (double buffered),
-// leaving the chain lane one LDS + one FADD per element.  Experts are split 32 per CTA; the last
-// CTA to finish performs the top-k.
+// changing bits, so one lane owns one expert and walks the whole row: 4 cycles of dependent
+// FADD latency per element is the floor of this stage.  The lane is kept fed from a ring of
+// shared-memory tiles; each tile is ONE bulk asynchronous copy, because the router matrix is
+// re-laid at load time as [32-expert group][tile][32 experts][128 + 4 floats] (the 4-float row
+// padding makes a 128-bit read per lane bank-conflict free).  Experts are split 32 per CTA; with
+// several CTAs the last one to finish runs the top-k.
 #include "brrr_kernels.h"
 #include "brrr_block.cuh"
+#include "brrr_tma.cuh"
 
 namespace brrr {
 
-constexpr int RT_TJ = 256;                 // tile width (elements of d)
-constexpr int RT_STRIDE = RT_TJ + 1;       // padded row stride: lane e reads bank (e + j) % 32
-constexpr int RT_THREADS = 1024;
+constexpr int RT_STAGES = 8;
+constexpr int RT_THREADS = 256;
 
-__global__ void __launch_bounds__(RT_THREADS) ffn_in_kernel(const float *__restrict__ x_in, const float *__restrict__ norm_w, float eps, int d,
-                                                            int8_t *__restrict__ xq_out, float *__restrict__ xs_out,
-                                                            const float *__restrict__ W, const float *__restrict__ b, int ne, int topk,
-                                                            float *__restrict__ logits, int32_t *__restrict__ top, float *__restrict__ wts,
-                                                            unsigned int *counter) {
-    extern __shared__ __align__(16) unsigned char smraw[];
-    float *xn = reinterpret_cast<float *>(smraw);                 // d floats
-    float *prod = xn + d;                                         // [2][32][RT_STRIDE]
+// ---------------------------------------------------------------- pack: W[ne][d] -> tiled layout
+__global__ void router_pack_kernel(const float *__restrict__ W, int ne, int d, float *__restrict__ out) {
+    const int ntiles = (d + RT_TJ - 1) / RT_TJ;
+    const size_t total = (size_t)((ne + 31) / 32) * ntiles * RT_TILE_FLOATS;
+    for (size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x; i < total; i += (size_t)gridDim.x * blockDim.x) {
+        int jj = (int)(i % RT_STRIDE);
+        size_t r = i / RT_STRIDE;
+        int el = (int)(r % 32);
+        size_t gt = r / 32;
+        int t = (int)(gt % ntiles), g = (int)(gt / ntiles);
+        int e = g * 32 + el, j = t * RT_TJ + jj;
+        out[i] = (jj < RT_TJ && e < ne && j < d) ? W[(size_t)e * d + j] : 0.0f;
+    }
+}
+
+void launch_router_pack(const float *W, int ne, int d, float *out, cudaStream_t st) {
+    router_pack_kernel<<<148, 256, 0, st>>>(W, ne, d, out);
+}
+
+struct RouterArgs {
+    const float *x_in;       // residual stream (norm_w != null) or normalised vector
+    const float *norm_w;
+    float eps;
+    int d;
+    const float *Wt;         // tiled router matrix (router_pack_kernel)
+    const float *b;
+    int ne, topk;
+    float *logits;
+    int32_t *top;
+    float *wts;
+    unsigned int *counter;
+    DevState *state;
+};
+
+// k rounds of warp arg-max over the logits (lane l holds experts l, l+32, ...): the largest value
+// wins, the lower index among equals, which is the order the reference's strict-'>' insertion
+// produces.  Then the softmax over the selected k in rank order.  Warp 0 only.
+__device__ __forceinline__ void warp_topk(const RouterArgs &a, const float *lg, int lane) {
+    float v[8];                                  // up to 256 experts
+    const int per = (a.ne + 31) / 32;
+    for (int i = 0; i < 8; i++) v[i] = (i < per && lane + 32 * i < a.ne) ? lg[lane + 32 * i] : 0.0f;
+    unsigned taken = 0;
+    float tv[8];
+    int tp[8];
+    for (int r = 0; r < a.topk; r++) {
+        unsigned long long best = 0ull;
+        for (int i = 0; i < per; i++) {
+            int e = lane + 32 * i;
+            if (e < a.ne && !(taken & (1u << i))) {
+                unsigned long long key = ((unsigned long long)float_orderable(v[i]) << 32) | (0xFFFFFFFFu - (uint32_t)e);
+                best = key > best ? key : best;
+            }
+        }
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) {
+            unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+            best = other > best ? other : best;
+        }
+        int e = (int)(0xFFFFFFFFu - (uint32_t)(best & 0xFFFFFFFFull));
+        if ((e & 31) == lane) taken |= 1u << (e >> 5);
+        tp[r] = e;
+        tv[r] = lg[e];
+    }
+    if (lane == 0) {
+        float ex[8], wsum = 0.0f;
+        for (int i = 0; i < a.topk; i++) { ex[i] = brrr_expf_dev(__fsub_rn(tv[i], tv[0])); wsum = __fadd_rn(wsum, ex[i]); }
+        for (int i = 0; i < a.topk; i++) { a.wts[i] = __fdiv_rn(ex[i], wsum); a.top[i] = tp[i]; }
+    }
+}
+
+__global__ void __launch_bounds__(RT_THREADS) ffn_in_kernel(RouterArgs a) {
+    extern __shared__ __align__(128) unsigned char smraw[];
+    float *tiles = reinterpret_cast<float *>(smraw);                                        // [RT_STAGES][32][RT_STRIDE]
+    float *xn = reinterpret_cast<float *>(smraw + (size_t)RT_TILE_FLOATS * 4 * RT_STAGES);   // d floats
+    float *lg = xn + a.d;                                                                   // ne floats (top-k staging)
+    uint64_t *bars = reinterpret_cast<uint64_t *>(lg + ((a.ne + 1) & ~1));
     __shared__ float inv_sh;
     __shared__ int last_sh;
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
-
-    for (int i = tid; i < d; i += RT_THREADS) xn[i] = x_in[i];
-    __syncthreads();
-    if (norm_w) {
-        float inv = block_rms_inv(xn, d, eps, &inv_sh);
-        for (int i = tid; i < d; i += RT_THREADS) xn[i] = __fmul_rn(__fmul_rn(xn[i], inv), norm_w[i]);
-        __syncthreads();
-    }
-    if (xq_out && blockIdx.x == 0)
-        for (int blk = warp; blk < d / 32; blk += RT_THREADS / 32) warp_quant_block(xn[blk * 32 + lane], lane, xq_out + blk * 32, xs_out + blk);
-
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, d = a.d;
+    uint32_t *err = a.state ? &a.state->err : nullptr;
+    Waiter waiter(err);
     const int e0 = blockIdx.x * 32;
-    const int nloc = min(32, ne - e0);
+    const int nloc = min(32, a.ne - e0);
     const int ntiles = (d + RT_TJ - 1) / RT_TJ;
-    const int ptid = tid - 32;                                    // producer thread id (warps 1..31)
-    float acc = (warp == 0 && lane < nloc && b) ? b[e0 + lane] : 0.0f;
+    const float *wsrc = a.Wt + (size_t)blockIdx.x * ntiles * RT_TILE_FLOATS;
 
-    // producers fill tile t into buffer t & 1
-    auto fill = [&](int t) {
-        float *buf = prod + (size_t)(t & 1) * 32 * RT_STRIDE;
-        int j0 = t * RT_TJ;
-        for (int idx = ptid; idx < 32 * RT_TJ; idx += RT_THREADS - 32) {
-            int e = idx / RT_TJ, jj = idx % RT_TJ, j = j0 + jj;
-            if (e < nloc && j < d) buf[e * RT_STRIDE + jj] = __fmul_rn(__ldg(W + (size_t)(e0 + e) * d + j), xn[j]);
-        }
+    auto issue = [&](int t) {                                       // one thread
+        int slot = t % RT_STAGES;
+        mbar_expect_tx(&bars[slot], (uint32_t)RT_TILE_FLOATS * 4);
+        bulk_g2s(tiles + (size_t)slot * RT_TILE_FLOATS, wsrc + (size_t)t * RT_TILE_FLOATS, (uint32_t)RT_TILE_FLOATS * 4, &bars[slot]);
     };
-    if (warp != 0) fill(0);
+    BRRR_STAMP(a.state, 0);
+    if (tid == 0) {
+        for (int s = 0; s < RT_STAGES; s++) mbar_init(&bars[s], 1);
+        mbar_fence_init();
+        for (int t = 0; t < min(RT_STAGES, ntiles); t++) issue(t);
+    }
+    BRRR_STAMP(a.state, 1);
+    pdl_wait();          // residual stream complete
+    BRRR_STAMP(a.state, 2);
+    pdl_trigger();
+    waiter.poison_if_failed();
+    for (int i = tid; i < d; i += RT_THREADS) xn[i] = a.x_in[i];
     __syncthreads();
-    for (int t = 0; t < ntiles; t++) {
-        if (warp != 0) {
-            if (t + 1 < ntiles) fill(t + 1);
-        } else if (lane < nloc) {
-            const float *row = prod + (size_t)(t & 1) * 32 * RT_STRIDE + lane * RT_STRIDE;
-            int len = min(RT_TJ, d - t * RT_TJ);
-#pragma unroll 16
-            for (int jj = 0; jj < len; jj++) acc = __fadd_rn(acc, row[jj]);
-        }
+    if (a.norm_w) {
+        float inv = block_rms_inv(xn, d, a.eps, &inv_sh);
+        for (int i = tid; i < d; i += RT_THREADS) xn[i] = __fmul_rn(__fmul_rn(xn[i], inv), a.norm_w[i]);
         __syncthreads();
     }
-    if (warp == 0 && lane < nloc) logits[e0 + lane] = acc;
 
-    // last CTA to arrive runs the top-k
+    BRRR_STAMP(a.state, 3);
+    if (warp == 0) {
+        float acc = (lane < nloc && a.b) ? a.b[e0 + lane] : 0.0f;
+        for (int t = 0; t < ntiles; t++) {
+            if (t < 12) BRRR_STAMP(a.state, 8 + t);
+            const int slot = t % RT_STAGES, j0 = t * RT_TJ, len = min(RT_TJ, d - j0);
+            waiter.wait(&bars[slot], (uint32_t)(t / RT_STAGES) & 1u);
+            const float *row = tiles + (size_t)slot * RT_TILE_FLOATS + lane * RT_STRIDE;
+            const float *xr = xn + j0;
+#pragma unroll 8
+            for (int jj = 0; jj < len; jj += 4) {
+                float4 w = *reinterpret_cast<const float4 *>(row + jj);
+                float4 x = *reinterpret_cast<const float4 *>(xr + jj);
+                acc = __fadd_rn(acc, __fmul_rn(w.x, x.x));
+                acc = __fadd_rn(acc, __fmul_rn(w.y, x.y));
+                acc = __fadd_rn(acc, __fmul_rn(w.z, x.z));
+                acc = __fadd_rn(acc, __fmul_rn(w.w, x.w));
+            }
+            if (t + RT_STAGES < ntiles) {
+                __syncwarp();                  // all lanes are done reading this slot
+                if (lane == 0) { fence_proxy_async(); issue(t + RT_STAGES); }
+            }
+        }
+        if (lane < nloc) {
+            if (gridDim.x == 1) lg[lane] = acc;
+            a.logits[e0 + lane] = acc;
+        }
+        BRRR_STAMP(a.state, 4);
+        if (gridDim.x == 1) {                  // single CTA: top-k straight from shared memory
+            __syncwarp();
+            warp_topk(a, lg, lane);
+        }
+        BRRR_STAMP(a.state, 5);
+    }
+    if (gridDim.x == 1) return;
+
+    // several CTAs: the last one to arrive runs the top-k over all logits
     __threadfence();
     __syncthreads();
     if (tid == 0) {
-        unsigned prev = atomicAdd(counter, 1u);
+        unsigned prev = atomicAdd(a.counter, 1u);
         last_sh = (prev == gridDim.x - 1);
     }
     __syncthreads();
     if (!last_sh) return;
     __threadfence();
-    if (tid == 0) {
-        // insertion top-k, strict '>', so equal logits keep the lower expert index first
-        int tp[8];
-        float tv[8];
-        for (int i = 0; i < 8; i++) { tp[i] = 0; tv[i] = -3.402823466e+38f; }
-        for (int e = 0; e < ne; e++) {
-            float v = __ldcg(logits + e);
-            if (v > tv[topk - 1]) {
-                int p = topk - 1;
-                while (p > 0 && tv[p - 1] < v) { tv[p] = tv[p - 1]; tp[p] = tp[p - 1]; p--; }
-                tv[p] = v; tp[p] = e;
-            }
-        }
-        float ex[8], wsum = 0.0f;
-        for (int i = 0; i < topk; i++) { ex[i] = brrr_expf_dev(__fsub_rn(tv[i], tv[0])); wsum = __fadd_rn(wsum, ex[i]); }
-        for (int i = 0; i < topk; i++) { wts[i] = __fdiv_rn(ex[i], wsum); top[i] = tp[i]; }
-        *counter = 0u;
+    for (int e = tid; e < a.ne; e += RT_THREADS) lg[e] = __ldcg(a.logits + e);
+    __syncthreads();
+    if (warp == 0) warp_topk(a, lg, lane);
+    if (tid == 0) *a.counter = 0u;
+}
+
+size_t router_packed_floats(int ne, int d) { return (size_t)((ne + 31) / 32) * ((d + RT_TJ - 1) / RT_TJ) * RT_TILE_FLOATS; }
+
+cudaError_t launch_ffn_in(const float *x_in, const float *norm_w, float eps, int d, const float *Wt, const float *b, int ne, int topk,
+                          float *logits, int32_t *top, float *wts, unsigned int *counter, DevState *state, bool pdl, cudaStream_t st) {
+    RouterArgs a{x_in, norm_w, eps, d, Wt, b, ne, topk, logits, top, wts, counter, state};
+    size_t smem = (size_t)RT_TILE_FLOATS * 4 * RT_STAGES + (size_t)d * 4 + (size_t)((ne + 1) & ~1) * 4 + RT_STAGES * 8;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(ffn_in_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return e;
+        configured = true;
     }
-}
-
-static size_t ffn_in_smem(int d) { return (size_t)d * sizeof(float) + (size_t)2 * 32 * RT_STRIDE * sizeof(float); }
-
-int ffn_in_init() {
-    return (int)cudaFuncSetAttribute(ffn_in_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)ffn_in_smem(8192));
-}
-
-void launch_ffn_in(const float *x_in, const float *norm_w, float eps, int d, int8_t *xq_out, float *xs_out,
-                   const float *W, const float *b, int ne, int topk, float *logits, int32_t *top, float *wts,
-                   unsigned int *counter, cudaStream_t st) {
-    unsigned grid = (ne + 31) / 32;
-    ffn_in_kernel<<<grid, RT_THREADS, ffn_in_smem(d), st>>>(x_in, norm_w, eps, d, xq_out, xs_out, W, b, ne, topk, logits, top, wts, counter);
+    return launch_k(ffn_in_kernel, dim3((ne + 31) / 32), dim3(RT_THREADS), smem, st, pdl, a);
 }
 
 }  // namespace brrr

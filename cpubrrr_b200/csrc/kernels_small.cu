@@ -2,6 +2,7 @@
 // SwiGLU, token hand-over, and the synthetic tensor fill.
 #include "brrr_kernels.h"
 #include "brrr_block.cuh"
+#include "brrr_tma.cuh"
 #include "brrr_synth.h"
 
 namespace brrr {
@@ -27,24 +28,19 @@ void launch_quant_q8(const float *x, int n, int8_t *q, float *s, cudaStream_t st
 // (x * inv) * w with two separately rounded multiplies.
 __global__ void __launch_bounds__(512) rmsnorm_quant_kernel(const float *__restrict__ x, const float *__restrict__ w, float eps, int n,
                                                             float *__restrict__ xn, int8_t *__restrict__ q, float *__restrict__ s) {
-    extern __shared__ float sm[];
-    float *xs = sm;          // n floats
+    extern __shared__ __align__(16) float sm[];
     __shared__ float inv_sh;
-    for (int i = threadIdx.x; i < n; i += blockDim.x) xs[i] = x[i];
-    __syncthreads();
-    float inv = block_rms_inv(xs, n, eps, &inv_sh);
-    for (int i = threadIdx.x; i < n; i += blockDim.x) {
-        float v = __fmul_rn(__fmul_rn(xs[i], inv), w[i]);
-        xs[i] = v;
-        if (xn) xn[i] = v;
+    pdl_wait();
+    pdl_trigger();
+    block_norm_quant<NQ_NATURAL>(x, w, eps, n, sm, reinterpret_cast<int2 *>(q), s, &inv_sh, threadIdx.x, blockDim.x);
+    if (xn) {
+        float inv = inv_sh;
+        for (int i = threadIdx.x; i < n; i += blockDim.x) xn[i] = __fmul_rn(__fmul_rn(sm[i], inv), w[i]);
     }
-    __syncthreads();
-    int warp = threadIdx.x >> 5, lane = threadIdx.x & 31, nw = blockDim.x >> 5;
-    for (int b = warp; b < n / 32; b += nw) warp_quant_block(xs[b * 32 + lane], lane, q + b * 32, s + b);
 }
 
-void launch_rmsnorm_quant(const float *x, const float *w, float eps, int n, float *xn, int8_t *q, float *s, cudaStream_t st) {
-    rmsnorm_quant_kernel<<<1, 512, n * sizeof(float), st>>>(x, w, eps, n, xn, q, s);
+cudaError_t launch_rmsnorm_quant(const float *x, const float *w, float eps, int n, float *xn, int8_t *q, float *s, bool pdl, cudaStream_t st) {
+    return launch_k(rmsnorm_quant_kernel, dim3(1), dim3(512), (size_t)n * sizeof(float), st, pdl, x, w, eps, n, xn, q, s);
 }
 
 // ---------------------------------------------------------------- embedding gather

@@ -118,7 +118,7 @@ struct brrr_model {
     uint32_t *h_in = nullptr, *h_out = nullptr;
     cudaGraphExec_t g_head = nullptr, g_nohead = nullptr;
     int launches_head = 0, launches_nohead = 0;
-    uint32_t pending_base = 0;   // n_out at the start of the enqueued decode run
+    bool use_pdl = true;         // chain the step's kernels with programmatic dependent launch
     std::vector<void *> allocs;
 
     template <typename T> int alloc(T **p, size_t n) {
@@ -164,8 +164,8 @@ int load_f32(brrr_model *m, const Source &s, uint32_t layer, int kind, size_t n,
 
 int alloc_q8(brrr_model *m, int rows, int cols, Q8Dev *q) {
     q->rows = rows; q->cols = cols;
-    TRY(m->alloc(&q->wq, (size_t)rows * cols));
-    TRY(m->alloc(&q->ws, (size_t)rows * (cols / 32)));
+    TRY(m->alloc(&q->data, q8_bytes(rows, cols)));
+    CU(cudaMemsetAsync(q->data, 0, q8_bytes(rows, cols), m->stream));   // padding rows quantise to zero
     return BRRR_OK;
 }
 
@@ -178,8 +178,7 @@ int load_q8_part(brrr_model *m, const Source &s, uint32_t layer, int kind, int r
 
 int load_mx(brrr_model *m, const Source &s, uint32_t layer, int kind, int rows, int blocks, MxDev *x, void *scratch) {
     x->rows = rows; x->blocks = blocks;
-    TRY(m->alloc(&x->nib, (size_t)rows * blocks * 16));
-    TRY(m->alloc(&x->exps, (size_t)rows * blocks));
+    TRY(m->alloc(&x->data, mx_bytes(rows, blocks)));
     TRY(fetch(m, s, layer, kind, 39, (size_t)rows * blocks * 32, scratch));
     launch_mx_pack((const uint8_t *)scratch, *x, m->stream);
     CU(cudaGetLastError());
@@ -226,36 +225,49 @@ int check_cfg(const brrr_cfg &c) {
 
 // The decode step, enqueued kernel by kernel (captured into a graph, or run directly by the
 // trace path).  Stage order and data flow follow forward_worker (engine_gpt2.rs:751-934).
-enum { ST_EMBED = 0, ST_ATTN_NORM, ST_QKV, ST_ATTN, ST_OPROJ, ST_FFN_IN, ST_GATE_UP, ST_SWIGLU, ST_DOWN, ST_HEAD_NORM, ST_HEAD, ST_FINISH, ST_COUNT };
-const char *const kStageNames[ST_COUNT] = {"embed", "attn_norm_quant", "qkv_gemv", "attention", "oproj_gemv", "ffn_norm_router",
-                                           "gate_up_mxfp4", "swiglu_quant", "down_combine_mxfp4", "head_norm_quant", "head_gemv_argmax", "finish_token"};
+enum { ST_EMBED = 0, ST_QKV, ST_ATTN, ST_OPROJ, ST_ROUTER, ST_GATE_UP, ST_DOWN, ST_HEAD_NORM, ST_HEAD, ST_FINISH, ST_COUNT };
+const char *const kStageNames[ST_COUNT] = {"embed", "norm_qkv_gemv", "attention", "oproj_gemv", "norm_router_topk",
+                                           "norm_gate_up_swiglu_mxfp4", "down_combine_mxfp4", "head_norm_quant", "head_gemv_argmax", "finish_token"};
 
+#define CUL(call)                                                                                        \
+    do {                                                                                                 \
+        cudaError_t _e = (call);                                                                         \
+        if (_e != cudaSuccess) {                                                                         \
+            snprintf(g_cuda_err, sizeof g_cuda_err, "%s:%d %s: %s", __FILE__, __LINE__, #call, cudaGetErrorString(_e)); \
+            return BRRR_ERR_CUDA;                                                                        \
+        }                                                                                                \
+    } while (0)
+
+// The decode step, enqueued kernel by kernel (captured into a graph, or run directly by the
+// trace path).  Stage order and data flow follow forward_worker (engine_gpt2.rs:751-934); the
+// reference's nine barrier-separated stages per layer are six kernels here, chained with
+// programmatic dependent launch.
 int enqueue_step(brrr_model *m, bool want, float *trace_dev, int *nlaunch, unsigned mask = ~0u) {
     const brrr_cfg &c = m->cfg;
     const int d = c.n_embd, nh = c.n_head, nkv = c.n_head_kv, topk = c.n_expert_used;
     cudaStream_t s = m->stream;
+    const bool pdl = m->use_pdl && !trace_dev && mask == ~0u;
     int n = 0;
     auto on = [&](int st) { if (mask & (1u << st)) { n++; return true; } return false; };
     if (on(ST_EMBED)) launch_embed(m->tok_embd, d, m->st, m->x, s);
     if (trace_dev) CU(cudaMemcpyAsync(trace_dev, m->x, d * sizeof(float), cudaMemcpyDeviceToDevice, s));
     for (int il = 0; il < c.n_layer; il++) {
         Layer &ly = m->L[il];
-        if (on(ST_ATTN_NORM)) launch_rmsnorm_quant(m->x, ly.attn_norm, c.rms_eps, d, nullptr, m->xq, m->xs, s);
-        if (on(ST_QKV)) launch_q8_gemv(ly.wqkv, m->xq, m->xs, ly.bqkv, m->qkv, Q8_EPI_BIAS, m->st, s);
+        if (on(ST_QKV)) CUL(launch_q8_stream(ly.wqkv, m->x, ly.attn_norm, c.rms_eps, nullptr, nullptr, ly.bqkv, m->qkv, Q8_EPI_BIAS, m->st, pdl && n > 1, s));
         int window = ((il + 1) % 2 != 0) ? c.sliding_window : 0;         // even layer index: sliding window
         if (window >= BRRR_MAXSEQ) window = 0;
-        if (on(ST_ATTN)) launch_attn_decode(m->qkv, ly.kc, ly.vc, m->rope, ly.sinks, nh, nkv, m->st, 0, window, m->ao, m->aq, m->as, s);
-        if (on(ST_OPROJ)) launch_q8_gemv(ly.wo, m->aq, m->as, ly.bo, m->x, Q8_EPI_RESID_BIAS, m->st, s);
-        if (on(ST_FFN_IN)) launch_ffn_in(m->x, ly.ffn_norm, c.rms_eps, d, m->xq, m->xs, ly.ginp, ly.ginp_b, c.n_expert, topk, m->rlogits, m->top, m->wts,
-                                         &m->st->router_done, s);
-        if (on(ST_GATE_UP)) launch_gate_up(ly.gate, ly.up, ly.gate_b, ly.up_b, m->top, topk, d, m->xq, m->xs, m->gu, s);
-        if (on(ST_SWIGLU)) launch_swiglu_quant(m->gu, topk, d, m->hq, m->hs, s);
-        if (on(ST_DOWN)) launch_down_combine(ly.down, ly.down_b, m->top, m->wts, topk, d, m->hq, m->hs, m->x, s);
+        if (on(ST_ATTN)) CUL(launch_attn_decode(m->qkv, ly.kc, ly.vc, m->rope, ly.sinks, nh, nkv, m->st, 0, window, m->ao, m->aq, m->as, m->st, pdl, s));
+        if (on(ST_OPROJ)) CUL(launch_q8_stream(ly.wo, nullptr, nullptr, 0.0f, m->aq, m->as, ly.bo, m->x, Q8_EPI_RESID_BIAS, m->st, pdl, s));
+        if (on(ST_ROUTER)) CUL(launch_ffn_in(m->x, ly.ffn_norm, c.rms_eps, d, ly.ginp, ly.ginp_b, c.n_expert, topk, m->rlogits, m->top, m->wts,
+                                             &m->st->router_done, m->st, pdl, s));
+        if (on(ST_GATE_UP)) CUL(launch_gate_up(ly.gate, ly.up, ly.gate_b, ly.up_b, m->top, topk, d, m->x, ly.ffn_norm, c.rms_eps, nullptr, nullptr,
+                                               m->hq, m->hs, nullptr, m->st, pdl, s));
+        if (on(ST_DOWN)) CUL(launch_down_combine(ly.down, ly.down_b, m->top, m->wts, topk, d, m->hq, m->hs, m->x, m->st, pdl, s));
         if (trace_dev) CU(cudaMemcpyAsync(trace_dev + (size_t)(il + 1) * d, m->x, d * sizeof(float), cudaMemcpyDeviceToDevice, s));
     }
     if (want) {
-        if (on(ST_HEAD_NORM)) launch_rmsnorm_quant(m->x, m->out_norm, c.rms_eps, d, nullptr, m->xq, m->xs, s);
-        if (on(ST_HEAD)) launch_q8_gemv(m->head, m->xq, m->xs, nullptr, m->logits, Q8_EPI_HEAD, m->st, s);
+        if (on(ST_HEAD_NORM)) CUL(launch_rmsnorm_quant(m->x, m->out_norm, c.rms_eps, d, nullptr, m->xq, m->xs, pdl, s));
+        if (on(ST_HEAD)) CUL(launch_q8_direct(m->head, m->xq, m->xs, nullptr, m->logits, Q8_EPI_HEAD, m->st, pdl, s));
         if (on(ST_FINISH)) launch_finish_token(m->st, s);
     }
     CU(cudaGetLastError());
@@ -280,7 +292,7 @@ int build_model(brrr_model *m, const Source &src) {
     const int d = c.n_embd, nh = c.n_head, nkv = c.n_head_kv, hd = c.head_dim, nb = d / 32, ne = c.n_expert, topk = c.n_expert_used;
     CU(cudaSetDevice(m->device));
     CU(cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking));
-    { int e = ffn_in_init(); if (e) { snprintf(g_cuda_err, sizeof g_cuda_err, "ffn_in_init: %s", cudaGetErrorString((cudaError_t)e)); return BRRR_ERR_CUDA; } }
+    if (const char *e = getenv("BRRR_NOPDL")) m->use_pdl = !(e[0] && e[0] != '0');
 
     // scratch for one raw tensor: the largest of the bf16 matrices and one MXFP4 expert tensor
     size_t scratch_bytes = std::max({(size_t)c.n_vocab * d * 2, (size_t)ne * d * nb * 17, (size_t)nh * hd * d * 2});
@@ -306,7 +318,10 @@ int build_model(brrr_model *m, const Source &src) {
         TRY(fetch(m, src, il, BRRR_T_BV, 0, nkv * hd, ly.bqkv + (nh + nkv) * hd));
         TRY(load_f32(m, src, il, BRRR_T_BO, d, &ly.bo));
         TRY(load_f32(m, src, il, BRRR_T_SINKS, nh, &ly.sinks));
-        TRY(load_f32(m, src, il, BRRR_T_ROUTER_W, (size_t)ne * d, &ly.ginp));
+        TRY(m->alloc(&ly.ginp, router_packed_floats(ne, d)));
+        TRY(fetch(m, src, il, BRRR_T_ROUTER_W, 0, (size_t)ne * d, scratch));
+        launch_router_pack((const float *)scratch, ne, d, ly.ginp, m->stream);
+        CU(cudaGetLastError());
         TRY(load_f32(m, src, il, BRRR_T_ROUTER_B, ne, &ly.ginp_b));
         TRY(load_mx(m, src, il, BRRR_T_GATE, ne * d, nb, &ly.gate, scratch));
         TRY(load_mx(m, src, il, BRRR_T_UP, ne * d, nb, &ly.up, scratch));
@@ -316,7 +331,7 @@ int build_model(brrr_model *m, const Source &src) {
         TRY(load_f32(m, src, il, BRRR_T_DOWN_B, (size_t)ne * d, &ly.down_b));
         TRY(m->alloc(&ly.kc, (size_t)BRRR_MAXSEQ * nkv * hd));
         TRY(m->alloc(&ly.vc, (size_t)BRRR_MAXSEQ * nkv * hd));
-        CU(cudaMemsetAsync(ly.kc, 0, (size_t)BRRR_MAXSEQ * nkv * hd * 4, m->stream));
+        CU(cudaMemsetAsync(ly.kc, 0, (size_t)BRRR_MAXSEQ * nkv * hd * 4, m->stream));   // layout [kv head][position][64]
         CU(cudaMemsetAsync(ly.vc, 0, (size_t)BRRR_MAXSEQ * nkv * hd * 4, m->stream));
     }
     TRY(m->alloc(&m->tok_embd, (size_t)c.n_vocab * d));
@@ -340,6 +355,10 @@ int build_model(brrr_model *m, const Source &src) {
     CU(cudaMallocHost(&m->h_in, 16));
     CU(cudaMallocHost(&m->h_out, BRRR_MAXSEQ * sizeof(uint32_t)));
     CU(cudaStreamSynchronize(m->stream));
+    // one direct (un-captured) step configures every kernel's attributes and validates the launches
+    TRY(enqueue_step(m, true, nullptr, nullptr));
+    CU(cudaStreamSynchronize(m->stream));
+    CU(cudaMemsetAsync(m->st, 0, sizeof(DevState), m->stream));
     TRY(capture(m, true, &m->g_head, &m->launches_head));
     TRY(capture(m, false, &m->g_nohead, &m->launches_nohead));
     CU(cudaStreamSynchronize(m->stream));
@@ -481,8 +500,9 @@ extern "C" int brrr_forward(brrr_model *m, uint32_t tok, uint32_t pos, int want,
     m->h_in[0] = tok; m->h_in[1] = pos;
     CU(cudaMemcpyAsync(m->st, m->h_in, 8, cudaMemcpyHostToDevice, m->stream));   // DevState.tok, .pos
     TRY(run_graph(m, want != 0));
-    if (want) CU(cudaMemcpyAsync(m->h_out, &m->st->tok, 4, cudaMemcpyDeviceToHost, m->stream));
+    CU(cudaMemcpyAsync(m->h_out, m->st, 32, cudaMemcpyDeviceToHost, m->stream));   // tok .. err
     CU(cudaStreamSynchronize(m->stream));
+    if (m->h_out[6] != 0) { snprintf(g_cuda_err, sizeof g_cuda_err, "device wait timed out (code %u)", m->h_out[6]); return BRRR_ERR_STATE; }
     if (want && out_tok) *out_tok = m->h_out[0];
     return BRRR_OK;
 }
@@ -512,7 +532,9 @@ extern "C" int brrr_decode_wait(brrr_model *m, uint32_t n, uint32_t *out_toks) {
     if (!m || !out_toks || n == 0 || n > BRRR_MAXSEQ) return BRRR_ERR_ARG;
     CU(cudaSetDevice(m->device));
     CU(cudaMemcpyAsync(m->h_out, m->st->out, n * sizeof(uint32_t), cudaMemcpyDeviceToHost, m->stream));
+    CU(cudaMemcpyAsync(m->h_in, &m->st->err, 4, cudaMemcpyDeviceToHost, m->stream));
     CU(cudaStreamSynchronize(m->stream));
+    if (m->h_in[0] != 0) { snprintf(g_cuda_err, sizeof g_cuda_err, "device wait timed out (code %u)", m->h_in[0]); return BRRR_ERR_STATE; }
     memcpy(out_toks, m->h_out, n * sizeof(uint32_t));
     return BRRR_OK;
 }
@@ -569,10 +591,9 @@ extern "C" int brrr_moe_ffn_step(brrr_model *m, int il, const float *d_xn, float
     const int d = c.n_embd, topk = c.n_expert_used;
     Layer &ly = m->L[il];
     cudaStream_t s = m->stream;
-    launch_ffn_in(d_xn, nullptr, c.rms_eps, d, m->xq, m->xs, ly.ginp, ly.ginp_b, c.n_expert, topk, m->rlogits, m->top, m->wts, &m->st->router_done, s);
-    launch_gate_up(ly.gate, ly.up, ly.gate_b, ly.up_b, m->top, topk, d, m->xq, m->xs, m->gu, s);
-    launch_swiglu_quant(m->gu, topk, d, m->hq, m->hs, s);
-    launch_down_combine(ly.down, ly.down_b, m->top, m->wts, topk, d, m->hq, m->hs, d_x, s);
+    CUL(launch_ffn_in(d_xn, nullptr, c.rms_eps, d, ly.ginp, ly.ginp_b, c.n_expert, topk, m->rlogits, m->top, m->wts, &m->st->router_done, m->st, false, s));
+    CUL(launch_gate_up(ly.gate, ly.up, ly.gate_b, ly.up_b, m->top, topk, d, d_xn, nullptr, c.rms_eps, nullptr, nullptr, m->hq, m->hs, nullptr, m->st, false, s));
+    CUL(launch_down_combine(ly.down, ly.down_b, m->top, m->wts, topk, d, m->hq, m->hs, d_x, m->st, false, s));
     CU(cudaGetLastError());
     if (d_top) CU(cudaMemcpyAsync(d_top, m->top, topk * sizeof(int32_t), cudaMemcpyDeviceToDevice, s));
     if (d_wts) CU(cudaMemcpyAsync(d_wts, m->wts, topk * sizeof(float), cudaMemcpyDeviceToDevice, s));
@@ -587,8 +608,7 @@ static uint64_t stage_bytes_per_launch(const brrr_model *m, int stage, uint32_t 
     auto q8 = [](uint64_t rows, uint64_t cols) { return rows * cols + rows * (cols / 32) * 4; };
     switch (stage) {
     case ST_EMBED: return d * 2;
-    case ST_ATTN_NORM: case ST_HEAD_NORM: return d * 8;
-    case ST_QKV: return q8((nh + 2 * nkv) * hd, d) + (nh + 2 * nkv) * hd * 4;
+    case ST_QKV: return q8((nh + 2 * nkv) * hd, d) + (nh + 2 * nkv) * hd * 4 + d * 8;
     case ST_ATTN: {
         uint64_t tot = 0;
         for (int il = 0; il < c.n_layer; il++) {
@@ -598,10 +618,10 @@ static uint64_t stage_bytes_per_launch(const brrr_model *m, int stage, uint32_t 
         return tot / c.n_layer;
     }
     case ST_OPROJ: return q8(d, nh * hd) + d * 4;
-    case ST_FFN_IN: return ne * d * 4 + ne * 4 + d * 8;
-    case ST_GATE_UP: return k * 2 * d * nb * 17 + k * 2 * d * 4;
-    case ST_SWIGLU: return k * 2 * d * 4;
+    case ST_ROUTER: return ne * d * 4 + ne * 4 + d * 8;
+    case ST_GATE_UP: return k * 2 * d * nb * 17 + k * 2 * d * 4 + d * 8;
     case ST_DOWN: return k * d * nb * 17 + k * d * 4;
+    case ST_HEAD_NORM: return d * 8;
     case ST_HEAD: return q8(c.n_vocab, d);
     }
     return 0;
@@ -638,5 +658,14 @@ extern "C" int brrr_stage_time(brrr_model *m, int stage, uint32_t pos, int reps,
     if (ms_per_launch) *ms_per_launch = n ? ms / ((float)reps * n) : 0.0f;
     if (bytes_per_launch) *bytes_per_launch = stage_bytes_per_launch(m, stage, pos);
     if (launches_per_step) *launches_per_step = n;
+    return BRRR_OK;
+}
+
+// Debug tap: the in-kernel clock stamps of the last step (all zero unless built with BRRR_TIMELINE).
+extern "C" int brrr_debug_stamps(brrr_model *m, long long *out32) {
+    if (!m || !out32) return BRRR_ERR_ARG;
+    CU(cudaSetDevice(m->device));
+    CU(cudaMemcpyAsync(out32, m->st->stamps, 32 * sizeof(long long), cudaMemcpyDeviceToHost, m->stream));
+    CU(cudaStreamSynchronize(m->stream));
     return BRRR_OK;
 }

@@ -114,6 +114,10 @@ int brrr_stage_count(void);
 const char *brrr_stage_name(int stage);
 int brrr_stage_time(brrr_model *m, int stage, uint32_t pos, int reps, float *ms_per_launch, uint64_t *bytes_per_launch, int *launches_per_step);
 
+/* Debug tap: 32 SM-clock stamps recorded inside the kernels of the last step; all zero unless the
+ * library was built with -DBRRR_TIMELINE.  No counterpart in the reference. */
+int brrr_debug_stamps(brrr_model *m, long long *out32);
+
 /* ---------------------------------------------------------------- stage-level entry points
  * Device pointers in, device pointers out.  They launch the same kernels the forward pass uses. */
 
@@ -130,7 +134,7 @@ typedef struct brrr_q8mat brrr_q8mat;
 typedef struct brrr_mxmat brrr_mxmat;
 
 /* bf16 [rows][cols] (device) -> Q8 matrix, quantised per 32-block as Q8Mat::from_bf16
- * (src/bin/engine_gpt2.rs:464-494). rows % 4 == 0, cols % 64 == 0. */
+ * (src/bin/engine_gpt2.rs:464-494). cols % 64 == 0. */
 int brrr_q8mat_from_bf16(const uint16_t *d_w, int rows, int cols, brrr_q8mat **out, void *stream);
 /* copies back the quantised values in natural order: q[rows][cols], s[rows][cols/32] (device) */
 int brrr_q8mat_export(const brrr_q8mat *m, int8_t *d_q, float *d_s, void *stream);
@@ -139,7 +143,7 @@ void brrr_q8mat_free(brrr_q8mat *m);
 int brrr_q8_matvec(const brrr_q8mat *w, const int8_t *d_xq, const float *d_xs, float *d_y, void *stream);
 
 /* GGUF MXFP4 rows (17-byte blocks, device) -> engine layout.  Replaces repack_mx
- * (src/bin/engine_gpt2.rs:439-461). rows % 8 == 0, blocks % 2 == 0. */
+ * (src/bin/engine_gpt2.rs:439-461). rows % 16 == 0, blocks % 2 == 0. */
 int brrr_mxmat_from_gguf(const uint8_t *d_raw, int rows, int blocks, brrr_mxmat **out, void *stream);
 void brrr_mxmat_free(brrr_mxmat *m);
 /* y[i] = row (row0 + i) . Q8 activation for i < nrows.  d_blockdots (nullable) receives the exact
@@ -158,7 +162,7 @@ int brrr_swiglu_quant(const float *d_gu, int topk, int d, int8_t *d_hq, float *d
 
 /* Decode attention for all heads at position pos.  d_qkv holds this token's projected q | k | v
  * (bias added, not rotated); the kernel rotates q and k, appends k/v to the cache
- * [pos][n_head_kv][64] and attends over start..pos, then quantises the output.  d_rope is the
+ * [n_head_kv][BRRR_MAXSEQ][64] and attends over start..pos, then quantises the output.  d_rope is the
  * [BRRR_MAXSEQ][32][2] cos/sin table.  Replaces rope_yarn + the cache write + the attention stage
  * (src/bin/engine_gpt2.rs:575-587, 783-837). head_dim is 64. */
 int brrr_attn_decode(const float *d_qkv, float *d_kc, float *d_vc, const float *d_rope, const float *d_sinks,

@@ -86,7 +86,7 @@ def test_q8_pack_and_matvec(L, orc, dev, rows, cols):
     L.brrr_q8mat_free(h)
 
 
-@pytest.mark.parametrize("rows,blocks", [(8, 2), (64, 90), (200, 4), (2880, 90)])
+@pytest.mark.parametrize("rows,blocks", [(16, 2), (64, 90), (208, 4), (2880, 90), (48, 26)])
 def test_mx_pack_and_matvec_int_exact(L, orc, dev, rows, blocks):
     """int32 lane accumulators of every (row, block) equal the oracle's; f32 row results too."""
     import torch
@@ -122,7 +122,7 @@ def test_mx_pack_and_matvec_int_exact(L, orc, dev, rows, blocks):
 def test_mx_all_nibble_codes(L, orc, dev):
     """Every 4-bit code against every sign of activation, one code pair per byte."""
     import torch
-    rows, blocks = 8, 16
+    rows, blocks = 16, 16
     raw = np.zeros((rows * blocks, 17), np.uint8)
     raw[:, 0] = 128
     codes = np.arange(256, dtype=np.uint8)
@@ -179,7 +179,7 @@ def test_swiglu_quant(L, orc, dev):
     assert np.array_equal(dq.cpu().numpy(), hq) and np.array_equal(bits(ds.cpu().numpy()), bits(hs))
 
 
-@pytest.mark.parametrize("pos,start", [(0, 0), (5, 0), (200, 0), (200, 73), (300, 173), (1500, 0)])
+@pytest.mark.parametrize("pos,start", [(0, 0), (5, 0), (128, 0), (129, 0), (200, 0), (200, 73), (300, 173), (1500, 0), (4095, 0), (4095, 3968)])
 def test_attention_decode(L, orc, brrr, dev, pos, start):
     """RoPE + cache append + sink softmax + Q8 of the output, all heads, vs the oracle per head."""
     import torch
@@ -190,11 +190,11 @@ def test_attention_decode(L, orc, brrr, dev, pos, start):
     ocfg = orc.make_cfg(d=nh * hd, nh=nh, nkv=nkv, hd=hd, nl=1, ne=8, topk=4, nvocab=512)
     assert np.array_equal(bits(tab), bits(orc.rope_table(ocfg)))
     rng = np.random.default_rng(pos)
-    kc = np.zeros((4096, nkv, hd), np.float32); vc = np.zeros((4096, nkv, hd), np.float32)
+    kc = np.zeros((4096, nkv, hd), np.float32); vc = np.zeros((4096, nkv, hd), np.float32)   # oracle layout [pos][kv head][64]
     kc[:pos] = rng.standard_normal((pos, nkv, hd)); vc[:pos] = rng.standard_normal((pos, nkv, hd))
     qkv = rng.standard_normal((nh + 2 * nkv) * hd).astype(np.float32)
     sinks = rng.standard_normal(nh).astype(np.float32)
-    dkc, dvc = to_dev(kc, dev), to_dev(vc, dev)
+    dkc, dvc = to_dev(kc.transpose(1, 0, 2), dev), to_dev(vc.transpose(1, 0, 2), dev)   # engine layout [kv head][pos][64]
     dao = torch.empty(nh * hd, dtype=torch.float32, device=dev)
     daq = torch.empty(nh * hd, dtype=torch.int8, device=dev)
     das = torch.empty(nh * hd // 32, dtype=torch.float32, device=dev)
@@ -211,7 +211,7 @@ def test_attention_decode(L, orc, brrr, dev, pos, start):
     kc[pos] = k; vc[pos] = v
     ao = np.concatenate([orc.attn_head(q[hh], kc, vc, nkv, hd, hh // (nh // nkv), start, pos, float(sinks[hh])) for hh in range(nh)])
     aq, asb = orc.quant_q8(ao)
-    assert np.array_equal(bits(dkc.cpu().numpy()[pos]), bits(k)) and np.array_equal(bits(dvc.cpu().numpy()[pos]), bits(v))
+    assert np.array_equal(bits(dkc.cpu().numpy()[:, pos]), bits(k)) and np.array_equal(bits(dvc.cpu().numpy()[:, pos]), bits(v))
     assert np.array_equal(bits(dao.cpu().numpy()), bits(ao))
     assert np.array_equal(daq.cpu().numpy(), aq) and np.array_equal(bits(das.cpu().numpy()), bits(asb))
 
