@@ -29,8 +29,17 @@ __device__ __forceinline__ float block_rms_inv(const float *x, int n, float eps,
         float acc = 0.0f;
         int n16 = n & ~15;
         if (c < 16) {
-#pragma unroll 8
-            for (int i = c; i < n16; i += 16) { float v = x[i]; acc = __fmaf_rn(v, v, acc); }
+            // chain c: x[c], x[c+16], ... in order; values are fetched 12 at a time so that only
+            // the fused multiply-adds sit on the dependent path
+            int i = c;
+            for (; i + 16 * 11 < n16; i += 16 * 12) {
+                float v[12];
+#pragma unroll
+                for (int k = 0; k < 12; k++) v[k] = x[i + 16 * k];
+#pragma unroll
+                for (int k = 0; k < 12; k++) acc = __fmaf_rn(v[k], v[k], acc);
+            }
+            for (; i < n16; i += 16) { float v = x[i]; acc = __fmaf_rn(v, v, acc); }
         }
         acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 4));
         acc = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 8));
@@ -51,11 +60,27 @@ __device__ __forceinline__ float block_rms_inv(const float *x, int n, float eps,
 //   NQ_Q8:      xp[b*4+j] = {elements 4j..4j+3, elements 16+4j..16+4j+3}   (Q8 GEMV image)
 //   NQ_MX:      xp[b*4+j] = the same two words byte-interleaved for the MXFP4 lane dot
 //   NQ_NATURAL: quants in element order to (int8_t*)xp, scales to xsc       (global buffers)
-// xf: n floats of shared scratch.  Must be called by all threads; nthreads % 32 == 0, n % 32 == 0,
-// x 16-byte aligned.  Ends with the image complete but NOT yet synchronised.
+// xf: n floats of shared scratch.  The static norm weights of the first MAXG passes are taken
+// from wreg[], which the caller fills with norm_prefetch() before it waits on the previous
+// kernel, so no cold global load sits on the critical path; later passes read norm_w directly.
+// Must be called by all threads; nthreads % 32 == 0, n % 32 == 0, x and norm_w 16-byte aligned.
+// Ends with the image complete but NOT yet synchronised.
 enum { NQ_Q8 = 0, NQ_MX = 1, NQ_NATURAL = 2 };
-template <int LAYOUT>
-__device__ __forceinline__ void block_norm_quant(const float *__restrict__ x, const float *__restrict__ norm_w, float eps, int n,
+__device__ __forceinline__ void stage_vec4(const float *__restrict__ src, float *dst, int n, int tid, int nthreads) {
+    for (int g = tid; g < (n >> 2); g += nthreads) reinterpret_cast<float4 *>(dst)[g] = reinterpret_cast<const float4 *>(src)[g];
+}
+
+template <int MAXG>
+__device__ __forceinline__ void norm_prefetch(const float *__restrict__ norm_w, int n, float4 (&wreg)[MAXG], int tid, int nthreads) {
+#pragma unroll
+    for (int p = 0; p < MAXG; p++) {
+        const int g = tid + p * nthreads;
+        wreg[p] = (norm_w && g < (n >> 2)) ? reinterpret_cast<const float4 *>(norm_w)[g] : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+}
+
+template <int LAYOUT, int MAXG>
+__device__ __forceinline__ void block_norm_quant(const float *__restrict__ x, const float *norm_w, const float4 (&wreg)[MAXG], float eps, int n,
                                                  float *xf, int2 *xp, float *xsc, float *inv_sh, int tid, int nthreads) {
     const int groups = n >> 2;
     const float4 *x4 = reinterpret_cast<const float4 *>(x);
@@ -65,12 +90,17 @@ __device__ __forceinline__ void block_norm_quant(const float *__restrict__ x, co
     float inv = 1.0f;
     if (norm_w) inv = block_rms_inv(xf, n, eps, inv_sh);
     const int npass = (groups + nthreads - 1) / nthreads;
-    for (int p = 0; p < npass; p++) {
+    // The passes are independent; unrolling lets their divisions and shuffles overlap.
+#pragma unroll
+    for (int p = 0; p < 8; p++) {
+        if (p >= npass) break;
         const int g = tid + p * nthreads;
         const bool live = g < groups;
         float4 v = live ? xf4[g] : make_float4(0.f, 0.f, 0.f, 0.f);
         if (norm_w && live) {
-            float4 w = reinterpret_cast<const float4 *>(norm_w)[g];
+            float4 w;
+            if (p < MAXG) w = wreg[p < MAXG ? p : 0];
+            else w = reinterpret_cast<const float4 *>(norm_w)[g];
             v.x = __fmul_rn(__fmul_rn(v.x, inv), w.x); v.y = __fmul_rn(__fmul_rn(v.y, inv), w.y);
             v.z = __fmul_rn(__fmul_rn(v.z, inv), w.z); v.w = __fmul_rn(__fmul_rn(v.w, inv), w.w);
         }

@@ -136,10 +136,16 @@ struct DevState {
     uint32_t err;                  // DEV_ERR_* (0 = none); set by a kernel whose bounded wait ran out
     uint32_t pad;
     uint32_t out[BRRR_MAXSEQ];
-    long long stamps[32];          // optional in-kernel clock stamps (timeline builds only)
+    long long stamps[256];          // optional in-kernel clock stamps (timeline builds only)
 };
 #ifdef BRRR_TIMELINE
+__device__ __forceinline__ unsigned long long brrr_gtime() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
+// wall-clock (ns) marks: END = latest finish over all CTAs of a kernel, GO = CTA 0 released from its dependency wait
+#define BRRR_GT_END(state, i) do { if ((state) && threadIdx.x == 0) atomicMax((unsigned long long *)&(state)->stamps[i], brrr_gtime()); } while (0)
+#define BRRR_GT_GO(state, i) do { if ((state) && threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0) (state)->stamps[i] = (long long)brrr_gtime(); } while (0)
 #define BRRR_STAMP(state, i) do { if ((state) && threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0) (state)->stamps[i] = clock64(); } while (0)
 #else
+#define BRRR_GT_END(state, i) do { } while (0)
+#define BRRR_GT_GO(state, i) do { } while (0)
 #define BRRR_STAMP(state, i) do { } while (0)
 #endif

@@ -40,7 +40,7 @@ cudaError_t launch_down_combine(MxDev down, const float *down_b, const int32_t *
 
 // ---- router (kernels_router.cu)
 // The router matrix is used in a tiled layout: [32-expert group][tile][32][RT_STRIDE] floats.
-constexpr int RT_TJ = 128;                       // tile width (elements of d)
+constexpr int RT_TJ = 256;                       // tile width (elements of d)
 constexpr int RT_STRIDE = RT_TJ + 4;             // padded row stride in floats
 constexpr int RT_TILE_FLOATS = 32 * RT_STRIDE;
 size_t router_packed_floats(int ne, int d);

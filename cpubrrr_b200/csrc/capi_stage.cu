@@ -27,7 +27,7 @@ extern "C" int brrr_rmsnorm_quant(const float *d_x, const float *d_w, float eps,
 }
 
 extern "C" int brrr_q8mat_from_bf16(const uint16_t *d_w, int rows, int cols, brrr_q8mat **out, void *stream) {
-    if (!d_w || !out || rows <= 0 || cols <= 0 || cols % 64 || cols > 8192) return BRRR_ERR_ARG;
+    if (!d_w || !out || rows <= 0 || cols <= 0 || cols % 64 || cols > 4096) return BRRR_ERR_ARG;
     brrr_q8mat *q = new brrr_q8mat();
     q->m.rows = rows; q->m.cols = cols;
     if (cudaMalloc(&q->m.data, q8_bytes(rows, cols)) != cudaSuccess) { delete q; return BRRR_ERR_NOMEM; }

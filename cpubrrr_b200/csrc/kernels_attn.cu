@@ -67,22 +67,29 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(AttnArgs a) {
         mbar_expect_tx(&bars[slot], (uint32_t)cnt * HD * 4);
         bulk_g2s(tiles + (size_t)slot * AT_TILE * HD, base + (size_t)t * AT_TILE * HD, (uint32_t)cnt * HD * 4, &bars[slot]);
     };
+    BRRR_STAMP(a.err_state, 160);
     if (tid == 0) {
         for (int s = 0; s < AT_SLOTS; s++) { mbar_init(&kbar[s], 1); mbar_init(&vbar[s], 1); }
         mbar_fence_init();
         for (int t = 0; t < min(AT_SLOTS, ntiles); t++) { issue(kbase, ktiles, kbar, t); issue(vbase, vtiles, vbar, t); }
     }
+    // static / step-constant operands: the sink and this position's rotation
+    const float sink = a.sinks[h];
+    float rc = 0.0f, rs = 0.0f;
+    if (tid < 64) { rc = a.rope[((size_t)pos * 32 + (tid & 31)) * 2]; rs = a.rope[((size_t)pos * 32 + (tid & 31)) * 2 + 1]; }
+    BRRR_STAMP(a.err_state, 161);
     pdl_wait();          // qkv projection done
+    BRRR_STAMP(a.err_state, 162);
+    BRRR_GT_GO(a.err_state, 190);
     pdl_trigger();
     waiter.poison_if_failed();
 
     // ---- RoPE (NeoX halves, table holds cos*mscale / sin*mscale) on q and k; v passes through
-    const float sink = a.sinks[h];
     if (tid < 64) {
         const float *src = tid < 32 ? a.qkv + h * HD : a.qkv + (a.nh + kvh) * HD;
         float *dst = tid < 32 ? q : kcur;
         int i = tid & 31;
-        float c = a.rope[((size_t)pos * 32 + i) * 2], s = a.rope[((size_t)pos * 32 + i) * 2 + 1];
+        const float c = rc, s = rs;
         float x0 = src[i], x1 = src[32 + i];
         dst[i] = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
         dst[32 + i] = __fadd_rn(__fmul_rn(x1, c), __fmul_rn(x0, s));
@@ -143,6 +150,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(AttnArgs a) {
     }
     __syncthreads();
 
+    BRRR_STAMP(a.err_state, 163);
     // ---- max (order-free), then exponentials in place
     float mx = sink;
     for (int t = tid; t < n; t += AT_THREADS) mx = fmaxf(mx, sc[t]);
@@ -155,6 +163,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(AttnArgs a) {
     for (int t = tid; t < n; t += AT_THREADS) sc[t] = brrr_expf_dev(__fsub_rn(sc[t], mx));
     __syncthreads();
 
+    BRRR_STAMP(a.err_state, 164);
     // ---- serial sums: thread u < 64 owns output dim u, thread 64 the denominator
     float acc = 0.0f;
     if (tid == 64) {
@@ -186,6 +195,8 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(AttnArgs a) {
         // this head owns Q8 blocks 2h and 2h+1 of the attention output
         warp_quant_block(o, tid & 31, a.aq + h * HD + (tid >> 5) * 32, a.as + h * 2 + (tid >> 5));
     }
+    BRRR_STAMP(a.err_state, 165);
+    BRRR_GT_END(a.err_state, 191);
 }
 
 static size_t attn_smem() { return AT_TILE_BYTES * AT_SLOTS * 2 + (size_t)BRRR_MAXSEQ * 4 + AT_SLOTS * 2 * 8; }

@@ -80,6 +80,49 @@ __device__ __forceinline__ float mx_pair_step(const unsigned char *unit, int rl,
     return acc;
 }
 
+// N consecutive block pairs of one lane chain from units resident in shared memory: operands
+// first, then the 2N exact lane dots and scales (independent work), then the 2N fused
+// multiply-adds in block order.
+// 2^(e-128) for every e8m0 byte, built once per CTA: one shared-memory read replaces the
+// compare/select/shift sequence in the inner loop.
+__device__ __forceinline__ void mx_fill_scale_table(float *tbl, int tid, int nthreads) {
+    for (int e = tid; e < 256; e += nthreads) tbl[e] = brrr_e8m0_scale((uint32_t)e);
+}
+
+template <int N>
+__device__ __forceinline__ float mx_pairs(const unsigned char *unit, int rl, int j, const int2 *xpj, const float *xsc, const float *tbl, int pair, float acc) {
+    uint2 w[N];
+    uint32_t e2[N];
+    int2 x0[N], x1[N];
+    float xs0[N], xs1[N];
+#pragma unroll
+    for (int i = 0; i < N; i++) {
+        const unsigned char *u = unit + (size_t)i * MX_UNIT;
+        w[i] = *reinterpret_cast<const uint2 *>(u + rl * 32 + j * 8);
+        e2[i] = *reinterpret_cast<const unsigned short *>(u + MX_UNIT_EXPS + rl * 2);
+        x0[i] = xpj[(pair + i) * 8]; x1[i] = xpj[(pair + i) * 8 + 4];
+        xs0[i] = xsc[2 * (pair + i)]; xs1[i] = xsc[2 * (pair + i) + 1];
+    }
+    float t0[N], t1[N], s0[N], s1[N];
+#pragma unroll
+    for (int i = 0; i < N; i++) {
+        t0[i] = (float)brrr_mx_lane_dot(w[i].x, x0[i].x, x0[i].y);
+        t1[i] = (float)brrr_mx_lane_dot(w[i].y, x1[i].x, x1[i].y);
+        s0[i] = __fmul_rn(tbl[e2[i] & 0xFFu], xs0[i]);
+        s1[i] = __fmul_rn(tbl[e2[i] >> 8], xs1[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < N; i++) { acc = __fmaf_rn(t0[i], s0[i], acc); acc = __fmaf_rn(t1[i], s1[i], acc); }
+    return acc;
+}
+
+__device__ __forceinline__ float mx_chunk(const unsigned char *base, int cnt, int rl, int j, const int2 *xpj, const float *xsc, const float *tbl, int pair0, float acc) {
+    int i = 0;
+    for (; i + 3 <= cnt; i += 3) acc = mx_pairs<3>(base + (size_t)i * MX_UNIT, rl, j, xpj, xsc, tbl, pair0 + i, acc);
+    for (; i < cnt; i++) acc = mx_pairs<1>(base + (size_t)i * MX_UNIT, rl, j, xpj, xsc, tbl, pair0 + i, acc);
+    return acc;
+}
+
 // ---------------------------------------------------------------- plain matvec (stage-level / tests)
 // Reads units straight from global memory; optionally dumps the int32 block accumulators.
 template <bool DBG>
@@ -131,9 +174,9 @@ struct MxLaunchShape { int ch, stages; };
 static MxLaunchShape mx_shape(int np, int ns, size_t budget) {
     MxLaunchShape s;
     s.ch = np;
-    for (int c = 9; c <= 12; c++) if (np % c == 0) { s.ch = c; break; }
-    if (s.ch == np) for (int c = 8; c >= 5; c--) if (np % c == 0) { s.ch = c; break; }
-    if (s.ch == np && np > 12) s.ch = 8;
+    for (int c = 16; c >= 12; c--) if (np % c == 0) { s.ch = c; break; }
+    if (s.ch == np) for (int c = 17; c <= 24; c++) if (np % c == 0) { s.ch = c; break; }
+    if (s.ch == np && np > 24) s.ch = 16;
     int nchunks = (np + s.ch - 1) / s.ch;
     int maxs = (int)(budget / ((size_t)ns * s.ch * MX_UNIT));
     if (maxs < 2) maxs = 2;
@@ -179,15 +222,24 @@ __global__ void __launch_bounds__(256) gate_up_kernel(GateUpArgs a) {
     uint32_t *err = a.state ? &a.state->err : nullptr;
     Waiter waiter(err);
     const int ei = blockIdx.y, blk32 = blockIdx.x;
-
+    BRRR_STAMP(a.state, 96);
+    __shared__ float tbl[256];
+    mx_fill_scale_table(tbl, tid, 256);
     if (tid == 0) {
         for (int s = 0; s < a.stages; s++) mbar_init(&r.bars[s], 1);
         mbar_fence_init();
     }
     // The activation comes from two kernels back (complete by the launch protocol), so it is
     // normalised and quantised here, before waiting for the router that runs alongside.
-    if (a.x_f32) block_norm_quant<NQ_MX>(a.x_f32, a.norm_w, a.eps, a.d, xf, xp, xsc, &inv_sh, tid, 256);
+    if (a.x_f32) {
+        float4 wreg[3];
+        norm_prefetch<3>(a.norm_w, a.d, wreg, tid, 256);
+        block_norm_quant<NQ_MX, 3>(a.x_f32, a.norm_w, wreg, a.eps, a.d, xf, xp, xsc, &inv_sh, tid, 256);
+    }
+    BRRR_STAMP(a.state, 97);
     pdl_wait();          // router done: top[] valid
+    BRRR_STAMP(a.state, 98);
+    BRRR_GT_GO(a.state, 126);
     pdl_trigger();
     waiter.poison_if_failed();
     if (!a.x_f32) mx_stage_x(a.xq, a.xs, nb, xp, xsc, tid, 256);
@@ -203,24 +255,28 @@ __global__ void __launch_bounds__(256) gate_up_kernel(GateUpArgs a) {
     }
     __syncthreads();
 
+    BRRR_STAMP(a.state, 99);
     const int sidx = tid >> 6, rl = (tid & 63) >> 2, j = tid & 3;
+    const int isup = sidx >> 1, r32 = (sidx & 1) * 16 + rl;
+    // the bias is fetched while the weight stream is in flight
+    const float bias_pre = j == 0 ? (isup ? a.up_b : a.gate_b)[(size_t)e * a.d + blk32 * 32 + r32] : 0.0f;
     float acc = 0.0f;
     for (int c = 0; c < nchunks; c++) {
+        if (c < 12) BRRR_STAMP(a.state, 104 + c);
         const int cnt = min(a.ch, np - c * a.ch), slot = c % a.stages;
         waiter.wait(&r.bars[slot], (uint32_t)(c / a.stages) & 1u);
+        if (c < 12) BRRR_STAMP(a.state, 116 + c);
         const unsigned char *base = r.ring + r.stage_bytes * slot + r.stream_bytes * sidx;
-#pragma unroll 3
-        for (int i = 0; i < cnt; i++) acc = mx_pair_step<false>(base + (size_t)i * MX_UNIT, rl, j, xp + j, xsc, c * a.ch + i, acc, nullptr);
+        acc = mx_chunk(base, cnt, rl, j, xp + j, xsc, tbl, c * a.ch, acc);
         if (c + a.stages < nchunks) {
             __syncthreads();
             if (tid == 0) { fence_proxy_async(); r.issue(c + a.stages, src); }
         }
     }
+    BRRR_STAMP(a.state, 100);
     acc = brrr_hsum4(acc);
-    const int isup = sidx >> 1, r32 = (sidx & 1) * 16 + rl;
     if (j == 0) {
-        const float *bias = isup ? a.up_b : a.gate_b;
-        float v = __fadd_rn(acc, bias[(size_t)e * a.d + blk32 * 32 + r32]);
+        float v = __fadd_rn(acc, bias_pre);
         gu_s[isup][r32] = v;
         if (a.gu) a.gu[(size_t)ei * 2 * a.d + (size_t)isup * a.d + blk32 * 32 + r32] = v;
     }
@@ -229,6 +285,8 @@ __global__ void __launch_bounds__(256) gate_up_kernel(GateUpArgs a) {
         float h = swiglu_oai(gu_s[0][lane], gu_s[1][lane]);
         warp_quant_block(h, lane, a.hq + (size_t)ei * a.d + blk32 * 32, a.hs + ei * nb + blk32);
     }
+    BRRR_STAMP(a.state, 101);
+    BRRR_GT_END(a.state, 127);
 }
 
 cudaError_t launch_gate_up(MxDev gate, MxDev up, const float *gate_b, const float *up_b, const int32_t *top, int topk, int d,
@@ -238,7 +296,10 @@ cudaError_t launch_gate_up(MxDev gate, MxDev up, const float *gate_b, const floa
     a.gate = gate; a.up = up; a.gate_b = gate_b; a.up_b = up_b; a.top = top; a.d = d;
     a.x_f32 = x_f32; a.norm_w = norm_w; a.eps = eps; a.xq = xq; a.xs = xs; a.hq = hq; a.hs = hs; a.gu = gu; a.state = state;
     const int nb = gate.blocks, np = nb / 2;
-    MxLaunchShape s = mx_shape(np, 4, 60 * 1024);
+    // Every CTA of the grid must be resident at once (3 per SM at the 20b shape), so the ring is
+    // kept near 52 KB: chunks of 8 pairs (4 streams x 4.3 KB), 3 stages.
+    MxLaunchShape s = mx_shape(np, 4, 56 * 1024);
+    if (np > 8) { s.ch = 8; int nch = (np + 7) / 8; s.stages = nch < 3 ? nch : 3; }
     a.ch = s.ch; a.stages = s.stages;
     size_t smem = (size_t)4 * a.ch * MX_UNIT * a.stages + (size_t)nb * 4 * 8 + (size_t)nb * 4 + (x_f32 ? (size_t)d * 4 : 0) + 8 + (size_t)a.stages * 8;
     static bool configured = false;
@@ -282,7 +343,9 @@ __global__ void __launch_bounds__(512) down_combine_kernel(DownArgs a) {
     uint32_t *err = a.state ? &a.state->err : nullptr;
     Waiter waiter(err);
     const int nchunks = (np + a.ch - 1) / a.ch;
-
+    BRRR_STAMP(a.state, 128);
+    __shared__ float tbl[256];
+    mx_fill_scale_table(tbl, tid, nthreads);
     if (tid == 0) {
         for (int s = 0; s < a.stages; s++) mbar_init(&r.bars[s], 1);
         mbar_fence_init();
@@ -291,7 +354,19 @@ __global__ void __launch_bounds__(512) down_combine_kernel(DownArgs a) {
         for (int s = 0; s < a.topk; s++) src[s] = a.down.data + mx_unit_off(((a.top[s] * a.d) >> 4) + blockIdx.x, 0, np);
         for (int c = 0; c < min(a.stages, nchunks); c++) r.issue(c, src);
     }
+    // operands of the final fold: routing is two kernels old, the residual three
+    float x_pre = 0.0f, b_pre[8], w_pre[8];
+    if (tid < 16) {
+        const int rr = blockIdx.x * 16 + tid;
+        x_pre = a.x[rr];
+#pragma unroll
+        for (int k = 0; k < 8; k++)
+            if (k < a.topk) { b_pre[k] = a.down_b[(size_t)a.top[k] * a.d + rr]; w_pre[k] = a.wts[k]; }
+    }
+    BRRR_STAMP(a.state, 129);
     pdl_wait();          // gate/up done: hq, hs valid
+    BRRR_STAMP(a.state, 130);
+    BRRR_GT_GO(a.state, 158);
     pdl_trigger();
     waiter.poison_if_failed();
     const int ei = tid >> 6, t64 = tid & 63;
@@ -300,29 +375,35 @@ __global__ void __launch_bounds__(512) down_combine_kernel(DownArgs a) {
     mx_stage_x(a.hq + (size_t)ei * a.d, a.hs + (size_t)ei * nb, nb, xp, xsc, t64, 64);
     __syncthreads();
 
+    BRRR_STAMP(a.state, 131);
     const int rl = t64 >> 2, j = t64 & 3;
     float acc = 0.0f;
     for (int c = 0; c < nchunks; c++) {
+        if (c < 12) BRRR_STAMP(a.state, 136 + c);
         const int cnt = min(a.ch, np - c * a.ch), slot = c % a.stages;
         waiter.wait(&r.bars[slot], (uint32_t)(c / a.stages) & 1u);
+        if (c < 12) BRRR_STAMP(a.state, 148 + c);
         const unsigned char *base = r.ring + r.stage_bytes * slot + r.stream_bytes * ei;
-#pragma unroll 3
-        for (int i = 0; i < cnt; i++) acc = mx_pair_step<false>(base + (size_t)i * MX_UNIT, rl, j, xp + j, xsc, c * a.ch + i, acc, nullptr);
+        acc = mx_chunk(base, cnt, rl, j, xp + j, xsc, tbl, c * a.ch, acc);
         if (c + a.stages < nchunks) {
             __syncthreads();
             if (tid == 0) { fence_proxy_async(); r.issue(c + a.stages, src); }
         }
     }
+    BRRR_STAMP(a.state, 132);
     acc = brrr_hsum4(acc);
     if (j == 0) part[ei * 16 + rl] = acc;
     __syncthreads();
     if (tid < 16) {
         int rr = blockIdx.x * 16 + tid;
-        float s = a.x[rr];
-        for (int k = 0; k < a.topk; k++)
-            s = __fadd_rn(s, __fmul_rn(a.wts[k], __fadd_rn(part[k * 16 + tid], a.down_b[(size_t)a.top[k] * a.d + rr])));
+        float s = x_pre;
+#pragma unroll
+        for (int k = 0; k < 8; k++)
+            if (k < a.topk) s = __fadd_rn(s, __fmul_rn(w_pre[k], __fadd_rn(part[k * 16 + tid], b_pre[k])));
         a.x[rr] = s;
     }
+    BRRR_STAMP(a.state, 133);
+    BRRR_GT_END(a.state, 159);
     (void)nthreads;
 }
 

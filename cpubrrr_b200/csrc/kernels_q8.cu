@@ -61,6 +61,31 @@ void launch_q8_export(Q8Dev m, int8_t *q, float *s, cudaStream_t st) {
     q8_export_kernel<<<(unsigned)((warps + 7) / 8), 256, 0, st>>>(m, q, s);
 }
 
+// N consecutive block pairs of one chain, from units resident in shared memory: all operands are
+// fetched and all integer dots formed first, then the N fused multiply-adds run in order.
+template <int N>
+__device__ __forceinline__ float q8_pairs(const unsigned char *unit, int rl, int c8, int p, const int2 *xp8, const float *xsc2, float acc) {
+    int2 w[N], xv[N];
+    float s[N], xs[N];
+#pragma unroll
+    for (int i = 0; i < N; i++) {
+        const unsigned char *u = unit + (size_t)i * Q8_UNIT;
+        w[i] = *reinterpret_cast<const int2 *>(u + rl * 64 + c8 * 8);
+        s[i] = *reinterpret_cast<const float *>(u + Q8_UNIT_SCALES + rl * 8 + p * 4);
+        xv[i] = xp8[i * 8];
+        xs[i] = xsc2[i * 2];
+    }
+    float tf[N], sv[N];
+#pragma unroll
+    for (int i = 0; i < N; i++) {
+        tf[i] = (float)__dp4a(w[i].y, xv[i].y, __dp4a(w[i].x, xv[i].x, 0));
+        sv[i] = __fmul_rn(s[i], xs[i]);
+    }
+#pragma unroll
+    for (int i = 0; i < N; i++) acc = __fmaf_rn(tf[i], sv[i], acc);
+    return acc;
+}
+
 // ---------------------------------------------------------------- streaming GEMV
 struct Q8Args {
     Q8Dev m;
@@ -109,6 +134,9 @@ __global__ void __launch_bounds__(Q8_THREADS) q8_stream_kernel(Q8Args a) {
         bulk_g2s(ring + stage_bytes * slot, a.m.data + q8_unit_off(u, k * a.ch, np), (uint32_t)cnt * Q8_UNIT, &bars[slot]);
     };
 
+    const int sb = NORM ? 32 : 64;      // timeline slots of this kernel flavour
+    (void)sb;
+    BRRR_STAMP(a.state, sb);
     if (tid == 0) {
         for (int s = 0; s < a.stages; s++) mbar_init(&bars[s], 1);
         mbar_fence_init();
@@ -116,14 +144,27 @@ __global__ void __launch_bounds__(Q8_THREADS) q8_stream_kernel(Q8Args a) {
     __syncthreads();
     if (tid == 0)
         for (int c = 0; c < min(a.stages, nchunks); c++) issue(c);
-
+    // static operands (norm weights, bias) and the residual written several kernels back are
+    // fetched now, while the predecessor is still running
+    const int rl = tid >> 3, c8 = tid & 7, p = c8 >> 2;
+    float4 wreg[6];
+    if (NORM) norm_prefetch<6>(a.norm_w, a.m.cols, wreg, tid, Q8_THREADS);
+    float bias_pre = 0.0f, resid_pre = 0.0f;
+    const bool one_row = (u1 - u0) == 1;
+    if (one_row && c8 == 0 && u0 * 16 + rl < a.m.rows) {
+        if (EPI == Q8_EPI_BIAS || EPI == Q8_EPI_RESID_BIAS) bias_pre = a.bias[u0 * 16 + rl];
+        if (EPI == Q8_EPI_RESID_BIAS) resid_pre = a.y[u0 * 16 + rl];
+    }
+    BRRR_STAMP(a.state, sb + 1);
     pdl_wait();          // predecessor's outputs (activation, residual) are now visible
+    BRRR_STAMP(a.state, sb + 2);
+    BRRR_GT_GO(a.state, sb + 30);
     pdl_trigger();
     waiter.poison_if_failed();
 
     // ---- activation: normalise + quantise, or stage the given Q8 vector
     if (NORM) {
-        block_norm_quant<NQ_Q8>(a.x_f32, a.norm_w, a.eps, a.m.cols, xf, xp, xsc, &inv_sh, tid, Q8_THREADS);
+        block_norm_quant<NQ_Q8, 6>(a.x_f32, a.norm_w, wreg, a.eps, a.m.cols, xf, xp, xsc, &inv_sh, tid, Q8_THREADS);
     } else {
         for (int idx = tid; idx < nb * 4; idx += Q8_THREADS) {
             int b = idx >> 2, j = idx & 3;
@@ -134,34 +175,38 @@ __global__ void __launch_bounds__(Q8_THREADS) q8_stream_kernel(Q8Args a) {
     }
     __syncthreads();
 
-    const int rl = tid >> 3, c8 = tid & 7, p = c8 >> 2;
+    BRRR_STAMP(a.state, sb + 3);
     float acc = 0.0f;
     unsigned long long best = 0ull;
     for (int c = 0; c < nchunks; c++) {
+        if (c < 12) BRRR_STAMP(a.state, sb + 8 + c);
         const int u = u0 + c / cpr, k = c % cpr;
         const int cnt = min(a.ch, np - k * a.ch);
         const int slot = c % a.stages;
         waiter.wait(&bars[slot], (uint32_t)(c / a.stages) & 1u);
+        if (c < 12) BRRR_STAMP(a.state, sb + 20 + c);
         const unsigned char *base = ring + stage_bytes * slot;
         const int pair0 = k * a.ch;
-#pragma unroll 4
-        for (int i = 0; i < cnt; i++) {
-            const unsigned char *unit = base + (size_t)i * Q8_UNIT;
-            int2 w = *reinterpret_cast<const int2 *>(unit + rl * 64 + c8 * 8);
-            float s = *reinterpret_cast<const float *>(unit + Q8_UNIT_SCALES + rl * 8 + p * 4);
-            int2 xv = xp[(pair0 + i) * 8 + c8];
-            int t = __dp4a(w.y, xv.y, __dp4a(w.x, xv.x, 0));
-            acc = __fmaf_rn((float)t, __fmul_rn(s, xsc[(pair0 + i) * 2 + p]), acc);
+        {
+            const int2 *xp8 = xp + (size_t)pair0 * 8 + c8;
+            const float *xsc2 = xsc + pair0 * 2 + p;
+            int i = 0;
+            for (; i + 8 <= cnt; i += 8) acc = q8_pairs<8>(base + (size_t)i * Q8_UNIT, rl, c8, p, xp8 + i * 8, xsc2 + i * 2, acc);
+            if (i + 4 <= cnt) { acc = q8_pairs<4>(base + (size_t)i * Q8_UNIT, rl, c8, p, xp8 + i * 8, xsc2 + i * 2, acc); i += 4; }
+            if (i + 2 <= cnt) { acc = q8_pairs<2>(base + (size_t)i * Q8_UNIT, rl, c8, p, xp8 + i * 8, xsc2 + i * 2, acc); i += 2; }
+            if (i < cnt) acc = q8_pairs<1>(base + (size_t)i * Q8_UNIT, rl, c8, p, xp8 + i * 8, xsc2 + i * 2, acc);
         }
         if (k == cpr - 1) {
+            BRRR_STAMP(a.state, sb + 4);
             // row finished: acc_even + acc_odd per lane, then (l0+l1)+(l2+l3)
             float r = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 4));
             r = brrr_hsum4(r);
             const int row = u * 16 + rl;
             if (c8 == 0 && row < a.m.rows) {
                 if (EPI == Q8_EPI_PLAIN) a.y[row] = r;
-                else if (EPI == Q8_EPI_BIAS) a.y[row] = __fadd_rn(r, a.bias[row]);
-                else if (EPI == Q8_EPI_RESID_BIAS) a.y[row] = __fadd_rn(a.y[row], __fadd_rn(r, a.bias[row]));   // x += dot + bias
+                else if (EPI == Q8_EPI_BIAS) a.y[row] = __fadd_rn(r, one_row ? bias_pre : a.bias[row]);
+                else if (EPI == Q8_EPI_RESID_BIAS)                                                               // x += dot + bias
+                    a.y[row] = __fadd_rn(one_row ? resid_pre : a.y[row], __fadd_rn(r, one_row ? bias_pre : a.bias[row]));
                 else {
                     a.y[row] = r;
                     unsigned long long key = ((unsigned long long)float_orderable(r) << 32) | (0xFFFFFFFFu - (uint32_t)row);
@@ -175,6 +220,8 @@ __global__ void __launch_bounds__(Q8_THREADS) q8_stream_kernel(Q8Args a) {
             if (tid == 0) { fence_proxy_async(); issue(c + a.stages); }
         }
     }
+    BRRR_STAMP(a.state, sb + 5);
+    BRRR_GT_END(a.state, sb + 31);
     if (EPI == Q8_EPI_HEAD) {
         // running argmax: first strict maximum = lowest index among equal values
 #pragma unroll
@@ -198,7 +245,7 @@ __global__ void __launch_bounds__(Q8_THREADS) q8_stream_kernel(Q8Args a) {
 template <int EPI>
 __global__ void __launch_bounds__(256) q8_direct_kernel(Q8Dev m, const int8_t *__restrict__ xq, const float *__restrict__ xs,
                                                         const float *__restrict__ bias, float *__restrict__ y, DevState *state) {
-    extern __shared__ __align__(16) unsigned char smraw[];
+    extern __shared__ __align__(128) unsigned char smraw[];
     const int nb = m.cols / 32, np = m.cols / 64;
     int2 *xp = reinterpret_cast<int2 *>(smraw);
     float *xsc = reinterpret_cast<float *>(smraw + (size_t)nb * 4 * sizeof(int2));
@@ -269,11 +316,12 @@ cudaError_t launch_q8_direct(Q8Dev m, const int8_t *xq, const float *xs, const f
     return cudaErrorInvalidValue;
 }
 
-// chunk size: a divisor of np between 6 and 12 pairs when there is one (no ragged tail), else 8
+// chunk size: bulk copies of 16-23 KB move fastest and every chunk costs one barrier wait, so
+// prefer a divisor of np between 14 and 20 pairs (no ragged tail), else 16
 static int pick_chunk(int np) {
-    for (int c = 9; c <= 12; c++) if (np % c == 0) return c;
-    for (int c = 8; c >= 6; c--) if (np % c == 0) return c;
-    return np < 8 ? np : 8;
+    for (int c = 16; c >= 14; c--) if (np % c == 0) return c;
+    for (int c = 17; c <= 20; c++) if (np % c == 0) return c;
+    return np < 16 ? np : 16;
 }
 
 static size_t q8_smem(const Q8Args &a, bool norm) {

@@ -14,7 +14,7 @@
 
 namespace brrr {
 
-constexpr int RT_STAGES = 8;
+constexpr int RT_STAGES = 5;
 constexpr int RT_THREADS = 256;
 
 // ---------------------------------------------------------------- pack: W[ne][d] -> tiled layout
@@ -34,6 +34,27 @@ __global__ void router_pack_kernel(const float *__restrict__ W, int ne, int d, f
 
 void launch_router_pack(const float *W, int ne, int d, float *out, cudaStream_t st) {
     router_pack_kernel<<<148, 256, 0, st>>>(W, ne, d, out);
+}
+
+// acc += w[j] * x[j] for j = 0..LEN-1, strictly in order, product and sum rounded separately.
+// Products are formed 32 at a time from 128-bit shared-memory reads so that only the adds sit
+// on the dependent chain.
+template <int LEN>
+__device__ __forceinline__ float chain_span(const float *__restrict__ w, const float *__restrict__ x, float acc) {
+#pragma unroll
+    for (int j0 = 0; j0 < LEN; j0 += 32) {
+        float p[32];
+#pragma unroll
+        for (int k = 0; k < 8; k++) {
+            float4 a = *reinterpret_cast<const float4 *>(w + j0 + 4 * k);
+            float4 b = *reinterpret_cast<const float4 *>(x + j0 + 4 * k);
+            p[4 * k] = __fmul_rn(a.x, b.x); p[4 * k + 1] = __fmul_rn(a.y, b.y);
+            p[4 * k + 2] = __fmul_rn(a.z, b.z); p[4 * k + 3] = __fmul_rn(a.w, b.w);
+        }
+#pragma unroll
+        for (int k = 0; k < 32; k++) acc = __fadd_rn(acc, p[k]);
+    }
+    return acc;
 }
 
 struct RouterArgs {
@@ -92,7 +113,9 @@ __global__ void __launch_bounds__(RT_THREADS) ffn_in_kernel(RouterArgs a) {
     float *tiles = reinterpret_cast<float *>(smraw);                                        // [RT_STAGES][32][RT_STRIDE]
     float *xn = reinterpret_cast<float *>(smraw + (size_t)RT_TILE_FLOATS * 4 * RT_STAGES);   // d floats
     float *lg = xn + a.d;                                                                   // ne floats (top-k staging)
-    uint64_t *bars = reinterpret_cast<uint64_t *>(lg + ((a.ne + 1) & ~1));
+    float *wn = lg + ((a.ne + 1) & ~1);                                        // d floats: norm weights
+    uint64_t *bars = reinterpret_cast<uint64_t *>(wn + a.d);                   // [RT_STAGES] tile landed
+    uint64_t *empty = bars + RT_STAGES;                                        // [RT_STAGES] tile consumed
     __shared__ float inv_sh;
     __shared__ int last_sh;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31, d = a.d;
@@ -110,45 +133,48 @@ __global__ void __launch_bounds__(RT_THREADS) ffn_in_kernel(RouterArgs a) {
     };
     BRRR_STAMP(a.state, 0);
     if (tid == 0) {
-        for (int s = 0; s < RT_STAGES; s++) mbar_init(&bars[s], 1);
+        for (int s = 0; s < RT_STAGES; s++) { mbar_init(&bars[s], 1); mbar_init(&empty[s], 1); }
         mbar_fence_init();
         for (int t = 0; t < min(RT_STAGES, ntiles); t++) issue(t);
     }
+    if (a.norm_w) stage_vec4(a.norm_w, wn, d, tid, RT_THREADS);             // static: fetched before the wait
+    const float bias_pre = (warp == 0 && lane < nloc && a.b) ? a.b[e0 + lane] : 0.0f;
     BRRR_STAMP(a.state, 1);
     pdl_wait();          // residual stream complete
     BRRR_STAMP(a.state, 2);
+    BRRR_GT_GO(a.state, 30);
     pdl_trigger();
     waiter.poison_if_failed();
-    for (int i = tid; i < d; i += RT_THREADS) xn[i] = a.x_in[i];
+    for (int i = tid; i < d / 4; i += RT_THREADS) reinterpret_cast<float4 *>(xn)[i] = reinterpret_cast<const float4 *>(a.x_in)[i];
     __syncthreads();
     if (a.norm_w) {
         float inv = block_rms_inv(xn, d, a.eps, &inv_sh);
-        for (int i = tid; i < d; i += RT_THREADS) xn[i] = __fmul_rn(__fmul_rn(xn[i], inv), a.norm_w[i]);
+        for (int i = tid; i < d; i += RT_THREADS) xn[i] = __fmul_rn(__fmul_rn(xn[i], inv), wn[i]);
         __syncthreads();
     }
 
     BRRR_STAMP(a.state, 3);
+    if (warp == 1 && lane == 0) {
+        // refill thread: as soon as the chain warp releases a slot, the tile RT_STAGES ahead goes in
+        for (int t = RT_STAGES; t < ntiles; t++) {
+            waiter.wait(&empty[t % RT_STAGES], (uint32_t)(t / RT_STAGES - 1) & 1u);
+            fence_proxy_async();
+            issue(t);
+        }
+    }
     if (warp == 0) {
-        float acc = (lane < nloc && a.b) ? a.b[e0 + lane] : 0.0f;
+        float acc = bias_pre;
         for (int t = 0; t < ntiles; t++) {
             if (t < 12) BRRR_STAMP(a.state, 8 + t);
             const int slot = t % RT_STAGES, j0 = t * RT_TJ, len = min(RT_TJ, d - j0);
             waiter.wait(&bars[slot], (uint32_t)(t / RT_STAGES) & 1u);
             const float *row = tiles + (size_t)slot * RT_TILE_FLOATS + lane * RT_STRIDE;
             const float *xr = xn + j0;
-#pragma unroll 8
-            for (int jj = 0; jj < len; jj += 4) {
-                float4 w = *reinterpret_cast<const float4 *>(row + jj);
-                float4 x = *reinterpret_cast<const float4 *>(xr + jj);
-                acc = __fadd_rn(acc, __fmul_rn(w.x, x.x));
-                acc = __fadd_rn(acc, __fmul_rn(w.y, x.y));
-                acc = __fadd_rn(acc, __fmul_rn(w.z, x.z));
-                acc = __fadd_rn(acc, __fmul_rn(w.w, x.w));
-            }
-            if (t + RT_STAGES < ntiles) {
-                __syncwarp();                  // all lanes are done reading this slot
-                if (lane == 0) { fence_proxy_async(); issue(t + RT_STAGES); }
-            }
+            if (len == RT_TJ) acc = chain_span<RT_TJ>(row, xr, acc);
+            else
+                for (int jj = 0; jj < len; jj += 32) acc = chain_span<32>(row + jj, xr + jj, acc);   // d % 64 == 0
+            __syncwarp();                      // all lanes are done reading this slot
+            if (lane == 0 && t + RT_STAGES < ntiles) mbar_arrive(&empty[slot]);
         }
         if (lane < nloc) {
             if (gridDim.x == 1) lg[lane] = acc;
@@ -160,6 +186,7 @@ __global__ void __launch_bounds__(RT_THREADS) ffn_in_kernel(RouterArgs a) {
             warp_topk(a, lg, lane);
         }
         BRRR_STAMP(a.state, 5);
+        BRRR_GT_END(a.state, 31);
     }
     if (gridDim.x == 1) return;
 
@@ -184,7 +211,7 @@ size_t router_packed_floats(int ne, int d) { return (size_t)((ne + 31) / 32) * (
 cudaError_t launch_ffn_in(const float *x_in, const float *norm_w, float eps, int d, const float *Wt, const float *b, int ne, int topk,
                           float *logits, int32_t *top, float *wts, unsigned int *counter, DevState *state, bool pdl, cudaStream_t st) {
     RouterArgs a{x_in, norm_w, eps, d, Wt, b, ne, topk, logits, top, wts, counter, state};
-    size_t smem = (size_t)RT_TILE_FLOATS * 4 * RT_STAGES + (size_t)d * 4 + (size_t)((ne + 1) & ~1) * 4 + RT_STAGES * 8;
+    size_t smem = (size_t)RT_TILE_FLOATS * 4 * RT_STAGES + (size_t)d * 8 + (size_t)((ne + 1) & ~1) * 4 + RT_STAGES * 16;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(ffn_in_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);

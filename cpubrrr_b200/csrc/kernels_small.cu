@@ -28,19 +28,23 @@ void launch_quant_q8(const float *x, int n, int8_t *q, float *s, cudaStream_t st
 // (x * inv) * w with two separately rounded multiplies.
 __global__ void __launch_bounds__(512) rmsnorm_quant_kernel(const float *__restrict__ x, const float *__restrict__ w, float eps, int n,
                                                             float *__restrict__ xn, int8_t *__restrict__ q, float *__restrict__ s) {
-    extern __shared__ __align__(16) float sm[];
+    extern __shared__ __align__(16) float sm[];      // n floats of x, then n floats of norm weights
     __shared__ float inv_sh;
+    float *wn = sm + n;
+    stage_vec4(w, wn, n, threadIdx.x, blockDim.x);   // static: fetched before the wait
+    float4 wreg[4];
+    norm_prefetch<4>(w, n, wreg, threadIdx.x, blockDim.x);
     pdl_wait();
     pdl_trigger();
-    block_norm_quant<NQ_NATURAL>(x, w, eps, n, sm, reinterpret_cast<int2 *>(q), s, &inv_sh, threadIdx.x, blockDim.x);
+    block_norm_quant<NQ_NATURAL, 4>(x, w, wreg, eps, n, sm, reinterpret_cast<int2 *>(q), s, &inv_sh, threadIdx.x, blockDim.x);
     if (xn) {
         float inv = inv_sh;
-        for (int i = threadIdx.x; i < n; i += blockDim.x) xn[i] = __fmul_rn(__fmul_rn(sm[i], inv), w[i]);
+        for (int i = threadIdx.x; i < n; i += blockDim.x) xn[i] = __fmul_rn(__fmul_rn(sm[i], inv), wn[i]);
     }
 }
 
 cudaError_t launch_rmsnorm_quant(const float *x, const float *w, float eps, int n, float *xn, int8_t *q, float *s, bool pdl, cudaStream_t st) {
-    return launch_k(rmsnorm_quant_kernel, dim3(1), dim3(512), (size_t)n * sizeof(float), st, pdl, x, w, eps, n, xn, q, s);
+    return launch_k(rmsnorm_quant_kernel, dim3(1), dim3(512), (size_t)n * 2 * sizeof(float), st, pdl, x, w, eps, n, xn, q, s);
 }
 
 // ---------------------------------------------------------------- embedding gather

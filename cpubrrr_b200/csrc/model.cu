@@ -213,7 +213,7 @@ void rope_table_host(const brrr_cfg &c, float *tab) {
 }
 
 int check_cfg(const brrr_cfg &c) {
-    if (c.n_embd <= 0 || c.n_embd % 64 || c.n_embd > 8192) return BRRR_ERR_ARG;
+    if (c.n_embd <= 0 || c.n_embd % 64 || c.n_embd > 4096) return BRRR_ERR_ARG;
     if (c.n_ff_exp != c.n_embd) return BRRR_ERR_ARG;                     // engine_gpt2.rs:73
     if (c.head_dim != 64) return BRRR_ERR_ARG;                           // engine_gpt2.rs:74
     if (c.n_head <= 0 || c.n_head_kv <= 0 || c.n_head % c.n_head_kv) return BRRR_ERR_ARG;
@@ -662,10 +662,10 @@ extern "C" int brrr_stage_time(brrr_model *m, int stage, uint32_t pos, int reps,
 }
 
 // Debug tap: the in-kernel clock stamps of the last step (all zero unless built with BRRR_TIMELINE).
-extern "C" int brrr_debug_stamps(brrr_model *m, long long *out32) {
-    if (!m || !out32) return BRRR_ERR_ARG;
+extern "C" int brrr_debug_stamps(brrr_model *m, long long *out256) {
+    if (!m || !out256) return BRRR_ERR_ARG;
     CU(cudaSetDevice(m->device));
-    CU(cudaMemcpyAsync(out32, m->st->stamps, 32 * sizeof(long long), cudaMemcpyDeviceToHost, m->stream));
+    CU(cudaMemcpyAsync(out256, m->st->stamps, 256 * sizeof(long long), cudaMemcpyDeviceToHost, m->stream));
     CU(cudaStreamSynchronize(m->stream));
     return BRRR_OK;
 }

@@ -114,9 +114,9 @@ int brrr_stage_count(void);
 const char *brrr_stage_name(int stage);
 int brrr_stage_time(brrr_model *m, int stage, uint32_t pos, int reps, float *ms_per_launch, uint64_t *bytes_per_launch, int *launches_per_step);
 
-/* Debug tap: 32 SM-clock stamps recorded inside the kernels of the last step; all zero unless the
+/* Debug tap: 256 SM-clock stamps recorded inside the kernels of the last step; all zero unless the
  * library was built with -DBRRR_TIMELINE.  No counterpart in the reference. */
-int brrr_debug_stamps(brrr_model *m, long long *out32);
+int brrr_debug_stamps(brrr_model *m, long long *out256);
 
 /* ---------------------------------------------------------------- stage-level entry points
  * Device pointers in, device pointers out.  They launch the same kernels the forward pass uses. */
