@@ -18,7 +18,7 @@ OBJ = os.path.join(HERE, "_obj")
 LIB = os.path.join(HERE, "libbrrr.so")
 
 SOURCES = ["kernels_small.cu", "kernels_q8.cu", "kernels_mx.cu", "kernels_router.cu", "kernels_attn.cu",
-           "model.cu", "capi_stage.cu"]
+           "model.cu", "capi_stage.cu", "capi_noalloc.cu"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",

@@ -156,6 +156,18 @@ int brrr_mx_matvec(const brrr_mxmat *w, int row0, int nrows, const int8_t *d_xq,
 int brrr_router_topk(const float *d_w, const float *d_b, const float *d_xn, int ne, int d, int topk,
                      float *d_logits, int32_t *d_top, float *d_wts, void *stream);
 
+/* The same router, for callers that cannot allocate device memory: a host that has given all of
+ * its free HBM to its own pools, or a request path that must stay clear of cudaMalloc / cudaFree
+ * because they take the driver's allocation lock and cudaFree synchronises the device.  Nothing
+ * is allocated: the re-tiled matrix and the CTA arrival counter live in a fixed array inside the
+ * library image (about 2.1 MB, held by every GPU that loads the library until the process
+ * exits).  Limits: ne <= 128 and d <= 4096, otherwise BRRR_ERR_RANGE.  The first call on each
+ * device looks up the array's device address; make that call before any stream capture.  All
+ * calls share the one array, so two calls whose work overlaps on the GPU (different streams)
+ * race; calls on one stream are safe.  It has no counterpart in the reference. */
+int brrr_router_topk_noalloc(const float *d_w, const float *d_b, const float *d_xn, int ne, int d, int topk,
+                             float *d_logits, int32_t *d_top, float *d_wts, void *stream);
+
 /* Clamped SwiGLU on gu[topk][2d] (gate | up) then the per-32 quantiser.  Replaces
  * src/bin/engine_gpt2.rs:886-907. */
 int brrr_swiglu_quant(const float *d_gu, int topk, int d, int8_t *d_hq, float *d_hs, void *stream);
