@@ -37,6 +37,7 @@ SIGNATURES = {
     "brrr_forward_trace": (_I, [_P, C.c_uint32, C.c_uint32, _P]),
     "brrr_model_stream": (_P, [_P]),
     "brrr_model_launches_per_step": (_I, [_P, _I]),
+    "brrr_model_spec_redos": (C.c_uint64, [_P]),
     "brrr_model_bytes_per_step": (C.c_uint64, [_P, C.c_uint32]),
     "brrr_stage_count": (_I, []),
     "brrr_stage_name": (C.c_char_p, [_I]),

@@ -4,6 +4,12 @@
 
 namespace brrr {
 
+// order-preserving map float -> uint32 (larger float = larger uint)
+__device__ __forceinline__ uint32_t float_orderable(float v) {
+    uint32_t b = __float_as_uint(v);
+    return b ^ ((b >> 31) ? 0xFFFFFFFFu : 0x80000000u);
+}
+
 __device__ __forceinline__ float warp_max(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
@@ -125,6 +131,28 @@ __device__ __forceinline__ void block_norm_quant(const float *__restrict__ x, co
     }
 }
 
+// The k largest of est[0..ne) by (value, lower index first): sel[r] gets the expert of rank r.
+// Every thread ranks the experts it owns against all others in shared memory (no shuffles, one
+// global round trip).  Used identically by every kernel that needs the speculative expert set
+// (the set comes from an order-free router estimate; correctness never depends on it).
+// sabotage: test hook that replaces the last pick on every third position.
+// Block-wide; ends with sel[] written but not yet synchronised.  lg: ne floats of scratch.
+__device__ __forceinline__ void block_spec_select(const float *est, int ne, int topk, const uint32_t *pos_ptr, int sabotage,
+                                                  float *lg, int *sel, int tid, int nthreads) {
+    const uint32_t pos = (sabotage && pos_ptr) ? *pos_ptr : 0u;
+    for (int e = tid; e < ne; e += nthreads) lg[e] = __ldcg(est + e);
+    __syncthreads();
+    for (int e = tid; e < ne; e += nthreads) {
+        const float v = lg[e];
+        int rank = 0;
+        for (int o = 0; o < ne; o++) {
+            const float u = lg[o];
+            rank += (u > v || (u == v && o < e)) ? 1 : 0;
+        }
+        if (rank < topk) sel[rank] = (sabotage && rank == topk - 1 && pos % 3 == 0) ? (e + 1) % ne : e;
+    }
+}
+
 // gpt-oss clamped SwiGLU: xg = min(g, 7), yu = clamp(u, -7, 7), (xg / (1 + exp(-1.702 xg))) (yu + 1)
 __device__ __forceinline__ float swiglu_oai(float g, float u) {
     float xg = fminf(g, 7.0f);
@@ -133,10 +161,5 @@ __device__ __forceinline__ float swiglu_oai(float g, float u) {
     return __fmul_rn(__fdiv_rn(xg, den), __fadd_rn(yu, 1.0f));
 }
 
-// order-preserving map float -> uint32 (larger float = larger uint)
-__device__ __forceinline__ uint32_t float_orderable(float v) {
-    uint32_t b = __float_as_uint(v);
-    return b ^ ((b >> 31) ? 0xFFFFFFFFu : 0x80000000u);
-}
 
 }  // namespace brrr

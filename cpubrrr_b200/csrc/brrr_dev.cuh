@@ -134,7 +134,9 @@ struct DevState {
     uint32_t router_done;          // CTA arrival counter of the router kernel
     unsigned long long best;       // (orderable logit << 32) | ~index
     uint32_t err;                  // DEV_ERR_* (0 = none); set by a kernel whose bounded wait ran out
-    uint32_t pad;
+    uint32_t spec_fail_step;       // smallest n_out at which speculative routing missed (0xFFFFFFFF = never)
+    uint32_t hint_done;            // CTA arrival counter of the routing-hint kernel
+    uint32_t pad[3];
     uint32_t out[BRRR_MAXSEQ];
     long long stamps[256];          // optional in-kernel clock stamps (timeline builds only)
 };

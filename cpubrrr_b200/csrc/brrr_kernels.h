@@ -34,9 +34,13 @@ void launch_mx_gemv(MxDev m, int row0, int nrows, const int8_t *xq, const float 
 // (RMSNorm + quantise), x_f32 without norm_w (quantise only), or (xq, xs).  gu nullable.
 cudaError_t launch_gate_up(MxDev gate, MxDev up, const float *gate_b, const float *up_b, const int32_t *top, int topk, int d,
                            const float *x_f32, const float *norm_w, float eps, const int8_t *xq, const float *xs,
-                           int8_t *hq, float *hs, float *gu, DevState *state, bool pdl, cudaStream_t st);
-cudaError_t launch_down_combine(MxDev down, const float *down_b, const int32_t *top, const float *wts, int topk, int d,
-                                const int8_t *hq, const float *hs, float *x, DevState *state, bool pdl, cudaStream_t st);
+                           int8_t *hq, float *hs, float *gu, DevState *state, bool pdl, cudaStream_t st,
+                           const float *est = nullptr, int ne = 0, int sabotage = 0);
+// est (nullable): slot s of hq/hs belongs to the s-th largest of the router estimate est[0..ne)
+// rather than to top[s]; a step whose
+// exact experts are not all among them is flagged in state->spec_fail_step.
+cudaError_t launch_down_combine(MxDev down, const float *down_b, const int32_t *top, const float *wts, const float *est, int ne, int sabotage,
+                                int topk, int d, const int8_t *hq, const float *hs, float *x, DevState *state, bool pdl, cudaStream_t st);
 
 // ---- router (kernels_router.cu)
 // The router matrix is used in a tiled layout: [32-expert group][tile][32][RT_STRIDE] floats.
@@ -49,6 +53,12 @@ void launch_router_pack(const float *W, int ne, int d, float *out, cudaStream_t 
 // normalised vector otherwise.
 cudaError_t launch_ffn_in(const float *x_in, const float *norm_w, float eps, int d, const float *Wt, const float *b, int ne, int topk,
                           float *logits, int32_t *top, float *wts, unsigned int *counter, DevState *state, bool pdl, cudaStream_t st);
+
+// Order-free estimate of the router used only to start the gate/up weight stream early
+// (speculative routing): est[ne] receives the estimated logits, xq_out/xs_out the Q8 image of the
+// normalised vector (each CTA writes a share).
+cudaError_t launch_router_hint(const float *x_in, const float *norm_w, float eps, int d, const float *Wt, const float *b, int ne, int topk,
+                               float *est, int8_t *xq_out, float *xs_out, DevState *state, bool pdl, cudaStream_t st);
 
 // ---- attention (kernels_attn.cu)
 // KV cache layout [n_head_kv][BRRR_MAXSEQ][64].  pos is read from state when state != nullptr,

@@ -203,6 +203,8 @@ struct GateUpArgs {
     float *gu;               // nullable: [topk][2d] gate | up (bias added), for inspection
     DevState *state;
     int ch, stages;
+    const float *est;        // nullable: router estimate; the expert set is its top-k instead of top[]
+    int ne, topk, sabotage;
 };
 
 __global__ void __launch_bounds__(256) gate_up_kernel(GateUpArgs a) {
@@ -242,8 +244,27 @@ __global__ void __launch_bounds__(256) gate_up_kernel(GateUpArgs a) {
     BRRR_GT_GO(a.state, 126);
     pdl_trigger();
     waiter.poison_if_failed();
-    if (!a.x_f32) mx_stage_x(a.xq, a.xs, nb, xp, xsc, tid, 256);
-    const int e = a.top[ei];
+    __shared__ int sel[8];
+    __shared__ float lg[256];
+    // all global reads of this phase are issued together: the activation words go to registers
+    // first, the expert set is ranked, then the activation is staged
+    uint32_t xlo[2], xhi[2];
+    if (!a.x_f32) {
+#pragma unroll
+        for (int k = 0; k < 2; k++) {
+            const int idx = tid + k * 256;
+            if (idx < nb * 4) {
+                const uint32_t *xw = reinterpret_cast<const uint32_t *>(a.xq + (idx >> 2) * 32);
+                xlo[k] = xw[idx & 3]; xhi[k] = xw[4 + (idx & 3)];
+            }
+        }
+    }
+    if (a.est) {
+        block_spec_select(a.est, a.ne, a.topk, a.state ? &a.state->pos : nullptr, a.sabotage, lg, sel, tid, 256);
+        __syncthreads();
+    }
+    BRRR_STAMP(a.state, 102);
+    const int e = a.est ? sel[ei] : a.top[ei];
     const int nchunks = (np + a.ch - 1) / a.ch;
     if (tid == 0) {
         int urow = (e * a.d + blk32 * 32) >> 4;
@@ -252,6 +273,19 @@ __global__ void __launch_bounds__(256) gate_up_kernel(GateUpArgs a) {
         src[2] = a.up.data + mx_unit_off(urow, 0, np);
         src[3] = a.up.data + mx_unit_off(urow + 1, 0, np);
         for (int c = 0; c < min(a.stages, nchunks); c++) r.issue(c, src);
+    }
+    BRRR_STAMP(a.state, 103);
+    if (!a.x_f32) {
+#pragma unroll
+        for (int k = 0; k < 2; k++) {
+            const int idx = tid + k * 256;
+            if (idx < nb * 4) xp[idx] = mx_interleave(xlo[k], xhi[k]);
+        }
+        for (int idx = tid + 512; idx < nb * 4; idx += 256) {          // d > 4096 only
+            const uint32_t *xw = reinterpret_cast<const uint32_t *>(a.xq + (idx >> 2) * 32);
+            xp[idx] = mx_interleave(xw[idx & 3], xw[4 + (idx & 3)]);
+        }
+        for (int b = tid; b < nb; b += 256) xsc[b] = a.xs[b];
     }
     __syncthreads();
 
@@ -291,8 +325,10 @@ __global__ void __launch_bounds__(256) gate_up_kernel(GateUpArgs a) {
 
 cudaError_t launch_gate_up(MxDev gate, MxDev up, const float *gate_b, const float *up_b, const int32_t *top, int topk, int d,
                            const float *x_f32, const float *norm_w, float eps, const int8_t *xq, const float *xs,
-                           int8_t *hq, float *hs, float *gu, DevState *state, bool pdl, cudaStream_t st) {
+                           int8_t *hq, float *hs, float *gu, DevState *state, bool pdl, cudaStream_t st,
+                           const float *est, int ne, int sabotage) {
     GateUpArgs a{};
+    a.est = est; a.ne = ne; a.topk = topk; a.sabotage = sabotage;
     a.gate = gate; a.up = up; a.gate_b = gate_b; a.up_b = up_b; a.top = top; a.d = d;
     a.x_f32 = x_f32; a.norm_w = norm_w; a.eps = eps; a.xq = xq; a.xs = xs; a.hq = hq; a.hs = hs; a.gu = gu; a.state = state;
     const int nb = gate.blocks, np = nb / 2;
@@ -320,6 +356,8 @@ struct DownArgs {
     const float *down_b;
     const int32_t *top;
     const float *wts;
+    const float *est;          // nullable: router estimate whose top-k the hq/hs slots were computed for
+    int ne, sabotage;
     int topk, d;
     const int8_t *hq;
     const float *hs;
@@ -372,7 +410,22 @@ __global__ void __launch_bounds__(512) down_combine_kernel(DownArgs a) {
     const int ei = tid >> 6, t64 = tid & 63;
     int2 *xp = reinterpret_cast<int2 *>(xbase + per * ei);
     float *xsc = reinterpret_cast<float *>(xbase + per * ei + (size_t)nb * 4 * sizeof(int2));
-    mx_stage_x(a.hq + (size_t)ei * a.d, a.hs + (size_t)ei * nb, nb, xp, xsc, t64, 64);
+    // which slot of hq/hs holds this rank's expert (identity without speculation)
+    int slot = ei;
+    if (a.est) {
+        __shared__ int sel[8];
+        __shared__ float lg[256];
+        block_spec_select(a.est, a.ne, a.topk, a.state ? &a.state->pos : nullptr, a.sabotage, lg, sel, tid, nthreads);
+        __syncthreads();
+        slot = -1;
+        const int want = a.top[ei];
+        for (int s = 0; s < a.topk; s++) if (sel[s] == want) slot = s;
+        if (slot < 0) {                       // the estimate missed this expert: flag the step, keep going
+            slot = 0;
+            if (t64 == 0 && blockIdx.x == 0 && a.state) atomicMin(&a.state->spec_fail_step, a.state->n_out);
+        }
+    }
+    mx_stage_x(a.hq + (size_t)slot * a.d, a.hs + (size_t)slot * nb, nb, xp, xsc, t64, 64);
     __syncthreads();
 
     BRRR_STAMP(a.state, 131);
@@ -407,10 +460,10 @@ __global__ void __launch_bounds__(512) down_combine_kernel(DownArgs a) {
     (void)nthreads;
 }
 
-cudaError_t launch_down_combine(MxDev down, const float *down_b, const int32_t *top, const float *wts, int topk, int d,
-                                const int8_t *hq, const float *hs, float *x, DevState *state, bool pdl, cudaStream_t st) {
+cudaError_t launch_down_combine(MxDev down, const float *down_b, const int32_t *top, const float *wts, const float *est, int ne, int sabotage,
+                                int topk, int d, const int8_t *hq, const float *hs, float *x, DevState *state, bool pdl, cudaStream_t st) {
     DownArgs a{};
-    a.down = down; a.down_b = down_b; a.top = top; a.wts = wts; a.topk = topk; a.d = d; a.hq = hq; a.hs = hs; a.x = x; a.state = state;
+    a.down = down; a.down_b = down_b; a.top = top; a.wts = wts; a.est = est; a.ne = ne; a.sabotage = sabotage; a.topk = topk; a.d = d; a.hq = hq; a.hs = hs; a.x = x; a.state = state;
     const int nb = down.blocks, np = nb / 2;
     MxLaunchShape s = mx_shape(np, topk, 80 * 1024);
     a.ch = s.ch; a.stages = s.stages;

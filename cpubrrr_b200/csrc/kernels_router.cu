@@ -221,4 +221,90 @@ cudaError_t launch_ffn_in(const float *x_in, const float *norm_w, float eps, int
     return launch_k(ffn_in_kernel, dim3((ne + 31) / 32), dim3(RT_THREADS), smem, st, pdl, a);
 }
 
+// ---------------------------------------------------------------- routing hint (speculation)
+// A fast, order-free estimate of the router: one CTA per expert forms its logit with a parallel
+// reduction (a few ulps away from the serial chain); consumers pick the k largest themselves
+// (warp_spec_select).  The estimate only decides WHICH experts' gate/up weights start streaming while ffn_in_kernel walks
+// the exact serial chains next to it; the exact top-k, its order and its weights still come from
+// ffn_in_kernel, and down_combine_kernel refuses (spec_fail_step) any step whose exact expert set
+// is not covered by the estimate, so results never depend on this kernel.
+struct HintArgs {
+    const float *x_in, *norm_w;
+    float eps;
+    int d;
+    const float *Wt, *b;
+    int ne, topk;
+    float *est;              // [ne] estimated logits
+    int8_t *xq_out;          // nullable: Q8 of the normalised vector, each CTA writes a share
+    float *xs_out;
+    DevState *state;
+};
+
+constexpr int HINT_THREADS = 128;
+constexpr int HINT_MAXG = 8;         // float4 groups per thread kept in registers (d <= 4096)
+
+__global__ void __launch_bounds__(HINT_THREADS) router_hint_kernel(HintArgs a) {
+    extern __shared__ __align__(16) float hsm[];      // d floats of x, then ne floats
+    float *xf = hsm, *lg = hsm + a.d;
+    __shared__ float inv_sh, red[HINT_THREADS / 32];
+    const int tid = threadIdx.x, e = blockIdx.x, d = a.d, groups = d >> 2;
+    const int ntiles = (d + RT_TJ - 1) / RT_TJ;
+    // static operands first: this expert's row of the tiled matrix and the norm weights
+    const float *wrow = a.Wt + ((size_t)(e >> 5) * ntiles * 32 + (e & 31)) * RT_STRIDE;
+    float4 w[HINT_MAXG], nw[HINT_MAXG];
+#pragma unroll
+    for (int p = 0; p < HINT_MAXG; p++) {
+        const int g = tid + p * HINT_THREADS;
+        if (g < groups) {
+            const int j = g * 4, t = j / RT_TJ, jj = j % RT_TJ;
+            w[p] = *reinterpret_cast<const float4 *>(wrow + (size_t)t * RT_TILE_FLOATS + jj);
+            nw[p] = a.norm_w ? reinterpret_cast<const float4 *>(a.norm_w)[g] : make_float4(1.f, 1.f, 1.f, 1.f);
+        } else { w[p] = make_float4(0.f, 0.f, 0.f, 0.f); nw[p] = w[p]; }
+    }
+    const float bias = a.b ? a.b[e] : 0.0f;
+    pdl_wait();
+    BRRR_GT_GO(a.state, 224);
+    pdl_trigger();
+    stage_vec4(a.x_in, xf, d, tid, HINT_THREADS);
+    __syncthreads();
+    float inv = 1.0f;
+    if (a.norm_w) inv = block_rms_inv(xf, d, a.eps, &inv_sh);
+    float part = 0.0f;
+#pragma unroll
+    for (int p = 0; p < HINT_MAXG; p++) {
+        const int g = tid + p * HINT_THREADS;
+        if (g < groups) {
+            float4 x = reinterpret_cast<const float4 *>(xf)[g];
+            part += w[p].x * (x.x * inv * nw[p].x) + w[p].y * (x.y * inv * nw[p].y) + w[p].z * (x.z * inv * nw[p].z) + w[p].w * (x.w * inv * nw[p].w);
+        }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) part += __shfl_xor_sync(0xffffffffu, part, o);
+    if ((tid & 31) == 0) red[tid >> 5] = part;
+    __syncthreads();
+    if (tid == 0) {
+        float s = bias;
+        for (int i = 0; i < HINT_THREADS / 32; i++) s += red[i];
+        a.est[e] = s;
+    }
+    // This CTA's share of the Q8 quantisation of the normalised vector (exact, block-local):
+    // gate/up then stages 3 KB instead of normalising and quantising in every CTA.
+    if (a.xq_out) {
+        const int nb = d / 32, warp = tid >> 5, lane = tid & 31;
+        for (int blk = e * (HINT_THREADS / 32) + warp; blk < nb; blk += gridDim.x * (HINT_THREADS / 32)) {
+            float v = xf[blk * 32 + lane];
+            if (a.norm_w) v = __fmul_rn(__fmul_rn(v, inv), a.norm_w[blk * 32 + lane]);
+            warp_quant_block(v, lane, a.xq_out + blk * 32, a.xs_out + blk);
+        }
+    }
+    BRRR_GT_END(a.state, 225);
+}
+
+cudaError_t launch_router_hint(const float *x_in, const float *norm_w, float eps, int d, const float *Wt, const float *b, int ne, int topk,
+                               float *est, int8_t *xq_out, float *xs_out, DevState *state, bool pdl, cudaStream_t st) {
+    HintArgs a{x_in, norm_w, eps, d, Wt, b, ne, topk, est, xq_out, xs_out, state};
+    size_t smem = (size_t)(d + ne + 4) * sizeof(float);
+    return launch_k(router_hint_kernel, dim3(ne), dim3(HINT_THREADS), smem, st, pdl, a);
+}
+
 }  // namespace brrr

@@ -116,7 +116,15 @@ struct brrr_model {
     DevState *st = nullptr;
     // host staging (pinned)
     uint32_t *h_in = nullptr, *h_out = nullptr;
-    cudaGraphExec_t g_head = nullptr, g_nohead = nullptr;
+    cudaGraphExec_t g_head = nullptr, g_nohead = nullptr;            // speculative-routing step (or plain when disabled)
+    cudaGraphExec_t g_head_safe = nullptr, g_nohead_safe = nullptr;  // plain step, used to redo a missed speculation
+    cudaStream_t side = nullptr;                                     // the exact router runs here, beside gate/up
+    cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
+    bool use_spec = true;        // start gate/up from a fast router estimate, verify with the exact router
+    int sabotage = 0;            // test hook: make the estimate wrong on every third position
+    float *est = nullptr;        // estimated router logits
+    uint32_t run_tok = 0, run_pos = 0;   // arguments of the decode run in flight (for a redo)
+    uint64_t spec_redos = 0;
     int launches_head = 0, launches_nohead = 0;
     bool use_pdl = true;         // chain the step's kernels with programmatic dependent launch
     std::vector<void *> allocs;
@@ -217,7 +225,7 @@ int check_cfg(const brrr_cfg &c) {
     if (c.n_ff_exp != c.n_embd) return BRRR_ERR_ARG;                     // engine_gpt2.rs:73
     if (c.head_dim != 64) return BRRR_ERR_ARG;                           // engine_gpt2.rs:74
     if (c.n_head <= 0 || c.n_head_kv <= 0 || c.n_head % c.n_head_kv) return BRRR_ERR_ARG;
-    if (c.n_expert <= 0 || c.n_expert_used <= 0 || c.n_expert_used > 8 || c.n_expert_used > c.n_expert) return BRRR_ERR_ARG;
+    if (c.n_expert <= 0 || c.n_expert > 256 || c.n_expert_used <= 0 || c.n_expert_used > 8 || c.n_expert_used > c.n_expert) return BRRR_ERR_ARG;
     if (c.n_vocab <= 0 || c.n_vocab % 4 || c.n_layer <= 0) return BRRR_ERR_ARG;
     if (c.sliding_window <= 0) return BRRR_ERR_ARG;
     return BRRR_OK;
@@ -242,7 +250,7 @@ const char *const kStageNames[ST_COUNT] = {"embed", "norm_qkv_gemv", "attention"
 // trace path).  Stage order and data flow follow forward_worker (engine_gpt2.rs:751-934); the
 // reference's nine barrier-separated stages per layer are six kernels here, chained with
 // programmatic dependent launch.
-int enqueue_step(brrr_model *m, bool want, float *trace_dev, int *nlaunch, unsigned mask = ~0u) {
+int enqueue_step(brrr_model *m, bool want, float *trace_dev, int *nlaunch, unsigned mask = ~0u, bool spec = false) {
     const brrr_cfg &c = m->cfg;
     const int d = c.n_embd, nh = c.n_head, nkv = c.n_head_kv, topk = c.n_expert_used;
     cudaStream_t s = m->stream;
@@ -258,11 +266,33 @@ int enqueue_step(brrr_model *m, bool want, float *trace_dev, int *nlaunch, unsig
         if (window >= BRRR_MAXSEQ) window = 0;
         if (on(ST_ATTN)) CUL(launch_attn_decode(m->qkv, ly.kc, ly.vc, m->rope, ly.sinks, nh, nkv, m->st, 0, window, m->ao, m->aq, m->as, m->st, pdl, s));
         if (on(ST_OPROJ)) CUL(launch_q8_stream(ly.wo, nullptr, nullptr, 0.0f, m->aq, m->as, ly.bo, m->x, Q8_EPI_RESID_BIAS, m->st, pdl, s));
+        if (spec) {
+            // Speculative routing: the exact serial-chain router runs on the side stream while the
+            // main stream estimates the expert set and streams gate/up for it; down joins both,
+            // uses the exact routing and flags the step if the estimate missed an expert.
+            CU(cudaEventRecord(m->ev_fork, s));
+            CU(cudaStreamWaitEvent(m->side, m->ev_fork, 0));
+            n++;
+            CUL(launch_ffn_in(m->x, ly.ffn_norm, c.rms_eps, d, ly.ginp, ly.ginp_b, c.n_expert, topk, m->rlogits, m->top, m->wts,
+                              &m->st->router_done, m->st, false, m->side));
+            CU(cudaEventRecord(m->ev_join, m->side));
+            n++;
+            CUL(launch_router_hint(m->x, ly.ffn_norm, c.rms_eps, d, ly.ginp, ly.ginp_b, c.n_expert, topk, m->est, m->xq, m->xs, m->st, pdl, s));
+            n++;
+            CUL(launch_gate_up(ly.gate, ly.up, ly.gate_b, ly.up_b, nullptr, topk, d, nullptr, nullptr, c.rms_eps, m->xq, m->xs,
+                               m->hq, m->hs, nullptr, m->st, pdl, s, m->est, c.n_expert, m->sabotage));
+            CU(cudaStreamWaitEvent(s, m->ev_join, 0));
+            n++;
+            // full dependency on both predecessors: a programmatic launch here was observed to start
+            // before the side-stream router had finished
+            CUL(launch_down_combine(ly.down, ly.down_b, m->top, m->wts, m->est, c.n_expert, m->sabotage, topk, d, m->hq, m->hs, m->x, m->st, false, s));
+        } else {
         if (on(ST_ROUTER)) CUL(launch_ffn_in(m->x, ly.ffn_norm, c.rms_eps, d, ly.ginp, ly.ginp_b, c.n_expert, topk, m->rlogits, m->top, m->wts,
                                              &m->st->router_done, m->st, pdl, s));
         if (on(ST_GATE_UP)) CUL(launch_gate_up(ly.gate, ly.up, ly.gate_b, ly.up_b, m->top, topk, d, m->x, ly.ffn_norm, c.rms_eps, nullptr, nullptr,
                                                m->hq, m->hs, nullptr, m->st, pdl, s));
-        if (on(ST_DOWN)) CUL(launch_down_combine(ly.down, ly.down_b, m->top, m->wts, topk, d, m->hq, m->hs, m->x, m->st, pdl, s));
+        if (on(ST_DOWN)) CUL(launch_down_combine(ly.down, ly.down_b, m->top, m->wts, nullptr, 0, 0, topk, d, m->hq, m->hs, m->x, m->st, pdl, s));
+        }
         if (trace_dev) CU(cudaMemcpyAsync(trace_dev + (size_t)(il + 1) * d, m->x, d * sizeof(float), cudaMemcpyDeviceToDevice, s));
     }
     if (want) {
@@ -275,10 +305,10 @@ int enqueue_step(brrr_model *m, bool want, float *trace_dev, int *nlaunch, unsig
     return BRRR_OK;
 }
 
-int capture(brrr_model *m, bool want, cudaGraphExec_t *out, int *nlaunch, unsigned mask = ~0u) {
+int capture(brrr_model *m, bool want, cudaGraphExec_t *out, int *nlaunch, unsigned mask = ~0u, bool spec = false) {
     cudaGraph_t g = nullptr;
     CU(cudaStreamBeginCapture(m->stream, cudaStreamCaptureModeThreadLocal));
-    int s = enqueue_step(m, want, nullptr, nlaunch, mask);
+    int s = enqueue_step(m, want, nullptr, nlaunch, mask, spec);
     cudaError_t e = cudaStreamEndCapture(m->stream, &g);
     if (s != BRRR_OK) { if (g) cudaGraphDestroy(g); return s; }
     CU(e);
@@ -293,6 +323,11 @@ int build_model(brrr_model *m, const Source &src) {
     CU(cudaSetDevice(m->device));
     CU(cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking));
     if (const char *e = getenv("BRRR_NOPDL")) m->use_pdl = !(e[0] && e[0] != '0');
+    if (const char *e = getenv("BRRR_NOSPEC")) m->use_spec = !(e[0] && e[0] != '0');
+    if (const char *e = getenv("BRRR_SPEC_SABOTAGE")) m->sabotage = (e[0] && e[0] != '0');
+    CU(cudaStreamCreateWithFlags(&m->side, cudaStreamNonBlocking));
+    CU(cudaEventCreateWithFlags(&m->ev_fork, cudaEventDisableTiming));
+    CU(cudaEventCreateWithFlags(&m->ev_join, cudaEventDisableTiming));
 
     // scratch for one raw tensor: the largest of the bf16 matrices and one MXFP4 expert tensor
     size_t scratch_bytes = std::max({(size_t)c.n_vocab * d * 2, (size_t)ne * d * nb * 17, (size_t)nh * hd * d * 2});
@@ -350,6 +385,7 @@ int build_model(brrr_model *m, const Source &src) {
     TRY(m->alloc(&m->xs, nb)); TRY(m->alloc(&m->as, nh * hd / 32)); TRY(m->alloc(&m->hs, (size_t)topk * nb)); TRY(m->alloc(&m->wts, 8));
     TRY(m->alloc(&m->xq, d)); TRY(m->alloc(&m->aq, nh * hd)); TRY(m->alloc(&m->hq, (size_t)topk * d));
     TRY(m->alloc(&m->top, 8)); TRY(m->alloc(&m->st, 1));
+    TRY(m->alloc(&m->est, (size_t)ne));
     CU(cudaMemsetAsync(m->st, 0, sizeof(DevState), m->stream));
     CU(cudaMemsetAsync(m->x, 0, d * 4, m->stream));
     CU(cudaMallocHost(&m->h_in, 16));
@@ -359,8 +395,21 @@ int build_model(brrr_model *m, const Source &src) {
     TRY(enqueue_step(m, true, nullptr, nullptr));
     CU(cudaStreamSynchronize(m->stream));
     CU(cudaMemsetAsync(m->st, 0, sizeof(DevState), m->stream));
-    TRY(capture(m, true, &m->g_head, &m->launches_head));
-    TRY(capture(m, false, &m->g_nohead, &m->launches_nohead));
+    CU(cudaMemsetAsync(&m->st->spec_fail_step, 0xFF, 4, m->stream));
+    TRY(capture(m, true, &m->g_head_safe, &m->launches_head));
+    TRY(capture(m, false, &m->g_nohead_safe, &m->launches_nohead));
+    if (m->use_spec) {
+        // direct speculative step once (kernel attributes), then capture
+        TRY(enqueue_step(m, true, nullptr, nullptr, ~0u, true));
+        CU(cudaStreamSynchronize(m->stream));
+        CU(cudaMemsetAsync(m->st, 0, sizeof(DevState), m->stream));
+        CU(cudaMemsetAsync(&m->st->spec_fail_step, 0xFF, 4, m->stream));
+        TRY(capture(m, true, &m->g_head, &m->launches_head, ~0u, true));
+        TRY(capture(m, false, &m->g_nohead, &m->launches_nohead, ~0u, true));
+    } else {
+        TRY(capture(m, true, &m->g_head, &m->launches_head));
+        TRY(capture(m, false, &m->g_nohead, &m->launches_nohead));
+    }
     CU(cudaStreamSynchronize(m->stream));
     return BRRR_OK;
 }
@@ -452,6 +501,11 @@ extern "C" void brrr_model_close(brrr_model *m) {
     if (m->stream) cudaStreamSynchronize(m->stream);
     if (m->g_head) cudaGraphExecDestroy(m->g_head);
     if (m->g_nohead) cudaGraphExecDestroy(m->g_nohead);
+    if (m->g_head_safe) cudaGraphExecDestroy(m->g_head_safe);
+    if (m->g_nohead_safe) cudaGraphExecDestroy(m->g_nohead_safe);
+    if (m->ev_fork) cudaEventDestroy(m->ev_fork);
+    if (m->ev_join) cudaEventDestroy(m->ev_join);
+    if (m->side) cudaStreamDestroy(m->side);
     for (void *p : m->allocs) cudaFree(p);
     if (m->h_in) cudaFreeHost(m->h_in);
     if (m->h_out) cudaFreeHost(m->h_out);
@@ -488,10 +542,13 @@ extern "C" uint64_t brrr_model_bytes_per_step(const brrr_model *m, uint32_t pos)
     return total;
 }
 
-static int run_graph(brrr_model *m, bool want) {
-    CU(cudaGraphLaunch(want ? m->g_head : m->g_nohead, m->stream));
+static int run_graph(brrr_model *m, bool want, bool safe = false) {
+    cudaGraphExec_t g = safe ? (want ? m->g_head_safe : m->g_nohead_safe) : (want ? m->g_head : m->g_nohead);
+    CU(cudaGraphLaunch(g, m->stream));
     return BRRR_OK;
 }
+
+extern "C" uint64_t brrr_model_spec_redos(const brrr_model *m) { return m ? m->spec_redos : 0; }
 
 extern "C" int brrr_forward(brrr_model *m, uint32_t tok, uint32_t pos, int want, uint32_t *out_tok) {
     if (!m) return BRRR_ERR_ARG;
@@ -503,6 +560,16 @@ extern "C" int brrr_forward(brrr_model *m, uint32_t tok, uint32_t pos, int want,
     CU(cudaMemcpyAsync(m->h_out, m->st, 32, cudaMemcpyDeviceToHost, m->stream));   // tok .. err
     CU(cudaStreamSynchronize(m->stream));
     if (m->h_out[6] != 0) { snprintf(g_cuda_err, sizeof g_cuda_err, "device wait timed out (code %u)", m->h_out[6]); return BRRR_ERR_STATE; }
+    if (m->h_out[7] != 0xFFFFFFFFu) {
+        // the router estimate missed an expert somewhere in this step: run it again without speculation
+        m->spec_redos++;
+        CU(cudaMemsetAsync(&m->st->spec_fail_step, 0xFF, 4, m->stream));
+        CU(cudaMemcpyAsync(m->st, m->h_in, 8, cudaMemcpyHostToDevice, m->stream));
+        TRY(run_graph(m, want != 0, true));
+        CU(cudaMemcpyAsync(m->h_out, m->st, 32, cudaMemcpyDeviceToHost, m->stream));
+        CU(cudaStreamSynchronize(m->stream));
+        if (m->h_out[6] != 0) return BRRR_ERR_STATE;
+    }
     if (want && out_tok) *out_tok = m->h_out[0];
     return BRRR_OK;
 }
@@ -523,6 +590,7 @@ extern "C" int brrr_decode_enqueue(brrr_model *m, uint32_t first_tok, uint32_t p
     if (first_tok >= (uint32_t)m->cfg.n_vocab || n == 0 || n > BRRR_MAXSEQ || pos + n > BRRR_MAXSEQ) return BRRR_ERR_RANGE;
     CU(cudaSetDevice(m->device));
     m->h_in[0] = first_tok; m->h_in[1] = pos; m->h_in[2] = 0;
+    m->run_tok = first_tok; m->run_pos = pos;
     CU(cudaMemcpyAsync(m->st, m->h_in, 12, cudaMemcpyHostToDevice, m->stream));  // tok, pos, n_out = 0
     for (uint32_t i = 0; i < n; i++) TRY(run_graph(m, true));
     return BRRR_OK;
@@ -532,9 +600,23 @@ extern "C" int brrr_decode_wait(brrr_model *m, uint32_t n, uint32_t *out_toks) {
     if (!m || !out_toks || n == 0 || n > BRRR_MAXSEQ) return BRRR_ERR_ARG;
     CU(cudaSetDevice(m->device));
     CU(cudaMemcpyAsync(m->h_out, m->st->out, n * sizeof(uint32_t), cudaMemcpyDeviceToHost, m->stream));
-    CU(cudaMemcpyAsync(m->h_in, &m->st->err, 4, cudaMemcpyDeviceToHost, m->stream));
-    CU(cudaStreamSynchronize(m->stream));
-    if (m->h_in[0] != 0) { snprintf(g_cuda_err, sizeof g_cuda_err, "device wait timed out (code %u)", m->h_in[0]); return BRRR_ERR_STATE; }
+    for (int guard = 0; guard < (int)n + 1; guard++) {
+        CU(cudaMemcpyAsync(m->h_in, &m->st->err, 8, cudaMemcpyDeviceToHost, m->stream));   // err, spec_fail_step
+        CU(cudaStreamSynchronize(m->stream));
+        if (m->h_in[0] != 0) { snprintf(g_cuda_err, sizeof g_cuda_err, "device wait timed out (code %u)", m->h_in[0]); return BRRR_ERR_STATE; }
+        const uint32_t f = m->h_in[1];
+        if (f >= n) break;
+        // Step f ran with an expert set the exact router did not confirm: its token and every later
+        // one are void.  Resume from step f without speculation (the KV cache entries of the voided
+        // steps are simply overwritten).
+        m->spec_redos++;
+        CU(cudaMemsetAsync(&m->st->spec_fail_step, 0xFF, 4, m->stream));
+        m->h_in[0] = f ? m->h_out[f - 1] : m->run_tok; m->h_in[1] = m->run_pos + f; m->h_in[2] = f;
+        CU(cudaMemcpyAsync(m->st, m->h_in, 12, cudaMemcpyHostToDevice, m->stream));
+        TRY(run_graph(m, true, true));                                  // the failed step, exactly
+        for (uint32_t i = f + 1; i < n; i++) TRY(run_graph(m, true));   // the rest speculates again
+        CU(cudaMemcpyAsync(m->h_out, m->st->out, n * sizeof(uint32_t), cudaMemcpyDeviceToHost, m->stream));
+    }
     memcpy(out_toks, m->h_out, n * sizeof(uint32_t));
     return BRRR_OK;
 }
@@ -593,7 +675,7 @@ extern "C" int brrr_moe_ffn_step(brrr_model *m, int il, const float *d_xn, float
     cudaStream_t s = m->stream;
     CUL(launch_ffn_in(d_xn, nullptr, c.rms_eps, d, ly.ginp, ly.ginp_b, c.n_expert, topk, m->rlogits, m->top, m->wts, &m->st->router_done, m->st, false, s));
     CUL(launch_gate_up(ly.gate, ly.up, ly.gate_b, ly.up_b, m->top, topk, d, d_xn, nullptr, c.rms_eps, nullptr, nullptr, m->hq, m->hs, nullptr, m->st, false, s));
-    CUL(launch_down_combine(ly.down, ly.down_b, m->top, m->wts, topk, d, m->hq, m->hs, d_x, m->st, false, s));
+    CUL(launch_down_combine(ly.down, ly.down_b, m->top, m->wts, nullptr, 0, 0, topk, d, m->hq, m->hs, d_x, m->st, false, s));
     CU(cudaGetLastError());
     if (d_top) CU(cudaMemcpyAsync(d_top, m->top, topk * sizeof(int32_t), cudaMemcpyDeviceToDevice, s));
     if (d_wts) CU(cudaMemcpyAsync(d_wts, m->wts, topk * sizeof(float), cudaMemcpyDeviceToDevice, s));

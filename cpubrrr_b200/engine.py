@@ -112,6 +112,10 @@ class Engine:
     def launches_per_step(self, want=True):
         return lib().brrr_model_launches_per_step(self._h, int(bool(want)))
 
+    def spec_redos(self):
+        """Steps re-run because the routing estimate missed an expert (performance counter)."""
+        return int(lib().brrr_model_spec_redos(self._h))
+
     def bytes_per_step(self, pos):
         return int(lib().brrr_model_bytes_per_step(self._h, int(pos)))
 

@@ -100,6 +100,10 @@ int brrr_forward_trace(brrr_model *m, uint32_t tok, uint32_t pos, float *trace);
 void *brrr_model_stream(brrr_model *m);
 /* Number of kernel launches one decode step performs (graph kernel nodes). */
 int brrr_model_launches_per_step(const brrr_model *m, int want_logits);
+/* How many steps had to be re-run because the fast router estimate that starts the expert weight
+ * stream early missed an expert the exact router chose (results are unaffected; this is a
+ * performance counter).  No counterpart in the reference. */
+uint64_t brrr_model_spec_redos(const brrr_model *m);
 /* Weight + KV bytes one decode step at position `pos` must read in the run-time formats. */
 uint64_t brrr_model_bytes_per_step(const brrr_model *m, uint32_t pos);
 

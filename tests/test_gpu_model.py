@@ -179,3 +179,37 @@ def test_full_size_gptoss20b_parity_and_properties(brrr, orc):
     assert np.array_equal(a, eng.decode(first, len(prompt), 140))          # replay determinism past the window
     assert eng.launches_per_step(True) > 0 and eng.bytes_per_step(100) > 2.6e9
     eng.close()
+
+
+def test_speculative_routing_miss_is_redone_exactly(brrr, orc, monkeypatch):
+    """The expert weight stream starts from a fast router estimate; a step whose exact experts the
+    estimate missed must be detected and re-run, leaving results bit-identical.  The test hook
+    makes the estimate wrong on every third position."""
+    cfg = brrr.make_cfg(128, 2, 4, 2, 8, 4, 512, sliding_window=8)
+    monkeypatch.setenv("BRRR_SPEC_SABOTAGE", "1")
+    eng = brrr.Engine.synth(cfg, 17)
+    monkeypatch.delenv("BRRR_SPEC_SABOTAGE")
+    om = orc.Model.synth(ocfg_of(orc, cfg), 17)
+    prompt = S.synth_prompt(17, 9, 500)
+    want = greedy(om.run, prompt, 40)
+    assert greedy(eng.run, prompt, 40) == want                  # host-driven steps
+    assert np.array_equal(bits(eng.logits()), bits(om.logits()))
+    first = eng.prefill(prompt)
+    toks = eng.decode(first, len(prompt), 40)                   # device-chained run with redos inside
+    assert [first] + [int(t) for t in toks[:-1]] == want
+    assert eng.spec_redos() > 10
+    # and without the hook the estimate practically never misses
+    clean = brrr.Engine.synth(cfg, 17)
+    assert greedy(clean.run, prompt, 40) == want and clean.spec_redos() == 0
+    eng.close(); clean.close()
+
+
+def test_speculation_can_be_disabled(brrr, orc, monkeypatch):
+    cfg = brrr.make_cfg(128, 2, 4, 2, 8, 4, 512)
+    monkeypatch.setenv("BRRR_NOSPEC", "1")
+    eng = brrr.Engine.synth(cfg, 5)
+    monkeypatch.delenv("BRRR_NOSPEC")
+    om = orc.Model.synth(ocfg_of(orc, cfg), 5)
+    prompt = S.synth_prompt(5, 6, 500)
+    assert greedy(eng.run, prompt, 20) == greedy(om.run, prompt, 20)
+    eng.close()
