@@ -44,6 +44,9 @@ SIGNATURES = {
     "brrr_stage_time": (_I, [_P, _I, C.c_uint32, _I, C.POINTER(C.c_float), C.POINTER(C.c_uint64), C.POINTER(_I)]),
     "brrr_debug_stamps": (_I, [_P, _P]),
     "brrr_quant_q8": (_I, [_P, _I, _P, _P, _P]),
+    "brrr_quant_q8k": (_I, [_P, _I, _P, _P, _P, _P]),
+    "brrr_q4k_matvec": (_I, [_P, _I, _I, _P, _P, _P, _P, _P, _P]),
+    "brrr_q6k_matvec": (_I, [_P, _I, _I, _P, _P, _P, _P, _P]),
     "brrr_rmsnorm_quant": (_I, [_P, _P, C.c_float, _I, _P, _P, _P, _P]),
     "brrr_q8mat_from_bf16": (_I, [_P, _I, _I, C.POINTER(_P), _P]),
     "brrr_q8mat_export": (_I, [_P, _P, _P, _P]),

@@ -15,6 +15,12 @@ void launch_finish_token(DevState *state, cudaStream_t st);
 void launch_expf(const float *x, int n, float *y, cudaStream_t st);
 void launch_synth(uint64_t seed, uint32_t layer, uint32_t kind, uint32_t type, uint64_t nelems, void *out, cudaStream_t st);
 
+// ---- K-quants of the qwen3moe path (kernels_kq.cu): weights stay in the GGUF byte layout
+void launch_quant_q8k(const float *x, int n, int8_t *q, float *s, int32_t *bsum, cudaStream_t st);
+void launch_q4k_matvec(const uint8_t *w, int rows, int cols, const int8_t *xq, const float *ys, const int32_t *bsum, float *y,
+                       int32_t *dbg, cudaStream_t st);
+void launch_q6k_matvec(const uint8_t *w, int rows, int cols, const int8_t *xq, const float *ys, float *y, int32_t *dbg, cudaStream_t st);
+
 // ---- Q8 matrices (kernels_q8.cu)
 void launch_q8_pack(const uint16_t *w_bf16, int rows_src, int row0_dst, Q8Dev m, cudaStream_t st);
 void launch_q8_export(Q8Dev m, int8_t *q, float *s, cudaStream_t st);

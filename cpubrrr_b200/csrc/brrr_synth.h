@@ -7,7 +7,7 @@
  * tensor it needs.
  *
  * The generator emits tensors in the GGUF on-disk formats the engine reads
- * (f32, bf16, MXFP4 17-byte blocks), i.e. the same bytes a data directory's blob would hold.
+ * (f32, bf16, MXFP4 17-byte blocks, Q4_K 144-byte and Q6_K 210-byte superblocks), i.e. the same bytes a data directory's blob would hold.
  *
  * This header is C99 / C++ / CUDA compatible and has no dependencies.
  */
@@ -31,6 +31,7 @@ enum {
     BRRR_T_SINKS = 10, BRRR_T_ROUTER_W = 11, BRRR_T_ROUTER_B = 12,
     BRRR_T_GATE = 13, BRRR_T_UP = 14, BRRR_T_DOWN = 15,
     BRRR_T_GATE_B = 16, BRRR_T_UP_B = 17, BRRR_T_DOWN_B = 18,
+    BRRR_T_Q_NORM = 19, BRRR_T_K_NORM = 20,
     /* global tensors use layer = BRRR_L_GLOBAL */
     BRRR_T_TOK_EMBD = 32, BRRR_T_OUT_NORM = 33, BRRR_T_OUTPUT = 34,
     BRRR_T_PROMPT = 40, BRRR_T_INPUT = 41
@@ -100,6 +101,35 @@ BRRR_HD void brrr_synth_mxfp4_block(uint64_t key, uint64_t blk, uint8_t out[17])
     uint64_t d0 = brrr_draw(key, 3 * blk), d1 = brrr_draw(key, 3 * blk + 1), d2 = brrr_draw(key, 3 * blk + 2);
     out[0] = (uint8_t)(117u + (uint32_t)(d2 % 7u));
     for (int i = 0; i < 8; i++) { out[1 + i] = (uint8_t)(d0 >> (8 * i)); out[9 + i] = (uint8_t)(d1 >> (8 * i)); }
+}
+
+/* One 144-byte GGUF Q4_K superblock (256 values): f16 d, f16 dmin, 12 bytes of packed 6-bit
+ * scales/mins, 128 bytes of nibbles.  All bytes random; d is an f16 in [2^-13, 2^-12) and, for one
+ * block in 16, an f16 subnormal; dmin is an f16 in [2^-11, 2^-9).  20 draws per block. */
+BRRR_HD void brrr_synth_q4k_block(uint64_t key, uint64_t blk, uint8_t out[144]) {
+    uint64_t h = brrr_draw(key, 20 * blk);
+    uint32_t mant = (uint32_t)(h & 0x3ffu), sub = ((h >> 10) & 15u) == 0;
+    uint16_t d = (uint16_t)((sub ? 0u : (2u << 10)) | (sub ? (mant | 0x200u) : mant));
+    uint16_t dmin = (uint16_t)(((4u + (uint32_t)((h >> 14) & 1u)) << 10) | (uint32_t)((h >> 16) & 0x3ffu));
+    out[0] = (uint8_t)d; out[1] = (uint8_t)(d >> 8); out[2] = (uint8_t)dmin; out[3] = (uint8_t)(dmin >> 8);
+    out[4] = (uint8_t)(h >> 32); out[5] = (uint8_t)(h >> 40); out[6] = (uint8_t)(h >> 48); out[7] = (uint8_t)(h >> 56);
+    for (int j = 0; j < 17; j++) {
+        uint64_t v = brrr_draw(key, 20 * blk + 1 + j);
+        for (int i = 0; i < 8; i++) out[8 + 8 * j + i] = (uint8_t)(v >> (8 * i));
+    }
+}
+
+/* One 210-byte GGUF Q6_K superblock: 128 bytes of low nibbles, 64 bytes of 2-bit fields, 16 int8
+ * scales (uniform over -128..127), f16 d (a subnormal, m * 2^-24 with m in 128..639, the range real
+ * checkpoints use).  All other bytes random.  27 draws per block. */
+BRRR_HD void brrr_synth_q6k_block(uint64_t key, uint64_t blk, uint8_t out[210]) {
+    for (int j = 0; j < 26; j++) {
+        uint64_t v = brrr_draw(key, 27 * blk + j);
+        for (int i = 0; i < 8; i++) out[8 * j + i] = (uint8_t)(v >> (8 * i));
+    }
+    uint64_t h = brrr_draw(key, 27 * blk + 26);
+    uint16_t d = (uint16_t)(128u + (uint32_t)(h & 0x1ffu));
+    out[208] = (uint8_t)d; out[209] = (uint8_t)(d >> 8);
 }
 
 /* uniform token id in [0, bound) */

@@ -20,6 +20,29 @@ extern "C" int brrr_quant_q8(const float *d_x, int n, int8_t *d_q, float *d_s, v
     return check_launch();
 }
 
+extern "C" int brrr_quant_q8k(const float *d_x, int n, int8_t *d_q, float *d_s, int32_t *d_bsum, void *stream) {
+    if (!d_x || !d_q || !d_s || !d_bsum || n <= 0 || n % 256) return BRRR_ERR_ARG;
+    if (((uintptr_t)d_x & 15) || ((uintptr_t)d_q & 7)) return BRRR_ERR_ARG;
+    launch_quant_q8k(d_x, n, d_q, d_s, d_bsum, (cudaStream_t)stream);
+    return check_launch();
+}
+
+extern "C" int brrr_q4k_matvec(const uint8_t *d_w, int rows, int cols, const int8_t *d_xq, const float *d_ys, const int32_t *d_bsum,
+                               float *d_y, int32_t *d_sbdots, void *stream) {
+    if (!d_w || !d_xq || !d_ys || !d_bsum || !d_y || rows <= 0 || cols <= 0 || cols % 256) return BRRR_ERR_ARG;
+    if (((uintptr_t)d_w & 3) || ((uintptr_t)d_xq & 3)) return BRRR_ERR_ARG;
+    launch_q4k_matvec(d_w, rows, cols, d_xq, d_ys, d_bsum, d_y, d_sbdots, (cudaStream_t)stream);
+    return check_launch();
+}
+
+extern "C" int brrr_q6k_matvec(const uint8_t *d_w, int rows, int cols, const int8_t *d_xq, const float *d_ys, float *d_y,
+                               int32_t *d_sbdots, void *stream) {
+    if (!d_w || !d_xq || !d_ys || !d_y || rows <= 0 || cols <= 0 || cols % 256) return BRRR_ERR_ARG;
+    if (((uintptr_t)d_w & 1) || ((uintptr_t)d_xq & 1)) return BRRR_ERR_ARG;
+    launch_q6k_matvec(d_w, rows, cols, d_xq, d_ys, d_y, d_sbdots, (cudaStream_t)stream);
+    return check_launch();
+}
+
 extern "C" int brrr_rmsnorm_quant(const float *d_x, const float *d_w, float eps, int n, float *d_xn, int8_t *d_q, float *d_s, void *stream) {
     if (!d_x || !d_w || !d_q || !d_s || n <= 0 || n % 32 || n > 8192) return BRRR_ERR_ARG;
     if (launch_rmsnorm_quant(d_x, d_w, eps, n, d_xn, d_q, d_s, false, (cudaStream_t)stream) != cudaSuccess) return BRRR_ERR_CUDA;

@@ -15,7 +15,7 @@ import numpy as np
 PHI = np.uint64(0x9E3779B97F4A7C15)
 L_GLOBAL = 0xFFFF
 T = dict(ATTN_NORM=0, FFN_NORM=1, WQ=2, WK=3, WV=4, WO=5, BQ=6, BK=7, BV=8, BO=9, SINKS=10, ROUTER_W=11,
-         ROUTER_B=12, GATE=13, UP=14, DOWN=15, GATE_B=16, UP_B=17, DOWN_B=18, TOK_EMBD=32, OUT_NORM=33,
+         ROUTER_B=12, GATE=13, UP=14, DOWN=15, GATE_B=16, UP_B=17, DOWN_B=18, Q_NORM=19, K_NORM=20, TOK_EMBD=32, OUT_NORM=33,
          OUTPUT=34, PROMPT=40, INPUT=41)
 
 _old = np.seterr(over="ignore")
@@ -79,6 +79,37 @@ def synth_mxfp4(seed, layer, kind, nblocks):
     out[:, 1:9] = d0.view(np.uint8).reshape(nblocks, 8)      # little-endian bytes
     out[:, 9:17] = d1.view(np.uint8).reshape(nblocks, 8)
     return out.reshape(-1)
+
+
+def synth_q4k_blocks(seed, layer, kind, nblocks):
+    """numpy port of brrr_synth_q4k_block: uint8 [nblocks, 144]."""
+    key = tensor_key(seed, layer, kind)
+    b = np.arange(nblocks, dtype=np.uint64) * np.uint64(20)
+    h = draw(key, b)
+    mant = (h & np.uint64(0x3ff)).astype(np.uint32)
+    sub = ((h >> np.uint64(10)) & np.uint64(15)) == 0
+    d = np.where(sub, mant | np.uint32(0x200), np.uint32(2 << 10) | mant).astype(np.uint16)
+    dmin = (((np.uint64(4) + ((h >> np.uint64(14)) & np.uint64(1))) << np.uint64(10)) | ((h >> np.uint64(16)) & np.uint64(0x3ff))).astype(np.uint16)
+    out = np.empty((nblocks, 144), np.uint8)
+    out[:, 0:2] = d.view(np.uint8).reshape(nblocks, 2)
+    out[:, 2:4] = dmin.view(np.uint8).reshape(nblocks, 2)
+    out[:, 4:8] = h.view(np.uint8).reshape(nblocks, 8)[:, 4:8]
+    for j in range(17):
+        out[:, 8 + 8 * j:16 + 8 * j] = draw(key, b + np.uint64(1 + j)).view(np.uint8).reshape(nblocks, 8)
+    return out
+
+
+def synth_q6k_blocks(seed, layer, kind, nblocks):
+    """numpy port of brrr_synth_q6k_block: uint8 [nblocks, 210]."""
+    key = tensor_key(seed, layer, kind)
+    b = np.arange(nblocks, dtype=np.uint64) * np.uint64(27)
+    out = np.empty((nblocks, 210), np.uint8)
+    for j in range(26):
+        out[:, 8 * j:8 * j + 8] = draw(key, b + np.uint64(j)).view(np.uint8).reshape(nblocks, 8)
+    h = draw(key, b + np.uint64(26))
+    d = (np.uint64(128) + (h & np.uint64(0x1ff))).astype(np.uint16)
+    out[:, 208:210] = d.view(np.uint8).reshape(nblocks, 2)
+    return out
 
 
 def synth_prompt(seed, n, bound):
@@ -325,3 +356,44 @@ def write_synth_model(out_dir, cfg, seed):
     write_gguf(blob, cfg, seed)
     write_data_dir(out_dir, blob)
     return out_dir, blob
+
+
+# ---- K-quant test tensors (qwen3moe path) ------------------------------------------------------
+
+def _f16_bits(v):
+    return np.asarray(v, dtype=np.float16).view(np.uint16)
+
+
+def synth_q4k(seed, rows, cols):
+    """Random but well-formed Q4_K rows in the GGUF byte layout (144 B per 256 values: f16 d, f16 dmin,
+    12 B of packed 6-bit scales/mins, 128 B of nibbles).  Returns uint8 [rows, cols/256*144]."""
+    rng = np.random.default_rng(seed)
+    nsb = cols // 256
+    out = np.empty((rows, nsb, 144), np.uint8)
+    d = rng.uniform(2e-4, 2e-3, size=(rows, nsb)).astype(np.float32)
+    dmin = rng.uniform(2e-4, 2e-3, size=(rows, nsb)).astype(np.float32)
+    out[:, :, 0:2] = _f16_bits(d)[..., None].view(np.uint8).reshape(rows, nsb, 2)
+    out[:, :, 2:4] = _f16_bits(dmin)[..., None].view(np.uint8).reshape(rows, nsb, 2)
+    out[:, :, 4:144] = rng.integers(0, 256, size=(rows, nsb, 140), dtype=np.uint8)
+    return out.reshape(rows, nsb * 144)
+
+
+def synth_q6k(seed, rows, cols):
+    """Random but well-formed Q6_K rows (210 B per 256 values: 128 B low nibbles, 64 B high 2-bit
+    fields, 16 int8 scales, f16 d).  Returns uint8 [rows, cols/256*210]."""
+    rng = np.random.default_rng(seed)
+    nsb = cols // 256
+    out = np.empty((rows, nsb, 210), np.uint8)
+    out[:, :, 0:192] = rng.integers(0, 256, size=(rows, nsb, 192), dtype=np.uint8)
+    out[:, :, 192:208] = rng.integers(-128, 128, size=(rows, nsb, 16), dtype=np.int8).view(np.uint8)
+    d = rng.uniform(1e-5, 1e-4, size=(rows, nsb)).astype(np.float32)
+    out[:, :, 208:210] = _f16_bits(d)[..., None].view(np.uint8).reshape(rows, nsb, 2)
+    return out.reshape(rows, nsb * 210)
+
+
+def synth_activation(seed, n, scale=1.0):
+    """Seeded normal activations with a few outliers, float32 [n]."""
+    rng = np.random.default_rng(seed)
+    x = rng.standard_normal(n).astype(np.float32) * np.float32(scale)
+    x[rng.integers(0, n, size=max(1, n // 97))] *= np.float32(7.5)
+    return x

@@ -129,7 +129,26 @@ int brrr_debug_stamps(brrr_model *m, long long *out256);
  * Replaces qblock32 / quant_i8 (src/bin/engine_gpt2.rs:689-699; src/bin/engine.rs:264-279). */
 int brrr_quant_q8(const float *d_x, int n, int8_t *d_q, float *d_s, void *stream);
 
-/* RMSNorm then the quantiser above; d_xn (nullable) receives the normalised floats.
+/* Q8_K activation quantiser of the qwen3moe engine: one scale per 256 values
+ * (max(1e-12, amax)/127), int8 quants rounded half away from zero, and the int32 sum of every 32
+ * quants (d_bsum [n/32]).  n % 256 == 0; d_x 16-byte, d_q 8-byte aligned.
+ * Replaces qblock (src/bin/engine_qwen2.rs:287-300). */
+int brrr_quant_q8k(const float *d_x, int n, int8_t *d_q, float *d_s, int32_t *d_bsum, void *stream);
+
+/* y[r] = Q4_K row r . Q8_K activation, rows in the GGUF Q4_K byte layout (144 bytes per 256
+ * values, rows contiguous).  d_sbdots (nullable) receives the exact integers of every superblock
+ * as [rows][cols/256][2] = {scaled quant sum, min sum}.  cols % 256 == 0; d_w and d_xq 4-byte
+ * aligned.  Replaces q4k_dot (src/bin/engine_qwen2.rs:84-114). */
+int brrr_q4k_matvec(const uint8_t *d_w, int rows, int cols, const int8_t *d_xq, const float *d_ys, const int32_t *d_bsum,
+                    float *d_y, int32_t *d_sbdots, void *stream);
+
+/* y[r] = Q6_K row r . Q8_K activation, rows in the GGUF Q6_K byte layout (210 bytes per 256
+ * values).  d_sbdots (nullable): [rows][cols/256] integer accumulators.  d_w and d_xq 2-byte
+ * aligned.  Replaces q6k_dot (src/bin/engine_qwen2.rs:164-200). */
+int brrr_q6k_matvec(const uint8_t *d_w, int rows, int cols, const int8_t *d_xq, const float *d_ys, float *d_y,
+                    int32_t *d_sbdots, void *stream);
+
+/* RMSNorm then brrr_quant_q8; d_xn (nullable) receives the normalised floats.
  * Replaces ssq + rmsnorm_quant_par (src/bin/engine_gpt2.rs:709-738). */
 int brrr_rmsnorm_quant(const float *d_x, const float *d_w, float eps, int n, float *d_xn, int8_t *d_q, float *d_s, void *stream);
 

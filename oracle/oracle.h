@@ -60,6 +60,40 @@ void orc_moe_ffn_step(const orc_cfg *c, const float *xn, const float *ginp, cons
                       const float *gate_b, const float *up_b, const float *down_b,
                       float *x_io, int32_t *top_out, float *wts_out);
 
+/* ---- qwen3moe kernels (src/bin/engine_qwen2.rs) ---- */
+float orc_half_to_f32(uint16_t h);
+void orc_scale_min_k4(int j, const uint8_t *q, uint8_t *sc, uint8_t *mn);
+void orc_qblock_q8k(const float *xn, int8_t *xq, float *ys, int32_t *xsum, int sb);
+void orc_quant_q8k(const float *x, int n, int8_t *q, float *s, int32_t *bsum);
+float orc_q4k_dot(const uint8_t *row, const int8_t *xq, const float *ys, const int32_t *xsum32, int cols, int32_t *dbg);
+float orc_q6k_dot(const uint8_t *row, const int8_t *xq, const float *ys, int cols, int32_t *dbg);
+void orc_q4k_matvec(const uint8_t *w, int rows, int cols, const int8_t *xq, const float *ys, const int32_t *xsum, float *y, int32_t *dbg);
+void orc_q6k_matvec(const uint8_t *w, int rows, int cols, const int8_t *xq, const float *ys, float *y, int32_t *dbg);
+
+/* ---- qwen3moe model (oracle_qwen_model.c) ---- */
+typedef struct {
+    int32_t d, nh, nkv, hd, nl, ne, topk, ff, nvocab;
+    float rope_base, rms_eps;
+} orcq_cfg;
+typedef struct orcq_model orcq_model;
+orcq_model *orcq_open_dir(const char *dir, const char *blob);
+orcq_model *orcq_open_synth(const orcq_cfg *c, uint64_t seed);
+void orcq_close(orcq_model *m);
+void orcq_get_cfg(const orcq_model *m, orcq_cfg *out);
+/* == run(tok, pos) of engine_qwen2.rs:587; the head runs (and the greedy token returns) when want != 0 */
+uint32_t orcq_forward(orcq_model *m, uint32_t tok, uint32_t pos, int want);
+const float *orcq_logits(const orcq_model *m);
+const float *orcq_hidden(const orcq_model *m);
+void orcq_set_trace(orcq_model *m, float *buf);   /* [(nl+1)][d] */
+const uint8_t *orcq_layer_k(const orcq_model *m, int il, int which, uint32_t *type, int *rows, int *cols);
+const float *orcq_layer_f32(const orcq_model *m, int il, int kind);
+void orcq_rope_table(const orcq_cfg *c, float *tab /* [MAXSEQ][hd/2][2] */);
+void orcq_rmsnorm(const float *x, const float *w, float eps, int d, float *out);
+void orcq_head_norm_rope(float *v, const float *w, int hd, int pos, float eps, const float *tab);
+void orcq_attn_head(const float *qh, const float *kcl, const float *vcl, int nkv, int hd, int kvh, int pos, float *sc, float *aop);
+void orcq_router_topk(const float *w, const float *xn, int ne, int d, int topk, float *logits, int32_t *top, float *wts);
+void orcq_embed_row(const uint8_t *row, int d, float *x);
+
 /* ---- model ---- */
 orc_model *orc_open_dir(const char *dir, const char *blob);
 orc_model *orc_open_synth(const orc_cfg *c, uint64_t seed);

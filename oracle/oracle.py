@@ -21,6 +21,37 @@ def build(force=False):
     return _SO
 
 
+_REF_SO = os.path.join(_HERE, "_ref", "libref_kq.so")
+_REF_SRC = "/root/reference/metal/engine_metal.m"
+
+
+def build_ref():
+    """Build oracle/_ref/libref_kq.so (the reference's own scalar C Q4_K/Q6_K dots) when the reference
+    checkout is present; returns the path, or None when neither the checkout nor a prebuilt file exists."""
+    if os.path.exists(_REF_SRC):
+        subprocess.run(["make", "-s", "-C", _HERE, "ref"], check=True)
+    return _REF_SO if os.path.exists(_REF_SO) else None
+
+
+_ref = None
+
+
+def ref_kq():
+    """ctypes handle of the reference-built dots, or None when unavailable."""
+    global _ref
+    if _ref is None:
+        so = build_ref()
+        if so is None:
+            return None
+        L = C.CDLL(so)
+        L.refkq_q4k_dot.restype = C.c_float
+        L.refkq_q6k_dot.restype = C.c_float
+        L.refkq_half2f.restype = C.c_float
+        L.refkq_half2f.argtypes = [C.c_uint16]
+        _ref = L
+    return _ref
+
+
 class Cfg(C.Structure):
     _fields_ = [(n, C.c_int32) for n in ("d", "nh", "nkv", "hd", "nl", "ne", "topk", "nvocab", "swa")] + [
         ("rope_base", C.c_float), ("rms_eps", C.c_float)]
@@ -47,6 +78,10 @@ def lib():
         L.orc_expf_c.argtypes = [C.c_float]
         L.orc_ssq.restype = C.c_float
         L.orc_dot_q8_i8.restype = C.c_float
+        L.orc_half_to_f32.restype = C.c_float
+        L.orc_half_to_f32.argtypes = [C.c_uint16]
+        L.orc_q4k_dot.restype = C.c_float
+        L.orc_q6k_dot.restype = C.c_float
         L.orc_open_dir.restype = C.c_void_p
         L.orc_open_dir.argtypes = [C.c_char_p, C.c_char_p]
         L.orc_open_synth.restype = C.c_void_p
@@ -175,6 +210,36 @@ def attn_head(q, kc, vc, nkv, hd, kvh, start, pos, sink):
     lib().orc_attn_head(_p(q), _p(kc), _p(vc), C.c_int(nkv), C.c_int(hd), C.c_int(kvh), C.c_int(start), C.c_int(pos),
                         C.c_float(sink), _p(sc), _p(ao))
     return ao
+
+
+def half_to_f32(h):
+    return np.float32(lib().orc_half_to_f32(int(h)))
+
+
+def quant_q8k(x):
+    """Q8_K activation quantiser: int8 quants, one f32 scale per 256, int32 sums per 32."""
+    x = _c(x, np.float32)
+    q = np.empty(x.size, np.int8); s = np.empty(x.size // 256, np.float32); bs = np.empty(x.size // 32, np.int32)
+    lib().orc_quant_q8k(_p(x), C.c_int(x.size), _p(q), _p(s), _p(bs))
+    return q, s, bs
+
+
+def q4k_matvec(w, rows, cols, xq, ys, bsum, want_dbg=False):
+    w = _c(w, np.uint8); xq = _c(xq, np.int8); ys = _c(ys, np.float32); bsum = _c(bsum, np.int32)
+    assert w.size == rows * (cols // 256) * 144
+    y = np.empty(rows, np.float32)
+    dbg = np.empty((rows, cols // 256, 2), np.int32) if want_dbg else None
+    lib().orc_q4k_matvec(_p(w), C.c_int(rows), C.c_int(cols), _p(xq), _p(ys), _p(bsum), _p(y), _p(dbg))
+    return (y, dbg) if want_dbg else y
+
+
+def q6k_matvec(w, rows, cols, xq, ys, want_dbg=False):
+    w = _c(w, np.uint8); xq = _c(xq, np.int8); ys = _c(ys, np.float32)
+    assert w.size == rows * (cols // 256) * 210
+    y = np.empty(rows, np.float32)
+    dbg = np.empty((rows, cols // 256), np.int32) if want_dbg else None
+    lib().orc_q6k_matvec(_p(w), C.c_int(rows), C.c_int(cols), _p(xq), _p(ys), _p(y), _p(dbg))
+    return (y, dbg) if want_dbg else y
 
 
 def synth_prompt(seed, n, bound):

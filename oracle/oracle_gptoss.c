@@ -1,17 +1,13 @@
 /* TEST INFRASTRUCTURE — CPU oracle: gpt-oss model container, loaders and the single-token
  * forward pass, restating src/bin/engine_gpt2.rs (load: 1276-1315; forward_worker: 751-934;
  * head semantics: full-Q8 argmax, first strict maximum, as in sample_logits 95-100). */
-#define _GNU_SOURCE
+#include "oracle_src.h"
 #include "oracle.h"
 #include "oracle_math.h"
 #include "../cpubrrr_b200/csrc/brrr_synth.h"
 #include <stdio.h>
 #include <stdlib.h>
 #include <float.h>
-#include <fcntl.h>
-#include <unistd.h>
-#include <sys/mman.h>
-#include <sys/stat.h>
 
 typedef struct {
     float *attn_norm, *ffn_norm;
@@ -36,13 +32,7 @@ struct orc_model {
 };
 
 /* ------------------------------------------------------------------ tensor sources */
-typedef struct {
-    int synth;
-    uint64_t seed;
-    /* file source */
-    uint8_t *blob; size_t blob_len;
-    char **names; uint32_t *types; size_t *offs; size_t *nel; int nt;
-} source;
+typedef orc_source source;
 
 static const char *kind_name(int kind) {
     switch (kind) {
@@ -62,20 +52,17 @@ static const char *kind_name(int kind) {
     return "?";
 }
 
-static void die(const char *msg, const char *arg) { fprintf(stderr, "oracle: %s %s\n", msg, arg ? arg : ""); abort(); }
+#define die orc_die
 
 static const uint8_t *file_tensor(const source *s, int layer, int kind, uint32_t want_type, size_t nel) {
     char name[128];
     if (layer == (int)BRRR_L_GLOBAL) snprintf(name, sizeof name, "%s", kind_name(kind));
     else snprintf(name, sizeof name, "blk.%d.%s", layer, kind_name(kind));
-    for (int i = 0; i < s->nt; i++)
-        if (!strcmp(s->names[i], name)) {
-            if (s->types[i] != want_type) die("tensor type mismatch", name);
-            if (s->nel[i] != nel) die("tensor size mismatch", name);
-            return s->blob + s->offs[i];
-        }
-    die("missing tensor", name);
-    return NULL;
+    uint32_t ty; size_t n;
+    const uint8_t *p = orc_source_find(s, name, &ty, &n);
+    if (ty != want_type) die("tensor type mismatch", name);
+    if (n != nel) die("tensor size mismatch", name);
+    return p;
 }
 
 /* f32 tensor: synthetic mean/sigma follow the seeded-input recipe: norms 1+N(0,.02), sinks N(0,1),
@@ -197,30 +184,10 @@ orc_model *orc_open_dir(const char *dir, const char *blobp) {
     fclose(f);
     if (ffexp != c.d) die("engine assumes expert ff dim == d", NULL);   /* engine_gpt2.rs:73 */
     if (c.hd != 64) die("attention kernels assume hd=64", NULL);        /* engine_gpt2.rs:74 */
-    source s = {0};
-    int fd = open(blobp, O_RDONLY);
-    if (fd < 0) die("cannot open", blobp);
-    struct stat st; fstat(fd, &st);
-    s.blob_len = st.st_size;
-    s.blob = mmap(NULL, s.blob_len, PROT_READ, MAP_PRIVATE, fd, 0);
-    close(fd);
-    snprintf(path, sizeof path, "%s/manifest.txt", dir);
-    f = fopen(path, "r");
-    if (!f) die("cannot open", path);
-    size_t data_start = 0;
-    if (fscanf(f, "%127s %zu", key, &data_start) != 2) die("bad manifest", path);
-    int cap = 1024;
-    s.names = malloc(sizeof(char *) * cap); s.types = malloc(4 * cap); s.offs = malloc(sizeof(size_t) * cap); s.nel = malloc(sizeof(size_t) * cap);
-    char nm[256]; unsigned ty; size_t off, nel;
-    while (fscanf(f, "%255s %u %zu %zu", nm, &ty, &off, &nel) == 4) {
-        if (s.nt == cap) { cap *= 2; s.names = realloc(s.names, sizeof(char *) * cap); s.types = realloc(s.types, 4 * cap); s.offs = realloc(s.offs, sizeof(size_t) * cap); s.nel = realloc(s.nel, sizeof(size_t) * cap); }
-        s.names[s.nt] = strdup(nm); s.types[s.nt] = ty; s.offs[s.nt] = data_start + off; s.nel[s.nt] = nel; s.nt++;
-    }
-    fclose(f);
+    source s;
+    orc_source_open(&s, dir, blobp);
     orc_model *m = build(&c, &s);
-    munmap(s.blob, s.blob_len);
-    for (int i = 0; i < s.nt; i++) free(s.names[i]);
-    free(s.names); free(s.types); free(s.offs); free(s.nel);
+    orc_source_close(&s);
     return m;
 }
 
