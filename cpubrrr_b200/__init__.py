@@ -4,5 +4,6 @@ The package is a thin host-side mirror of the reference engine's interface over 
 libbrrr.so (include/brrr.h).  All computation runs in hand-written sm_100a CUDA kernels; there is
 no CPU fallback: importing `cpubrrr_b200.lib()` without the built library raises.
 """
-from ._lib import lib, BrrrError, Cfg, LIB_PATH  # noqa: F401
+from ._lib import lib, BrrrError, Cfg, QwenCfg, LIB_PATH  # noqa: F401
 from .engine import Engine, gptoss_20b_cfg, make_cfg  # noqa: F401
+from .qwen import QwenEngine, make_qwen_cfg, qwen3_30b_a3b_cfg  # noqa: F401

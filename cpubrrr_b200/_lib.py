@@ -17,6 +17,13 @@ class Cfg(C.Structure):
         ("rope_freq_base", C.c_float), ("rms_eps", C.c_float)]
 
 
+class QwenCfg(C.Structure):
+    """brrr_qwen_cfg: config.txt keys of the qwen3moe engine."""
+    _fields_ = [(n, C.c_int32) for n in ("n_embd", "n_layer", "n_head", "n_head_kv", "head_dim", "n_expert",
+                                         "n_expert_used", "n_ff_exp", "n_vocab")] + [
+        ("rope_freq_base", C.c_float), ("rms_eps", C.c_float)]
+
+
 _P = C.c_void_p
 _I = C.c_int
 # name -> (restype, argtypes); the authoritative list of exported entry points
@@ -43,6 +50,18 @@ SIGNATURES = {
     "brrr_stage_name": (C.c_char_p, [_I]),
     "brrr_stage_time": (_I, [_P, _I, C.c_uint32, _I, C.POINTER(C.c_float), C.POINTER(C.c_uint64), C.POINTER(_I)]),
     "brrr_debug_stamps": (_I, [_P, _P]),
+    "brrr_qwen_open": (_I, [C.c_char_p, C.c_char_p, _I, C.POINTER(_P)]),
+    "brrr_qwen_open_synth": (_I, [C.POINTER(QwenCfg), C.c_uint64, _I, C.POINTER(_P)]),
+    "brrr_qwen_cfg_get": (_I, [_P, C.POINTER(QwenCfg)]),
+    "brrr_qwen_close": (None, [_P]),
+    "brrr_qwen_forward": (_I, [_P, C.c_uint32, C.c_uint32, _I, C.POINTER(C.c_uint32)]),
+    "brrr_qwen_decode": (_I, [_P, C.c_uint32, C.c_uint32, C.c_uint32, _P]),
+    "brrr_qwen_logits": (_I, [_P, _P]),
+    "brrr_qwen_hidden": (_I, [_P, _P]),
+    "brrr_qwen_forward_trace": (_I, [_P, C.c_uint32, C.c_uint32, _P]),
+    "brrr_qwen_stream": (_P, [_P]),
+    "brrr_qwen_launches_per_step": (_I, [_P, _I]),
+    "brrr_qwen_bytes_per_step": (C.c_uint64, [_P, C.c_uint32]),
     "brrr_quant_q8": (_I, [_P, _I, _P, _P, _P]),
     "brrr_quant_q8k": (_I, [_P, _I, _P, _P, _P, _P]),
     "brrr_q4k_matvec": (_I, [_P, _I, _I, _P, _P, _P, _P, _P, _P]),

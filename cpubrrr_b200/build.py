@@ -17,7 +17,7 @@ CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "_obj")
 LIB = os.path.join(HERE, "libbrrr.so")
 
-SOURCES = ["kernels_small.cu", "kernels_q8.cu", "kernels_mx.cu", "kernels_router.cu", "kernels_attn.cu", "kernels_kq.cu",
+SOURCES = ["kernels_small.cu", "kernels_q8.cu", "kernels_mx.cu", "kernels_router.cu", "kernels_attn.cu", "kernels_kq.cu", "kernels_qwen.cu", "qwen_model.cu",
            "model.cu", "capi_stage.cu", "capi_noalloc.cu"]
 
 NVCC_FLAGS = [

@@ -21,6 +21,28 @@ void launch_q4k_matvec(const uint8_t *w, int rows, int cols, const int8_t *xq, c
                        int32_t *dbg, cudaStream_t st);
 void launch_q6k_matvec(const uint8_t *w, int rows, int cols, const int8_t *xq, const float *ys, float *y, int32_t *dbg, cudaStream_t st);
 
+// ---- qwen3moe decode kernels (kernels_qwen.cu); KMatDev is declared in brrr_kq.cuh
+struct KMatDev;
+cudaError_t launch_qw_embed(const uint8_t *embd_q4k, int d, const DevState *state, float *x, bool pdl, cudaStream_t st);
+cudaError_t launch_qw_norm_quant(const float *x, const float *w, float eps, int d, float *xn, int8_t *q, float *s, int32_t *bsum,
+                                 bool pdl, cudaStream_t st);
+cudaError_t launch_qw_quant(const float *x, int n, int8_t *q, float *s, int32_t *bsum, bool pdl, cudaStream_t st);
+// y_i = M_i . x for up to three stacked matrices (resid: y_i += M_i . x)
+cudaError_t launch_qw_matvec(const KMatDev *mats, float *const *ys_out, int n, bool resid, const int8_t *xq, const float *ys,
+                             const int32_t *bsum, bool pdl, cudaStream_t st);
+cudaError_t launch_qw_qknorm_rope(float *q, const float *k, const float *v, const float *q_norm, const float *k_norm, const float *rope,
+                                  float eps, int nh, int nkv, const DevState *state, int pos_val, float *kc, float *vc, bool pdl,
+                                  cudaStream_t st);
+cudaError_t launch_qw_attn(const float *q, const float *kc, const float *vc, int nh, int nkv, const DevState *state, int pos_val, float *ao,
+                           bool pdl, cudaStream_t st);
+cudaError_t launch_qw_gate_up(const KMatDev &gate, const KMatDev &up, const int32_t *top, int topk, int ff, const int8_t *xq, const float *ys,
+                              const int32_t *bsum, float *hbuf, bool pdl, cudaStream_t st);
+cudaError_t launch_qw_down(const KMatDev &down, const int32_t *top, const float *wts, int topk, int d, int ff, const int8_t *hq,
+                           const float *hs, const int32_t *hsum, float *x, bool pdl, cudaStream_t st);
+cudaError_t launch_qw_head(const KMatDev &head, const int8_t *xq, const float *ys, const int32_t *bsum, float *logits, DevState *state,
+                           bool pdl, cudaStream_t st);
+char *host_err_buf();   // thread-local text behind brrr_last_cuda_error (512 bytes)
+
 // ---- Q8 matrices (kernels_q8.cu)
 void launch_q8_pack(const uint16_t *w_bf16, int rows_src, int row0_dst, Q8Dev m, cudaStream_t st);
 void launch_q8_export(Q8Dev m, int8_t *q, float *s, cudaStream_t st);

@@ -104,13 +104,15 @@ BRRR_HD void brrr_synth_mxfp4_block(uint64_t key, uint64_t blk, uint8_t out[17])
 }
 
 /* One 144-byte GGUF Q4_K superblock (256 values): f16 d, f16 dmin, 12 bytes of packed 6-bit
- * scales/mins, 128 bytes of nibbles.  All bytes random; d is an f16 in [2^-13, 2^-12) and, for one
- * block in 16, an f16 subnormal; dmin is an f16 in [2^-11, 2^-9).  20 draws per block. */
+ * scales/mins, 128 bytes of nibbles.  Scales, mins and nibbles are uniform random bytes.  d is an
+ * f16 in [2^-13, 1.125 * 2^-13) and dmin an f16 in [7, 8) * 2^-13, so that the weights
+ * d*sc*q - dmin*mn are nearly zero-mean (E[q] = 7.5); one block in 16 has a subnormal d
+ * (m * 2^-24, m in 64..127) with dmin = 7.5 d, subnormal too.  20 draws per block. */
 BRRR_HD void brrr_synth_q4k_block(uint64_t key, uint64_t blk, uint8_t out[144]) {
     uint64_t h = brrr_draw(key, 20 * blk);
-    uint32_t mant = (uint32_t)(h & 0x3ffu), sub = ((h >> 10) & 15u) == 0;
-    uint16_t d = (uint16_t)((sub ? 0u : (2u << 10)) | (sub ? (mant | 0x200u) : mant));
-    uint16_t dmin = (uint16_t)(((4u + (uint32_t)((h >> 14) & 1u)) << 10) | (uint32_t)((h >> 16) & 0x3ffu));
+    uint32_t m7 = (uint32_t)(h & 0x7fu), sub = ((h >> 10) & 15u) == 0, m8 = (uint32_t)((h >> 16) & 0xffu);
+    uint16_t d = (uint16_t)(sub ? (64u + (m7 & 63u)) : ((2u << 10) | m7));
+    uint16_t dmin = (uint16_t)(sub ? ((64u + (m7 & 63u)) * 15u) >> 1 : ((4u << 10) | (768u + m8)));
     out[0] = (uint8_t)d; out[1] = (uint8_t)(d >> 8); out[2] = (uint8_t)dmin; out[3] = (uint8_t)(dmin >> 8);
     out[4] = (uint8_t)(h >> 32); out[5] = (uint8_t)(h >> 40); out[6] = (uint8_t)(h >> 48); out[7] = (uint8_t)(h >> 56);
     for (int j = 0; j < 17; j++) {

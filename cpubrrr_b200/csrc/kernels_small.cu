@@ -115,16 +115,36 @@ __global__ void synth_mxfp4_kernel(uint64_t key, uint64_t nblocks, uint8_t *out)
     }
 }
 
+__global__ void synth_q4k_kernel(uint64_t key, uint64_t nblocks, uint8_t *out) {
+    for (uint64_t b = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; b < nblocks; b += (uint64_t)gridDim.x * blockDim.x) {
+        uint8_t tmp[144];
+        brrr_synth_q4k_block(key, b, tmp);
+        uint32_t *dst = reinterpret_cast<uint32_t *>(out + b * 144);
+        for (int i = 0; i < 36; i++) dst[i] = tmp[4 * i] | (tmp[4 * i + 1] << 8) | (tmp[4 * i + 2] << 16) | ((uint32_t)tmp[4 * i + 3] << 24);
+    }
+}
+__global__ void synth_q6k_kernel(uint64_t key, uint64_t nblocks, uint8_t *out) {
+    for (uint64_t b = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; b < nblocks; b += (uint64_t)gridDim.x * blockDim.x) {
+        uint8_t tmp[210];
+        brrr_synth_q6k_block(key, b, tmp);
+        unsigned short *dst = reinterpret_cast<unsigned short *>(out + b * 210);
+        for (int i = 0; i < 105; i++) dst[i] = (unsigned short)(tmp[2 * i] | (tmp[2 * i + 1] << 8));
+    }
+}
+
 void launch_synth(uint64_t seed, uint32_t layer, uint32_t kind, uint32_t type, uint64_t nelems, void *out, cudaStream_t st) {
     uint64_t key = brrr_tensor_key(seed, layer, kind);
-    float mean = (kind == BRRR_T_ATTN_NORM || kind == BRRR_T_FFN_NORM || kind == BRRR_T_OUT_NORM) ? 1.0f : 0.0f;
+    float mean = (kind == BRRR_T_ATTN_NORM || kind == BRRR_T_FFN_NORM || kind == BRRR_T_OUT_NORM || kind == BRRR_T_Q_NORM ||
+                  kind == BRRR_T_K_NORM) ? 1.0f : 0.0f;
     float sigma = kind == BRRR_T_SINKS ? 1.0f : 0.02f;
-    uint64_t units = type == 39 ? nelems / 32 : nelems;
+    uint64_t units = type == 39 ? nelems / 32 : (type == 12 || type == 14) ? nelems / 256 : nelems;
     if (units == 0) return;
     unsigned grid = (unsigned)((units + 255) / 256 < 148 * 16 ? (units + 255) / 256 : 148 * 16);
     if (type == 0) synth_f32_kernel<<<grid, 256, 0, st>>>(key, nelems, mean, sigma, (float *)out);
     else if (type == 30) synth_bf16_kernel<<<grid, 256, 0, st>>>(key, nelems, sigma, (uint16_t *)out);
     else if (type == 39) synth_mxfp4_kernel<<<grid, 256, 0, st>>>(key, units, (uint8_t *)out);
+    else if (type == 12) synth_q4k_kernel<<<grid, 256, 0, st>>>(key, units, (uint8_t *)out);
+    else if (type == 14) synth_q6k_kernel<<<grid, 256, 0, st>>>(key, units, (uint8_t *)out);
 }
 
 }  // namespace brrr

@@ -36,6 +36,7 @@ static thread_local char g_cuda_err[512] = "";
     } while (0)
 
 extern "C" const char *brrr_last_cuda_error(void) { return g_cuda_err; }
+namespace brrr { char *host_err_buf() { return g_cuda_err; } }   // shared with the other model files (512 bytes)
 extern "C" const char *brrr_strerror(int s) {
     switch (s) {
     case BRRR_OK: return "ok";

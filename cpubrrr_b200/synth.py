@@ -54,7 +54,7 @@ def normal(key, n):
 
 
 def synth_f32(seed, layer, kind, n):
-    mean = np.float32(1.0 if kind in (T["ATTN_NORM"], T["FFN_NORM"], T["OUT_NORM"]) else 0.0)
+    mean = np.float32(1.0 if kind in (T["ATTN_NORM"], T["FFN_NORM"], T["OUT_NORM"], T["Q_NORM"], T["K_NORM"]) else 0.0)
     sigma = np.float32(1.0 if kind == T["SINKS"] else 0.02)
     z = normal(tensor_key(seed, layer, kind), n)
     return (z * sigma).astype(np.float32) + mean
@@ -86,10 +86,12 @@ def synth_q4k_blocks(seed, layer, kind, nblocks):
     key = tensor_key(seed, layer, kind)
     b = np.arange(nblocks, dtype=np.uint64) * np.uint64(20)
     h = draw(key, b)
-    mant = (h & np.uint64(0x3ff)).astype(np.uint32)
+    m7 = (h & np.uint64(0x7f)).astype(np.uint32)
     sub = ((h >> np.uint64(10)) & np.uint64(15)) == 0
-    d = np.where(sub, mant | np.uint32(0x200), np.uint32(2 << 10) | mant).astype(np.uint16)
-    dmin = (((np.uint64(4) + ((h >> np.uint64(14)) & np.uint64(1))) << np.uint64(10)) | ((h >> np.uint64(16)) & np.uint64(0x3ff))).astype(np.uint16)
+    m8 = ((h >> np.uint64(16)) & np.uint64(0xff)).astype(np.uint32)
+    dsub = np.uint32(64) + (m7 & np.uint32(63))
+    d = np.where(sub, dsub, np.uint32(2 << 10) | m7).astype(np.uint16)
+    dmin = np.where(sub, (dsub * np.uint32(15)) >> np.uint32(1), np.uint32(4 << 10) | (np.uint32(768) + m8)).astype(np.uint16)
     out = np.empty((nblocks, 144), np.uint8)
     out[:, 0:2] = d.view(np.uint8).reshape(nblocks, 2)
     out[:, 2:4] = dmin.view(np.uint8).reshape(nblocks, 2)
@@ -159,6 +161,39 @@ def model_tensors(cfg, seed):
     yield ("output.weight", GGML_BF16, [d, nv], synth_bf16(seed, L_GLOBAL, T["OUTPUT"], nv * d).tobytes())
 
 
+GGML_Q4_K, GGML_Q6_K = 12, 14
+
+
+def qwen_model_tensors(cfg, seed):
+    """(name, ggml type, dims, raw bytes) of a synthetic qwen3moe model, in the tensor names the
+    reference's loader looks up (src/bin/engine_qwen2.rs:528-541).  Down experts and the output head
+    are Q6_K, every other matrix Q4_K."""
+    d, nh, nkv, hd, ne, ff, nv = cfg.n_embd, cfg.n_head, cfg.n_head_kv, cfg.head_dim, cfg.n_expert, cfg.n_ff_exp, cfg.n_vocab
+
+    def k(name, layer, kind, rows, cols, dims):
+        if kind in ("DOWN", "OUTPUT"):
+            return (name, GGML_Q6_K, dims, synth_q6k_blocks(seed, layer, T[kind], rows * cols // 256).tobytes())
+        return (name, GGML_Q4_K, dims, synth_q4k_blocks(seed, layer, T[kind], rows * cols // 256).tobytes())
+
+    for il in range(cfg.n_layer):
+        p = f"blk.{il}."
+        yield (p + "attn_norm.weight", GGML_F32, [d], synth_f32(seed, il, T["ATTN_NORM"], d).tobytes())
+        yield (p + "ffn_norm.weight", GGML_F32, [d], synth_f32(seed, il, T["FFN_NORM"], d).tobytes())
+        yield (p + "attn_q_norm.weight", GGML_F32, [hd], synth_f32(seed, il, T["Q_NORM"], hd).tobytes())
+        yield (p + "attn_k_norm.weight", GGML_F32, [hd], synth_f32(seed, il, T["K_NORM"], hd).tobytes())
+        yield k(p + "attn_q.weight", il, "WQ", nh * hd, d, [d, nh * hd])
+        yield k(p + "attn_k.weight", il, "WK", nkv * hd, d, [d, nkv * hd])
+        yield k(p + "attn_v.weight", il, "WV", nkv * hd, d, [d, nkv * hd])
+        yield k(p + "attn_output.weight", il, "WO", d, nh * hd, [nh * hd, d])
+        yield (p + "ffn_gate_inp.weight", GGML_F32, [d, ne], synth_f32(seed, il, T["ROUTER_W"], ne * d).tobytes())
+        yield k(p + "ffn_gate_exps.weight", il, "GATE", ne * ff, d, [d, ff, ne])
+        yield k(p + "ffn_up_exps.weight", il, "UP", ne * ff, d, [d, ff, ne])
+        yield k(p + "ffn_down_exps.weight", il, "DOWN", ne * d, ff, [ff, d, ne])
+    yield k("token_embd.weight", L_GLOBAL, "TOK_EMBD", nv, d, [d, nv])
+    yield ("output_norm.weight", GGML_F32, [d], synth_f32(seed, L_GLOBAL, T["OUT_NORM"], d).tobytes())
+    yield k("output.weight", L_GLOBAL, "OUTPUT", nv, d, [d, nv])
+
+
 def _gguf_str(s):
     b = s.encode() if isinstance(s, str) else s
     return struct.pack("<Q", len(b)) + b
@@ -183,7 +218,8 @@ def write_gguf(path, cfg, seed, tokens=None, arch="gpt-oss"):
     kv_u32(f"{arch}.expert_count", cfg.n_expert)
     kv_u32(f"{arch}.expert_used_count", cfg.n_expert_used)
     kv_u32(f"{arch}.expert_feed_forward_length", cfg.n_ff_exp)
-    kv_u32(f"{arch}.attention.sliding_window", cfg.sliding_window)
+    if hasattr(cfg, "sliding_window"):
+        kv_u32(f"{arch}.attention.sliding_window", cfg.sliding_window)
     kv_f32(f"{arch}.rope.freq_base", cfg.rope_freq_base)
     kv_f32(f"{arch}.attention.layer_norm_rms_epsilon", cfg.rms_eps)
     kv_u32(f"{arch}.vocab_size", cfg.n_vocab)
@@ -193,7 +229,7 @@ def write_gguf(path, cfg, seed, tokens=None, arch="gpt-oss"):
     arr = struct.pack("<IQ", 8, len(tokens)) + b"".join(_gguf_str(t) for t in tokens)
     kv.append(_gguf_str("tokenizer.ggml.tokens") + struct.pack("<I", 9) + arr)
 
-    tensors = list(model_tensors(cfg, seed))
+    tensors = list(qwen_model_tensors(cfg, seed) if arch == "qwen3moe" else model_tensors(cfg, seed))
     infos, off = [], 0
     for name, ty, dims, raw in tensors:
         infos.append(_gguf_str(name) + struct.pack("<I", len(dims)) + struct.pack(f"<{len(dims)}Q", *dims) + struct.pack("<IQ", ty, off))
@@ -349,11 +385,11 @@ def write_data_dir(out_dir, blob_path):
     return cfg
 
 
-def write_synth_model(out_dir, cfg, seed):
+def write_synth_model(out_dir, cfg, seed, arch="gpt-oss"):
     """GGUF blob + data directory for a synthetic model; returns (data_dir, blob_path)."""
     os.makedirs(out_dir, exist_ok=True)
     blob = os.path.join(out_dir, "model.gguf")
-    write_gguf(blob, cfg, seed)
+    write_gguf(blob, cfg, seed, arch=arch)
     write_data_dir(out_dir, blob)
     return out_dir, blob
 

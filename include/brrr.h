@@ -122,6 +122,43 @@ int brrr_stage_time(brrr_model *m, int stage, uint32_t pos, int reps, float *ms_
  * library was built with -DBRRR_TIMELINE.  No counterpart in the reference. */
 int brrr_debug_stamps(brrr_model *m, long long *out256);
 
+/* ---------------------------------------------------------------- qwen3moe engine
+ * The reference's second engine binary (src/bin/engine_qwen2.rs): Qwen3-MoE models with Q4_K / Q6_K
+ * weights used straight in the GGUF byte layout, Q8_K activations, QK-norm, NeoX RoPE, full
+ * causal attention (head_dim 128), top-k-of-n experts with SiLU-GLU.  Same conventions as the
+ * brrr_model_* functions above. */
+typedef struct brrr_qwen_cfg {          /* config.txt keys, src/bin/engine_qwen2.rs:27-38 */
+    int32_t n_embd, n_layer, n_head, n_head_kv, head_dim;
+    int32_t n_expert, n_expert_used, n_ff_exp, n_vocab;
+    float rope_freq_base, rms_eps;
+} brrr_qwen_cfg;
+typedef struct brrr_qwen brrr_qwen;
+
+/* Load from a data directory and its GGUF blob.  Replaces load_cfg and the loader in main
+ * (src/bin/engine_qwen2.rs:27-38, 512-545); token_embd must be Q4_K, matrices Q4_K or Q6_K. */
+int brrr_qwen_open(const char *data_dir, const char *blob_path, int device, brrr_qwen **out);
+/* Seeded synthetic model generated on the device in the GGUF formats (down experts and the output
+ * head Q6_K, every other matrix Q4_K).  No counterpart in the reference. */
+int brrr_qwen_open_synth(const brrr_qwen_cfg *cfg, uint64_t seed, int device, brrr_qwen **out);
+int brrr_qwen_cfg_get(const brrr_qwen *m, brrr_qwen_cfg *out);
+void brrr_qwen_close(brrr_qwen *m);
+/* One token at position pos; with want_logits != 0 the vocabulary projection runs and *out_tok is
+ * the greedy token (first strict maximum).  Replaces run(t, pos) and the worker pool
+ * (src/bin/engine_qwen2.rs:302-451, 571-595). */
+int brrr_qwen_forward(brrr_qwen *m, uint32_t tok, uint32_t pos, int want_logits, uint32_t *out_tok);
+/* n greedy steps starting from first_tok at position pos with the token fed back on the device;
+ * out_toks[i] is the token produced by step i.  Replaces the decode loop of generate
+ * (src/bin/engine_qwen2.rs:613-619) without its stop test. */
+int brrr_qwen_decode(brrr_qwen *m, uint32_t first_tok, uint32_t pos, uint32_t n, uint32_t *out_toks);
+int brrr_qwen_logits(brrr_qwen *m, float *out);               /* [n_vocab], of the last want_logits step */
+int brrr_qwen_hidden(brrr_qwen *m, float *out);               /* [n_embd], residual stream after the last step */
+/* One step run kernel by kernel, recording the residual stream after the embedding and after each
+ * layer: trace is host memory [(n_layer + 1)][n_embd]. */
+int brrr_qwen_forward_trace(brrr_qwen *m, uint32_t tok, uint32_t pos, float *trace);
+void *brrr_qwen_stream(brrr_qwen *m);
+int brrr_qwen_launches_per_step(const brrr_qwen *m, int want_logits);
+uint64_t brrr_qwen_bytes_per_step(const brrr_qwen *m, uint32_t pos);
+
 /* ---------------------------------------------------------------- stage-level entry points
  * Device pointers in, device pointers out.  They launch the same kernels the forward pass uses. */
 
@@ -212,7 +249,7 @@ int brrr_rope_table(const brrr_cfg *cfg, float *out);
 int brrr_moe_ffn_step(brrr_model *m, int il, const float *d_xn, float *d_x, int32_t *d_top, float *d_wts);
 
 /* Fill a device buffer with a synthetic tensor in its GGUF format (type 0 = f32, 30 = bf16,
- * 39 = MXFP4; nelems counts values). Same generator brrr_model_open_synth uses. */
+ * 39 = MXFP4, 12 = Q4_K, 14 = Q6_K; nelems counts values). Same generator brrr_model_open_synth uses. */
 int brrr_synth_tensor(uint64_t seed, uint32_t layer, uint32_t kind, uint32_t type, uint64_t nelems, void *d_out, void *stream);
 
 /* exp as the engine defines it (fixed IEEE sequence); d_y[i] = exp(d_x[i]). */

@@ -310,3 +310,97 @@ class Model:
             self.close()
         except Exception:
             pass
+
+
+# ---- qwen3moe model ---------------------------------------------------------------------------
+
+class QCfg(C.Structure):
+    _fields_ = [(n, C.c_int32) for n in ("d", "nh", "nkv", "hd", "nl", "ne", "topk", "ff", "nvocab")] + [
+        ("rope_base", C.c_float), ("rms_eps", C.c_float)]
+
+
+def make_qcfg(d, nh, nkv, hd, nl, ne, topk, ff, nvocab, rope_base=1000000.0, rms_eps=1e-6):
+    return QCfg(d, nh, nkv, hd, nl, ne, topk, ff, nvocab, rope_base, rms_eps)
+
+
+_qready = False
+
+
+def _qlib():
+    global _qready
+    L = lib()
+    if not _qready:
+        L.orcq_open_dir.restype = C.c_void_p
+        L.orcq_open_dir.argtypes = [C.c_char_p, C.c_char_p]
+        L.orcq_open_synth.restype = C.c_void_p
+        L.orcq_open_synth.argtypes = [C.POINTER(QCfg), C.c_uint64]
+        L.orcq_close.argtypes = [C.c_void_p]
+        L.orcq_get_cfg.argtypes = [C.c_void_p, C.POINTER(QCfg)]
+        L.orcq_forward.restype = C.c_uint32
+        L.orcq_forward.argtypes = [C.c_void_p, C.c_uint32, C.c_uint32, C.c_int]
+        L.orcq_logits.restype = C.POINTER(C.c_float)
+        L.orcq_logits.argtypes = [C.c_void_p]
+        L.orcq_hidden.restype = C.POINTER(C.c_float)
+        L.orcq_hidden.argtypes = [C.c_void_p]
+        L.orcq_set_trace.argtypes = [C.c_void_p, C.c_void_p]
+        L.orcq_layer_k.restype = C.POINTER(C.c_uint8)
+        L.orcq_layer_k.argtypes = [C.c_void_p, C.c_int, C.c_int, C.POINTER(C.c_uint32), C.POINTER(C.c_int), C.POINTER(C.c_int)]
+        L.orcq_layer_f32.restype = C.POINTER(C.c_float)
+        L.orcq_layer_f32.argtypes = [C.c_void_p, C.c_int, C.c_int]
+        _qready = True
+    return L
+
+
+class QwenModel:
+    """The oracle's qwen3moe model: run(tok, pos, want) as the reference's run closure."""
+
+    def __init__(self, handle):
+        if not handle:
+            raise RuntimeError("oracle qwen model failed to open")
+        self.h = handle
+        self.cfg = QCfg()
+        _qlib().orcq_get_cfg(self.h, C.byref(self.cfg))
+        self._trace = None
+
+    @classmethod
+    def synth(cls, cfg, seed):
+        return cls(_qlib().orcq_open_synth(C.byref(cfg), C.c_uint64(seed)))
+
+    @classmethod
+    def open(cls, data_dir, blob):
+        return cls(_qlib().orcq_open_dir(data_dir.encode(), blob.encode()))
+
+    def run(self, tok, pos, want=True):
+        return int(_qlib().orcq_forward(self.h, int(tok), int(pos), int(bool(want))))
+
+    def logits(self):
+        return np.ctypeslib.as_array(_qlib().orcq_logits(self.h), shape=(self.cfg.nvocab,)).copy()
+
+    def hidden(self):
+        return np.ctypeslib.as_array(_qlib().orcq_hidden(self.h), shape=(self.cfg.d,)).copy()
+
+    def enable_trace(self):
+        self._trace = np.zeros((self.cfg.nl + 1, self.cfg.d), np.float32)
+        _qlib().orcq_set_trace(self.h, _p(self._trace))
+        return self._trace
+
+    def layer_k(self, il, which):
+        """Raw K-quant bytes of a matrix: (uint8 array, ggml type, rows, cols)."""
+        ty = C.c_uint32(); rows = C.c_int(); cols = C.c_int()
+        p = _qlib().orcq_layer_k(self.h, il, which, C.byref(ty), C.byref(rows), C.byref(cols))
+        n = rows.value * (cols.value // 256) * (144 if ty.value == 12 else 210)
+        return np.ctypeslib.as_array(p, shape=(n,)), ty.value, rows.value, cols.value
+
+    def layer_f32(self, il, kind, n):
+        return np.ctypeslib.as_array(_qlib().orcq_layer_f32(self.h, il, kind), shape=(n,))
+
+    def close(self):
+        if self.h:
+            _qlib().orcq_close(self.h)
+            self.h = None
+
+    def __del__(self):
+        try:
+            self.close()
+        except Exception:
+            pass

@@ -128,3 +128,62 @@ def test_dots_against_gguf_dequantiser(orc, kind):
     assert np.linalg.norm(y - full) / np.linalg.norm(full) < 2e-2
     assert np.max(np.abs(y - exact)) / np.max(np.abs(exact)) < 1e-3
     assert dbg.dtype == np.int32
+
+
+# ---- the oracle's qwen3moe forward pass ---------------------------------------------------------
+QGOLD = json.load(open(os.path.join(HERE, "golden", "qwen_tiny_tokens.json")))
+
+
+def _greedy(m, prompt, n):
+    tok = 0
+    for i, t in enumerate(prompt):
+        tok = m.run(t, i, i == len(prompt) - 1)
+    out, pos = [], len(prompt)
+    for _ in range(n):
+        out.append(tok)
+        tok = m.run(tok, pos, True)
+        pos += 1
+    return out
+
+
+def test_qwen_golden_tokens(orc):
+    g = QGOLD
+    m = orc.QwenModel.synth(orc.make_qcfg(**g["cfg"]), g["seed"])
+    assert _greedy(m, g["prompt"], len(g["tokens"])) == g["tokens"]
+    assert [int(b) for b in m.logits()[:8].view(np.uint32)] == g["last_logit_bits"]
+
+
+def test_qwen_data_dir_equals_synth(orc, tmp_path):
+    """The file-loading path (GGUF blob + config.txt + manifest.txt in the reference's formats)
+    gives the same model as the in-memory generator: same tensors, same tokens."""
+    from cpubrrr_b200 import make_qwen_cfg
+    c = QGOLD["cfg"]
+    cfg = make_qwen_cfg(c["d"], c["nl"], c["nh"], c["nkv"], c["ne"], c["topk"], c["ff"], c["nvocab"])
+    d, blob = S.write_synth_model(str(tmp_path / "qw"), cfg, QGOLD["seed"], arch="qwen3moe")
+    text = open(os.path.join(d, "config.txt")).read()
+    assert "n_ff_exp 256" in text and "head_dim 128" in text
+    m = orc.QwenModel.open(d, blob)
+    assert m.cfg.ff == c["ff"] and m.cfg.nvocab == c["nvocab"]
+    assert _greedy(m, QGOLD["prompt"], 24) == QGOLD["tokens"][:24]
+
+
+def test_qwen_norm_and_router_pieces(orc):
+    """12-slice RMS norm against a float64 computation; router order on exact ties."""
+    L = orc.lib()
+    d = 2048
+    x = S.synth_activation(3, d, 2.0)
+    w = S.synth_f32(1, 0, S.T["ATTN_NORM"], d)
+    out = np.empty(d, np.float32)
+    L.orcq_rmsnorm(x.ctypes.data_as(C.c_void_p), w.ctypes.data_as(C.c_void_p), C.c_float(1e-6), d, out.ctypes.data_as(C.c_void_p))
+    ref = x.astype(np.float64) / np.sqrt((x.astype(np.float64) ** 2).mean() + 1e-6) * w
+    assert np.max(np.abs(out - ref)) < 1e-5 * np.max(np.abs(ref))
+    ne, k = 16, 4
+    W = np.zeros((ne, 256), np.float32)
+    W[3, 0] = W[9, 0] = 1.0
+    W[5, 0] = 2.0
+    xn = np.zeros(256, np.float32); xn[0] = 1.0
+    lg = np.empty(ne, np.float32); top = np.empty(k, np.int32); wts = np.empty(k, np.float32)
+    L.orcq_router_topk(W.ctypes.data_as(C.c_void_p), xn.ctypes.data_as(C.c_void_p), ne, 256, k, lg.ctypes.data_as(C.c_void_p),
+                       top.ctypes.data_as(C.c_void_p), wts.ctypes.data_as(C.c_void_p))
+    assert list(top) == [5, 3, 9, 0]           # value first, then the lower index among equals (stable sort)
+    assert abs(float(wts.sum()) - 1.0) < 1e-6 and wts[0] > wts[1] == wts[2] > wts[3]
