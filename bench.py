@@ -34,6 +34,29 @@ PROMPT_LEN = 73
 SEED = 2
 WORKLOAD = "gpt-oss-20b decode, 73-token prompt, batch 1, greedy"
 METRIC = "batch-1 decode tok/s (gpt-oss-20b shape, MXFP4)"
+ARCH = "24 layers, d 2880, 64/8 heads x 64, 32 experts top-4, vocab 201088"
+DTYPE = "int8xfp4->int32,f32"
+TOK_BOUND = 199999
+
+
+def use_qwen_workload():
+    """--workload qwen3-30b-a3b: the reference's second engine (qwen3moe, K-quants) instead of the
+    headline gpt-oss workload: 64-token prompt, then K decode steps."""
+    global PROMPT_LEN, SEED, WORKLOAD, METRIC, ARCH, DTYPE, TOK_BOUND
+    PROMPT_LEN, SEED = 64, 3
+    WORKLOAD = "Qwen3-30B-A3B (qwen3moe) decode, 64-token prompt, batch 1, greedy"
+    METRIC = "batch-1 decode tok/s (Qwen3-30B-A3B shape, Q4_K/Q6_K)"
+    ARCH = "48 layers, d 2048, 32/4 heads x 128, 128 experts top-8 x 768, vocab 151936"
+    DTYPE = "int8 x (4|6)-bit->int32,f32"
+    TOK_BOUND = 151936
+
+
+def oracle_model(qwen):
+    from oracle import oracle as O
+    O.build()
+    if qwen:
+        return O, O.QwenModel.synth(O.make_qcfg(2048, 32, 4, 128, 48, 128, 8, 768, 151936), SEED)
+    return O, O.Model.synth(O.make_cfg(d=2880, nh=64, nkv=8, hd=64, nl=24, ne=32, topk=4, nvocab=201088), SEED)
 
 
 def measured_peaks():
@@ -96,12 +119,9 @@ def run_reference(args, rank, world):
     """CPU arm: the oracle (a port of the reference's algorithm) on all host threads."""
     if rank != 0:
         return
-    from oracle import oracle as O
-    O.build()
     cores = os.cpu_count() or 1
-    cfg = O.make_cfg(d=2880, nh=64, nkv=8, hd=64, nl=24, ne=32, topk=4, nvocab=201088)
-    m = O.Model.synth(cfg, SEED)
-    prompt = O.synth_prompt(SEED, PROMPT_LEN, 199999)
+    O, m = oracle_model(args.workload != "gptoss20b")
+    prompt = O.synth_prompt(SEED, PROMPT_LEN, TOK_BOUND)
     tok = 0
     for i, t in enumerate(prompt):
         tok = m.run(int(t), i, i == len(prompt) - 1)
@@ -119,21 +139,18 @@ def run_reference(args, rank, world):
     sample = f"{steps} decode steps from position {PROMPT_LEN + warm} after a {PROMPT_LEN}-token prompt (full model)"
     print(json.dumps({
         "impl": "reference", "metric": METRIC, "value": v, "unit": "tok/s", "n_gpus": args.gpus, "steps": steps, "warmup": warm,
-        "ms_per_step": 1000.0 * dt / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8xfp4->int32,f32",
+        "ms_per_step": 1000.0 * dt / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": DTYPE,
         "data": "synthetic", "config": {"workload": WORKLOAD, "l2": "inputs larger than L2"},
         "cpu_baseline": {"value": v, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
         "e2e": {"value": v, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }), flush=True)
 
 
-def cpu_baseline_and_parity(eng_tokens, first_tok, nsteps):
+def cpu_baseline_and_parity(eng_tokens, first_tok, nsteps, qwen=False):
     """Rank 0, N = 1: time the oracle on a bounded sample of the same workload and use it as the
     checker of the GPU's first decoded tokens."""
-    from oracle import oracle as O
-    O.build()
-    cfg = O.make_cfg(d=2880, nh=64, nkv=8, hd=64, nl=24, ne=32, topk=4, nvocab=201088)
-    m = O.Model.synth(cfg, SEED)
-    prompt = O.synth_prompt(SEED, PROMPT_LEN, 199999)
+    O, m = oracle_model(qwen)
+    prompt = O.synth_prompt(SEED, PROMPT_LEN, TOK_BOUND)
     tok = 0
     for i, t in enumerate(prompt):
         tok = m.run(int(t), i, i == len(prompt) - 1)
@@ -160,9 +177,14 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline / parity leg")
     ap.add_argument("--no-stages", action="store_true", help="skip the per-kernel-class timing")
+    ap.add_argument("--workload", default="gptoss20b", choices=["gptoss20b", "qwen3-30b-a3b"],
+                    help="gptoss20b is the benchmark workload; qwen3-30b-a3b measures the reference's second engine")
     ap.add_argument("--layers", type=int, default=24, help="profiling aid: fewer layers (not the benchmark workload)")
     ap.add_argument("--vocab", type=int, default=201088, help="profiling aid: smaller vocabulary (not the benchmark workload)")
     args = ap.parse_args()
+    qwen = args.workload != "gptoss20b"
+    if qwen:
+        use_qwen_workload()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -185,11 +207,20 @@ def main():
 
     cfg = B.gptoss_20b_cfg()
     reduced = args.layers != 24 or args.vocab != 201088
-    if reduced:                                                 # small case for profiler captures only
-        cfg = B.make_cfg(2880, args.layers, 64, 8, 32, 4, args.vocab)
-        args.no_cpu = True
-    eng = B.Engine.synth(cfg, SEED, device=local_rank)
-    prompt = S.synth_prompt(SEED + rank, PROMPT_LEN, min(199999, args.vocab))   # every replica decodes its own sequence
+    if qwen:
+        full = B.qwen3_30b_a3b_cfg()
+        reduced = args.layers != 24                             # --layers N: small case for profiler captures only
+        cfg = B.make_qwen_cfg(2048, args.layers, 32, 4, 128, 8, 768, 151936) if reduced else full
+        args.no_cpu = args.no_cpu or reduced
+        args.no_stages = True
+        eng = B.QwenEngine.synth(cfg, SEED, device=local_rank)
+        prompt = S.synth_prompt(SEED + rank, PROMPT_LEN, TOK_BOUND)
+    else:
+        if reduced:                                             # small case for profiler captures only
+            cfg = B.make_cfg(2880, args.layers, 64, 8, 32, 4, args.vocab)
+            args.no_cpu = True
+        eng = B.Engine.synth(cfg, SEED, device=local_rank)
+        prompt = S.synth_prompt(SEED + rank, PROMPT_LEN, min(199999, args.vocab))   # every replica decodes its own sequence
     first = eng.prefill(prompt)
     stream = torch.cuda.ExternalStream(eng.stream, device=torch.device("cuda", local_rank))
 
@@ -253,10 +284,10 @@ def main():
     out = {
         "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": args.warmup,
         "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-        "dtype": "int8xfp4->int32,f32", "data": "synthetic",
-        "config": {"workload": WORKLOAD if not reduced else f"PROFILING CASE ({args.layers} layers, vocab {args.vocab}) - not the benchmark workload", "arch": "24 layers, d 2880, 64/8 heads x 64, 32 experts top-4, vocab 201088",
+        "dtype": DTYPE, "data": "synthetic",
+        "config": {"workload": WORKLOAD if not reduced else f"PROFILING CASE ({args.layers} layers, vocab {args.vocab}) - not the benchmark workload", "arch": ARCH,
                    "positions": [PROMPT_LEN, PROMPT_LEN + K], "parallelism": f"replicas x{world}" if world > 1 else "single GPU",
-                   "l2": "inputs larger than L2 (2.66 GB of weights streamed per step)"},
+                   "l2": f"inputs larger than L2 ({eng.bytes_per_step(PROMPT_LEN) / 1e9:.2f} GB of weights streamed per step)"},
         "e2e": {"value": world * K / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 4},
         "gpu_launches": K * eng.launches_per_step(True),
         "clocks": clocks,
@@ -280,7 +311,7 @@ def main():
                            "frac": top["gbs"] / peak, "traffic": ncu_traffic.get(top["kernel"]), "peak_kind": peak_kind,
                            "bytes_per_launch": top["bytes_per_launch"], "us_per_launch": top["us_per_launch"]}
     if world == 1 and not args.no_cpu:
-        cpu, parity = cpu_baseline_and_parity(toks, first, 16)
+        cpu, parity = cpu_baseline_and_parity(toks, first, 16, qwen)
         out["cpu_baseline"] = cpu
         out["parity"] = parity
     eng.close()

@@ -56,6 +56,8 @@ SIGNATURES = {
     "brrr_qwen_close": (None, [_P]),
     "brrr_qwen_forward": (_I, [_P, C.c_uint32, C.c_uint32, _I, C.POINTER(C.c_uint32)]),
     "brrr_qwen_decode": (_I, [_P, C.c_uint32, C.c_uint32, C.c_uint32, _P]),
+    "brrr_qwen_decode_enqueue": (_I, [_P, C.c_uint32, C.c_uint32, C.c_uint32]),
+    "brrr_qwen_decode_wait": (_I, [_P, C.c_uint32, _P]),
     "brrr_qwen_logits": (_I, [_P, _P]),
     "brrr_qwen_hidden": (_I, [_P, _P]),
     "brrr_qwen_forward_trace": (_I, [_P, C.c_uint32, C.c_uint32, _P]),

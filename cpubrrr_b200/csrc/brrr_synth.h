@@ -105,14 +105,15 @@ BRRR_HD void brrr_synth_mxfp4_block(uint64_t key, uint64_t blk, uint8_t out[17])
 
 /* One 144-byte GGUF Q4_K superblock (256 values): f16 d, f16 dmin, 12 bytes of packed 6-bit
  * scales/mins, 128 bytes of nibbles.  Scales, mins and nibbles are uniform random bytes.  d is an
- * f16 in [2^-13, 1.125 * 2^-13) and dmin an f16 in [7, 8) * 2^-13, so that the weights
- * d*sc*q - dmin*mn are nearly zero-mean (E[q] = 7.5); one block in 16 has a subnormal d
- * (m * 2^-24, m in 64..127) with dmin = 7.5 d, subnormal too.  20 draws per block. */
+ * f16 2^-13 * (1 + 8k/1024), k uniform in 0..7, and dmin = 7.5 * d exactly (an f16 too), which makes
+ * the weights d*sc*q - dmin*mn zero-mean (E[q] = 7.5, E[sc] = E[mn]): a deep random network whose
+ * weights have a common mean collapses onto one token.  One block in 16 has a subnormal d
+ * (m * 2^-24, m even in 64..126) with dmin = 7.5 d, subnormal too.  20 draws per block. */
 BRRR_HD void brrr_synth_q4k_block(uint64_t key, uint64_t blk, uint8_t out[144]) {
     uint64_t h = brrr_draw(key, 20 * blk);
-    uint32_t m7 = (uint32_t)(h & 0x7fu), sub = ((h >> 10) & 15u) == 0, m8 = (uint32_t)((h >> 16) & 0xffu);
-    uint16_t d = (uint16_t)(sub ? (64u + (m7 & 63u)) : ((2u << 10) | m7));
-    uint16_t dmin = (uint16_t)(sub ? ((64u + (m7 & 63u)) * 15u) >> 1 : ((4u << 10) | (768u + m8)));
+    uint32_t k = (uint32_t)(h & 7u), sub = ((h >> 10) & 15u) == 0, ms = 64u + 2u * (uint32_t)((h >> 3) & 31u);
+    uint16_t d = (uint16_t)(sub ? ms : ((2u << 10) | (8u * k)));
+    uint16_t dmin = (uint16_t)(sub ? (ms * 15u) >> 1 : ((4u << 10) | (896u + 15u * k)));
     out[0] = (uint8_t)d; out[1] = (uint8_t)(d >> 8); out[2] = (uint8_t)dmin; out[3] = (uint8_t)(dmin >> 8);
     out[4] = (uint8_t)(h >> 32); out[5] = (uint8_t)(h >> 40); out[6] = (uint8_t)(h >> 48); out[7] = (uint8_t)(h >> 56);
     for (int j = 0; j < 17; j++) {

@@ -437,19 +437,32 @@ extern "C" int brrr_qwen_forward(brrr_qwen *m, uint32_t tok, uint32_t pos, int w
     return BRRR_OK;
 }
 
-extern "C" int brrr_qwen_decode(brrr_qwen *m, uint32_t first_tok, uint32_t pos, uint32_t n, uint32_t *out_toks) {
-    if (!m || !out_toks) return BRRR_ERR_ARG;
+extern "C" int brrr_qwen_decode_enqueue(brrr_qwen *m, uint32_t first_tok, uint32_t pos, uint32_t n) {
+    if (!m) return BRRR_ERR_ARG;
     if (first_tok >= (uint32_t)m->cfg.n_vocab || n == 0 || n > BRRR_MAXSEQ || pos + n > BRRR_MAXSEQ) return BRRR_ERR_RANGE;
     CU(cudaSetDevice(m->device));
     m->h_in[0] = first_tok; m->h_in[1] = pos; m->h_in[2] = 0;
     CU(cudaMemcpyAsync(m->st, m->h_in, 12, cudaMemcpyHostToDevice, m->stream));  // tok, pos, n_out = 0
     for (uint32_t i = 0; i < n; i++) TRY(qrun_graph(m, true));
+    return BRRR_OK;
+}
+
+extern "C" int brrr_qwen_decode_wait(brrr_qwen *m, uint32_t n, uint32_t *out_toks) {
+    if (!m || !out_toks || n == 0 || n > BRRR_MAXSEQ) return BRRR_ERR_ARG;
+    CU(cudaSetDevice(m->device));
     CU(cudaMemcpyAsync(m->h_out, m->st->out, n * sizeof(uint32_t), cudaMemcpyDeviceToHost, m->stream));
     CU(cudaMemcpyAsync(m->h_in, &m->st->err, 4, cudaMemcpyDeviceToHost, m->stream));
     CU(cudaStreamSynchronize(m->stream));
     if (m->h_in[0] != 0) { QERR("device wait timed out (code %u)", m->h_in[0]); return BRRR_ERR_STATE; }
     memcpy(out_toks, m->h_out, n * sizeof(uint32_t));
     return BRRR_OK;
+}
+
+extern "C" int brrr_qwen_decode(brrr_qwen *m, uint32_t first_tok, uint32_t pos, uint32_t n, uint32_t *out_toks) {
+    if (!out_toks) return BRRR_ERR_ARG;
+    int s = brrr_qwen_decode_enqueue(m, first_tok, pos, n);
+    if (s != BRRR_OK) return s;
+    return brrr_qwen_decode_wait(m, n, out_toks);
 }
 
 extern "C" int brrr_qwen_logits(brrr_qwen *m, float *out) {

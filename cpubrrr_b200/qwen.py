@@ -71,6 +71,14 @@ class QwenEngine:
         check(lib().brrr_qwen_decode(self._h, int(first_tok), int(pos), int(n), out.ctypes.data), "brrr_qwen_decode")
         return out
 
+    def decode_enqueue(self, first_tok, pos, n):
+        check(lib().brrr_qwen_decode_enqueue(self._h, int(first_tok), int(pos), int(n)), "brrr_qwen_decode_enqueue")
+
+    def decode_wait(self, n):
+        out = np.empty(n, np.uint32)
+        check(lib().brrr_qwen_decode_wait(self._h, int(n), out.ctypes.data), "brrr_qwen_decode_wait")
+        return out
+
     def logits(self):
         out = np.empty(self.cfg.n_vocab, np.float32)
         check(lib().brrr_qwen_logits(self._h, out.ctypes.data), "brrr_qwen_logits")

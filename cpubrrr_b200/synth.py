@@ -86,12 +86,11 @@ def synth_q4k_blocks(seed, layer, kind, nblocks):
     key = tensor_key(seed, layer, kind)
     b = np.arange(nblocks, dtype=np.uint64) * np.uint64(20)
     h = draw(key, b)
-    m7 = (h & np.uint64(0x7f)).astype(np.uint32)
+    k = (h & np.uint64(7)).astype(np.uint32)
     sub = ((h >> np.uint64(10)) & np.uint64(15)) == 0
-    m8 = ((h >> np.uint64(16)) & np.uint64(0xff)).astype(np.uint32)
-    dsub = np.uint32(64) + (m7 & np.uint32(63))
-    d = np.where(sub, dsub, np.uint32(2 << 10) | m7).astype(np.uint16)
-    dmin = np.where(sub, (dsub * np.uint32(15)) >> np.uint32(1), np.uint32(4 << 10) | (np.uint32(768) + m8)).astype(np.uint16)
+    ms = np.uint32(64) + np.uint32(2) * ((h >> np.uint64(3)) & np.uint64(31)).astype(np.uint32)
+    d = np.where(sub, ms, np.uint32(2 << 10) | (np.uint32(8) * k)).astype(np.uint16)
+    dmin = np.where(sub, (ms * np.uint32(15)) >> np.uint32(1), np.uint32(4 << 10) | (np.uint32(896) + np.uint32(15) * k)).astype(np.uint16)
     out = np.empty((nblocks, 144), np.uint8)
     out[:, 0:2] = d.view(np.uint8).reshape(nblocks, 2)
     out[:, 2:4] = dmin.view(np.uint8).reshape(nblocks, 2)

@@ -150,6 +150,10 @@ int brrr_qwen_forward(brrr_qwen *m, uint32_t tok, uint32_t pos, int want_logits,
  * out_toks[i] is the token produced by step i.  Replaces the decode loop of generate
  * (src/bin/engine_qwen2.rs:613-619) without its stop test. */
 int brrr_qwen_decode(brrr_qwen *m, uint32_t first_tok, uint32_t pos, uint32_t n, uint32_t *out_toks);
+/* The same in two halves: enqueue returns as soon as the n steps are queued on the model's stream,
+ * wait blocks and fetches the tokens. */
+int brrr_qwen_decode_enqueue(brrr_qwen *m, uint32_t first_tok, uint32_t pos, uint32_t n);
+int brrr_qwen_decode_wait(brrr_qwen *m, uint32_t n, uint32_t *out_toks);
 int brrr_qwen_logits(brrr_qwen *m, float *out);               /* [n_vocab], of the last want_logits step */
 int brrr_qwen_hidden(brrr_qwen *m, float *out);               /* [n_embd], residual stream after the last step */
 /* One step run kernel by kernel, recording the residual stream after the embedding and after each

@@ -132,3 +132,26 @@ def test_qwen_open_errors(brrr, tmp_path):
     assert L.brrr_qwen_forward(eng._h, 100, 0, 1, C.byref(out)) == 5
     assert L.brrr_qwen_forward(eng._h, 0, 4096, 1, C.byref(out)) == 5
     eng.close()
+
+
+def test_full_size_qwen3_30b_a3b_parity_and_properties(brrr, orc):
+    """Qwen3-30B-A3B architecture at full size (48 layers, 128 experts top-8, vocab 151936): a short
+    prompt and greedy steps against the oracle, then size-independent properties (replay determinism,
+    prefill idempotence) over a longer device-chained run."""
+    cfg = brrr.qwen3_30b_a3b_cfg()
+    eng = brrr.QwenEngine.synth(cfg, 3)
+    om = orc.QwenModel.synth(ocfg_of(orc, cfg), 3)
+    prompt = S.synth_prompt(3, 6, cfg.n_vocab)
+    want = greedy(om.run, prompt, 10)
+    got = greedy(eng.run, prompt, 10)
+    assert got == want
+    assert np.array_equal(bits(eng.logits()), bits(om.logits()))
+    assert np.array_equal(bits(eng.hidden()), bits(om.hidden()))
+    om.close()
+    first = eng.prefill(prompt)
+    a = eng.decode(first, len(prompt), 140)
+    assert [first] + [int(t) for t in a[:9]] == want
+    assert eng.prefill(prompt) == first
+    assert np.array_equal(a, eng.decode(first, len(prompt), 140))
+    assert eng.bytes_per_step(100) > 1.5e9
+    eng.close()
