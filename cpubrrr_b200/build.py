@@ -49,8 +49,11 @@ def build(force=False, verbose=False):
     nvcc = _nvcc()
     os.makedirs(OBJ, exist_ok=True)
     extra = ["-Xptxas", "-v"] if verbose else []
+    extra += [f"-D{d}" for d in os.environ.get("BRRR_DEFS", "").split()]
     if os.environ.get("BRRR_TIMELINE"):
         extra.append("-DBRRR_TIMELINE")
+        if os.environ.get("BRRR_TIMELINE_CTA"):
+            extra.append("-DBRRR_TIMELINE_CTA=" + os.environ["BRRR_TIMELINE_CTA"])
 
     def compile_one(src):
         obj = os.path.join(OBJ, src.replace(".cu", ".o"))

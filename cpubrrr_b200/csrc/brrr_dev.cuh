@@ -145,7 +145,10 @@ __device__ __forceinline__ unsigned long long brrr_gtime() { unsigned long long 
 // wall-clock (ns) marks: END = latest finish over all CTAs of a kernel, GO = CTA 0 released from its dependency wait
 #define BRRR_GT_END(state, i) do { if ((state) && threadIdx.x == 0) atomicMax((unsigned long long *)&(state)->stamps[i], brrr_gtime()); } while (0)
 #define BRRR_GT_GO(state, i) do { if ((state) && threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0) (state)->stamps[i] = (long long)brrr_gtime(); } while (0)
-#define BRRR_STAMP(state, i) do { if ((state) && threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0) (state)->stamps[i] = clock64(); } while (0)
+#ifndef BRRR_STAMP_BX
+#define BRRR_STAMP_BX 0
+#endif
+#define BRRR_STAMP(state, i) do { if ((state) && threadIdx.x == 0 && blockIdx.x == BRRR_STAMP_BX && blockIdx.y == 0) (state)->stamps[i] = clock64(); } while (0)
 #else
 #define BRRR_GT_END(state, i) do { } while (0)
 #define BRRR_GT_GO(state, i) do { } while (0)

@@ -71,7 +71,12 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(AttnArgs a) {
     if (tid == 0) {
         for (int s = 0; s < AT_SLOTS; s++) { mbar_init(&kbar[s], 1); mbar_init(&vbar[s], 1); }
         mbar_fence_init();
-        for (int t = 0; t < min(AT_SLOTS, ntiles); t++) { issue(kbase, ktiles, kbar, t); issue(vbase, vtiles, vbar, t); }
+    }
+    __syncwarp();
+    // one lane per copy (K and V of the first tiles): their address translations overlap
+    if (tid < 2 * min(AT_SLOTS, ntiles)) {
+        if (tid & 1) issue(vbase, vtiles, vbar, tid >> 1);
+        else issue(kbase, ktiles, kbar, tid >> 1);
     }
     // static / step-constant operands: the sink and this position's rotation
     const float sink = a.sinks[h];

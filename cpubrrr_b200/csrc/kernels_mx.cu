@@ -118,7 +118,18 @@ __device__ __forceinline__ float mx_pairs(const unsigned char *unit, int rl, int
 
 __device__ __forceinline__ float mx_chunk(const unsigned char *base, int cnt, int rl, int j, const int2 *xpj, const float *xsc, const float *tbl, int pair0, float acc) {
     int i = 0;
-    for (; i + 3 <= cnt; i += 3) acc = mx_pairs<3>(base + (size_t)i * MX_UNIT, rl, j, xpj, xsc, tbl, pair0 + i, acc);
+#ifndef MX_UNROLL
+#define MX_UNROLL 1
+#endif
+#ifndef MX_TAIL_UNROLL
+#define MX_TAIL_UNROLL 4
+#endif
+#define MX_PRAGMA_(x) _Pragma(#x)
+#define MX_PRAGMA_UNROLL(n) MX_PRAGMA_(unroll n)
+#if MX_UNROLL > 1
+    for (; i + MX_UNROLL <= cnt; i += MX_UNROLL) acc = mx_pairs<MX_UNROLL>(base + (size_t)i * MX_UNIT, rl, j, xpj, xsc, tbl, pair0 + i, acc);
+#endif
+MX_PRAGMA_UNROLL(MX_TAIL_UNROLL)
     for (; i < cnt; i++) acc = mx_pairs<1>(base + (size_t)i * MX_UNIT, rl, j, xpj, xsc, tbl, pair0 + i, acc);
     return acc;
 }
@@ -162,11 +173,19 @@ struct MxRing {
     uint64_t *bars;
     int ch, stages, np, ns;
     size_t stream_bytes, stage_bytes;
-    __device__ __forceinline__ void issue(int c, const uint8_t *const *src) const {   // thread 0 only
-        int cnt = min(ch, np - c * ch), slot = c % stages;
-        mbar_expect_tx(&bars[slot], (uint32_t)cnt * MX_UNIT * ns);
-        for (int s = 0; s < ns; s++)
+    // Lane `lane` of one warp issues the copy of stream lane % ns of chunk c0 + lane / ns, for nc
+    // chunks at once (nc * ns <= 32).  Issued by one thread one after the other, every copy waits
+    // for the address translation of the one before (about 500 cycles each on cold expert
+    // weights); issued by different lanes they overlap.  A chunk's barrier cannot complete before
+    // its arrive.expect_tx, so the order of the lanes does not matter.
+    __device__ __forceinline__ void issue_warp(int c0, int nc, const uint8_t *const *src, int lane) const {
+        const int c = c0 + lane / ns, s = lane % ns;
+        if (lane < nc * ns) {
+            const int cnt = min(ch, np - c * ch), slot = c % stages;
+            fence_proxy_async();
+            if (s == 0) mbar_expect_tx(&bars[slot], (uint32_t)cnt * MX_UNIT * ns);
             bulk_g2s(ring + stage_bytes * slot + stream_bytes * s, src[s] + (size_t)c * ch * MX_UNIT, (uint32_t)cnt * MX_UNIT, &bars[slot]);
+        }
     }
 };
 
@@ -266,13 +285,10 @@ __global__ void __launch_bounds__(256) gate_up_kernel(GateUpArgs a) {
     BRRR_STAMP(a.state, 102);
     const int e = a.est ? sel[ei] : a.top[ei];
     const int nchunks = (np + a.ch - 1) / a.ch;
-    if (tid == 0) {
-        int urow = (e * a.d + blk32 * 32) >> 4;
-        src[0] = a.gate.data + mx_unit_off(urow, 0, np);
-        src[1] = a.gate.data + mx_unit_off(urow + 1, 0, np);
-        src[2] = a.up.data + mx_unit_off(urow, 0, np);
-        src[3] = a.up.data + mx_unit_off(urow + 1, 0, np);
-        for (int c = 0; c < min(a.stages, nchunks); c++) r.issue(c, src);
+    if (warp == 0) {
+        if (lane < 4) src[lane] = ((lane & 2) ? a.up.data : a.gate.data) + mx_unit_off(((e * a.d + blk32 * 32) >> 4) + (lane & 1), 0, np);
+        __syncwarp();
+        r.issue_warp(0, min(a.stages, nchunks), src, lane);
     }
     BRRR_STAMP(a.state, 103);
     if (!a.x_f32) {
@@ -304,7 +320,7 @@ __global__ void __launch_bounds__(256) gate_up_kernel(GateUpArgs a) {
         acc = mx_chunk(base, cnt, rl, j, xp + j, xsc, tbl, c * a.ch, acc);
         if (c + a.stages < nchunks) {
             __syncthreads();
-            if (tid == 0) { fence_proxy_async(); r.issue(c + a.stages, src); }
+            if (warp == 0) r.issue_warp(c + a.stages, 1, src, lane);
         }
     }
     BRRR_STAMP(a.state, 100);
@@ -387,10 +403,14 @@ __global__ void __launch_bounds__(512) down_combine_kernel(DownArgs a) {
     if (tid == 0) {
         for (int s = 0; s < a.stages; s++) mbar_init(&r.bars[s], 1);
         mbar_fence_init();
+    }
+    if (tid < 32) {
         // expert ids come from the router, two kernels back: complete by the launch protocol,
         // so the weight stream starts before this kernel waits for gate/up
-        for (int s = 0; s < a.topk; s++) src[s] = a.down.data + mx_unit_off(((a.top[s] * a.d) >> 4) + blockIdx.x, 0, np);
-        for (int c = 0; c < min(a.stages, nchunks); c++) r.issue(c, src);
+        if (tid < a.topk) src[tid] = a.down.data + mx_unit_off(((a.top[tid] * a.d) >> 4) + blockIdx.x, 0, np);
+        __syncwarp();
+        r.issue_warp(0, min(min(a.stages, nchunks), 32 / a.topk), src, tid);
+        for (int c = 32 / a.topk; c < min(a.stages, nchunks); c++) r.issue_warp(c, 1, src, tid);
     }
     // operands of the final fold: routing is two kernels old, the residual three
     float x_pre = 0.0f, b_pre[8], w_pre[8];
@@ -440,7 +460,7 @@ __global__ void __launch_bounds__(512) down_combine_kernel(DownArgs a) {
         acc = mx_chunk(base, cnt, rl, j, xp + j, xsc, tbl, c * a.ch, acc);
         if (c + a.stages < nchunks) {
             __syncthreads();
-            if (tid == 0) { fence_proxy_async(); r.issue(c + a.stages, src); }
+            if (tid < 32) r.issue_warp(c + a.stages, 1, src, tid);
         }
     }
     BRRR_STAMP(a.state, 132);

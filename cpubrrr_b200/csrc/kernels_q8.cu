@@ -86,6 +86,24 @@ __device__ __forceinline__ float q8_pairs(const unsigned char *unit, int rl, int
     return acc;
 }
 
+// cnt block pairs of one chain from a ring stage
+__device__ __forceinline__ float q8_chunk(const unsigned char *base, int cnt, int rl, int c8, int p, const int2 *xp8, const float *xsc2, float acc) {
+    int i = 0;
+#ifndef Q8_UNROLL
+#define Q8_UNROLL 8
+#endif
+#if Q8_UNROLL == 8
+    for (; i + 8 <= cnt; i += 8) acc = q8_pairs<8>(base + (size_t)i * Q8_UNIT, rl, c8, p, xp8 + i * 8, xsc2 + i * 2, acc);
+    if (i + 4 <= cnt) { acc = q8_pairs<4>(base + (size_t)i * Q8_UNIT, rl, c8, p, xp8 + i * 8, xsc2 + i * 2, acc); i += 4; }
+    if (i + 2 <= cnt) { acc = q8_pairs<2>(base + (size_t)i * Q8_UNIT, rl, c8, p, xp8 + i * 8, xsc2 + i * 2, acc); i += 2; }
+    if (i < cnt) acc = q8_pairs<1>(base + (size_t)i * Q8_UNIT, rl, c8, p, xp8 + i * 8, xsc2 + i * 2, acc);
+#else
+    for (; i + Q8_UNROLL <= cnt; i += Q8_UNROLL) acc = q8_pairs<Q8_UNROLL>(base + (size_t)i * Q8_UNIT, rl, c8, p, xp8 + i * 8, xsc2 + i * 2, acc);
+    for (; i < cnt; i++) acc = q8_pairs<1>(base + (size_t)i * Q8_UNIT, rl, c8, p, xp8 + i * 8, xsc2 + i * 2, acc);
+#endif
+    return acc;
+}
+
 // ---------------------------------------------------------------- streaming GEMV
 struct Q8Args {
     Q8Dev m;
@@ -126,7 +144,7 @@ __global__ void __launch_bounds__(Q8_THREADS) q8_stream_kernel(Q8Args a) {
     const int cpr = (np + a.ch - 1) / a.ch;                          // chunks per unit row
     const int nchunks = (u1 - u0) * cpr;
 
-    auto issue = [&](int c) {                                        // thread 0 only
+    auto issue = [&](int c) {                                        // one thread per chunk
         int u = u0 + c / cpr, k = c % cpr;
         int cnt = min(a.ch, np - k * a.ch);
         int slot = c % a.stages;
@@ -142,8 +160,8 @@ __global__ void __launch_bounds__(Q8_THREADS) q8_stream_kernel(Q8Args a) {
         mbar_fence_init();
     }
     __syncthreads();
-    if (tid == 0)
-        for (int c = 0; c < min(a.stages, nchunks); c++) issue(c);
+    // one lane per stage: the copies' address translations overlap instead of queueing behind one thread
+    if (tid < min(a.stages, nchunks)) issue(tid);
     // static operands (norm weights, bias) and the residual written several kernels back are
     // fetched now, while the predecessor is still running
     const int rl = tid >> 3, c8 = tid & 7, p = c8 >> 2;
@@ -187,15 +205,7 @@ __global__ void __launch_bounds__(Q8_THREADS) q8_stream_kernel(Q8Args a) {
         if (c < 12) BRRR_STAMP(a.state, sb + 20 + c);
         const unsigned char *base = ring + stage_bytes * slot;
         const int pair0 = k * a.ch;
-        {
-            const int2 *xp8 = xp + (size_t)pair0 * 8 + c8;
-            const float *xsc2 = xsc + pair0 * 2 + p;
-            int i = 0;
-            for (; i + 8 <= cnt; i += 8) acc = q8_pairs<8>(base + (size_t)i * Q8_UNIT, rl, c8, p, xp8 + i * 8, xsc2 + i * 2, acc);
-            if (i + 4 <= cnt) { acc = q8_pairs<4>(base + (size_t)i * Q8_UNIT, rl, c8, p, xp8 + i * 8, xsc2 + i * 2, acc); i += 4; }
-            if (i + 2 <= cnt) { acc = q8_pairs<2>(base + (size_t)i * Q8_UNIT, rl, c8, p, xp8 + i * 8, xsc2 + i * 2, acc); i += 2; }
-            if (i < cnt) acc = q8_pairs<1>(base + (size_t)i * Q8_UNIT, rl, c8, p, xp8 + i * 8, xsc2 + i * 2, acc);
-        }
+        acc = q8_chunk(base, cnt, rl, c8, p, xp + (size_t)pair0 * 8 + c8, xsc + pair0 * 2 + p, acc);
         if (k == cpr - 1) {
             BRRR_STAMP(a.state, sb + 4);
             // row finished: acc_even + acc_odd per lane, then (l0+l1)+(l2+l3)

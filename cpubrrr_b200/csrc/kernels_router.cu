@@ -135,8 +135,9 @@ __global__ void __launch_bounds__(RT_THREADS) ffn_in_kernel(RouterArgs a) {
     if (tid == 0) {
         for (int s = 0; s < RT_STAGES; s++) { mbar_init(&bars[s], 1); mbar_init(&empty[s], 1); }
         mbar_fence_init();
-        for (int t = 0; t < min(RT_STAGES, ntiles); t++) issue(t);
     }
+    __syncwarp();
+    if (tid < min(RT_STAGES, ntiles)) issue(tid);        // one lane per stage: the copies' address translations overlap
     if (a.norm_w) stage_vec4(a.norm_w, wn, d, tid, RT_THREADS);             // static: fetched before the wait
     const float bias_pre = (warp == 0 && lane < nloc && a.b) ? a.b[e0 + lane] : 0.0f;
     BRRR_STAMP(a.state, 1);
