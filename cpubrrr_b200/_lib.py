@@ -50,6 +50,18 @@ SIGNATURES = {
     "brrr_stage_name": (C.c_char_p, [_I]),
     "brrr_stage_time": (_I, [_P, _I, C.c_uint32, _I, C.POINTER(C.c_float), C.POINTER(C.c_uint64), C.POINTER(_I)]),
     "brrr_debug_stamps": (_I, [_P, _P]),
+    "brrr_tokenizer_open": (_I, [C.c_char_p, C.POINTER(_P)]),
+    "brrr_tokenizer_close": (None, [_P]),
+    "brrr_tokenizer_size": (C.c_uint32, [_P]),
+    "brrr_tokenizer_token": (_I, [_P, C.c_uint32, C.POINTER(C.c_char_p), C.POINTER(C.c_uint32)]),
+    "brrr_tokenizer_special": (_I, [_P, C.c_char_p, C.POINTER(C.c_uint32)]),
+    "brrr_tokenizer_encode": (_I, [_P, C.c_char_p, C.c_size_t, C.c_uint32, _P, C.c_size_t, C.POINTER(C.c_size_t)]),
+    "brrr_rng_seed": (C.c_uint64, [C.c_uint64]),
+    "brrr_sample_logits": (C.c_uint32, [_P, C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(C.c_uint64)]),
+    "brrr_chat_prompt": (_I, [_P, C.c_char_p, _P, C.c_size_t, C.POINTER(C.c_size_t)]),
+    "brrr_generate": (_I, [_P, _P, _P, C.c_size_t, C.c_uint32, C.c_uint32, C.c_uint32, C.POINTER(C.c_uint64), _P, _P, _P, C.c_size_t, _P]),
+    "brrr_serve_parse": (_I, [C.c_char_p, C.POINTER(C.c_float), C.POINTER(C.c_uint64), C.POINTER(C.c_uint32), C.c_char_p, C.c_size_t]),
+    "brrr_cli_main": (_I, [_I, _P]),
     "brrr_qwen_open": (_I, [C.c_char_p, C.c_char_p, _I, C.POINTER(_P)]),
     "brrr_qwen_open_synth": (_I, [C.POINTER(QwenCfg), C.c_uint64, _I, C.POINTER(_P)]),
     "brrr_qwen_cfg_get": (_I, [_P, C.POINTER(QwenCfg)]),

@@ -16,9 +16,10 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "_obj")
 LIB = os.path.join(HERE, "libbrrr.so")
+EXE = os.path.join(HERE, "brrr_engine")
 
 SOURCES = ["kernels_small.cu", "kernels_q8.cu", "kernels_mx.cu", "kernels_router.cu", "kernels_attn.cu", "kernels_kq.cu", "kernels_qwen.cu", "qwen_model.cu",
-           "model.cu", "capi_stage.cu", "capi_noalloc.cu"]
+           "model.cu", "capi_stage.cu", "capi_noalloc.cu", "host_text.cpp"]
 
 NVCC_FLAGS = [
     "-gencode", "arch=compute_100a,code=sm_100a", "-lineinfo", "-O3", "-std=c++17",
@@ -56,7 +57,7 @@ def build(force=False, verbose=False):
             extra.append("-DBRRR_TIMELINE_CTA=" + os.environ["BRRR_TIMELINE_CTA"])
 
     def compile_one(src):
-        obj = os.path.join(OBJ, src.replace(".cu", ".o"))
+        obj = os.path.join(OBJ, os.path.splitext(src)[0] + ".o")
         cmd = [nvcc, *NVCC_FLAGS, *extra, "-c", os.path.join(CSRC, src), "-o", obj]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
@@ -71,6 +72,11 @@ def build(force=False, verbose=False):
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
+    # the command-line front end (reference binary's arguments and protocol), linked against the library
+    cmd = ["g++", "-O2", "-o", EXE, os.path.join(CSRC, "engine_main.cpp"), "-L" + HERE, "-lbrrr", "-Wl,-rpath,$ORIGIN"]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"link of brrr_engine failed:\n{r.stdout}\n{r.stderr}")
     return LIB
 
 

@@ -122,6 +122,51 @@ int brrr_stage_time(brrr_model *m, int stage, uint32_t pos, int reps, float *ms_
  * library was built with -DBRRR_TIMELINE.  No counterpart in the reference. */
 int brrr_debug_stamps(brrr_model *m, long long *out256);
 
+/* ---------------------------------------------------------------- host text layer (gpt-oss engine)
+ * Pure host code around the forward pass: tokenizer, sampler, chat prompt, generate, serve. */
+typedef struct brrr_tokenizer brrr_tokenizer;
+/* Reads <data_dir>/tokens.bin (u32 count, then u16 length + bytes per token).  Tokens spelled
+ * "<|...|>" are special (never matched by encode); among equal byte strings the lowest id wins.
+ * Replaces the tokenizer set-up of main (src/bin/engine_gpt2.rs:1261-1268). */
+int brrr_tokenizer_open(const char *data_dir, brrr_tokenizer **out);
+void brrr_tokenizer_close(brrr_tokenizer *t);
+uint32_t brrr_tokenizer_size(const brrr_tokenizer *t);
+int brrr_tokenizer_token(const brrr_tokenizer *t, uint32_t id, const char **bytes, uint32_t *len);
+int brrr_tokenizer_special(const brrr_tokenizer *t, const char *text, uint32_t *id);
+/* Greedy longest match with pieces of at most max_piece bytes (32 for gpt-oss, 48 for qwen3moe).
+ * out nullable (count only); *n_out receives the number of ids; BRRR_ERR_RANGE when a byte is
+ * not encodable or cap is too small.  Replaces the closure `encode`
+ * (src/bin/engine_gpt2.rs:1269-1274, src/bin/engine_qwen2.rs:501-506). */
+int brrr_tokenizer_encode(const brrr_tokenizer *t, const char *text, size_t len, uint32_t max_piece, uint32_t *out, size_t cap, size_t *n_out);
+
+/* Sampler state from a request seed (splitmix64 scramble, never zero; src/bin/engine_gpt2.rs:1462-1466). */
+uint64_t brrr_rng_seed(uint64_t seed);
+/* Temperature + top-k sampling over host logits; greedy (first strict maximum) when temp_milli == 0
+ * or rng_state == NULL.  top_k is clamped to 1..64; the random draw is one xorshift64 step of
+ * *rng_state.  Replaces sample_logits (src/bin/engine_gpt2.rs:82-126); exp is the engine's fixed
+ * operation sequence instead of the platform's libm. */
+uint32_t brrr_sample_logits(const float *logits, uint32_t n, uint32_t temp_milli, uint32_t top_k, uint64_t *rng_state);
+
+/* Token ids of the harmony chat prompt for one user turn (src/bin/engine_gpt2.rs:1401-1414). */
+int brrr_chat_prompt(const brrr_tokenizer *t, const char *user_text, uint32_t *out, size_t cap, size_t *n_out);
+
+typedef struct brrr_gen_stats {
+    uint32_t prefill_tokens, decode_tokens;
+    double prefill_seconds, decode_seconds;
+} brrr_gen_stats;
+/* Prefill ids, then decode until a stop token (200002, 199999), ngen tokens or the context limit;
+ * emit (nullable) gets the bytes of every produced token, out_ids (nullable) the ids.  Greedy
+ * decoding runs on the device in bursts.  Replaces generate (src/bin/engine_gpt2.rs:1400-1440). */
+int brrr_generate(brrr_model *m, const brrr_tokenizer *t, const uint32_t *ids, size_t n_ids, uint32_t ngen, uint32_t temp_milli,
+                  uint32_t top_k, uint64_t *rng_state, void (*emit)(const char *, uint32_t, void *), void *emit_arg,
+                  uint32_t *out_ids, size_t out_cap, brrr_gen_stats *stats);
+/* One request line of the serve protocol: bare prompt (returns 0) or `temp \t seed \t ngen \t prompt`
+ * with \n, \t, \\ escapes (returns 1); -1 on bad arguments (src/bin/engine_gpt2.rs:1454-1482). */
+int brrr_serve_parse(const char *line, float *temp, uint64_t *seed, uint32_t *ngen, char *prompt, size_t prompt_cap);
+/* main() of the engine binary: <data-dir> <blob> [prompt|--serve] [ngen]; [READY] on stderr, streamed
+ * tokens, "[STATS] ..." and "[DONE]" lines on stdout (src/bin/engine_gpt2.rs:1252-1500). */
+int brrr_cli_main(int argc, char **argv);
+
 /* ---------------------------------------------------------------- qwen3moe engine
  * The reference's second engine binary (src/bin/engine_qwen2.rs): Qwen3-MoE models with Q4_K / Q6_K
  * weights used straight in the GGUF byte layout, Q8_K activations, QK-norm, NeoX RoPE, full
