@@ -50,6 +50,11 @@ SIGNATURES = {
     "brrr_stage_name": (C.c_char_p, [_I]),
     "brrr_stage_time": (_I, [_P, _I, C.c_uint32, _I, C.POINTER(C.c_float), C.POINTER(C.c_uint64), C.POINTER(_I)]),
     "brrr_debug_stamps": (_I, [_P, _P]),
+    "brrr_model_open_synth_ep": (_I, [C.POINTER(Cfg), C.c_uint64, _I, _I, _I, C.POINTER(_P)]),
+    "brrr_model_open_ep": (_I, [C.c_char_p, C.c_char_p, _I, _I, _I, C.POINTER(_P)]),
+    "brrr_model_ep_handle": (_I, [_P, _P]),
+    "brrr_model_ep_attach": (_I, [_P, _P]),
+    "brrr_model_ep_info": (_I, [_P, C.POINTER(_I), C.POINTER(_I), C.POINTER(_I), C.POINTER(_I)]),
     "brrr_tokenizer_open": (_I, [C.c_char_p, C.POINTER(_P)]),
     "brrr_tokenizer_close": (None, [_P]),
     "brrr_tokenizer_size": (C.c_uint32, [_P]),

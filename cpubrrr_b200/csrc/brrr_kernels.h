@@ -13,7 +13,8 @@ void launch_embed(const uint16_t *embd, int d, const DevState *state, float *x, 
 void launch_swiglu_quant(const float *gu, int topk, int d, int8_t *hq, float *hs, cudaStream_t st);
 void launch_finish_token(DevState *state, cudaStream_t st);
 void launch_expf(const float *x, int n, float *y, cudaStream_t st);
-void launch_synth(uint64_t seed, uint32_t layer, uint32_t kind, uint32_t type, uint64_t nelems, void *out, cudaStream_t st);
+// first_elem: index of the first generated element within the whole tensor (MXFP4 only; a multiple of 32)
+void launch_synth(uint64_t seed, uint32_t layer, uint32_t kind, uint32_t type, uint64_t nelems, void *out, cudaStream_t st, uint64_t first_elem = 0);
 
 // ---- K-quants of the qwen3moe path (kernels_kq.cu): weights stay in the GGUF byte layout
 void launch_quant_q8k(const float *x, int n, int8_t *q, float *s, int32_t *bsum, cudaStream_t st);
@@ -63,12 +64,28 @@ void launch_mx_gemv(MxDev m, int row0, int nrows, const int8_t *xq, const float 
 cudaError_t launch_gate_up(MxDev gate, MxDev up, const float *gate_b, const float *up_b, const int32_t *top, int topk, int d,
                            const float *x_f32, const float *norm_w, float eps, const int8_t *xq, const float *xs,
                            int8_t *hq, float *hs, float *gu, DevState *state, bool pdl, cudaStream_t st,
-                           const float *est = nullptr, int ne = 0, int sabotage = 0);
+                           const float *est = nullptr, int ne = 0, int sabotage = 0, int e_lo = 0, int e_cnt = 1 << 30);
+// e_lo, e_cnt: the matrices hold experts [e_lo, e_lo + e_cnt) only (biases stay indexed by the
+// global expert id); CTAs of slots whose expert lives elsewhere return at once.
 // est (nullable): slot s of hq/hs belongs to the s-th largest of the router estimate est[0..ne)
 // rather than to top[s]; a step whose
 // exact experts are not all among them is flagged in state->spec_fail_step.
 cudaError_t launch_down_combine(MxDev down, const float *down_b, const int32_t *top, const float *wts, const float *est, int ne, int sabotage,
                                 int topk, int d, const int8_t *hq, const float *hs, float *x, DevState *state, bool pdl, cudaStream_t st);
+
+// ---- expert parallelism over NVLink peer memory (kernels_ep.cu)
+constexpr int EP_MAX_WORLD = 8;
+struct EpCtx {
+    int rank, world, e_lo, e_cnt;          // experts [e_lo, e_lo + e_cnt) live on this rank
+    uint32_t *epoch;                       // local: number of the step in flight
+    float *xchg[EP_MAX_WORLD];             // every rank's exchange buffer [layer][slot][d]
+    uint32_t *flags[EP_MAX_WORLD];         // every rank's slice flags [layer][slot][d / 16]
+    uint32_t *done[EP_MAX_WORLD];          // every rank's completed-step counters [world]
+};
+void launch_ep_begin(const EpCtx &c, DevState *state, cudaStream_t st);
+// down-projection of the local experts, exchange of the 16-row slices, fold in slot order
+cudaError_t launch_down_ep(MxDev down, const float *down_b, const int32_t *top, const float *wts, int topk, int d, int layer, const int8_t *hq,
+                           const float *hs, float *x, DevState *state, const EpCtx &ep, bool pdl, cudaStream_t st);
 
 // ---- router (kernels_router.cu)
 // The router matrix is used in a tiled layout: [32-expert group][tile][32][RT_STRIDE] floats.

@@ -3,7 +3,7 @@
 //
 // Every wait is bounded (Waiter): when a wait runs out the waiter records an error code in the
 // device state and carries on (results are then garbage, but the kernel terminates and the host
-// reports the failure).  No copy here uses cluster multicast.
+// reports the failure).  Every copy targets the issuing CTA only.
 #pragma once
 #include "brrr_dev.cuh"
 
@@ -53,7 +53,7 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t *bar, uint32_t parity) {
 }
 
 constexpr long long WAIT_CYCLES = 2000000000ll;      // about one second of SM clock
-enum { DEV_ERR_NONE = 0, DEV_ERR_COPY_TIMEOUT = 1 };
+enum { DEV_ERR_NONE = 0, DEV_ERR_COPY_TIMEOUT = 1, DEV_ERR_PEER_TIMEOUT = 2 };
 
 // Bounded waiting on copy barriers.  A wait that exceeds WAIT_CYCLES records the error once in
 // the device state and marks the thread dead: every later wait returns at once, so a lost copy

@@ -107,10 +107,10 @@ __global__ void synth_bf16_kernel(uint64_t key, uint64_t n, float sigma, uint16_
     for (uint64_t i = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; i < n; i += (uint64_t)gridDim.x * blockDim.x)
         out[i] = brrr_synth_bf16(key, i, sigma);
 }
-__global__ void synth_mxfp4_kernel(uint64_t key, uint64_t nblocks, uint8_t *out) {
+__global__ void synth_mxfp4_kernel(uint64_t key, uint64_t first, uint64_t nblocks, uint8_t *out) {
     for (uint64_t b = blockIdx.x * (uint64_t)blockDim.x + threadIdx.x; b < nblocks; b += (uint64_t)gridDim.x * blockDim.x) {
         uint8_t tmp[17];
-        brrr_synth_mxfp4_block(key, b, tmp);
+        brrr_synth_mxfp4_block(key, first + b, tmp);
         for (int i = 0; i < 17; i++) out[b * 17 + i] = tmp[i];
     }
 }
@@ -132,7 +132,7 @@ __global__ void synth_q6k_kernel(uint64_t key, uint64_t nblocks, uint8_t *out) {
     }
 }
 
-void launch_synth(uint64_t seed, uint32_t layer, uint32_t kind, uint32_t type, uint64_t nelems, void *out, cudaStream_t st) {
+void launch_synth(uint64_t seed, uint32_t layer, uint32_t kind, uint32_t type, uint64_t nelems, void *out, cudaStream_t st, uint64_t first_elem) {
     uint64_t key = brrr_tensor_key(seed, layer, kind);
     float mean = (kind == BRRR_T_ATTN_NORM || kind == BRRR_T_FFN_NORM || kind == BRRR_T_OUT_NORM || kind == BRRR_T_Q_NORM ||
                   kind == BRRR_T_K_NORM) ? 1.0f : 0.0f;
@@ -142,7 +142,7 @@ void launch_synth(uint64_t seed, uint32_t layer, uint32_t kind, uint32_t type, u
     unsigned grid = (unsigned)((units + 255) / 256 < 148 * 16 ? (units + 255) / 256 : 148 * 16);
     if (type == 0) synth_f32_kernel<<<grid, 256, 0, st>>>(key, nelems, mean, sigma, (float *)out);
     else if (type == 30) synth_bf16_kernel<<<grid, 256, 0, st>>>(key, nelems, sigma, (uint16_t *)out);
-    else if (type == 39) synth_mxfp4_kernel<<<grid, 256, 0, st>>>(key, units, (uint8_t *)out);
+    else if (type == 39) synth_mxfp4_kernel<<<grid, 256, 0, st>>>(key, first_elem / 32, units, (uint8_t *)out);
     else if (type == 12) synth_q4k_kernel<<<grid, 256, 0, st>>>(key, units, (uint8_t *)out);
     else if (type == 14) synth_q6k_kernel<<<grid, 256, 0, st>>>(key, units, (uint8_t *)out);
 }

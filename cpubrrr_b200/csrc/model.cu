@@ -128,6 +128,12 @@ struct brrr_model {
     uint64_t spec_redos = 0;
     int launches_head = 0, launches_nohead = 0;
     bool use_pdl = true;         // chain the step's kernels with programmatic dependent launch
+    // expert parallelism: this rank holds experts [epc.e_lo, epc.e_lo + epc.e_cnt); the exchange
+    // region (slices, flags, step counters) is one allocation shared with the peers through IPC
+    bool ep = false, ep_attached = false;
+    EpCtx epc{};
+    void *ep_buf = nullptr;
+    std::vector<void *> ep_peers;
     std::vector<void *> allocs;
 
     template <typename T> int alloc(T **p, size_t n) {
@@ -146,10 +152,12 @@ namespace {
 
 #define TRY(expr) do { int _s = (expr); if (_s != BRRR_OK) return _s; } while (0)
 
-// Fetch one tensor's raw bytes into device scratch.
-int fetch(brrr_model *m, const Source &s, uint32_t layer, int kind, uint32_t type, size_t nel, void *scratch) {
+// Fetch one tensor's raw bytes into device scratch: nel elements starting at element `first` of a
+// tensor of `total` elements (total = 0: the whole tensor, first = 0).
+int fetch(brrr_model *m, const Source &s, uint32_t layer, int kind, uint32_t type, size_t nel, void *scratch, size_t first = 0, size_t total = 0) {
+    if (total == 0) total = nel;
     if (s.synth) {
-        launch_synth(s.seed, layer, kind, type, nel, scratch, m->stream);
+        launch_synth(s.seed, layer, kind, type, nel, scratch, m->stream, first);
         CU(cudaGetLastError());
         return BRRR_OK;
     }
@@ -158,10 +166,10 @@ int fetch(brrr_model *m, const Source &s, uint32_t layer, int kind, uint32_t typ
     else snprintf(name, sizeof name, "blk.%u.%s", layer, kind_name(kind));
     auto it = s.idx.find(name);
     if (it == s.idx.end()) { snprintf(g_cuda_err, sizeof g_cuda_err, "missing tensor %s", name); return BRRR_ERR_IO; }
-    if (it->second.type != type || it->second.nel != nel) { snprintf(g_cuda_err, sizeof g_cuda_err, "tensor %s: type/size mismatch", name); return BRRR_ERR_IO; }
-    size_t bytes = type_bytes(type, nel);
-    if (it->second.off + bytes > s.blob_len) { snprintf(g_cuda_err, sizeof g_cuda_err, "tensor %s exceeds blob", name); return BRRR_ERR_IO; }
-    CU(cudaMemcpyAsync(scratch, s.blob + it->second.off, bytes, cudaMemcpyHostToDevice, m->stream));
+    if (it->second.type != type || it->second.nel != total) { snprintf(g_cuda_err, sizeof g_cuda_err, "tensor %s: type/size mismatch", name); return BRRR_ERR_IO; }
+    size_t bytes = type_bytes(type, nel), skip = type_bytes(type, first);
+    if (it->second.off + skip + bytes > s.blob_len) { snprintf(g_cuda_err, sizeof g_cuda_err, "tensor %s exceeds blob", name); return BRRR_ERR_IO; }
+    CU(cudaMemcpyAsync(scratch, s.blob + it->second.off + skip, bytes, cudaMemcpyHostToDevice, m->stream));
     CU(cudaStreamSynchronize(m->stream));
     return BRRR_OK;
 }
@@ -185,10 +193,11 @@ int load_q8_part(brrr_model *m, const Source &s, uint32_t layer, int kind, int r
     return BRRR_OK;
 }
 
-int load_mx(brrr_model *m, const Source &s, uint32_t layer, int kind, int rows, int blocks, MxDev *x, void *scratch) {
+// rows [row0, row0 + rows) of an MXFP4 tensor of rows_total rows (an expert-parallel rank loads its experts only)
+int load_mx(brrr_model *m, const Source &s, uint32_t layer, int kind, int rows, int blocks, MxDev *x, void *scratch, int row0 = 0, int rows_total = 0) {
     x->rows = rows; x->blocks = blocks;
     TRY(m->alloc(&x->data, mx_bytes(rows, blocks)));
-    TRY(fetch(m, s, layer, kind, 39, (size_t)rows * blocks * 32, scratch));
+    TRY(fetch(m, s, layer, kind, 39, (size_t)rows * blocks * 32, scratch, (size_t)row0 * blocks * 32, (size_t)(rows_total ? rows_total : rows) * blocks * 32));
     launch_mx_pack((const uint8_t *)scratch, *x, m->stream);
     CU(cudaGetLastError());
     return BRRR_OK;
@@ -258,6 +267,7 @@ int enqueue_step(brrr_model *m, bool want, float *trace_dev, int *nlaunch, unsig
     const bool pdl = m->use_pdl && !trace_dev && mask == ~0u;
     int n = 0;
     auto on = [&](int st) { if (mask & (1u << st)) { n++; return true; } return false; };
+    if (m->ep) { launch_ep_begin(m->epc, m->st, s); n++; }
     if (on(ST_EMBED)) launch_embed(m->tok_embd, d, m->st, m->x, s);
     if (trace_dev) CU(cudaMemcpyAsync(trace_dev, m->x, d * sizeof(float), cudaMemcpyDeviceToDevice, s));
     for (int il = 0; il < c.n_layer; il++) {
@@ -291,8 +301,10 @@ int enqueue_step(brrr_model *m, bool want, float *trace_dev, int *nlaunch, unsig
         if (on(ST_ROUTER)) CUL(launch_ffn_in(m->x, ly.ffn_norm, c.rms_eps, d, ly.ginp, ly.ginp_b, c.n_expert, topk, m->rlogits, m->top, m->wts,
                                              &m->st->router_done, m->st, pdl, s));
         if (on(ST_GATE_UP)) CUL(launch_gate_up(ly.gate, ly.up, ly.gate_b, ly.up_b, m->top, topk, d, m->x, ly.ffn_norm, c.rms_eps, nullptr, nullptr,
-                                               m->hq, m->hs, nullptr, m->st, pdl, s));
-        if (on(ST_DOWN)) CUL(launch_down_combine(ly.down, ly.down_b, m->top, m->wts, nullptr, 0, 0, topk, d, m->hq, m->hs, m->x, m->st, pdl, s));
+                                               m->hq, m->hs, nullptr, m->st, pdl, s, nullptr, 0, 0, m->ep ? m->epc.e_lo : 0,
+                                               m->ep ? m->epc.e_cnt : (1 << 30)));
+        if (m->ep) { if (on(ST_DOWN)) CUL(launch_down_ep(ly.down, ly.down_b, m->top, m->wts, topk, d, il, m->hq, m->hs, m->x, m->st, m->epc, pdl, s)); }
+        else if (on(ST_DOWN)) CUL(launch_down_combine(ly.down, ly.down_b, m->top, m->wts, nullptr, 0, 0, topk, d, m->hq, m->hs, m->x, m->st, pdl, s));
         }
         if (trace_dev) CU(cudaMemcpyAsync(trace_dev + (size_t)(il + 1) * d, m->x, d * sizeof(float), cudaMemcpyDeviceToDevice, s));
     }
@@ -315,6 +327,32 @@ int capture(brrr_model *m, bool want, cudaGraphExec_t *out, int *nlaunch, unsign
     CU(e);
     CU(cudaGraphInstantiate(out, g, 0));
     CU(cudaGraphDestroy(g));
+    return BRRR_OK;
+}
+
+// First step and graph capture (needs every buffer the step touches, peers included).
+int finish_build(brrr_model *m) {
+    if (m->ep) m->use_spec = false;    // the routing estimate is not used across ranks
+    // one direct (un-captured) step configures every kernel's attributes and validates the launches
+    TRY(enqueue_step(m, true, nullptr, nullptr));
+    CU(cudaStreamSynchronize(m->stream));
+    CU(cudaMemsetAsync(m->st, 0, sizeof(DevState), m->stream));
+    CU(cudaMemsetAsync(&m->st->spec_fail_step, 0xFF, 4, m->stream));
+    TRY(capture(m, true, &m->g_head_safe, &m->launches_head));
+    TRY(capture(m, false, &m->g_nohead_safe, &m->launches_nohead));
+    if (m->use_spec) {
+        // direct speculative step once (kernel attributes), then capture
+        TRY(enqueue_step(m, true, nullptr, nullptr, ~0u, true));
+        CU(cudaStreamSynchronize(m->stream));
+        CU(cudaMemsetAsync(m->st, 0, sizeof(DevState), m->stream));
+        CU(cudaMemsetAsync(&m->st->spec_fail_step, 0xFF, 4, m->stream));
+        TRY(capture(m, true, &m->g_head, &m->launches_head, ~0u, true));
+        TRY(capture(m, false, &m->g_nohead, &m->launches_nohead, ~0u, true));
+    } else {
+        TRY(capture(m, true, &m->g_head, &m->launches_head));
+        TRY(capture(m, false, &m->g_nohead, &m->launches_nohead));
+    }
+    CU(cudaStreamSynchronize(m->stream));
     return BRRR_OK;
 }
 
@@ -359,9 +397,10 @@ int build_model(brrr_model *m, const Source &src) {
         launch_router_pack((const float *)scratch, ne, d, ly.ginp, m->stream);
         CU(cudaGetLastError());
         TRY(load_f32(m, src, il, BRRR_T_ROUTER_B, ne, &ly.ginp_b));
-        TRY(load_mx(m, src, il, BRRR_T_GATE, ne * d, nb, &ly.gate, scratch));
-        TRY(load_mx(m, src, il, BRRR_T_UP, ne * d, nb, &ly.up, scratch));
-        TRY(load_mx(m, src, il, BRRR_T_DOWN, ne * d, nb, &ly.down, scratch));
+        const int e_lo = m->ep ? m->epc.e_lo : 0, e_cnt = m->ep ? m->epc.e_cnt : ne;
+        TRY(load_mx(m, src, il, BRRR_T_GATE, e_cnt * d, nb, &ly.gate, scratch, e_lo * d, ne * d));
+        TRY(load_mx(m, src, il, BRRR_T_UP, e_cnt * d, nb, &ly.up, scratch, e_lo * d, ne * d));
+        TRY(load_mx(m, src, il, BRRR_T_DOWN, e_cnt * d, nb, &ly.down, scratch, e_lo * d, ne * d));
         TRY(load_f32(m, src, il, BRRR_T_GATE_B, (size_t)ne * d, &ly.gate_b));
         TRY(load_f32(m, src, il, BRRR_T_UP_B, (size_t)ne * d, &ly.up_b));
         TRY(load_f32(m, src, il, BRRR_T_DOWN_B, (size_t)ne * d, &ly.down_b));
@@ -392,27 +431,16 @@ int build_model(brrr_model *m, const Source &src) {
     CU(cudaMallocHost(&m->h_in, 16));
     CU(cudaMallocHost(&m->h_out, BRRR_MAXSEQ * sizeof(uint32_t)));
     CU(cudaStreamSynchronize(m->stream));
-    // one direct (un-captured) step configures every kernel's attributes and validates the launches
-    TRY(enqueue_step(m, true, nullptr, nullptr));
-    CU(cudaStreamSynchronize(m->stream));
-    CU(cudaMemsetAsync(m->st, 0, sizeof(DevState), m->stream));
-    CU(cudaMemsetAsync(&m->st->spec_fail_step, 0xFF, 4, m->stream));
-    TRY(capture(m, true, &m->g_head_safe, &m->launches_head));
-    TRY(capture(m, false, &m->g_nohead_safe, &m->launches_nohead));
-    if (m->use_spec) {
-        // direct speculative step once (kernel attributes), then capture
-        TRY(enqueue_step(m, true, nullptr, nullptr, ~0u, true));
+    if (m->ep) {
+        // exchange region: slices [layer][slot][d] | slice flags [layer][slot][d/16] | step counters [8] (+ the local epoch word)
+        const size_t nslice = (size_t)c.n_layer * topk * d, nflag = (size_t)c.n_layer * topk * (d / 16);
+        const size_t bytes = nslice * 4 + nflag * 4 + (EP_MAX_WORLD + 8) * 4;
+        CU(cudaMalloc(&m->ep_buf, bytes));
+        CU(cudaMemsetAsync(m->ep_buf, 0, bytes, m->stream));
         CU(cudaStreamSynchronize(m->stream));
-        CU(cudaMemsetAsync(m->st, 0, sizeof(DevState), m->stream));
-        CU(cudaMemsetAsync(&m->st->spec_fail_step, 0xFF, 4, m->stream));
-        TRY(capture(m, true, &m->g_head, &m->launches_head, ~0u, true));
-        TRY(capture(m, false, &m->g_nohead, &m->launches_nohead, ~0u, true));
-    } else {
-        TRY(capture(m, true, &m->g_head, &m->launches_head));
-        TRY(capture(m, false, &m->g_nohead, &m->launches_nohead));
+        return BRRR_OK;               // the first step needs the peers: brrr_model_ep_attach finishes the build
     }
-    CU(cudaStreamSynchronize(m->stream));
-    return BRRR_OK;
+    return finish_build(m);
 }
 
 int parse_dir(const char *dir, brrr_cfg *c, Source *src) {
@@ -496,6 +524,105 @@ extern "C" int brrr_model_open_synth(const brrr_cfg *cfg, uint64_t seed, int dev
     return BRRR_OK;
 }
 
+// ---------------------------------------------------------------- expert parallelism
+static int ep_prepare(brrr_model *m, int rank, int world) {
+    const int ne = m->cfg.n_expert;
+    if (world < 1 || world > EP_MAX_WORLD || rank < 0 || rank >= world || ne % world) return BRRR_ERR_ARG;
+    m->ep = true;
+    m->epc.rank = rank; m->epc.world = world;
+    m->epc.e_cnt = ne / world; m->epc.e_lo = rank * (ne / world);
+    return BRRR_OK;
+}
+
+extern "C" int brrr_model_open_synth_ep(const brrr_cfg *cfg, uint64_t seed, int device, int rank, int world, brrr_model **out) {
+    if (!cfg || !out) return BRRR_ERR_ARG;
+    *out = nullptr;
+    int s = check_cfg(*cfg);
+    if (s != BRRR_OK) return s;
+    brrr_model *m = new brrr_model();
+    m->cfg = *cfg;
+    m->device = device;
+    s = ep_prepare(m, rank, world);
+    Source src;
+    src.synth = true; src.seed = seed;
+    if (s == BRRR_OK) s = build_model(m, src);
+    if (s != BRRR_OK) { brrr_model_close(m); return s; }
+    *out = m;
+    return BRRR_OK;
+}
+
+extern "C" int brrr_model_open_ep(const char *data_dir, const char *blob_path, int device, int rank, int world, brrr_model **out) {
+    if (!data_dir || !blob_path || !out) return BRRR_ERR_ARG;
+    *out = nullptr;
+    brrr_model *m = new brrr_model();
+    m->device = device;
+    Source src;
+    int s = parse_dir(data_dir, &m->cfg, &src);
+    if (s == BRRR_OK) s = check_cfg(m->cfg);
+    if (s == BRRR_OK) s = ep_prepare(m, rank, world);
+    void *map = MAP_FAILED;
+    if (s == BRRR_OK) {
+        int fd = open(blob_path, O_RDONLY);
+        struct stat stt;
+        if (fd < 0 || fstat(fd, &stt) != 0) { snprintf(g_cuda_err, sizeof g_cuda_err, "cannot open blob %s", blob_path); s = BRRR_ERR_IO; }
+        else {
+            src.blob_len = stt.st_size;
+            map = mmap(nullptr, src.blob_len, PROT_READ, MAP_PRIVATE, fd, 0);
+            if (map == MAP_FAILED) { snprintf(g_cuda_err, sizeof g_cuda_err, "mmap of %s failed", blob_path); s = BRRR_ERR_IO; }
+            src.blob = (const uint8_t *)map;
+        }
+        if (fd >= 0) close(fd);
+    }
+    if (s == BRRR_OK) s = build_model(m, src);
+    if (map != MAP_FAILED) munmap(map, src.blob_len);
+    if (s != BRRR_OK) { brrr_model_close(m); return s; }
+    *out = m;
+    return BRRR_OK;
+}
+
+extern "C" int brrr_model_ep_handle(brrr_model *m, void *handle64) {
+    if (!m || !handle64 || !m->ep || !m->ep_buf) return BRRR_ERR_STATE;
+    static_assert(sizeof(cudaIpcMemHandle_t) == 64, "IPC handle size");
+    CU(cudaSetDevice(m->device));
+    cudaIpcMemHandle_t h;
+    CU(cudaIpcGetMemHandle(&h, m->ep_buf));
+    memcpy(handle64, &h, 64);
+    return BRRR_OK;
+}
+
+extern "C" int brrr_model_ep_attach(brrr_model *m, const void *handles) {
+    if (!m || !m->ep || !m->ep_buf || m->ep_attached) return BRRR_ERR_STATE;
+    if (!handles && m->epc.world > 1) return BRRR_ERR_ARG;
+    CU(cudaSetDevice(m->device));
+    const brrr_cfg &c = m->cfg;
+    const size_t nslice = (size_t)c.n_layer * c.n_expert_used * c.n_embd, nflag = (size_t)c.n_layer * c.n_expert_used * (c.n_embd / 16);
+    m->ep_peers.assign(m->epc.world, nullptr);
+    for (int p = 0; p < m->epc.world; p++) {
+        void *base = m->ep_buf;
+        if (p != m->epc.rank) {
+            cudaIpcMemHandle_t h;
+            memcpy(&h, (const char *)handles + (size_t)p * 64, 64);
+            CU(cudaIpcOpenMemHandle(&base, h, cudaIpcMemLazyEnablePeerAccess));
+            m->ep_peers[p] = base;
+        }
+        m->epc.xchg[p] = (float *)base;
+        m->epc.flags[p] = (uint32_t *)((char *)base + nslice * 4);
+        m->epc.done[p] = m->epc.flags[p] + nflag;
+    }
+    m->epc.epoch = m->epc.done[m->epc.rank] + EP_MAX_WORLD;
+    m->ep_attached = true;
+    return finish_build(m);
+}
+
+extern "C" int brrr_model_ep_info(const brrr_model *m, int *rank, int *world, int *e_lo, int *e_cnt) {
+    if (!m) return BRRR_ERR_ARG;
+    if (rank) *rank = m->ep ? m->epc.rank : 0;
+    if (world) *world = m->ep ? m->epc.world : 1;
+    if (e_lo) *e_lo = m->ep ? m->epc.e_lo : 0;
+    if (e_cnt) *e_cnt = m->ep ? m->epc.e_cnt : m->cfg.n_expert;
+    return BRRR_OK;
+}
+
 extern "C" void brrr_model_close(brrr_model *m) {
     if (!m) return;
     cudaSetDevice(m->device);
@@ -507,6 +634,8 @@ extern "C" void brrr_model_close(brrr_model *m) {
     if (m->ev_fork) cudaEventDestroy(m->ev_fork);
     if (m->ev_join) cudaEventDestroy(m->ev_join);
     if (m->side) cudaStreamDestroy(m->side);
+    for (void *p : m->ep_peers) if (p) cudaIpcCloseMemHandle(p);
+    if (m->ep_buf) cudaFree(m->ep_buf);
     for (void *p : m->allocs) cudaFree(p);
     if (m->h_in) cudaFreeHost(m->h_in);
     if (m->h_out) cudaFreeHost(m->h_out);
@@ -544,6 +673,7 @@ extern "C" uint64_t brrr_model_bytes_per_step(const brrr_model *m, uint32_t pos)
 }
 
 static int run_graph(brrr_model *m, bool want, bool safe = false) {
+    if (m->ep && !m->ep_attached) return BRRR_ERR_STATE;
     cudaGraphExec_t g = safe ? (want ? m->g_head_safe : m->g_nohead_safe) : (want ? m->g_head : m->g_nohead);
     CU(cudaGraphLaunch(g, m->stream));
     return BRRR_OK;
@@ -714,6 +844,7 @@ extern "C" int brrr_stage_count(void) { return ST_COUNT; }
 extern "C" const char *brrr_stage_name(int stage) { return stage >= 0 && stage < ST_COUNT ? kStageNames[stage] : ""; }
 
 extern "C" int brrr_stage_time(brrr_model *m, int stage, uint32_t pos, int reps, float *ms_per_launch, uint64_t *bytes_per_launch, int *launches_per_step) {
+    if (m && m->ep) return BRRR_ERR_STATE;      // per-kernel replays would not be matched by the peers
     if (!m || stage < 0 || stage >= ST_COUNT || stage == ST_FINISH || reps <= 0 || pos >= BRRR_MAXSEQ) return BRRR_ERR_ARG;
     CU(cudaSetDevice(m->device));
     cudaGraphExec_t g = nullptr;

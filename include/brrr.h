@@ -122,6 +122,25 @@ int brrr_stage_time(brrr_model *m, int stage, uint32_t pos, int reps, float *ms_
  * library was built with -DBRRR_TIMELINE.  No counterpart in the reference. */
 int brrr_debug_stamps(brrr_model *m, long long *out256);
 
+/* ---------------------------------------------------------------- expert parallelism (one process per GPU)
+ * Rank r of `world` (<= 8, dividing n_expert) loads the experts [r * n_expert / world, (r + 1) *
+ * n_expert / world) only; attention, router, norms, embedding and head are replicated and computed
+ * redundantly, so every rank produces the same token.  Per layer the ranks exchange the selected
+ * experts' down-projection slices through peer memory inside the down-projection kernel and fold
+ * them in slot order: results equal the single-GPU model bit for bit.  Every rank must issue the
+ * same sequence of forward / decode calls.  No counterpart in the reference (single process, CPU);
+ * it serves the gpt-oss-120b configuration, whose experts are sharded by index over the GPUs of a node.
+ *
+ * Set-up: open on every rank, exchange the 64-byte handles (any host-side all-gather), make sure
+ * every rank has opened (a host barrier), then attach on every rank at the same time: attach runs
+ * the first step, which already synchronises with the peers (a rank whose peers do not show up
+ * within about ten seconds fails with BRRR_ERR_STATE on its next call instead of hanging). */
+int brrr_model_open_synth_ep(const brrr_cfg *cfg, uint64_t seed, int device, int rank, int world, brrr_model **out);
+int brrr_model_open_ep(const char *data_dir, const char *blob_path, int device, int rank, int world, brrr_model **out);
+int brrr_model_ep_handle(brrr_model *m, void *handle64);          /* IPC handle of this rank's exchange region */
+int brrr_model_ep_attach(brrr_model *m, const void *handles);     /* world x 64 bytes in rank order (own entry ignored) */
+int brrr_model_ep_info(const brrr_model *m, int *rank, int *world, int *first_expert, int *n_local_experts);
+
 /* ---------------------------------------------------------------- host text layer (gpt-oss engine)
  * Pure host code around the forward pass: tokenizer, sampler, chat prompt, generate, serve. */
 typedef struct brrr_tokenizer brrr_tokenizer;
