@@ -51,6 +51,14 @@ def use_qwen_workload():
     TOK_BOUND = 151936
 
 
+def use_120b_workload():
+    """--workload gptoss120b: 36 layers, 128 experts top-4; meant for --parallel ep over 1/2/4/8 GPUs."""
+    global WORKLOAD, METRIC, ARCH
+    WORKLOAD = "gpt-oss-120b decode, 73-token prompt, batch 1, greedy"
+    METRIC = "batch-1 decode tok/s (gpt-oss-120b shape, MXFP4)"
+    ARCH = "36 layers, d 2880, 64/8 heads x 64, 128 experts top-4, vocab 201088"
+
+
 def oracle_model(qwen):
     from oracle import oracle as O
     O.build()
@@ -177,14 +185,21 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline / parity leg")
     ap.add_argument("--no-stages", action="store_true", help="skip the per-kernel-class timing")
-    ap.add_argument("--workload", default="gptoss20b", choices=["gptoss20b", "qwen3-30b-a3b"],
-                    help="gptoss20b is the benchmark workload; qwen3-30b-a3b measures the reference's second engine")
+    ap.add_argument("--workload", default="gptoss20b", choices=["gptoss20b", "gptoss120b", "qwen3-30b-a3b"],
+                    help="gptoss20b is the benchmark workload; gptoss120b is the expert-parallel configuration; qwen3-30b-a3b measures the reference's second engine")
+    ap.add_argument("--parallel", default="replicas", choices=["replicas", "ep"],
+                    help="N > 1: independent replicas (weak scaling, default) or one sequence with the experts sharded over the ranks (strong scaling)")
     ap.add_argument("--layers", type=int, default=24, help="profiling aid: fewer layers (not the benchmark workload)")
     ap.add_argument("--vocab", type=int, default=201088, help="profiling aid: smaller vocabulary (not the benchmark workload)")
     args = ap.parse_args()
-    qwen = args.workload != "gptoss20b"
+    qwen = args.workload == "qwen3-30b-a3b"
+    big = args.workload == "gptoss120b"
     if qwen:
         use_qwen_workload()
+    if big:
+        use_120b_workload()
+        args.no_cpu = True                  # the CPU port would need the 61 GB of expert weights in host memory
+    ep_mode = args.parallel == "ep" or (big and int(os.environ.get("WORLD_SIZE", "1")) > 1)
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
     world = int(os.environ.get("WORLD_SIZE", "1"))
@@ -216,11 +231,21 @@ def main():
         eng = B.QwenEngine.synth(cfg, SEED, device=local_rank)
         prompt = S.synth_prompt(SEED + rank, PROMPT_LEN, TOK_BOUND)
     else:
-        if reduced:                                             # small case for profiler captures only
+        if big:
+            reduced = args.layers != 24
+            cfg = B.make_cfg(2880, args.layers if reduced else 36, 64, 8, 128, 4, 201088)
+        elif reduced:                                           # small case for profiler captures only
             cfg = B.make_cfg(2880, args.layers, 64, 8, 32, 4, args.vocab)
             args.no_cpu = True
-        eng = B.Engine.synth(cfg, SEED, device=local_rank)
-        prompt = S.synth_prompt(SEED + rank, PROMPT_LEN, min(199999, args.vocab))   # every replica decodes its own sequence
+        if ep_mode:
+            # one sequence, experts sharded by index over the ranks; every rank computes the same tokens
+            from cpubrrr_b200 import ep
+            args.no_stages = True
+            eng = ep.open_synth_ep(cfg, SEED, rank, world, device=local_rank, dist=dist, torch_device=torch.device("cuda", local_rank))
+            prompt = S.synth_prompt(SEED, PROMPT_LEN, min(199999, args.vocab))
+        else:
+            eng = B.Engine.synth(cfg, SEED, device=local_rank)
+            prompt = S.synth_prompt(SEED + rank, PROMPT_LEN, min(199999, args.vocab))   # every replica decodes its own sequence
     first = eng.prefill(prompt)
     stream = torch.cuda.ExternalStream(eng.stream, device=torch.device("cuda", local_rank))
 
@@ -243,16 +268,16 @@ def main():
     toks = eng.decode_wait(K)
     barrier()
     ms = e0.elapsed_time(e1)
-    # keep the GPU busy long enough for the clock sampler on short runs
-    if sampler:
-        t_end = time.time() + max(0.0, 1.0 - ms / 1000.0)
-        while time.time() < t_end:
-            eng.decode(first, PROMPT_LEN, 16)
-    clocks = sampler.stop() if sampler else None
     if dist is not None:
         t = torch.tensor([ms], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
+    # keep the GPUs busy long enough for the clock sampler on short runs; the number of extra calls
+    # is derived from the reduced time, so every rank issues the same calls (expert-parallel ranks must)
+    extra = int(max(0.0, 1.0 - ms / 1000.0) / (16 * ms / K / 1000.0)) + 1
+    for _ in range(extra):
+        eng.decode(first, PROMPT_LEN, 16)
+    clocks = sampler.stop() if sampler else None
 
     # ---- end to end through the public API: host token in, host token out, every step
     tok, pos = first, PROMPT_LEN
@@ -271,28 +296,30 @@ def main():
         e2e_s = float(t.item())
 
     if rank != 0:
+        if dist is not None:
+            dist.barrier()              # nobody frees memory its peers may still write to
         eng.close()
         if dist is not None:
-            dist.barrier()
             dist.destroy_process_group()
         return
 
     peak, peak_kind = measured_peaks()
     mid = PROMPT_LEN + K // 2
     step_bytes = sum(eng.bytes_per_step(PROMPT_LEN + i) for i in range(K)) / K
-    value = world * K / (ms / 1000.0)
+    nseq = 1 if ep_mode else world          # expert-parallel ranks share one sequence
+    value = nseq * K / (ms / 1000.0)
     out = {
         "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": args.warmup,
-        "ms_per_step": ms / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong" if ep_mode else "weak", "vs_baseline": None,
         "dtype": DTYPE, "data": "synthetic",
         "config": {"workload": WORKLOAD if not reduced else f"PROFILING CASE ({args.layers} layers, vocab {args.vocab}) - not the benchmark workload", "arch": ARCH,
-                   "positions": [PROMPT_LEN, PROMPT_LEN + K], "parallelism": f"replicas x{world}" if world > 1 else "single GPU",
+                   "positions": [PROMPT_LEN, PROMPT_LEN + K], "parallelism": (f"expert-parallel x{world}" if ep_mode else f"replicas x{world}") if (world > 1 or ep_mode) else "single GPU",
                    "l2": f"inputs larger than L2 ({eng.bytes_per_step(PROMPT_LEN) / 1e9:.2f} GB of weights streamed per step)"},
-        "e2e": {"value": world * K / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 4},
+        "e2e": {"value": nseq * K / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 4},
         "gpu_launches": K * eng.launches_per_step(True),
         "clocks": clocks,
-        "step_roofline": {"bound": "hbm", "bytes_per_step": step_bytes, "achieved": step_bytes / (ms / K) / 1e6, "peak": peak,
-                          "unit": "GB/s", "frac": step_bytes / (ms / K) / 1e6 / peak, "peak_kind": peak_kind,
+        "step_roofline": {"bound": "hbm", "bytes_per_step": step_bytes, "achieved": step_bytes / (ms / K) / 1e6, "peak": peak * (world if ep_mode else 1),
+                          "unit": "GB/s", "frac": step_bytes / (ms / K) / 1e6 / (peak * (world if ep_mode else 1)), "peak_kind": peak_kind,
                           "frac_of_8TBs": step_bytes / (ms / K) / 1e6 / 8000.0},
     }
     if not args.no_stages:
@@ -314,10 +341,11 @@ def main():
         cpu, parity = cpu_baseline_and_parity(toks, first, 16, qwen)
         out["cpu_baseline"] = cpu
         out["parity"] = parity
+    if dist is not None:
+        dist.barrier()
     eng.close()
     print(json.dumps(out), flush=True)
     if dist is not None:
-        dist.barrier()
         dist.destroy_process_group()
 
 
