@@ -73,6 +73,11 @@ cudaError_t launch_gate_up(MxDev gate, MxDev up, const float *gate_b, const floa
 cudaError_t launch_down_combine(MxDev down, const float *down_b, const int32_t *top, const float *wts, const float *est, int ne, int sabotage,
                                 int topk, int d, const int8_t *hq, const float *hs, float *x, DevState *state, bool pdl, cudaStream_t st);
 
+// ---- token-tile matmul on tcgen05 tensor cores (kernels_tile.cu): y[t][r] = row (row0 + r) . activation t,
+// t < ntok <= 16, every value bit-identical to launch_mx_gemv on token t alone
+cudaError_t launch_mx_tile(MxDev w, int row0, int nrows, const int8_t *xq, const float *xs, int ntok, float *y, int ldy, DevState *state,
+                           cudaStream_t st);
+
 // ---- expert parallelism over NVLink peer memory (kernels_ep.cu)
 constexpr int EP_MAX_WORLD = 8;
 struct EpCtx {

@@ -279,6 +279,14 @@ void brrr_mxmat_free(brrr_mxmat *m);
  * (src/bin/engine_gpt2.rs:193-228). */
 int brrr_mx_matvec(const brrr_mxmat *w, int row0, int nrows, const int8_t *d_xq, const float *d_xs, float *d_y, int32_t *d_blockdots, void *stream);
 
+/* The same product for a tile of up to 16 tokens in one pass over the weights, on the tcgen05
+ * tensor cores (int8 MMA into tensor memory, float chains in the epilogue): d_y[t * ldy + i] = row
+ * (row0 + i) . activation t, each value bit-identical to brrr_mx_matvec on token t alone.
+ * d_xq [ntok][blocks * 32] int8, d_xs [ntok][blocks].  Replaces the expert products of the tile
+ * path (forward_tile_worker, src/bin/engine_gpt2.rs:1011-1250, TILE = 16). */
+int brrr_mx_matmul_tile(const brrr_mxmat *w, int row0, int nrows, const int8_t *d_xq, const float *d_xs, int ntok, float *d_y, int ldy,
+                        void *stream);
+
 /* Router GEMV + top-k + softmax over the selected k.  d_b nullable.  d_logits [ne], d_top [k],
  * d_wts [k].  Replaces src/bin/engine_gpt2.rs:848-867. */
 int brrr_router_topk(const float *d_w, const float *d_b, const float *d_xn, int ne, int d, int topk,
