@@ -94,6 +94,7 @@ SIGNATURES = {
     "brrr_mxmat_free": (None, [_P]),
     "brrr_mx_matvec": (_I, [_P, _I, _I, _P, _P, _P, _P, _P]),
     "brrr_mx_matmul_tile": (_I, [_P, _I, _I, _P, _P, _I, _P, _I, _P]),
+    "brrr_moe_ffn_tile": (_I, [_P, _I, _P, _P, _I, _P, _P]),
     "brrr_router_topk": (_I, [_P, _P, _P, _I, _I, _I, _P, _P, _P, _P]),
     "brrr_router_topk_noalloc": (_I, [_P, _P, _P, _I, _I, _I, _P, _P, _P, _P]),
     "brrr_swiglu_quant": (_I, [_P, _I, _I, _P, _P, _P]),

@@ -78,6 +78,13 @@ cudaError_t launch_down_combine(MxDev down, const float *down_b, const int32_t *
 cudaError_t launch_mx_tile(MxDev w, int row0, int nrows, const int8_t *xq, const float *xs, int ntok, float *y, int ldy, DevState *state,
                            cudaStream_t st);
 
+// every expert of one matrix kind against the (token, slot) entries routed to it (cnt[e], list[e][16]);
+// entry i reads activation row entry / src_div and writes y[entry * ldy + col0 + row] (+ bias[e][row])
+cudaError_t launch_mx_tile_experts(MxDev w, int ne, int rows_per_expert, const int *cnt, const int *list, int src_div, const int8_t *xq,
+                                   const float *xs, const float *bias, float *y, int ldy, int col0, DevState *state, cudaStream_t st);
+void launch_tile_route(const int32_t *top, int ntok, int topk, int ne, int *cnt, int *list, cudaStream_t st);
+void launch_tile_combine(const float *part, const float *wts, int topk, int d, int ntok, float *x, cudaStream_t st);
+
 // ---- expert parallelism over NVLink peer memory (kernels_ep.cu)
 constexpr int EP_MAX_WORLD = 8;
 struct EpCtx {
@@ -102,7 +109,9 @@ void launch_router_pack(const float *W, int ne, int d, float *out, cudaStream_t 
 // x_in is the residual stream when norm_w != nullptr (RMSNorm applied first) or an already
 // normalised vector otherwise.
 cudaError_t launch_ffn_in(const float *x_in, const float *norm_w, float eps, int d, const float *Wt, const float *b, int ne, int topk,
-                          float *logits, int32_t *top, float *wts, unsigned int *counter, DevState *state, bool pdl, cudaStream_t st);
+                          float *logits, int32_t *top, float *wts, unsigned int *counter, DevState *state, bool pdl, cudaStream_t st,
+                          int ntok = 1);
+// ntok > 1: a tile of tokens in one launch (token t reads x_in + t * d, writes logits + t * ne, top + 8 t, wts + 8 t, uses counter + t)
 
 // Order-free estimate of the router used only to start the gate/up weight stream early
 // (speculative routing): est[ne] receives the estimated logits, xq_out/xs_out the Q8 image of the

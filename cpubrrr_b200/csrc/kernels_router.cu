@@ -109,6 +109,12 @@ __device__ __forceinline__ void warp_topk(const RouterArgs &a, const float *lg, 
 }
 
 __global__ void __launch_bounds__(RT_THREADS) ffn_in_kernel(RouterArgs a) {
+    // blockIdx.y = token of a tile: inputs d apart, logits ne apart, routing 8 entries apart, one arrival counter each
+    a.x_in += (size_t)blockIdx.y * a.d;
+    a.logits += (size_t)blockIdx.y * a.ne;
+    a.top += blockIdx.y * 8;
+    a.wts += blockIdx.y * 8;
+    a.counter += blockIdx.y;
     extern __shared__ __align__(128) unsigned char smraw[];
     float *tiles = reinterpret_cast<float *>(smraw);                                        // [RT_STAGES][32][RT_STRIDE]
     float *xn = reinterpret_cast<float *>(smraw + (size_t)RT_TILE_FLOATS * 4 * RT_STAGES);   // d floats
@@ -210,7 +216,7 @@ __global__ void __launch_bounds__(RT_THREADS) ffn_in_kernel(RouterArgs a) {
 size_t router_packed_floats(int ne, int d) { return (size_t)((ne + 31) / 32) * ((d + RT_TJ - 1) / RT_TJ) * RT_TILE_FLOATS; }
 
 cudaError_t launch_ffn_in(const float *x_in, const float *norm_w, float eps, int d, const float *Wt, const float *b, int ne, int topk,
-                          float *logits, int32_t *top, float *wts, unsigned int *counter, DevState *state, bool pdl, cudaStream_t st) {
+                          float *logits, int32_t *top, float *wts, unsigned int *counter, DevState *state, bool pdl, cudaStream_t st, int ntok) {
     RouterArgs a{x_in, norm_w, eps, d, Wt, b, ne, topk, logits, top, wts, counter, state};
     size_t smem = (size_t)RT_TILE_FLOATS * 4 * RT_STAGES + (size_t)d * 8 + (size_t)((ne + 1) & ~1) * 4 + RT_STAGES * 16;
     static bool configured = false;
@@ -219,7 +225,7 @@ cudaError_t launch_ffn_in(const float *x_in, const float *norm_w, float eps, int
         if (e != cudaSuccess) return e;
         configured = true;
     }
-    return launch_k(ffn_in_kernel, dim3((ne + 31) / 32), dim3(RT_THREADS), smem, st, pdl, a);
+    return launch_k(ffn_in_kernel, dim3((ne + 31) / 32, ntok), dim3(RT_THREADS), smem, st, pdl, a);
 }
 
 // ---------------------------------------------------------------- routing hint (speculation)

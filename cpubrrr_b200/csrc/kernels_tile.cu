@@ -70,14 +70,21 @@ __device__ __forceinline__ void tl_ld16(uint32_t taddr, int (&r)[16]) {
 }
 __device__ __forceinline__ void tl_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
+// One launch serves blockIdx.y = expert (or a single matrix).  Each expert has a list of up to 16
+// entries; entry i multiplies the activation row entry / src_div and writes output row entry.
 struct TileArgs {
     MxDev w;
-    int row0, nrows;
-    const int8_t *xq;        // [ntok][blocks * 32]
-    const float *xs;         // [ntok][blocks]
+    int row0, nrows;         // rows [row0, row0 + nrows) of each expert's matrix
+    int rows_per_expert;     // matrix row of (expert e, row r) = e * rows_per_expert + r
+    const int *cnt;          // [experts] entries per expert; nullptr: one matrix, entries 0 .. ntok - 1
+    const int *list;         // [experts][16]
+    int src_div;
+    const int8_t *xq;        // [activation rows][blocks * 32]
+    const float *xs;         // [activation rows][blocks]
     int ntok;
-    float *y;                // [ntok][ldy], element [t][row - row0]
-    int ldy;
+    const float *bias;       // nullable: [experts][rows_per_expert], added to every output
+    float *y;                // element [entry][col0 + row - row0], rows ldy apart
+    int ldy, col0;
     DevState *state;
 };
 
@@ -88,8 +95,13 @@ __global__ void __launch_bounds__(128) mx_tile_kernel(TileArgs a) {
     __shared__ float xs_pair[2][TL_MAXTOK];
     __shared__ __align__(8) uint64_t bar;
     __shared__ uint32_t tmem_base_sh;
+    __shared__ int ent[TL_MAXTOK];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int nb = a.w.blocks, np = nb / 2;
+    const int e = blockIdx.y;
+    const int n_ent = a.cnt ? a.cnt[e] : a.ntok;
+    if (n_ent == 0) return;                      // no token routed to this expert (before anything is allocated)
+    if (tid < TL_MAXTOK) ent[tid] = tid < n_ent ? (a.list ? a.list[e * TL_MAXTOK + tid] : tid) : 0;
     uint32_t *err = a.state ? &a.state->err : nullptr;
     Waiter waiter(err);
     const uint32_t P_LO = 0x04030200u, P_HI = 0x0D090705u, N_LO = 0xFDFEFF00u, N_HI = 0xF4F8FAFCu;
@@ -109,7 +121,7 @@ __global__ void __launch_bounds__(128) mx_tile_kernel(TileArgs a) {
     // this thread's row: weights of (row, all four lanes) for a block pair are 32 contiguous bytes
     const int row_local = blockIdx.x * TL_ROWS + tid;
     const bool row_live = row_local < a.nrows;
-    const int row = a.row0 + (row_live ? row_local : a.nrows - 1);       // out-of-range rows reread the last row, never stored
+    const int row = e * a.rows_per_expert + a.row0 + (row_live ? row_local : a.nrows - 1);   // out-of-range rows reread the last row, never stored
     const unsigned char *wrow = a.w.data + mx_unit_off(row >> 4, 0, np) + (row & 15) * 32;
     const unsigned char *erow = a.w.data + mx_unit_off(row >> 4, 0, np) + MX_UNIT_EXPS + (row & 15) * 2;
     // A element (row m, byte k) lives at (k / 16) * 2048 + (m / 8) * 128 + (m % 8) * 16 + k % 16
@@ -142,13 +154,14 @@ __global__ void __launch_bounds__(128) mx_tile_kernel(TileArgs a) {
         {
             const int b = 2 * p + bblk;
             uint2 v = make_uint2(0u, 0u);
-            if (bt < a.ntok) {
-                const uint32_t *xw = reinterpret_cast<const uint32_t *>(a.xq + ((size_t)bt * nb + b) * 32);
+            const size_t srow = (size_t)(ent[bt] / a.src_div);
+            if (bt < n_ent) {
+                const uint32_t *xw = reinterpret_cast<const uint32_t *>(a.xq + (srow * nb + b) * 32);
                 const int2 iv = mx_interleave(xw[bl], xw[4 + bl]);
                 v = make_uint2((uint32_t)iv.x, (uint32_t)iv.y);
             }
             *reinterpret_cast<uint2 *>(&b_tiles[bblk][b_off]) = v;
-            if (bl == 0) xs_pair[bblk][bt] = bt < a.ntok ? a.xs[(size_t)bt * nb + b] : 0.0f;
+            if (bl == 0) xs_pair[bblk][bt] = bt < n_ent ? a.xs[srow * nb + b] : 0.0f;
         }
         fence_proxy_async();               // generic-proxy writes above -> visible to the tensor core's reads
         __syncthreads();
@@ -187,21 +200,65 @@ __global__ void __launch_bounds__(128) mx_tile_kernel(TileArgs a) {
         __syncthreads();                   // tiles and accumulators are free for the next pair
     }
     if (row_live) {
+        const float bias = a.bias ? a.bias[(size_t)e * a.rows_per_expert + a.row0 + row_local] : 0.0f;
 #pragma unroll
         for (int t = 0; t < TL_MAXTOK; t++)
-            if (t < a.ntok)
-                a.y[(size_t)t * a.ldy + row_local] = __fadd_rn(__fadd_rn(acc[4 * t], acc[4 * t + 1]), __fadd_rn(acc[4 * t + 2], acc[4 * t + 3]));
+            if (t < n_ent) {
+                float v = __fadd_rn(__fadd_rn(acc[4 * t], acc[4 * t + 1]), __fadd_rn(acc[4 * t + 2], acc[4 * t + 3]));
+                if (a.bias) v = __fadd_rn(v, bias);
+                a.y[(size_t)ent[t] * a.ldy + a.col0 + row_local] = v;
+            }
     }
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TL_TMEM_COLS) : "memory");
+}
+
+// Per expert, the (token, slot) pairs routed to it, in ascending order: entry = token * topk + slot.
+__global__ void tile_route_kernel(const int32_t *__restrict__ top, int ntok, int topk, int ne, int *__restrict__ cnt, int *__restrict__ list) {
+    const int e = blockIdx.x * blockDim.x + threadIdx.x;
+    if (e >= ne) return;
+    int c = 0;
+    for (int t = 0; t < ntok; t++)
+        for (int s = 0; s < topk; s++)
+            if (top[t * 8 + s] == e && c < TL_MAXTOK) list[e * TL_MAXTOK + c++] = t * topk + s;
+    cnt[e] = c;
+}
+
+// x[t] += w[t][k] * part[t * topk + k], k ascending (part already holds the bias): the fold of
+// down_combine_kernel, one thread per (token, row).
+__global__ void tile_combine_kernel(const float *__restrict__ part, const float *__restrict__ wts, int topk, int d, float *__restrict__ x) {
+    const int t = blockIdx.y, r = blockIdx.x * blockDim.x + threadIdx.x;
+    if (r >= d) return;
+    float s = x[(size_t)t * d + r];
+    for (int k = 0; k < topk; k++) s = __fadd_rn(s, __fmul_rn(wts[t * 8 + k], part[((size_t)t * topk + k) * d + r]));
+    x[(size_t)t * d + r] = s;
 }
 
 }  // namespace
 
 cudaError_t launch_mx_tile(MxDev w, int row0, int nrows, const int8_t *xq, const float *xs, int ntok, float *y, int ldy, DevState *state,
                            cudaStream_t st) {
-    TileArgs a{w, row0, nrows, xq, xs, ntok, y, ldy, state};
-    mx_tile_kernel<<<(nrows + TL_ROWS - 1) / TL_ROWS, 128, 0, st>>>(a);
+    TileArgs a{};
+    a.w = w; a.row0 = row0; a.nrows = nrows; a.src_div = 1; a.xq = xq; a.xs = xs; a.ntok = ntok; a.y = y; a.ldy = ldy; a.state = state;
+    mx_tile_kernel<<<dim3((nrows + TL_ROWS - 1) / TL_ROWS, 1), 128, 0, st>>>(a);
     return cudaGetLastError();
+}
+
+// All experts of one matrix kind against their routed entries (see TileArgs).
+cudaError_t launch_mx_tile_experts(MxDev w, int ne, int rows_per_expert, const int *cnt, const int *list, int src_div, const int8_t *xq,
+                                   const float *xs, const float *bias, float *y, int ldy, int col0, DevState *state, cudaStream_t st) {
+    TileArgs a{};
+    a.w = w; a.row0 = 0; a.nrows = rows_per_expert; a.rows_per_expert = rows_per_expert; a.cnt = cnt; a.list = list; a.src_div = src_div;
+    a.xq = xq; a.xs = xs; a.bias = bias; a.y = y; a.ldy = ldy; a.col0 = col0; a.state = state;
+    mx_tile_kernel<<<dim3((rows_per_expert + TL_ROWS - 1) / TL_ROWS, ne), 128, 0, st>>>(a);
+    return cudaGetLastError();
+}
+
+void launch_tile_route(const int32_t *top, int ntok, int topk, int ne, int *cnt, int *list, cudaStream_t st) {
+    tile_route_kernel<<<(ne + 63) / 64, 64, 0, st>>>(top, ntok, topk, ne, cnt, list);
+}
+
+void launch_tile_combine(const float *part, const float *wts, int topk, int d, int ntok, float *x, cudaStream_t st) {
+    tile_combine_kernel<<<dim3((d + 255) / 256, ntok), 256, 0, st>>>(part, wts, topk, d, x);
 }
 
 }  // namespace brrr

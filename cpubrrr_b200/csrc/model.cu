@@ -134,6 +134,12 @@ struct brrr_model {
     EpCtx epc{};
     void *ep_buf = nullptr;
     std::vector<void *> ep_peers;
+    // scratch of the token-tile MoE step (allocated at first use): 16 tokens x top-k entries
+    int8_t *tl_xq = nullptr, *tl_hq = nullptr;
+    float *tl_xs = nullptr, *tl_hs = nullptr, *tl_logits = nullptr, *tl_wts = nullptr, *tl_gu = nullptr, *tl_part = nullptr;
+    int32_t *tl_top = nullptr;
+    int *tl_cnt = nullptr, *tl_list = nullptr;
+    unsigned int *tl_counter = nullptr;
     std::vector<void *> allocs;
 
     template <typename T> int alloc(T **p, size_t n) {
@@ -811,6 +817,44 @@ extern "C" int brrr_moe_ffn_step(brrr_model *m, int il, const float *d_xn, float
     if (d_top) CU(cudaMemcpyAsync(d_top, m->top, topk * sizeof(int32_t), cudaMemcpyDeviceToDevice, s));
     if (d_wts) CU(cudaMemcpyAsync(d_wts, m->wts, topk * sizeof(float), cudaMemcpyDeviceToDevice, s));
     CU(cudaStreamSynchronize(s));
+    return BRRR_OK;
+}
+
+// MoE FFN of one layer for a tile of up to 16 normalised tokens: per-token router (one launch),
+// routing lists per expert, then three grouped tensor-core matmuls (gate, up, down) that read every
+// needed expert matrix once for all its tokens, SwiGLU + Q8 per (token, slot), and the fold in slot
+// order.  Bit-identical to brrr_moe_ffn_step applied to the tokens one by one.
+extern "C" int brrr_moe_ffn_tile(brrr_model *m, int il, const float *d_xn, float *d_x, int ntok, int32_t *d_top, float *d_wts) {
+    if (!m || !d_xn || !d_x || il < 0 || il >= m->cfg.n_layer || ntok < 1 || ntok > 16) return BRRR_ERR_ARG;
+    if (m->ep) return BRRR_ERR_STATE;
+    CU(cudaSetDevice(m->device));
+    const brrr_cfg &c = m->cfg;
+    const int d = c.n_embd, nb = d / 32, topk = c.n_expert_used, ne = c.n_expert, np_ = 16 * topk;
+    if (!m->tl_xq) {
+        TRY(m->alloc(&m->tl_xq, (size_t)16 * d)); TRY(m->alloc(&m->tl_xs, (size_t)16 * nb));
+        TRY(m->alloc(&m->tl_logits, (size_t)16 * ne)); TRY(m->alloc(&m->tl_top, 16 * 8)); TRY(m->alloc(&m->tl_wts, 16 * 8));
+        TRY(m->alloc(&m->tl_counter, 16)); TRY(m->alloc(&m->tl_cnt, ne)); TRY(m->alloc(&m->tl_list, (size_t)ne * 16));
+        TRY(m->alloc(&m->tl_gu, (size_t)np_ * 2 * d)); TRY(m->alloc(&m->tl_hq, (size_t)np_ * d)); TRY(m->alloc(&m->tl_hs, (size_t)np_ * nb));
+        TRY(m->alloc(&m->tl_part, (size_t)np_ * d));
+        CU(cudaMemsetAsync(m->tl_counter, 0, 16 * sizeof(unsigned int), m->stream));
+    }
+    Layer &ly = m->L[il];
+    cudaStream_t s = m->stream;
+    launch_quant_q8(d_xn, ntok * d, m->tl_xq, m->tl_xs, s);
+    CUL(launch_ffn_in(d_xn, nullptr, c.rms_eps, d, ly.ginp, ly.ginp_b, ne, topk, m->tl_logits, m->tl_top, m->tl_wts, m->tl_counter, m->st, false, s, ntok));
+    launch_tile_route(m->tl_top, ntok, topk, ne, m->tl_cnt, m->tl_list, s);
+    CUL(launch_mx_tile_experts(ly.gate, ne, d, m->tl_cnt, m->tl_list, topk, m->tl_xq, m->tl_xs, ly.gate_b, m->tl_gu, 2 * d, 0, m->st, s));
+    CUL(launch_mx_tile_experts(ly.up, ne, d, m->tl_cnt, m->tl_list, topk, m->tl_xq, m->tl_xs, ly.up_b, m->tl_gu, 2 * d, d, m->st, s));
+    launch_swiglu_quant(m->tl_gu, ntok * topk, d, m->tl_hq, m->tl_hs, s);
+    CUL(launch_mx_tile_experts(ly.down, ne, d, m->tl_cnt, m->tl_list, 1, m->tl_hq, m->tl_hs, ly.down_b, m->tl_part, d, 0, m->st, s));
+    launch_tile_combine(m->tl_part, m->tl_wts, topk, d, ntok, d_x, s);
+    CU(cudaGetLastError());
+    if (d_top) CU(cudaMemcpy2DAsync(d_top, topk * sizeof(int32_t), m->tl_top, 8 * sizeof(int32_t), topk * sizeof(int32_t), ntok, cudaMemcpyDeviceToDevice, s));
+    if (d_wts) CU(cudaMemcpy2DAsync(d_wts, topk * sizeof(float), m->tl_wts, 8 * sizeof(float), topk * sizeof(float), ntok, cudaMemcpyDeviceToDevice, s));
+    CU(cudaStreamSynchronize(s));
+    uint32_t derr = 0;
+    CU(cudaMemcpy(&derr, &m->st->err, 4, cudaMemcpyDeviceToHost));
+    if (derr) { snprintf(g_cuda_err, sizeof g_cuda_err, "device wait timed out (code %u)", derr); return BRRR_ERR_STATE; }
     return BRRR_OK;
 }
 

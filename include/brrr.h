@@ -324,6 +324,13 @@ int brrr_rope_table(const brrr_cfg *cfg, float *out);
  * Replaces src/bin/engine_gpt2.rs:847-923. */
 int brrr_moe_ffn_step(brrr_model *m, int il, const float *d_xn, float *d_x, int32_t *d_top, float *d_wts);
 
+/* The same MoE FFN for a tile of 1..16 normalised tokens (d_xn [ntok][n_embd], d_x [ntok][n_embd]
+ * residuals, d_top / d_wts nullable [ntok][n_expert_used]): per-token router, then gate / up /
+ * down as grouped tensor-core matmuls (tcgen05) that read each selected expert once for all the
+ * tokens routed to it.  Bit-identical to brrr_moe_ffn_step applied token by token.  Replaces the MoE
+ * part of forward_tile_worker (src/bin/engine_gpt2.rs:1120-1250). */
+int brrr_moe_ffn_tile(brrr_model *m, int il, const float *d_xn, float *d_x, int ntok, int32_t *d_top, float *d_wts);
+
 /* Fill a device buffer with a synthetic tensor in its GGUF format (type 0 = f32, 30 = bf16,
  * 39 = MXFP4, 12 = Q4_K, 14 = Q6_K; nelems counts values). Same generator brrr_model_open_synth uses. */
 int brrr_synth_tensor(uint64_t seed, uint32_t layer, uint32_t kind, uint32_t type, uint64_t nelems, void *d_out, void *stream);
