@@ -14,7 +14,8 @@
 // warps read their 32 lanes of tensor memory (tcgen05.ld) and run the float chains, one thread per
 // row with 64 accumulators.
 //
-// This first version is serialised per block pair (decode -> MMA -> epilogue); operands are
+// This version is serialised per block pair inside a CTA (decode -> MMA -> epilogue; several CTAs
+// per SM overlap each other, and the next pair's operands are fetched one pair ahead); operands are
 // written to shared memory by the threads themselves in the canonical K-major no-swizzle layout
 // (8-row x 16-byte core matrices).
 #include "brrr_kernels.h"
@@ -134,12 +135,26 @@ __global__ void __launch_bounds__(128) mx_tile_kernel(TileArgs a) {
 #pragma unroll
     for (int i = 0; i < TL_N; i++) acc[i] = 0.0f;
 
+    // operands of a block pair are fetched one pair ahead, so their global-memory latency hides
+    // behind the tensor-core work and the epilogue of the current pair
+    const size_t srow = (size_t)(ent[bt] / a.src_div);
+    const bool b_live = bt < n_ent;
+    auto fetch_b = [&](int p, uint32_t &lo, uint32_t &hi, float &sc) {
+        const int b = 2 * p + bblk;
+        const uint32_t *xw = reinterpret_cast<const uint32_t *>(a.xq + (srow * nb + b) * 32);
+        lo = b_live ? xw[bl] : 0u; hi = b_live ? xw[4 + bl] : 0u;
+        sc = (b_live && bl == 0) ? a.xs[srow * nb + b] : 0.0f;
+    };
+    uint4 w0 = *reinterpret_cast<const uint4 *>(wrow), w1 = *reinterpret_cast<const uint4 *>(wrow + 16);
+    uint32_t e2 = *reinterpret_cast<const unsigned short *>(erow);
+    uint32_t xlo, xhi;
+    float xsc;
+    fetch_b(0, xlo, xhi, xsc);
+
     for (int p = 0; p < np; p++) {
         // ---- decode this row's two blocks into the four A tiles
-        const uint4 w0 = *reinterpret_cast<const uint4 *>(wrow + (size_t)p * MX_UNIT);        // lanes 0, 1: (blk0, blk1) words each
-        const uint4 w1 = *reinterpret_cast<const uint4 *>(wrow + (size_t)p * MX_UNIT + 16);   // lanes 2, 3
-        const uint32_t e2 = *reinterpret_cast<const unsigned short *>(erow + (size_t)p * MX_UNIT);
         const uint32_t wl[4][2] = {{w0.x, w0.y}, {w0.z, w0.w}, {w1.x, w1.y}, {w1.z, w1.w}};
+        const uint32_t e2c = e2;
 #pragma unroll
         for (int j = 0; j < 4; j++) {
 #pragma unroll
@@ -150,18 +165,11 @@ __global__ void __launch_bounds__(128) mx_tile_kernel(TileArgs a) {
                 *reinterpret_cast<uint2 *>(&a_tiles[2 * k + 1][off]) = make_uint2(brrr_prmt(N_LO, N_HI, wx), brrr_prmt(N_LO, N_HI, wx >> 16));
             }
         }
-        // ---- activations of the pair's two blocks into the B tiles (zero rows for absent tokens stay zero)
+        // ---- activations of the pair's two blocks into the B tiles (rows of absent tokens stay zero)
         {
-            const int b = 2 * p + bblk;
-            uint2 v = make_uint2(0u, 0u);
-            const size_t srow = (size_t)(ent[bt] / a.src_div);
-            if (bt < n_ent) {
-                const uint32_t *xw = reinterpret_cast<const uint32_t *>(a.xq + (srow * nb + b) * 32);
-                const int2 iv = mx_interleave(xw[bl], xw[4 + bl]);
-                v = make_uint2((uint32_t)iv.x, (uint32_t)iv.y);
-            }
-            *reinterpret_cast<uint2 *>(&b_tiles[bblk][b_off]) = v;
-            if (bl == 0) xs_pair[bblk][bt] = bt < n_ent ? a.xs[srow * nb + b] : 0.0f;
+            const int2 iv = mx_interleave(xlo, xhi);
+            *reinterpret_cast<uint2 *>(&b_tiles[bblk][b_off]) = make_uint2((uint32_t)iv.x, (uint32_t)iv.y);
+            if (bl == 0) xs_pair[bblk][bt] = xsc;
         }
         fence_proxy_async();               // generic-proxy writes above -> visible to the tensor core's reads
         __syncthreads();
@@ -176,23 +184,30 @@ __global__ void __launch_bounds__(128) mx_tile_kernel(TileArgs a) {
             }
             tl_commit(&bar);
         }
+        if (p + 1 < np) {                  // next pair's operands
+            w0 = *reinterpret_cast<const uint4 *>(wrow + (size_t)(p + 1) * MX_UNIT);
+            w1 = *reinterpret_cast<const uint4 *>(wrow + (size_t)(p + 1) * MX_UNIT + 16);
+            e2 = *reinterpret_cast<const unsigned short *>(erow + (size_t)(p + 1) * MX_UNIT);
+            fetch_b(p + 1, xlo, xhi, xsc);
+        }
         waiter.wait(&bar, (uint32_t)p & 1u);
         tl_fence_after();
         // ---- float chains: thread = row (tensor-memory lane), 64 columns per block
         const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
 #pragma unroll
         for (int k = 0; k < 2; k++) {
-            const float esc = tbl[k ? e2 >> 8 : e2 & 0xFFu];
+            const float esc = tbl[k ? e2c >> 8 : e2c & 0xFFu];
+            int d[4][16];
 #pragma unroll
-            for (int c = 0; c < TL_N; c += 16) {
-                int d[16];
-                tl_ld16(lane_addr + k * TL_N + c, d);
-                tl_wait_ld();
+            for (int c = 0; c < 4; c++) tl_ld16(lane_addr + k * TL_N + 16 * c, d[c]);
+            tl_wait_ld();
+#pragma unroll
+            for (int c = 0; c < 4; c++) {
 #pragma unroll
                 for (int t = 0; t < 4; t++) {
-                    const float s = __fmul_rn(esc, xs_pair[k][(c >> 2) + t]);
+                    const float s = __fmul_rn(esc, xs_pair[k][4 * c + t]);
 #pragma unroll
-                    for (int l = 0; l < 4; l++) acc[c + 4 * t + l] = __fmaf_rn((float)d[4 * t + l], s, acc[c + 4 * t + l]);
+                    for (int l = 0; l < 4; l++) acc[16 * c + 4 * t + l] = __fmaf_rn((float)d[c][4 * t + l], s, acc[16 * c + 4 * t + l]);
                 }
             }
         }
