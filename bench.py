@@ -177,6 +177,57 @@ def cpu_baseline_and_parity(eng_tokens, first_tok, nsteps, qwen=False):
            {"tokens_checked": nsteps + 1, "identical": bool(ok)}
 
 
+def run_moe_tile(args):
+    """--workload moe-tile: the MoE FFN stage of the gpt-oss-20b layers on token tiles (batched
+    decode / prefill building block): per-token kernels against the grouped tcgen05 matmuls at tile
+    sizes 1, 4 and 16.  One step = one pass of a tile through the MoE FFN of all 24 layers."""
+    import ctypes as C
+    import torch
+    import cpubrrr_b200 as B
+    torch.cuda.set_device(0)
+    dev = torch.device("cuda", 0)
+    eng = B.Engine.synth(B.gptoss_20b_cfg() if args.layers == 24 else B.make_cfg(2880, args.layers, 64, 8, 32, 4, 32768), SEED)
+    L = B.lib()
+    nl, d = eng.cfg.n_layer, eng.cfg.n_embd
+    P = lambda t: C.c_void_p(t.data_ptr())
+    g = torch.Generator(device=dev); g.manual_seed(SEED)
+    rows = []
+    for ntok in (1, 4, 16):
+        xn = torch.randn((ntok, d), device=dev, generator=g)
+        x = torch.zeros((ntok, d), device=dev)
+
+        def tile_pass():
+            for il in range(nl):
+                B._lib.check(L.brrr_moe_ffn_tile(eng._h, il, P(xn), P(x), ntok, None, None), "brrr_moe_ffn_tile")
+
+        def token_pass():
+            for il in range(nl):
+                for t in range(ntok):
+                    eng.moe_ffn_step(il, P(xn[t]), P(x[t]))
+
+        res = {}
+        for name, fn in (("tile_tcgen05", tile_pass), ("per_token", token_pass)):
+            for _ in range(max(args.warmup // 4, 1)):
+                fn()
+            torch.cuda.synchronize()
+            reps = max(args.steps // 16, 3)
+            t0 = time.perf_counter()
+            for _ in range(reps):
+                fn()
+            torch.cuda.synchronize()
+            dt = (time.perf_counter() - t0) / reps
+            res[name] = {"ms_per_pass": 1000 * dt, "token_layers_per_s": ntok * nl / dt}
+        rows.append({"tile_tokens": ntok, **res, "speedup": res["per_token"]["ms_per_pass"] / res["tile_tcgen05"]["ms_per_pass"]})
+    best = rows[-1]["tile_tcgen05"]
+    print(json.dumps({"metric": "MoE FFN stage token-layers/s (gpt-oss-20b layers, token tiles on tcgen05)", "value": best["token_layers_per_s"],
+                      "unit": "token-layers/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "ms_per_step": best["ms_per_pass"],
+                      "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "int8xfp4->int32 (tcgen05 kind::i8),f32",
+                      "data": "synthetic", "config": {"workload": "gpt-oss-20b MoE FFN stage on tiles of 1/4/16 tokens, all layers, host-synchronous calls",
+                                                      "l2": "inputs larger than L2 (every pass streams the selected experts of all layers)"},
+                      "tiles": rows}), flush=True)
+    eng.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -185,13 +236,16 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline / parity leg")
     ap.add_argument("--no-stages", action="store_true", help="skip the per-kernel-class timing")
-    ap.add_argument("--workload", default="gptoss20b", choices=["gptoss20b", "gptoss120b", "qwen3-30b-a3b"],
+    ap.add_argument("--workload", default="gptoss20b", choices=["gptoss20b", "gptoss120b", "qwen3-30b-a3b", "moe-tile"],
                     help="gptoss20b is the benchmark workload; gptoss120b is the expert-parallel configuration; qwen3-30b-a3b measures the reference's second engine")
     ap.add_argument("--parallel", default="replicas", choices=["replicas", "ep"],
                     help="N > 1: independent replicas (weak scaling, default) or one sequence with the experts sharded over the ranks (strong scaling)")
     ap.add_argument("--layers", type=int, default=24, help="profiling aid: fewer layers (not the benchmark workload)")
     ap.add_argument("--vocab", type=int, default=201088, help="profiling aid: smaller vocabulary (not the benchmark workload)")
     args = ap.parse_args()
+    if args.workload == "moe-tile":
+        run_moe_tile(args)
+        return
     qwen = args.workload == "qwen3-30b-a3b"
     big = args.workload == "gptoss120b"
     if qwen:
@@ -329,10 +383,10 @@ def main():
                    "bytes_per_launch": by, "gbs": by / t / 1e6 if t > 0 else 0.0} for nm, t, by, n in st]
         out["stages"] = stages
         # dram__bytes_read+write per launch from the committed ncu capture (profiles/
-        # layer_kernels_ncu_set_full_small_case.md); the layer kernels' shapes do not depend on the
-        # layer count or vocabulary of the captured case.
-        ncu_traffic = {"norm_gate_up_swiglu_mxfp4": 35.43e6, "down_combine_mxfp4": 17.74e6, "norm_qkv_gemv": 16.69e6,
-                       "oproj_gemv": 13.33e6, "norm_router_topk": 0.49e6, "attention": 0.07e6}
+        # gptoss20b_layer_kernels_ncu_full_small_case.md); the layer kernels' shapes do not depend on
+        # the layer count or vocabulary of the captured case.
+        ncu_traffic = {"norm_gate_up_swiglu_mxfp4": 35.42e6, "down_combine_mxfp4": 17.74e6, "norm_qkv_gemv": 16.68e6,
+                       "oproj_gemv": 13.32e6, "norm_router_topk": 0.49e6, "attention": 0.06e6}
         top = max(stages, key=lambda s: s["share"])
         out["roofline"] = {"bound": "hbm", "kernel": top["kernel"], "achieved": top["gbs"], "peak": peak, "unit": "GB/s",
                            "frac": top["gbs"] / peak, "traffic": ncu_traffic.get(top["kernel"]), "peak_kind": peak_kind,
