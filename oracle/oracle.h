@@ -8,6 +8,14 @@
  * (b) dequantise-then-dot in float64 within the reference's own verifier thresholds, and
  * (c) the reference's invariants and constants.  Float summation orders follow the NEON lane
  * structure of the reference exactly; integer block dots are exact.
+ * The MoE FFN step additionally agrees, to int8-activation quantisation error, with the output of the
+ * reference's float64 numpy statement (scripts/ffn_reference.py) run on a seeded synthetic layer
+ * (tests/golden/ffn_ref, made by tests/golden/make_ffn_ref_golden.py).
+ * The K-quant dots of the qwen3moe path (oracle_qwen.c) ARE pinned by reference-produced data: the
+ * reference's plain-C versions (metal/engine_metal.m:589-643), compiled from the reference checkout
+ * into _ref/ by the Makefile, produced tests/golden/kq_ref_dots.json, which the oracle matches bit
+ * for bit (Q6_K directly; Q4_K through its integer accumulators, the C code using the other of the
+ * reference's two float associations).  The forward passes above the kernels are unpinned.
  */
 #ifndef ORACLE_H
 #define ORACLE_H

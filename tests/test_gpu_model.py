@@ -161,6 +161,31 @@ def test_moe_ffn_step_config1_shape(brrr, orc, dev):
     eng.close()
 
 
+def test_moe_ffn_step_against_reference_script_fixture(brrr, dev):
+    """The CUDA MoE FFN step against the output of the reference's float64 numpy statement
+    (scripts/ffn_reference.py; fixture tests/golden/ffn_ref, made by tests/golden/make_ffn_ref_golden.py)
+    on the seeded one-layer model of the gpt-oss-20b layer shape: same experts in the same order,
+    softmax weights to float rounding, output to int8-activation quantisation error (the reference's
+    criterion for that, src/bin/ffn_quant.rs:119-129, is cosine > 0.999)."""
+    import ctypes as C
+    import os
+    import torch
+    g = os.path.join(os.path.dirname(__file__), "golden", "ffn_ref")
+    fx = {k: np.load(os.path.join(g, k + ".npy")) for k in ("x", "yref", "top", "w")}
+    eng = brrr.Engine.synth(brrr.make_cfg(2880, 1, 64, 8, 32, 4, 256), 77)
+    dxn = to_dev(fx["x"].astype(np.float32), dev)
+    dy = torch.zeros(2880, dtype=torch.float32, device=dev)
+    dt = torch.zeros(4, dtype=torch.int32, device=dev); dw = torch.zeros(4, dtype=torch.float32, device=dev)
+    torch.cuda.synchronize()
+    eng.moe_ffn_step(0, C.c_void_p(dxn.data_ptr()), C.c_void_p(dy.data_ptr()), C.c_void_p(dt.data_ptr()), C.c_void_p(dw.data_ptr()))
+    assert dt.cpu().numpy().tolist() == fx["top"].tolist()
+    assert np.max(np.abs(dw.cpu().numpy() - fx["w"])) < 2e-5
+    y, r = dy.cpu().numpy().astype(np.float64), fx["yref"].astype(np.float64)
+    assert float(y @ r) / (np.linalg.norm(y) * np.linalg.norm(r)) > 0.9999
+    assert np.linalg.norm(y - r) / np.linalg.norm(r) < 2e-2
+    eng.close()
+
+
 def test_full_size_gptoss20b_parity_and_properties(brrr, orc):
     """gpt-oss-20b architecture at full size (24 layers, vocab 201088): a short prompt and greedy
     steps against the oracle, then size-independent properties over a longer device-chained run."""
