@@ -101,6 +101,8 @@ SIGNATURES = {
     "brrr_attn_decode": (_I, [_P, _P, _P, _P, _P, _I, _I, _I, _I, _P, _P, _P, _P]),
     "brrr_rope_table": (_I, [C.POINTER(Cfg), _P]),
     "brrr_moe_ffn_step": (_I, [_P, _I, _P, _P, _P, _P]),
+    "brrr_moe_ffn_step_tc": (_I, [_P, _I, _P, _P, _P, _P]),
+    "brrr_model_uses_tensor_experts": (_I, [_P]),
     "brrr_synth_tensor": (_I, [C.c_uint64, C.c_uint32, C.c_uint32, C.c_uint32, C.c_uint64, _P, _P]),
     "brrr_expf": (_I, [_P, _I, _P, _P]),
 }

@@ -18,7 +18,7 @@ OBJ = os.path.join(HERE, "_obj")
 LIB = os.path.join(HERE, "libbrrr.so")
 EXE = os.path.join(HERE, "brrr_engine")
 
-SOURCES = ["kernels_small.cu", "kernels_q8.cu", "kernels_mx.cu", "kernels_router.cu", "kernels_attn.cu", "kernels_ep.cu", "kernels_tile.cu", "kernels_kq.cu", "kernels_qwen.cu", "qwen_model.cu",
+SOURCES = ["kernels_small.cu", "kernels_q8.cu", "kernels_mx.cu", "kernels_router.cu", "kernels_attn.cu", "kernels_ep.cu", "kernels_tile.cu", "kernels_mxt.cu", "kernels_kq.cu", "kernels_qwen.cu", "qwen_model.cu",
            "model.cu", "capi_stage.cu", "capi_noalloc.cu", "host_text.cpp"]
 
 NVCC_FLAGS = [

@@ -73,6 +73,36 @@ cudaError_t launch_gate_up(MxDev gate, MxDev up, const float *gate_b, const floa
 cudaError_t launch_down_combine(MxDev down, const float *down_b, const int32_t *top, const float *wts, const float *est, int ne, int sabotage,
                                 int topk, int d, const int8_t *hq, const float *hs, float *x, DevState *state, bool pdl, cudaStream_t st);
 
+// ---- single-token expert matvecs on the tensor cores in native fp4 (kernels_mxt.cu)
+// Tile units: [expert][tile of 128 rows][block pair][4096 B operand image | 128 x 2 e8m0 bytes].
+constexpr int MXT_UNIT = 4352;
+constexpr int MXT_UNIT_EXPS = 4096;
+struct MxtDev {
+    uint8_t *data;
+    int tiles_per_expert, np;
+};
+size_t mxt_bytes(int experts, int tiles_per_expert, int np);
+// b.data == nullptr: tiles of 128 rows of a (rows past the end are zero); else rows 0-63 of a tile
+// come from a and rows 64-127 from b (same 64 row indices)
+void launch_mxt_pack(MxDev a, MxDev b, int experts, int rows_per_expert, MxtDev out, cudaStream_t st);
+// The activation enters as its digit-plane operand image (brrr_mxt.cuh; [blocks / 2][768] bytes, zero
+// except for the words its producer writes) and its block scales.
+void launch_xt_bimg(const int8_t *xq, int nb, uint8_t *bimg, cudaStream_t st);
+// same results, bit for bit, as launch_gate_up / launch_down_combine on the same Q8 activation;
+// himg: [topk][blocks / 2][768] operand images of h for launch_down_t
+cudaError_t launch_gate_up_t(MxtDev gu, const float *gate_b, const float *up_b, const int32_t *top, const float *est, int ne, int topk,
+                             int sabotage, int d, const uint8_t *ximg, const float *xs, int8_t *hq, float *hs, uint8_t *himg, DevState *state,
+                             bool pdl, cudaStream_t st);
+// part: [topk][tiles_per_expert * 128] floats of scratch; counter: [tiles_per_expert] words, zero before the first launch.
+// wts != nullptr (exact routing in top/wts, est == nullptr): the last CTA of a row tile folds it onto x.
+// wts == nullptr: slot s is the s-th largest entry of est (or top[s]); only part[] is written and
+// launch_down_fold finishes the step once the exact routing is there.
+cudaError_t launch_down_fold(const int32_t *top, const float *wts, const float *est, int ne, int topk, int sabotage, int d, const float *part,
+                             const float *down_b, float *x, DevState *state, bool pdl, cudaStream_t st);
+cudaError_t launch_down_t(MxtDev down, const float *down_b, const int32_t *top, const float *wts, const float *est, int ne, int topk,
+                          int sabotage, int d, const uint8_t *himg, const float *hs, float *x, float *part, uint32_t *counter, DevState *state,
+                          bool pdl, cudaStream_t st);
+
 // ---- token-tile matmul on tcgen05 tensor cores (kernels_tile.cu): y[t][r] = row (row0 + r) . activation t,
 // t < ntok <= 16, every value bit-identical to launch_mx_gemv on token t alone
 cudaError_t launch_mx_tile(MxDev w, int row0, int nrows, const int8_t *xq, const float *xs, int ntok, float *y, int ldy, DevState *state,
@@ -117,7 +147,9 @@ cudaError_t launch_ffn_in(const float *x_in, const float *norm_w, float eps, int
 // (speculative routing): est[ne] receives the estimated logits, xq_out/xs_out the Q8 image of the
 // normalised vector (each CTA writes a share).
 cudaError_t launch_router_hint(const float *x_in, const float *norm_w, float eps, int d, const float *Wt, const float *b, int ne, int topk,
-                               float *est, int8_t *xq_out, float *xs_out, DevState *state, bool pdl, cudaStream_t st);
+                               float *est, int8_t *xq_out, float *xs_out, DevState *state, bool pdl, cudaStream_t st,
+                               uint8_t *bimg_out = nullptr);
+// bimg_out (nullable): also the operand image of the quantised vector for the tensor-core expert kernels
 
 // ---- attention (kernels_attn.cu)
 // KV cache layout [n_head_kv][BRRR_MAXSEQ][64].  pos is read from state when state != nullptr,

@@ -79,6 +79,24 @@ struct Waiter {
         if (err) atomicCAS(err, (uint32_t)DEV_ERR_NONE, (uint32_t)DEV_ERR_COPY_TIMEOUT);
         return false;
     }
+    // The same bounded wait for a thread that is not on the critical path (a producer or an issuing
+    // thread that runs ahead of its consumers): it sleeps between polls, because a thread that
+    // polls a barrier back to back keeps the shared-memory pipeline busy and slows every other
+    // shared-memory access of the SM.
+    __device__ __forceinline__ bool wait_relaxed(uint64_t *bar, uint32_t parity) {
+        if (dead) return false;
+        if (mbar_test_wait(bar, parity)) return true;
+        const long long t0 = clock64();
+        do {
+            for (int i = 0; i < 64; i++) {
+                __nanosleep(32);
+                if (mbar_test_wait(bar, parity)) return true;
+            }
+        } while (clock64() - t0 < WAIT_CYCLES);
+        dead = true;
+        if (err) atomicCAS(err, (uint32_t)DEV_ERR_NONE, (uint32_t)DEV_ERR_COPY_TIMEOUT);
+        return false;
+    }
 };
 
 // Programmatic dependent launch.  pdl_wait(): block until the preceding kernel in the stream has

@@ -1,0 +1,529 @@
+// Single-token MXFP4 expert matvecs on the 5th-generation tensor cores in their native 4-bit format
+// (tcgen05.mma kind::mxf4.block_scale): the e2m1 codes of the GGUF blocks are the tensor-core operand
+// as they are, so the weight bytes go from HBM to shared memory by bulk copy and from there straight
+// into the MMA, with no decode instructions at all.
+//
+// Arithmetic (bit-identical to the integer-unit kernels of kernels_mx.cu).  A row's value is four
+// lane chains, chain j accumulating fma(float(t_j(b)), 2^(e_b-128) * xs[b], acc) over the 32-blocks
+// b, where t_j(b) is the exact integer dot of the lane's 8 doubled e2m1 values with the lane's 8
+// activation bytes.  The tensor core supplies t_j(b):
+//   * an activation byte x in [-127, 127] is written as 49 a + 7 b + c with digits in [-3, 3];
+//     twice a digit (0, +-2, +-4, +-6) is an e2m1 value, and (true e2m1 value) x (twice the digit)
+//     = (doubled e2m1 value) x digit, so the three digit planes give three exact partial sums;
+//   * one MMA covers a block pair (K = 64): operand A = 128 weight rows x 64 codes, operand B = 24
+//     columns (digit plane t, block of the pair q, lane j), each holding the plane's codes of the 8
+//     positions of lane j in block q and zero elsewhere; all block scales are 1 (ue8m0 0x7F);
+//   * every product and partial sum is a small dyadic number (|sum| <= 8 * 12 * 3), exact in the
+//     f32 accumulator, and t_j(b) = fma(D_a, 49, fma(D_b, 7, D_c)) is exact as well.
+// The four epilogue warps read the 24 accumulator columns of their rows from tensor memory
+// (tcgen05.ld) and run the float chains, one thread per row.
+//
+// Layout ("tile units").  A tile is 128 matrix rows; its unit for block pair p is the 4096-byte
+// shared-memory image of operand A in the canonical K-major no-swizzle layout (16-byte chunk of
+// (row m, block q) at q * 2048 + (m / 8) * 128 + (m % 8) * 16, the chunk being the 16 nibble bytes
+// of the GGUF block) followed by 128 x 2 e8m0 bytes.  The units of a tile are contiguous, so any run
+// of them is one bulk copy.  Gate and up share tiles (rows 0-63 gate, 64-127 up, same 64 outputs),
+// so the SwiGLU and the Q8 quantiser of h run in the same CTA.
+//
+// Operand B (brrr_mxt.cuh) is written once per activation by the kernel that quantises it (the
+// routing-estimate kernel for the token, the gate/up epilogue for h) and bulk-copied by every CTA.
+//
+// Pipeline per CTA: warp 4 issues the bulk copies into a ring of stages, one thread of warp 5 issues
+// the MMAs into a ring of 8 accumulator regions of tensor memory, warps 0-3 drain them two pairs at
+// a time with the next loads in flight.  Every wait is bounded.
+#include "brrr_kernels.h"
+#include "brrr_block.cuh"
+#include "brrr_tma.cuh"
+#include "brrr_mx.cuh"
+#include "brrr_mxt.cuh"
+
+namespace brrr {
+
+namespace {
+
+constexpr int XT_CH = 4;                 // block pairs per ring stage = per round of the pipeline
+constexpr int XT_REGION_COLS = XT_CH * XT_N;   // accumulator region = one round = 96 tensor-memory columns
+constexpr int XT_REGIONS = 2;
+constexpr uint32_t XT_TMEM_COLS = 256;   // 2 regions + 64 columns of unit scale factors
+constexpr int XT_SF_COL = XT_REGIONS * XT_REGION_COLS;
+constexpr int XT_THREADS = 192;
+#ifdef BRRR_TIMELINE
+#define XT_T0() long long xt_t0_ = clock64()
+#define XT_ACC(v) do { long long xt_t1_ = clock64(); (v) += xt_t1_ - xt_t0_; xt_t0_ = xt_t1_; } while (0)
+#define XT_STAMP(state, i) do { if ((state) && blockIdx.x == BRRR_STAMP_BX && blockIdx.y == 0) (state)->stamps[i] = clock64(); } while (0)
+#else
+#define XT_T0() do { } while (0)
+#define XT_ACC(v) do { } while (0)
+#define XT_STAMP(state, i) do { } while (0)
+#endif
+
+// ---------------------------------------------------------------- pack: 16-row units -> tile units
+struct PackArgs {
+    MxDev a, b;              // b.data == nullptr: one matrix, 128 rows per tile; else rows 0-63 from a, 64-127 from b
+    int rows_per_expert;     // logical rows of one expert in a (and b)
+    int tiles_per_expert;
+    MxtDev out;
+};
+
+__global__ void mxt_pack_kernel(PackArgs p, size_t total_words) {
+    size_t idx = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total_words) return;
+    // word index within the destination: [tile][pair][1024 words of operand A | 64 words of exponents]
+    const int np = p.out.np;
+    const size_t unit = idx / (MXT_UNIT / 4);
+    const int w = (int)(idx % (MXT_UNIT / 4));
+    const int pair = (int)(unit % np);
+    const size_t tile = unit / np;
+    const int e = (int)(tile / p.tiles_per_expert), t = (int)(tile % p.tiles_per_expert);
+    // source unit and row within it of tile row m; nullptr for rows past the end of the matrix
+    auto locate = [&](int m, int &rl) -> const uint8_t * {
+        const MxDev &mat = (p.b.data && m >= 64) ? p.b : p.a;
+        const int r = p.b.data ? t * 64 + (m & 63) : t * 128 + m;
+        if (r >= p.rows_per_expert) return nullptr;
+        const int row = e * p.rows_per_expert + r;
+        rl = row & 15;
+        return mat.data + mx_unit_off(row >> 4, pair, np);
+    };
+    uint32_t v = 0;
+    if (w < 1024) {
+        const int q = w >> 9, rem = w & 511, m = (rem >> 5) * 8 + ((rem >> 2) & 7), j = rem & 3;
+        int rl = 0;
+        const uint8_t *u = locate(m, rl);
+        if (u) v = *reinterpret_cast<const uint32_t *>(u + rl * 32 + j * 8 + q * 4);
+    } else {
+        for (int k = 0; k < 2; k++) {                 // rows m0, m0 + 1: two exponent bytes each
+            int rl = 0;
+            const uint8_t *u = locate((w - 1024) * 2 + k, rl);
+            if (u) v |= (uint32_t)*reinterpret_cast<const unsigned short *>(u + MX_UNIT_EXPS + rl * 2) << (16 * k);
+        }
+    }
+    reinterpret_cast<uint32_t *>(p.out.data + unit * MXT_UNIT)[w] = v;
+}
+
+// ---------------------------------------------------------------- tensor-core plumbing
+// shared-memory matrix descriptor: K-major, no swizzle; core matrix = 8 rows x 16 bytes, 128 bytes
+// apart along M/N, `lbo` bytes apart along K
+// block-scaled instruction descriptor: A = B = e2m1 (format 1), both K-major, N / 8 at bit 17,
+// ue8m0 scales (bit 23), M / 16 at bit 24, scale-factor ids 0, K = 64
+constexpr uint32_t XT_IDESC = (1u << 7) | (1u << 10) | ((uint32_t)(XT_N >> 3) << 17) | (1u << 23) | ((128u >> 4) << 24);
+
+__device__ __forceinline__ void xt_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t tmem_sfa, uint32_t tmem_sfb) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::mxf4.block_scale.block32 [%0], %1, %2, %3, [%5], [%6], p;\n\t}"
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(XT_IDESC), "r"(0u), "r"(tmem_sfa), "r"(tmem_sfb)
+        : "memory");
+}
+__device__ __forceinline__ void xt_commit(uint64_t *bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void xt_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void xt_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// The 96 accumulator columns of a region (four block pairs) of this thread's row, asynchronously:
+// the registers are valid only after xt_wait_ld96 on the same array
+__device__ __forceinline__ void xt_ld96(uint32_t taddr, uint32_t *v) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x64.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32,%33,%34,%35,%36,%37,%38,%39,%40,%41,%42,%43,%44,%45,%46,%47,%48,%49,%50,%51,%52,%53,%54,%55,%56,%57,%58,%59,%60,%61,%62,%63}, [%64];"
+                 : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]), "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]), "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]), "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31]), "=r"(v[32]), "=r"(v[33]), "=r"(v[34]), "=r"(v[35]), "=r"(v[36]), "=r"(v[37]), "=r"(v[38]), "=r"(v[39]), "=r"(v[40]), "=r"(v[41]), "=r"(v[42]), "=r"(v[43]), "=r"(v[44]), "=r"(v[45]), "=r"(v[46]), "=r"(v[47]), "=r"(v[48]), "=r"(v[49]), "=r"(v[50]), "=r"(v[51]), "=r"(v[52]), "=r"(v[53]), "=r"(v[54]), "=r"(v[55]), "=r"(v[56]), "=r"(v[57]), "=r"(v[58]), "=r"(v[59]), "=r"(v[60]), "=r"(v[61]), "=r"(v[62]), "=r"(v[63])
+                 : "r"(taddr) : "memory");
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(v[64]), "=r"(v[65]), "=r"(v[66]), "=r"(v[67]), "=r"(v[68]), "=r"(v[69]), "=r"(v[70]), "=r"(v[71]), "=r"(v[72]), "=r"(v[73]), "=r"(v[74]), "=r"(v[75]), "=r"(v[76]), "=r"(v[77]), "=r"(v[78]), "=r"(v[79]), "=r"(v[80]), "=r"(v[81]), "=r"(v[82]), "=r"(v[83]), "=r"(v[84]), "=r"(v[85]), "=r"(v[86]), "=r"(v[87]), "=r"(v[88]), "=r"(v[89]), "=r"(v[90]), "=r"(v[91]), "=r"(v[92]), "=r"(v[93]), "=r"(v[94]), "=r"(v[95])
+                 : "r"(taddr + 64) : "memory");
+}
+// Wait for the loads in flight; the registers pass through the statement so that no use of them can
+// be scheduled before it.
+__device__ __forceinline__ void xt_wait_ld96(uint32_t *v) {
+    asm volatile("tcgen05.wait::ld.sync.aligned;"
+                 : "+r"(v[0]), "+r"(v[1]), "+r"(v[2]), "+r"(v[3]), "+r"(v[4]), "+r"(v[5]), "+r"(v[6]), "+r"(v[7]), "+r"(v[8]), "+r"(v[9]), "+r"(v[10]), "+r"(v[11]), "+r"(v[12]), "+r"(v[13]), "+r"(v[14]), "+r"(v[15]), "+r"(v[16]), "+r"(v[17]), "+r"(v[18]), "+r"(v[19]), "+r"(v[20]), "+r"(v[21]), "+r"(v[22]), "+r"(v[23]), "+r"(v[24]), "+r"(v[25]), "+r"(v[26]), "+r"(v[27]), "+r"(v[28]), "+r"(v[29]), "+r"(v[30]), "+r"(v[31]), "+r"(v[32]), "+r"(v[33]), "+r"(v[34]), "+r"(v[35]), "+r"(v[36]), "+r"(v[37]), "+r"(v[38]), "+r"(v[39]), "+r"(v[40]), "+r"(v[41]), "+r"(v[42]), "+r"(v[43]), "+r"(v[44]), "+r"(v[45]), "+r"(v[46]), "+r"(v[47]), "+r"(v[48]), "+r"(v[49]), "+r"(v[50]), "+r"(v[51]), "+r"(v[52]), "+r"(v[53]), "+r"(v[54]), "+r"(v[55]), "+r"(v[56]), "+r"(v[57]), "+r"(v[58]), "+r"(v[59]), "+r"(v[60]), "+r"(v[61]), "+r"(v[62]), "+r"(v[63]), "+r"(v[64]), "+r"(v[65]), "+r"(v[66]), "+r"(v[67]), "+r"(v[68]), "+r"(v[69]), "+r"(v[70]), "+r"(v[71]), "+r"(v[72]), "+r"(v[73]), "+r"(v[74]), "+r"(v[75]), "+r"(v[76]), "+r"(v[77]), "+r"(v[78]), "+r"(v[79]), "+r"(v[80]), "+r"(v[81]), "+r"(v[82]), "+r"(v[83]), "+r"(v[84]), "+r"(v[85]), "+r"(v[86]), "+r"(v[87]), "+r"(v[88]), "+r"(v[89]), "+r"(v[90]), "+r"(v[91]), "+r"(v[92]), "+r"(v[93]), "+r"(v[94]), "+r"(v[95])
+                 :: "memory");
+}
+__device__ __forceinline__ void xt_bar_epi() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+
+// Waits of the pipeline loops.  The loops are executed by one warp per scheduler, so their code
+// has to stay small enough for the instruction cache next to the scheduler: the common case (phase
+// already complete) is one probe inline, everything else is out of line.  Bounded like Waiter::wait;
+// returns false (after recording the error) when the wait ran out.
+__device__ __noinline__ bool xt_wait_slow(uint64_t *bar, uint32_t parity, uint32_t *err, bool sleep) {
+    if (err && *reinterpret_cast<volatile uint32_t *>(err) != 0u) return false;      // a wait has already failed: do not wait again
+    const long long t0 = clock64();
+    do {
+        for (int i = 0; i < 64; i++) {
+            if (sleep) __nanosleep(32);
+            if (sleep ? mbar_test_wait(bar, parity) : mbar_try_wait(bar, parity)) return true;
+        }
+    } while (clock64() - t0 < WAIT_CYCLES);
+    if (err) atomicCAS(err, (uint32_t)DEV_ERR_NONE, (uint32_t)DEV_ERR_COPY_TIMEOUT);
+    return false;
+}
+__device__ __forceinline__ void xt_wait(uint64_t *bar, uint32_t parity, uint32_t *err, bool sleep = false) {
+    if (!mbar_test_wait(bar, parity)) xt_wait_slow(bar, parity, err, sleep);
+}
+
+// Operand image of an activation that some other kernel quantised (stage-level entry points).
+__global__ void xt_bimg_kernel(const int8_t *__restrict__ xq, int nb, uint8_t *bimg) {
+    const int b = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5), lane = threadIdx.x & 31;
+    if (b >= nb) return;
+    xt_emit_block((int)xq[b * 32 + lane], lane, b, bimg);
+}
+
+// ---------------------------------------------------------------- the two expert kernels
+struct XtArgs {
+    MxtDev w;                   // gate|up tiles, or down tiles
+    const float *bias_a;        // gate bias, or down bias       [expert][d]
+    const float *bias_b;        // up bias
+    const int32_t *top;         // exact routing (used when est == nullptr)
+    const float *wts;           // down: nullable, see launch_down_t
+    const float *est;           // nullable: router estimate; slot s belongs to its s-th largest entry
+    int ne, topk, sabotage, d;
+    const uint8_t *bimg;        // operand image of the activation: gate/up [np][768]; down [slot][np][768]
+    const float *xs;            // its block scales:                gate/up [blocks];   down [slot][blocks]
+    int8_t *hq;                 // gate/up outputs: Q8 of h per slot, its scales, its operand image
+    float *hs;
+    uint8_t *himg;
+    float *x;                   // down: residual stream, updated in place
+    float *part;                // down: [topk][tiles * 128] row sums before bias
+    uint32_t *counter;          // down: [tiles] arrival counters, zero between launches
+    DevState *state;
+    int stages;
+};
+
+struct XtShared {
+    unsigned char *ring, *bimg;
+    float *xsc, *tbl;
+    uint64_t *full, *empty, *dfull, *dempty, *bfull;
+};
+
+// One block pair of one row: the 8 exact lane dots from the three digit planes, then the two
+// blocks' fused multiply-adds of the four chains, in block order.
+__device__ __forceinline__ void xt_pair(const uint32_t *v, float s0, float s1, float &acc0, float &acc1, float &acc2, float &acc3) {
+    float tq[8];
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+        tq[i] = __fmaf_rn(__uint_as_float(v[i]), 49.0f, __fmaf_rn(__uint_as_float(v[8 + i]), 7.0f, __uint_as_float(v[16 + i])));
+    acc0 = __fmaf_rn(tq[0], s0, acc0); acc1 = __fmaf_rn(tq[1], s0, acc1); acc2 = __fmaf_rn(tq[2], s0, acc2); acc3 = __fmaf_rn(tq[3], s0, acc3);
+    acc0 = __fmaf_rn(tq[4], s1, acc0); acc1 = __fmaf_rn(tq[5], s1, acc1); acc2 = __fmaf_rn(tq[6], s1, acc2); acc3 = __fmaf_rn(tq[7], s1, acc3);
+}
+
+template <bool DOWN>
+__global__ void __launch_bounds__(XT_THREADS) xt_expert_kernel(XtArgs a) {
+    extern __shared__ __align__(128) unsigned char smraw[];
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int np = a.w.np, nb = np * 2;
+    const int t = blockIdx.x, ei = blockIdx.y;
+    const int nchunks = (np + XT_CH - 1) / XT_CH;
+    const size_t stage_bytes = (size_t)XT_CH * MXT_UNIT;
+    XtShared sh;
+    sh.ring = smraw;
+    sh.bimg = smraw + stage_bytes * a.stages;
+    sh.xsc = reinterpret_cast<float *>(sh.bimg + (size_t)np * XT_B_PAIR);
+    sh.tbl = sh.xsc + nb;
+    sh.full = reinterpret_cast<uint64_t *>(sh.tbl + 256);
+    sh.empty = sh.full + a.stages;
+    sh.dfull = sh.empty + a.stages;
+    sh.dempty = sh.dfull + XT_REGIONS;
+    sh.bfull = sh.dempty + XT_REGIONS;
+    __shared__ uint32_t tmem_base_sh;
+    __shared__ int sel[8];
+    __shared__ float lg[256];
+    __shared__ float gu_s[2][64];
+    __shared__ int last_sh;
+    uint32_t *err = a.state ? &a.state->err : nullptr;
+    constexpr int SB = DOWN ? 128 : 96;          // clock stamps of timeline builds
+    (void)SB;
+    BRRR_STAMP(a.state, SB);
+
+    // ---- set-up that needs nothing from the kernels before
+    mx_fill_scale_table(sh.tbl, tid, XT_THREADS);
+    if (tid == 0) {
+        for (int s = 0; s < a.stages; s++) { mbar_init(&sh.full[s], 1); mbar_init(&sh.empty[s], 4); }
+        for (int r = 0; r < XT_REGIONS; r++) { mbar_init(&sh.dfull[r], 1); mbar_init(&sh.dempty[r], 4); }
+        mbar_init(sh.bfull, 1);
+        mbar_fence_init();
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_sh)), "r"(XT_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    xt_fence_before();
+    __syncthreads();
+    xt_fence_after();
+    const uint32_t tmem_base = tmem_base_sh;
+    if (warp < 4) {
+        // unit scale factors (ue8m0 0x7F) in the 64 columns behind the accumulator regions, every lane
+        const uint32_t one = 0x7F7F7F7Fu, addr = tmem_base + ((uint32_t)(warp * 32) << 16) + XT_SF_COL;
+        for (int c = 0; c < 64; c += 8)
+            asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%1,%1,%1,%1,%1,%1,%1};" ::"r"(addr + c), "r"(one) : "memory");
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+    }
+    BRRR_STAMP(a.state, SB + 1);
+    pdl_wait();
+    BRRR_STAMP(a.state, SB + 2);
+    BRRR_GT_GO(a.state, SB + 30);
+    pdl_trigger();
+
+    // ---- everything that does not depend on the expert goes first: the activation image (one bulk
+    // copy) and its block scales; then the routing of this slot (the ei-th largest entry of the
+    // estimate, or the exact routing) and the weight stream.  One round trip to global memory.
+    if (warp == 4 && lane == 31) {
+        const uint8_t *img = a.bimg + (DOWN ? (size_t)ei * np * XT_B_PAIR : 0);
+        mbar_expect_tx(sh.bfull, (uint32_t)np * XT_B_PAIR);
+        bulk_g2s(sh.bimg, img, (uint32_t)np * XT_B_PAIR, sh.bfull);
+    }
+    const float *xs = DOWN ? a.xs + (size_t)ei * nb : a.xs;
+    const float xs_mine = tid < nb ? xs[tid] : 0.0f;            // nb <= 128 < XT_THREADS
+    int e_top = 0;
+    if (a.est) block_spec_select(a.est, a.ne, a.topk, a.state ? &a.state->pos : nullptr, a.sabotage, lg, sel, tid, XT_THREADS);
+    else e_top = a.top[ei];
+    if (tid < nb) sh.xsc[tid] = xs_mine;
+    xt_fence_before();
+    __syncthreads();
+    xt_fence_after();
+    const int e = a.est ? sel[ei] : e_top;
+    const unsigned char *src = a.w.data + ((size_t)e * a.w.tiles_per_expert + t) * np * MXT_UNIT;
+    if (warp == 4 && lane < min(a.stages, nchunks)) {            // one lane per copy: the first stages of the weight stream
+        const int cnt = min(XT_CH, np - lane * XT_CH);
+        mbar_expect_tx(&sh.full[lane], (uint32_t)cnt * MXT_UNIT);
+        bulk_g2s(sh.ring + stage_bytes * lane, src + (size_t)lane * stage_bytes, (uint32_t)cnt * MXT_UNIT, &sh.full[lane]);
+    }
+    BRRR_STAMP(a.state, SB + 3);
+
+    // Loop structure shared by the three roles: round r = ring stage r % stages = 4 block pairs =
+    // accumulator region r % 2.  All indices advance incrementally.
+    if (warp == 4) {
+        // ---- producer: refill a stage once the four epilogue warps have left it
+        if (lane == 0) {
+            int s = 0;
+            uint32_t par = 0;                        // parity of the release being waited for
+            for (int c = a.stages; c < nchunks; c++) {
+                const int cnt = min(XT_CH, np - c * XT_CH);
+                xt_wait(&sh.empty[s], par, err, true);
+                mbar_expect_tx(&sh.full[s], (uint32_t)cnt * MXT_UNIT);
+                bulk_g2s(sh.ring + stage_bytes * s, src + (size_t)c * stage_bytes, (uint32_t)cnt * MXT_UNIT, &sh.full[s]);
+                if (++s == a.stages) { s = 0; par ^= 1u; }
+            }
+        }
+    } else if (warp == 5) {
+        // ---- MMA issue: one instruction per block pair, four per round into one accumulator region
+        if (lane == 0) {
+            const uint32_t sfa = tmem_base + XT_SF_COL, sfb = tmem_base + XT_SF_COL + 32;
+            const uint64_t dhi = ((uint64_t)((128u >> 4) & 0x3FFF) << 32) | ((uint64_t)1 << 46);     // descriptor bits common to A and B
+            const uint64_t alo = dhi | ((uint64_t)((2048u >> 4) & 0x3FFF) << 16), blo = dhi | ((uint64_t)(((uint32_t)XT_B_PAIR / 2 >> 4) & 0x3FFF) << 16);
+            uint32_t baddr = smem_u32(sh.bimg) >> 4;              // descriptor start-address fields (16-byte units)
+            const uint32_t r0 = smem_u32(sh.ring) >> 4, stage16 = (uint32_t)(stage_bytes >> 4);
+            xt_wait(sh.bfull, 0u, err, true);
+            int s = 0, reg = 0, left = np;
+            uint32_t fpar = 0, epar = 1;             // full-stage parity; region-free parity (first pass: free)
+#pragma unroll 1
+            for (int r = 0; r < nchunks; r++) {
+                xt_wait(&sh.full[s], fpar, err, true);
+                xt_wait(&sh.dempty[reg], epar, err, true);
+                xt_fence_after();
+                const uint32_t aaddr = r0 + s * stage16, d0 = tmem_base + reg * XT_REGION_COLS;
+                const int cnt = left < XT_CH ? left : XT_CH;
+#pragma unroll
+                for (int k = 0; k < XT_CH; k++)
+                    if (k < cnt) xt_mma(d0 + k * XT_N, alo | (aaddr + k * (MXT_UNIT / 16)), blo | (baddr + k * (XT_B_PAIR / 16)), sfa, sfb);
+                xt_commit(&sh.dfull[reg]);
+                baddr += XT_CH * XT_B_PAIR / 16;
+                left -= XT_CH;
+                if (++s == a.stages) { s = 0; fpar ^= 1u; }
+                if (++reg == XT_REGIONS) { reg = 0; epar ^= 1u; }
+            }
+        }
+    } else {
+        // ---- epilogue: thread m owns tile row m
+        const int m = tid;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+        float acc0 = 0.0f, acc1 = 0.0f, acc2 = 0.0f, acc3 = 0.0f;
+        uint32_t dv[XT_REGION_COLS] = {};
+        int s = 0, reg = 0, left = np;
+        uint32_t spar = 0, dpar = 0;
+        const float *xsp = sh.xsc;
+#pragma unroll 1
+        for (int r = 0; r < nchunks; r++) {
+            const int cnt = left < XT_CH ? left : XT_CH;
+            xt_wait(&sh.full[s], spar, err);                    // the stage's exponent bytes are visible
+            const unsigned char *ex = sh.ring + stage_bytes * s + MXT_UNIT_EXPS + m * 2;
+            uint32_t e2[XT_CH];
+#pragma unroll
+            for (int k = 0; k < XT_CH; k++) e2[k] = k < cnt ? *reinterpret_cast<const unsigned short *>(ex + k * MXT_UNIT) : 0u;
+            const float4 xa = *reinterpret_cast<const float4 *>(xsp), xb = *reinterpret_cast<const float4 *>(xsp + 4);
+            float sc[2 * XT_CH];                                // block scales: 2^(e-128) * xs
+            sc[0] = __fmul_rn(sh.tbl[e2[0] & 0xFFu], xa.x); sc[1] = __fmul_rn(sh.tbl[e2[0] >> 8], xa.y);
+            sc[2] = __fmul_rn(sh.tbl[e2[1] & 0xFFu], xa.z); sc[3] = __fmul_rn(sh.tbl[e2[1] >> 8], xa.w);
+            sc[4] = __fmul_rn(sh.tbl[e2[2] & 0xFFu], xb.x); sc[5] = __fmul_rn(sh.tbl[e2[2] >> 8], xb.y);
+            sc[6] = __fmul_rn(sh.tbl[e2[3] & 0xFFu], xb.z); sc[7] = __fmul_rn(sh.tbl[e2[3] >> 8], xb.w);
+            xt_wait(&sh.dfull[reg], dpar, err);
+            xt_fence_after();
+            xt_ld96(lane_addr + reg * XT_REGION_COLS, dv);
+            xt_wait_ld96(dv);
+            xt_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                mbar_arrive(&sh.dempty[reg]);
+                mbar_arrive(&sh.empty[s]);                      // the stage's MMAs are complete and its exponents read
+            }
+#pragma unroll
+            for (int k = 0; k < XT_CH; k++)
+                if (k < cnt) xt_pair(dv + XT_N * k, sc[2 * k], sc[2 * k + 1], acc0, acc1, acc2, acc3);
+            xsp += 2 * XT_CH;
+            left -= XT_CH;
+            if (++s == a.stages) { s = 0; spar ^= 1u; }
+            if (++reg == XT_REGIONS) { reg = 0; dpar ^= 1u; }
+            if (r < 12) BRRR_STAMP(a.state, SB + 4 + r);
+        }
+        BRRR_STAMP(a.state, SB + 16);
+        const float v = __fadd_rn(__fadd_rn(acc0, acc1), __fadd_rn(acc2, acc3));
+        if (!DOWN) {
+            const int isup = m >> 6, r = t * 64 + (m & 63);
+            gu_s[isup][m & 63] = __fadd_rn(v, (isup ? a.bias_b : a.bias_a)[(size_t)e * a.d + r]);
+            xt_bar_epi();
+            if (warp < 2) {
+                // SwiGLU, Q8 of this 32-block of h, and its share of the operand image down reads
+                const float h = swiglu_oai(gu_s[0][warp * 32 + lane], gu_s[1][warp * 32 + lane]);
+                const float amax = fmaxf(warp_max(fabsf(h)), 1e-12f);
+                const float sc = __fdiv_rn(amax, 127.0f);
+                const int qv = brrr_q8_round(h, sc), b = t * 2 + warp;
+                if (lane == 0) a.hs[ei * nb + b] = sc;
+                a.hq[(size_t)ei * a.d + b * 32 + lane] = (int8_t)qv;
+                xt_emit_block(qv, lane, b, a.himg + (size_t)ei * np * XT_B_PAIR);
+            }
+        } else {
+            const int r = t * 128 + m, dpad = a.w.tiles_per_expert * 128;
+            a.part[(size_t)ei * dpad + r] = v;
+            if (a.wts) {                     // exact routing known: fold here; else a fold kernel follows
+                __threadfence();
+                xt_bar_epi();
+                if (m == 0) last_sh = atomicAdd(&a.counter[t], 1u) == (uint32_t)(a.topk - 1);
+                xt_bar_epi();
+            } else if (m == 0) last_sh = 0;
+            if (a.wts && last_sh) {
+                // the last of the top-k CTAs of these 128 rows folds them in slot order
+                __threadfence();
+                if (r < a.d) {
+                    float s = a.x[r];
+                    for (int k = 0; k < a.topk; k++)
+                        s = __fadd_rn(s, __fmul_rn(a.wts[k], __fadd_rn(__ldcg(&a.part[(size_t)k * dpad + r]), a.bias_a[(size_t)a.top[k] * a.d + r])));
+                    a.x[r] = s;
+                }
+                if (m == 0) a.counter[t] = 0;
+            }
+        }
+    }
+    BRRR_STAMP(a.state, SB + 17);
+    BRRR_GT_END(a.state, SB + 31);
+    xt_fence_before();
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(XT_TMEM_COLS) : "memory");
+}
+
+// Fold of the down-projection partial sums once the exact routing is known:
+//   x[r] += sum over k ascending of wts[k] * (part[slot of top[k]][r] + bias[top[k]][r])
+// (multiply, then add, as the reference's combine).  With est != nullptr the partial sums were
+// computed for the top-k of the estimate: exact experts missing from it flag the step.
+struct FoldArgs {
+    const int32_t *top;
+    const float *wts, *est;
+    int ne, topk, sabotage, d, dpad;
+    const float *part, *down_b;
+    float *x;
+    DevState *state;
+};
+
+__global__ void __launch_bounds__(128) xt_fold_kernel(FoldArgs a) {
+    __shared__ int sel[8];
+    __shared__ float lg[256];
+    __shared__ int slot_of[8];
+    const int tid = threadIdx.x;
+    pdl_wait();
+    pdl_trigger();
+    if (a.est) {
+        block_spec_select(a.est, a.ne, a.topk, a.state ? &a.state->pos : nullptr, a.sabotage, lg, sel, tid, 128);
+        __syncthreads();
+    }
+    if (tid < a.topk) {
+        int slot = tid;
+        if (a.est) {
+            slot = -1;
+            const int want = a.top[tid];
+            for (int s = 0; s < a.topk; s++) if (sel[s] == want) slot = s;
+            if (slot < 0) {                  // the estimate missed this expert: flag the step, keep going
+                slot = 0;
+                if (blockIdx.x == 0 && a.state) atomicMin(&a.state->spec_fail_step, a.state->n_out);
+            }
+        }
+        slot_of[tid] = slot;
+    }
+    __syncthreads();
+    const int r = blockIdx.x * 128 + tid;
+    if (r < a.d) {
+        float s = a.x[r];
+        for (int k = 0; k < a.topk; k++)
+            s = __fadd_rn(s, __fmul_rn(a.wts[k], __fadd_rn(a.part[(size_t)slot_of[k] * a.dpad + r], a.down_b[(size_t)a.top[k] * a.d + r])));
+        a.x[r] = s;
+    }
+}
+
+size_t xt_smem_bytes(int np, int stages) {
+    return (size_t)stages * XT_CH * MXT_UNIT + (size_t)np * XT_B_PAIR + (size_t)np * 2 * 4 + 256 * 4 + (size_t)(2 * stages + 2 * XT_REGIONS + 1) * 8;
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------- launchers
+size_t mxt_bytes(int experts, int tiles_per_expert, int np) { return (size_t)experts * tiles_per_expert * np * MXT_UNIT; }
+
+void launch_mxt_pack(MxDev a, MxDev b, int experts, int rows_per_expert, MxtDev out, cudaStream_t st) {
+    PackArgs p{};
+    p.a = a; p.b = b; p.rows_per_expert = rows_per_expert; p.tiles_per_expert = out.tiles_per_expert; p.out = out;
+    const size_t words = mxt_bytes(experts, out.tiles_per_expert, out.np) / 4;
+    if (!words) return;
+    mxt_pack_kernel<<<(unsigned)((words + 255) / 256), 256, 0, st>>>(p, words);
+}
+
+void launch_xt_bimg(const int8_t *xq, int nb, uint8_t *bimg, cudaStream_t st) {
+    if (nb > 0) xt_bimg_kernel<<<(nb + 3) / 4, 128, 0, st>>>(xq, nb, bimg);
+}
+
+cudaError_t launch_gate_up_t(MxtDev gu, const float *gate_b, const float *up_b, const int32_t *top, const float *est, int ne, int topk,
+                             int sabotage, int d, const uint8_t *ximg, const float *xs, int8_t *hq, float *hs, uint8_t *himg, DevState *state,
+                             bool pdl, cudaStream_t st) {
+    XtArgs a{};
+    a.w = gu; a.bias_a = gate_b; a.bias_b = up_b; a.top = top; a.est = est; a.ne = ne; a.topk = topk; a.sabotage = sabotage; a.d = d;
+    a.bimg = ximg; a.xs = xs; a.hq = hq; a.hs = hs; a.himg = himg; a.state = state;
+    const int nchunks = (gu.np + XT_CH - 1) / XT_CH;
+    a.stages = nchunks < 4 ? nchunks : 4;            // two CTAs per SM at the 20b shape
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(xt_expert_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    return launch_k(xt_expert_kernel<false>, dim3(gu.tiles_per_expert, topk), dim3(XT_THREADS), xt_smem_bytes(gu.np, a.stages), st, pdl, a);
+}
+
+cudaError_t launch_down_t(MxtDev down, const float *down_b, const int32_t *top, const float *wts, const float *est, int ne, int topk,
+                          int sabotage, int d, const uint8_t *himg, const float *hs, float *x, float *part, uint32_t *counter, DevState *state,
+                          bool pdl, cudaStream_t st) {
+    XtArgs a{};
+    a.w = down; a.bias_a = down_b; a.top = top; a.wts = wts; a.est = est; a.ne = ne; a.topk = topk; a.sabotage = sabotage; a.d = d;
+    a.bimg = himg; a.xs = hs; a.x = x; a.part = part; a.counter = counter; a.state = state;
+    const int nchunks = (down.np + XT_CH - 1) / XT_CH;
+    a.stages = nchunks < 9 ? nchunks : 9;            // one CTA per SM: a deep ring keeps more bytes in flight
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(xt_expert_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024);
+        if (e != cudaSuccess) return e;
+        configured = true;
+    }
+    return launch_k(xt_expert_kernel<true>, dim3(down.tiles_per_expert, topk), dim3(XT_THREADS), xt_smem_bytes(down.np, a.stages), st, pdl, a);
+}
+
+cudaError_t launch_down_fold(const int32_t *top, const float *wts, const float *est, int ne, int topk, int sabotage, int d, const float *part,
+                             const float *down_b, float *x, DevState *state, bool pdl, cudaStream_t st) {
+    FoldArgs a{};
+    a.top = top; a.wts = wts; a.est = est; a.ne = ne; a.topk = topk; a.sabotage = sabotage; a.d = d; a.dpad = (d + 127) / 128 * 128;
+    a.part = part; a.down_b = down_b; a.x = x; a.state = state;
+    return launch_k(xt_fold_kernel, dim3((d + 127) / 128), dim3(128), 0, st, pdl, a);
+}
+
+}  // namespace brrr

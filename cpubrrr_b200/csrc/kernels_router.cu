@@ -11,6 +11,7 @@
 #include "brrr_kernels.h"
 #include "brrr_block.cuh"
 #include "brrr_tma.cuh"
+#include "brrr_mxt.cuh"
 
 namespace brrr {
 
@@ -119,7 +120,7 @@ __global__ void __launch_bounds__(RT_THREADS) ffn_in_kernel(RouterArgs a) {
     float *tiles = reinterpret_cast<float *>(smraw);                                        // [RT_STAGES][32][RT_STRIDE]
     float *xn = reinterpret_cast<float *>(smraw + (size_t)RT_TILE_FLOATS * 4 * RT_STAGES);   // d floats
     float *lg = xn + a.d;                                                                   // ne floats (top-k staging)
-    float *wn = lg + ((a.ne + 1) & ~1);                                        // d floats: norm weights
+    float *wn = lg + ((a.ne + 3) & ~3);                                        // d floats: norm weights (16-byte aligned: float4 stores)
     uint64_t *bars = reinterpret_cast<uint64_t *>(wn + a.d);                   // [RT_STAGES] tile landed
     uint64_t *empty = bars + RT_STAGES;                                        // [RT_STAGES] tile consumed
     __shared__ float inv_sh;
@@ -218,7 +219,7 @@ size_t router_packed_floats(int ne, int d) { return (size_t)((ne + 31) / 32) * (
 cudaError_t launch_ffn_in(const float *x_in, const float *norm_w, float eps, int d, const float *Wt, const float *b, int ne, int topk,
                           float *logits, int32_t *top, float *wts, unsigned int *counter, DevState *state, bool pdl, cudaStream_t st, int ntok) {
     RouterArgs a{x_in, norm_w, eps, d, Wt, b, ne, topk, logits, top, wts, counter, state};
-    size_t smem = (size_t)RT_TILE_FLOATS * 4 * RT_STAGES + (size_t)d * 8 + (size_t)((ne + 1) & ~1) * 4 + RT_STAGES * 16;
+    size_t smem = (size_t)RT_TILE_FLOATS * 4 * RT_STAGES + (size_t)d * 8 + (size_t)((ne + 3) & ~3) * 4 + RT_STAGES * 16;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(ffn_in_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
@@ -245,6 +246,7 @@ struct HintArgs {
     int8_t *xq_out;          // nullable: Q8 of the normalised vector, each CTA writes a share
     float *xs_out;
     DevState *state;
+    uint8_t *bimg_out;       // nullable: digit-plane operand image of the same vector (brrr_mxt.cuh)
 };
 
 constexpr int HINT_THREADS = 128;
@@ -301,15 +303,20 @@ __global__ void __launch_bounds__(HINT_THREADS) router_hint_kernel(HintArgs a) {
         for (int blk = e * (HINT_THREADS / 32) + warp; blk < nb; blk += gridDim.x * (HINT_THREADS / 32)) {
             float v = xf[blk * 32 + lane];
             if (a.norm_w) v = __fmul_rn(__fmul_rn(v, inv), a.norm_w[blk * 32 + lane]);
-            warp_quant_block(v, lane, a.xq_out + blk * 32, a.xs_out + blk);
+            const float amax = fmaxf(warp_max(fabsf(v)), 1e-12f);
+            const float sc = __fdiv_rn(amax, 127.0f);
+            const int qv = brrr_q8_round(v, sc);
+            if (lane == 0) a.xs_out[blk] = sc;
+            a.xq_out[blk * 32 + lane] = (int8_t)qv;
+            if (a.bimg_out) xt_emit_block(qv, lane, blk, a.bimg_out);
         }
     }
     BRRR_GT_END(a.state, 225);
 }
 
 cudaError_t launch_router_hint(const float *x_in, const float *norm_w, float eps, int d, const float *Wt, const float *b, int ne, int topk,
-                               float *est, int8_t *xq_out, float *xs_out, DevState *state, bool pdl, cudaStream_t st) {
-    HintArgs a{x_in, norm_w, eps, d, Wt, b, ne, topk, est, xq_out, xs_out, state};
+                               float *est, int8_t *xq_out, float *xs_out, DevState *state, bool pdl, cudaStream_t st, uint8_t *bimg_out) {
+    HintArgs a{x_in, norm_w, eps, d, Wt, b, ne, topk, est, xq_out, xs_out, state, bimg_out};
     size_t smem = (size_t)(d + ne + 4) * sizeof(float);
     return launch_k(router_hint_kernel, dim3(ne), dim3(HINT_THREADS), smem, st, pdl, a);
 }

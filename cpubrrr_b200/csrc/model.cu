@@ -58,6 +58,7 @@ struct Layer {
     float *bqkv = nullptr, *bo = nullptr, *sinks = nullptr, *ginp = nullptr, *ginp_b = nullptr;
     MxDev gate{}, up{}, down{};
     float *gate_b = nullptr, *up_b = nullptr, *down_b = nullptr;
+    MxtDev gu_t{}, down_t{};     // tensor-core tile units of gate|up and down (use_mxt)
     float *kc = nullptr, *vc = nullptr;
 };
 
@@ -128,6 +129,12 @@ struct brrr_model {
     uint64_t spec_redos = 0;
     int launches_head = 0, launches_nohead = 0;
     bool use_pdl = true;         // chain the step's kernels with programmatic dependent launch
+    // expert matvecs of the speculative step on the tensor cores in native fp4 (kernels_mxt.cu);
+    // needs a second copy of the expert matrices in tile units
+    bool use_mxt = false;
+    float *dpart = nullptr;      // down: [topk][tiles * 128] row sums
+    uint32_t *dcount = nullptr;  // down: arrival counters per row tile
+    uint8_t *ximg = nullptr, *himg = nullptr;   // operand images of the token's and of h's Q8 activation
     // expert parallelism: this rank holds experts [epc.e_lo, epc.e_lo + epc.e_cnt); the exchange
     // region (slices, flags, step counters) is one allocation shared with the peers through IPC
     bool ep = false, ep_attached = false;
@@ -294,15 +301,34 @@ int enqueue_step(brrr_model *m, bool want, float *trace_dev, int *nlaunch, unsig
                               &m->st->router_done, m->st, false, m->side));
             CU(cudaEventRecord(m->ev_join, m->side));
             n++;
-            CUL(launch_router_hint(m->x, ly.ffn_norm, c.rms_eps, d, ly.ginp, ly.ginp_b, c.n_expert, topk, m->est, m->xq, m->xs, m->st, pdl, s));
+            CUL(launch_router_hint(m->x, ly.ffn_norm, c.rms_eps, d, ly.ginp, ly.ginp_b, c.n_expert, topk, m->est, m->xq, m->xs, m->st, pdl, s,
+                                   m->use_mxt ? m->ximg : nullptr));
             n++;
-            CUL(launch_gate_up(ly.gate, ly.up, ly.gate_b, ly.up_b, nullptr, topk, d, nullptr, nullptr, c.rms_eps, m->xq, m->xs,
-                               m->hq, m->hs, nullptr, m->st, pdl, s, m->est, c.n_expert, m->sabotage));
+            if (m->use_mxt) CUL(launch_gate_up_t(ly.gu_t, ly.gate_b, ly.up_b, nullptr, m->est, c.n_expert, topk, m->sabotage, d, m->ximg, m->xs,
+                                                 m->hq, m->hs, m->himg, m->st, pdl, s));
+            else CUL(launch_gate_up(ly.gate, ly.up, ly.gate_b, ly.up_b, nullptr, topk, d, nullptr, nullptr, c.rms_eps, m->xq, m->xs,
+                                    m->hq, m->hs, nullptr, m->st, pdl, s, m->est, c.n_expert, m->sabotage));
+            if (m->use_mxt) {
+                // down for the estimated experts as well; only the fold waits for the exact routing
+                n++;
+                CUL(launch_down_t(ly.down_t, ly.down_b, nullptr, nullptr, m->est, c.n_expert, topk, m->sabotage, d, m->himg, m->hs, m->x,
+                                  m->dpart, m->dcount, m->st, pdl, s));
+            }
             CU(cudaStreamWaitEvent(s, m->ev_join, 0));
             n++;
             // full dependency on both predecessors: a programmatic launch here was observed to start
             // before the side-stream router had finished
-            CUL(launch_down_combine(ly.down, ly.down_b, m->top, m->wts, m->est, c.n_expert, m->sabotage, topk, d, m->hq, m->hs, m->x, m->st, false, s));
+            if (m->use_mxt) CUL(launch_down_fold(m->top, m->wts, m->est, c.n_expert, topk, m->sabotage, d, m->dpart, ly.down_b, m->x, m->st, false, s));
+            else CUL(launch_down_combine(ly.down, ly.down_b, m->top, m->wts, m->est, c.n_expert, m->sabotage, topk, d, m->hq, m->hs, m->x, m->st, false, s));
+        } else if (m->use_mxt && mask != ~0u) {
+            // single-stage replays (stage timing) of the kernels the speculative step runs, on the
+            // activation and routing the last step left behind
+            if (on(ST_ROUTER)) CUL(launch_ffn_in(m->x, ly.ffn_norm, c.rms_eps, d, ly.ginp, ly.ginp_b, c.n_expert, topk, m->rlogits, m->top, m->wts,
+                                                 &m->st->router_done, m->st, pdl, s));
+            if (on(ST_GATE_UP)) CUL(launch_gate_up_t(ly.gu_t, ly.gate_b, ly.up_b, m->top, nullptr, 0, topk, 0, d, m->ximg, m->xs, m->hq, m->hs, m->himg,
+                                                     m->st, pdl, s));
+            if (on(ST_DOWN)) CUL(launch_down_t(ly.down_t, ly.down_b, m->top, m->wts, nullptr, 0, topk, 0, d, m->himg, m->hs, m->x, m->dpart, m->dcount,
+                                               m->st, pdl, s));
         } else {
         if (on(ST_ROUTER)) CUL(launch_ffn_in(m->x, ly.ffn_norm, c.rms_eps, d, ly.ginp, ly.ginp_b, c.n_expert, topk, m->rlogits, m->top, m->wts,
                                              &m->st->router_done, m->st, pdl, s));
@@ -382,6 +408,16 @@ int build_model(brrr_model *m, const Source &src) {
 
     m->L.resize(c.n_layer);
     const int qkv_rows = (nh + 2 * nkv) * hd;
+    {
+        // tensor-core expert path: single GPU, speculative step, shapes the tiles cover, and room
+        // for the second copy of the expert matrices (about 1.08 x their size)
+        size_t free_b = 0, total_b = 0;
+        CU(cudaMemGetInfo(&free_b, &total_b));
+        const size_t experts = (size_t)c.n_layer * ne * 3 * d * nb * 17;
+        const size_t rest = (size_t)c.n_vocab * d * 4 + (size_t)c.n_layer * ((size_t)(qkv_rows + d) * d * 2 + (size_t)BRRR_MAXSEQ * nkv * hd * 8) + (2ull << 30);
+        m->use_mxt = !m->ep && d % 64 == 0 && nb % 2 == 0 && topk <= 8 && free_b > experts * 2.2 + rest;
+        if (const char *e = getenv("BRRR_NOMXT")) if (e[0] && e[0] != '0') m->use_mxt = false;
+    }
     for (int il = 0; il < c.n_layer; il++) {
         Layer &ly = m->L[il];
         TRY(load_f32(m, src, il, BRRR_T_ATTN_NORM, d, &ly.attn_norm));
@@ -407,6 +443,15 @@ int build_model(brrr_model *m, const Source &src) {
         TRY(load_mx(m, src, il, BRRR_T_GATE, e_cnt * d, nb, &ly.gate, scratch, e_lo * d, ne * d));
         TRY(load_mx(m, src, il, BRRR_T_UP, e_cnt * d, nb, &ly.up, scratch, e_lo * d, ne * d));
         TRY(load_mx(m, src, il, BRRR_T_DOWN, e_cnt * d, nb, &ly.down, scratch, e_lo * d, ne * d));
+        if (m->use_mxt) {
+            ly.gu_t.tiles_per_expert = d / 64; ly.gu_t.np = nb / 2;
+            ly.down_t.tiles_per_expert = (d + 127) / 128; ly.down_t.np = nb / 2;
+            TRY(m->alloc(&ly.gu_t.data, mxt_bytes(ne, ly.gu_t.tiles_per_expert, nb / 2)));
+            TRY(m->alloc(&ly.down_t.data, mxt_bytes(ne, ly.down_t.tiles_per_expert, nb / 2)));
+            launch_mxt_pack(ly.gate, ly.up, ne, d, ly.gu_t, m->stream);
+            launch_mxt_pack(ly.down, MxDev{nullptr, 0, 0}, ne, d, ly.down_t, m->stream);
+            CU(cudaGetLastError());
+        }
         TRY(load_f32(m, src, il, BRRR_T_GATE_B, (size_t)ne * d, &ly.gate_b));
         TRY(load_f32(m, src, il, BRRR_T_UP_B, (size_t)ne * d, &ly.up_b));
         TRY(load_f32(m, src, il, BRRR_T_DOWN_B, (size_t)ne * d, &ly.down_b));
@@ -432,6 +477,13 @@ int build_model(brrr_model *m, const Source &src) {
     TRY(m->alloc(&m->xq, d)); TRY(m->alloc(&m->aq, nh * hd)); TRY(m->alloc(&m->hq, (size_t)topk * d));
     TRY(m->alloc(&m->top, 8)); TRY(m->alloc(&m->st, 1));
     TRY(m->alloc(&m->est, (size_t)ne));
+    TRY(m->alloc(&m->dpart, (size_t)topk * ((d + 127) / 128) * 128));
+    TRY(m->alloc(&m->dcount, (size_t)(d + 127) / 128));
+    CU(cudaMemsetAsync(m->dcount, 0, (size_t)((d + 127) / 128) * 4, m->stream));
+    TRY(m->alloc(&m->ximg, (size_t)(nb / 2 + 1) * 768));
+    TRY(m->alloc(&m->himg, (size_t)topk * (nb / 2 + 1) * 768));
+    CU(cudaMemsetAsync(m->ximg, 0, (size_t)(nb / 2 + 1) * 768, m->stream));      // producers only write the non-zero words
+    CU(cudaMemsetAsync(m->himg, 0, (size_t)topk * (nb / 2 + 1) * 768, m->stream));
     CU(cudaMemsetAsync(m->st, 0, sizeof(DevState), m->stream));
     CU(cudaMemsetAsync(m->x, 0, d * 4, m->stream));
     CU(cudaMallocHost(&m->h_in, 16));
@@ -819,6 +871,31 @@ extern "C" int brrr_moe_ffn_step(brrr_model *m, int il, const float *d_xn, float
     CU(cudaStreamSynchronize(s));
     return BRRR_OK;
 }
+
+// The same step through the tensor-core expert kernels (the ones the speculative decode step runs):
+// exact router, Q8 of the normalised token, gate/up tiles, down tiles with the last-arriver fold.
+// BRRR_ERR_STATE when the model was opened without the tile-unit copy of the experts.
+extern "C" int brrr_moe_ffn_step_tc(brrr_model *m, int il, const float *d_xn, float *d_x, int32_t *d_top, float *d_wts) {
+    if (!m || !d_xn || !d_x || il < 0 || il >= m->cfg.n_layer) return BRRR_ERR_ARG;
+    if (!m->use_mxt) return BRRR_ERR_STATE;
+    CU(cudaSetDevice(m->device));
+    const brrr_cfg &c = m->cfg;
+    const int d = c.n_embd, topk = c.n_expert_used;
+    Layer &ly = m->L[il];
+    cudaStream_t s = m->stream;
+    CUL(launch_ffn_in(d_xn, nullptr, c.rms_eps, d, ly.ginp, ly.ginp_b, c.n_expert, topk, m->rlogits, m->top, m->wts, &m->st->router_done, m->st, false, s));
+    launch_quant_q8(d_xn, d, m->xq, m->xs, s);
+    launch_xt_bimg(m->xq, d / 32, m->ximg, s);
+    CUL(launch_gate_up_t(ly.gu_t, ly.gate_b, ly.up_b, m->top, nullptr, 0, topk, 0, d, m->ximg, m->xs, m->hq, m->hs, m->himg, m->st, false, s));
+    CUL(launch_down_t(ly.down_t, ly.down_b, m->top, m->wts, nullptr, 0, topk, 0, d, m->himg, m->hs, d_x, m->dpart, m->dcount, m->st, false, s));
+    CU(cudaGetLastError());
+    if (d_top) CU(cudaMemcpyAsync(d_top, m->top, topk * sizeof(int32_t), cudaMemcpyDeviceToDevice, s));
+    if (d_wts) CU(cudaMemcpyAsync(d_wts, m->wts, topk * sizeof(float), cudaMemcpyDeviceToDevice, s));
+    CU(cudaStreamSynchronize(s));
+    return BRRR_OK;
+}
+
+extern "C" int brrr_model_uses_tensor_experts(const brrr_model *m) { return m && m->use_mxt ? 1 : 0; }
 
 // MoE FFN of one layer for a tile of up to 16 normalised tokens: per-token router (one launch),
 // routing lists per expert, then three grouped tensor-core matmuls (gate, up, down) that read every

@@ -105,6 +105,13 @@ class Engine:
     def moe_ffn_step(self, il, d_xn, d_x, d_top=None, d_wts=None):
         check(lib().brrr_moe_ffn_step(self._h, il, d_xn, d_x, d_top, d_wts), "brrr_moe_ffn_step")
 
+    def moe_ffn_step_tc(self, il, d_xn, d_x, d_top=None, d_wts=None):
+        check(lib().brrr_moe_ffn_step_tc(self._h, il, d_xn, d_x, d_top, d_wts), "brrr_moe_ffn_step_tc")
+
+    @property
+    def uses_tensor_experts(self):
+        return bool(lib().brrr_model_uses_tensor_experts(self._h))
+
     @property
     def stream(self):
         return lib().brrr_model_stream(self._h)

@@ -324,6 +324,16 @@ int brrr_rope_table(const brrr_cfg *cfg, float *out);
  * Replaces src/bin/engine_gpt2.rs:847-923. */
 int brrr_moe_ffn_step(brrr_model *m, int il, const float *d_xn, float *d_x, int32_t *d_top, float *d_wts);
 
+/* The same step through the expert kernels the speculative decode step runs: gate/up and down on
+ * the tensor cores in their native 4-bit format (tcgen05.mma kind::mxf4.block_scale on the raw e2m1
+ * codes, the Q8 activation split into three exact digit planes), results bit-identical to
+ * brrr_moe_ffn_step.  BRRR_ERR_STATE when the model holds no tile-unit copy of the experts
+ * (expert-parallel models, shapes with n_embd % 64 != 0, BRRR_NOMXT=1, or not enough memory).
+ * Replaces src/bin/engine_gpt2.rs:847-923. */
+int brrr_moe_ffn_step_tc(brrr_model *m, int il, const float *d_xn, float *d_x, int32_t *d_top, float *d_wts);
+/* 1 when the decode step of this model runs its expert matvecs on the tensor cores. */
+int brrr_model_uses_tensor_experts(const brrr_model *m);
+
 /* The same MoE FFN for a tile of 1..16 normalised tokens (d_xn [ntok][n_embd], d_x [ntok][n_embd]
  * residuals, d_top / d_wts nullable [ntok][n_expert_used]): per-token router, then gate / up /
  * down as grouped tensor-core matmuls (tcgen05) that read each selected expert once for all the
