@@ -153,6 +153,23 @@ __device__ __forceinline__ void block_spec_select(const float *est, int ne, int 
     }
 }
 
+// The same selection for ne <= 32 inside one warp, without shared memory or block-wide barriers:
+// returns the expert of rank `want` (what block_spec_select would leave in sel[want]).  All 32
+// lanes must call it.
+__device__ __forceinline__ int warp_spec_expert(const float *est, int ne, int topk, const uint32_t *pos_ptr, int sabotage, int want, int lane) {
+    const uint32_t pos = (sabotage && pos_ptr) ? *pos_ptr : 0u;
+    const float v = lane < ne ? __ldcg(est + lane) : 0.0f;
+    int rank = 0;
+#pragma unroll 8
+    for (int o = 0; o < 32; o++) {
+        const float u = __shfl_sync(0xffffffffu, v, o);
+        rank += (o < ne && (u > v || (u == v && o < lane))) ? 1 : 0;
+    }
+    const unsigned hit = __ballot_sync(0xffffffffu, lane < ne && rank == want);
+    const int e = __ffs(hit) - 1;
+    return (sabotage && want == topk - 1 && pos % 3 == 0) ? (e + 1) % ne : e;
+}
+
 // gpt-oss clamped SwiGLU: xg = min(g, 7), yu = clamp(u, -7, 7), (xg / (1 + exp(-1.702 xg))) (yu + 1)
 __device__ __forceinline__ float swiglu_oai(float g, float u) {
     float xg = fminf(g, 7.0f);

@@ -193,14 +193,34 @@ struct XtShared {
 };
 
 // One block pair of one row: the 8 exact lane dots from the three digit planes, then the two
-// blocks' fused multiply-adds of the four chains, in block order.
-__device__ __forceinline__ void xt_pair(const uint32_t *v, float s0, float s1, float &acc0, float &acc1, float &acc2, float &acc3) {
-    float tq[8];
+// blocks' fused multiply-adds of the four chains, in block order.  Two chains share an instruction
+// (fma.rn.f32x2: two independent round-to-nearest fused multiply-adds).
+struct XtAcc { unsigned long long a01, a23; };       // chains (0, 1) and (2, 3), packed f32x2
+__device__ __forceinline__ unsigned long long xt_pack(uint32_t lo, uint32_t hi) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(lo), "r"(hi));
+    return r;
+}
+__device__ __forceinline__ unsigned long long xt_fma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+    unsigned long long r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+__device__ __forceinline__ void xt_pair(const uint32_t *v, float s0, float s1, XtAcc &acc) {
+    const unsigned long long k49 = xt_pack(0x42440000u, 0x42440000u), k7 = xt_pack(0x40E00000u, 0x40E00000u);
+    unsigned long long tq[4];
 #pragma unroll
-    for (int i = 0; i < 8; i++)
-        tq[i] = __fmaf_rn(__uint_as_float(v[i]), 49.0f, __fmaf_rn(__uint_as_float(v[8 + i]), 7.0f, __uint_as_float(v[16 + i])));
-    acc0 = __fmaf_rn(tq[0], s0, acc0); acc1 = __fmaf_rn(tq[1], s0, acc1); acc2 = __fmaf_rn(tq[2], s0, acc2); acc3 = __fmaf_rn(tq[3], s0, acc3);
-    acc0 = __fmaf_rn(tq[4], s1, acc0); acc1 = __fmaf_rn(tq[5], s1, acc1); acc2 = __fmaf_rn(tq[6], s1, acc2); acc3 = __fmaf_rn(tq[7], s1, acc3);
+    for (int i = 0; i < 4; i++)
+        tq[i] = xt_fma2(xt_pack(v[2 * i], v[2 * i + 1]), k49, xt_fma2(xt_pack(v[8 + 2 * i], v[9 + 2 * i]), k7, xt_pack(v[16 + 2 * i], v[17 + 2 * i])));
+    const unsigned long long p0 = xt_pack(__float_as_uint(s0), __float_as_uint(s0)), p1 = xt_pack(__float_as_uint(s1), __float_as_uint(s1));
+    acc.a01 = xt_fma2(tq[0], p0, acc.a01); acc.a23 = xt_fma2(tq[1], p0, acc.a23);
+    acc.a01 = xt_fma2(tq[2], p1, acc.a01); acc.a23 = xt_fma2(tq[3], p1, acc.a23);
+}
+__device__ __forceinline__ float xt_row_sum(const XtAcc &acc) {       // (a0 + a1) + (a2 + a3)
+    uint32_t a0, a1, a2, a3;
+    asm("mov.b64 {%0, %1}, %2;" : "=r"(a0), "=r"(a1) : "l"(acc.a01));
+    asm("mov.b64 {%0, %1}, %2;" : "=r"(a2), "=r"(a3) : "l"(acc.a23));
+    return __fadd_rn(__fadd_rn(__uint_as_float(a0), __uint_as_float(a1)), __fadd_rn(__uint_as_float(a2), __uint_as_float(a3)));
 }
 
 template <bool DOWN>
@@ -254,36 +274,46 @@ __global__ void __launch_bounds__(XT_THREADS) xt_expert_kernel(XtArgs a) {
             asm volatile("tcgen05.st.sync.aligned.32x32b.x8.b32 [%0], {%1,%1,%1,%1,%1,%1,%1,%1};" ::"r"(addr + c), "r"(one) : "memory");
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
     }
+    xt_fence_before();
+    __syncthreads();                 // scale factors in place before the issuing thread can reach its first MMA
+    xt_fence_after();
+    // ---- routing of this slot (the ei-th largest entry of the estimate, or the exact routing), the
+    // weight stream, the activation image (one bulk copy) and its block scales
+    int e = 0;
+    const unsigned char *src = nullptr;
+    auto route_and_start = [&]() {
+        if (a.est) {
+            block_spec_select(a.est, a.ne, a.topk, a.state ? &a.state->pos : nullptr, a.sabotage, lg, sel, tid, XT_THREADS);
+            __syncthreads();
+            e = sel[ei];
+        } else e = a.top[ei];
+        src = a.w.data + ((size_t)e * a.w.tiles_per_expert + t) * np * MXT_UNIT;
+        if (warp == 4 && lane < min(a.stages, nchunks)) {          // one lane per copy: the first stages of the weight stream
+            const int cnt = min(XT_CH, np - lane * XT_CH);
+            mbar_expect_tx(&sh.full[lane], (uint32_t)cnt * MXT_UNIT);
+            bulk_g2s(sh.ring + stage_bytes * lane, src + (size_t)lane * stage_bytes, (uint32_t)cnt * MXT_UNIT, &sh.full[lane]);
+        }
+    };
+    // The down projection knows its expert before gate/up has finished (the routing is two kernels
+    // old), and its CTAs have the footprint of a gate/up CTA: they become resident beside running
+    // gate/up CTAs and start their weight stream there, before they wait for h.
+    constexpr bool early = DOWN;
+    if (early) route_and_start();
     BRRR_STAMP(a.state, SB + 1);
     pdl_wait();
     BRRR_STAMP(a.state, SB + 2);
     BRRR_GT_GO(a.state, SB + 30);
     pdl_trigger();
-
-    // ---- everything that does not depend on the expert goes first: the activation image (one bulk
-    // copy) and its block scales; then the routing of this slot (the ei-th largest entry of the
-    // estimate, or the exact routing) and the weight stream.  One round trip to global memory.
     if (warp == 4 && lane == 31) {
         const uint8_t *img = a.bimg + (DOWN ? (size_t)ei * np * XT_B_PAIR : 0);
         mbar_expect_tx(sh.bfull, (uint32_t)np * XT_B_PAIR);
         bulk_g2s(sh.bimg, img, (uint32_t)np * XT_B_PAIR, sh.bfull);
     }
-    const float *xs = DOWN ? a.xs + (size_t)ei * nb : a.xs;
-    const float xs_mine = tid < nb ? xs[tid] : 0.0f;            // nb <= 128 < XT_THREADS
-    int e_top = 0;
-    if (a.est) block_spec_select(a.est, a.ne, a.topk, a.state ? &a.state->pos : nullptr, a.sabotage, lg, sel, tid, XT_THREADS);
-    else e_top = a.top[ei];
+    float xs_mine = 0.0f;
+    if (tid < nb) xs_mine = (DOWN ? a.xs + (size_t)ei * nb : a.xs)[tid];      // nb <= 128: the epilogue warps hold all of it
+    if (!early) route_and_start();
     if (tid < nb) sh.xsc[tid] = xs_mine;
-    xt_fence_before();
-    __syncthreads();
-    xt_fence_after();
-    const int e = a.est ? sel[ei] : e_top;
-    const unsigned char *src = a.w.data + ((size_t)e * a.w.tiles_per_expert + t) * np * MXT_UNIT;
-    if (warp == 4 && lane < min(a.stages, nchunks)) {            // one lane per copy: the first stages of the weight stream
-        const int cnt = min(XT_CH, np - lane * XT_CH);
-        mbar_expect_tx(&sh.full[lane], (uint32_t)cnt * MXT_UNIT);
-        bulk_g2s(sh.ring + stage_bytes * lane, src + (size_t)lane * stage_bytes, (uint32_t)cnt * MXT_UNIT, &sh.full[lane]);
-    }
+    if (warp < 4) xt_bar_epi();                                  // block scales visible to the epilogue warps
     BRRR_STAMP(a.state, SB + 3);
 
     // Loop structure shared by the three roles: round r = ring stage r % stages = 4 block pairs =
@@ -333,7 +363,8 @@ __global__ void __launch_bounds__(XT_THREADS) xt_expert_kernel(XtArgs a) {
         // ---- epilogue: thread m owns tile row m
         const int m = tid;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
-        float acc0 = 0.0f, acc1 = 0.0f, acc2 = 0.0f, acc3 = 0.0f;
+        XtAcc acc{0ull, 0ull};
+        const float bias_pre = DOWN ? 0.0f : ((m >> 6) ? a.bias_b : a.bias_a)[(size_t)e * a.d + t * 64 + (m & 63)];   // in flight during the stream
         uint32_t dv[XT_REGION_COLS] = {};
         int s = 0, reg = 0, left = np;
         uint32_t spar = 0, dpar = 0;
@@ -364,7 +395,7 @@ __global__ void __launch_bounds__(XT_THREADS) xt_expert_kernel(XtArgs a) {
             }
 #pragma unroll
             for (int k = 0; k < XT_CH; k++)
-                if (k < cnt) xt_pair(dv + XT_N * k, sc[2 * k], sc[2 * k + 1], acc0, acc1, acc2, acc3);
+                if (k < cnt) xt_pair(dv + XT_N * k, sc[2 * k], sc[2 * k + 1], acc);
             xsp += 2 * XT_CH;
             left -= XT_CH;
             if (++s == a.stages) { s = 0; spar ^= 1u; }
@@ -372,10 +403,9 @@ __global__ void __launch_bounds__(XT_THREADS) xt_expert_kernel(XtArgs a) {
             if (r < 12) BRRR_STAMP(a.state, SB + 4 + r);
         }
         BRRR_STAMP(a.state, SB + 16);
-        const float v = __fadd_rn(__fadd_rn(acc0, acc1), __fadd_rn(acc2, acc3));
+        const float v = xt_row_sum(acc);
         if (!DOWN) {
-            const int isup = m >> 6, r = t * 64 + (m & 63);
-            gu_s[isup][m & 63] = __fadd_rn(v, (isup ? a.bias_b : a.bias_a)[(size_t)e * a.d + r]);
+            gu_s[m >> 6][m & 63] = __fadd_rn(v, bias_pre);
             xt_bar_epi();
             if (warp < 2) {
                 // SwiGLU, Q8 of this 32-block of h, and its share of the operand image down reads
@@ -508,7 +538,10 @@ cudaError_t launch_down_t(MxtDev down, const float *down_b, const int32_t *top, 
     a.w = down; a.bias_a = down_b; a.top = top; a.wts = wts; a.est = est; a.ne = ne; a.topk = topk; a.sabotage = sabotage; a.d = d;
     a.bimg = himg; a.xs = hs; a.x = x; a.part = part; a.counter = counter; a.state = state;
     const int nchunks = (down.np + XT_CH - 1) / XT_CH;
-    a.stages = nchunks < 9 ? nchunks : 9;            // one CTA per SM: a deep ring keeps more bytes in flight
+    // the same footprint as a gate/up CTA: a down CTA fits beside a running gate/up CTA, sets up and
+    // starts its weight stream there, before gate/up has finished (measured: 745 tok/s against 728
+    // with a 9-stage ring that needs an SM of its own)
+    a.stages = nchunks < 4 ? nchunks : 4;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(xt_expert_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024);
