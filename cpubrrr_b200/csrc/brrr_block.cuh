@@ -86,6 +86,10 @@ __device__ __forceinline__ void norm_prefetch(const float *__restrict__ norm_w, 
 }
 
 template <int LAYOUT, int MAXG>
+__device__ __forceinline__ void block_norm_quant_staged(const float *norm_w, const float4 (&wreg)[MAXG], float eps, int n,
+                                                        float *xf, int2 *xp, float *xsc, float *inv_sh, int tid, int nthreads);
+
+template <int LAYOUT, int MAXG>
 __device__ __forceinline__ void block_norm_quant(const float *__restrict__ x, const float *norm_w, const float4 (&wreg)[MAXG], float eps, int n,
                                                  float *xf, int2 *xp, float *xsc, float *inv_sh, int tid, int nthreads) {
     const int groups = n >> 2;
@@ -93,6 +97,15 @@ __device__ __forceinline__ void block_norm_quant(const float *__restrict__ x, co
     float4 *xf4 = reinterpret_cast<float4 *>(xf);
     for (int g = tid; g < groups; g += nthreads) xf4[g] = x4[g];
     __syncthreads();
+    block_norm_quant_staged<LAYOUT, MAXG>(norm_w, wreg, eps, n, xf, xp, xsc, inv_sh, tid, nthreads);
+}
+
+// The same with x already in xf (shared memory) and visible to the whole block.
+template <int LAYOUT, int MAXG>
+__device__ __forceinline__ void block_norm_quant_staged(const float *norm_w, const float4 (&wreg)[MAXG], float eps, int n,
+                                                        float *xf, int2 *xp, float *xsc, float *inv_sh, int tid, int nthreads) {
+    const int groups = n >> 2;
+    float4 *xf4 = reinterpret_cast<float4 *>(xf);
     float inv = 1.0f;
     if (norm_w) inv = block_rms_inv(xf, n, eps, inv_sh);
     const int npass = (groups + nthreads - 1) / nthreads;

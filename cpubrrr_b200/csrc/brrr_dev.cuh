@@ -136,15 +136,21 @@ struct DevState {
     uint32_t err;                  // DEV_ERR_* (0 = none); set by a kernel whose bounded wait ran out
     uint32_t spec_fail_step;       // smallest n_out at which speculative routing missed (0xFFFFFFFF = never)
     uint32_t hint_done;            // CTA arrival counter of the routing-hint kernel
-    uint32_t pad[3];
+    uint32_t router_seq;           // exact-router launches that have published their routing (speculative step)
+    uint32_t fold_seq;             // fold launches that have consumed one
+    uint32_t pad[1];
     uint32_t out[BRRR_MAXSEQ];
     long long stamps[256];          // optional in-kernel clock stamps (timeline builds only)
+    // routing of the exact router, published for a consumer that runs beside it: word k = (router_seq << 32) | top[k],
+    // word 8 + k = (router_seq << 32) | bits of wts[k]; every word validates itself, so no fence is needed
+    unsigned long long route_pub[16];
 };
 #ifdef BRRR_TIMELINE
 __device__ __forceinline__ unsigned long long brrr_gtime() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
 // wall-clock (ns) marks: END = latest finish over all CTAs of a kernel, GO = CTA 0 released from its dependency wait
 #define BRRR_GT_END(state, i) do { if ((state) && threadIdx.x == 0) atomicMax((unsigned long long *)&(state)->stamps[i], brrr_gtime()); } while (0)
 #define BRRR_GT_GO(state, i) do { if ((state) && threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0) (state)->stamps[i] = (long long)brrr_gtime(); } while (0)
+#define BRRR_GT_START(state, i) BRRR_GT_GO(state, i)
 #ifndef BRRR_STAMP_BX
 #define BRRR_STAMP_BX 0
 #endif
@@ -152,5 +158,6 @@ __device__ __forceinline__ unsigned long long brrr_gtime() { unsigned long long 
 #else
 #define BRRR_GT_END(state, i) do { } while (0)
 #define BRRR_GT_GO(state, i) do { } while (0)
+#define BRRR_GT_START(state, i) do { } while (0)
 #define BRRR_STAMP(state, i) do { } while (0)
 #endif

@@ -99,6 +99,13 @@ cudaError_t launch_gate_up_t(MxtDev gu, const float *gate_b, const float *up_b, 
 // launch_down_fold finishes the step once the exact routing is there.
 cudaError_t launch_down_fold(const int32_t *top, const float *wts, const float *est, int ne, int topk, int sabotage, int d, const float *part,
                              const float *down_b, float *x, DevState *state, bool pdl, cudaStream_t st);
+// The fold for a step whose exact router runs on another stream: one CTA waits (bounded) until
+// *router_seq == *fold_seq + 1, folds as launch_down_fold, then RMS-normalises the new residual with
+// next_norm_w and writes its Q8 image (nq natural int8 order, ns block scales) for the projection
+// that follows, and increments *fold_seq.  next_norm_w == nullptr: fold only.
+cudaError_t launch_fold_norm(const int32_t *top, const float *wts, const float *est, int ne, int topk, int sabotage, int d, const float *part,
+                             const float *down_b, float *x, const float *next_norm_w, float eps, int8_t *nq, float *ns,
+                             uint32_t *router_seq, uint32_t *fold_seq, DevState *state, bool pdl, cudaStream_t st);
 cudaError_t launch_down_t(MxtDev down, const float *down_b, const int32_t *top, const float *wts, const float *est, int ne, int topk,
                           int sabotage, int d, const uint8_t *himg, const float *hs, float *x, float *part, uint32_t *counter, DevState *state,
                           bool pdl, cudaStream_t st);
@@ -140,8 +147,10 @@ void launch_router_pack(const float *W, int ne, int d, float *out, cudaStream_t 
 // normalised vector otherwise.
 cudaError_t launch_ffn_in(const float *x_in, const float *norm_w, float eps, int d, const float *Wt, const float *b, int ne, int topk,
                           float *logits, int32_t *top, float *wts, unsigned int *counter, DevState *state, bool pdl, cudaStream_t st,
-                          int ntok = 1);
+                          int ntok = 1, uint32_t *signal = nullptr);
 // ntok > 1: a tile of tokens in one launch (token t reads x_in + t * d, writes logits + t * ne, top + 8 t, wts + 8 t, uses counter + t)
+// signal (nullable, ntok == 1): a device word the kernel increments after its routing is written, for a
+// consumer that runs beside it instead of after it (launch_fold_norm)
 
 // Order-free estimate of the router used only to start the gate/up weight stream early
 // (speculative routing): est[ne] receives the estimated logits, xq_out/xs_out the Q8 image of the

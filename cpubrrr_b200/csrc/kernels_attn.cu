@@ -68,6 +68,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(AttnArgs a) {
         bulk_g2s(tiles + (size_t)slot * AT_TILE * HD, base + (size_t)t * AT_TILE * HD, (uint32_t)cnt * HD * 4, &bars[slot]);
     };
     BRRR_STAMP(a.err_state, 160);
+    BRRR_GT_START(a.err_state, 233);
     if (tid == 0) {
         for (int s = 0; s < AT_SLOTS; s++) { mbar_init(&kbar[s], 1); mbar_init(&vbar[s], 1); }
         mbar_fence_init();

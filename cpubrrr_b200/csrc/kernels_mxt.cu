@@ -250,6 +250,7 @@ __global__ void __launch_bounds__(XT_THREADS) xt_expert_kernel(XtArgs a) {
     constexpr int SB = DOWN ? 128 : 96;          // clock stamps of timeline builds
     (void)SB;
     BRRR_STAMP(a.state, SB);
+    BRRR_GT_START(a.state, DOWN ? 237 : 236);
 
     // ---- set-up that needs nothing from the kernels before
     mx_fill_scale_table(sh.tbl, tid, XT_THREADS);
@@ -464,7 +465,9 @@ __global__ void __launch_bounds__(128) xt_fold_kernel(FoldArgs a) {
     __shared__ float lg[256];
     __shared__ int slot_of[8];
     const int tid = threadIdx.x;
+    BRRR_GT_START(a.state, 238);
     pdl_wait();
+    BRRR_GT_GO(a.state, 239);
     pdl_trigger();
     if (a.est) {
         block_spec_select(a.est, a.ne, a.topk, a.state ? &a.state->pos : nullptr, a.sabotage, lg, sel, tid, 128);
@@ -491,6 +494,147 @@ __global__ void __launch_bounds__(128) xt_fold_kernel(FoldArgs a) {
             s = __fadd_rn(s, __fmul_rn(a.wts[k], __fadd_rn(a.part[(size_t)slot_of[k] * a.dpad + r], a.down_b[(size_t)a.top[k] * a.d + r])));
         a.x[r] = s;
     }
+    BRRR_GT_END(a.state, 240);
+}
+
+// The same fold as one CTA that also prepares the next projection's activation.  Used by the
+// speculative decode step, where the exact router runs on another stream beside gate/up and down:
+// instead of a graph edge from the router (which would cost this kernel its programmatic launch),
+// one lane per word polls, bounded, the routing words the router publishes, each tagged with the
+// router's sequence number (this launch expects fold_seq + 1; the router does not depend on this
+// kernel, so the wait cannot deadlock).  The partial sums, the
+// residual and the routing estimate are fetched before that wait.  After the fold the whole
+// residual is in shared memory, so the RMS norm (fixed 16-chain order) and the Q8 image that the
+// next q/k/v projection (or the vocabulary head) needs are computed here once, rather than by every
+// CTA of that projection.
+struct FoldNormArgs {
+    FoldArgs f;
+    const float *norm_w;     // nullable: fold only
+    float eps;
+    int8_t *nq;              // Q8 of the normalised residual, element order
+    float *ns;               // its block scales
+    uint32_t *router_seq, *fold_seq;
+};
+
+constexpr int FN_THREADS = 1024;
+
+template <int MAXS>       // slots held in registers: top-k <= MAXS
+__global__ void __launch_bounds__(FN_THREADS) xt_fold_norm_kernel(FoldNormArgs a) {
+    extern __shared__ __align__(16) float fsm[];          // d floats of the residual
+    __shared__ int sel[8];
+    __shared__ float lg[256];
+    __shared__ int slot_of[8];
+    __shared__ float wts_sh[8];
+    __shared__ float inv_sh;
+    const int tid = threadIdx.x, d = a.f.d, dpad = a.f.dpad, topk = a.f.topk;
+    float *xf = fsm;
+    // ---- everything that kernels before down produced, before the dependency wait: norm weights,
+    // the residual, the speculative expert set and those experts' biases
+    float4 wreg[1];
+    norm_prefetch<1>(a.norm_w, d, wreg, tid, FN_THREADS);
+    BRRR_GT_START(a.f.state, 238);
+    // thread g owns rows 4g .. 4g+3 (one 16-byte access per operand)
+    const bool live = tid < (d >> 2);
+    const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
+    float4 xr = live ? reinterpret_cast<const float4 *>(a.f.x)[tid] : zero4, pb[MAXS], ps[MAXS];
+    if (a.f.est) {
+        block_spec_select(a.f.est, a.f.ne, topk, a.f.state ? &a.f.state->pos : nullptr, a.f.sabotage, lg, sel, tid, FN_THREADS);
+        __syncthreads();
+#pragma unroll
+        for (int s = 0; s < MAXS; s++) pb[s] = (live && s < topk) ? reinterpret_cast<const float4 *>(a.f.down_b + (size_t)sel[s] * d)[tid] : zero4;
+    }
+    const uint32_t want_seq = a.fold_seq ? __ldcg(a.fold_seq) + 1u : 0u;      // written by the previous launch of this kernel
+#ifdef BRRR_FOLD_EARLY_TRIGGER
+    pdl_trigger();       // the next projection may become resident and stream its weights while down still runs
+#endif
+    pdl_wait();          // down's partial sums are complete
+    BRRR_GT_GO(a.f.state, 239);
+    BRRR_STAMP(a.f.state, 241);
+#ifndef BRRR_FOLD_EARLY_TRIGGER
+    pdl_trigger();
+#endif
+    // ---- slot s: partial sum of the s-th expert of the estimate
+#pragma unroll
+    for (int s = 0; s < MAXS; s++) ps[s] = (live && s < topk) ? reinterpret_cast<const float4 *>(a.f.part + (size_t)s * dpad)[tid] : zero4;
+    BRRR_STAMP(a.f.state, 242);
+    // ---- the exact routing: the router publishes sequence-tagged words; one lane per word polls
+    // (bounded) until its word carries this launch's sequence number
+    if (tid < 32) {
+        uint32_t payload = 0u;
+        if (a.router_seq) {
+            if (tid < 16 && (tid & 7) < topk) {
+                const volatile unsigned long long *w = a.f.state->route_pub + tid;
+                bool ok = false;
+                const long long t0 = clock64();
+                do {
+                    for (int i = 0; i < 64 && !ok; i++) {
+                        const unsigned long long v = *w;
+                        ok = (uint32_t)(v >> 32) == want_seq;
+                        payload = (uint32_t)v;
+                    }
+                } while (!ok && clock64() - t0 < WAIT_CYCLES);
+                if (!ok) atomicCAS(&a.f.state->err, (uint32_t)DEV_ERR_NONE, (uint32_t)DEV_ERR_PEER_TIMEOUT);
+            }
+        } else if (tid < 16 && (tid & 7) < topk) {
+            payload = tid < 8 ? (uint32_t)__ldcg(a.f.top + tid) : __float_as_uint(__ldcg(a.f.wts + (tid - 8)));
+        }
+        __syncwarp();
+        if (tid >= 8 && tid < 8 + topk) wts_sh[tid - 8] = __uint_as_float(payload);
+        if (tid < topk) {
+            const int want = (int)payload;
+            int slot = tid;
+            if (a.f.est) {
+                slot = -1;
+                for (int s = 0; s < topk; s++) if (sel[s] == want) slot = s;
+                if (slot < 0) {                  // the estimate missed this expert: flag the step, keep going
+                    slot = 0;
+                    if (a.f.state) atomicMin(&a.f.state->spec_fail_step, a.f.state->n_out);
+                }
+            }
+            slot_of[tid] = slot;
+            if (!a.f.est) sel[tid] = want;
+        }
+    }
+    BRRR_STAMP(a.f.state, 243);
+    __syncthreads();
+    BRRR_STAMP(a.f.state, 244);
+    if (!a.f.est) {      // exact routing only: the biases could not be fetched ahead
+#pragma unroll
+        for (int s = 0; s < MAXS; s++) pb[s] = (live && s < topk) ? reinterpret_cast<const float4 *>(a.f.down_b + (size_t)sel[s] * d)[tid] : zero4;
+    }
+    if (live) {
+        float4 acc = xr;
+        for (int kk = 0; kk < topk; kk++) {
+            const int sl = slot_of[kk];
+            const float w = wts_sh[kk];
+            float4 p = ps[0], bb = pb[0];
+            switch (sl) {                    // uniform over the block: a branch, not a chain of selects
+            case 1: p = ps[1]; bb = pb[1]; break;
+            case 2: p = ps[2]; bb = pb[2]; break;
+            case 3: p = ps[3]; bb = pb[3]; break;
+            default:
+                if (MAXS > 4) {
+#pragma unroll
+                    for (int q = 4; q < MAXS; q++) if (q == sl) { p = ps[q]; bb = pb[q]; }
+                }
+            }
+            acc.x = __fadd_rn(acc.x, __fmul_rn(w, __fadd_rn(p.x, bb.x)));
+            acc.y = __fadd_rn(acc.y, __fmul_rn(w, __fadd_rn(p.y, bb.y)));
+            acc.z = __fadd_rn(acc.z, __fmul_rn(w, __fadd_rn(p.z, bb.z)));
+            acc.w = __fadd_rn(acc.w, __fmul_rn(w, __fadd_rn(p.w, bb.w)));
+        }
+        reinterpret_cast<float4 *>(a.f.x)[tid] = acc;
+        reinterpret_cast<float4 *>(xf)[tid] = acc;
+    }
+    BRRR_STAMP(a.f.state, 245);
+    if (a.norm_w) {
+        __syncthreads();
+        BRRR_STAMP(a.f.state, 246);
+        block_norm_quant_staged<NQ_NATURAL, 1>(a.norm_w, wreg, a.eps, d, xf, reinterpret_cast<int2 *>(a.nq), a.ns, &inv_sh, tid, FN_THREADS);
+    }
+    BRRR_STAMP(a.f.state, 247);
+    if (tid == 0 && a.fold_seq) *a.fold_seq = want_seq;
+    BRRR_GT_END(a.f.state, 240);
 }
 
 size_t xt_smem_bytes(int np, int stages) {
@@ -521,7 +665,10 @@ cudaError_t launch_gate_up_t(MxtDev gu, const float *gate_b, const float *up_b, 
     a.w = gu; a.bias_a = gate_b; a.bias_b = up_b; a.top = top; a.est = est; a.ne = ne; a.topk = topk; a.sabotage = sabotage; a.d = d;
     a.bimg = ximg; a.xs = xs; a.hq = hq; a.hs = hs; a.himg = himg; a.state = state;
     const int nchunks = (gu.np + XT_CH - 1) / XT_CH;
-    a.stages = nchunks < 4 ? nchunks : 4;            // two CTAs per SM at the 20b shape
+#ifndef XT_GU_STAGES
+#define XT_GU_STAGES 4
+#endif
+    a.stages = nchunks < XT_GU_STAGES ? nchunks : XT_GU_STAGES;            // two CTAs per SM at the 20b shape
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(xt_expert_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
@@ -541,7 +688,10 @@ cudaError_t launch_down_t(MxtDev down, const float *down_b, const int32_t *top, 
     // the same footprint as a gate/up CTA: a down CTA fits beside a running gate/up CTA, sets up and
     // starts its weight stream there, before gate/up has finished (measured: 745 tok/s against 728
     // with a 9-stage ring that needs an SM of its own)
-    a.stages = nchunks < 4 ? nchunks : 4;
+#ifndef XT_DOWN_STAGES
+#define XT_DOWN_STAGES 4
+#endif
+    a.stages = nchunks < XT_DOWN_STAGES ? nchunks : XT_DOWN_STAGES;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(xt_expert_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024);
@@ -557,6 +707,19 @@ cudaError_t launch_down_fold(const int32_t *top, const float *wts, const float *
     a.top = top; a.wts = wts; a.est = est; a.ne = ne; a.topk = topk; a.sabotage = sabotage; a.d = d; a.dpad = (d + 127) / 128 * 128;
     a.part = part; a.down_b = down_b; a.x = x; a.state = state;
     return launch_k(xt_fold_kernel, dim3((d + 127) / 128), dim3(128), 0, st, pdl, a);
+}
+
+cudaError_t launch_fold_norm(const int32_t *top, const float *wts, const float *est, int ne, int topk, int sabotage, int d, const float *part,
+                             const float *down_b, float *x, const float *next_norm_w, float eps, int8_t *nq, float *ns,
+                             uint32_t *router_seq, uint32_t *fold_seq, DevState *state, bool pdl, cudaStream_t st) {
+    if (d > 4 * FN_THREADS || d % 32 || topk > 8 || (router_seq && !state)) return cudaErrorInvalidValue;
+    FoldNormArgs a{};
+    a.f.top = top; a.f.wts = wts; a.f.est = est; a.f.ne = ne; a.f.topk = topk; a.f.sabotage = sabotage; a.f.d = d; a.f.dpad = (d + 127) / 128 * 128;
+    a.f.part = part; a.f.down_b = down_b; a.f.x = x; a.f.state = state;
+    a.norm_w = next_norm_w; a.eps = eps; a.nq = nq; a.ns = ns; a.router_seq = router_seq; a.fold_seq = fold_seq;
+    const size_t smem = (size_t)d * sizeof(float);
+    if (topk <= 4) return launch_k(xt_fold_norm_kernel<4>, dim3(1), dim3(FN_THREADS), smem, st, pdl, a);
+    return launch_k(xt_fold_norm_kernel<8>, dim3(1), dim3(FN_THREADS), smem, st, pdl, a);
 }
 
 }  // namespace brrr

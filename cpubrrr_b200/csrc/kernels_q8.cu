@@ -152,9 +152,10 @@ __global__ void __launch_bounds__(Q8_THREADS) q8_stream_kernel(Q8Args a) {
         bulk_g2s(ring + stage_bytes * slot, a.m.data + q8_unit_off(u, k * a.ch, np), (uint32_t)cnt * Q8_UNIT, &bars[slot]);
     };
 
-    const int sb = NORM ? 32 : 64;      // timeline slots of this kernel flavour
+    const int sb = (NORM || EPI == Q8_EPI_BIAS) ? 32 : 64;      // timeline slots of this kernel flavour (q/k/v, o-proj)
     (void)sb;
     BRRR_STAMP(a.state, sb);
+    BRRR_GT_START(a.state, (NORM || EPI == Q8_EPI_BIAS) ? 232 : 234);
     if (tid == 0) {
         for (int s = 0; s < a.stages; s++) mbar_init(&bars[s], 1);
         mbar_fence_init();

@@ -71,6 +71,8 @@ struct RouterArgs {
     float *wts;
     unsigned int *counter;
     DevState *state;
+    uint32_t *signal;        // nullable: sequence number of the published routing (see publish_route)
+    unsigned long long *pub;
 };
 
 // k rounds of warp arg-max over the logits (lane l holds experts l, l+32, ...): the largest value
@@ -107,6 +109,18 @@ __device__ __forceinline__ void warp_topk(const RouterArgs &a, const float *lg, 
         for (int i = 0; i < a.topk; i++) { ex[i] = brrr_expf_dev(__fsub_rn(tv[i], tv[0])); wsum = __fadd_rn(wsum, ex[i]); }
         for (int i = 0; i < a.topk; i++) { a.wts[i] = __fdiv_rn(ex[i], wsum); a.top[i] = tp[i]; }
     }
+}
+
+// Publication for a consumer that does not wait for this kernel to end (the fused fold of the
+// speculative step): sequence-tagged 64-bit copies of the routing this thread has just written.
+// Launches that publish are serialised on one stream, so the sequence word has a single writer.
+__device__ __forceinline__ void publish_route(const RouterArgs &a) {
+    const uint32_t seq = __ldcg(a.signal) + 1u;
+    for (int i = 0; i < a.topk; i++) {
+        __stcg(&a.pub[i], ((unsigned long long)seq << 32) | (uint32_t)a.top[i]);
+        __stcg(&a.pub[8 + i], ((unsigned long long)seq << 32) | __float_as_uint(a.wts[i]));
+    }
+    __stcg(a.signal, seq);
 }
 
 __global__ void __launch_bounds__(RT_THREADS) ffn_in_kernel(RouterArgs a) {
@@ -195,6 +209,7 @@ __global__ void __launch_bounds__(RT_THREADS) ffn_in_kernel(RouterArgs a) {
         }
         BRRR_STAMP(a.state, 5);
         BRRR_GT_END(a.state, 31);
+        if (gridDim.x == 1 && lane == 0 && a.signal) publish_route(a);      // routing written by this lane
     }
     if (gridDim.x == 1) return;
 
@@ -211,14 +226,19 @@ __global__ void __launch_bounds__(RT_THREADS) ffn_in_kernel(RouterArgs a) {
     for (int e = tid; e < a.ne; e += RT_THREADS) lg[e] = __ldcg(a.logits + e);
     __syncthreads();
     if (warp == 0) warp_topk(a, lg, lane);
-    if (tid == 0) *a.counter = 0u;
+    if (tid == 0) {
+        *a.counter = 0u;
+        if (a.signal) publish_route(a);
+    }
 }
 
 size_t router_packed_floats(int ne, int d) { return (size_t)((ne + 31) / 32) * ((d + RT_TJ - 1) / RT_TJ) * RT_TILE_FLOATS; }
 
 cudaError_t launch_ffn_in(const float *x_in, const float *norm_w, float eps, int d, const float *Wt, const float *b, int ne, int topk,
-                          float *logits, int32_t *top, float *wts, unsigned int *counter, DevState *state, bool pdl, cudaStream_t st, int ntok) {
-    RouterArgs a{x_in, norm_w, eps, d, Wt, b, ne, topk, logits, top, wts, counter, state};
+                          float *logits, int32_t *top, float *wts, unsigned int *counter, DevState *state, bool pdl, cudaStream_t st, int ntok,
+                          uint32_t *signal) {
+    RouterArgs a{x_in, norm_w, eps, d, Wt, b, ne, topk, logits, top, wts, counter, state, signal, (signal && state) ? state->route_pub : nullptr};
+    if (signal && !state) return cudaErrorInvalidValue;
     size_t smem = (size_t)RT_TILE_FLOATS * 4 * RT_STAGES + (size_t)d * 8 + (size_t)((ne + 3) & ~3) * 4 + RT_STAGES * 16;
     static bool configured = false;
     if (!configured) {
@@ -271,6 +291,7 @@ __global__ void __launch_bounds__(HINT_THREADS) router_hint_kernel(HintArgs a) {
         } else { w[p] = make_float4(0.f, 0.f, 0.f, 0.f); nw[p] = w[p]; }
     }
     const float bias = a.b ? a.b[e] : 0.0f;
+    BRRR_GT_START(a.state, 235);
     pdl_wait();
     BRRR_GT_GO(a.state, 224);
     pdl_trigger();

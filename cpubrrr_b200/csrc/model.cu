@@ -135,6 +135,9 @@ struct brrr_model {
     float *dpart = nullptr;      // down: [topk][tiles * 128] row sums
     uint32_t *dcount = nullptr;  // down: arrival counters per row tile
     uint8_t *ximg = nullptr, *himg = nullptr;   // operand images of the token's and of h's Q8 activation
+    int8_t *nq = nullptr;        // Q8 of the normalised residual that the fold leaves for the next q/k/v projection
+    float *ns = nullptr;
+    bool fused_fold = true;      // speculative tensor-core step: fold + next norm/quant in one kernel that waits for the router by flag
     // expert parallelism: this rank holds experts [epc.e_lo, epc.e_lo + epc.e_cnt); the exchange
     // region (slices, flags, step counters) is one allocation shared with the peers through IPC
     bool ep = false, ep_attached = false;
@@ -285,7 +288,10 @@ int enqueue_step(brrr_model *m, bool want, float *trace_dev, int *nlaunch, unsig
     if (trace_dev) CU(cudaMemcpyAsync(trace_dev, m->x, d * sizeof(float), cudaMemcpyDeviceToDevice, s));
     for (int il = 0; il < c.n_layer; il++) {
         Layer &ly = m->L[il];
-        if (on(ST_QKV)) CUL(launch_q8_stream(ly.wqkv, m->x, ly.attn_norm, c.rms_eps, nullptr, nullptr, ly.bqkv, m->qkv, Q8_EPI_BIAS, m->st, pdl && n > 1, s));
+        // fused: the previous layer's fold has left the normalised, quantised residual in nq / ns
+        const bool fused = spec && m->use_mxt && m->fused_fold;
+        if (fused && il > 0) { n++; CUL(launch_q8_stream(ly.wqkv, nullptr, nullptr, 0.0f, m->nq, m->ns, ly.bqkv, m->qkv, Q8_EPI_BIAS, m->st, pdl, s)); }
+        else if (on(ST_QKV)) CUL(launch_q8_stream(ly.wqkv, m->x, ly.attn_norm, c.rms_eps, nullptr, nullptr, ly.bqkv, m->qkv, Q8_EPI_BIAS, m->st, pdl && n > 1, s));
         int window = ((il + 1) % 2 != 0) ? c.sliding_window : 0;         // even layer index: sliding window
         if (window >= BRRR_MAXSEQ) window = 0;
         if (on(ST_ATTN)) CUL(launch_attn_decode(m->qkv, ly.kc, ly.vc, m->rope, ly.sinks, nh, nkv, m->st, 0, window, m->ao, m->aq, m->as, m->st, pdl, s));
@@ -298,7 +304,7 @@ int enqueue_step(brrr_model *m, bool want, float *trace_dev, int *nlaunch, unsig
             CU(cudaStreamWaitEvent(m->side, m->ev_fork, 0));
             n++;
             CUL(launch_ffn_in(m->x, ly.ffn_norm, c.rms_eps, d, ly.ginp, ly.ginp_b, c.n_expert, topk, m->rlogits, m->top, m->wts,
-                              &m->st->router_done, m->st, false, m->side));
+                              &m->st->router_done, m->st, false, m->side, 1, fused ? &m->st->router_seq : nullptr));
             CU(cudaEventRecord(m->ev_join, m->side));
             n++;
             CUL(launch_router_hint(m->x, ly.ffn_norm, c.rms_eps, d, ly.ginp, ly.ginp_b, c.n_expert, topk, m->est, m->xq, m->xs, m->st, pdl, s,
@@ -313,6 +319,19 @@ int enqueue_step(brrr_model *m, bool want, float *trace_dev, int *nlaunch, unsig
                 n++;
                 CUL(launch_down_t(ly.down_t, ly.down_b, nullptr, nullptr, m->est, c.n_expert, topk, m->sabotage, d, m->himg, m->hs, m->x,
                                   m->dpart, m->dcount, m->st, pdl, s));
+            }
+            if (fused) {
+                // The fold is launched programmatically behind down and waits for the router's
+                // publication counter itself; it also normalises and quantises the new residual for
+                // the next q/k/v projection (the last layer: for the vocabulary head).  The side
+                // stream joins once, after the last layer.
+                const bool last = il == c.n_layer - 1;
+                const float *nw = last ? (want ? m->out_norm : nullptr) : m->L[il + 1].attn_norm;
+                n++;
+                CUL(launch_fold_norm(m->top, m->wts, m->est, c.n_expert, topk, m->sabotage, d, m->dpart, ly.down_b, m->x, nw, c.rms_eps,
+                                     last ? m->xq : m->nq, last ? m->xs : m->ns, &m->st->router_seq, &m->st->fold_seq, m->st, pdl, s));
+                if (last) CU(cudaStreamWaitEvent(s, m->ev_join, 0));
+                continue;
             }
             CU(cudaStreamWaitEvent(s, m->ev_join, 0));
             n++;
@@ -341,8 +360,9 @@ int enqueue_step(brrr_model *m, bool want, float *trace_dev, int *nlaunch, unsig
         if (trace_dev) CU(cudaMemcpyAsync(trace_dev + (size_t)(il + 1) * d, m->x, d * sizeof(float), cudaMemcpyDeviceToDevice, s));
     }
     if (want) {
-        if (on(ST_HEAD_NORM)) CUL(launch_rmsnorm_quant(m->x, m->out_norm, c.rms_eps, d, nullptr, m->xq, m->xs, pdl, s));
-        if (on(ST_HEAD)) CUL(launch_q8_direct(m->head, m->xq, m->xs, nullptr, m->logits, Q8_EPI_HEAD, m->st, pdl, s));
+        const bool fused = spec && m->use_mxt && m->fused_fold;      // the last fold has written the head's activation; the side stream has just joined
+        if (!fused && on(ST_HEAD_NORM)) CUL(launch_rmsnorm_quant(m->x, m->out_norm, c.rms_eps, d, nullptr, m->xq, m->xs, pdl, s));
+        if (on(ST_HEAD)) CUL(launch_q8_direct(m->head, m->xq, m->xs, nullptr, m->logits, Q8_EPI_HEAD, m->st, pdl && !fused, s));
         if (on(ST_FINISH)) launch_finish_token(m->st, s);
     }
     CU(cudaGetLastError());
@@ -417,6 +437,7 @@ int build_model(brrr_model *m, const Source &src) {
         const size_t rest = (size_t)c.n_vocab * d * 4 + (size_t)c.n_layer * ((size_t)(qkv_rows + d) * d * 2 + (size_t)BRRR_MAXSEQ * nkv * hd * 8) + (2ull << 30);
         m->use_mxt = !m->ep && d % 64 == 0 && nb % 2 == 0 && topk <= 8 && free_b > experts * 2.2 + rest;
         if (const char *e = getenv("BRRR_NOMXT")) if (e[0] && e[0] != '0') m->use_mxt = false;
+        if (const char *e = getenv("BRRR_NOFUSEDFOLD")) if (e[0] && e[0] != '0') m->fused_fold = false;
     }
     for (int il = 0; il < c.n_layer; il++) {
         Layer &ly = m->L[il];
@@ -477,6 +498,7 @@ int build_model(brrr_model *m, const Source &src) {
     TRY(m->alloc(&m->xq, d)); TRY(m->alloc(&m->aq, nh * hd)); TRY(m->alloc(&m->hq, (size_t)topk * d));
     TRY(m->alloc(&m->top, 8)); TRY(m->alloc(&m->st, 1));
     TRY(m->alloc(&m->est, (size_t)ne));
+    TRY(m->alloc(&m->nq, d)); TRY(m->alloc(&m->ns, nb));
     TRY(m->alloc(&m->dpart, (size_t)topk * ((d + 127) / 128) * 128));
     TRY(m->alloc(&m->dcount, (size_t)(d + 127) / 128));
     CU(cudaMemsetAsync(m->dcount, 0, (size_t)((d + 127) / 128) * 4, m->stream));
