@@ -72,8 +72,20 @@ __device__ __forceinline__ float block_rms_inv(const float *x, int n, float eps,
 // Must be called by all threads; nthreads % 32 == 0, n % 32 == 0, x and norm_w 16-byte aligned.
 // Ends with the image complete but NOT yet synchronised.
 enum { NQ_Q8 = 0, NQ_MX = 1, NQ_NATURAL = 2 };
+// global -> shared copy of n floats (n % 4 == 0, 16-byte aligned).  Up to eight loads are issued before the first
+// store: a store to shared memory between them would keep the compiler from overlapping the loads
+// (it cannot rule out aliasing), and every load is a full round trip to L2.
 __device__ __forceinline__ void stage_vec4(const float *__restrict__ src, float *dst, int n, int tid, int nthreads) {
-    for (int g = tid; g < (n >> 2); g += nthreads) reinterpret_cast<float4 *>(dst)[g] = reinterpret_cast<const float4 *>(src)[g];
+    const int groups = n >> 2;
+    const float4 *s4 = reinterpret_cast<const float4 *>(src);
+    float4 *d4 = reinterpret_cast<float4 *>(dst);
+    for (int g0 = tid; g0 < groups; g0 += 8 * nthreads) {
+        float4 v[8];
+#pragma unroll
+        for (int k = 0; k < 8; k++) if (g0 + k * nthreads < groups) v[k] = s4[g0 + k * nthreads];
+#pragma unroll
+        for (int k = 0; k < 8; k++) if (g0 + k * nthreads < groups) d4[g0 + k * nthreads] = v[k];
+    }
 }
 
 template <int MAXG>
@@ -92,10 +104,7 @@ __device__ __forceinline__ void block_norm_quant_staged(const float *norm_w, con
 template <int LAYOUT, int MAXG>
 __device__ __forceinline__ void block_norm_quant(const float *__restrict__ x, const float *norm_w, const float4 (&wreg)[MAXG], float eps, int n,
                                                  float *xf, int2 *xp, float *xsc, float *inv_sh, int tid, int nthreads) {
-    const int groups = n >> 2;
-    const float4 *x4 = reinterpret_cast<const float4 *>(x);
-    float4 *xf4 = reinterpret_cast<float4 *>(xf);
-    for (int g = tid; g < groups; g += nthreads) xf4[g] = x4[g];
+    stage_vec4(x, xf, n, tid, nthreads);
     __syncthreads();
     block_norm_quant_staged<LAYOUT, MAXG>(norm_w, wreg, eps, n, xf, xp, xsc, inv_sh, tid, nthreads);
 }

@@ -371,9 +371,13 @@ __global__ void __launch_bounds__(XT_THREADS) xt_expert_kernel(XtArgs a) {
         uint32_t spar = 0, dpar = 0;
         const float *xsp = sh.xsc;
 #pragma unroll 1
+        long long tw_full = 0, tw_sc = 0, tw_d = 0, tw_ld = 0, tw_math = 0;
+        (void)tw_full; (void)tw_sc; (void)tw_d; (void)tw_ld; (void)tw_math;
         for (int r = 0; r < nchunks; r++) {
             const int cnt = left < XT_CH ? left : XT_CH;
+            XT_T0();
             xt_wait(&sh.full[s], spar, err);                    // the stage's exponent bytes are visible
+            XT_ACC(tw_full);
             const unsigned char *ex = sh.ring + stage_bytes * s + MXT_UNIT_EXPS + m * 2;
             uint32_t e2[XT_CH];
 #pragma unroll
@@ -384,10 +388,13 @@ __global__ void __launch_bounds__(XT_THREADS) xt_expert_kernel(XtArgs a) {
             sc[2] = __fmul_rn(sh.tbl[e2[1] & 0xFFu], xa.z); sc[3] = __fmul_rn(sh.tbl[e2[1] >> 8], xa.w);
             sc[4] = __fmul_rn(sh.tbl[e2[2] & 0xFFu], xb.x); sc[5] = __fmul_rn(sh.tbl[e2[2] >> 8], xb.y);
             sc[6] = __fmul_rn(sh.tbl[e2[3] & 0xFFu], xb.z); sc[7] = __fmul_rn(sh.tbl[e2[3] >> 8], xb.w);
+            XT_ACC(tw_sc);
             xt_wait(&sh.dfull[reg], dpar, err);
+            XT_ACC(tw_d);
             xt_fence_after();
             xt_ld96(lane_addr + reg * XT_REGION_COLS, dv);
             xt_wait_ld96(dv);
+            XT_ACC(tw_ld);
             xt_fence_before();
             __syncwarp();
             if (lane == 0) {
@@ -401,9 +408,16 @@ __global__ void __launch_bounds__(XT_THREADS) xt_expert_kernel(XtArgs a) {
             left -= XT_CH;
             if (++s == a.stages) { s = 0; spar ^= 1u; }
             if (++reg == XT_REGIONS) { reg = 0; dpar ^= 1u; }
+            XT_ACC(tw_math);
             if (r < 12) BRRR_STAMP(a.state, SB + 4 + r);
         }
         BRRR_STAMP(a.state, SB + 16);
+#ifdef BRRR_TIMELINE
+        if (a.state && tid == 0 && blockIdx.x == BRRR_STAMP_BX && blockIdx.y == 0) {
+            long long *o = a.state->stamps + (DOWN ? 205 : 200);
+            o[0] = tw_full; o[1] = tw_sc; o[2] = tw_d; o[3] = tw_ld; o[4] = tw_math;
+        }
+#endif
         const float v = xt_row_sum(acc);
         if (!DOWN) {
             gu_s[m >> 6][m & 63] = __fadd_rn(v, bias_pre);

@@ -185,12 +185,28 @@ __global__ void __launch_bounds__(Q8_THREADS) q8_stream_kernel(Q8Args a) {
     if (NORM) {
         block_norm_quant<NQ_Q8, 6>(a.x_f32, a.norm_w, wreg, a.eps, a.m.cols, xf, xp, xsc, &inv_sh, tid, Q8_THREADS);
     } else {
-        for (int idx = tid; idx < nb * 4; idx += Q8_THREADS) {
-            int b = idx >> 2, j = idx & 3;
-            const int *xw = reinterpret_cast<const int *>(a.xq + b * 32);
-            xp[idx] = make_int2(xw[j], xw[4 + j]);
+        // every load before the first store to shared memory: a store in between would order the
+        // loads behind it (possible aliasing), and each is a round trip to L2 on the critical path
+        const int nidx = nb * 4;
+        float sv[2];
+#pragma unroll
+        for (int k = 0; k < 2; k++) sv[k] = tid + k * Q8_THREADS < nb ? a.xs[tid + k * Q8_THREADS] : 0.0f;
+        for (int i0 = tid; i0 < nidx; i0 += 8 * Q8_THREADS) {
+            int2 v[8];
+#pragma unroll
+            for (int k = 0; k < 8; k++) {
+                const int idx = i0 + k * Q8_THREADS;
+                if (idx < nidx) {
+                    const int *xw = reinterpret_cast<const int *>(a.xq + (idx >> 2) * 32);
+                    v[k] = make_int2(xw[idx & 3], xw[4 + (idx & 3)]);
+                }
+            }
+#pragma unroll
+            for (int k = 0; k < 8; k++) if (i0 + k * Q8_THREADS < nidx) xp[i0 + k * Q8_THREADS] = v[k];
         }
-        for (int b = tid; b < nb; b += Q8_THREADS) xsc[b] = a.xs[b];
+#pragma unroll
+        for (int k = 0; k < 2; k++) if (tid + k * Q8_THREADS < nb) xsc[tid + k * Q8_THREADS] = sv[k];
+        for (int b = tid + 2 * Q8_THREADS; b < nb; b += Q8_THREADS) xsc[b] = a.xs[b];
     }
     __syncthreads();
 

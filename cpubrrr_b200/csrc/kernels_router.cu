@@ -167,7 +167,7 @@ __global__ void __launch_bounds__(RT_THREADS) ffn_in_kernel(RouterArgs a) {
     BRRR_GT_GO(a.state, 30);
     pdl_trigger();
     waiter.poison_if_failed();
-    for (int i = tid; i < d / 4; i += RT_THREADS) reinterpret_cast<float4 *>(xn)[i] = reinterpret_cast<const float4 *>(a.x_in)[i];
+    stage_vec4(a.x_in, xn, d, tid, RT_THREADS);
     __syncthreads();
     if (a.norm_w) {
         float inv = block_rms_inv(xn, d, a.eps, &inv_sh);
