@@ -377,7 +377,7 @@ def main():
                           "frac_of_8TBs": step_bytes / (ms / K) / 1e6 / 8000.0},
     }
     if not args.no_stages:
-        st = eng.stage_times(mid, reps=10)
+        st = [r for r in eng.stage_times(mid, reps=10) if r[3] > 0]      # classes the step does not launch report 0 launches
         tot = sum(t * n for _, t, _, n in st)
         stages = [{"kernel": nm, "launches_per_step": n, "us_per_launch": 1000 * t, "share": t * n / tot,
                    "bytes_per_launch": by, "gbs": by / t / 1e6 if t > 0 else 0.0} for nm, t, by, n in st]

@@ -10,6 +10,7 @@ namespace brrr {
 void launch_quant_q8(const float *x, int n, int8_t *q, float *s, cudaStream_t st);
 cudaError_t launch_rmsnorm_quant(const float *x, const float *w, float eps, int n, float *xn, int8_t *q, float *s, bool pdl, cudaStream_t st);
 void launch_embed(const uint16_t *embd, int d, const DevState *state, float *x, cudaStream_t st);
+void launch_embed_tok(const uint16_t *embd, int d, uint32_t tok, float *x, cudaStream_t st);
 void launch_swiglu_quant(const float *gu, int topk, int d, int8_t *hq, float *hs, cudaStream_t st);
 void launch_finish_token(DevState *state, cudaStream_t st);
 void launch_expf(const float *x, int n, float *y, cudaStream_t st);

@@ -54,6 +54,16 @@ __global__ void embed_kernel(const uint16_t *__restrict__ embd, int d, const Dev
         x[j] = brrr_bf16_to_f32(embd[tok * d + j]);
 }
 
+// the same for a token id given by the host (token tiles)
+__global__ void embed_tok_kernel(const uint16_t *__restrict__ embd, int d, uint32_t tok, float *__restrict__ x) {
+    for (int j = blockIdx.x * blockDim.x + threadIdx.x; j < d; j += gridDim.x * blockDim.x)
+        x[j] = brrr_bf16_to_f32(embd[(size_t)tok * d + j]);
+}
+
+void launch_embed_tok(const uint16_t *embd, int d, uint32_t tok, float *x, cudaStream_t st) {
+    embed_tok_kernel<<<(d + 255) / 256, 256, 0, st>>>(embd, d, tok, x);
+}
+
 void launch_embed(const uint16_t *embd, int d, const DevState *state, float *x, cudaStream_t st) {
     embed_kernel<<<(d + 255) / 256, 256, 0, st>>>(embd, d, state, x);
 }

@@ -149,6 +149,8 @@ struct brrr_model {
     float *tl_xs = nullptr, *tl_hs = nullptr, *tl_logits = nullptr, *tl_wts = nullptr, *tl_gu = nullptr, *tl_part = nullptr;
     int32_t *tl_top = nullptr;
     int *tl_cnt = nullptr, *tl_list = nullptr;
+    float *tl_x = nullptr, *tl_xn = nullptr;     // prompt tiles: residual and normalised residual of up to 16 tokens
+    bool serial_tiles = false;                   // BRRR_SERIAL_TILES=1: run_tile token by token (A/B and cross-check)
     unsigned int *tl_counter = nullptr;
     std::vector<void *> allocs;
 
@@ -259,9 +261,10 @@ int check_cfg(const brrr_cfg &c) {
 
 // The decode step, enqueued kernel by kernel (captured into a graph, or run directly by the
 // trace path).  Stage order and data flow follow forward_worker (engine_gpt2.rs:751-934).
-enum { ST_EMBED = 0, ST_QKV, ST_ATTN, ST_OPROJ, ST_ROUTER, ST_GATE_UP, ST_DOWN, ST_HEAD_NORM, ST_HEAD, ST_FINISH, ST_COUNT };
+enum { ST_EMBED = 0, ST_QKV, ST_ATTN, ST_OPROJ, ST_ROUTER, ST_GATE_UP, ST_DOWN, ST_FOLD, ST_HEAD_NORM, ST_HEAD, ST_FINISH, ST_COUNT };
 const char *const kStageNames[ST_COUNT] = {"embed", "norm_qkv_gemv", "attention", "oproj_gemv", "norm_router_topk",
-                                           "norm_gate_up_swiglu_mxfp4", "down_combine_mxfp4", "head_norm_quant", "head_gemv_argmax", "finish_token"};
+                                           "norm_gate_up_swiglu_mxfp4", "down_combine_mxfp4", "fold_norm_quant", "head_norm_quant", "head_gemv_argmax",
+                                           "finish_token"};
 
 #define CUL(call)                                                                                        \
     do {                                                                                                 \
@@ -291,7 +294,9 @@ int enqueue_step(brrr_model *m, bool want, float *trace_dev, int *nlaunch, unsig
         // fused: the previous layer's fold has left the normalised, quantised residual in nq / ns
         const bool fused = spec && m->use_mxt && m->fused_fold;
         if (fused && il > 0) { n++; CUL(launch_q8_stream(ly.wqkv, nullptr, nullptr, 0.0f, m->nq, m->ns, ly.bqkv, m->qkv, Q8_EPI_BIAS, m->st, pdl, s)); }
-        else if (on(ST_QKV)) CUL(launch_q8_stream(ly.wqkv, m->x, ly.attn_norm, c.rms_eps, nullptr, nullptr, ly.bqkv, m->qkv, Q8_EPI_BIAS, m->st, pdl && n > 1, s));
+        else if (mask != ~0u && m->use_mxt && m->use_spec && m->fused_fold && il > 0) {      // stage replay of the fused step's q/k/v (image left by the last step)
+            if (on(ST_QKV)) CUL(launch_q8_stream(ly.wqkv, nullptr, nullptr, 0.0f, m->nq, m->ns, ly.bqkv, m->qkv, Q8_EPI_BIAS, m->st, pdl, s));
+        } else if (on(ST_QKV)) CUL(launch_q8_stream(ly.wqkv, m->x, ly.attn_norm, c.rms_eps, nullptr, nullptr, ly.bqkv, m->qkv, Q8_EPI_BIAS, m->st, pdl && n > 1, s));
         int window = ((il + 1) % 2 != 0) ? c.sliding_window : 0;         // even layer index: sliding window
         if (window >= BRRR_MAXSEQ) window = 0;
         if (on(ST_ATTN)) CUL(launch_attn_decode(m->qkv, ly.kc, ly.vc, m->rope, ly.sinks, nh, nkv, m->st, 0, window, m->ao, m->aq, m->as, m->st, pdl, s));
@@ -346,8 +351,12 @@ int enqueue_step(brrr_model *m, bool want, float *trace_dev, int *nlaunch, unsig
                                                  &m->st->router_done, m->st, pdl, s));
             if (on(ST_GATE_UP)) CUL(launch_gate_up_t(ly.gu_t, ly.gate_b, ly.up_b, m->top, nullptr, 0, topk, 0, d, m->ximg, m->xs, m->hq, m->hs, m->himg,
                                                      m->st, pdl, s));
-            if (on(ST_DOWN)) CUL(launch_down_t(ly.down_t, ly.down_b, m->top, m->wts, nullptr, 0, topk, 0, d, m->himg, m->hs, m->x, m->dpart, m->dcount,
-                                               m->st, pdl, s));
+            const bool ff = m->use_spec && m->fused_fold;     // the fused step: down leaves partial sums, a fold kernel finishes
+            if (on(ST_DOWN)) CUL(launch_down_t(ly.down_t, ly.down_b, m->top, ff ? nullptr : m->wts, nullptr, 0, topk, 0, d, m->himg, m->hs, m->x, m->dpart,
+                                               m->dcount, m->st, pdl, s));
+            if (ff && on(ST_FOLD))
+                CUL(launch_fold_norm(m->top, m->wts, nullptr, 0, topk, 0, d, m->dpart, ly.down_b, m->x,
+                                     il + 1 < c.n_layer ? m->L[il + 1].attn_norm : m->out_norm, c.rms_eps, m->nq, m->ns, nullptr, nullptr, m->st, pdl, s));
         } else {
         if (on(ST_ROUTER)) CUL(launch_ffn_in(m->x, ly.ffn_norm, c.rms_eps, d, ly.ginp, ly.ginp_b, c.n_expert, topk, m->rlogits, m->top, m->wts,
                                              &m->st->router_done, m->st, pdl, s));
@@ -361,7 +370,8 @@ int enqueue_step(brrr_model *m, bool want, float *trace_dev, int *nlaunch, unsig
     }
     if (want) {
         const bool fused = spec && m->use_mxt && m->fused_fold;      // the last fold has written the head's activation; the side stream has just joined
-        if (!fused && on(ST_HEAD_NORM)) CUL(launch_rmsnorm_quant(m->x, m->out_norm, c.rms_eps, d, nullptr, m->xq, m->xs, pdl, s));
+        const bool replay_fused = mask != ~0u && m->use_mxt && m->use_spec && m->fused_fold;      // stage replays mirror the fused step
+        if (!fused && !replay_fused && on(ST_HEAD_NORM)) CUL(launch_rmsnorm_quant(m->x, m->out_norm, c.rms_eps, d, nullptr, m->xq, m->xs, pdl, s));
         if (on(ST_HEAD)) CUL(launch_q8_direct(m->head, m->xq, m->xs, nullptr, m->logits, Q8_EPI_HEAD, m->st, pdl && !fused, s));
         if (on(ST_FINISH)) launch_finish_token(m->st, s);
     }
@@ -438,6 +448,7 @@ int build_model(brrr_model *m, const Source &src) {
         m->use_mxt = !m->ep && d % 64 == 0 && nb % 2 == 0 && topk <= 8 && free_b > experts * 2.2 + rest;
         if (const char *e = getenv("BRRR_NOMXT")) if (e[0] && e[0] != '0') m->use_mxt = false;
         if (const char *e = getenv("BRRR_NOFUSEDFOLD")) if (e[0] && e[0] != '0') m->fused_fold = false;
+        if (const char *e = getenv("BRRR_SERIAL_TILES")) if (e[0] && e[0] != '0') m->serial_tiles = true;
     }
     for (int il = 0; il < c.n_layer; il++) {
         Layer &ly = m->L[il];
@@ -785,13 +796,69 @@ extern "C" int brrr_forward(brrr_model *m, uint32_t tok, uint32_t pos, int want,
     return BRRR_OK;
 }
 
+static int moe_tile_enqueue(brrr_model *m, int il, const float *d_xn, float *d_x, int ntok);
+
+// One tile of up to 16 prompt tokens (forward_tile_worker, src/bin/engine_gpt2.rs:1011-1250): the
+// tokens walk the layers together.  Attention is causal inside the tile, so q/k/v, attention and the
+// output projection run token by token (each token's K and V are in the cache before the next token
+// attends); the MoE block, where the weight bytes are, runs once per layer for the whole tile on the
+// tensor-core tile kernels (kernels_tile.cu), streaming each routed expert once for all its tokens.
+// Every value is bit-identical to the token-serial schedule.
+static int forward_tile_16(brrr_model *m, const uint32_t *toks, int n, uint32_t pos0, bool want) {
+    const brrr_cfg &c = m->cfg;
+    const int d = c.n_embd, nh = c.n_head, nkv = c.n_head_kv;
+    cudaStream_t s = m->stream;
+    if (!m->tl_x) { TRY(m->alloc(&m->tl_x, (size_t)16 * d)); TRY(m->alloc(&m->tl_xn, (size_t)16 * d)); }
+    for (int t = 0; t < n; t++) launch_embed_tok(m->tok_embd, d, toks[t], m->tl_x + (size_t)t * d, s);
+    for (int il = 0; il < c.n_layer; il++) {
+        Layer &ly = m->L[il];
+        int window = ((il + 1) % 2 != 0) ? c.sliding_window : 0;
+        if (window >= BRRR_MAXSEQ) window = 0;
+        for (int t = 0; t < n; t++) {
+            float *x = m->tl_x + (size_t)t * d;
+            CUL(launch_q8_stream(ly.wqkv, x, ly.attn_norm, c.rms_eps, nullptr, nullptr, ly.bqkv, m->qkv, Q8_EPI_BIAS, m->st, false, s));
+            CUL(launch_attn_decode(m->qkv, ly.kc, ly.vc, m->rope, ly.sinks, nh, nkv, nullptr, (int)pos0 + t, window, m->ao, m->aq, m->as, m->st, false, s));
+            CUL(launch_q8_stream(ly.wo, nullptr, nullptr, 0.0f, m->aq, m->as, ly.bo, x, Q8_EPI_RESID_BIAS, m->st, false, s));
+            CUL(launch_rmsnorm_quant(x, ly.ffn_norm, c.rms_eps, d, m->tl_xn + (size_t)t * d, m->xq, m->xs, false, s));
+        }
+        TRY(moe_tile_enqueue(m, il, m->tl_xn, m->tl_x, n));
+    }
+    // leave the engine as the serial schedule would after the tile's last token
+    CU(cudaMemcpyAsync(m->x, m->tl_x + (size_t)(n - 1) * d, (size_t)d * sizeof(float), cudaMemcpyDeviceToDevice, s));
+    m->h_in[0] = toks[n - 1]; m->h_in[1] = pos0 + (uint32_t)n - 1;
+    CU(cudaMemcpyAsync(m->st, m->h_in, 8, cudaMemcpyHostToDevice, s));
+    if (want) {
+        CUL(launch_rmsnorm_quant(m->x, m->out_norm, c.rms_eps, d, nullptr, m->xq, m->xs, false, s));
+        CUL(launch_q8_direct(m->head, m->xq, m->xs, nullptr, m->logits, Q8_EPI_HEAD, m->st, false, s));
+        launch_finish_token(m->st, s);
+    }
+    CU(cudaGetLastError());
+    return BRRR_OK;
+}
+
 extern "C" int brrr_forward_tile(brrr_model *m, const uint32_t *toks, uint32_t n, uint32_t pos0, int want, uint32_t *out_tok) {
     if (!m || !toks || n == 0) return BRRR_ERR_ARG;
     if (pos0 + n > BRRR_MAXSEQ) return BRRR_ERR_RANGE;
-    // Token-serial schedule: bit-identical to the batched tile by the reference's own guarantee.
-    for (uint32_t i = 0; i < n; i++) {
-        int s = brrr_forward(m, toks[i], pos0 + i, want && i == n - 1, out_tok);
-        if (s != BRRR_OK) return s;
+    for (uint32_t i = 0; i < n; i++) if (toks[i] >= (uint32_t)m->cfg.n_vocab) return BRRR_ERR_RANGE;
+    CU(cudaSetDevice(m->device));
+    const bool serial = m->ep || m->serial_tiles;     // expert-parallel ranks keep the token-serial schedule (same results)
+    for (uint32_t i0 = 0; i0 < n; i0 += 16) {
+        const uint32_t cnt = n - i0 < 16 ? n - i0 : 16;
+        const bool last = i0 + cnt == n;
+        if (serial || cnt == 1) {
+            for (uint32_t i = i0; i < i0 + cnt; i++) {
+                int st = brrr_forward(m, toks[i], pos0 + i, want && i == n - 1, out_tok);
+                if (st != BRRR_OK) return st;
+            }
+            continue;
+        }
+        TRY(forward_tile_16(m, toks + i0, (int)cnt, pos0 + i0, want && last));
+        if (last) {
+            CU(cudaMemcpyAsync(m->h_out, m->st, 32, cudaMemcpyDeviceToHost, m->stream));   // tok .. err
+            CU(cudaStreamSynchronize(m->stream));
+            if (m->h_out[6] != 0) { snprintf(g_cuda_err, sizeof g_cuda_err, "device wait timed out (code %u)", m->h_out[6]); return BRRR_ERR_STATE; }
+            if (want && out_tok) *out_tok = m->h_out[0];
+        }
     }
     return BRRR_OK;
 }
@@ -923,10 +990,8 @@ extern "C" int brrr_model_uses_tensor_experts(const brrr_model *m) { return m &&
 // routing lists per expert, then three grouped tensor-core matmuls (gate, up, down) that read every
 // needed expert matrix once for all its tokens, SwiGLU + Q8 per (token, slot), and the fold in slot
 // order.  Bit-identical to brrr_moe_ffn_step applied to the tokens one by one.
-extern "C" int brrr_moe_ffn_tile(brrr_model *m, int il, const float *d_xn, float *d_x, int ntok, int32_t *d_top, float *d_wts) {
-    if (!m || !d_xn || !d_x || il < 0 || il >= m->cfg.n_layer || ntok < 1 || ntok > 16) return BRRR_ERR_ARG;
-    if (m->ep) return BRRR_ERR_STATE;
-    CU(cudaSetDevice(m->device));
+// Enqueue only (no synchronisation): the tile's MoE step on m->stream.
+static int moe_tile_enqueue(brrr_model *m, int il, const float *d_xn, float *d_x, int ntok) {
     const brrr_cfg &c = m->cfg;
     const int d = c.n_embd, nb = d / 32, topk = c.n_expert_used, ne = c.n_expert, np_ = 16 * topk;
     if (!m->tl_xq) {
@@ -948,6 +1013,16 @@ extern "C" int brrr_moe_ffn_tile(brrr_model *m, int il, const float *d_xn, float
     CUL(launch_mx_tile_experts(ly.down, ne, d, m->tl_cnt, m->tl_list, 1, m->tl_hq, m->tl_hs, ly.down_b, m->tl_part, d, 0, m->st, s));
     launch_tile_combine(m->tl_part, m->tl_wts, topk, d, ntok, d_x, s);
     CU(cudaGetLastError());
+    return BRRR_OK;
+}
+
+extern "C" int brrr_moe_ffn_tile(brrr_model *m, int il, const float *d_xn, float *d_x, int ntok, int32_t *d_top, float *d_wts) {
+    if (!m || !d_xn || !d_x || il < 0 || il >= m->cfg.n_layer || ntok < 1 || ntok > 16) return BRRR_ERR_ARG;
+    if (m->ep) return BRRR_ERR_STATE;
+    CU(cudaSetDevice(m->device));
+    const int topk = m->cfg.n_expert_used;
+    cudaStream_t s = m->stream;
+    TRY(moe_tile_enqueue(m, il, d_xn, d_x, ntok));
     if (d_top) CU(cudaMemcpy2DAsync(d_top, topk * sizeof(int32_t), m->tl_top, 8 * sizeof(int32_t), topk * sizeof(int32_t), ntok, cudaMemcpyDeviceToDevice, s));
     if (d_wts) CU(cudaMemcpy2DAsync(d_wts, topk * sizeof(float), m->tl_wts, 8 * sizeof(float), topk * sizeof(float), ntok, cudaMemcpyDeviceToDevice, s));
     CU(cudaStreamSynchronize(s));
@@ -977,6 +1052,7 @@ static uint64_t stage_bytes_per_launch(const brrr_model *m, int stage, uint32_t 
     case ST_ROUTER: return ne * d * 4 + ne * 4 + d * 8;
     case ST_GATE_UP: return k * 2 * d * nb * 17 + k * 2 * d * 4 + d * 8;
     case ST_DOWN: return k * d * nb * 17 + k * d * 4;
+    case ST_FOLD: return 2 * k * d * 4 + 3 * d * 4 + d + nb * 4;       // partial sums, biases, residual in and out, norm weights, Q8 image out
     case ST_HEAD_NORM: return d * 8;
     case ST_HEAD: return q8(c.n_vocab, d);
     }

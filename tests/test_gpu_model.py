@@ -238,3 +238,30 @@ def test_speculation_can_be_disabled(brrr, orc, monkeypatch):
     prompt = S.synth_prompt(5, 6, 500)
     assert greedy(eng.run, prompt, 20) == greedy(om.run, prompt, 20)
     eng.close()
+
+
+def test_prompt_tiles_match_serial(brrr):
+    """run_tile walks tiles of 16 tokens through the layers together (MoE block on the tensor-core tile
+    kernels); the reference guarantees its batched prefill is bit-identical to the token-serial
+    schedule (src/bin/engine_gpt2.rs:1005-1010).  Checked on the last token's hidden state and logits,
+    on the returned token, and on a decode run that reads the KV cache the tiles wrote.  37 tokens =
+    two full tiles and a ragged one; a 1-token call takes the serial path."""
+    cfg = brrr.make_cfg(256, 3, 8, 2, 8, 4, 1024, sliding_window=8)
+    eng = brrr.Engine.synth(cfg, 11)
+    prompt = [int(t) for t in S.synth_prompt(11, 37, 1000)]
+    tok_s = 0
+    for i, t in enumerate(prompt):
+        tok_s = eng.run(t, i, i == len(prompt) - 1)
+    h_s, l_s = eng.hidden(), eng.logits()
+    dec_s = eng.decode(tok_s, len(prompt), 24)
+    tok_t = eng.run_tile(prompt, 0, True)
+    h_t, l_t = eng.hidden(), eng.logits()
+    dec_t = eng.decode(tok_t, len(prompt), 24)
+    assert tok_t == tok_s
+    assert np.array_equal(bits(h_t), bits(h_s)) and np.array_equal(bits(l_t), bits(l_s))
+    assert np.array_equal(dec_t, dec_s)
+    # want=False leaves the same state; a following single step continues from it
+    eng.run_tile(prompt[:-1], 0, False)
+    assert eng.run(prompt[-1], len(prompt) - 1, True) == tok_s
+    assert eng.run_tile(prompt[:1], 0, True) == eng.run(prompt[0], 0, True)
+    eng.close()
