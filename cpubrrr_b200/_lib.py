@@ -36,6 +36,7 @@ SIGNATURES = {
     "brrr_model_close": (None, [_P]),
     "brrr_forward": (_I, [_P, C.c_uint32, C.c_uint32, _I, C.POINTER(C.c_uint32)]),
     "brrr_forward_tile": (_I, [_P, _P, C.c_uint32, C.c_uint32, _I, C.POINTER(C.c_uint32)]),
+    "brrr_model_set_tile_prefill": (_I, [_P, _I]),
     "brrr_decode": (_I, [_P, C.c_uint32, C.c_uint32, C.c_uint32, _P]),
     "brrr_decode_enqueue": (_I, [_P, C.c_uint32, C.c_uint32, C.c_uint32]),
     "brrr_decode_wait": (_I, [_P, C.c_uint32, _P]),

@@ -150,7 +150,7 @@ struct brrr_model {
     int32_t *tl_top = nullptr;
     int *tl_cnt = nullptr, *tl_list = nullptr;
     float *tl_x = nullptr, *tl_xn = nullptr;     // prompt tiles: residual and normalised residual of up to 16 tokens
-    bool serial_tiles = false;                   // BRRR_SERIAL_TILES=1: run_tile token by token (A/B and cross-check)
+    bool tile_prefill = false;                   // run_tile on 16-token tiles (brrr_model_set_tile_prefill / BRRR_TILE_PREFILL=1); default: token-serial, which is faster today
     unsigned int *tl_counter = nullptr;
     std::vector<void *> allocs;
 
@@ -448,7 +448,7 @@ int build_model(brrr_model *m, const Source &src) {
         m->use_mxt = !m->ep && d % 64 == 0 && nb % 2 == 0 && topk <= 8 && free_b > experts * 2.2 + rest;
         if (const char *e = getenv("BRRR_NOMXT")) if (e[0] && e[0] != '0') m->use_mxt = false;
         if (const char *e = getenv("BRRR_NOFUSEDFOLD")) if (e[0] && e[0] != '0') m->fused_fold = false;
-        if (const char *e = getenv("BRRR_SERIAL_TILES")) if (e[0] && e[0] != '0') m->serial_tiles = true;
+        if (const char *e = getenv("BRRR_TILE_PREFILL")) if (e[0] && e[0] != '0') m->tile_prefill = true;
     }
     for (int il = 0; il < c.n_layer; il++) {
         Layer &ly = m->L[il];
@@ -841,7 +841,10 @@ extern "C" int brrr_forward_tile(brrr_model *m, const uint32_t *toks, uint32_t n
     if (pos0 + n > BRRR_MAXSEQ) return BRRR_ERR_RANGE;
     for (uint32_t i = 0; i < n; i++) if (toks[i] >= (uint32_t)m->cfg.n_vocab) return BRRR_ERR_RANGE;
     CU(cudaSetDevice(m->device));
-    const bool serial = m->ep || m->serial_tiles;     // expert-parallel ranks keep the token-serial schedule (same results)
+    // Both schedules give the same bits.  The tile schedule amortises only the MoE block so far (the
+    // dense projections still run per token, without the decode step's graph), and measures slower
+    // than the graph-per-token schedule; it is therefore opt-in.  Expert-parallel ranks stay serial.
+    const bool serial = m->ep || !m->tile_prefill;
     for (uint32_t i0 = 0; i0 < n; i0 += 16) {
         const uint32_t cnt = n - i0 < 16 ? n - i0 : 16;
         const bool last = i0 + cnt == n;
@@ -860,6 +863,12 @@ extern "C" int brrr_forward_tile(brrr_model *m, const uint32_t *toks, uint32_t n
             if (want && out_tok) *out_tok = m->h_out[0];
         }
     }
+    return BRRR_OK;
+}
+
+extern "C" int brrr_model_set_tile_prefill(brrr_model *m, int on) {
+    if (!m) return BRRR_ERR_ARG;
+    m->tile_prefill = on != 0;
     return BRRR_OK;
 }
 

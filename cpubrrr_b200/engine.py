@@ -63,6 +63,10 @@ class Engine:
         check(lib().brrr_forward(self._h, int(tok), int(pos), int(bool(want)), C.byref(out)), "brrr_forward")
         return int(out.value)
 
+    def set_tile_prefill(self, on):
+        """run_tile on 16-token tiles (True) or one graph launch per token (False, default); same results."""
+        check(lib().brrr_model_set_tile_prefill(self._h, int(bool(on))), "brrr_model_set_tile_prefill")
+
     def run_tile(self, toks, pos0, want=True):
         t = np.ascontiguousarray(toks, dtype=np.uint32)
         out = C.c_uint32(0)

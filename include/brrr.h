@@ -76,6 +76,13 @@ int brrr_forward(brrr_model *m, uint32_t tok, uint32_t pos, int want_logits, uin
  * the reference guarantees for run_tile (src/bin/engine_gpt2.rs:1004-1010, 1387-1393). */
 int brrr_forward_tile(brrr_model *m, const uint32_t *toks, uint32_t n, uint32_t pos0, int want_logits, uint32_t *out_tok);
 
+/* Schedule of brrr_forward_tile.  on = 0 (default): one graph launch per token.  on != 0: tiles of 16
+ * tokens walk the layers together as in forward_tile_worker (src/bin/engine_gpt2.rs:1011-1250, TILE = 16):
+ * q/k/v, attention and the output projection per token, the MoE block once per layer and tile on the
+ * tensor-core tile kernels.  Same bits either way; the environment variable BRRR_TILE_PREFILL=1
+ * sets the initial value.  Ignored by expert-parallel ranks (always token-serial). */
+int brrr_model_set_tile_prefill(brrr_model *m, int on);
+
 /* n greedy decode steps starting from `first_tok` at position `pos`, the token id staying on the
  * device between steps (one graph launch per step, no host round trip); out_toks[i] is the token
  * produced by step i.  Replaces the decode loop of generate (src/bin/engine_gpt2.rs:1431-1438)

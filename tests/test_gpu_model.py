@@ -241,8 +241,8 @@ def test_speculation_can_be_disabled(brrr, orc, monkeypatch):
 
 
 def test_prompt_tiles_match_serial(brrr):
-    """run_tile walks tiles of 16 tokens through the layers together (MoE block on the tensor-core tile
-    kernels); the reference guarantees its batched prefill is bit-identical to the token-serial
+    """With the tile schedule switched on, run_tile walks tiles of 16 tokens through the layers together
+    (MoE block on the tensor-core tile kernels); the reference guarantees its batched prefill is bit-identical to the token-serial
     schedule (src/bin/engine_gpt2.rs:1005-1010).  Checked on the last token's hidden state and logits,
     on the returned token, and on a decode run that reads the KV cache the tiles wrote.  37 tokens =
     two full tiles and a ragged one; a 1-token call takes the serial path."""
@@ -254,6 +254,7 @@ def test_prompt_tiles_match_serial(brrr):
         tok_s = eng.run(t, i, i == len(prompt) - 1)
     h_s, l_s = eng.hidden(), eng.logits()
     dec_s = eng.decode(tok_s, len(prompt), 24)
+    eng.set_tile_prefill(True)
     tok_t = eng.run_tile(prompt, 0, True)
     h_t, l_t = eng.hidden(), eng.logits()
     dec_t = eng.decode(tok_t, len(prompt), 24)
