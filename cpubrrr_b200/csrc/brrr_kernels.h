@@ -11,6 +11,8 @@ void launch_quant_q8(const float *x, int n, int8_t *q, float *s, cudaStream_t st
 cudaError_t launch_rmsnorm_quant(const float *x, const float *w, float eps, int n, float *xn, int8_t *q, float *s, bool pdl, cudaStream_t st);
 void launch_embed(const uint16_t *embd, int d, const DevState *state, float *x, cudaStream_t st);
 void launch_embed_tok(const uint16_t *embd, int d, uint32_t tok, float *x, cudaStream_t st);
+// ntok rows from token ids in device memory: x[t] = embedding of toks[t]
+void launch_embed_tile(const uint16_t *embd, int d, const uint32_t *toks_dev, int ntok, float *x, cudaStream_t st);
 void launch_swiglu_quant(const float *gu, int topk, int d, int8_t *hq, float *hs, cudaStream_t st);
 void launch_finish_token(DevState *state, cudaStream_t st);
 void launch_expf(const float *x, int n, float *y, cudaStream_t st);
@@ -166,6 +168,7 @@ cudaError_t launch_router_hint(const float *x_in, const float *norm_w, float eps
 // else pos_val.  window = 0 means full attention.
 cudaError_t launch_attn_decode(const float *qkv, float *kc, float *vc, const float *rope, const float *sinks, int nh, int nkv,
                                const DevState *state, int pos_val, int window, float *ao, int8_t *aq, float *as,
-                               DevState *err_state, bool pdl, cudaStream_t st);
+                               DevState *err_state, bool pdl, cudaStream_t st, int pos_off = 0);
+// pos_off is added to the position read from state (ignored with pos_val)
 
 }  // namespace brrr

@@ -31,6 +31,7 @@ struct AttnArgs {
     int nh, nkv;
     const DevState *state;
     int pos_val, window;
+    int pos_off;             // added to the device-side position (token t of a prompt tile: t)
     float *ao;
     int8_t *aq;
     float *as;
@@ -54,7 +55,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(AttnArgs a) {
 
     // The position is an input of this step (written before the graph launch or by the previous
     // step's last kernel), never by the immediate predecessor, so it may be read before the wait.
-    const int pos = a.state ? (int)a.state->pos : a.pos_val;
+    const int pos = a.state ? (int)a.state->pos + a.pos_off : a.pos_val;
     const int start = a.window > 0 ? max(pos - (a.window - 1), 0) : 0;
     const int n = pos - start + 1;                  // keys including the current one
     const int ncached = n - 1;                      // keys that come from the cache
@@ -209,8 +210,8 @@ static size_t attn_smem() { return AT_TILE_BYTES * AT_SLOTS * 2 + (size_t)BRRR_M
 
 cudaError_t launch_attn_decode(const float *qkv, float *kc, float *vc, const float *rope, const float *sinks, int nh, int nkv,
                                const DevState *state, int pos_val, int window, float *ao, int8_t *aq, float *as,
-                               DevState *err_state, bool pdl, cudaStream_t st) {
-    AttnArgs a{qkv, kc, vc, rope, sinks, nh, nkv, state, pos_val, window, ao, aq, as, err_state};
+                               DevState *err_state, bool pdl, cudaStream_t st, int pos_off) {
+    AttnArgs a{qkv, kc, vc, rope, sinks, nh, nkv, state, pos_val, window, pos_off, ao, aq, as, err_state};
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_smem());

@@ -64,6 +64,16 @@ void launch_embed_tok(const uint16_t *embd, int d, uint32_t tok, float *x, cudaS
     embed_tok_kernel<<<(d + 255) / 256, 256, 0, st>>>(embd, d, tok, x);
 }
 
+__global__ void embed_tile_kernel(const uint16_t *__restrict__ embd, int d, const uint32_t *__restrict__ toks, float *__restrict__ x) {
+    const size_t tok = toks[blockIdx.y];
+    for (int j = blockIdx.x * blockDim.x + threadIdx.x; j < d; j += gridDim.x * blockDim.x)
+        x[(size_t)blockIdx.y * d + j] = brrr_bf16_to_f32(embd[tok * d + j]);
+}
+
+void launch_embed_tile(const uint16_t *embd, int d, const uint32_t *toks_dev, int ntok, float *x, cudaStream_t st) {
+    embed_tile_kernel<<<dim3((d + 255) / 256, ntok), 256, 0, st>>>(embd, d, toks_dev, x);
+}
+
 void launch_embed(const uint16_t *embd, int d, const DevState *state, float *x, cudaStream_t st) {
     embed_kernel<<<(d + 255) / 256, 256, 0, st>>>(embd, d, state, x);
 }

@@ -150,6 +150,10 @@ struct brrr_model {
     int32_t *tl_top = nullptr;
     int *tl_cnt = nullptr, *tl_list = nullptr;
     float *tl_x = nullptr, *tl_xn = nullptr;     // prompt tiles: residual and normalised residual of up to 16 tokens
+    uint32_t *tl_toks = nullptr;                 // token ids of the tile being replayed
+    uint32_t *h_tile = nullptr;                  // pinned: one 20-word slot per tile of a call
+    cudaGraphExec_t g_tile = nullptr;            // a full 16-token tile without the head
+    bool tile_graph_failed = false;
     bool tile_prefill = false;                   // run_tile on 16-token tiles (brrr_model_set_tile_prefill / BRRR_TILE_PREFILL=1); default: token-serial, which is faster today
     unsigned int *tl_counter = nullptr;
     std::vector<void *> allocs;
@@ -729,6 +733,8 @@ extern "C" void brrr_model_close(brrr_model *m) {
     if (m->ep_buf) cudaFree(m->ep_buf);
     for (void *p : m->allocs) cudaFree(p);
     if (m->h_in) cudaFreeHost(m->h_in);
+    if (m->h_tile) cudaFreeHost(m->h_tile);
+    if (m->g_tile) cudaGraphExecDestroy(m->g_tile);
     if (m->h_out) cudaFreeHost(m->h_out);
     if (m->stream) cudaStreamDestroy(m->stream);
     delete m;
@@ -804,25 +810,32 @@ static int moe_tile_enqueue(brrr_model *m, int il, const float *d_xn, float *d_x
 // attends); the MoE block, where the weight bytes are, runs once per layer for the whole tile on the
 // tensor-core tile kernels (kernels_tile.cu), streaming each routed expert once for all its tokens.
 // Every value is bit-identical to the token-serial schedule.
-static int forward_tile_16(brrr_model *m, const uint32_t *toks, int n, uint32_t pos0, bool want) {
+// graph_mode: the replayable form of a full tile without the head: token ids come from m->tl_toks,
+// the tile's first position from the device state (attention adds the token's offset), and the
+// per-token kernels are chained by programmatic dependent launch.
+static int forward_tile_16(brrr_model *m, const uint32_t *toks, int n, uint32_t pos0, bool want, bool graph_mode) {
     const brrr_cfg &c = m->cfg;
     const int d = c.n_embd, nh = c.n_head, nkv = c.n_head_kv;
     cudaStream_t s = m->stream;
-    if (!m->tl_x) { TRY(m->alloc(&m->tl_x, (size_t)16 * d)); TRY(m->alloc(&m->tl_xn, (size_t)16 * d)); }
-    for (int t = 0; t < n; t++) launch_embed_tok(m->tok_embd, d, toks[t], m->tl_x + (size_t)t * d, s);
+    const bool pdl = graph_mode && m->use_pdl;
+    if (graph_mode) launch_embed_tile(m->tok_embd, d, m->tl_toks, n, m->tl_x, s);
+    else for (int t = 0; t < n; t++) launch_embed_tok(m->tok_embd, d, toks[t], m->tl_x + (size_t)t * d, s);
     for (int il = 0; il < c.n_layer; il++) {
         Layer &ly = m->L[il];
         int window = ((il + 1) % 2 != 0) ? c.sliding_window : 0;
         if (window >= BRRR_MAXSEQ) window = 0;
         for (int t = 0; t < n; t++) {
             float *x = m->tl_x + (size_t)t * d;
-            CUL(launch_q8_stream(ly.wqkv, x, ly.attn_norm, c.rms_eps, nullptr, nullptr, ly.bqkv, m->qkv, Q8_EPI_BIAS, m->st, false, s));
-            CUL(launch_attn_decode(m->qkv, ly.kc, ly.vc, m->rope, ly.sinks, nh, nkv, nullptr, (int)pos0 + t, window, m->ao, m->aq, m->as, m->st, false, s));
-            CUL(launch_q8_stream(ly.wo, nullptr, nullptr, 0.0f, m->aq, m->as, ly.bo, x, Q8_EPI_RESID_BIAS, m->st, false, s));
-            CUL(launch_rmsnorm_quant(x, ly.ffn_norm, c.rms_eps, d, m->tl_xn + (size_t)t * d, m->xq, m->xs, false, s));
+            // the first kernel after a plain launch takes the full dependency
+            CUL(launch_q8_stream(ly.wqkv, x, ly.attn_norm, c.rms_eps, nullptr, nullptr, ly.bqkv, m->qkv, Q8_EPI_BIAS, m->st, pdl && t > 0, s));
+            CUL(launch_attn_decode(m->qkv, ly.kc, ly.vc, m->rope, ly.sinks, nh, nkv, graph_mode ? m->st : nullptr, (int)pos0 + t, window, m->ao, m->aq, m->as,
+                                   m->st, pdl, s, t));
+            CUL(launch_q8_stream(ly.wo, nullptr, nullptr, 0.0f, m->aq, m->as, ly.bo, x, Q8_EPI_RESID_BIAS, m->st, pdl, s));
+            CUL(launch_rmsnorm_quant(x, ly.ffn_norm, c.rms_eps, d, m->tl_xn + (size_t)t * d, m->xq, m->xs, pdl, s));
         }
         TRY(moe_tile_enqueue(m, il, m->tl_xn, m->tl_x, n));
     }
+    if (graph_mode) return BRRR_OK;
     // leave the engine as the serial schedule would after the tile's last token
     CU(cudaMemcpyAsync(m->x, m->tl_x + (size_t)(n - 1) * d, (size_t)d * sizeof(float), cudaMemcpyDeviceToDevice, s));
     m->h_in[0] = toks[n - 1]; m->h_in[1] = pos0 + (uint32_t)n - 1;
@@ -842,9 +855,14 @@ extern "C" int brrr_forward_tile(brrr_model *m, const uint32_t *toks, uint32_t n
     for (uint32_t i = 0; i < n; i++) if (toks[i] >= (uint32_t)m->cfg.n_vocab) return BRRR_ERR_RANGE;
     CU(cudaSetDevice(m->device));
     // Both schedules give the same bits.  The tile schedule amortises only the MoE block so far (the
-    // dense projections still run per token, without the decode step's graph), and measures slower
-    // than the graph-per-token schedule; it is therefore opt-in.  Expert-parallel ranks stay serial.
+    // dense projections still run per token); it is opt-in.  Expert-parallel ranks stay serial.
     const bool serial = m->ep || !m->tile_prefill;
+    const int d = m->cfg.n_embd;
+    if (!serial && !m->tl_x) {
+        TRY(m->alloc(&m->tl_x, (size_t)16 * d)); TRY(m->alloc(&m->tl_xn, (size_t)16 * d)); TRY(m->alloc(&m->tl_toks, 16));
+        CU(cudaMallocHost(&m->h_tile, (size_t)(BRRR_MAXSEQ / 16) * 20 * sizeof(uint32_t)));
+    }
+    bool tiled_last = false;
     for (uint32_t i0 = 0; i0 < n; i0 += 16) {
         const uint32_t cnt = n - i0 < 16 ? n - i0 : 16;
         const bool last = i0 + cnt == n;
@@ -855,13 +873,40 @@ extern "C" int brrr_forward_tile(brrr_model *m, const uint32_t *toks, uint32_t n
             }
             continue;
         }
-        TRY(forward_tile_16(m, toks + i0, (int)cnt, pos0 + i0, want && last));
-        if (last) {
-            CU(cudaMemcpyAsync(m->h_out, m->st, 32, cudaMemcpyDeviceToHost, m->stream));   // tok .. err
-            CU(cudaStreamSynchronize(m->stream));
-            if (m->h_out[6] != 0) { snprintf(g_cuda_err, sizeof g_cuda_err, "device wait timed out (code %u)", m->h_out[6]); return BRRR_ERR_STATE; }
-            if (want && out_tok) *out_tok = m->h_out[0];
+        if (cnt == 16 && !(want && last) && m->g_tile) {
+            // a full tile without the head: replay the captured tile step.  Host words of the tile
+            // (16 token ids; state before = {-, pos0}; state after = {last token, last position}) sit in
+            // their own pinned slot, so nothing is overwritten before the stream has read it.
+            uint32_t *h = m->h_tile + (size_t)(i0 / 16) * 20;
+            for (int t = 0; t < 16; t++) h[t] = toks[i0 + t];
+            h[16] = toks[i0]; h[17] = pos0 + i0; h[18] = toks[i0 + 15]; h[19] = pos0 + i0 + 15;
+            CU(cudaMemcpyAsync(m->tl_toks, h, 64, cudaMemcpyHostToDevice, m->stream));
+            CU(cudaMemcpyAsync(m->st, h + 16, 8, cudaMemcpyHostToDevice, m->stream));
+            CU(cudaGraphLaunch(m->g_tile, m->stream));
+            CU(cudaMemcpyAsync(m->x, m->tl_x + (size_t)15 * d, (size_t)d * sizeof(float), cudaMemcpyDeviceToDevice, m->stream));
+            CU(cudaMemcpyAsync(m->st, h + 18, 8, cudaMemcpyHostToDevice, m->stream));
+        } else {
+            TRY(forward_tile_16(m, toks + i0, (int)cnt, pos0 + i0, want && last, false));
+            if (cnt == 16 && !m->g_tile && !m->tile_graph_failed) {
+                // every kernel of the tile step has now run once directly (attributes set, scratch
+                // allocated): capture the replayable form for the tiles that follow
+                CU(cudaStreamSynchronize(m->stream));
+                cudaGraph_t g = nullptr;
+                CU(cudaStreamBeginCapture(m->stream, cudaStreamCaptureModeThreadLocal));
+                int st = forward_tile_16(m, nullptr, 16, 0, false, true);
+                cudaError_t e = cudaStreamEndCapture(m->stream, &g);
+                if (st == BRRR_OK && e == cudaSuccess && cudaGraphInstantiate(&m->g_tile, g, 0) == cudaSuccess) { }
+                else { m->g_tile = nullptr; m->tile_graph_failed = true; (void)cudaGetLastError(); }
+                if (g) cudaGraphDestroy(g);
+            }
         }
+        tiled_last = last;
+    }
+    if (tiled_last) {
+        CU(cudaMemcpyAsync(m->h_out, m->st, 32, cudaMemcpyDeviceToHost, m->stream));   // tok .. err
+        CU(cudaStreamSynchronize(m->stream));
+        if (m->h_out[6] != 0) { snprintf(g_cuda_err, sizeof g_cuda_err, "device wait timed out (code %u)", m->h_out[6]); return BRRR_ERR_STATE; }
+        if (want && out_tok) *out_tok = m->h_out[0];
     }
     return BRRR_OK;
 }
