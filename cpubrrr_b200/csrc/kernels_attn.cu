@@ -38,6 +38,11 @@ struct AttnArgs {
     DevState *err_state;
 };
 
+#ifndef AT_SCORE_UNROLL
+#define AT_SCORE_UNROLL 8
+#endif
+constexpr int kScoreUnroll = AT_SCORE_UNROLL;      // keys of the score loop in flight per thread group (their shuffle chains overlap)
+
 __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(AttnArgs a) {
     extern __shared__ __align__(128) unsigned char smraw[];
     float *ktiles = reinterpret_cast<float *>(smraw);                                   // [AT_SLOTS][128][64]
@@ -118,7 +123,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(AttnArgs a) {
             const int slot = t % AT_SLOTS, cnt = min(AT_TILE, ncached - t * AT_TILE);
             waiter.wait(&kbar[slot], (uint32_t)(t / AT_SLOTS) & 1u);
             const float *kt = ktiles + (size_t)slot * AT_TILE * HD;
-#pragma unroll 2
+#pragma unroll kScoreUnroll
             for (int k0 = 0; k0 < cnt; k0 += AT_THREADS / 16) {
                 int kk = k0 + g;
                 bool live = kk < cnt;
