@@ -87,6 +87,7 @@ SIGNATURES = {
     "brrr_q4k_matvec": (_I, [_P, _I, _I, _P, _P, _P, _P, _P, _P]),
     "brrr_q6k_matvec": (_I, [_P, _I, _I, _P, _P, _P, _P, _P]),
     "brrr_rmsnorm_quant": (_I, [_P, _P, C.c_float, _I, _P, _P, _P, _P]),
+    "brrr_fold_norm": (_I, [_P, _P, _I, _I, _P, _P, _P, _P, C.c_float, _P, _P, _I, _P]),
     "brrr_q8mat_from_bf16": (_I, [_P, _I, _I, C.POINTER(_P), _P]),
     "brrr_q8mat_export": (_I, [_P, _P, _P, _P]),
     "brrr_q8mat_free": (None, [_P]),

@@ -153,3 +153,28 @@ extern "C" int brrr_expf(const float *d_x, int n, float *d_y, void *stream) {
     launch_expf(d_x, n, d_y, (cudaStream_t)stream);
     return check_launch();
 }
+
+// The last kernel of a layer in the default decode step, as a stage: fold of the down-projection
+// partial sums with the exact routing, then RMS norm + Q8 of the new residual.
+extern "C" int brrr_fold_norm(const int32_t *d_top, const float *d_wts, int topk, int d, const float *d_part, const float *d_down_b, float *d_x,
+                              const float *d_norm_w, float eps, int8_t *d_q, float *d_s, int wait_for_router, void *stream) {
+    if (!d_top || !d_wts || !d_part || !d_down_b || !d_x || topk <= 0 || topk > 8 || d <= 0 || d % 32 || d > 4096) return BRRR_ERR_ARG;
+    if (d_norm_w && (!d_q || !d_s)) return BRRR_ERR_ARG;
+    cudaStream_t st = (cudaStream_t)stream;
+    // a private device state: the kernel reports a wait that ran out through its error word
+    DevState *state = nullptr;
+    if (cudaMalloc(&state, sizeof(DevState)) != cudaSuccess) return BRRR_ERR_NOMEM;
+    int rc = BRRR_OK;
+    if (cudaMemsetAsync(state, 0, sizeof(DevState), st) != cudaSuccess) rc = BRRR_ERR_CUDA;
+    // wait_for_router: the kernel polls for routing words tagged 1; nobody publishes them here
+    if (rc == BRRR_OK &&
+        launch_fold_norm(d_top, d_wts, nullptr, 0, topk, 0, d, d_part, d_down_b, d_x, d_norm_w, eps, d_q, d_s, wait_for_router ? &state->router_seq : nullptr,
+                         wait_for_router ? &state->fold_seq : nullptr, state, false, st) != cudaSuccess)
+        rc = BRRR_ERR_CUDA;
+    uint32_t err = 0;
+    if (rc == BRRR_OK && cudaMemcpyAsync(&err, &state->err, sizeof err, cudaMemcpyDeviceToHost, st) != cudaSuccess) rc = BRRR_ERR_CUDA;
+    if (rc == BRRR_OK && cudaStreamSynchronize(st) != cudaSuccess) rc = BRRR_ERR_CUDA;
+    cudaFree(state);
+    if (rc == BRRR_OK && err != 0) rc = BRRR_ERR_STATE;
+    return rc == BRRR_OK ? check_launch() : rc;
+}

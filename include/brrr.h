@@ -264,6 +264,17 @@ int brrr_q6k_matvec(const uint8_t *d_w, int rows, int cols, const int8_t *d_xq, 
  * Replaces ssq + rmsnorm_quant_par (src/bin/engine_gpt2.rs:709-738). */
 int brrr_rmsnorm_quant(const float *d_x, const float *d_w, float eps, int n, float *d_xn, int8_t *d_q, float *d_s, void *stream);
 
+/* x[r] += sum over k ascending of wts[k] * (part[k][r] + down_b[top[k]][r]) (multiply, then add), then
+ * brrr_rmsnorm_quant of the new x with d_norm_w (nullable: fold only) into d_q / d_s: the combine of
+ * src/bin/engine_gpt2.rs:908-923 together with the norm + quantiser that opens the next layer
+ * (709-738), as the decode step's last kernel of a layer runs them.  d_part: [topk][ceil(d / 128) * 128]
+ * row sums of the down projection before bias, 16-byte aligned like d_x and d_down_b ([experts][d]).
+ * wait_for_router != 0: the kernel first polls (bounded, about a second) for routing words that the
+ * router of the decode step would publish; this call publishes none, so the wait runs out and the call
+ * returns BRRR_ERR_STATE with the CUDA context intact (the test of that bounded wait).  Synchronous. */
+int brrr_fold_norm(const int32_t *d_top, const float *d_wts, int topk, int d, const float *d_part, const float *d_down_b, float *d_x,
+                   const float *d_norm_w, float eps, int8_t *d_q, float *d_s, int wait_for_router, void *stream);
+
 /* Opaque device matrices in the engine's streaming layouts. */
 typedef struct brrr_q8mat brrr_q8mat;
 typedef struct brrr_mxmat brrr_mxmat;

@@ -230,3 +230,54 @@ def test_synth_device_equals_numpy(L, dev, kind, type_, n):
     else:
         want = S.synth_mxfp4(5, 3, S.T[kind], n // 32)
     assert np.array_equal(got, want)
+
+
+def _fold_case(dev, d, topk, ne, seed):
+    import torch
+    rng = np.random.default_rng(seed)
+    dpad = (d + 127) // 128 * 128
+    x = rng.standard_normal(d).astype(np.float32) * np.float32(3.0)
+    part = rng.standard_normal((topk, dpad)).astype(np.float32)
+    bias = (rng.standard_normal((ne, d)) * 0.02).astype(np.float32)
+    top = rng.permutation(ne)[:topk].astype(np.int32)
+    wts = rng.random(topk).astype(np.float32)
+    wts /= wts.sum(dtype=np.float32)
+    w = (1.0 + 0.02 * rng.standard_normal(d)).astype(np.float32)
+    want = x.copy()
+    for k in range(topk):                       # multiply, then add, slot by slot (float32 at every step)
+        want = want + wts[k] * (part[k, :d] + bias[top[k]])
+    dv = dict(x=to_dev(x, dev), part=to_dev(part, dev), bias=to_dev(bias, dev), top=to_dev(top, dev), wts=to_dev(wts, dev), w=to_dev(w, dev),
+              q=torch.empty(d, dtype=torch.int8, device=dev), s=torch.empty(d // 32, dtype=torch.float32, device=dev))
+    return dv, want.astype(np.float32), w
+
+
+@pytest.mark.parametrize("d,topk,ne", [(2880, 4, 32), (128, 4, 8), (2048, 8, 128), (4096, 2, 4)])
+def test_fold_norm_stage(L, orc, dev, d, topk, ne):
+    """The decode step's last kernel of a layer (fold with the exact routing, next RMS norm, Q8 image)
+    against a float32 numpy fold followed by the oracle's norm and quantiser; also without the norm."""
+    dv, want, w = _fold_case(dev, d, topk, ne, 5)
+    ok(L.brrr_fold_norm(P(dv["top"]), P(dv["wts"]), topk, d, P(dv["part"]), P(dv["bias"]), P(dv["x"]), P(dv["w"]), C.c_float(1e-5),
+                        P(dv["q"]), P(dv["s"]), 0, None))
+    assert np.array_equal(bits(dv["x"].cpu().numpy()), bits(want))
+    q, s = orc.quant_q8(orc.rmsnorm(want, w, 1e-5))
+    assert np.array_equal(dv["q"].cpu().numpy(), q) and np.array_equal(bits(dv["s"].cpu().numpy()), bits(s))
+    dv2, want2, _ = _fold_case(dev, d, topk, ne, 6)
+    ok(L.brrr_fold_norm(P(dv2["top"]), P(dv2["wts"]), topk, d, P(dv2["part"]), P(dv2["bias"]), P(dv2["x"]), None, C.c_float(0.0), None, None, 0, None))
+    assert np.array_equal(bits(dv2["x"].cpu().numpy()), bits(want2))
+
+
+def test_fold_wait_runs_out_and_reports(L, dev):
+    """The fold of the decode step waits for the router's routing words with a limit.  Here nothing
+    publishes them: the kernel gives up after about a second, records the failure in its state word and
+    returns; the call reports BRRR_ERR_STATE, and the context keeps working (the next call passes)."""
+    import time
+    dv, want, _ = _fold_case(dev, 256, 4, 8, 7)
+    t0 = time.time()
+    st = L.brrr_fold_norm(P(dv["top"]), P(dv["wts"]), 4, 256, P(dv["part"]), P(dv["bias"]), P(dv["x"]), P(dv["w"]), C.c_float(1e-5),
+                          P(dv["q"]), P(dv["s"]), 1, None)
+    assert st == 6, st          # BRRR_ERR_STATE
+    assert time.time() - t0 < 30
+    dv, want, _ = _fold_case(dev, 256, 4, 8, 8)
+    ok(L.brrr_fold_norm(P(dv["top"]), P(dv["wts"]), 4, 256, P(dv["part"]), P(dv["bias"]), P(dv["x"]), P(dv["w"]), C.c_float(1e-5),
+                        P(dv["q"]), P(dv["s"]), 0, None))
+    assert np.array_equal(bits(dv["x"].cpu().numpy()), bits(want))
