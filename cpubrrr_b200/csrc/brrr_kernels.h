@@ -10,9 +10,6 @@ namespace brrr {
 void launch_quant_q8(const float *x, int n, int8_t *q, float *s, cudaStream_t st);
 cudaError_t launch_rmsnorm_quant(const float *x, const float *w, float eps, int n, float *xn, int8_t *q, float *s, bool pdl, cudaStream_t st);
 void launch_embed(const uint16_t *embd, int d, const DevState *state, float *x, cudaStream_t st);
-// embedding row + RMSNorm(norm_w) + Q8 image (nq natural int8 order, ns block scales) in one CTA; d <= 4096
-cudaError_t launch_embed_norm(const uint16_t *embd, int d, const DevState *state, float *x, const float *norm_w, float eps, int8_t *nq, float *ns,
-                              cudaStream_t st);
 void launch_embed_tok(const uint16_t *embd, int d, uint32_t tok, float *x, cudaStream_t st);
 // ntok rows from token ids in device memory: x[t] = embedding of toks[t]
 void launch_embed_tile(const uint16_t *embd, int d, const uint32_t *toks_dev, int ntok, float *x, cudaStream_t st);

@@ -54,35 +54,6 @@ __global__ void embed_kernel(const uint16_t *__restrict__ embd, int d, const Dev
         x[j] = brrr_bf16_to_f32(embd[tok * d + j]);
 }
 
-// Embedding row of the step's token, then the first layer's RMS norm and Q8 image in the same CTA
-// (the whole vector is there): the first q/k/v projection then stages the ready image like the others.
-__global__ void __launch_bounds__(1024) embed_norm_kernel(const uint16_t *__restrict__ embd, int d, const DevState *__restrict__ state,
-                                                          float *__restrict__ x, const float *__restrict__ norm_w, float eps,
-                                                          int8_t *__restrict__ nq, float *__restrict__ ns) {
-    extern __shared__ __align__(16) float esm[];      // d floats
-    __shared__ float inv_sh;
-    const int tid = threadIdx.x;
-    float4 wreg[1];
-    norm_prefetch<1>(norm_w, d, wreg, tid, 1024);
-    const size_t tok = state->tok;
-    if (tid < (d >> 2)) {
-        const uint2 raw = reinterpret_cast<const uint2 *>(embd + tok * d)[tid];
-        const float4 v = make_float4(brrr_bf16_to_f32((uint16_t)(raw.x & 0xffffu)), brrr_bf16_to_f32((uint16_t)(raw.x >> 16)),
-                                     brrr_bf16_to_f32((uint16_t)(raw.y & 0xffffu)), brrr_bf16_to_f32((uint16_t)(raw.y >> 16)));
-        reinterpret_cast<float4 *>(x)[tid] = v;
-        reinterpret_cast<float4 *>(esm)[tid] = v;
-    }
-    __syncthreads();
-    block_norm_quant_staged<NQ_NATURAL, 1>(norm_w, wreg, eps, d, esm, reinterpret_cast<int2 *>(nq), ns, &inv_sh, tid, 1024);
-}
-
-cudaError_t launch_embed_norm(const uint16_t *embd, int d, const DevState *state, float *x, const float *norm_w, float eps, int8_t *nq, float *ns,
-                              cudaStream_t st) {
-    if (d > 4096 || d % 32) return cudaErrorInvalidValue;
-    embed_norm_kernel<<<1, 1024, (size_t)d * sizeof(float), st>>>(embd, d, state, x, norm_w, eps, nq, ns);
-    return cudaGetLastError();
-}
-
 // the same for a token id given by the host (token tiles)
 __global__ void embed_tok_kernel(const uint16_t *__restrict__ embd, int d, uint32_t tok, float *__restrict__ x) {
     for (int j = blockIdx.x * blockDim.x + threadIdx.x; j < d; j += gridDim.x * blockDim.x)

@@ -291,16 +291,14 @@ int enqueue_step(brrr_model *m, bool want, float *trace_dev, int *nlaunch, unsig
     int n = 0;
     auto on = [&](int st) { if (mask & (1u << st)) { n++; return true; } return false; };
     if (m->ep) { launch_ep_begin(m->epc, m->st, s); n++; }
-    const bool fused_step = spec && m->use_mxt && m->fused_fold;
-    if (fused_step) { n++; CUL(launch_embed_norm(m->tok_embd, d, m->st, m->x, m->L[0].attn_norm, c.rms_eps, m->nq, m->ns, s)); }
-    else if (on(ST_EMBED)) launch_embed(m->tok_embd, d, m->st, m->x, s);
+    if (on(ST_EMBED)) launch_embed(m->tok_embd, d, m->st, m->x, s);
     if (trace_dev) CU(cudaMemcpyAsync(trace_dev, m->x, d * sizeof(float), cudaMemcpyDeviceToDevice, s));
     for (int il = 0; il < c.n_layer; il++) {
         Layer &ly = m->L[il];
-        // fused: the previous layer's fold (layer 0: the embedding kernel) has left the normalised, quantised residual in nq / ns
+        // fused: the previous layer's fold has left the normalised, quantised residual in nq / ns
         const bool fused = spec && m->use_mxt && m->fused_fold;
-        if (fused) { n++; CUL(launch_q8_stream(ly.wqkv, nullptr, nullptr, 0.0f, m->nq, m->ns, ly.bqkv, m->qkv, Q8_EPI_BIAS, m->st, pdl, s)); }
-        else if (mask != ~0u && m->use_mxt && m->use_spec && m->fused_fold) {      // stage replay of the fused step's q/k/v (image left by the last step)
+        if (fused && il > 0) { n++; CUL(launch_q8_stream(ly.wqkv, nullptr, nullptr, 0.0f, m->nq, m->ns, ly.bqkv, m->qkv, Q8_EPI_BIAS, m->st, pdl, s)); }
+        else if (mask != ~0u && m->use_mxt && m->use_spec && m->fused_fold && il > 0) {      // stage replay of the fused step's q/k/v (image left by the last step)
             if (on(ST_QKV)) CUL(launch_q8_stream(ly.wqkv, nullptr, nullptr, 0.0f, m->nq, m->ns, ly.bqkv, m->qkv, Q8_EPI_BIAS, m->st, pdl, s));
         } else if (on(ST_QKV)) CUL(launch_q8_stream(ly.wqkv, m->x, ly.attn_norm, c.rms_eps, nullptr, nullptr, ly.bqkv, m->qkv, Q8_EPI_BIAS, m->st, pdl && n > 1, s));
         int window = ((il + 1) % 2 != 0) ? c.sliding_window : 0;         // even layer index: sliding window
