@@ -1,13 +1,11 @@
 """numpy port of the counter-based synthetic tensor generator (csrc/brrr_synth.h) and a writer
-that lays a synthetic model out as the reference's data directory: a GGUF blob plus
-config.txt / manifest.txt / tokens.bin in the formats scripts/setup_model.sh,
-scripts/gguf_index.py and scripts/dump_tokenizer.py of the reference emit.
+of GGUF blobs holding a synthetic model whose bytes equal what brrr_model_open_synth generates
+on the device for the same seed.
 
-Used to exercise the file-loading path (brrr_model_open) with models whose bytes equal what
-brrr_model_open_synth generates on the device for the same seed.
+The data directory around a blob (config.txt, manifest.txt, tokens.bin) is the job of the
+reference's own preparation scripts (scripts/setup_model.sh, gguf_index.py, dump_tokenizer.py);
+this module writes none of it except tokens.bin for the toy vocabulary it defines itself.
 """
-import json
-import os
 import struct
 
 import numpy as np
@@ -163,14 +161,17 @@ def model_tensors(cfg, seed):
 GGML_Q4_K, GGML_Q6_K = 12, 14
 
 
-def qwen_model_tensors(cfg, seed):
+def qwen_model_tensors(cfg, seed, ktypes=None):
     """(name, ggml type, dims, raw bytes) of a synthetic qwen3moe model, in the tensor names the
     reference's loader looks up (src/bin/engine_qwen2.rs:528-541).  Down experts and the output head
-    are Q6_K, every other matrix Q4_K."""
+    are Q6_K, every other matrix Q4_K; `ktypes` maps tensor names to another K-quant type (files
+    in the wild mix the two per tensor, e.g. attn_v stored as Q6_K)."""
+    ktypes = ktypes or {}
     d, nh, nkv, hd, ne, ff, nv = cfg.n_embd, cfg.n_head, cfg.n_head_kv, cfg.head_dim, cfg.n_expert, cfg.n_ff_exp, cfg.n_vocab
 
     def k(name, layer, kind, rows, cols, dims):
-        if kind in ("DOWN", "OUTPUT"):
+        ty = ktypes.get(name, GGML_Q6_K if kind in ("DOWN", "OUTPUT") else GGML_Q4_K)
+        if ty == GGML_Q6_K:
             return (name, GGML_Q6_K, dims, synth_q6k_blocks(seed, layer, T[kind], rows * cols // 256).tobytes())
         return (name, GGML_Q4_K, dims, synth_q4k_blocks(seed, layer, T[kind], rows * cols // 256).tobytes())
 
@@ -198,7 +199,7 @@ def _gguf_str(s):
     return struct.pack("<Q", len(b)) + b
 
 
-def write_gguf(path, cfg, seed, tokens=None, arch="gpt-oss"):
+def write_gguf(path, cfg, seed, tokens=None, arch="gpt-oss", ktypes=None):
     """Write a GGUF v3 file by hand (little-endian, alignment 32): header, metadata key/values
     (the hyper-parameters setup_model.sh looks up, and the token list), tensor infos, data."""
     kv = []
@@ -228,7 +229,7 @@ def write_gguf(path, cfg, seed, tokens=None, arch="gpt-oss"):
     arr = struct.pack("<IQ", 8, len(tokens)) + b"".join(_gguf_str(t) for t in tokens)
     kv.append(_gguf_str("tokenizer.ggml.tokens") + struct.pack("<I", 9) + arr)
 
-    tensors = list(qwen_model_tensors(cfg, seed) if arch == "qwen3moe" else model_tensors(cfg, seed))
+    tensors = list(qwen_model_tensors(cfg, seed, ktypes) if arch == "qwen3moe" else model_tensors(cfg, seed))
     infos, off = [], 0
     for name, ty, dims, raw in tensors:
         infos.append(_gguf_str(name) + struct.pack("<I", len(dims)) + struct.pack(f"<{len(dims)}Q", *dims) + struct.pack("<IQ", ty, off))
@@ -242,155 +243,49 @@ def write_gguf(path, cfg, seed, tokens=None, arch="gpt-oss"):
             f.write(b"\0" * ((len(raw) + 31) // 32 * 32 - len(raw)))
 
 
-def default_tokens(n_vocab):
-    """Byte-level toy vocabulary: 256 single bytes (GPT-2 byte-to-unicode spelling), then short
-    words; special tokens spelled with '<|' so the engine's lookup skips them."""
-    bs = list(range(33, 127)) + list(range(161, 173)) + list(range(174, 256))
-    cs = bs[:]
-    n = 0
+def _byte_spelling():
+    """GPT-2's byte-level spelling used by GGUF token lists: printable Latin-1 bytes stand for
+    themselves, the other 68 byte values are written as U+0100, U+0101, ... in ascending byte order."""
+    keep = set(range(0x21, 0x7F)) | set(range(0xA1, 0xAD)) | set(range(0xAE, 0x100))
+    table, extra = [], 0
     for b in range(256):
-        if b not in bs:
-            bs.append(b); cs.append(256 + n); n += 1
-    b2u = dict(zip(bs, [chr(c) for c in cs]))
-    toks = [b2u[b].encode("utf-8") for b in range(256)]
+        if b in keep:
+            table.append(chr(b))
+        else:
+            table.append(chr(0x100 + extra))
+            extra += 1
+    return table
+
+
+def raw_tokens(n_vocab):
+    """Toy vocabulary as the raw byte strings tokens.bin holds: the 256 single bytes, then short
+    words "w0", "w1", ...; the last four entries are special tokens (spelled with '<|', which the
+    engine's lookup skips)."""
+    toks = [bytes([b]) for b in range(256)]
     i = 0
     while len(toks) < n_vocab - 4:
-        toks.append(("".join(b2u[ord(ch)] for ch in f"w{i}")).encode("utf-8"))
+        toks.append(f"w{i}".encode())
         i += 1
-    for s in ("<|start|>", "<|end|>", "<|message|>", "<|return|>"):
+    for s in (b"<|start|>", b"<|end|>", b"<|message|>", b"<|return|>"):
         if len(toks) < n_vocab:
-            toks.append(s.encode())
+            toks.append(s)
     return toks[:n_vocab]
 
 
-# ---- index / manifest / config / tokenizer dump: the behaviour of the reference's
-# scripts/gguf_index.py, scripts/dump_tokenizer.py and the inline generator of
-# scripts/setup_model.sh:41-93, restated.
-def _rd_str(f):
-    (n,) = struct.unpack("<Q", f.read(8))
-    return f.read(n)
+def default_tokens(n_vocab):
+    """The toy vocabulary in its GGUF spelling (UTF-8 of the byte-level characters; special tokens
+    literal)."""
+    sp = _byte_spelling()
+    return [t if t.startswith(b"<|") else "".join(sp[b] for b in t).encode("utf-8") for t in raw_tokens(n_vocab)]
 
 
-_SCALAR = {0: "<B", 1: "<b", 2: "<H", 3: "<h", 4: "<I", 5: "<i", 6: "<f", 7: "<?", 10: "<Q", 11: "<q", 12: "<d"}
-
-
-def _rd_val(f, t):
-    if t in _SCALAR:
-        return struct.unpack(_SCALAR[t], f.read(struct.calcsize(_SCALAR[t])))[0]
-    if t == 8:
-        return _rd_str(f)
-    if t == 9:
-        (et,) = struct.unpack("<I", f.read(4))
-        (n,) = struct.unpack("<Q", f.read(8))
-        return [_rd_val(f, et) for _ in range(n)]
-    raise ValueError(f"bad kv type {t}")
-
-
-def gguf_index(path):
-    with open(path, "rb") as f:
-        assert f.read(4) == b"GGUF"
-        (ver,) = struct.unpack("<I", f.read(4))
-        n_tensors, n_kv = struct.unpack("<QQ", f.read(16))
-        meta, tokens = {}, None
-        for _ in range(n_kv):
-            k = _rd_str(f).decode()
-            (t,) = struct.unpack("<I", f.read(4))
-            v = _rd_val(f, t)
-            if k == "tokenizer.ggml.tokens":
-                tokens = v
-            if isinstance(v, bytes):
-                v = v.decode("utf-8", "replace")
-            if not isinstance(v, list):
-                meta[k] = v
-        infos = []
-        for _ in range(n_tensors):
-            name = _rd_str(f).decode()
-            (nd,) = struct.unpack("<I", f.read(4))
-            dims = struct.unpack(f"<{nd}Q", f.read(8 * nd))
-            ttype, off = struct.unpack("<IQ", f.read(12))
-            infos.append({"name": name, "dims": list(dims), "type": ttype, "offset": off})
-        align = meta.get("general.alignment", 32)
-        data_start = (f.tell() + align - 1) // align * align
-    return {"version": ver, "data_start": data_start, "meta": meta, "tensors": infos, "tokens": tokens}
-
-
-def _bytes_to_unicode():
-    bs = list(range(33, 127)) + list(range(161, 173)) + list(range(174, 256))
-    cs = bs[:]
-    n = 0
-    for b in range(256):
-        if b not in bs:
-            bs.append(b); cs.append(256 + n); n += 1
-    return dict(zip([chr(c) for c in cs], bs))
-
-
-def write_data_dir(out_dir, blob_path):
-    """Emit config.txt, manifest.txt, tokens.bin, blob_path.txt for a GGUF blob."""
-    os.makedirs(out_dir, exist_ok=True)
-    d = gguf_index(blob_path)
-    m = d["meta"]
-    with open(os.path.join(out_dir, "manifest.txt"), "w") as w:
-        w.write(f"data_start {d['data_start']}\n")
-        for t in d["tensors"]:
-            n = 1
-            for x in t["dims"]:
-                n *= x
-            w.write(f"{t['name']} {t['type']} {t['offset']} {n}\n")
-    arch = m.get("general.architecture", "?")
-
-    def g(*suffixes):
-        for k, v in m.items():
-            for s in suffixes:
-                if k == f"{arch}.{s}" or k.endswith("." + s):
-                    return v
-        return None
-
-    n_vocab = g("vocab_size")
-    if n_vocab is None:
-        for t in d["tensors"]:
-            if t["name"] in ("token_embd.weight", "output.weight"):
-                n_vocab = max(t["dims"]); break
-    n_ff_exp = g("expert_feed_forward_length")
-    if n_ff_exp is None:
-        for t in d["tensors"]:
-            if t["name"].endswith("ffn_gate_exps.weight"):
-                n_ff_exp = t["dims"][1]; break
-    cfg = {"arch": arch, "n_embd": g("embedding_length"), "n_layer": g("block_count"), "n_head": g("attention.head_count"),
-           "n_head_kv": g("attention.head_count_kv"), "head_dim": g("attention.key_length"), "n_expert": g("expert_count"),
-           "n_expert_used": g("expert_used_count"), "n_ff_exp": n_ff_exp, "sliding_window": g("attention.sliding_window"),
-           "rope_freq_base": g("rope.freq_base"), "rms_eps": g("attention.layer_norm_rms_epsilon"), "n_vocab": n_vocab,
-           "context_length": g("context_length")}
-    with open(os.path.join(out_dir, "config.txt"), "w") as w:
-        for k, v in cfg.items():
-            if v is not None:
-                w.write(f"{k} {v}\n")
-    u2b = _bytes_to_unicode()
-    with open(os.path.join(out_dir, "tokens.bin"), "wb") as w:
-        toks = d["tokens"] or []
-        w.write(struct.pack("<I", len(toks)))
-        for s in toks:
-            try:
-                t = s.decode("utf-8")
-                b = bytes(u2b[ch] for ch in t) if all(ch in u2b for ch in t) else s
-            except UnicodeDecodeError:
-                b = s
-            w.write(struct.pack("<H", len(b)))
-            w.write(b)
-    with open(os.path.join(out_dir, "blob_path.txt"), "w") as w:
-        w.write(str(blob_path) + "\n")
-    with open(os.path.join(out_dir, "index.json"), "w") as w:
-        json.dump({"version": d["version"], "data_start": d["data_start"],
-                   "meta": {k: v for k, v in m.items() if isinstance(v, (int, float, str))}, "tensors": d["tensors"]}, w, indent=1)
-    return cfg
-
-
-def write_synth_model(out_dir, cfg, seed, arch="gpt-oss"):
-    """GGUF blob + data directory for a synthetic model; returns (data_dir, blob_path)."""
-    os.makedirs(out_dir, exist_ok=True)
-    blob = os.path.join(out_dir, "model.gguf")
-    write_gguf(blob, cfg, seed, arch=arch)
-    write_data_dir(out_dir, blob)
-    return out_dir, blob
+def write_tokens_bin(path, toks):
+    """tokens.bin as the engine reads it (src/bin/engine_gpt2.rs:1260-1266): u32 count, then per
+    token a u16 length and the raw bytes."""
+    with open(path, "wb") as f:
+        f.write(struct.pack("<I", len(toks)))
+        for t in toks:
+            f.write(struct.pack("<H", len(t)) + t)
 
 
 # ---- K-quant test tensors (qwen3moe path) ------------------------------------------------------

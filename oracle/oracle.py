@@ -22,14 +22,15 @@ def build(force=False):
 
 
 _REF_SO = os.path.join(_HERE, "_ref", "libref_kq.so")
-_REF_SRC = "/root/reference/metal/engine_metal.m"
+_REF_DIR = os.environ.get("BRRR_REFERENCE_DIR", "/root/reference")
+_REF_SRC = os.path.join(_REF_DIR, "metal", "engine_metal.m")
 
 
 def build_ref():
     """Build oracle/_ref/libref_kq.so (the reference's own scalar C Q4_K/Q6_K dots) when the reference
     checkout is present; returns the path, or None when neither the checkout nor a prebuilt file exists."""
     if os.path.exists(_REF_SRC):
-        subprocess.run(["make", "-s", "-C", _HERE, "ref"], check=True)
+        subprocess.run(["make", "-s", "-C", _HERE, "ref", "REF=" + _REF_DIR], check=True)
     return _REF_SO if os.path.exists(_REF_SO) else None
 
 

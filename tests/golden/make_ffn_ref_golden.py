@@ -1,7 +1,7 @@
 """Generates tests/golden/ffn_ref/*.npy by RUNNING THE REFERENCE'S OWN PYTHON CODE:
 scripts/ffn_reference.py of the reference (a float64 numpy statement of the gpt-oss layer-0 MoE FFN:
 router + top-4 softmax, SwiGLU-OAI, biases, weighted combine) on a seeded synthetic one-layer model
-of the gpt-oss-20b layer shape, written as a GGUF blob + index.json by cpubrrr_b200.synth.
+of the gpt-oss-20b layer shape, written as a GGUF blob by cpubrrr_b200.synth and indexed by the reference's scripts/gguf_index.py.
 
     python tests/golden/make_ffn_ref_golden.py      # needs the reference checkout, ~1 GB of /tmp
 
@@ -25,7 +25,9 @@ import cpubrrr_b200 as B  # noqa: E402
 from cpubrrr_b200 import synth as S  # noqa: E402
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-REF = "/root/reference/scripts/ffn_reference.py"
+sys.path.insert(0, os.path.dirname(HERE))
+import refdata  # noqa: E402
+REF = os.path.join(refdata.REF, "scripts", "ffn_reference.py")
 SEED = 77
 
 
@@ -52,7 +54,11 @@ def main():
     os.makedirs(out, exist_ok=True)
     cfg = B.make_cfg(2880, 1, 64, 8, 32, 4, 256)
     with tempfile.TemporaryDirectory() as tmp:
-        d, blob = S.write_synth_model(os.path.join(tmp, "m"), cfg, SEED)
+        d = os.path.join(tmp, "m")
+        os.makedirs(d)
+        blob = os.path.join(d, "model.gguf")
+        S.write_gguf(blob, cfg, SEED)
+        refdata.run_reference_setup(blob, d)        # index.json by the reference's own gguf_index.py
         lower_expert_exponents(blob, os.path.join(d, "index.json"))
         res = os.path.join(tmp, "out")
         os.makedirs(res)

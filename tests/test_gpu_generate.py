@@ -95,8 +95,8 @@ def test_engine_binary_serve_protocol(brrr, orc, tmp_path):
     contains the harmony special ids: [READY], streamed bytes, [STATS] and [DONE] lines; the token
     count and text equal what the oracle generates for the same prompt ids."""
     from oracle import oracle_host as H
-    cfg = brrr.make_cfg(64, 1, 2, 1, 4, 2, 200064, sliding_window=16)
-    d, blob = S.write_synth_model(str(tmp_path / "m"), cfg, 37)
+    import refdata
+    cfg, d, blob = refdata.case_data_dir(str(tmp_path / "m"), "gptoss_serve", 37)
     exe = os.path.join(os.path.dirname(brrr.__file__), "brrr_engine")
     req = "What is 2+2?\n0\t1\t5\tw3 w4\\nw5\n"
     r = subprocess.run([exe, d, blob, "--serve"], input=req.encode(), capture_output=True, timeout=300)

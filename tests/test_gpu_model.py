@@ -86,8 +86,8 @@ def test_layer_trace_bit_exact(brrr, orc):
 def test_data_dir_load_equals_synth(brrr, orc, tmp_path):
     """brrr_model_open on a GGUF + config/manifest data directory == the device-generated synthetic
     model of the same seed == the oracle loading the same directory."""
-    cfg = brrr.make_cfg(128, 2, 4, 2, 8, 4, 512)
-    d, blob = S.write_synth_model(str(tmp_path), cfg, 12)
+    import refdata
+    cfg, d, blob = refdata.case_data_dir(str(tmp_path), "gptoss_d128", 12)
     e1 = brrr.Engine.open(d, blob)
     e2 = brrr.Engine.synth(cfg, 12)
     om = orc.Model.open(d, blob)

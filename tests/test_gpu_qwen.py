@@ -109,8 +109,8 @@ def test_qwen_long_context_bit_exact(brrr, orc):
 
 def test_qwen_data_dir_load(brrr, orc, tmp_path):
     """brrr_qwen_open on a GGUF blob + data directory == the synthetic builder (same bytes)."""
-    cfg = brrr.make_qwen_cfg(256, 2, 4, 2, 8, 4, 256, 600)
-    d, blob = S.write_synth_model(str(tmp_path / "qw"), cfg, 12, arch="qwen3moe")
+    import refdata
+    cfg, d, blob = refdata.case_data_dir(str(tmp_path / "qw"), "qwen_d256", 12)
     eng = brrr.QwenEngine.open(d, blob)
     ref = brrr.QwenEngine.synth(cfg, 12)
     assert eng.cfg.n_ff_exp == 256 and eng.cfg.n_vocab == 600
@@ -118,6 +118,28 @@ def test_qwen_data_dir_load(brrr, orc, tmp_path):
     assert greedy(eng.run, prompt, 40) == greedy(ref.run, prompt, 40)
     assert np.array_equal(bits(eng.logits()), bits(ref.logits()))
     eng.close(); ref.close()
+
+
+def test_qwen_mixed_kquant_types_per_tensor(brrr, orc, tmp_path):
+    """A file that mixes K-quant types per tensor the way real files do (attn_v of layer 0 stored as
+    Q6_K, the down experts of layer 1 as Q4_K; the reference dispatches on the manifest's type,
+    src/bin/engine_qwen2.rs:202-212): the engine and the oracle load the same directory and agree
+    bit for bit, and the result differs from the all-default-types model of the same seed."""
+    import refdata
+    cfg, d, blob = refdata.case_data_dir(str(tmp_path / "qm"), "qwen_mixed", 12)
+    man = open(os.path.join(d, "manifest.txt")).read()
+    assert "blk.0.attn_v.weight 14 " in man and "blk.1.ffn_down_exps.weight 12 " in man
+    eng = brrr.QwenEngine.open(d, blob)
+    om = orc.QwenModel.open(d, blob)
+    prompt = S.synth_prompt(12, 7, cfg.n_vocab)
+    got, want = greedy(eng.run, prompt, 40), greedy(om.run, prompt, 40)
+    assert got == want
+    assert np.array_equal(bits(eng.logits()), bits(om.logits()))
+    assert np.array_equal(bits(eng.hidden()), bits(om.hidden()))
+    plain = brrr.QwenEngine.synth(cfg, 12)
+    greedy(plain.run, prompt, 40)
+    assert not np.array_equal(bits(plain.hidden()), bits(eng.hidden()))
+    eng.close(); plain.close(); om.close()
 
 
 def test_qwen_open_errors(brrr, tmp_path):

@@ -18,8 +18,7 @@ def L(brrr):
 def tokdir(tmp_path_factory):
     """tokens.bin of a toy vocabulary: 256 bytes, short words, duplicates, long pieces, specials."""
     d = tmp_path_factory.mktemp("tok")
-    u2b = S._bytes_to_unicode()
-    toks = [t if t.startswith(b"<|") else bytes(u2b[ch] for ch in t.decode("utf-8")) for t in S.default_tokens(700)]   # raw bytes, as tokens.bin holds them
+    toks = S.raw_tokens(700)             # raw bytes, as tokens.bin holds them
     toks[300] = toks[65]                 # duplicate of a byte token: the lower id must win
     toks[301] = b"hello"
     toks[302] = b"hello world"

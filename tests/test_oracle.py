@@ -231,8 +231,8 @@ def test_synth_generator_numpy_equals_c(orc):
 def test_data_dir_route_equals_synth_route(orc, tmp_path):
     """A model written as GGUF + config/manifest and loaded through the data-directory contract
     gives the same tokens and logits as the in-memory synthetic model of the same seed."""
-    from cpubrrr_b200.engine import make_cfg
-    d, blob = S.write_synth_model(str(tmp_path), make_cfg(128, 2, 4, 2, 8, 4, 512), 7)
+    import refdata
+    _, d, blob = refdata.case_data_dir(str(tmp_path), "gptoss_d128", 7)
     m1 = orc.Model.open(d, blob)
     m2 = orc.Model.synth(orc.make_cfg(d=128, nh=4, nkv=2, hd=64, nl=2, ne=8, topk=4, nvocab=512), 7)
     p = S.synth_prompt(7, 6, 500)

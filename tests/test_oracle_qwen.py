@@ -156,15 +156,30 @@ def test_qwen_golden_tokens(orc):
 def test_qwen_data_dir_equals_synth(orc, tmp_path):
     """The file-loading path (GGUF blob + config.txt + manifest.txt in the reference's formats)
     gives the same model as the in-memory generator: same tensors, same tokens."""
-    from cpubrrr_b200 import make_qwen_cfg
+    import refdata
     c = QGOLD["cfg"]
-    cfg = make_qwen_cfg(c["d"], c["nl"], c["nh"], c["nkv"], c["ne"], c["topk"], c["ff"], c["nvocab"])
-    d, blob = S.write_synth_model(str(tmp_path / "qw"), cfg, QGOLD["seed"], arch="qwen3moe")
+    cfg, d, blob = refdata.case_data_dir(str(tmp_path / "qw"), "qwen_gold", QGOLD["seed"])
     text = open(os.path.join(d, "config.txt")).read()
     assert "n_ff_exp 256" in text and "head_dim 128" in text
     m = orc.QwenModel.open(d, blob)
     assert m.cfg.ff == c["ff"] and m.cfg.nvocab == c["nvocab"]
     assert _greedy(m, QGOLD["prompt"], 24) == QGOLD["tokens"][:24]
+
+
+def test_qwen_mixed_types_data_dir(orc, tmp_path):
+    """Per-tensor K-quant types come from the manifest (engine_qwen2.rs:202-212): a directory whose
+    attn_v (layer 0) is Q6_K and whose down experts (layer 1) are Q4_K loads and runs; its tensors
+    carry the stored types."""
+    import refdata
+    cfg, d, blob = refdata.case_data_dir(str(tmp_path / "qm"), "qwen_mixed", 12)
+    m = orc.QwenModel.open(d, blob)
+    p = S.synth_prompt(12, 7, cfg.n_vocab)
+    toks = _greedy(m, [int(t) for t in p], 12)
+    assert len(toks) == 12 and np.isfinite(m.logits()).all()
+    plain = orc.QwenModel.synth(orc.make_qcfg(cfg.n_embd, cfg.n_head, cfg.n_head_kv, cfg.head_dim, cfg.n_layer, cfg.n_expert,
+                                              cfg.n_expert_used, cfg.n_ff_exp, cfg.n_vocab), 12)
+    _greedy(plain, [int(t) for t in p], 12)
+    assert not np.array_equal(plain.hidden(), m.hidden())
 
 
 def test_qwen_norm_and_router_pieces(orc):
