@@ -123,58 +123,123 @@ class ClockSampler:
         return {"sm_mhz": statistics.median(sm), "sm_max_mhz": max(smax), "reasons": sorted(reasons), "samples": len(sm)}
 
 
-def run_reference(args, rank, world):
-    """CPU arm: the oracle (a port of the reference's algorithm) on all host threads."""
-    if rank != 0:
-        return
-    cores = os.cpu_count() or 1
-    O, m = oracle_model(args.workload != "gptoss20b")
-    prompt = O.synth_prompt(SEED, PROMPT_LEN, TOK_BOUND)
+def algorithmic_bytes(qwen, big, pos):
+    """Bytes one decode step must read once in the reference's run-time formats (weights + f32 KV
+    window + embedding row), the same accounting as brrr_model_bytes_per_step /
+    brrr_qwen_bytes_per_step; used where no engine is open (the CPU arm)."""
+    if qwen:
+        d, nh, nkv, hd, nl, ne, k, ff, nv = 2048, 32, 4, 128, 48, 128, 8, 768, 151936
+        q4, q6 = lambda r, c: r * (c // 256) * 144, lambda r, c: r * (c // 256) * 210
+        per = q4(nh * hd, d) + 2 * q4(nkv * hd, d) + q4(d, nh * hd) + k * (2 * q4(ff, d) + q6(d, ff)) + ne * d * 4 + 2 * d * 4 + 2 * hd * 4
+        return nl * (per + (pos + 1) * nkv * hd * 8) + q6(nv, d) + d * 4 + q4(1, d)
+    d, nh, nkv, hd, nl, ne, k, nv, swa = 2880, 64, 8, 64, (36 if big else 24), (128 if big else 32), 4, 201088, 128
+    nb = d // 32
+    q8 = lambda r, c: r * c + r * (c // 32) * 4
+    per = k * 3 * d * nb * 17 + q8((nh + 2 * nkv) * hd, d) + q8(d, nh * hd) + ne * d * 4 + ne * 4
+    per += ((nh + 2 * nkv) * hd + d) * 4 + k * 3 * d * 4 + 2 * d * 4 + nh * 4
+    tot = per * nl
+    for il in range(nl):
+        start = max(0, pos + 1 - swa) if (il + 1) % 2 else 0
+        tot += (pos - start + 1) * nkv * hd * 8
+    return tot + q8(nv, d) + d * 4 + d * 2
+
+
+def config_dict(K, world, ep_mode, reduced_note=None):
+    """The `config` object of the JSON line; both arms print the same one for the same arguments."""
+    par = (f"expert-parallel x{world}" if ep_mode else f"replicas x{world}") if (world > 1 or ep_mode) else "single GPU"
+    return {"workload": WORKLOAD if not reduced_note else reduced_note, "arch": ARCH, "positions": [PROMPT_LEN, PROMPT_LEN + K],
+            "parallelism": par, "l2": "inputs larger than L2 (a step streams 2-4 GB of weights; L2 holds 126 MB)"}
+
+
+def oracle_decode(m, prompt, nsteps, warm=0, want_gaps=False):
+    """Prompt, `warm` untimed greedy steps from the prompt's end, then - from the prompt's end again,
+    as the GPU arm does (recomputing a position overwrites its KV entries with the same values) -
+    nsteps timed greedy steps on the oracle.  Returns (first token after the prompt, tokens of the
+    timed steps, seconds, smallest top-1/top-2 logit gap of the timed steps or None)."""
+    import numpy as np
     tok = 0
     for i, t in enumerate(prompt):
         tok = m.run(int(t), i, i == len(prompt) - 1)
-    pos = PROMPT_LEN
-    # bounded sample: each call is one decode token; cap the total so the run ends within minutes
-    steps = min(args.steps, 64)
-    warm = min(args.warmup, 3)
+    first = tok
+    pos = len(prompt)
     for _ in range(warm):
         tok = m.run(tok, pos, True); pos += 1
+    tok, pos, got, gap = first, len(prompt), [], None
     t0 = time.perf_counter()
-    for _ in range(steps):
+    for _ in range(nsteps):
         tok = m.run(tok, pos, True); pos += 1
-    dt = time.perf_counter() - t0
-    v = steps / dt
-    sample = f"{steps} decode steps from position {PROMPT_LEN + warm} after a {PROMPT_LEN}-token prompt (full model)"
+        got.append(tok)
+        if want_gaps:
+            a = np.partition(m.logits(), -2)[-2:]
+            g = float(a[1] - a[0])
+            gap = g if gap is None else min(gap, g)
+    return first, got, time.perf_counter() - t0, gap
+
+
+def run_reference(args, rank, world):
+    """CPU arm: the oracle (a port of the reference's algorithm) on all host threads, same workload,
+    step count and warm-up as the GPU arm.  Under a multi-rank launcher rank 0 alone runs it."""
+    if rank != 0:
+        return
+    qwen, big = args.workload == "qwen3-30b-a3b", args.workload == "gptoss120b"
+    if big:
+        print(json.dumps({"impl": "reference", "unavailable": "the CPU port would need 61 GB of expert weights in host memory"}), flush=True)
+        return
+    cores = os.cpu_count() or 1
+    O, m = oracle_model(qwen)
+    threads = O.set_threads(cores)          # launchers export OMP_NUM_THREADS=1: ask for every core explicitly
+    prompt = O.synth_prompt(SEED, PROMPT_LEN, TOK_BOUND)
+    K = max(1, min(args.steps, 256))        # bounded: ~0.1 s per step
+    warm = max(args.warmup, 3)
+    first, toks, dt, _ = oracle_decode(m, prompt, K, warm)
+    v = K / dt
+    # one thread, two steps: the scalar figure beside the threaded one
+    O.set_threads(1)
+    t0 = time.perf_counter()
+    tok, pos = toks[-1], PROMPT_LEN + K
+    for _ in range(2):
+        tok = m.run(tok, pos, True); pos += 1
+    v1 = 2 / (time.perf_counter() - t0)
+    O.set_threads(cores)
+    by = sum(algorithmic_bytes(qwen, big, PROMPT_LEN + i) for i in range(K)) / K
+    sample = f"{K} decode steps from position {PROMPT_LEN} after the {PROMPT_LEN}-token prompt (full model)"
     print(json.dumps({
-        "impl": "reference", "metric": METRIC, "value": v, "unit": "tok/s", "n_gpus": args.gpus, "steps": steps, "warmup": warm,
-        "ms_per_step": 1000.0 * dt / steps, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": DTYPE,
-        "data": "synthetic", "config": {"workload": WORKLOAD, "l2": "inputs larger than L2"},
-        "cpu_baseline": {"value": v, "unit": "tok/s", "cores": cores, "kind": "port", "sample": sample},
+        "impl": "reference", "metric": METRIC, "value": v, "unit": "tok/s", "n_gpus": args.gpus, "steps": K, "warmup": warm,
+        "ms_per_step": 1000.0 * dt / K, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": DTYPE,
+        "data": "synthetic", "config": config_dict(K, world, False),
+        "cpu_baseline": {"value": v, "unit": "tok/s", "cores": threads, "kind": "port", "sample": sample,
+                         "value_1thread": v1, "gbs": by * v / 1e9, "gbs_1thread": by * v1 / 1e9},
         "e2e": {"value": v, "unit": "tok/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }), flush=True)
 
 
 def cpu_baseline_and_parity(eng_tokens, first_tok, nsteps, qwen=False):
-    """Rank 0, N = 1: time the oracle on a bounded sample of the same workload and use it as the
-    checker of the GPU's first decoded tokens."""
+    """Rank 0, N = 1: time the oracle on a bounded sample of the same workload (all host threads) and
+    use it as the checker of the GPU's decoded tokens."""
     O, m = oracle_model(qwen)
+    cores = O.set_threads(os.cpu_count() or 1)
     prompt = O.synth_prompt(SEED, PROMPT_LEN, TOK_BOUND)
-    tok = 0
-    for i, t in enumerate(prompt):
-        tok = m.run(int(t), i, i == len(prompt) - 1)
-    ok = tok == first_tok
-    pos = PROMPT_LEN
-    t0 = time.perf_counter()
-    got = []
-    for _ in range(nsteps):
-        tok = m.run(tok, pos, True); pos += 1
-        got.append(tok)
-    dt = time.perf_counter() - t0
-    ok = ok and got == [int(t) for t in eng_tokens[:nsteps]]
+    first, got, dt, gap = oracle_decode(m, prompt, nsteps, 0, want_gaps=True)
+    ok = first == first_tok and got == [int(t) for t in eng_tokens[:nsteps]]
+    by = sum(algorithmic_bytes(qwen, False, PROMPT_LEN + i) for i in range(nsteps)) / nsteps
     m.close()
-    return {"value": nsteps / dt, "unit": "tok/s", "cores": os.cpu_count() or 1, "kind": "port",
-            "sample": f"{nsteps} decode steps from position {PROMPT_LEN} after the {PROMPT_LEN}-token prompt (full model)"}, \
-           {"tokens_checked": nsteps + 1, "identical": bool(ok)}
+    return {"value": nsteps / dt, "unit": "tok/s", "cores": cores, "kind": "port", "gbs": by * nsteps / dt / 1e9,
+            "sample": f"{nsteps} decode steps from position {PROMPT_LEN} after the {PROMPT_LEN}-token prompt (full model; includes reading back the logits of every step for the gap statistic)"}, \
+           {"tokens_checked": nsteps + 1, "identical": bool(ok), "min_top1_top2_logit_gap": gap}
+
+
+def ncu_traffic_table():
+    """dram__bytes_read.sum + dram__bytes_write.sum per launch and kernel class, from the table in
+    profiles/ncu_dram_traffic_per_launch.md (rows `| class | bytes | capture |`)."""
+    import re
+    out = {}
+    p = os.path.join(ROOT, "profiles", "ncu_dram_traffic_per_launch.md")
+    if os.path.exists(p):
+        for line in open(p):
+            m = re.match(r"\|\s*([a-z0-9_]+)\s*\|\s*([0-9.]+(?:e[0-9]+)?)\s*\|", line)
+            if m:
+                out[m.group(1)] = float(m.group(2))
+    return out
 
 
 def run_moe_tile(args):
@@ -286,6 +351,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline / parity leg")
     ap.add_argument("--no-stages", action="store_true", help="skip the per-kernel-class timing")
+    ap.add_argument("--no-ep", action="store_true", help="N > 1: skip the expert-parallel gpt-oss-120b leg")
     ap.add_argument("--workload", default="gptoss20b", choices=["gptoss20b", "gptoss120b", "qwen3-30b-a3b", "moe-tile", "prefill"],
                     help="gptoss20b is the benchmark workload; gptoss120b is the expert-parallel configuration; qwen3-30b-a3b measures the reference's second engine")
     ap.add_argument("--parallel", default="replicas", choices=["replicas", "ep"],
@@ -353,108 +419,130 @@ def main():
         else:
             eng = B.Engine.synth(cfg, SEED, device=local_rank)
             prompt = S.synth_prompt(SEED + rank, PROMPT_LEN, min(199999, args.vocab))   # every replica decodes its own sequence
-    first = eng.prefill(prompt)
-    stream = torch.cuda.ExternalStream(eng.stream, device=torch.device("cuda", local_rank))
-
     def barrier():
         torch.cuda.synchronize()
         if dist is not None:
             dist.barrier()
         torch.cuda.synchronize()
 
-    # ---- device-chained decode: W warm-up steps, then exactly K timed steps
-    eng.decode(first, PROMPT_LEN, args.warmup)
-    sampler = ClockSampler(local_rank) if rank == 0 else None
-    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-    barrier()
-    if sampler:
-        sampler.start()
-    e0.record(stream)
-    eng.decode_enqueue(first, PROMPT_LEN, K)
-    e1.record(stream)
-    toks = eng.decode_wait(K)
-    barrier()
-    ms = e0.elapsed_time(e1)
-    if dist is not None:
-        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+    def reduce_max(x):
+        if dist is None:
+            return x
+        t = torch.tensor([x], device="cuda", dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        ms = float(t.item())
-    # keep the GPUs busy long enough for the clock sampler on short runs; the number of extra calls
-    # is derived from the reduced time, so every rank issues the same calls (expert-parallel ranks must)
-    extra = int(max(0.0, 1.0 - ms / 1000.0) / (16 * ms / K / 1000.0)) + 1
-    for _ in range(extra):
-        eng.decode(first, PROMPT_LEN, 16)
-    clocks = sampler.stop() if sampler else None
+        return float(t.item())
 
-    # ---- end to end through the public API: host token in, host token out, every step
-    tok, pos = first, PROMPT_LEN
-    for _ in range(args.warmup):
-        tok = eng.run(tok, pos, True); pos += 1
-    tok, pos = first, PROMPT_LEN
-    barrier()
-    t0 = time.perf_counter()
-    for _ in range(K):
-        tok = eng.run(tok, pos, True); pos += 1
-    torch.cuda.synchronize()
-    e2e_s = time.perf_counter() - t0
-    if dist is not None:
-        t = torch.tensor([e2e_s], device="cuda", dtype=torch.float64)
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        e2e_s = float(t.item())
+    def measure(eng, prompt, sample_clocks):
+        """Prompt, W warm-up steps, exactly K timed device-chained steps (CUDA events on the engine's
+        stream; the closing event is recorded after brrr_decode_wait, so any step the host had to
+        re-run because the routing estimate missed lies inside the timed region), then the same K steps
+        end to end through Engine.run.  Times are the maximum over ranks."""
+        first = eng.prefill(prompt)
+        stream = torch.cuda.ExternalStream(eng.stream, device=torch.device("cuda", local_rank))
+        eng.decode(first, PROMPT_LEN, args.warmup)
+        redos0 = eng.spec_redos() if hasattr(eng, "spec_redos") else 0
+        sampler = ClockSampler(local_rank) if (rank == 0 and sample_clocks) else None
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        barrier()
+        if sampler:
+            sampler.start()
+        e0.record(stream)
+        eng.decode_enqueue(first, PROMPT_LEN, K)
+        toks = eng.decode_wait(K)
+        e1.record(stream)
+        barrier()
+        ms = reduce_max(e0.elapsed_time(e1))
+        redos = (eng.spec_redos() if hasattr(eng, "spec_redos") else 0) - redos0
+        # keep the GPUs busy long enough for the clock sampler on short runs; the number of extra calls
+        # is derived from the reduced time, so every rank issues the same calls (expert-parallel ranks must)
+        clocks = None
+        if sample_clocks:
+            extra = int(max(0.0, 1.0 - ms / 1000.0) / (16 * ms / K / 1000.0)) + 1
+            for _ in range(extra):
+                eng.decode(first, PROMPT_LEN, 16)
+            clocks = sampler.stop() if sampler else None
+        # end to end through the public API: host token in, host token out, every step
+        tok, pos = first, PROMPT_LEN
+        for _ in range(args.warmup):
+            tok = eng.run(tok, pos, True); pos += 1
+        tok, pos = first, PROMPT_LEN
+        barrier()
+        t0 = time.perf_counter()
+        for _ in range(K):
+            tok = eng.run(tok, pos, True); pos += 1
+        torch.cuda.synchronize()
+        e2e_s = reduce_max(time.perf_counter() - t0)
+        return {"first": first, "toks": toks, "ms": ms, "e2e_s": e2e_s, "redos": redos, "clocks": clocks}
 
-    if rank != 0:
-        if dist is not None:
-            dist.barrier()              # nobody frees memory its peers may still write to
-        eng.close()
-        if dist is not None:
-            dist.destroy_process_group()
-        return
+    def roofline_of(eng, ms, ngpu):
+        by = sum(eng.bytes_per_step(PROMPT_LEN + i) for i in range(K)) / K
+        ach = by / (ms / K) / 1e6
+        return {"bound": "hbm", "bytes_per_step": by, "achieved": ach, "peak": peak * ngpu, "unit": "GB/s", "frac": ach / (peak * ngpu),
+                "peak_kind": peak_kind, "frac_of_8TBs": ach / (8000.0 * ngpu)}
 
     peak, peak_kind = measured_peaks()
-    mid = PROMPT_LEN + K // 2
-    step_bytes = sum(eng.bytes_per_step(PROMPT_LEN + i) for i in range(K)) / K
+    r = measure(eng, prompt, True)
+    ms, toks, first = r["ms"], r["toks"], r["first"]
     nseq = 1 if ep_mode else world          # expert-parallel ranks share one sequence
-    value = nseq * K / (ms / 1000.0)
-    out = {
-        "metric": METRIC, "value": value, "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": args.warmup,
-        "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong" if ep_mode else "weak", "vs_baseline": None,
-        "dtype": DTYPE, "data": "synthetic",
-        "config": {"workload": WORKLOAD if not reduced else f"PROFILING CASE ({args.layers} layers, vocab {args.vocab}) - not the benchmark workload", "arch": ARCH,
-                   "positions": [PROMPT_LEN, PROMPT_LEN + K], "parallelism": (f"expert-parallel x{world}" if ep_mode else f"replicas x{world}") if (world > 1 or ep_mode) else "single GPU",
-                   "l2": f"inputs larger than L2 ({eng.bytes_per_step(PROMPT_LEN) / 1e9:.2f} GB of weights streamed per step)"},
-        "e2e": {"value": nseq * K / e2e_s, "unit": "tok/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 4},
-        "gpu_launches": K * eng.launches_per_step(True),
-        "clocks": clocks,
-        "step_roofline": {"bound": "hbm", "bytes_per_step": step_bytes, "achieved": step_bytes / (ms / K) / 1e6, "peak": peak * (world if ep_mode else 1),
-                          "unit": "GB/s", "frac": step_bytes / (ms / K) / 1e6 / (peak * (world if ep_mode else 1)), "peak_kind": peak_kind,
-                          "frac_of_8TBs": step_bytes / (ms / K) / 1e6 / 8000.0},
-    }
-    if not args.no_stages:
-        st = [r for r in eng.stage_times(mid, reps=10) if r[3] > 0]      # classes the step does not launch report 0 launches
-        tot = sum(t * n for _, t, _, n in st)
-        stages = [{"kernel": nm, "launches_per_step": n, "us_per_launch": 1000 * t, "share": t * n / tot,
-                   "bytes_per_launch": by, "gbs": by / t / 1e6 if t > 0 else 0.0} for nm, t, by, n in st]
-        out["stages"] = stages
-        # dram__bytes_read+write per launch from the committed ncu captures (profiles/
-        # gptoss20b_expert_kernels_tcgen05_ncu_full_small_case.md for gate/up and down,
-        # gptoss20b_layer_kernels_ncu_full_small_case.md for the rest); the layer kernels' shapes do
-        # not depend on the layer count or vocabulary of the captured case.
-        ncu_traffic = {"norm_gate_up_swiglu_mxfp4": 35.42e6, "down_combine_mxfp4": 18.20e6, "norm_qkv_gemv": 16.68e6,
-                       "oproj_gemv": 13.32e6, "norm_router_topk": 0.49e6, "attention": 0.06e6}
-        # the dominant kernel of the step: the exact router is left out, it runs on a side stream
-        # beside gate/up and down and is not on the step's critical path
-        top = max((s for s in stages if s["kernel"] != "norm_router_topk" or qwen), key=lambda s: s["share"])
-        out["roofline"] = {"bound": "hbm", "kernel": top["kernel"], "achieved": top["gbs"], "peak": peak, "unit": "GB/s",
-                           "frac": top["gbs"] / peak, "traffic": ncu_traffic.get(top["kernel"]), "peak_kind": peak_kind,
-                           "bytes_per_launch": top["bytes_per_launch"], "us_per_launch": top["us_per_launch"]}
-    if world == 1 and not args.no_cpu:
-        cpu, parity = cpu_baseline_and_parity(toks, first, 16, qwen)
-        out["cpu_baseline"] = cpu
-        out["parity"] = parity
+    out = None
+    if rank == 0:
+        note = f"PROFILING CASE ({args.layers} layers, vocab {args.vocab}) - not the benchmark workload" if reduced else None
+        out = {
+            "metric": METRIC, "value": nseq * K / (ms / 1000.0), "unit": "tok/s", "n_gpus": world, "steps": K, "warmup": args.warmup,
+            "ms_per_step": ms / K, "higher_is_better": True, "scaling": "strong" if ep_mode else "weak", "vs_baseline": None,
+            "dtype": DTYPE, "data": "synthetic", "config": config_dict(K, world, ep_mode, note),
+            "e2e": {"value": nseq * K / r["e2e_s"], "unit": "tok/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 4},
+            "gpu_launches": K * eng.launches_per_step(True), "spec_redos": r["redos"], "clocks": r["clocks"],
+            "step_roofline": roofline_of(eng, ms, world if ep_mode else 1),
+        }
+        if not args.no_stages:
+            mid = PROMPT_LEN + K // 2
+            st = [x for x in eng.stage_times(mid, reps=10) if x[3] > 0]      # classes the step does not launch report 0 launches
+            tot = sum(t * n for _, t, _, n in st)
+            stages = [{"kernel": nm, "launches_per_step": n, "us_per_launch": 1000 * t, "share": t * n / tot,
+                       "bytes_per_launch": by, "gbs": by / t / 1e6 if t > 0 else 0.0} for nm, t, by, n in st]
+            out["stages"] = stages
+            traffic = ncu_traffic_table()
+            # the dominant kernel of the step: the exact router is left out, it runs on a side stream
+            # beside gate/up and down and is not on the step's critical path
+            top = max((x for x in stages if x["kernel"] != "norm_router_topk" or qwen), key=lambda x: x["share"])
+            out["roofline"] = {"bound": "hbm", "kernel": top["kernel"], "achieved": top["gbs"], "peak": peak, "unit": "GB/s",
+                               "frac": top["gbs"] / peak, "traffic": traffic.get(top["kernel"]), "peak_kind": peak_kind,
+                               "bytes_per_launch": top["bytes_per_launch"], "us_per_launch": top["us_per_launch"]}
+        if world == 1 and not args.no_cpu:
+            cpu, parity = cpu_baseline_and_parity(toks, first, min(K, 128), qwen)
+            out["cpu_baseline"] = cpu
+            out["parity"] = parity
     if dist is not None:
-        dist.barrier()
+        dist.barrier()                  # nobody frees memory its peers may still write to
     eng.close()
-    print(json.dumps(out), flush=True)
+
+    # ---- N > 1, default workload: the split the path has across GPUs - gpt-oss-120b with the experts
+    # sharded by index over the same ranks (one sequence, strong scaling) - reported under "ep"
+    if world > 1 and not ep_mode and not qwen and not big and not reduced and not args.no_ep:
+        from cpubrrr_b200 import ep
+        cfg120 = B.make_cfg(2880, 36, 64, 8, 128, 4, 201088)
+        if cfg120.n_expert % world == 0:
+            eng = ep.open_synth_ep(cfg120, SEED, rank, world, device=local_rank, dist=dist, torch_device=torch.device("cuda", local_rank))
+            prompt = S.synth_prompt(SEED, PROMPT_LEN, 199999)
+            r = measure(eng, prompt, False)
+            same = [int(t) for t in r["toks"]]
+            agree = True
+            if dist is not None:
+                t = torch.tensor(same, device="cuda", dtype=torch.int64)
+                lo, hi = t.clone(), t.clone()
+                dist.all_reduce(lo, op=dist.ReduceOp.MIN); dist.all_reduce(hi, op=dist.ReduceOp.MAX)
+                agree = bool(torch.equal(lo, hi))
+            if rank == 0:
+                out["ep"] = {"workload": "gpt-oss-120b decode (36 layers, 128 experts top-4), 73-token prompt, batch 1, greedy; experts sharded by index, dense layers replicated",
+                             "n_gpus": world, "scaling": "strong", "value": K / (r["ms"] / 1000.0), "unit": "tok/s", "ms_per_step": r["ms"] / K,
+                             "e2e": {"value": K / r["e2e_s"], "unit": "tok/s", "h2d_bytes_per_step": 8, "d2h_bytes_per_step": 4},
+                             "gpu_launches": K * eng.launches_per_step(True), "step_roofline": roofline_of(eng, r["ms"], world),
+                             "tokens_identical_across_ranks": agree}
+            dist.barrier()
+            eng.close()
+    if rank == 0:
+        print(json.dumps(out), flush=True)
     if dist is not None:
         dist.destroy_process_group()
 

@@ -118,6 +118,8 @@ const orc_q8mat *orc_layer_q8(const orc_model *m, int il, int which /*0 q,1 k,2 
 const orc_quadmx *orc_layer_mx(const orc_model *m, int il, int which /*0 gate,1 up,2 down*/);
 const float *orc_layer_f32(const orc_model *m, int il, int kind /* BRRR_T_* */);
 void orc_synth_prompt(uint64_t seed, int n, uint32_t bound, uint32_t *out);
+void orc_set_threads(int n);
+int orc_max_threads(void);
 
 #ifdef __cplusplus
 }

@@ -243,6 +243,12 @@ def q6k_matvec(w, rows, cols, xq, ys, want_dbg=False):
     return (y, dbg) if want_dbg else y
 
 
+def set_threads(n):
+    """OpenMP worker threads of the oracle's parallel loops; returns the count in effect."""
+    lib().orc_set_threads(C.c_int(int(n)))
+    return int(lib().orc_max_threads())
+
+
 def synth_prompt(seed, n, bound):
     out = np.empty(n, np.uint32)
     lib().orc_synth_prompt(C.c_uint64(seed), C.c_int(n), C.c_uint32(bound), _p(out))

@@ -5,10 +5,17 @@
 #include "oracle_math.h"
 #include <stdlib.h>
 #include <float.h>
+#include <omp.h>
 
 static const int8_t KVI[16] = {0, 1, 2, 3, 4, 6, 8, 12, 0, -1, -2, -3, -4, -6, -8, -12}; /* engine_gpt2.rs:152 */
 
 float orc_expf_c(float x) { return orc_expf(x); }
+
+/* Worker threads of the parallel loops (the reference runs NT worker threads, engine_gpt2.rs:26-38);
+ * set explicitly because launchers such as torchrun export OMP_NUM_THREADS=1.  Results do not
+ * depend on it: every loop iteration owns its outputs. */
+void orc_set_threads(int n) { if (n > 0) omp_set_num_threads(n); }
+int orc_max_threads(void) { return omp_get_max_threads(); }
 
 /* vaddvq_f32: pairwise (l0+l1)+(l2+l3) */
 static inline float hsum4(const float v[4]) { return (v[0] + v[1]) + (v[2] + v[3]); }

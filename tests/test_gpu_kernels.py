@@ -281,3 +281,56 @@ def test_fold_wait_runs_out_and_reports(L, dev):
     ok(L.brrr_fold_norm(P(dv["top"]), P(dv["wts"]), 4, 256, P(dv["part"]), P(dv["bias"]), P(dv["x"]), P(dv["w"]), C.c_float(1e-5),
                         P(dv["q"]), P(dv["s"]), 0, None))
     assert np.array_equal(bits(dv["x"].cpu().numpy()), bits(want))
+
+
+def test_attention_block_against_reference_script_fixture(L, orc, brrr, dev):
+    """The CUDA attention block (brrr_rmsnorm_quant -> brrr_q8_matvec q/k/v + bias -> brrr_attn_decode
+    with a plain NeoX table -> brrr_q8_matvec o-proj + bias) on the input and cache of
+    scripts/attn_reference.py of the reference (fixture tests/golden/attn_ref, made by running that
+    script): bit-identical to the oracle's block, and within the same bounds of the script's float64
+    output (cosine > 0.9998, relative L2 < 2e-2; the reference's own bar for an int8 path is
+    cosine > 0.999, src/bin/ffn_quant.rs:119-129)."""
+    import torch
+    import test_oracle as TO
+    fx = TO._attn_ref_fixture()
+    want, o = TO.attn_block_oracle(orc, 78, fx)
+    nh, nkv, hd, d, T = 64, 8, 64, 2880, 8
+    seed = 78
+    f32 = lambda kind, n: S.synth_f32(seed, 0, S.T[kind], n)
+    mats = []
+    for kind, rows, cols in (("WQ", nh * hd, d), ("WK", nkv * hd, d), ("WV", nkv * hd, d), ("WO", d, nh * hd)):
+        dw = to_dev(S.synth_bf16(seed, 0, S.T[kind], rows * cols), dev)
+        h = C.c_void_p()
+        ok(L.brrr_q8mat_from_bf16(P(dw), rows, cols, C.byref(h), None))
+        torch.cuda.synchronize()
+        mats.append(h)
+    dx, dw = to_dev(fx["h"], dev), to_dev(f32("ATTN_NORM", d), dev)
+    dq = torch.empty(d, dtype=torch.int8, device=dev); ds = torch.empty(d // 32, dtype=torch.float32, device=dev)
+    ok(L.brrr_rmsnorm_quant(P(dx), P(dw), C.c_float(1e-5), d, None, P(dq), P(ds), None))
+    assert np.array_equal(dq.cpu().numpy(), o["xq"]) and np.array_equal(bits(ds.cpu().numpy()), bits(o["xs"]))
+    dqkv = torch.empty((nh + 2 * nkv) * hd, dtype=torch.float32, device=dev)
+    off = 0
+    for h, kind, rows in zip(mats[:3], ("BQ", "BK", "BV"), (nh * hd, nkv * hd, nkv * hd)):
+        dy = torch.empty(rows, dtype=torch.float32, device=dev)
+        ok(L.brrr_q8_matvec(h, P(dq), P(ds), P(dy), None))
+        torch.cuda.synchronize()
+        dqkv[off:off + rows] = dy + to_dev(f32(kind, rows), dev)
+        off += rows
+    kc = np.zeros((nkv, 4096, hd), np.float32); vc = np.zeros((nkv, 4096, hd), np.float32)       # engine layout [kv head][pos][64]
+    kc[:, :T] = fx["kcache"].reshape(T, nkv, hd).transpose(1, 0, 2); vc[:, :T] = fx["vcache"].reshape(T, nkv, hd).transpose(1, 0, 2)
+    dkc, dvc, dtab, dsinks = to_dev(kc, dev), to_dev(vc, dev), to_dev(o["tab"], dev), to_dev(o["sinks"], dev)
+    dao = torch.empty(nh * hd, dtype=torch.float32, device=dev)
+    daq = torch.empty(nh * hd, dtype=torch.int8, device=dev); das = torch.empty(nh * hd // 32, dtype=torch.float32, device=dev)
+    ok(L.brrr_attn_decode(P(dqkv), P(dkc), P(dvc), P(dtab), P(dsinks), nh, nkv, T, 0, P(dao), P(daq), P(das), None))
+    torch.cuda.synchronize()
+    assert np.array_equal(bits(dao.cpu().numpy()), bits(o["ao"]))
+    assert np.array_equal(daq.cpu().numpy(), o["aq"])
+    dy = torch.empty(d, dtype=torch.float32, device=dev)
+    ok(L.brrr_q8_matvec(mats[3], P(daq), P(das), P(dy), None))
+    torch.cuda.synchronize()
+    y = (dy + to_dev(f32("BO", d), dev)).cpu().numpy()
+    assert np.array_equal(bits(y), bits(want))
+    cos, rel = TO.attn_ref_agreement(y, fx["attn_yref"])
+    assert cos > 0.9998 and rel < 2e-2, (cos, rel)
+    for h in mats:
+        L.brrr_q8mat_free(h)

@@ -206,6 +206,51 @@ def test_full_size_gptoss20b_parity_and_properties(brrr, orc):
     eng.close()
 
 
+def top2_gap(logits):
+    """Difference between the largest and the second largest logit, and the logits' standard deviation."""
+    a = np.partition(logits, -2)[-2:]
+    return float(a[1] - a[0]), float(logits.std())
+
+
+def test_full_size_gptoss20b_73_token_prompt_128_steps(brrr, orc, record_property):
+    """The headline configuration as stated: gpt-oss-20b architecture at full size, a 73-token random-id
+    prompt, then 128 greedy decode steps (positions 73 -> 201, src/bin/engine_gpt2.rs:1420-1438): every
+    token identical to the oracle's, through the host-driven run() loop and through the device-chained
+    decode loop, and the last step's logits and hidden state identical on their bit patterns (which
+    implies the 1e-2 relative-L2 bound).  The smallest top-1/top-2 logit gap of the run is recorded:
+    it says how little float reordering it would take to flip a token."""
+    cfg = brrr.gptoss_20b_cfg()
+    eng = brrr.Engine.synth(cfg, 2)
+    om = orc.Model.synth(ocfg_of(orc, cfg), 2)
+    prompt = S.synth_prompt(2, 73, 199999)
+    tok = 0
+    for i, t in enumerate(prompt):
+        tok = om.run(int(t), i, i == len(prompt) - 1)
+    want, gaps, pos = [tok], [top2_gap(om.logits())], len(prompt)
+    for _ in range(128):
+        tok = om.run(tok, pos, True); pos += 1
+        want.append(tok)
+        gaps.append(top2_gap(om.logits()))
+    first = eng.prefill(prompt)
+    toks = eng.decode(first, len(prompt), 128)
+    assert [first] + [int(t) for t in toks] == want
+    assert np.array_equal(bits(eng.logits()), bits(om.logits()))
+    assert np.array_equal(bits(eng.hidden()), bits(om.hidden()))
+    assert eng.spec_redos() == 0
+    # the same 128 steps with a host token in and out every step
+    tok, pos, got = first, len(prompt), [first]
+    for _ in range(128):
+        tok = eng.run(tok, pos, True); pos += 1
+        got.append(tok)
+    assert got == want
+    assert np.array_equal(bits(eng.logits()), bits(om.logits()))
+    g = min(x for x, _ in gaps)
+    record_property("min_top1_top2_gap", g)
+    record_property("logit_std", gaps[-1][1])
+    print(f"gpt-oss-20b 73+128: min top-1/top-2 gap {g:.3e}, logit std {gaps[-1][1]:.3e}, distinct tokens {len(set(want))}")
+    eng.close(); om.close()
+
+
 def test_speculative_routing_miss_is_redone_exactly(brrr, orc, monkeypatch):
     """The expert weight stream starts from a fast router estimate; a step whose exact experts the
     estimate missed must be detected and re-run, leaving results bit-identical.  The test hook

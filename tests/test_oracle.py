@@ -320,3 +320,72 @@ def test_moe_ffn_against_reference_float64_script(orc):
     assert cos > 0.9999, cos
     assert abs(np.linalg.norm(y64) - np.linalg.norm(r64)) / np.linalg.norm(r64) < 5e-3
     assert rel < 2e-2, rel
+
+
+# ---- attention block against the reference's own float64 script ---------------------------------
+
+def _attn_ref_fixture():
+    d = os.path.join(os.path.dirname(__file__), "golden", "attn_ref")
+    return {k: np.load(os.path.join(d, k + ".npy")) for k in ("h", "kcache", "vcache", "attn_yref")}
+
+
+def plain_rope_table(hd=64, base=150000.0, npos=4096):
+    """cos/sin of pos * base^(-2i/hd): the NeoX rotation scripts/attn_reference.py applies (no YaRN
+    ramp, no mscale), in the [pos][hd/2][2] layout of the engine's table."""
+    inv = np.float64(base) ** (-(np.arange(hd // 2, dtype=np.float64) * 2) / hd)
+    ang = np.arange(npos, dtype=np.float64)[:, None] * inv[None, :]
+    return np.stack([np.cos(ang), np.sin(ang)], axis=-1).astype(np.float32)
+
+
+def attn_block_oracle(orc, seed, fx, T=8):
+    """The oracle's attention block of layer 0 (engine_gpt2.rs:773-841) stage by stage, on the
+    fixture's input and cache, with a plain rope table: returns wo . attention + bo (no residual)."""
+    nh, nkv, hd, d = 64, 8, 64, 2880
+    cfg = orc.make_cfg(d, nh, nkv, hd, 1, 4, 4, 256)
+    om = orc.Model.synth(cfg, seed)
+    Lo = orc.lib()
+    f32 = lambda kind, n: om.layer_f32(0, S.T[kind], n).copy()
+    xn = orc.rmsnorm(fx["h"], f32("ATTN_NORM", d), 1e-5)
+    xq, xs = orc.quant_q8(xn)
+    (wq, sq), (wk, sk), (wv, sv), (wo, so) = (om.layer_q8(0, i) for i in range(4))
+    q = (orc.q8_matvec(wq, sq, xq, xs) + f32("BQ", nh * hd)).reshape(nh, hd)
+    k = (orc.q8_matvec(wk, sk, xq, xs) + f32("BK", nkv * hd)).reshape(nkv, hd)
+    v = (orc.q8_matvec(wv, sv, xq, xs) + f32("BV", nkv * hd)).reshape(nkv, hd)
+    tab = plain_rope_table()
+    vp = lambda a: a.ctypes.data_as(C.c_void_p)
+    for hh in range(nh):
+        Lo.orc_rope_apply(vp(q[hh]), vp(tab), C.c_int(T), C.c_int(hd))
+    for hh in range(nkv):
+        Lo.orc_rope_apply(vp(k[hh]), vp(tab), C.c_int(T), C.c_int(hd))
+    kc = np.zeros((T + 1, nkv, hd), np.float32); vc = np.zeros((T + 1, nkv, hd), np.float32)
+    kc[:T] = fx["kcache"].reshape(T, nkv, hd); vc[:T] = fx["vcache"].reshape(T, nkv, hd)
+    kc[T] = k; vc[T] = v
+    sinks = f32("SINKS", nh)
+    ao = np.concatenate([orc.attn_head(q[hh], kc, vc, nkv, hd, hh // (nh // nkv), 0, T, float(sinks[hh])) for hh in range(nh)])
+    aq, asb = orc.quant_q8(ao)
+    y = orc.q8_matvec(wo, so, aq, asb) + f32("BO", d)
+    om.close()
+    return y, dict(xq=xq, xs=xs, q=q, k=k, v=v, ao=ao, aq=aq, asb=asb, kc=kc, vc=vc, sinks=sinks, tab=tab)
+
+
+def attn_ref_agreement(y, yref):
+    y64, r64 = y.astype(np.float64), yref.astype(np.float64)
+    cos = float(y64 @ r64) / (np.linalg.norm(y64) * np.linalg.norm(r64))
+    rel = np.linalg.norm(y64 - r64) / np.linalg.norm(r64)
+    return cos, rel
+
+
+def test_attention_block_against_reference_float64_script(orc):
+    """Pin of the attention block (RMS norm, q/k/v + bias, NeoX rotation, cache append, GQA head map,
+    sink in the softmax denominator, causal softmax, o-proj + bias) against the reference's own
+    float64 statement, scripts/attn_reference.py, run on the seeded one-layer model of the gpt-oss-20b
+    layer shape (tests/golden/make_attn_ref_golden.py).  The reference accepts its float32 attention
+    against this script at cosine > 0.99999 (src/bin/attn_forward.rs:98-109) and its int8 path at
+    cosine > 0.999 (src/bin/ffn_quant.rs:119-129).  The engine's block quantises the weights
+    (Q8Mat::from_bf16) and the two activations to 8 bits per 32-block; achieved here: cosine 0.99990,
+    relative L2 1.41e-2.  Asserted: cosine > 0.9998, relative L2 < 2e-2."""
+    fx = _attn_ref_fixture()
+    y, _ = attn_block_oracle(orc, 78, fx)
+    cos, rel = attn_ref_agreement(y, fx["attn_yref"])
+    assert cos > 0.9998, cos
+    assert rel < 2e-2, rel
