@@ -58,6 +58,7 @@ cudaError_t launch_q8_stream(Q8Dev m, const float *x_f32, const float *norm_w, f
 
 // Direct-from-global GEMV for very large matrices (the vocabulary head); activation pre-quantised.
 cudaError_t launch_q8_direct(Q8Dev m, const int8_t *xq, const float *xs, const float *bias, float *y, int epi, DevState *state, bool pdl, cudaStream_t st);
+cudaError_t launch_q8_head(Q8Dev m, const int8_t *xq, const float *xs, float *y, DevState *state, bool pdl, cudaStream_t st);
 
 // ---- MXFP4 matrices (kernels_mx.cu)
 void launch_mx_pack(const uint8_t *raw, MxDev m, cudaStream_t st);

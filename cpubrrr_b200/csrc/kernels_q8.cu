@@ -330,6 +330,112 @@ __global__ void __launch_bounds__(256) q8_direct_kernel(Q8Dev m, const int8_t *_
     }
 }
 
+// ---------------------------------------------------------------- vocabulary head: persistent ring
+// The head is one long contiguous stream, so it runs as persistent CTAs (two per SM), each owning a
+// run of consecutive unit rows: a producer thread keeps a ring of chunks (ch units, about 17 KB, one
+// bulk copy each) in flight; the four consumer warps (16 rows x 8 chains) walk the chunks in order
+// and hand each stage back through an mbarrier, so the loop has no block-wide barrier.  Every
+// barrier has one waiting side that consumes in order (a waiter is never more than one phase
+// behind).  Same chain order as every other Q8 row dot.
+constexpr int QH_THREADS = 128 + 32;
+
+struct QHeadArgs {
+    Q8Dev m;
+    const int8_t *xq;
+    const float *xs;
+    float *y;
+    DevState *state;
+    int ch;                 // pairs per chunk
+    int stages;             // ring depth
+};
+
+__global__ void __launch_bounds__(QH_THREADS) q8_head_ring_kernel(QHeadArgs a) {
+    extern __shared__ __align__(128) unsigned char smraw[];
+    const int nb = a.m.cols / 32, np = a.m.cols / 64;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const size_t stage_bytes = (size_t)a.ch * Q8_UNIT;
+    unsigned char *ring = smraw;
+    int2 *xp = reinterpret_cast<int2 *>(smraw + stage_bytes * a.stages);
+    float *xsc = reinterpret_cast<float *>(xp + nb * 4);
+    uint64_t *full = reinterpret_cast<uint64_t *>(xsc + nb + (nb & 1));
+    uint64_t *empty = full + a.stages;
+    __shared__ unsigned long long wbest[4];
+    uint32_t *err = a.state ? &a.state->err : nullptr;
+    Waiter waiter(err);
+    const int urows = q8_urows(a.m.rows);
+    const int u0 = (int)((long long)urows * blockIdx.x / gridDim.x);
+    const int u1 = (int)((long long)urows * (blockIdx.x + 1) / gridDim.x);
+    const int cpr = (np + a.ch - 1) / a.ch;                          // chunks per unit row
+    const int nchunks = (u1 - u0) * cpr;
+    if (tid == 0) {
+        for (int s = 0; s < a.stages; s++) { mbar_init(&full[s], 1); mbar_init(&empty[s], 4); }
+        mbar_fence_init();
+    }
+    __syncthreads();
+    auto issue = [&](int c) {
+        const int u = u0 + c / cpr, k = c % cpr, slot = c % a.stages;
+        const uint32_t bytes = (uint32_t)min(a.ch, np - k * a.ch) * Q8_UNIT;
+        mbar_expect_tx(&full[slot], bytes);
+        bulk_g2s(ring + stage_bytes * slot, a.m.data + q8_unit_off(u, k * a.ch, np), bytes, &full[slot]);
+    };
+    // the weights do not depend on the step: the first ring goes out before the dependency wait
+    const bool producer = warp == 4;
+    if (producer && lane < min(a.stages, nchunks)) issue(lane);
+    pdl_wait();
+    pdl_trigger();
+    waiter.poison_if_failed();
+    if (producer) {
+        if (lane == 0) {
+            for (int c = a.stages; c < nchunks; c++) {
+                waiter.wait_relaxed(&empty[c % a.stages], (uint32_t)(c / a.stages - 1) & 1u);
+                fence_proxy_async();
+                issue(c);
+            }
+        }
+        return;
+    }
+    const int nidx = nb * 4;
+    for (int idx = tid; idx < nidx; idx += 128) {
+        const int *xw = reinterpret_cast<const int *>(a.xq + (idx >> 2) * 32);
+        xp[idx] = make_int2(xw[idx & 3], xw[4 + (idx & 3)]);
+    }
+    for (int b = tid; b < nb; b += 128) xsc[b] = a.xs[b];
+    asm volatile("bar.sync 1, 128;" ::: "memory");                   // the consumer warps only
+    const int rl = tid >> 3, c8 = tid & 7, p = c8 >> 2;
+    unsigned long long best = 0ull;
+    float acc = 0.0f;
+    for (int c = 0; c < nchunks; c++) {
+        const int k = c % cpr, slot = c % a.stages, pair0 = k * a.ch;
+        waiter.wait(&full[slot], (uint32_t)(c / a.stages) & 1u);
+        acc = q8_chunk(ring + stage_bytes * slot, min(a.ch, np - pair0), rl, c8, p, xp + (size_t)pair0 * 8 + c8, xsc + pair0 * 2 + p, acc);
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[slot]);             // this warp has read its four rows of the stage
+        if (k == cpr - 1) {
+            float r = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 4));
+            r = brrr_hsum4(r);
+            const int row = (u0 + c / cpr) * 16 + rl;
+            if (c8 == 0 && row < a.m.rows) {
+                a.y[row] = r;
+                const unsigned long long key = ((unsigned long long)float_orderable(r) << 32) | (0xFFFFFFFFu - (uint32_t)row);
+                best = key > best ? key : best;
+            }
+            acc = 0.0f;
+        }
+    }
+    // running argmax: first strict maximum = lowest index among equal values
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+        best = other > best ? other : best;
+    }
+    if (lane == 0) wbest[warp] = best;
+    asm volatile("bar.sync 1, 128;" ::: "memory");
+    if (tid == 0) {
+        for (int w = 1; w < 4; w++) best = wbest[w] > best ? wbest[w] : best;
+        if (best) atomicMax(&a.state->best, best);
+    }
+}
+
 cudaError_t launch_q8_direct(Q8Dev m, const int8_t *xq, const float *xs, const float *bias, float *y, int epi, DevState *state, bool pdl, cudaStream_t st) {
     const int nb = m.cols / 32;
     size_t smem = (size_t)nb * 4 * sizeof(int2) + (size_t)nb * sizeof(float);
@@ -349,6 +455,26 @@ static int pick_chunk(int np) {
     for (int c = 16; c >= 14; c--) if (np % c == 0) return c;
     for (int c = 17; c <= 20; c++) if (np % c == 0) return c;
     return np < 16 ? np : 16;
+}
+
+// The vocabulary projection with its running argmax (logits to y, best (value, lowest row) to
+// state->best): two persistent CTAs per SM.
+cudaError_t launch_q8_head(Q8Dev m, const int8_t *xq, const float *xs, float *y, DevState *state, bool pdl, cudaStream_t st) {
+    const int nb = m.cols / 32, np = m.cols / 64;
+    int dev = 0, sms = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0)
+        return cudaErrorInvalidDevice;
+    QHeadArgs a{m, xq, xs, y, state, pick_chunk(np), 0};
+    const size_t stage = (size_t)a.ch * Q8_UNIT, fixed = (size_t)nb * 4 * 8 + (size_t)(nb + (nb & 1)) * 4 + 256;
+    a.stages = (int)((100 * 1024 - fixed) / stage);
+    if (a.stages > 8) a.stages = 8;
+    if (a.stages < 2) return launch_q8_direct(m, xq, xs, nullptr, y, Q8_EPI_HEAD, state, pdl, st);
+    const int urows = q8_urows(m.rows);
+    const unsigned grid = (unsigned)(urows < 2 * sms ? urows : 2 * sms);
+    const size_t smem = stage * a.stages + fixed;
+    cudaError_t e = cudaFuncSetAttribute(q8_head_ring_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+    if (e != cudaSuccess) return e;
+    return launch_k(q8_head_ring_kernel, dim3(grid), dim3(QH_THREADS), smem, st, pdl, a);
 }
 
 static size_t q8_smem(const Q8Args &a, bool norm) {

@@ -376,7 +376,7 @@ int enqueue_step(brrr_model *m, bool want, float *trace_dev, int *nlaunch, unsig
         const bool fused = spec && m->use_mxt && m->fused_fold;      // the last fold has written the head's activation; the side stream has just joined
         const bool replay_fused = mask != ~0u && m->use_mxt && m->use_spec && m->fused_fold;      // stage replays mirror the fused step
         if (!fused && !replay_fused && on(ST_HEAD_NORM)) CUL(launch_rmsnorm_quant(m->x, m->out_norm, c.rms_eps, d, nullptr, m->xq, m->xs, pdl, s));
-        if (on(ST_HEAD)) CUL(launch_q8_direct(m->head, m->xq, m->xs, nullptr, m->logits, Q8_EPI_HEAD, m->st, pdl && !fused, s));
+        if (on(ST_HEAD)) CUL(launch_q8_head(m->head, m->xq, m->xs, m->logits, m->st, pdl && !fused, s));
         if (on(ST_FINISH)) launch_finish_token(m->st, s);
     }
     CU(cudaGetLastError());
@@ -842,7 +842,7 @@ static int forward_tile_16(brrr_model *m, const uint32_t *toks, int n, uint32_t 
     CU(cudaMemcpyAsync(m->st, m->h_in, 8, cudaMemcpyHostToDevice, s));
     if (want) {
         CUL(launch_rmsnorm_quant(m->x, m->out_norm, c.rms_eps, d, nullptr, m->xq, m->xs, false, s));
-        CUL(launch_q8_direct(m->head, m->xq, m->xs, nullptr, m->logits, Q8_EPI_HEAD, m->st, false, s));
+        CUL(launch_q8_head(m->head, m->xq, m->xs, m->logits, m->st, false, s));
         launch_finish_token(m->st, s);
     }
     CU(cudaGetLastError());

@@ -49,6 +49,7 @@ def test_golden_tokens_tiny(brrr):
     dict(n_embd=128, n_layer=2, n_head=4, n_head_kv=2, n_expert=8, n_expert_used=4, n_vocab=512),
     dict(n_embd=256, n_layer=3, n_head=8, n_head_kv=8, n_expert=40, n_expert_used=8, n_vocab=2052, sliding_window=32),
     dict(n_embd=320, n_layer=2, n_head=10, n_head_kv=2, n_expert=4, n_expert_used=1, n_vocab=1000),
+    dict(n_embd=128, n_layer=1, n_head=4, n_head_kv=2, n_expert=8, n_expert_used=4, n_vocab=40000),    # many unit rows per CTA in the head's ring
 ])
 def test_tokens_logits_hidden_bit_exact(brrr, orc, shape):
     cfg = brrr.make_cfg(**shape)
