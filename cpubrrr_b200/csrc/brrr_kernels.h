@@ -54,7 +54,8 @@ enum { Q8_EPI_PLAIN = 0, Q8_EPI_BIAS = 1, Q8_EPI_RESID_BIAS = 2, Q8_EPI_HEAD = 3
 // Streaming GEMV.  x_f32 != nullptr: RMSNorm(x_f32, norm_w, eps) + Q8 quantisation in the prologue;
 // otherwise the Q8 activation (xq, xs) is used.  pdl: launch with programmatic stream serialization.
 cudaError_t launch_q8_stream(Q8Dev m, const float *x_f32, const float *norm_w, float eps, const int8_t *xq, const float *xs,
-                             const float *bias, float *y, int epi, DevState *state, bool pdl, cudaStream_t st);
+                             const float *bias, float *y, int epi, DevState *state, bool pdl, cudaStream_t st,
+                             const float *pf_k = nullptr, const float *pf_v = nullptr, int pf_nkv = 0, int pf_window = 0);
 
 // Direct-from-global GEMV for very large matrices (the vocabulary head); activation pre-quantised.
 cudaError_t launch_q8_direct(Q8Dev m, const int8_t *xq, const float *xs, const float *bias, float *y, int epi, DevState *state, bool pdl, cudaStream_t st);

@@ -117,9 +117,18 @@ struct Q8Args {
     DevState *state;
     int ch;                 // pairs per chunk
     int stages;             // ring depth
+    // optional: K/V cache of the attention kernel that follows ([nkv][MAXSEQ][64] each); the window
+    // it will read is requested into L2 ahead of time (it was last touched a whole step ago)
+    const float *pf_k, *pf_v;
+    int pf_nkv, pf_window;
 };
 
 constexpr int Q8_THREADS = 128;
+
+// Ask for bytes [p, p + n) to be brought into L2 (n a multiple of 16); no completion is awaited.
+__device__ __forceinline__ void l2_prefetch(const void *p, uint32_t n) {
+    asm volatile("cp.async.bulk.prefetch.L2.global [%0], %1;" ::"l"(p), "r"(n) : "memory");
+}
 
 template <int EPI, bool NORM>
 __global__ void __launch_bounds__(Q8_THREADS) q8_stream_kernel(Q8Args a) {
@@ -330,6 +339,91 @@ __global__ void __launch_bounds__(256) q8_direct_kernel(Q8Dev m, const int8_t *_
     }
 }
 
+// ---------------------------------------------------------------- register-resident GEMV (q/k/v, o-proj)
+// For the layer projections one CTA owns one unit row (16 rows) and the whole grid is resident at
+// once, so every thread can fetch ALL the weights of its chain (NP block pairs: 8 weight bytes and one
+// scale each) straight into registers before the dependency wait, while the kernel before it is
+// still running.  After the wait only the activation goes through shared memory: no ring, no
+// barrier per chunk, a third of the shared-memory reads of the ring kernel.  Same chain order.
+template <int EPI, int NP>
+__global__ void __launch_bounds__(Q8_THREADS) q8_reg_kernel(Q8Args a) {
+    __shared__ __align__(16) int2 xp[NP * 8];
+    __shared__ float xsc[NP * 2];
+    const int tid = threadIdx.x, rl = tid >> 3, c8 = tid & 7, p = c8 >> 2;
+    const int u = blockIdx.x, row = u * 16 + rl;
+    const uint8_t *unit0 = a.m.data + q8_unit_off(u, 0, NP);
+    const int2 *wp = reinterpret_cast<const int2 *>(unit0 + rl * 64 + c8 * 8);
+    const float *sp = reinterpret_cast<const float *>(unit0 + Q8_UNIT_SCALES + rl * 8 + p * 4);
+    int2 w[NP];
+    float s[NP];
+#pragma unroll
+    for (int i = 0; i < NP; i++) {
+        w[i] = __ldg(wp + (size_t)i * (Q8_UNIT / 8));
+        s[i] = __ldg(sp + (size_t)i * (Q8_UNIT / 4));
+    }
+    float bias_pre = 0.0f, resid_pre = 0.0f;
+    if (c8 == 0 && row < a.m.rows) {
+        if (EPI == Q8_EPI_BIAS || EPI == Q8_EPI_RESID_BIAS) bias_pre = a.bias[row];
+        if (EPI == Q8_EPI_RESID_BIAS) resid_pre = a.y[row];          // written several kernels back
+    }
+#ifndef BRRR_NO_KV_PREFETCH
+    if (a.pf_k && tid == 0 && u < 2 * a.pf_nkv && a.state) {
+        // CTA 2h / 2h+1: the K / V window of KV head h that the attention kernel after this one reads
+        // (positions start .. pos-1; the position is an input of the step, written long before)
+        const int pos = (int)a.state->pos, start = a.pf_window > 0 ? max(pos - (a.pf_window - 1), 0) : 0;
+        const float *base = ((u & 1) ? a.pf_v : a.pf_k) + ((size_t)(u >> 1) * BRRR_MAXSEQ + start) * 64;
+        for (int k = 0; k < pos - start; k += 128) l2_prefetch(base + (size_t)k * 64, (uint32_t)min(128, pos - start - k) * 256u);
+    }
+#endif
+    BRRR_GT_START(a.state, EPI == Q8_EPI_BIAS ? 232 : 234);
+    pdl_wait();          // the activation is now visible
+    BRRR_GT_GO(a.state, (EPI == Q8_EPI_BIAS ? 32 : 64) + 30);
+    pdl_trigger();
+    {
+        // every global load before the first shared-memory store (a store in between would order the loads behind it)
+        constexpr int NIDX = NP * 8, PASSES = (NIDX + Q8_THREADS - 1) / Q8_THREADS;
+        int2 v[PASSES];
+#pragma unroll
+        for (int k = 0; k < PASSES; k++) {
+            const int idx = tid + k * Q8_THREADS;
+            if (idx < NIDX) {
+                const int *xw = reinterpret_cast<const int *>(a.xq + (idx >> 2) * 32);
+                v[k] = make_int2(xw[idx & 3], xw[4 + (idx & 3)]);
+            }
+        }
+        const float sv = tid < NP * 2 ? a.xs[tid] : 0.0f;
+#pragma unroll
+        for (int k = 0; k < PASSES; k++) if (tid + k * Q8_THREADS < NIDX) xp[tid + k * Q8_THREADS] = v[k];
+        if (tid < NP * 2) xsc[tid] = sv;
+    }
+    __syncthreads();
+    float acc = 0.0f;
+#pragma unroll
+    for (int i = 0; i < NP; i++) {
+        const int2 xv = xp[i * 8 + c8];
+        const int t = __dp4a(w[i].y, xv.y, __dp4a(w[i].x, xv.x, 0));
+        acc = __fmaf_rn((float)t, __fmul_rn(s[i], xsc[i * 2 + p]), acc);
+    }
+    float r = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 4));      // acc_even + acc_odd per lane, then (l0+l1)+(l2+l3)
+    r = brrr_hsum4(r);
+    if (c8 == 0 && row < a.m.rows) {
+        if (EPI == Q8_EPI_PLAIN) a.y[row] = r;
+        else if (EPI == Q8_EPI_BIAS) a.y[row] = __fadd_rn(r, bias_pre);
+        else a.y[row] = __fadd_rn(resid_pre, __fadd_rn(r, bias_pre));     // x += dot + bias
+    }
+    BRRR_GT_END(a.state, (EPI == Q8_EPI_BIAS ? 32 : 64) + 31);
+}
+
+template <int NP>
+static cudaError_t q8_reg_launch(const Q8Args &a, int epi, unsigned grid, bool pdl, cudaStream_t st) {
+    switch (epi) {
+    case Q8_EPI_PLAIN: return launch_k(q8_reg_kernel<Q8_EPI_PLAIN, NP>, dim3(grid), dim3(Q8_THREADS), 0, st, pdl, a);
+    case Q8_EPI_BIAS: return launch_k(q8_reg_kernel<Q8_EPI_BIAS, NP>, dim3(grid), dim3(Q8_THREADS), 0, st, pdl, a);
+    case Q8_EPI_RESID_BIAS: return launch_k(q8_reg_kernel<Q8_EPI_RESID_BIAS, NP>, dim3(grid), dim3(Q8_THREADS), 0, st, pdl, a);
+    }
+    return cudaErrorInvalidValue;
+}
+
 // ---------------------------------------------------------------- vocabulary head: persistent ring
 // The head is one long contiguous stream, so it runs as persistent CTAs (two per SM), each owning a
 // run of consecutive unit rows: a producer thread keeps a ring of chunks (ch units, about 17 KB, one
@@ -496,10 +590,21 @@ static cudaError_t q8_launch_t(const Q8Args &a, unsigned grid, bool pdl, cudaStr
 }
 
 cudaError_t launch_q8_stream(Q8Dev m, const float *x_f32, const float *norm_w, float eps, const int8_t *xq, const float *xs,
-                             const float *bias, float *y, int epi, DevState *state, bool pdl, cudaStream_t st) {
+                             const float *bias, float *y, int epi, DevState *state, bool pdl, cudaStream_t st,
+                             const float *pf_k, const float *pf_v, int pf_nkv, int pf_window) {
     Q8Args a{};
     a.m = m; a.x_f32 = x_f32; a.norm_w = norm_w; a.eps = eps; a.xq = xq; a.xs = xs; a.bias = bias; a.y = y; a.state = state;
+    a.pf_k = pf_k; a.pf_v = pf_v; a.pf_nkv = pf_nkv; a.pf_window = pf_window;
     const int np = m.cols / 64, urows = q8_urows(m.rows);
+#ifndef BRRR_NO_Q8_REG
+    // layer projections of the gpt-oss shapes (d 2880, 64 heads x 64): every weight in registers
+    // before the dependency wait; the grid (one CTA per unit row) is resident as a whole
+    // (about 160 registers per thread at 45 pairs: three CTAs per SM; about 220 at 64 pairs: two)
+    if (!x_f32 && epi != Q8_EPI_HEAD) {
+        if (np == 45 && urows <= 148 * 3) return q8_reg_launch<45>(a, epi, (unsigned)urows, pdl, st);
+        if (np == 64 && urows <= 148 * 2) return q8_reg_launch<64>(a, epi, (unsigned)urows, pdl, st);
+    }
+#endif
     a.ch = pick_chunk(np);
     const int cpr = (np + a.ch - 1) / a.ch;
     // Small matrices: one unit row per CTA, whole row resident.  Large ones: a persistent grid.

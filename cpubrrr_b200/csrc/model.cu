@@ -297,7 +297,9 @@ int enqueue_step(brrr_model *m, bool want, float *trace_dev, int *nlaunch, unsig
         Layer &ly = m->L[il];
         // fused: the previous layer's fold has left the normalised, quantised residual in nq / ns
         const bool fused = spec && m->use_mxt && m->fused_fold;
-        if (fused && il > 0) { n++; CUL(launch_q8_stream(ly.wqkv, nullptr, nullptr, 0.0f, m->nq, m->ns, ly.bqkv, m->qkv, Q8_EPI_BIAS, m->st, pdl, s)); }
+        const int kv_window = (((il + 1) % 2 != 0) && c.sliding_window < BRRR_MAXSEQ) ? c.sliding_window : 0;
+        if (fused && il > 0) { n++; CUL(launch_q8_stream(ly.wqkv, nullptr, nullptr, 0.0f, m->nq, m->ns, ly.bqkv, m->qkv, Q8_EPI_BIAS, m->st, pdl, s,
+                                                         ly.kc, ly.vc, nkv, kv_window)); }
         else if (mask != ~0u && m->use_mxt && m->use_spec && m->fused_fold && il > 0) {      // stage replay of the fused step's q/k/v (image left by the last step)
             if (on(ST_QKV)) CUL(launch_q8_stream(ly.wqkv, nullptr, nullptr, 0.0f, m->nq, m->ns, ly.bqkv, m->qkv, Q8_EPI_BIAS, m->st, pdl, s));
         } else if (on(ST_QKV)) CUL(launch_q8_stream(ly.wqkv, m->x, ly.attn_norm, c.rms_eps, nullptr, nullptr, ly.bqkv, m->qkv, Q8_EPI_BIAS, m->st, pdl && n > 1, s));
