@@ -3,7 +3,8 @@ import ctypes as C
 import os
 
 HERE = os.path.dirname(os.path.abspath(__file__))
-LIB_PATH = os.path.join(HERE, "libbrrr.so")
+# BRRR_LIBRARY: another build of the same library (the tests load the test-hook build this way)
+LIB_PATH = os.environ.get("BRRR_LIBRARY") or os.path.join(HERE, "libbrrr.so")
 
 
 class BrrrError(RuntimeError):
@@ -46,11 +47,11 @@ SIGNATURES = {
     "brrr_model_stream": (_P, [_P]),
     "brrr_model_launches_per_step": (_I, [_P, _I]),
     "brrr_model_spec_redos": (C.c_uint64, [_P]),
+    "brrr_model_wait_fallbacks": (C.c_uint64, [_P]),
     "brrr_model_bytes_per_step": (C.c_uint64, [_P, C.c_uint32]),
     "brrr_stage_count": (_I, []),
     "brrr_stage_name": (C.c_char_p, [_I]),
     "brrr_stage_time": (_I, [_P, _I, C.c_uint32, _I, C.POINTER(C.c_float), C.POINTER(C.c_uint64), C.POINTER(_I)]),
-    "brrr_debug_stamps": (_I, [_P, _P]),
     "brrr_model_open_synth_ep": (_I, [C.POINTER(Cfg), C.c_uint64, _I, _I, _I, C.POINTER(_P)]),
     "brrr_model_open_ep": (_I, [C.c_char_p, C.c_char_p, _I, _I, _I, C.POINTER(_P)]),
     "brrr_model_ep_handle": (_I, [_P, _P]),

@@ -1,6 +1,11 @@
 """Build the engine's shared library (cpubrrr_b200/libbrrr.so) with nvcc for sm_100a.
 
-    python -m cpubrrr_b200.build [--force] [--verbose]
+    python -m cpubrrr_b200.build [--force] [--verbose] [--hooks]
+
+--hooks also builds libbrrr_hooks.so: the same sources with -DBRRR_TEST_HOOKS, which compiles in what
+only tests and timeline measurements use (a way to spoil the routing estimate, a way to silence the
+router's publication, in-kernel clock stamps and the entry point that reads them).  The default
+library contains none of it.
 
 The library is built in-tree so that it travels with the source tree.  nvcc cross-compiles
 without a GPU.  -fmad=false: kernels fuse multiply-adds only where written explicitly, which
@@ -16,6 +21,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OBJ = os.path.join(HERE, "_obj")
 LIB = os.path.join(HERE, "libbrrr.so")
+HOOKS_LIB = os.path.join(HERE, "libbrrr_hooks.so")
 EXE = os.path.join(HERE, "brrr_engine")
 
 SOURCES = ["kernels_small.cu", "kernels_q8.cu", "kernels_mx.cu", "kernels_router.cu", "kernels_attn.cu", "kernels_ep.cu", "kernels_tile.cu", "kernels_mxt.cu", "kernels_kq.cu", "kernels_qwen.cu", "qwen_model.cu",
@@ -35,29 +41,28 @@ def _nvcc():
     raise RuntimeError("nvcc not found")
 
 
-def _stale():
-    if not os.path.exists(LIB):
+def _stale(lib):
+    if not os.path.exists(lib):
         return True
-    t = os.path.getmtime(LIB)
+    t = os.path.getmtime(lib)
     deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC)] + [os.path.join(HERE, "..", "include", "brrr.h"), __file__]
     return any(os.path.getmtime(p) > t for p in deps)
 
 
-def build(force=False, verbose=False):
-    """Compile every CUDA source and link libbrrr.so; returns its path."""
-    if not force and not _stale():
-        return LIB
+def build(force=False, verbose=False, defines=(), out=LIB):
+    """Compile every CUDA source with the given -D defines and link the shared library `out`
+    (default: libbrrr.so, plus the brrr_engine binary); returns its path."""
+    if not force and not _stale(out):
+        return out
     nvcc = _nvcc()
-    os.makedirs(OBJ, exist_ok=True)
+    tag = "" if out == LIB else "_" + os.path.splitext(os.path.basename(out))[0]
+    objdir = OBJ + tag
+    os.makedirs(objdir, exist_ok=True)
     extra = ["-Xptxas", "-v"] if verbose else []
-    extra += [f"-D{d}" for d in os.environ.get("BRRR_DEFS", "").split()]
-    if os.environ.get("BRRR_TIMELINE"):
-        extra.append("-DBRRR_TIMELINE")
-        if os.environ.get("BRRR_TIMELINE_CTA"):
-            extra.append("-DBRRR_TIMELINE_CTA=" + os.environ["BRRR_TIMELINE_CTA"])
+    extra += [f"-D{d}" for d in defines]
 
     def compile_one(src):
-        obj = os.path.join(OBJ, os.path.splitext(src)[0] + ".o")
+        obj = os.path.join(objdir, os.path.splitext(src)[0] + ".o")
         cmd = [nvcc, *NVCC_FLAGS, *extra, "-c", os.path.join(CSRC, src), "-o", obj]
         r = subprocess.run(cmd, capture_output=True, text=True)
         if r.returncode != 0:
@@ -68,17 +73,25 @@ def build(force=False, verbose=False):
 
     with ThreadPoolExecutor(max_workers=8) as ex:
         objs = list(ex.map(compile_one, SOURCES))
-    cmd = [nvcc, "-shared", "-o", LIB, *objs, "-gencode", "arch=compute_100a,code=sm_100a", "-ccbin", "g++"]
+    cmd = [nvcc, "-shared", "-o", out, *objs, "-gencode", "arch=compute_100a,code=sm_100a", "-ccbin", "g++"]
     r = subprocess.run(cmd, capture_output=True, text=True)
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
-    # the command-line front end (reference binary's arguments and protocol), linked against the library
-    cmd = ["g++", "-O2", "-o", EXE, os.path.join(CSRC, "engine_main.cpp"), "-L" + HERE, "-lbrrr", "-Wl,-rpath,$ORIGIN"]
-    r = subprocess.run(cmd, capture_output=True, text=True)
-    if r.returncode != 0:
-        raise RuntimeError(f"link of brrr_engine failed:\n{r.stdout}\n{r.stderr}")
-    return LIB
+    if out == LIB:
+        # the command-line front end (reference binary's arguments and protocol), linked against the library
+        cmd = ["g++", "-O2", "-o", EXE, os.path.join(CSRC, "engine_main.cpp"), "-L" + HERE, "-lbrrr", "-Wl,-rpath,$ORIGIN"]
+        r = subprocess.run(cmd, capture_output=True, text=True)
+        if r.returncode != 0:
+            raise RuntimeError(f"link of brrr_engine failed:\n{r.stdout}\n{r.stderr}")
+    return out
+
+
+def build_hooks(force=False):
+    """The test-hook build of the library (libbrrr_hooks.so, -DBRRR_TEST_HOOKS)."""
+    return build(force=force, defines=("BRRR_TEST_HOOKS",), out=HOOKS_LIB)
 
 
 if __name__ == "__main__":
     print(build(force="--force" in sys.argv, verbose="--verbose" in sys.argv))
+    if "--hooks" in sys.argv:
+        print(build_hooks(force="--force" in sys.argv))

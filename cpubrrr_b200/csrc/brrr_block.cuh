@@ -157,11 +157,19 @@ __device__ __forceinline__ void block_norm_quant_staged(const float *norm_w, con
 // Every thread ranks the experts it owns against all others in shared memory (no shuffles, one
 // global round trip).  Used identically by every kernel that needs the speculative expert set
 // (the set comes from an order-free router estimate; correctness never depends on it).
-// sabotage: test hook that replaces the last pick on every third position.
+// Builds with BRRR_TEST_HOOKS only: when the state's test_hooks word has bit 0 set, the last pick is
+// replaced on every third position (the tests use it to force a missed speculation).
 // Block-wide; ends with sel[] written but not yet synchronised.  lg: ne floats of scratch.
-__device__ __forceinline__ void block_spec_select(const float *est, int ne, int topk, const uint32_t *pos_ptr, int sabotage,
+__device__ __forceinline__ void block_spec_select(const float *est, int ne, int topk, const DevState *state,
                                                   float *lg, int *sel, int tid, int nthreads) {
-    const uint32_t pos = (sabotage && pos_ptr) ? *pos_ptr : 0u;
+#ifdef BRRR_TEST_HOOKS
+    const bool sabotage = state && (state->test_hooks & 1u);
+    const uint32_t pos = sabotage ? state->pos : 0u;
+#else
+    constexpr bool sabotage = false;
+    constexpr uint32_t pos = 0u;
+    (void)state;
+#endif
     for (int e = tid; e < ne; e += nthreads) lg[e] = __ldcg(est + e);
     __syncthreads();
     for (int e = tid; e < ne; e += nthreads) {
@@ -178,8 +186,15 @@ __device__ __forceinline__ void block_spec_select(const float *est, int ne, int 
 // The same selection for ne <= 32 inside one warp, without shared memory or block-wide barriers:
 // returns the expert of rank `want` (what block_spec_select would leave in sel[want]).  All 32
 // lanes must call it.
-__device__ __forceinline__ int warp_spec_expert(const float *est, int ne, int topk, const uint32_t *pos_ptr, int sabotage, int want, int lane) {
-    const uint32_t pos = (sabotage && pos_ptr) ? *pos_ptr : 0u;
+__device__ __forceinline__ int warp_spec_expert(const float *est, int ne, int topk, const DevState *state, int want, int lane) {
+#ifdef BRRR_TEST_HOOKS
+    const bool sabotage = state && (state->test_hooks & 1u);
+    const uint32_t pos = sabotage ? state->pos : 0u;
+#else
+    constexpr bool sabotage = false;
+    constexpr uint32_t pos = 0u;
+    (void)state;
+#endif
     const float v = lane < ne ? __ldcg(est + lane) : 0.0f;
     int rank = 0;
 #pragma unroll 8

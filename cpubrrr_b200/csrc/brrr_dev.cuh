@@ -125,6 +125,9 @@ struct MxDev {
 __host__ __device__ __forceinline__ size_t mx_bytes(int rows, int blocks) { return (size_t)(rows / 16) * (blocks / 2) * MX_UNIT; }
 __host__ __device__ __forceinline__ size_t mx_unit_off(int urow, int pair, int np) { return ((size_t)urow * np + pair) * MX_UNIT; }
 
+// Values of DevState.err: a bounded wait on a bulk copy, or on a word another kernel publishes, ran out.
+enum { DEV_ERR_NONE = 0, DEV_ERR_COPY_TIMEOUT = 1, DEV_ERR_PEER_TIMEOUT = 2 };
+
 // Device-resident decode state: the token and position of the step being run, the running
 // argmax of the vocabulary projection, the ring of emitted tokens and a sticky error word.
 struct DevState {
@@ -138,14 +141,16 @@ struct DevState {
     uint32_t hint_done;            // CTA arrival counter of the routing-hint kernel
     uint32_t router_seq;           // exact-router launches that have published their routing (speculative step)
     uint32_t fold_seq;             // fold launches that have consumed one
-    uint32_t pad[1];
+    uint32_t test_hooks;           // read by BRRR_TEST_HOOKS builds only: bit 0 = spoil the routing estimate on every third position,
+                                   // bit 1 = the exact router does not publish its routing (the fold's bounded wait runs out)
     uint32_t out[BRRR_MAXSEQ];
     long long stamps[256];          // optional in-kernel clock stamps (timeline builds only)
     // routing of the exact router, published for a consumer that runs beside it: word k = (router_seq << 32) | top[k],
     // word 8 + k = (router_seq << 32) | bits of wts[k]; every word validates itself, so no fence is needed
     unsigned long long route_pub[16];
 };
-#ifdef BRRR_TIMELINE
+// In-kernel clock stamps: BRRR_TEST_HOOKS builds only (timeline of one step, read back by brrr_debug_stamps).
+#ifdef BRRR_TEST_HOOKS
 __device__ __forceinline__ unsigned long long brrr_gtime() { unsigned long long t; asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t)); return t; }
 // wall-clock (ns) marks: END = latest finish over all CTAs of a kernel, GO = CTA 0 released from its dependency wait
 #define BRRR_GT_END(state, i) do { if ((state) && threadIdx.x == 0) atomicMax((unsigned long long *)&(state)->stamps[i], brrr_gtime()); } while (0)

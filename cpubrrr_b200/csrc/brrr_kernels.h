@@ -69,13 +69,13 @@ void launch_mx_gemv(MxDev m, int row0, int nrows, const int8_t *xq, const float 
 cudaError_t launch_gate_up(MxDev gate, MxDev up, const float *gate_b, const float *up_b, const int32_t *top, int topk, int d,
                            const float *x_f32, const float *norm_w, float eps, const int8_t *xq, const float *xs,
                            int8_t *hq, float *hs, float *gu, DevState *state, bool pdl, cudaStream_t st,
-                           const float *est = nullptr, int ne = 0, int sabotage = 0, int e_lo = 0, int e_cnt = 1 << 30);
+                           const float *est = nullptr, int ne = 0, int e_lo = 0, int e_cnt = 1 << 30);
 // e_lo, e_cnt: the matrices hold experts [e_lo, e_lo + e_cnt) only (biases stay indexed by the
 // global expert id); CTAs of slots whose expert lives elsewhere return at once.
 // est (nullable): slot s of hq/hs belongs to the s-th largest of the router estimate est[0..ne)
 // rather than to top[s]; a step whose
 // exact experts are not all among them is flagged in state->spec_fail_step.
-cudaError_t launch_down_combine(MxDev down, const float *down_b, const int32_t *top, const float *wts, const float *est, int ne, int sabotage,
+cudaError_t launch_down_combine(MxDev down, const float *down_b, const int32_t *top, const float *wts, const float *est, int ne,
                                 int topk, int d, const int8_t *hq, const float *hs, float *x, DevState *state, bool pdl, cudaStream_t st);
 
 // ---- single-token expert matvecs on the tensor cores in native fp4 (kernels_mxt.cu)
@@ -96,23 +96,23 @@ void launch_xt_bimg(const int8_t *xq, int nb, uint8_t *bimg, cudaStream_t st);
 // same results, bit for bit, as launch_gate_up / launch_down_combine on the same Q8 activation;
 // himg: [topk][blocks / 2][768] operand images of h for launch_down_t
 cudaError_t launch_gate_up_t(MxtDev gu, const float *gate_b, const float *up_b, const int32_t *top, const float *est, int ne, int topk,
-                             int sabotage, int d, const uint8_t *ximg, const float *xs, int8_t *hq, float *hs, uint8_t *himg, DevState *state,
+                             int d, const uint8_t *ximg, const float *xs, int8_t *hq, float *hs, uint8_t *himg, DevState *state,
                              bool pdl, cudaStream_t st);
 // part: [topk][tiles_per_expert * 128] floats of scratch; counter: [tiles_per_expert] words, zero before the first launch.
 // wts != nullptr (exact routing in top/wts, est == nullptr): the last CTA of a row tile folds it onto x.
 // wts == nullptr: slot s is the s-th largest entry of est (or top[s]); only part[] is written and
 // launch_down_fold finishes the step once the exact routing is there.
-cudaError_t launch_down_fold(const int32_t *top, const float *wts, const float *est, int ne, int topk, int sabotage, int d, const float *part,
+cudaError_t launch_down_fold(const int32_t *top, const float *wts, const float *est, int ne, int topk, int d, const float *part,
                              const float *down_b, float *x, DevState *state, bool pdl, cudaStream_t st);
 // The fold for a step whose exact router runs on another stream: one CTA waits (bounded) until
 // *router_seq == *fold_seq + 1, folds as launch_down_fold, then RMS-normalises the new residual with
 // next_norm_w and writes its Q8 image (nq natural int8 order, ns block scales) for the projection
 // that follows, and increments *fold_seq.  next_norm_w == nullptr: fold only.
-cudaError_t launch_fold_norm(const int32_t *top, const float *wts, const float *est, int ne, int topk, int sabotage, int d, const float *part,
+cudaError_t launch_fold_norm(const int32_t *top, const float *wts, const float *est, int ne, int topk, int d, const float *part,
                              const float *down_b, float *x, const float *next_norm_w, float eps, int8_t *nq, float *ns,
                              uint32_t *router_seq, uint32_t *fold_seq, DevState *state, bool pdl, cudaStream_t st);
 cudaError_t launch_down_t(MxtDev down, const float *down_b, const int32_t *top, const float *wts, const float *est, int ne, int topk,
-                          int sabotage, int d, const uint8_t *himg, const float *hs, float *x, float *part, uint32_t *counter, DevState *state,
+                          int d, const uint8_t *himg, const float *hs, float *x, float *part, uint32_t *counter, DevState *state,
                           bool pdl, cudaStream_t st);
 
 // ---- token-tile matmul on tcgen05 tensor cores (kernels_tile.cu): y[t][r] = row (row0 + r) . activation t,

@@ -53,7 +53,6 @@ __device__ __forceinline__ bool mbar_test_wait(uint64_t *bar, uint32_t parity) {
 }
 
 constexpr long long WAIT_CYCLES = 2000000000ll;      // about one second of SM clock
-enum { DEV_ERR_NONE = 0, DEV_ERR_COPY_TIMEOUT = 1, DEV_ERR_PEER_TIMEOUT = 2 };
 
 // Bounded waiting on copy barriers.  A wait that exceeds WAIT_CYCLES records the error once in
 // the device state and marks the thread dead: every later wait returns at once, so a lost copy
@@ -105,6 +104,20 @@ struct Waiter {
 // next kernel starts only after the kernel before this one has finished.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+// Opt a kernel in to `bytes` of dynamic shared memory, once per kernel and device: the attribute
+// belongs to the device's copy of the kernel, and one process may open models on several GPUs.
+// done_mask: a static word of the caller, one bit per device.
+template <typename K>
+inline cudaError_t smem_optin(K kern, int bytes, unsigned long long &done_mask) {
+    int dev = 0;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return e;
+    if (dev >= 0 && dev < 64 && ((done_mask >> dev) & 1ull)) return cudaSuccess;
+    e = cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, bytes);
+    if (e == cudaSuccess && dev >= 0 && dev < 64) done_mask |= 1ull << dev;
+    return e;
+}
 
 template <typename... KArgs, typename... Args>
 inline cudaError_t launch_k(void (*kern)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t st, bool pdl, Args... args) {

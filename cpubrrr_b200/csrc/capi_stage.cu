@@ -110,13 +110,18 @@ extern "C" int brrr_mx_matmul_tile(const brrr_mxmat *w, int row0, int nrows, con
 
 extern "C" int brrr_router_topk(const float *d_w, const float *d_b, const float *d_xn, int ne, int d, int topk,
                                 float *d_logits, int32_t *d_top, float *d_wts, void *stream) {
-    if (!d_w || !d_xn || !d_logits || !d_top || !d_wts || ne <= 0 || d <= 0 || d > 8192 || topk <= 0 || topk > 8 || topk > ne) return BRRR_ERR_ARG;
-    static unsigned int *counter = nullptr;   // arrival counter of the router CTAs (self-resetting)
-    if (!counter) {
-        if (cudaMalloc(&counter, sizeof(unsigned int)) != cudaSuccess) return BRRR_ERR_NOMEM;
-        if (cudaMemset(counter, 0, sizeof(unsigned int)) != cudaSuccess) return BRRR_ERR_CUDA;
-    }
+    if (!d_w || !d_xn || !d_logits || !d_top || !d_wts || ne <= 0 || d <= 0 || topk <= 0 || topk > 8 || topk > ne) return BRRR_ERR_ARG;
+    if (ne > 256 || d > 4096) return BRRR_ERR_RANGE;      // the top-k keeps 8 experts per lane; d floats of x and of norm weights share the CTA's shared memory with the tile ring
     if (d % 64) return BRRR_ERR_ARG;
+    // arrival counter of the router CTAs (self-resetting), one per device
+    static unsigned int *counters[64] = {};
+    int dev = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return BRRR_ERR_CUDA;
+    if (!counters[dev]) {
+        if (cudaMalloc(&counters[dev], sizeof(unsigned int)) != cudaSuccess) return BRRR_ERR_NOMEM;
+        if (cudaMemset(counters[dev], 0, sizeof(unsigned int)) != cudaSuccess) return BRRR_ERR_CUDA;
+    }
+    unsigned int *counter = counters[dev];
     // stage-level call: re-lay the natural [ne][d] matrix into the tiled form first
     float *wt = nullptr;
     if (cudaMalloc(&wt, router_packed_floats(ne, d) * sizeof(float)) != cudaSuccess) return BRRR_ERR_NOMEM;
@@ -168,7 +173,7 @@ extern "C" int brrr_fold_norm(const int32_t *d_top, const float *d_wts, int topk
     if (cudaMemsetAsync(state, 0, sizeof(DevState), st) != cudaSuccess) rc = BRRR_ERR_CUDA;
     // wait_for_router: the kernel polls for routing words tagged 1; nobody publishes them here
     if (rc == BRRR_OK &&
-        launch_fold_norm(d_top, d_wts, nullptr, 0, topk, 0, d, d_part, d_down_b, d_x, d_norm_w, eps, d_q, d_s, wait_for_router ? &state->router_seq : nullptr,
+        launch_fold_norm(d_top, d_wts, nullptr, 0, topk, d, d_part, d_down_b, d_x, d_norm_w, eps, d_q, d_s, wait_for_router ? &state->router_seq : nullptr,
                          wait_for_router ? &state->fold_seq : nullptr, state, false, st) != cudaSuccess)
         rc = BRRR_ERR_CUDA;
     uint32_t err = 0;

@@ -358,15 +358,23 @@ extern "C" int brrr_cli_main(int argc, char **argv) {
     int rc = 0;
     if (prompt == "--serve") {
         fprintf(stderr, "[READY]\n");
-        char line[1 << 16], ptext[1 << 16];
-        while (fgets(line, sizeof line, stdin)) {
+        // Temperature and random state belong to the process, as the reference's TEMP_MILLI /
+        // RNG_STATE globals (src/bin/engine_gpt2.rs:1456-1466): a bare-prompt line after a
+        // temp/seed/ngen/prompt line keeps that line's temperature and continues its random stream.
+        uint32_t temp_milli = 0;
+        char *line = nullptr;
+        size_t cap = 0;
+        std::vector<char> ptext;
+        ssize_t got;
+        while ((got = getline(&line, &cap, stdin)) >= 0) {       // whole lines, whatever their length
             float temp = 0.0f; uint64_t seed = 0; uint32_t ngen = 0;
-            int form = brrr_serve_parse(line, &temp, &seed, &ngen, ptext, sizeof ptext);
+            ptext.assign((size_t)got + 2, 0);
+            int form = brrr_serve_parse(line, &temp, &seed, &ngen, ptext.data(), ptext.size());
             if (form < 0 || ptext[0] == 0) continue;
-            uint32_t temp_milli = 0;
             if (form == 1) { temp_milli = (uint32_t)(temp * 1000.0f); rng = brrr_rng_seed(seed); }
-            if (run(ptext, form == 1 ? ngen : 256, temp_milli, true) != BRRR_OK) { rc = 1; break; }
+            if (run(ptext.data(), form == 1 ? ngen : 256, temp_milli, true) != BRRR_OK) { rc = 1; break; }
         }
+        free(line);
     } else {
         uint32_t ngen = argc > 4 ? (uint32_t)strtoul(argv[4], nullptr, 10) : 96;
         rc = run(prompt, ngen ? ngen : 96, 0, false) == BRRR_OK ? 0 : 1;

@@ -217,11 +217,10 @@ cudaError_t launch_attn_decode(const float *qkv, float *kc, float *vc, const flo
                                const DevState *state, int pos_val, int window, float *ao, int8_t *aq, float *as,
                                DevState *err_state, bool pdl, cudaStream_t st, int pos_off) {
     AttnArgs a{qkv, kc, vc, rope, sinks, nh, nkv, state, pos_val, window, pos_off, ao, aq, as, err_state};
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(attn_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)attn_smem());
+    static unsigned long long configured = 0;      // one bit per device
+    {
+        cudaError_t e = smem_optin(attn_decode_kernel, (int)attn_smem(), configured);
         if (e != cudaSuccess) return e;
-        configured = true;
     }
     return launch_k(attn_decode_kernel, dim3(nh), dim3(AT_THREADS), attn_smem(), st, pdl, a);
 }

@@ -196,11 +196,10 @@ cudaError_t launch_down_ep(MxDev down, const float *down_b, const int32_t *top, 
     a.ch = sh.ch; a.stages = sh.stages;
     size_t per = (size_t)nb * 4 * 8 + (size_t)nb * 4;
     size_t smem = (size_t)topk * a.ch * MX_UNIT * a.stages + per * topk + (size_t)topk * 16 * 4 + (size_t)a.stages * 8 + 8;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(down_ep_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    static unsigned long long configured = 0;      // one bit per device
+    {
+        cudaError_t e = smem_optin(down_ep_kernel, 200 * 1024, configured);
         if (e != cudaSuccess) return e;
-        configured = true;
     }
     return launch_k(down_ep_kernel, dim3(d / 16), dim3(topk * 64), smem, st, pdl, a);
 }

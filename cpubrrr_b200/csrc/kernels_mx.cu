@@ -105,7 +105,7 @@ struct GateUpArgs {
     DevState *state;
     int ch, stages;
     const float *est;        // nullable: router estimate; the expert set is its top-k instead of top[]
-    int ne, topk, sabotage;
+    int ne, topk;
     int e_lo, e_cnt;         // experts held by gate/up: [e_lo, e_lo + e_cnt)
 };
 
@@ -162,7 +162,7 @@ __global__ void __launch_bounds__(256) gate_up_kernel(GateUpArgs a) {
         }
     }
     if (a.est) {
-        block_spec_select(a.est, a.ne, a.topk, a.state ? &a.state->pos : nullptr, a.sabotage, lg, sel, tid, 256);
+        block_spec_select(a.est, a.ne, a.topk, a.state, lg, sel, tid, 256);
         __syncthreads();
     }
     BRRR_STAMP(a.state, 102);
@@ -227,10 +227,10 @@ __global__ void __launch_bounds__(256) gate_up_kernel(GateUpArgs a) {
 cudaError_t launch_gate_up(MxDev gate, MxDev up, const float *gate_b, const float *up_b, const int32_t *top, int topk, int d,
                            const float *x_f32, const float *norm_w, float eps, const int8_t *xq, const float *xs,
                            int8_t *hq, float *hs, float *gu, DevState *state, bool pdl, cudaStream_t st,
-                           const float *est, int ne, int sabotage, int e_lo, int e_cnt) {
+                           const float *est, int ne, int e_lo, int e_cnt) {
     GateUpArgs a{};
     a.e_lo = e_lo; a.e_cnt = e_cnt;
-    a.est = est; a.ne = ne; a.topk = topk; a.sabotage = sabotage;
+    a.est = est; a.ne = ne; a.topk = topk;
     a.gate = gate; a.up = up; a.gate_b = gate_b; a.up_b = up_b; a.top = top; a.d = d;
     a.x_f32 = x_f32; a.norm_w = norm_w; a.eps = eps; a.xq = xq; a.xs = xs; a.hq = hq; a.hs = hs; a.gu = gu; a.state = state;
     const int nb = gate.blocks, np = nb / 2;
@@ -240,11 +240,10 @@ cudaError_t launch_gate_up(MxDev gate, MxDev up, const float *gate_b, const floa
     if (np > 8) { s.ch = 8; int nch = (np + 7) / 8; s.stages = nch < 3 ? nch : 3; }
     a.ch = s.ch; a.stages = s.stages;
     size_t smem = (size_t)4 * a.ch * MX_UNIT * a.stages + (size_t)nb * 4 * 8 + (size_t)nb * 4 + (x_f32 ? (size_t)d * 4 : 0) + 8 + (size_t)a.stages * 8;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gate_up_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    static unsigned long long configured = 0;      // one bit per device
+    {
+        cudaError_t e = smem_optin(gate_up_kernel, 200 * 1024, configured);
         if (e != cudaSuccess) return e;
-        configured = true;
     }
     return launch_k(gate_up_kernel, dim3(d / 32, topk), dim3(256), smem, st, pdl, a);
 }
@@ -259,7 +258,7 @@ struct DownArgs {
     const int32_t *top;
     const float *wts;
     const float *est;          // nullable: router estimate whose top-k the hq/hs slots were computed for
-    int ne, sabotage;
+    int ne;
     int topk, d;
     const int8_t *hq;
     const float *hs;
@@ -321,7 +320,7 @@ __global__ void __launch_bounds__(512) down_combine_kernel(DownArgs a) {
     if (a.est) {
         __shared__ int sel[8];
         __shared__ float lg[256];
-        block_spec_select(a.est, a.ne, a.topk, a.state ? &a.state->pos : nullptr, a.sabotage, lg, sel, tid, nthreads);
+        block_spec_select(a.est, a.ne, a.topk, a.state, lg, sel, tid, nthreads);
         __syncthreads();
         slot = -1;
         const int want = a.top[ei];
@@ -366,20 +365,19 @@ __global__ void __launch_bounds__(512) down_combine_kernel(DownArgs a) {
     (void)nthreads;
 }
 
-cudaError_t launch_down_combine(MxDev down, const float *down_b, const int32_t *top, const float *wts, const float *est, int ne, int sabotage,
+cudaError_t launch_down_combine(MxDev down, const float *down_b, const int32_t *top, const float *wts, const float *est, int ne,
                                 int topk, int d, const int8_t *hq, const float *hs, float *x, DevState *state, bool pdl, cudaStream_t st) {
     DownArgs a{};
-    a.down = down; a.down_b = down_b; a.top = top; a.wts = wts; a.est = est; a.ne = ne; a.sabotage = sabotage; a.topk = topk; a.d = d; a.hq = hq; a.hs = hs; a.x = x; a.state = state;
+    a.down = down; a.down_b = down_b; a.top = top; a.wts = wts; a.est = est; a.ne = ne; a.topk = topk; a.d = d; a.hq = hq; a.hs = hs; a.x = x; a.state = state;
     const int nb = down.blocks, np = nb / 2;
     MxLaunchShape s = mx_shape(np, topk, 80 * 1024);
     a.ch = s.ch; a.stages = s.stages;
     size_t per = (size_t)nb * 4 * 8 + (size_t)nb * 4;
     size_t smem = (size_t)topk * a.ch * MX_UNIT * a.stages + per * topk + (size_t)topk * 16 * 4 + (size_t)a.stages * 8 + 8;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(down_combine_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    static unsigned long long configured = 0;      // one bit per device
+    {
+        cudaError_t e = smem_optin(down_combine_kernel, 200 * 1024, configured);
         if (e != cudaSuccess) return e;
-        configured = true;
     }
     return launch_k(down_combine_kernel, dim3(d / 16), dim3(topk * 64), smem, st, pdl, a);
 }

@@ -47,7 +47,7 @@ constexpr int XT_REGIONS = 2;
 constexpr uint32_t XT_TMEM_COLS = 256;   // 2 regions + 64 columns of unit scale factors
 constexpr int XT_SF_COL = XT_REGIONS * XT_REGION_COLS;
 constexpr int XT_THREADS = 192;
-#ifdef BRRR_TIMELINE
+#ifdef BRRR_TEST_HOOKS
 #define XT_T0() long long xt_t0_ = clock64()
 #define XT_ACC(v) do { long long xt_t1_ = clock64(); (v) += xt_t1_ - xt_t0_; xt_t0_ = xt_t1_; } while (0)
 #define XT_STAMP(state, i) do { if ((state) && blockIdx.x == BRRR_STAMP_BX && blockIdx.y == 0) (state)->stamps[i] = clock64(); } while (0)
@@ -173,7 +173,7 @@ struct XtArgs {
     const int32_t *top;         // exact routing (used when est == nullptr)
     const float *wts;           // down: nullable, see launch_down_t
     const float *est;           // nullable: router estimate; slot s belongs to its s-th largest entry
-    int ne, topk, sabotage, d;
+    int ne, topk, d;
     const uint8_t *bimg;        // operand image of the activation: gate/up [np][768]; down [slot][np][768]
     const float *xs;            // its block scales:                gate/up [blocks];   down [slot][blocks]
     int8_t *hq;                 // gate/up outputs: Q8 of h per slot, its scales, its operand image
@@ -284,7 +284,7 @@ __global__ void __launch_bounds__(XT_THREADS) xt_expert_kernel(XtArgs a) {
     const unsigned char *src = nullptr;
     auto route_and_start = [&]() {
         if (a.est) {
-            block_spec_select(a.est, a.ne, a.topk, a.state ? &a.state->pos : nullptr, a.sabotage, lg, sel, tid, XT_THREADS);
+            block_spec_select(a.est, a.ne, a.topk, a.state, lg, sel, tid, XT_THREADS);
             __syncthreads();
             e = sel[ei];
         } else e = a.top[ei];
@@ -370,9 +370,9 @@ __global__ void __launch_bounds__(XT_THREADS) xt_expert_kernel(XtArgs a) {
         int s = 0, reg = 0, left = np;
         uint32_t spar = 0, dpar = 0;
         const float *xsp = sh.xsc;
-#pragma unroll 1
         long long tw_full = 0, tw_sc = 0, tw_d = 0, tw_ld = 0, tw_math = 0;
         (void)tw_full; (void)tw_sc; (void)tw_d; (void)tw_ld; (void)tw_math;
+#pragma unroll 1
         for (int r = 0; r < nchunks; r++) {
             const int cnt = left < XT_CH ? left : XT_CH;
             XT_T0();
@@ -412,7 +412,7 @@ __global__ void __launch_bounds__(XT_THREADS) xt_expert_kernel(XtArgs a) {
             if (r < 12) BRRR_STAMP(a.state, SB + 4 + r);
         }
         BRRR_STAMP(a.state, SB + 16);
-#ifdef BRRR_TIMELINE
+#ifdef BRRR_TEST_HOOKS
         if (a.state && tid == 0 && blockIdx.x == BRRR_STAMP_BX && blockIdx.y == 0) {
             long long *o = a.state->stamps + (DOWN ? 205 : 200);
             o[0] = tw_full; o[1] = tw_sc; o[2] = tw_d; o[3] = tw_ld; o[4] = tw_math;
@@ -468,7 +468,7 @@ __global__ void __launch_bounds__(XT_THREADS) xt_expert_kernel(XtArgs a) {
 struct FoldArgs {
     const int32_t *top;
     const float *wts, *est;
-    int ne, topk, sabotage, d, dpad;
+    int ne, topk, d, dpad;
     const float *part, *down_b;
     float *x;
     DevState *state;
@@ -484,7 +484,7 @@ __global__ void __launch_bounds__(128) xt_fold_kernel(FoldArgs a) {
     BRRR_GT_GO(a.state, 239);
     pdl_trigger();
     if (a.est) {
-        block_spec_select(a.est, a.ne, a.topk, a.state ? &a.state->pos : nullptr, a.sabotage, lg, sel, tid, 128);
+        block_spec_select(a.est, a.ne, a.topk, a.state, lg, sel, tid, 128);
         __syncthreads();
     }
     if (tid < a.topk) {
@@ -552,7 +552,7 @@ __global__ void __launch_bounds__(FN_THREADS) xt_fold_norm_kernel(FoldNormArgs a
     const float4 zero4 = make_float4(0.f, 0.f, 0.f, 0.f);
     float4 xr = live ? reinterpret_cast<const float4 *>(a.f.x)[tid] : zero4, pb[MAXS], ps[MAXS];
     if (a.f.est) {
-        block_spec_select(a.f.est, a.f.ne, topk, a.f.state ? &a.f.state->pos : nullptr, a.f.sabotage, lg, sel, tid, FN_THREADS);
+        block_spec_select(a.f.est, a.f.ne, topk, a.f.state, lg, sel, tid, FN_THREADS);
         __syncthreads();
 #pragma unroll
         for (int s = 0; s < MAXS; s++) pb[s] = (live && s < topk) ? reinterpret_cast<const float4 *>(a.f.down_b + (size_t)sel[s] * d)[tid] : zero4;
@@ -586,8 +586,13 @@ __global__ void __launch_bounds__(FN_THREADS) xt_fold_norm_kernel(FoldNormArgs a
                         ok = (uint32_t)(v >> 32) == want_seq;
                         payload = (uint32_t)v;
                     }
-                } while (!ok && clock64() - t0 < WAIT_CYCLES);
-                if (!ok) atomicCAS(&a.f.state->err, (uint32_t)DEV_ERR_NONE, (uint32_t)DEV_ERR_PEER_TIMEOUT);
+                    // give up at once when the error word is already set (an earlier wait of this step ran out)
+                } while (!ok && clock64() - t0 < WAIT_CYCLES && *reinterpret_cast<volatile uint32_t *>(&a.f.state->err) == 0u);
+                if (!ok) {
+                    // the step is void from here: record where, so that the host can run it again without speculation
+                    atomicCAS(&a.f.state->err, (uint32_t)DEV_ERR_NONE, (uint32_t)DEV_ERR_PEER_TIMEOUT);
+                    atomicMin(&a.f.state->spec_fail_step, a.f.state->n_out);
+                }
             }
         } else if (tid < 16 && (tid & 7) < topk) {
             payload = tid < 8 ? (uint32_t)__ldcg(a.f.top + tid) : __float_as_uint(__ldcg(a.f.wts + (tid - 8)));
@@ -673,30 +678,29 @@ void launch_xt_bimg(const int8_t *xq, int nb, uint8_t *bimg, cudaStream_t st) {
 }
 
 cudaError_t launch_gate_up_t(MxtDev gu, const float *gate_b, const float *up_b, const int32_t *top, const float *est, int ne, int topk,
-                             int sabotage, int d, const uint8_t *ximg, const float *xs, int8_t *hq, float *hs, uint8_t *himg, DevState *state,
+                             int d, const uint8_t *ximg, const float *xs, int8_t *hq, float *hs, uint8_t *himg, DevState *state,
                              bool pdl, cudaStream_t st) {
     XtArgs a{};
-    a.w = gu; a.bias_a = gate_b; a.bias_b = up_b; a.top = top; a.est = est; a.ne = ne; a.topk = topk; a.sabotage = sabotage; a.d = d;
+    a.w = gu; a.bias_a = gate_b; a.bias_b = up_b; a.top = top; a.est = est; a.ne = ne; a.topk = topk; a.d = d;
     a.bimg = ximg; a.xs = xs; a.hq = hq; a.hs = hs; a.himg = himg; a.state = state;
     const int nchunks = (gu.np + XT_CH - 1) / XT_CH;
 #ifndef XT_GU_STAGES
 #define XT_GU_STAGES 4
 #endif
     a.stages = nchunks < XT_GU_STAGES ? nchunks : XT_GU_STAGES;            // two CTAs per SM at the 20b shape
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(xt_expert_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    static unsigned long long configured = 0;      // one bit per device
+    {
+        cudaError_t e = smem_optin(xt_expert_kernel<false>, 200 * 1024, configured);
         if (e != cudaSuccess) return e;
-        configured = true;
     }
     return launch_k(xt_expert_kernel<false>, dim3(gu.tiles_per_expert, topk), dim3(XT_THREADS), xt_smem_bytes(gu.np, a.stages), st, pdl, a);
 }
 
 cudaError_t launch_down_t(MxtDev down, const float *down_b, const int32_t *top, const float *wts, const float *est, int ne, int topk,
-                          int sabotage, int d, const uint8_t *himg, const float *hs, float *x, float *part, uint32_t *counter, DevState *state,
+                          int d, const uint8_t *himg, const float *hs, float *x, float *part, uint32_t *counter, DevState *state,
                           bool pdl, cudaStream_t st) {
     XtArgs a{};
-    a.w = down; a.bias_a = down_b; a.top = top; a.wts = wts; a.est = est; a.ne = ne; a.topk = topk; a.sabotage = sabotage; a.d = d;
+    a.w = down; a.bias_a = down_b; a.top = top; a.wts = wts; a.est = est; a.ne = ne; a.topk = topk; a.d = d;
     a.bimg = himg; a.xs = hs; a.x = x; a.part = part; a.counter = counter; a.state = state;
     const int nchunks = (down.np + XT_CH - 1) / XT_CH;
     // the same footprint as a gate/up CTA: a down CTA fits beside a running gate/up CTA, sets up and
@@ -706,29 +710,28 @@ cudaError_t launch_down_t(MxtDev down, const float *down_b, const int32_t *top, 
 #define XT_DOWN_STAGES 4
 #endif
     a.stages = nchunks < XT_DOWN_STAGES ? nchunks : XT_DOWN_STAGES;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(xt_expert_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, 210 * 1024);
+    static unsigned long long configured = 0;      // one bit per device
+    {
+        cudaError_t e = smem_optin(xt_expert_kernel<true>, 210 * 1024, configured);
         if (e != cudaSuccess) return e;
-        configured = true;
     }
     return launch_k(xt_expert_kernel<true>, dim3(down.tiles_per_expert, topk), dim3(XT_THREADS), xt_smem_bytes(down.np, a.stages), st, pdl, a);
 }
 
-cudaError_t launch_down_fold(const int32_t *top, const float *wts, const float *est, int ne, int topk, int sabotage, int d, const float *part,
+cudaError_t launch_down_fold(const int32_t *top, const float *wts, const float *est, int ne, int topk, int d, const float *part,
                              const float *down_b, float *x, DevState *state, bool pdl, cudaStream_t st) {
     FoldArgs a{};
-    a.top = top; a.wts = wts; a.est = est; a.ne = ne; a.topk = topk; a.sabotage = sabotage; a.d = d; a.dpad = (d + 127) / 128 * 128;
+    a.top = top; a.wts = wts; a.est = est; a.ne = ne; a.topk = topk; a.d = d; a.dpad = (d + 127) / 128 * 128;
     a.part = part; a.down_b = down_b; a.x = x; a.state = state;
     return launch_k(xt_fold_kernel, dim3((d + 127) / 128), dim3(128), 0, st, pdl, a);
 }
 
-cudaError_t launch_fold_norm(const int32_t *top, const float *wts, const float *est, int ne, int topk, int sabotage, int d, const float *part,
+cudaError_t launch_fold_norm(const int32_t *top, const float *wts, const float *est, int ne, int topk, int d, const float *part,
                              const float *down_b, float *x, const float *next_norm_w, float eps, int8_t *nq, float *ns,
                              uint32_t *router_seq, uint32_t *fold_seq, DevState *state, bool pdl, cudaStream_t st) {
     if (d > 4 * FN_THREADS || d % 32 || topk > 8 || (router_seq && !state)) return cudaErrorInvalidValue;
     FoldNormArgs a{};
-    a.f.top = top; a.f.wts = wts; a.f.est = est; a.f.ne = ne; a.f.topk = topk; a.f.sabotage = sabotage; a.f.d = d; a.f.dpad = (d + 127) / 128 * 128;
+    a.f.top = top; a.f.wts = wts; a.f.est = est; a.f.ne = ne; a.f.topk = topk; a.f.d = d; a.f.dpad = (d + 127) / 128 * 128;
     a.f.part = part; a.f.down_b = down_b; a.f.x = x; a.f.state = state;
     a.norm_w = next_norm_w; a.eps = eps; a.nq = nq; a.ns = ns; a.router_seq = router_seq; a.fold_seq = fold_seq;
     const size_t smem = (size_t)d * sizeof(float);

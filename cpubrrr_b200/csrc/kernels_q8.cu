@@ -566,7 +566,8 @@ cudaError_t launch_q8_head(Q8Dev m, const int8_t *xq, const float *xs, float *y,
     const int urows = q8_urows(m.rows);
     const unsigned grid = (unsigned)(urows < 2 * sms ? urows : 2 * sms);
     const size_t smem = stage * a.stages + fixed;
-    cudaError_t e = cudaFuncSetAttribute(q8_head_ring_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 100 * 1024);
+    static unsigned long long configured = 0;      // one bit per device
+    cudaError_t e = smem_optin(q8_head_ring_kernel, 100 * 1024, configured);
     if (e != cudaSuccess) return e;
     return launch_k(q8_head_ring_kernel, dim3(grid), dim3(QH_THREADS), smem, st, pdl, a);
 }
@@ -579,12 +580,11 @@ static size_t q8_smem(const Q8Args &a, bool norm) {
 
 template <int EPI, bool NORM>
 static cudaError_t q8_launch_t(const Q8Args &a, unsigned grid, bool pdl, cudaStream_t st) {
-    static size_t configured = 0;
+    static unsigned long long configured = 0;      // one bit per device
     size_t smem = q8_smem(a, NORM);
-    if (smem > configured) {
-        cudaError_t e = cudaFuncSetAttribute(q8_stream_kernel<EPI, NORM>, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    {
+        cudaError_t e = smem_optin(q8_stream_kernel<EPI, NORM>, 200 * 1024, configured);
         if (e != cudaSuccess) return e;
-        configured = 200 * 1024;
     }
     return launch_k(q8_stream_kernel<EPI, NORM>, dim3(grid), dim3(Q8_THREADS), smem, st, pdl, a);
 }

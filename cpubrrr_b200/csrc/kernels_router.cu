@@ -115,6 +115,9 @@ __device__ __forceinline__ void warp_topk(const RouterArgs &a, const float *lg, 
 // speculative step): sequence-tagged 64-bit copies of the routing this thread has just written.
 // Launches that publish are serialised on one stream, so the sequence word has a single writer.
 __device__ __forceinline__ void publish_route(const RouterArgs &a) {
+#ifdef BRRR_TEST_HOOKS
+    if (a.state && (a.state->test_hooks & 2u)) return;      // test hook: stay silent, the consumer's bounded wait runs out
+#endif
     const uint32_t seq = __ldcg(a.signal) + 1u;
     for (int i = 0; i < a.topk; i++) {
         __stcg(&a.pub[i], ((unsigned long long)seq << 32) | (uint32_t)a.top[i]);
@@ -240,11 +243,10 @@ cudaError_t launch_ffn_in(const float *x_in, const float *norm_w, float eps, int
     RouterArgs a{x_in, norm_w, eps, d, Wt, b, ne, topk, logits, top, wts, counter, state, signal, (signal && state) ? state->route_pub : nullptr};
     if (signal && !state) return cudaErrorInvalidValue;
     size_t smem = (size_t)RT_TILE_FLOATS * 4 * RT_STAGES + (size_t)d * 8 + (size_t)((ne + 3) & ~3) * 4 + RT_STAGES * 16;
-    static bool configured = false;
-    if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(ffn_in_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, 200 * 1024);
+    static unsigned long long configured = 0;      // one bit per device
+    {
+        cudaError_t e = smem_optin(ffn_in_kernel, 200 * 1024, configured);
         if (e != cudaSuccess) return e;
-        configured = true;
     }
     return launch_k(ffn_in_kernel, dim3((ne + 31) / 32, ntok), dim3(RT_THREADS), smem, st, pdl, a);
 }

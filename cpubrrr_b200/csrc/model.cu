@@ -123,7 +123,9 @@ struct brrr_model {
     cudaStream_t side = nullptr;                                     // the exact router runs here, beside gate/up
     cudaEvent_t ev_fork = nullptr, ev_join = nullptr;
     bool use_spec = true;        // start gate/up from a fast router estimate, verify with the exact router
-    int sabotage = 0;            // test hook: make the estimate wrong on every third position
+    uint32_t test_hooks = 0;     // BRRR_TEST_HOOKS builds: copied into DevState.test_hooks (see there)
+    bool spec_off = false;       // a bounded device wait of the speculative step ran out once: plain graphs from then on
+    uint64_t wait_fallbacks = 0; // how often that happened
     float *est = nullptr;        // estimated router logits
     uint32_t run_tok = 0, run_pos = 0;   // arguments of the decode run in flight (for a redo)
     uint64_t spec_redos = 0;
@@ -321,14 +323,14 @@ int enqueue_step(brrr_model *m, bool want, float *trace_dev, int *nlaunch, unsig
             CUL(launch_router_hint(m->x, ly.ffn_norm, c.rms_eps, d, ly.ginp, ly.ginp_b, c.n_expert, topk, m->est, m->xq, m->xs, m->st, pdl, s,
                                    m->use_mxt ? m->ximg : nullptr));
             n++;
-            if (m->use_mxt) CUL(launch_gate_up_t(ly.gu_t, ly.gate_b, ly.up_b, nullptr, m->est, c.n_expert, topk, m->sabotage, d, m->ximg, m->xs,
+            if (m->use_mxt) CUL(launch_gate_up_t(ly.gu_t, ly.gate_b, ly.up_b, nullptr, m->est, c.n_expert, topk, d, m->ximg, m->xs,
                                                  m->hq, m->hs, m->himg, m->st, pdl, s));
             else CUL(launch_gate_up(ly.gate, ly.up, ly.gate_b, ly.up_b, nullptr, topk, d, nullptr, nullptr, c.rms_eps, m->xq, m->xs,
-                                    m->hq, m->hs, nullptr, m->st, pdl, s, m->est, c.n_expert, m->sabotage));
+                                    m->hq, m->hs, nullptr, m->st, pdl, s, m->est, c.n_expert));
             if (m->use_mxt) {
                 // down for the estimated experts as well; only the fold waits for the exact routing
                 n++;
-                CUL(launch_down_t(ly.down_t, ly.down_b, nullptr, nullptr, m->est, c.n_expert, topk, m->sabotage, d, m->himg, m->hs, m->x,
+                CUL(launch_down_t(ly.down_t, ly.down_b, nullptr, nullptr, m->est, c.n_expert, topk, d, m->himg, m->hs, m->x,
                                   m->dpart, m->dcount, m->st, pdl, s));
             }
             if (fused) {
@@ -339,7 +341,7 @@ int enqueue_step(brrr_model *m, bool want, float *trace_dev, int *nlaunch, unsig
                 const bool last = il == c.n_layer - 1;
                 const float *nw = last ? (want ? m->out_norm : nullptr) : m->L[il + 1].attn_norm;
                 n++;
-                CUL(launch_fold_norm(m->top, m->wts, m->est, c.n_expert, topk, m->sabotage, d, m->dpart, ly.down_b, m->x, nw, c.rms_eps,
+                CUL(launch_fold_norm(m->top, m->wts, m->est, c.n_expert, topk, d, m->dpart, ly.down_b, m->x, nw, c.rms_eps,
                                      last ? m->xq : m->nq, last ? m->xs : m->ns, &m->st->router_seq, &m->st->fold_seq, m->st, pdl, s));
                 if (last) CU(cudaStreamWaitEvent(s, m->ev_join, 0));
                 continue;
@@ -348,29 +350,29 @@ int enqueue_step(brrr_model *m, bool want, float *trace_dev, int *nlaunch, unsig
             n++;
             // full dependency on both predecessors: a programmatic launch here was observed to start
             // before the side-stream router had finished
-            if (m->use_mxt) CUL(launch_down_fold(m->top, m->wts, m->est, c.n_expert, topk, m->sabotage, d, m->dpart, ly.down_b, m->x, m->st, false, s));
-            else CUL(launch_down_combine(ly.down, ly.down_b, m->top, m->wts, m->est, c.n_expert, m->sabotage, topk, d, m->hq, m->hs, m->x, m->st, false, s));
+            if (m->use_mxt) CUL(launch_down_fold(m->top, m->wts, m->est, c.n_expert, topk, d, m->dpart, ly.down_b, m->x, m->st, false, s));
+            else CUL(launch_down_combine(ly.down, ly.down_b, m->top, m->wts, m->est, c.n_expert, topk, d, m->hq, m->hs, m->x, m->st, false, s));
         } else if (m->use_mxt && mask != ~0u) {
             // single-stage replays (stage timing) of the kernels the speculative step runs, on the
             // activation and routing the last step left behind
             if (on(ST_ROUTER)) CUL(launch_ffn_in(m->x, ly.ffn_norm, c.rms_eps, d, ly.ginp, ly.ginp_b, c.n_expert, topk, m->rlogits, m->top, m->wts,
                                                  &m->st->router_done, m->st, pdl, s));
-            if (on(ST_GATE_UP)) CUL(launch_gate_up_t(ly.gu_t, ly.gate_b, ly.up_b, m->top, nullptr, 0, topk, 0, d, m->ximg, m->xs, m->hq, m->hs, m->himg,
+            if (on(ST_GATE_UP)) CUL(launch_gate_up_t(ly.gu_t, ly.gate_b, ly.up_b, m->top, nullptr, 0, topk, d, m->ximg, m->xs, m->hq, m->hs, m->himg,
                                                      m->st, pdl, s));
             const bool ff = m->use_spec && m->fused_fold;     // the fused step: down leaves partial sums, a fold kernel finishes
-            if (on(ST_DOWN)) CUL(launch_down_t(ly.down_t, ly.down_b, m->top, ff ? nullptr : m->wts, nullptr, 0, topk, 0, d, m->himg, m->hs, m->x, m->dpart,
+            if (on(ST_DOWN)) CUL(launch_down_t(ly.down_t, ly.down_b, m->top, ff ? nullptr : m->wts, nullptr, 0, topk, d, m->himg, m->hs, m->x, m->dpart,
                                                m->dcount, m->st, pdl, s));
             if (ff && on(ST_FOLD))
-                CUL(launch_fold_norm(m->top, m->wts, nullptr, 0, topk, 0, d, m->dpart, ly.down_b, m->x,
+                CUL(launch_fold_norm(m->top, m->wts, nullptr, 0, topk, d, m->dpart, ly.down_b, m->x,
                                      il + 1 < c.n_layer ? m->L[il + 1].attn_norm : m->out_norm, c.rms_eps, m->nq, m->ns, nullptr, nullptr, m->st, pdl, s));
         } else {
         if (on(ST_ROUTER)) CUL(launch_ffn_in(m->x, ly.ffn_norm, c.rms_eps, d, ly.ginp, ly.ginp_b, c.n_expert, topk, m->rlogits, m->top, m->wts,
                                              &m->st->router_done, m->st, pdl, s));
         if (on(ST_GATE_UP)) CUL(launch_gate_up(ly.gate, ly.up, ly.gate_b, ly.up_b, m->top, topk, d, m->x, ly.ffn_norm, c.rms_eps, nullptr, nullptr,
-                                               m->hq, m->hs, nullptr, m->st, pdl, s, nullptr, 0, 0, m->ep ? m->epc.e_lo : 0,
+                                               m->hq, m->hs, nullptr, m->st, pdl, s, nullptr, 0, m->ep ? m->epc.e_lo : 0,
                                                m->ep ? m->epc.e_cnt : (1 << 30)));
         if (m->ep) { if (on(ST_DOWN)) CUL(launch_down_ep(ly.down, ly.down_b, m->top, m->wts, topk, d, il, m->hq, m->hs, m->x, m->st, m->epc, pdl, s)); }
-        else if (on(ST_DOWN)) CUL(launch_down_combine(ly.down, ly.down_b, m->top, m->wts, nullptr, 0, 0, topk, d, m->hq, m->hs, m->x, m->st, pdl, s));
+        else if (on(ST_DOWN)) CUL(launch_down_combine(ly.down, ly.down_b, m->top, m->wts, nullptr, 0, topk, d, m->hq, m->hs, m->x, m->st, pdl, s));
         }
         if (trace_dev) CU(cudaMemcpyAsync(trace_dev + (size_t)(il + 1) * d, m->x, d * sizeof(float), cudaMemcpyDeviceToDevice, s));
     }
@@ -398,22 +400,29 @@ int capture(brrr_model *m, bool want, cudaGraphExec_t *out, int *nlaunch, unsign
     return BRRR_OK;
 }
 
+// Device state as a fresh model has it.
+int reset_state(brrr_model *m) {
+    CU(cudaMemsetAsync(m->st, 0, sizeof(DevState), m->stream));
+    CU(cudaMemsetAsync(&m->st->spec_fail_step, 0xFF, 4, m->stream));
+    if (m->test_hooks) CU(cudaMemcpyAsync(&m->st->test_hooks, &m->test_hooks, 4, cudaMemcpyHostToDevice, m->stream));
+    return BRRR_OK;
+}
+
 // First step and graph capture (needs every buffer the step touches, peers included).
 int finish_build(brrr_model *m) {
     if (m->ep) m->use_spec = false;    // the routing estimate is not used across ranks
     // one direct (un-captured) step configures every kernel's attributes and validates the launches
+    TRY(reset_state(m));
     TRY(enqueue_step(m, true, nullptr, nullptr));
     CU(cudaStreamSynchronize(m->stream));
-    CU(cudaMemsetAsync(m->st, 0, sizeof(DevState), m->stream));
-    CU(cudaMemsetAsync(&m->st->spec_fail_step, 0xFF, 4, m->stream));
+    TRY(reset_state(m));
     TRY(capture(m, true, &m->g_head_safe, &m->launches_head));
     TRY(capture(m, false, &m->g_nohead_safe, &m->launches_nohead));
     if (m->use_spec) {
         // direct speculative step once (kernel attributes), then capture
         TRY(enqueue_step(m, true, nullptr, nullptr, ~0u, true));
         CU(cudaStreamSynchronize(m->stream));
-        CU(cudaMemsetAsync(m->st, 0, sizeof(DevState), m->stream));
-        CU(cudaMemsetAsync(&m->st->spec_fail_step, 0xFF, 4, m->stream));
+        TRY(reset_state(m));
         TRY(capture(m, true, &m->g_head, &m->launches_head, ~0u, true));
         TRY(capture(m, false, &m->g_nohead, &m->launches_nohead, ~0u, true));
     } else {
@@ -431,7 +440,10 @@ int build_model(brrr_model *m, const Source &src) {
     CU(cudaStreamCreateWithFlags(&m->stream, cudaStreamNonBlocking));
     if (const char *e = getenv("BRRR_NOPDL")) m->use_pdl = !(e[0] && e[0] != '0');
     if (const char *e = getenv("BRRR_NOSPEC")) m->use_spec = !(e[0] && e[0] != '0');
-    if (const char *e = getenv("BRRR_SPEC_SABOTAGE")) m->sabotage = (e[0] && e[0] != '0');
+#ifdef BRRR_TEST_HOOKS
+    if (const char *e = getenv("BRRR_SPEC_SABOTAGE")) if (e[0] && e[0] != '0') m->test_hooks |= 1u;
+    if (const char *e = getenv("BRRR_ROUTER_MUTE")) if (e[0] && e[0] != '0') m->test_hooks |= 2u;
+#endif
     CU(cudaStreamCreateWithFlags(&m->side, cudaStreamNonBlocking));
     CU(cudaEventCreateWithFlags(&m->ev_fork, cudaEventDisableTiming));
     CU(cudaEventCreateWithFlags(&m->ev_join, cudaEventDisableTiming));
@@ -773,12 +785,30 @@ extern "C" uint64_t brrr_model_bytes_per_step(const brrr_model *m, uint32_t pos)
 
 static int run_graph(brrr_model *m, bool want, bool safe = false) {
     if (m->ep && !m->ep_attached) return BRRR_ERR_STATE;
+    safe = safe || m->spec_off;
     cudaGraphExec_t g = safe ? (want ? m->g_head_safe : m->g_nohead_safe) : (want ? m->g_head : m->g_nohead);
     CU(cudaGraphLaunch(g, m->stream));
     return BRRR_OK;
 }
 
 extern "C" uint64_t brrr_model_spec_redos(const brrr_model *m) { return m ? m->spec_redos : 0; }
+extern "C" uint64_t brrr_model_wait_fallbacks(const brrr_model *m) { return m ? m->wait_fallbacks : 0; }
+
+// The fold of the speculative step takes the exact routing from words the router publishes on
+// another branch of the graph; nothing guarantees that the two branches run at the same time, so
+// its bounded wait can run out.  The kernel then flags the step like a missed speculation (error
+// word DEV_ERR_PEER_TIMEOUT, spec_fail_step = the step).  Here: the stream is idle; clear the error,
+// bring the fold's sequence number back in line with the router's, and never speculate again on
+// this model - the caller re-runs the flagged step with the plain graph.  Returns false when the
+// error is not of that kind (the caller reports BRRR_ERR_STATE).
+static bool recover_from_router_wait(brrr_model *m, uint32_t err) {
+    if (err != (uint32_t)DEV_ERR_PEER_TIMEOUT || !m->use_spec || m->spec_off || m->ep) return false;
+    if (cudaMemsetAsync(&m->st->err, 0, 4, m->stream) != cudaSuccess) return false;
+    if (cudaMemcpyAsync(&m->st->fold_seq, &m->st->router_seq, 4, cudaMemcpyDeviceToDevice, m->stream) != cudaSuccess) return false;
+    m->spec_off = true;
+    m->wait_fallbacks++;
+    return true;
+}
 
 extern "C" int brrr_forward(brrr_model *m, uint32_t tok, uint32_t pos, int want, uint32_t *out_tok) {
     if (!m) return BRRR_ERR_ARG;
@@ -789,9 +819,13 @@ extern "C" int brrr_forward(brrr_model *m, uint32_t tok, uint32_t pos, int want,
     TRY(run_graph(m, want != 0));
     CU(cudaMemcpyAsync(m->h_out, m->st, 32, cudaMemcpyDeviceToHost, m->stream));   // tok .. err
     CU(cudaStreamSynchronize(m->stream));
-    if (m->h_out[6] != 0) { snprintf(g_cuda_err, sizeof g_cuda_err, "device wait timed out (code %u)", m->h_out[6]); return BRRR_ERR_STATE; }
+    if (m->h_out[6] != 0 && !recover_from_router_wait(m, m->h_out[6])) {
+        snprintf(g_cuda_err, sizeof g_cuda_err, "device wait timed out (code %u)", m->h_out[6]);
+        return BRRR_ERR_STATE;
+    }
     if (m->h_out[7] != 0xFFFFFFFFu) {
-        // the router estimate missed an expert somewhere in this step: run it again without speculation
+        // the router estimate missed an expert somewhere in this step (or the fold gave up waiting
+        // for the router): run it again without speculation
         m->spec_redos++;
         CU(cudaMemsetAsync(&m->st->spec_fail_step, 0xFF, 4, m->stream));
         CU(cudaMemcpyAsync(m->st, m->h_in, 8, cudaMemcpyHostToDevice, m->stream));
@@ -937,7 +971,10 @@ extern "C" int brrr_decode_wait(brrr_model *m, uint32_t n, uint32_t *out_toks) {
     for (int guard = 0; guard < (int)n + 1; guard++) {
         CU(cudaMemcpyAsync(m->h_in, &m->st->err, 8, cudaMemcpyDeviceToHost, m->stream));   // err, spec_fail_step
         CU(cudaStreamSynchronize(m->stream));
-        if (m->h_in[0] != 0) { snprintf(g_cuda_err, sizeof g_cuda_err, "device wait timed out (code %u)", m->h_in[0]); return BRRR_ERR_STATE; }
+        if (m->h_in[0] != 0 && !recover_from_router_wait(m, m->h_in[0])) {
+            snprintf(g_cuda_err, sizeof g_cuda_err, "device wait timed out (code %u)", m->h_in[0]);
+            return BRRR_ERR_STATE;
+        }
         const uint32_t f = m->h_in[1];
         if (f >= n) break;
         // Step f ran with an expert set the exact router did not confirm: its token and every later
@@ -1009,7 +1046,7 @@ extern "C" int brrr_moe_ffn_step(brrr_model *m, int il, const float *d_xn, float
     cudaStream_t s = m->stream;
     CUL(launch_ffn_in(d_xn, nullptr, c.rms_eps, d, ly.ginp, ly.ginp_b, c.n_expert, topk, m->rlogits, m->top, m->wts, &m->st->router_done, m->st, false, s));
     CUL(launch_gate_up(ly.gate, ly.up, ly.gate_b, ly.up_b, m->top, topk, d, d_xn, nullptr, c.rms_eps, nullptr, nullptr, m->hq, m->hs, nullptr, m->st, false, s));
-    CUL(launch_down_combine(ly.down, ly.down_b, m->top, m->wts, nullptr, 0, 0, topk, d, m->hq, m->hs, d_x, m->st, false, s));
+    CUL(launch_down_combine(ly.down, ly.down_b, m->top, m->wts, nullptr, 0, topk, d, m->hq, m->hs, d_x, m->st, false, s));
     CU(cudaGetLastError());
     if (d_top) CU(cudaMemcpyAsync(d_top, m->top, topk * sizeof(int32_t), cudaMemcpyDeviceToDevice, s));
     if (d_wts) CU(cudaMemcpyAsync(d_wts, m->wts, topk * sizeof(float), cudaMemcpyDeviceToDevice, s));
@@ -1031,8 +1068,8 @@ extern "C" int brrr_moe_ffn_step_tc(brrr_model *m, int il, const float *d_xn, fl
     CUL(launch_ffn_in(d_xn, nullptr, c.rms_eps, d, ly.ginp, ly.ginp_b, c.n_expert, topk, m->rlogits, m->top, m->wts, &m->st->router_done, m->st, false, s));
     launch_quant_q8(d_xn, d, m->xq, m->xs, s);
     launch_xt_bimg(m->xq, d / 32, m->ximg, s);
-    CUL(launch_gate_up_t(ly.gu_t, ly.gate_b, ly.up_b, m->top, nullptr, 0, topk, 0, d, m->ximg, m->xs, m->hq, m->hs, m->himg, m->st, false, s));
-    CUL(launch_down_t(ly.down_t, ly.down_b, m->top, m->wts, nullptr, 0, topk, 0, d, m->himg, m->hs, d_x, m->dpart, m->dcount, m->st, false, s));
+    CUL(launch_gate_up_t(ly.gu_t, ly.gate_b, ly.up_b, m->top, nullptr, 0, topk, d, m->ximg, m->xs, m->hq, m->hs, m->himg, m->st, false, s));
+    CUL(launch_down_t(ly.down_t, ly.down_b, m->top, m->wts, nullptr, 0, topk, d, m->himg, m->hs, d_x, m->dpart, m->dcount, m->st, false, s));
     CU(cudaGetLastError());
     if (d_top) CU(cudaMemcpyAsync(d_top, m->top, topk * sizeof(int32_t), cudaMemcpyDeviceToDevice, s));
     if (d_wts) CU(cudaMemcpyAsync(d_wts, m->wts, topk * sizeof(float), cudaMemcpyDeviceToDevice, s));
@@ -1150,7 +1187,8 @@ extern "C" int brrr_stage_time(brrr_model *m, int stage, uint32_t pos, int reps,
     return BRRR_OK;
 }
 
-// Debug tap: the in-kernel clock stamps of the last step (all zero unless built with BRRR_TIMELINE).
+#ifdef BRRR_TEST_HOOKS
+// Test-hook builds only (not part of the public interface): the in-kernel clock stamps of the last step.
 extern "C" int brrr_debug_stamps(brrr_model *m, long long *out256) {
     if (!m || !out256) return BRRR_ERR_ARG;
     CU(cudaSetDevice(m->device));
@@ -1158,3 +1196,4 @@ extern "C" int brrr_debug_stamps(brrr_model *m, long long *out256) {
     CU(cudaStreamSynchronize(m->stream));
     return BRRR_OK;
 }
+#endif

@@ -123,6 +123,10 @@ class Engine:
     def launches_per_step(self, want=True):
         return lib().brrr_model_launches_per_step(self._h, int(bool(want)))
 
+    def wait_fallbacks(self):
+        """Times a bounded device wait of the speculative step ran out and the model fell back to the plain step (0 or 1)."""
+        return int(lib().brrr_model_wait_fallbacks(self._h))
+
     def spec_redos(self):
         """Steps re-run because the routing estimate missed an expert (performance counter)."""
         return int(lib().brrr_model_spec_redos(self._h))

@@ -111,6 +111,11 @@ int brrr_model_launches_per_step(const brrr_model *m, int want_logits);
  * stream early missed an expert the exact router chose (results are unaffected; this is a
  * performance counter).  No counterpart in the reference. */
 uint64_t brrr_model_spec_redos(const brrr_model *m);
+/* How many times a bounded device wait of the speculative step ran out (the exact router, which
+ * runs on its own branch of the step's graph, had not published its routing within about a
+ * second).  The step concerned was re-run without speculation and the model has used the plain
+ * step since; results are unaffected.  0 or 1.  No counterpart in the reference. */
+uint64_t brrr_model_wait_fallbacks(const brrr_model *m);
 /* Weight + KV bytes one decode step at position `pos` must read in the run-time formats. */
 uint64_t brrr_model_bytes_per_step(const brrr_model *m, uint32_t pos);
 
@@ -125,9 +130,6 @@ int brrr_stage_count(void);
 const char *brrr_stage_name(int stage);
 int brrr_stage_time(brrr_model *m, int stage, uint32_t pos, int reps, float *ms_per_launch, uint64_t *bytes_per_launch, int *launches_per_step);
 
-/* Debug tap: 256 SM-clock stamps recorded inside the kernels of the last step; all zero unless the
- * library was built with -DBRRR_TIMELINE.  No counterpart in the reference. */
-int brrr_debug_stamps(brrr_model *m, long long *out256);
 
 /* ---------------------------------------------------------------- expert parallelism (one process per GPU)
  * Rank r of `world` (<= 8, dividing n_expert) loads the experts [r * n_expert / world, (r + 1) *
