@@ -78,6 +78,18 @@ cudaError_t launch_gate_up(MxDev gate, MxDev up, const float *gate_b, const floa
 cudaError_t launch_down_combine(MxDev down, const float *down_b, const int32_t *top, const float *wts, const float *est, int ne,
                                 int topk, int d, const int8_t *hq, const float *hs, float *x, DevState *state, bool pdl, cudaStream_t st);
 
+// ---- expert parallelism over NVLink peer memory (kernels_ep.cu)
+constexpr int EP_MAX_WORLD = 8;
+struct EpCtx {
+    int rank, world, e_lo, e_cnt;          // experts [e_lo, e_lo + e_cnt) live on this rank
+    uint32_t *epoch;                       // local: number of the step in flight
+    float *xchg[EP_MAX_WORLD];             // every rank's exchange buffer [layer][slot][d]
+    uint32_t *flags[EP_MAX_WORLD];         // every rank's slice flags [layer][slot][d / 16]
+    uint32_t *done[EP_MAX_WORLD];          // every rank's completed-step counters [world]
+    // speculative step: every rank's buffer of self-validating row sums [layer][slot][d], one 64-bit
+    // word each = (step number << 32) | float bits, written with one store: no flag, no fence
+    unsigned long long *pairs[EP_MAX_WORLD];
+};
 // ---- single-token expert matvecs on the tensor cores in native fp4 (kernels_mxt.cu)
 // Tile units: [expert][tile of 128 rows][block pair][4096 B operand image | 128 x 2 e8m0 bytes].
 constexpr int MXT_UNIT = 4352;
@@ -97,7 +109,7 @@ void launch_xt_bimg(const int8_t *xq, int nb, uint8_t *bimg, cudaStream_t st);
 // himg: [topk][blocks / 2][768] operand images of h for launch_down_t
 cudaError_t launch_gate_up_t(MxtDev gu, const float *gate_b, const float *up_b, const int32_t *top, const float *est, int ne, int topk,
                              int d, const uint8_t *ximg, const float *xs, int8_t *hq, float *hs, uint8_t *himg, DevState *state,
-                             bool pdl, cudaStream_t st);
+                             bool pdl, cudaStream_t st, const EpCtx *ep = nullptr, int layer = 0);
 // part: [topk][tiles_per_expert * 128] floats of scratch; counter: [tiles_per_expert] words, zero before the first launch.
 // wts != nullptr (exact routing in top/wts, est == nullptr): the last CTA of a row tile folds it onto x.
 // wts == nullptr: slot s is the s-th largest entry of est (or top[s]); only part[] is written and
@@ -110,10 +122,11 @@ cudaError_t launch_down_fold(const int32_t *top, const float *wts, const float *
 // that follows, and increments *fold_seq.  next_norm_w == nullptr: fold only.
 cudaError_t launch_fold_norm(const int32_t *top, const float *wts, const float *est, int ne, int topk, int d, const float *part,
                              const float *down_b, float *x, const float *next_norm_w, float eps, int8_t *nq, float *ns,
-                             uint32_t *router_seq, uint32_t *fold_seq, DevState *state, bool pdl, cudaStream_t st);
+                             uint32_t *router_seq, uint32_t *fold_seq, DevState *state, bool pdl, cudaStream_t st,
+                             const EpCtx *ep = nullptr, int layer = 0);
 cudaError_t launch_down_t(MxtDev down, const float *down_b, const int32_t *top, const float *wts, const float *est, int ne, int topk,
                           int d, const uint8_t *himg, const float *hs, float *x, float *part, uint32_t *counter, DevState *state,
-                          bool pdl, cudaStream_t st);
+                          bool pdl, cudaStream_t st, const EpCtx *ep = nullptr, int layer = 0);
 
 // ---- token-tile matmul on tcgen05 tensor cores (kernels_tile.cu): y[t][r] = row (row0 + r) . activation t,
 // t < ntok <= 16, every value bit-identical to launch_mx_gemv on token t alone
@@ -127,15 +140,6 @@ cudaError_t launch_mx_tile_experts(MxDev w, int ne, int rows_per_expert, const i
 void launch_tile_route(const int32_t *top, int ntok, int topk, int ne, int *cnt, int *list, cudaStream_t st);
 void launch_tile_combine(const float *part, const float *wts, int topk, int d, int ntok, float *x, cudaStream_t st);
 
-// ---- expert parallelism over NVLink peer memory (kernels_ep.cu)
-constexpr int EP_MAX_WORLD = 8;
-struct EpCtx {
-    int rank, world, e_lo, e_cnt;          // experts [e_lo, e_lo + e_cnt) live on this rank
-    uint32_t *epoch;                       // local: number of the step in flight
-    float *xchg[EP_MAX_WORLD];             // every rank's exchange buffer [layer][slot][d]
-    uint32_t *flags[EP_MAX_WORLD];         // every rank's slice flags [layer][slot][d / 16]
-    uint32_t *done[EP_MAX_WORLD];          // every rank's completed-step counters [world]
-};
 void launch_ep_begin(const EpCtx &c, DevState *state, cudaStream_t st);
 // down-projection of the local experts, exchange of the 16-row slices, fold in slot order
 cudaError_t launch_down_ep(MxDev down, const float *down_b, const int32_t *top, const float *wts, int topk, int d, int layer, const int8_t *hq,

@@ -98,6 +98,32 @@ struct Waiter {
     }
 };
 
+// ---- words that another GPU writes or reads over NVLink peer memory (expert parallelism)
+constexpr long long EP_WAIT_CYCLES = 20000000000ll;     // about ten seconds of SM clock
+__device__ __forceinline__ uint32_t ld_sys(const uint32_t *p) {
+    uint32_t v;
+    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+    return v;
+}
+__device__ __forceinline__ void st_sys(uint32_t *p, uint32_t v) { asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
+__device__ __forceinline__ float ld_f32_sys(const float *p) {
+    float v;
+    asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
+    return v;
+}
+// Wait until *p >= want (wrap-safe), at most EP_WAIT_CYCLES; on expiry record the error and give up.
+__device__ __forceinline__ bool ep_wait(const uint32_t *p, uint32_t want, uint32_t *err) {
+    if (err && *reinterpret_cast<volatile uint32_t *>(err) != 0u) return false;
+    const long long t0 = clock64();
+    for (;;) {
+        for (int i = 0; i < 64; i++)
+            if ((int32_t)(ld_sys(p) - want) >= 0) return true;
+        if (clock64() - t0 > EP_WAIT_CYCLES) break;
+    }
+    if (err) atomicCAS(err, (uint32_t)DEV_ERR_NONE, (uint32_t)DEV_ERR_PEER_TIMEOUT);
+    return false;
+}
+
 // Programmatic dependent launch.  pdl_wait(): block until the preceding kernel in the stream has
 // completed and its writes are visible.  pdl_trigger(): allow the next kernel's CTAs to be
 // scheduled.  Kernels here issue their weight copies first, then wait, then trigger, so the

@@ -22,33 +22,6 @@ namespace brrr {
 
 namespace {
 
-constexpr long long EP_WAIT_CYCLES = 20000000000ll;     // about ten seconds of SM clock
-
-__device__ __forceinline__ uint32_t ld_sys(const uint32_t *p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
-    return v;
-}
-__device__ __forceinline__ void st_sys(uint32_t *p, uint32_t v) { asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory"); }
-__device__ __forceinline__ float ld_f32_sys(const float *p) {
-    float v;
-    asm volatile("ld.relaxed.sys.global.f32 %0, [%1];" : "=f"(v) : "l"(p) : "memory");
-    return v;
-}
-
-// Wait until *p >= want (wrap-safe), at most EP_WAIT_CYCLES; on expiry record the error and give up.
-__device__ __forceinline__ bool ep_wait(const uint32_t *p, uint32_t want, uint32_t *err) {
-    if (err && *reinterpret_cast<volatile uint32_t *>(err) != 0u) return false;
-    const long long t0 = clock64();
-    for (;;) {
-        for (int i = 0; i < 64; i++)
-            if ((int32_t)(ld_sys(p) - want) >= 0) return true;
-        if (clock64() - t0 > EP_WAIT_CYCLES) break;
-    }
-    if (err) atomicCAS(err, (uint32_t)DEV_ERR_NONE, (uint32_t)DEV_ERR_PEER_TIMEOUT);
-    return false;
-}
-
 // Start of a step: tell every rank that this rank has finished step `epoch`, wait until every
 // rank has, then advance the epoch.  One warp.
 __global__ void ep_begin_kernel(EpCtx c, DevState *state) {

@@ -184,6 +184,11 @@ struct XtArgs {
     uint32_t *counter;          // down: [tiles] arrival counters, zero between launches
     DevState *state;
     int stages;
+    // expert parallelism (ep_on): w holds the experts [ep.e_lo, ep.e_lo + ep.e_cnt) only; CTAs of a slot
+    // whose expert lives on another rank do nothing; down stores its row sums, each tagged with the step
+    // number in one 64-bit word, into every rank's buffer ep.pairs ([layer][slot][d])
+    int ep_on, layer;
+    EpCtx ep;
 };
 
 struct XtShared {
@@ -281,15 +286,18 @@ __global__ void __launch_bounds__(XT_THREADS) xt_expert_kernel(XtArgs a) {
     // ---- routing of this slot (the ei-th largest entry of the estimate, or the exact routing), the
     // weight stream, the activation image (one bulk copy) and its block scales
     int e = 0;
+    bool local = true;
     const unsigned char *src = nullptr;
+    const uint32_t ep_epoch = a.ep_on ? *a.ep.epoch : 0u;          // the step in flight (written by the step's first kernel)
     auto route_and_start = [&]() {
         if (a.est) {
             block_spec_select(a.est, a.ne, a.topk, a.state, lg, sel, tid, XT_THREADS);
             __syncthreads();
             e = sel[ei];
         } else e = a.top[ei];
-        src = a.w.data + ((size_t)e * a.w.tiles_per_expert + t) * np * MXT_UNIT;
-        if (warp == 4 && lane < min(a.stages, nchunks)) {          // one lane per copy: the first stages of the weight stream
+        local = !a.ep_on || (e >= a.ep.e_lo && e < a.ep.e_lo + a.ep.e_cnt);
+        src = a.w.data + ((size_t)(a.ep_on ? e - a.ep.e_lo : e) * a.w.tiles_per_expert + t) * np * MXT_UNIT;
+        if (local && warp == 4 && lane < min(a.stages, nchunks)) {          // one lane per copy: the first stages of the weight stream
             const int cnt = min(XT_CH, np - lane * XT_CH);
             mbar_expect_tx(&sh.full[lane], (uint32_t)cnt * MXT_UNIT);
             bulk_g2s(sh.ring + stage_bytes * lane, src + (size_t)lane * stage_bytes, (uint32_t)cnt * MXT_UNIT, &sh.full[lane]);
@@ -305,7 +313,9 @@ __global__ void __launch_bounds__(XT_THREADS) xt_expert_kernel(XtArgs a) {
     BRRR_STAMP(a.state, SB + 2);
     BRRR_GT_GO(a.state, SB + 30);
     pdl_trigger();
-    if (warp == 4 && lane == 31) {
+    // (gate/up learns whether its slot is local only below: it copies the image in any case)
+    const bool img_copy = early ? local : true;
+    if (img_copy && warp == 4 && lane == 31) {
         const uint8_t *img = a.bimg + (DOWN ? (size_t)ei * np * XT_B_PAIR : 0);
         mbar_expect_tx(sh.bfull, (uint32_t)np * XT_B_PAIR);
         bulk_g2s(sh.bimg, img, (uint32_t)np * XT_B_PAIR, sh.bfull);
@@ -319,7 +329,10 @@ __global__ void __launch_bounds__(XT_THREADS) xt_expert_kernel(XtArgs a) {
 
     // Loop structure shared by the three roles: round r = ring stage r % stages = 4 block pairs =
     // accumulator region r % 2.  All indices advance incrementally.
-    if (warp == 4) {
+    if (!local) {
+        // the slot's expert lives on another rank: nothing to compute here (a copy in flight must land first)
+        if (img_copy && warp == 4 && lane == 31) xt_wait(sh.bfull, 0u, err, true);
+    } else if (warp == 4) {
         // ---- producer: refill a stage once the four epilogue warps have left it
         if (lane == 0) {
             int s = 0;
@@ -434,7 +447,15 @@ __global__ void __launch_bounds__(XT_THREADS) xt_expert_kernel(XtArgs a) {
             }
         } else {
             const int r = t * 128 + m, dpad = a.w.tiles_per_expert * 128;
-            a.part[(size_t)ei * dpad + r] = v;
+            if (a.ep_on) {
+                // the row sum, tagged with the step number, to every rank: one plain 64-bit store over
+                // NVLink peer memory per rank; the consumer polls the word itself
+                const size_t off = ((size_t)a.layer * a.topk + ei) * a.d + r;
+                const unsigned long long word = ((unsigned long long)ep_epoch << 32) | __float_as_uint(v);
+                if (r < a.d)
+                    for (int p = 0; p < a.ep.world; p++) if (p != a.ep.rank) a.ep.pairs[p][off] = word;
+                a.part[(size_t)ei * dpad + r] = v;          // this rank's own fold reads it after the kernel boundary
+            } else a.part[(size_t)ei * dpad + r] = v;
             if (a.wts) {                     // exact routing known: fold here; else a fold kernel follows
                 __threadfence();
                 xt_bar_epi();
@@ -528,6 +549,12 @@ struct FoldNormArgs {
     int8_t *nq;              // Q8 of the normalised residual, element order
     float *ns;               // its block scales
     uint32_t *router_seq, *fold_seq;
+    // expert parallelism: the row sums come from the ranks that own the estimate's experts, as 64-bit
+    // words (step number << 32 | float bits) in this rank's buffer of the layer ([slot][d]); a word is
+    // valid once it carries the step number *ep_epoch
+    const unsigned long long *ep_pairs;
+    const uint32_t *ep_epoch;
+    int ep_lo, ep_cnt;       // this rank's experts: their slots' row sums are in f.part, as on a single GPU
 };
 
 constexpr int FN_THREADS = 1024;
@@ -558,6 +585,7 @@ __global__ void __launch_bounds__(FN_THREADS) xt_fold_norm_kernel(FoldNormArgs a
         for (int s = 0; s < MAXS; s++) pb[s] = (live && s < topk) ? reinterpret_cast<const float4 *>(a.f.down_b + (size_t)sel[s] * d)[tid] : zero4;
     }
     const uint32_t want_seq = a.fold_seq ? __ldcg(a.fold_seq) + 1u : 0u;      // written by the previous launch of this kernel
+    const uint32_t ep_epoch = a.ep_pairs ? *a.ep_epoch : 0u;                  // the step in flight (written by the step's first kernel)
 #ifdef BRRR_FOLD_EARLY_TRIGGER
     pdl_trigger();       // the next projection may become resident and stream its weights while down still runs
 #endif
@@ -569,7 +597,36 @@ __global__ void __launch_bounds__(FN_THREADS) xt_fold_norm_kernel(FoldNormArgs a
 #endif
     // ---- slot s: partial sum of the s-th expert of the estimate
 #pragma unroll
-    for (int s = 0; s < MAXS; s++) ps[s] = (live && s < topk) ? reinterpret_cast<const float4 *>(a.f.part + (size_t)s * dpad)[tid] : zero4;
+    for (int s = 0; s < MAXS; s++) {
+        const bool mine = !a.ep_pairs || (sel[s < topk ? s : 0] >= a.ep_lo && sel[s < topk ? s : 0] < a.ep_lo + a.ep_cnt);
+        ps[s] = (live && s < topk && mine) ? reinterpret_cast<const float4 *>(a.f.part + (size_t)s * dpad)[tid] : zero4;
+    }
+    if (a.ep_pairs && live) {
+        // slots whose expert lives on another rank: every thread polls (bounded) the four tagged words
+        // of its rows until all of them carry this step's number
+        uint32_t *errp = a.f.state ? &a.f.state->err : nullptr;
+        const long long t0 = clock64();
+        bool ok = false;
+        while (!ok) {
+            ok = true;
+#pragma unroll
+            for (int s = 0; s < MAXS; s++) {
+                if (s < topk && !(sel[s] >= a.ep_lo && sel[s] < a.ep_lo + a.ep_cnt)) {
+                    // read at the L2, where the peers' stores to this GPU's memory land
+                    const ulonglong2 *w = reinterpret_cast<const ulonglong2 *>(a.ep_pairs + (size_t)s * d) + 2 * tid;
+                    const ulonglong2 lo = __ldcg(w), hi = __ldcg(w + 1);
+                    ok = ok && (uint32_t)(lo.x >> 32) == ep_epoch && (uint32_t)(lo.y >> 32) == ep_epoch && (uint32_t)(hi.x >> 32) == ep_epoch &&
+                         (uint32_t)(hi.y >> 32) == ep_epoch;
+                    ps[s] = make_float4(__uint_as_float((uint32_t)lo.x), __uint_as_float((uint32_t)lo.y), __uint_as_float((uint32_t)hi.x),
+                                        __uint_as_float((uint32_t)hi.y));
+                }
+            }
+            if (!ok && (clock64() - t0 > EP_WAIT_CYCLES || (errp && *reinterpret_cast<volatile uint32_t *>(errp) != 0u))) {
+                if (errp) atomicCAS(errp, (uint32_t)DEV_ERR_NONE, (uint32_t)DEV_ERR_PEER_TIMEOUT);
+                break;
+            }
+        }
+    }
     BRRR_STAMP(a.f.state, 242);
     // ---- the exact routing: the router publishes sequence-tagged words; one lane per word polls
     // (bounded) until its word carries this launch's sequence number
@@ -679,8 +736,9 @@ void launch_xt_bimg(const int8_t *xq, int nb, uint8_t *bimg, cudaStream_t st) {
 
 cudaError_t launch_gate_up_t(MxtDev gu, const float *gate_b, const float *up_b, const int32_t *top, const float *est, int ne, int topk,
                              int d, const uint8_t *ximg, const float *xs, int8_t *hq, float *hs, uint8_t *himg, DevState *state,
-                             bool pdl, cudaStream_t st) {
+                             bool pdl, cudaStream_t st, const EpCtx *ep, int layer) {
     XtArgs a{};
+    if (ep) { a.ep_on = 1; a.ep = *ep; a.layer = layer; }
     a.w = gu; a.bias_a = gate_b; a.bias_b = up_b; a.top = top; a.est = est; a.ne = ne; a.topk = topk; a.d = d;
     a.bimg = ximg; a.xs = xs; a.hq = hq; a.hs = hs; a.himg = himg; a.state = state;
     const int nchunks = (gu.np + XT_CH - 1) / XT_CH;
@@ -698,8 +756,9 @@ cudaError_t launch_gate_up_t(MxtDev gu, const float *gate_b, const float *up_b, 
 
 cudaError_t launch_down_t(MxtDev down, const float *down_b, const int32_t *top, const float *wts, const float *est, int ne, int topk,
                           int d, const uint8_t *himg, const float *hs, float *x, float *part, uint32_t *counter, DevState *state,
-                          bool pdl, cudaStream_t st) {
+                          bool pdl, cudaStream_t st, const EpCtx *ep, int layer) {
     XtArgs a{};
+    if (ep) { a.ep_on = 1; a.ep = *ep; a.layer = layer; }
     a.w = down; a.bias_a = down_b; a.top = top; a.wts = wts; a.est = est; a.ne = ne; a.topk = topk; a.d = d;
     a.bimg = himg; a.xs = hs; a.x = x; a.part = part; a.counter = counter; a.state = state;
     const int nchunks = (down.np + XT_CH - 1) / XT_CH;
@@ -728,12 +787,14 @@ cudaError_t launch_down_fold(const int32_t *top, const float *wts, const float *
 
 cudaError_t launch_fold_norm(const int32_t *top, const float *wts, const float *est, int ne, int topk, int d, const float *part,
                              const float *down_b, float *x, const float *next_norm_w, float eps, int8_t *nq, float *ns,
-                             uint32_t *router_seq, uint32_t *fold_seq, DevState *state, bool pdl, cudaStream_t st) {
+                             uint32_t *router_seq, uint32_t *fold_seq, DevState *state, bool pdl, cudaStream_t st, const EpCtx *ep, int layer) {
     if (d > 4 * FN_THREADS || d % 32 || topk > 8 || (router_seq && !state)) return cudaErrorInvalidValue;
     FoldNormArgs a{};
+
     a.f.top = top; a.f.wts = wts; a.f.est = est; a.f.ne = ne; a.f.topk = topk; a.f.d = d; a.f.dpad = (d + 127) / 128 * 128;
     a.f.part = part; a.f.down_b = down_b; a.f.x = x; a.f.state = state;
     a.norm_w = next_norm_w; a.eps = eps; a.nq = nq; a.ns = ns; a.router_seq = router_seq; a.fold_seq = fold_seq;
+    if (ep) { a.ep_pairs = ep->pairs[ep->rank] + (size_t)layer * topk * d; a.ep_epoch = ep->epoch; a.ep_lo = ep->e_lo; a.ep_cnt = ep->e_cnt; }
     const size_t smem = (size_t)d * sizeof(float);
     if (topk <= 4) return launch_k(xt_fold_norm_kernel<4>, dim3(1), dim3(FN_THREADS), smem, st, pdl, a);
     return launch_k(xt_fold_norm_kernel<8>, dim3(1), dim3(FN_THREADS), smem, st, pdl, a);

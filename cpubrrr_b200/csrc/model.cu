@@ -323,15 +323,16 @@ int enqueue_step(brrr_model *m, bool want, float *trace_dev, int *nlaunch, unsig
             CUL(launch_router_hint(m->x, ly.ffn_norm, c.rms_eps, d, ly.ginp, ly.ginp_b, c.n_expert, topk, m->est, m->xq, m->xs, m->st, pdl, s,
                                    m->use_mxt ? m->ximg : nullptr));
             n++;
+            const EpCtx *epc = m->ep ? &m->epc : nullptr;      // expert parallelism: local slots only, row sums exchanged by down, awaited by the fold
             if (m->use_mxt) CUL(launch_gate_up_t(ly.gu_t, ly.gate_b, ly.up_b, nullptr, m->est, c.n_expert, topk, d, m->ximg, m->xs,
-                                                 m->hq, m->hs, m->himg, m->st, pdl, s));
+                                                 m->hq, m->hs, m->himg, m->st, pdl, s, epc, il));
             else CUL(launch_gate_up(ly.gate, ly.up, ly.gate_b, ly.up_b, nullptr, topk, d, nullptr, nullptr, c.rms_eps, m->xq, m->xs,
                                     m->hq, m->hs, nullptr, m->st, pdl, s, m->est, c.n_expert));
             if (m->use_mxt) {
                 // down for the estimated experts as well; only the fold waits for the exact routing
                 n++;
                 CUL(launch_down_t(ly.down_t, ly.down_b, nullptr, nullptr, m->est, c.n_expert, topk, d, m->himg, m->hs, m->x,
-                                  m->dpart, m->dcount, m->st, pdl, s));
+                                  m->dpart, m->dcount, m->st, pdl, s, epc, il));
             }
             if (fused) {
                 // The fold is launched programmatically behind down and waits for the router's
@@ -342,7 +343,7 @@ int enqueue_step(brrr_model *m, bool want, float *trace_dev, int *nlaunch, unsig
                 const float *nw = last ? (want ? m->out_norm : nullptr) : m->L[il + 1].attn_norm;
                 n++;
                 CUL(launch_fold_norm(m->top, m->wts, m->est, c.n_expert, topk, d, m->dpart, ly.down_b, m->x, nw, c.rms_eps,
-                                     last ? m->xq : m->nq, last ? m->xs : m->ns, &m->st->router_seq, &m->st->fold_seq, m->st, pdl, s));
+                                     last ? m->xq : m->nq, last ? m->xs : m->ns, &m->st->router_seq, &m->st->fold_seq, m->st, pdl, s, epc, il));
                 if (last) CU(cudaStreamWaitEvent(s, m->ev_join, 0));
                 continue;
             }
@@ -410,7 +411,9 @@ int reset_state(brrr_model *m) {
 
 // First step and graph capture (needs every buffer the step touches, peers included).
 int finish_build(brrr_model *m) {
-    if (m->ep) m->use_spec = false;    // the routing estimate is not used across ranks
+    // expert-parallel ranks speculate only on the tensor-core path with the fused fold (its partial
+    // sums are what the ranks exchange); otherwise they run the plain step
+    if (m->ep && !(m->use_mxt && m->fused_fold)) m->use_spec = false;
     // one direct (un-captured) step configures every kernel's attributes and validates the launches
     TRY(reset_state(m));
     TRY(enqueue_step(m, true, nullptr, nullptr));
@@ -461,9 +464,9 @@ int build_model(brrr_model *m, const Source &src) {
         // for the second copy of the expert matrices (about 1.08 x their size)
         size_t free_b = 0, total_b = 0;
         CU(cudaMemGetInfo(&free_b, &total_b));
-        const size_t experts = (size_t)c.n_layer * ne * 3 * d * nb * 17;
+        const size_t experts = (size_t)c.n_layer * (m->ep ? m->epc.e_cnt : ne) * 3 * d * nb * 17;      // this rank's share
         const size_t rest = (size_t)c.n_vocab * d * 4 + (size_t)c.n_layer * ((size_t)(qkv_rows + d) * d * 2 + (size_t)BRRR_MAXSEQ * nkv * hd * 8) + (2ull << 30);
-        m->use_mxt = !m->ep && d % 64 == 0 && nb % 2 == 0 && topk <= 8 && free_b > experts * 2.2 + rest;
+        m->use_mxt = d % 64 == 0 && nb % 2 == 0 && topk <= 8 && free_b > experts * 2.2 + rest;
         if (const char *e = getenv("BRRR_NOMXT")) if (e[0] && e[0] != '0') m->use_mxt = false;
         if (const char *e = getenv("BRRR_NOFUSEDFOLD")) if (e[0] && e[0] != '0') m->fused_fold = false;
         if (const char *e = getenv("BRRR_TILE_PREFILL")) if (e[0] && e[0] != '0') m->tile_prefill = true;
@@ -496,10 +499,10 @@ int build_model(brrr_model *m, const Source &src) {
         if (m->use_mxt) {
             ly.gu_t.tiles_per_expert = d / 64; ly.gu_t.np = nb / 2;
             ly.down_t.tiles_per_expert = (d + 127) / 128; ly.down_t.np = nb / 2;
-            TRY(m->alloc(&ly.gu_t.data, mxt_bytes(ne, ly.gu_t.tiles_per_expert, nb / 2)));
-            TRY(m->alloc(&ly.down_t.data, mxt_bytes(ne, ly.down_t.tiles_per_expert, nb / 2)));
-            launch_mxt_pack(ly.gate, ly.up, ne, d, ly.gu_t, m->stream);
-            launch_mxt_pack(ly.down, MxDev{nullptr, 0, 0}, ne, d, ly.down_t, m->stream);
+            TRY(m->alloc(&ly.gu_t.data, mxt_bytes(e_cnt, ly.gu_t.tiles_per_expert, nb / 2)));       // this rank's experts
+            TRY(m->alloc(&ly.down_t.data, mxt_bytes(e_cnt, ly.down_t.tiles_per_expert, nb / 2)));
+            launch_mxt_pack(ly.gate, ly.up, e_cnt, d, ly.gu_t, m->stream);
+            launch_mxt_pack(ly.down, MxDev{nullptr, 0, 0}, e_cnt, d, ly.down_t, m->stream);
             CU(cudaGetLastError());
         }
         TRY(load_f32(m, src, il, BRRR_T_GATE_B, (size_t)ne * d, &ly.gate_b));
@@ -542,8 +545,9 @@ int build_model(brrr_model *m, const Source &src) {
     CU(cudaStreamSynchronize(m->stream));
     if (m->ep) {
         // exchange region: slices [layer][slot][d] | slice flags [layer][slot][d/16] | step counters [8] (+ the local epoch word)
+        // ... | tagged row sums of the speculative step [layer][slot][d] x 8 bytes
         const size_t nslice = (size_t)c.n_layer * topk * d, nflag = (size_t)c.n_layer * topk * (d / 16);
-        const size_t bytes = nslice * 4 + nflag * 4 + (EP_MAX_WORLD + 8) * 4;
+        const size_t bytes = nslice * 4 + nflag * 4 + (EP_MAX_WORLD + 8) * 4 + nslice * 8;
         CU(cudaMalloc(&m->ep_buf, bytes));
         CU(cudaMemsetAsync(m->ep_buf, 0, bytes, m->stream));
         CU(cudaStreamSynchronize(m->stream));
@@ -717,6 +721,7 @@ extern "C" int brrr_model_ep_attach(brrr_model *m, const void *handles) {
         m->epc.xchg[p] = (float *)base;
         m->epc.flags[p] = (uint32_t *)((char *)base + nslice * 4);
         m->epc.done[p] = m->epc.flags[p] + nflag;
+        m->epc.pairs[p] = (unsigned long long *)((char *)base + nslice * 4 + nflag * 4 + (EP_MAX_WORLD + 8) * 4);
     }
     m->epc.epoch = m->epc.done[m->epc.rank] + EP_MAX_WORLD;
     m->ep_attached = true;
@@ -1059,7 +1064,7 @@ extern "C" int brrr_moe_ffn_step(brrr_model *m, int il, const float *d_xn, float
 // BRRR_ERR_STATE when the model was opened without the tile-unit copy of the experts.
 extern "C" int brrr_moe_ffn_step_tc(brrr_model *m, int il, const float *d_xn, float *d_x, int32_t *d_top, float *d_wts) {
     if (!m || !d_xn || !d_x || il < 0 || il >= m->cfg.n_layer) return BRRR_ERR_ARG;
-    if (!m->use_mxt) return BRRR_ERR_STATE;
+    if (!m->use_mxt || m->ep) return BRRR_ERR_STATE;
     CU(cudaSetDevice(m->device));
     const brrr_cfg &c = m->cfg;
     const int d = c.n_embd, topk = c.n_expert_used;

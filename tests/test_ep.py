@@ -105,3 +105,25 @@ def test_ep_multi_rank_equals_oracle(brrr, orc, tmp_path, world):
         assert res["first"] == first and res["tokens"] == want, f"rank {rank}"
         assert res["hidden_bits"] == [int(b) for b in bits(om.hidden())], f"rank {rank}"
         assert res["logit_bits"] == [int(b) for b in bits(om.logits())[:64]], f"rank {rank}"
+
+
+@pytest.mark.gpu
+def test_ep_stalled_peer_is_reported_not_hung(brrr, orc, tmp_path):
+    """Two ranks attach; after the prompt the second one stops issuing steps (alive, memory mapped).
+    The first rank's next step waits (bounded, about ten seconds) for the row sums of the experts the
+    stalled rank owns, gives up, and the call returns BRRR_ERR_STATE; its CUDA context still works.
+    No kernel faults or hangs; NVLS is off and the exchange uses plain peer stores."""
+    import torch
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs 2 GPUs")
+    shape = dict(n_embd=128, n_layer=3, n_head=4, n_head_kv=2, n_expert=8, n_expert_used=4, n_vocab=512, sliding_window=16)
+    port = 29600 + (os.getpid() + 7) % 2000
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node=2", "--master-addr", "127.0.0.1",
+                        "--master-port", str(port), os.path.join(HERE, "ep_worker.py"), str(tmp_path), json.dumps(shape), "53", "0", "stall"],
+                       capture_output=True, timeout=600, env=env)
+    assert r.returncode == 0, r.stderr.decode()[-3000:]
+    res = json.load(open(tmp_path / "rank0.json"))
+    assert res["error"] is not None and "not valid in the current state" in res["error"], res
+    assert 5.0 < res["seconds"] < 60.0, res
+    assert res["small_ok"]
