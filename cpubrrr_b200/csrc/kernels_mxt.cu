@@ -228,7 +228,7 @@ __device__ __forceinline__ float xt_row_sum(const XtAcc &acc) {       // (a0 + a
     return __fadd_rn(__fadd_rn(__uint_as_float(a0), __uint_as_float(a1)), __fadd_rn(__uint_as_float(a2), __uint_as_float(a3)));
 }
 
-template <bool DOWN>
+template <bool DOWN, bool EP>
 __global__ void __launch_bounds__(XT_THREADS) xt_expert_kernel(XtArgs a) {
     extern __shared__ __align__(128) unsigned char smraw[];
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -288,15 +288,15 @@ __global__ void __launch_bounds__(XT_THREADS) xt_expert_kernel(XtArgs a) {
     int e = 0;
     bool local = true;
     const unsigned char *src = nullptr;
-    const uint32_t ep_epoch = a.ep_on ? *a.ep.epoch : 0u;          // the step in flight (written by the step's first kernel)
+    const uint32_t ep_epoch = EP ? *a.ep.epoch : 0u;          // the step in flight (written by the step's first kernel)
     auto route_and_start = [&]() {
         if (a.est) {
             block_spec_select(a.est, a.ne, a.topk, a.state, lg, sel, tid, XT_THREADS);
             __syncthreads();
             e = sel[ei];
         } else e = a.top[ei];
-        local = !a.ep_on || (e >= a.ep.e_lo && e < a.ep.e_lo + a.ep.e_cnt);
-        src = a.w.data + ((size_t)(a.ep_on ? e - a.ep.e_lo : e) * a.w.tiles_per_expert + t) * np * MXT_UNIT;
+        local = !EP || (e >= a.ep.e_lo && e < a.ep.e_lo + a.ep.e_cnt);
+        src = a.w.data + ((size_t)(EP ? e - a.ep.e_lo : e) * a.w.tiles_per_expert + t) * np * MXT_UNIT;
         if (local && warp == 4 && lane < min(a.stages, nchunks)) {          // one lane per copy: the first stages of the weight stream
             const int cnt = min(XT_CH, np - lane * XT_CH);
             mbar_expect_tx(&sh.full[lane], (uint32_t)cnt * MXT_UNIT);
@@ -329,7 +329,7 @@ __global__ void __launch_bounds__(XT_THREADS) xt_expert_kernel(XtArgs a) {
 
     // Loop structure shared by the three roles: round r = ring stage r % stages = 4 block pairs =
     // accumulator region r % 2.  All indices advance incrementally.
-    if (!local) {
+    if (EP && !local) {
         // the slot's expert lives on another rank: nothing to compute here (a copy in flight must land first)
         if (img_copy && warp == 4 && lane == 31) xt_wait(sh.bfull, 0u, err, true);
     } else if (warp == 4) {
@@ -447,7 +447,7 @@ __global__ void __launch_bounds__(XT_THREADS) xt_expert_kernel(XtArgs a) {
             }
         } else {
             const int r = t * 128 + m, dpad = a.w.tiles_per_expert * 128;
-            if (a.ep_on) {
+            if (EP) {
                 // the row sum, tagged with the step number, to every rank: one plain 64-bit store over
                 // NVLink peer memory per rank; the consumer polls the word itself
                 const size_t off = ((size_t)a.layer * a.topk + ei) * a.d + r;
@@ -559,7 +559,7 @@ struct FoldNormArgs {
 
 constexpr int FN_THREADS = 1024;
 
-template <int MAXS>       // slots held in registers: top-k <= MAXS
+template <int MAXS, bool EP>       // slots held in registers: top-k <= MAXS; EP: expert-parallel exchange
 __global__ void __launch_bounds__(FN_THREADS) xt_fold_norm_kernel(FoldNormArgs a) {
     extern __shared__ __align__(16) float fsm[];          // d floats of the residual
     __shared__ int sel[8];
@@ -585,7 +585,7 @@ __global__ void __launch_bounds__(FN_THREADS) xt_fold_norm_kernel(FoldNormArgs a
         for (int s = 0; s < MAXS; s++) pb[s] = (live && s < topk) ? reinterpret_cast<const float4 *>(a.f.down_b + (size_t)sel[s] * d)[tid] : zero4;
     }
     const uint32_t want_seq = a.fold_seq ? __ldcg(a.fold_seq) + 1u : 0u;      // written by the previous launch of this kernel
-    const uint32_t ep_epoch = a.ep_pairs ? *a.ep_epoch : 0u;                  // the step in flight (written by the step's first kernel)
+    const uint32_t ep_epoch = EP ? *a.ep_epoch : 0u;                  // the step in flight (written by the step's first kernel)
 #ifdef BRRR_FOLD_EARLY_TRIGGER
     pdl_trigger();       // the next projection may become resident and stream its weights while down still runs
 #endif
@@ -598,10 +598,10 @@ __global__ void __launch_bounds__(FN_THREADS) xt_fold_norm_kernel(FoldNormArgs a
     // ---- slot s: partial sum of the s-th expert of the estimate
 #pragma unroll
     for (int s = 0; s < MAXS; s++) {
-        const bool mine = !a.ep_pairs || (sel[s < topk ? s : 0] >= a.ep_lo && sel[s < topk ? s : 0] < a.ep_lo + a.ep_cnt);
+        const bool mine = !EP || (sel[s < topk ? s : 0] >= a.ep_lo && sel[s < topk ? s : 0] < a.ep_lo + a.ep_cnt);
         ps[s] = (live && s < topk && mine) ? reinterpret_cast<const float4 *>(a.f.part + (size_t)s * dpad)[tid] : zero4;
     }
-    if (a.ep_pairs && live) {
+    if (EP && live) {
         // slots whose expert lives on another rank: every thread polls (bounded) the four tagged words
         // of its rows until all of them carry this step's number
         uint32_t *errp = a.f.state ? &a.f.state->err : nullptr;
@@ -746,12 +746,14 @@ cudaError_t launch_gate_up_t(MxtDev gu, const float *gate_b, const float *up_b, 
 #define XT_GU_STAGES 4
 #endif
     a.stages = nchunks < XT_GU_STAGES ? nchunks : XT_GU_STAGES;            // two CTAs per SM at the 20b shape
-    static unsigned long long configured = 0;      // one bit per device
+    static unsigned long long configured = 0, configured_ep = 0;      // one bit per device
     {
-        cudaError_t e = smem_optin(xt_expert_kernel<false>, 200 * 1024, configured);
+        cudaError_t e = smem_optin(xt_expert_kernel<false, false>, 200 * 1024, configured);
+        if (e == cudaSuccess) e = smem_optin(xt_expert_kernel<false, true>, 200 * 1024, configured_ep);
         if (e != cudaSuccess) return e;
     }
-    return launch_k(xt_expert_kernel<false>, dim3(gu.tiles_per_expert, topk), dim3(XT_THREADS), xt_smem_bytes(gu.np, a.stages), st, pdl, a);
+    if (ep) return launch_k(xt_expert_kernel<false, true>, dim3(gu.tiles_per_expert, topk), dim3(XT_THREADS), xt_smem_bytes(gu.np, a.stages), st, pdl, a);
+    return launch_k(xt_expert_kernel<false, false>, dim3(gu.tiles_per_expert, topk), dim3(XT_THREADS), xt_smem_bytes(gu.np, a.stages), st, pdl, a);
 }
 
 cudaError_t launch_down_t(MxtDev down, const float *down_b, const int32_t *top, const float *wts, const float *est, int ne, int topk,
@@ -769,12 +771,14 @@ cudaError_t launch_down_t(MxtDev down, const float *down_b, const int32_t *top, 
 #define XT_DOWN_STAGES 4
 #endif
     a.stages = nchunks < XT_DOWN_STAGES ? nchunks : XT_DOWN_STAGES;
-    static unsigned long long configured = 0;      // one bit per device
+    static unsigned long long configured = 0, configured_ep = 0;      // one bit per device
     {
-        cudaError_t e = smem_optin(xt_expert_kernel<true>, 210 * 1024, configured);
+        cudaError_t e = smem_optin(xt_expert_kernel<true, false>, 210 * 1024, configured);
+        if (e == cudaSuccess) e = smem_optin(xt_expert_kernel<true, true>, 210 * 1024, configured_ep);
         if (e != cudaSuccess) return e;
     }
-    return launch_k(xt_expert_kernel<true>, dim3(down.tiles_per_expert, topk), dim3(XT_THREADS), xt_smem_bytes(down.np, a.stages), st, pdl, a);
+    if (ep) return launch_k(xt_expert_kernel<true, true>, dim3(down.tiles_per_expert, topk), dim3(XT_THREADS), xt_smem_bytes(down.np, a.stages), st, pdl, a);
+    return launch_k(xt_expert_kernel<true, false>, dim3(down.tiles_per_expert, topk), dim3(XT_THREADS), xt_smem_bytes(down.np, a.stages), st, pdl, a);
 }
 
 cudaError_t launch_down_fold(const int32_t *top, const float *wts, const float *est, int ne, int topk, int d, const float *part,
@@ -796,8 +800,10 @@ cudaError_t launch_fold_norm(const int32_t *top, const float *wts, const float *
     a.norm_w = next_norm_w; a.eps = eps; a.nq = nq; a.ns = ns; a.router_seq = router_seq; a.fold_seq = fold_seq;
     if (ep) { a.ep_pairs = ep->pairs[ep->rank] + (size_t)layer * topk * d; a.ep_epoch = ep->epoch; a.ep_lo = ep->e_lo; a.ep_cnt = ep->e_cnt; }
     const size_t smem = (size_t)d * sizeof(float);
-    if (topk <= 4) return launch_k(xt_fold_norm_kernel<4>, dim3(1), dim3(FN_THREADS), smem, st, pdl, a);
-    return launch_k(xt_fold_norm_kernel<8>, dim3(1), dim3(FN_THREADS), smem, st, pdl, a);
+    if (ep) return topk <= 4 ? launch_k(xt_fold_norm_kernel<4, true>, dim3(1), dim3(FN_THREADS), smem, st, pdl, a)
+                             : launch_k(xt_fold_norm_kernel<8, true>, dim3(1), dim3(FN_THREADS), smem, st, pdl, a);
+    if (topk <= 4) return launch_k(xt_fold_norm_kernel<4, false>, dim3(1), dim3(FN_THREADS), smem, st, pdl, a);
+    return launch_k(xt_fold_norm_kernel<8, false>, dim3(1), dim3(FN_THREADS), smem, st, pdl, a);
 }
 
 }  // namespace brrr
