@@ -30,21 +30,28 @@ struct KMatDev;
 cudaError_t launch_qw_embed(const uint8_t *embd_q4k, int d, const DevState *state, float *x, bool pdl, cudaStream_t st);
 cudaError_t launch_qw_norm_quant(const float *x, const float *w, float eps, int d, float *xn, int8_t *q, float *s, int32_t *bsum,
                                  bool pdl, cudaStream_t st);
-cudaError_t launch_qw_quant(const float *x, int n, int8_t *q, float *s, int32_t *bsum, bool pdl, cudaStream_t st);
-// y_i = M_i . x for up to three stacked matrices (resid: y_i += M_i . x)
+// mats: up to three matrices of equal width stacked row-wise (q | k | v); weights are fetched into registers before the
+// dependency wait.  pf_k / pf_v (nullable): K/V cache of the attention that follows, requested into L2 up to state->pos.
 cudaError_t launch_qw_matvec(const KMatDev *mats, float *const *ys_out, int n, bool resid, const int8_t *xq, const float *ys,
-                             const int32_t *bsum, bool pdl, cudaStream_t st);
+                             const int32_t *bsum, bool pdl, cudaStream_t st, const float *pf_k = nullptr, const float *pf_v = nullptr,
+                             int pf_nkv = 0, const DevState *state = nullptr);
 cudaError_t launch_qw_qknorm_rope(float *q, const float *k, const float *v, const float *q_norm, const float *k_norm, const float *rope,
                                   float eps, int nh, int nkv, const DevState *state, int pos_val, float *kc, float *vc, bool pdl,
                                   cudaStream_t st);
-cudaError_t launch_qw_attn(const float *q, const float *kc, const float *vc, int nh, int nkv, const DevState *state, int pos_val, float *ao,
-                           bool pdl, cudaStream_t st);
+// attention of all heads (two per CTA) and the Q8_K image of its output (aq, as per 256, asum per 32)
+cudaError_t launch_qw_attn(const float *q, const float *kc, const float *vc, int nh, int nkv, const DevState *state, int pos_val, int8_t *aq,
+                           float *as, int32_t *asum, bool pdl, cudaStream_t st);
 cudaError_t launch_qw_gate_up(const KMatDev &gate, const KMatDev &up, const int32_t *top, int topk, int ff, const int8_t *xq, const float *ys,
                               const int32_t *bsum, float *hbuf, bool pdl, cudaStream_t st);
-cudaError_t launch_qw_down(const KMatDev &down, const int32_t *top, const float *wts, int topk, int d, int ff, const int8_t *hq,
-                           const float *hs, const int32_t *hsum, float *x, bool pdl, cudaStream_t st);
+// hbuf: [topk][ff] floats of h (quantised in the kernel's prologue); counter: one zeroed word; next_norm_w (nullable): the last CTA
+// to finish writes the Q8_K image (nq, ns, nsum) of RMSNorm(x, next_norm_w)
+cudaError_t launch_qw_down(const KMatDev &down, const int32_t *top, const float *wts, int topk, int d, int ff, const float *hbuf, float *x,
+                           unsigned int *counter, const float *next_norm_w, float eps, int8_t *nq, float *ns, int32_t *nsum, bool pdl,
+                           cudaStream_t st);
 cudaError_t launch_qw_head(const KMatDev &head, const int8_t *xq, const float *ys, const int32_t *bsum, float *logits, DevState *state,
                            bool pdl, cudaStream_t st);
+// Q6_K rows from the GGUF layout (210-byte superblocks) into the aligned planes of KMatDev (planes = 1)
+void launch_q6k_planes(const uint8_t *src, size_t rows, int cols, uint8_t *dst, cudaStream_t st);
 char *host_err_buf();   // thread-local text behind brrr_last_cuda_error (512 bytes)
 
 // ---- Q8 matrices (kernels_q8.cu)
@@ -156,7 +163,8 @@ void launch_router_pack(const float *W, int ne, int d, float *out, cudaStream_t 
 // normalised vector otherwise.
 cudaError_t launch_ffn_in(const float *x_in, const float *norm_w, float eps, int d, const float *Wt, const float *b, int ne, int topk,
                           float *logits, int32_t *top, float *wts, unsigned int *counter, DevState *state, bool pdl, cudaStream_t st,
-                          int ntok = 1, uint32_t *signal = nullptr);
+                          int ntok = 1, uint32_t *signal = nullptr, int qwen_norm = 0, int8_t *q8k_q = nullptr, float *q8k_s = nullptr,
+                          int32_t *q8k_bsum = nullptr);
 // ntok > 1: a tile of tokens in one launch (token t reads x_in + t * d, writes logits + t * ne, top + 8 t, wts + 8 t, uses counter + t)
 // signal (nullable, ntok == 1): a device word the kernel increments after its routing is written, for a
 // consumer that runs beside it instead of after it (launch_fold_norm)

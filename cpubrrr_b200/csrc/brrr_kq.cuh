@@ -134,12 +134,110 @@ __device__ __forceinline__ float q6k_row_dot(const uint8_t *row, int nsb, const 
     return sumf;
 }
 
-// A K-quant matrix on the device: rows in the GGUF byte layout, type 12 (Q4_K) or 14 (Q6_K).
+// A K-quant matrix on the device, type 12 (Q4_K) or 14 (Q6_K).  Q4_K rows stay in the GGUF byte
+// layout (144-byte superblocks, 16-byte aligned).  Q6_K rows are either in the GGUF layout (210-byte
+// superblocks, 2-byte aligned: planes == 0) or re-laid at load time into four aligned planes per row
+// (planes == 1): ql [nsb][128] | qh [nsb][64] | scales [nsb][16] | d [nsb] f16, padded to 16 bytes -
+// a byte permutation, so every integer of the dot is unchanged.
 struct KMatDev {
     const uint8_t *p;
     int type, rows, cols;
-    __host__ __device__ size_t bpr() const { return (size_t)(cols / 256) * (type == 12 ? 144 : 210); }
+    int planes;
+    __host__ __device__ size_t bpr() const {
+        const size_t nsb = (size_t)(cols / 256);
+        if (type == 12) return nsb * 144;
+        return planes ? nsb * 208 + ((nsb * 2 + 15) & ~(size_t)15) : nsb * 210;
+    }
 };
+// bytes of a row in the GGUF layout (the algorithmic figure, whatever the device layout)
+__host__ __device__ __forceinline__ size_t kq_gguf_row_bytes(int type, int cols) { return (size_t)(cols / 256) * (type == 12 ? 144 : 210); }
+__host__ __device__ __forceinline__ size_t q6k_plane_row_bytes(int nsb) { return (size_t)nsb * 208 + (((size_t)nsb * 2 + 15) & ~(size_t)15); }
+
+// The qwen3moe RMS norm sums squares in 12 contiguous slices (the reference's 12 workers), each
+// serially and unfused, and adds the partial sums in worker order (engine_qwen2.rs:15, 453-465).
+constexpr int QW_NT = 12;
+// worker w's contiguous slice of n items (engine_qwen2.rs:246-252)
+__device__ __forceinline__ void qw_slice(int w, int n, int &a, int &b) {
+    int base = n / QW_NT, rem = n % QW_NT;
+    a = w * base + min(w, rem);
+    b = a + base + (w < rem ? 1 : 0);
+}
+
+// ---------------------------------------------------------------- lane-group form (decode kernels)
+// Eight lanes own one superblock (a warp covers four superblocks at a time) and every lane moves 16
+// bytes per load.  A unit = what one lane holds of one superblock.
+//   Q4_K:         a = the 16-byte header (d | dmin, 12 packed scale bytes), b = nibble bytes 16 l8 .. 16 l8 + 15
+//   Q6_K planes:  a = ql bytes 16 l8 .. +15, b = the 16 qh bytes that go with them,
+//                 c = scale of the low nibbles | scale of the high nibbles << 8 | d (f16 bits) << 16
+struct KUnit { uint4 a, b; uint32_t c; };
+
+__device__ __forceinline__ void kq_unit_load(const KMatDev &m, const uint8_t *row, int sb, int l8, KUnit &u) {
+    if (m.type == 12) {
+        const uint4 *p = reinterpret_cast<const uint4 *>(row + (size_t)sb * 144);
+        u.a = __ldg(p);
+        u.b = __ldg(p + 1 + l8);
+        u.c = 0u;
+    } else {
+        const int nsb = m.cols / 256, h = l8 >> 2, q = l8 & 3;
+        u.a = __ldg(reinterpret_cast<const uint4 *>(row + (size_t)sb * 128 + 16 * l8));
+        u.b = __ldg(reinterpret_cast<const uint4 *>(row + (size_t)nsb * 128 + (size_t)sb * 64 + 32 * h + 16 * (q & 1)));
+        const uint8_t *sc = row + (size_t)nsb * 192 + (size_t)sb * 16 + 8 * h + (q >= 2 ? 2 : 0) + (q & 1);
+        const uint32_t dh = __ldg(reinterpret_cast<const unsigned short *>(row + (size_t)nsb * 208 + (size_t)sb * 2));
+        u.c = (uint32_t)__ldg(sc) | ((uint32_t)__ldg(sc + 4) << 8) | (dh << 16);
+    }
+}
+
+// The superblock's term of the row sum, valid in all eight lanes of the group: (ys d) acc - (ys dmin) mint
+// for Q4_K, (ys d) acc for Q6_K, every product rounded separately as in q4k_row_dot / q6k_row_dot.
+// xsb: the 256 int8 activations of the superblock (16-byte aligned), bs: its eight 32-sums, gmask: the
+// group's lanes.
+__device__ __forceinline__ float kq_unit_term(int type, const KUnit &u, int l8, const int8_t *xsb, float ys, const int32_t *bs, unsigned gmask) {
+    if (type == 12) {
+        const int jj = l8 >> 1, hh = l8 & 1;
+        const int4 x0 = *reinterpret_cast<const int4 *>(xsb + (2 * jj) * 32 + 16 * hh);
+        const int4 x1 = *reinterpret_cast<const int4 *>(xsb + (2 * jj + 1) * 32 + 16 * hh);
+        int sc0, mn0, sc1, mn1, scj, mnj;
+        k4_scale_min(u.a.y, u.a.z, u.a.w, 2 * jj, sc0, mn0);
+        k4_scale_min(u.a.y, u.a.z, u.a.w, 2 * jj + 1, sc1, mn1);
+        k4_scale_min(u.a.y, u.a.z, u.a.w, l8, scj, mnj);
+        const uint32_t M = 0x0F0F0F0Fu;
+        int lo = __dp4a((int)(u.b.x & M), x0.x, 0);
+        lo = __dp4a((int)(u.b.y & M), x0.y, lo);
+        lo = __dp4a((int)(u.b.z & M), x0.z, lo);
+        lo = __dp4a((int)(u.b.w & M), x0.w, lo);
+        int hi = __dp4a((int)((u.b.x >> 4) & M), x1.x, 0);
+        hi = __dp4a((int)((u.b.y >> 4) & M), x1.y, hi);
+        hi = __dp4a((int)((u.b.z >> 4) & M), x1.z, hi);
+        hi = __dp4a((int)((u.b.w >> 4) & M), x1.w, hi);
+        int a = lo * sc0 + hi * sc1;
+        int mt = mnj * bs[l8];
+        a = __reduce_add_sync(gmask, a);
+        mt = __reduce_add_sync(gmask, mt);
+        const float d = half_bits_to_f32(u.a.x & 0xffffu), dmin = half_bits_to_f32(u.a.x >> 16);
+        return __fsub_rn(__fmul_rn(__fmul_rn(ys, d), (float)a), __fmul_rn(__fmul_rn(ys, dmin), (float)mt));
+    }
+    const int h = l8 >> 2, q = l8 & 3;
+    const int base = 128 * h + (q >= 2 ? 32 : 0) + 16 * (q & 1);
+    const int4 xl = *reinterpret_cast<const int4 *>(xsb + base);
+    const int4 xh = *reinterpret_cast<const int4 *>(xsb + base + 64);
+    const int sl = q >= 2 ? 2 : 0, sh = sl + 4;
+    const uint32_t M4 = 0x0F0F0F0Fu, M2 = 0x03030303u;
+    int accl = 0, acch = 0, sxl = 0, sxh = 0;
+#define BRRR_Q6_WORD(QL, QH, XL, XH)                                                                   \
+    accl = __dp4a((int)(((QL) & M4) | ((((QH) >> sl) & M2) << 4)), (XL), accl);                         \
+    acch = __dp4a((int)((((QL) >> 4) & M4) | ((((QH) >> sh) & M2) << 4)), (XH), acch);                  \
+    sxl = __dp4a(0x01010101, (XL), sxl);                                                                \
+    sxh = __dp4a(0x01010101, (XH), sxh);
+    BRRR_Q6_WORD(u.a.x, u.b.x, xl.x, xh.x)
+    BRRR_Q6_WORD(u.a.y, u.b.y, xl.y, xh.y)
+    BRRR_Q6_WORD(u.a.z, u.b.z, xl.z, xh.z)
+    BRRR_Q6_WORD(u.a.w, u.b.w, xl.w, xh.w)
+#undef BRRR_Q6_WORD
+    const int scl = (int)(signed char)(u.c & 0xffu), sch = (int)(signed char)((u.c >> 8) & 0xffu);
+    int a = (accl - 32 * sxl) * scl + (acch - 32 * sxh) * sch;
+    a = __reduce_add_sync(gmask, a);
+    return __fmul_rn(__fmul_rn(ys, half_bits_to_f32(u.c >> 16)), (float)a);
+}
 
 __device__ __forceinline__ float kq_row_dot(const KMatDev &m, size_t row, const int8_t *xq, const float *ys, const int32_t *bsum, int lane) {
     const uint8_t *r = m.p + row * m.bpr();

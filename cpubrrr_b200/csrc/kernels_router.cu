@@ -12,6 +12,7 @@
 #include "brrr_block.cuh"
 #include "brrr_tma.cuh"
 #include "brrr_mxt.cuh"
+#include "brrr_kq.cuh"
 
 namespace brrr {
 
@@ -73,6 +74,12 @@ struct RouterArgs {
     DevState *state;
     uint32_t *signal;        // nullable: sequence number of the published routing (see publish_route)
     unsigned long long *pub;
+    // qwen3moe: the norm is the 12-slice one, and the first CTA also leaves the Q8_K image of the
+    // normalised token (quants, scales per 256, sums per 32) for the gate/up kernel
+    int qwen_norm;
+    int8_t *q8k_q;
+    float *q8k_s;
+    int32_t *q8k_bsum;
 };
 
 // k rounds of warp arg-max over the logits (lane l holds experts l, l+32, ...): the largest value
@@ -173,9 +180,34 @@ __global__ void __launch_bounds__(RT_THREADS) ffn_in_kernel(RouterArgs a) {
     stage_vec4(a.x_in, xn, d, tid, RT_THREADS);
     __syncthreads();
     if (a.norm_w) {
-        float inv = block_rms_inv(xn, d, a.eps, &inv_sh);
+        float inv;
+        if (a.qwen_norm) {
+            __shared__ float part[QW_NT];
+            if (tid < QW_NT) {
+                int lo, hi;
+                qw_slice(tid, d, lo, hi);
+                float ps = 0.0f;
+#pragma unroll 8
+                for (int i = lo; i < hi; i++) { const float v = xn[i]; ps = __fadd_rn(ps, __fmul_rn(v, v)); }
+                part[tid] = ps;
+            }
+            __syncthreads();
+            float tot = 0.0f;
+#pragma unroll
+            for (int k = 0; k < QW_NT; k++) tot = __fadd_rn(tot, part[k]);
+            inv = __fdiv_rn(1.0f, __fsqrt_rn(__fadd_rn(__fdiv_rn(tot, (float)d), a.eps)));
+        } else inv = block_rms_inv(xn, d, a.eps, &inv_sh);
         for (int i = tid; i < d; i += RT_THREADS) xn[i] = __fmul_rn(__fmul_rn(xn[i], inv), wn[i]);
         __syncthreads();
+    }
+    if (a.q8k_q && blockIdx.x == 0 && blockIdx.y == 0 && warp >= 2) {
+        // warps 2..7 of the first CTA, beside the chain warp: Q8_K of the normalised token
+        for (int sb = warp - 2; sb < d / 256; sb += RT_THREADS / 32 - 2) {
+            float v[8];
+#pragma unroll
+            for (int i = 0; i < 8; i++) v[i] = xn[sb * 256 + lane * 8 + i];
+            warp_quant_q8k(v, lane, a.q8k_q + sb * 256, a.q8k_s + sb, a.q8k_bsum + sb * 8);
+        }
     }
 
     BRRR_STAMP(a.state, 3);
@@ -239,8 +271,9 @@ size_t router_packed_floats(int ne, int d) { return (size_t)((ne + 31) / 32) * (
 
 cudaError_t launch_ffn_in(const float *x_in, const float *norm_w, float eps, int d, const float *Wt, const float *b, int ne, int topk,
                           float *logits, int32_t *top, float *wts, unsigned int *counter, DevState *state, bool pdl, cudaStream_t st, int ntok,
-                          uint32_t *signal) {
-    RouterArgs a{x_in, norm_w, eps, d, Wt, b, ne, topk, logits, top, wts, counter, state, signal, (signal && state) ? state->route_pub : nullptr};
+                          uint32_t *signal, int qwen_norm, int8_t *q8k_q, float *q8k_s, int32_t *q8k_bsum) {
+    RouterArgs a{x_in, norm_w, eps, d, Wt, b, ne, topk, logits, top, wts, counter, state, signal, (signal && state) ? state->route_pub : nullptr,
+                 qwen_norm, q8k_q, q8k_s, q8k_bsum};
     if (signal && !state) return cudaErrorInvalidValue;
     size_t smem = (size_t)RT_TILE_FLOATS * 4 * RT_STAGES + (size_t)d * 8 + (size_t)((ne + 3) & ~3) * 4 + RT_STAGES * 16;
     static unsigned long long configured = 0;      // one bit per device

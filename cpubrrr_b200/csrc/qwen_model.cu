@@ -82,6 +82,7 @@ struct brrr_qwen {
           *logits = nullptr, *xs = nullptr, *as = nullptr, *hs = nullptr, *wts = nullptr;
     int8_t *xq = nullptr, *aq = nullptr, *hq = nullptr;
     int32_t *xsum = nullptr, *asum = nullptr, *hsum = nullptr, *top = nullptr;
+    unsigned int *down_counter = nullptr;      // arrival counter of the down kernel's CTAs (self-resetting)
     DevState *st = nullptr;
     uint32_t *h_in = nullptr, *h_out = nullptr;
     cudaGraphExec_t g_head = nullptr, g_nohead = nullptr;
@@ -95,6 +96,10 @@ struct brrr_qwen {
         allocs.push_back(vp);
         *p = (T *)vp;
         return BRRR_OK;
+    }
+    void release(void *vp) {          // give one allocation back early (raw bytes that were re-laid)
+        for (size_t i = 0; i < allocs.size(); i++)
+            if (allocs[i] == vp) { cudaFree(vp); allocs.erase(allocs.begin() + i); return; }
     }
 };
 
@@ -146,7 +151,18 @@ int qload_k(brrr_qwen *m, const QSource &s, uint32_t layer, int kind, int rows, 
     uint32_t t = (kind == BRRR_T_DOWN || kind == BRRR_T_OUTPUT) ? 14 : 12;
     void *p = nullptr;
     TRY(qfetch(m, s, layer, kind, &t, (size_t)rows * cols, &p));
-    *out = KMatDev{(const uint8_t *)p, (int)t, rows, cols};
+    if (t == 14 && kind != BRRR_T_TOK_EMBD) {
+        // Q6_K rows (210-byte superblocks, 2-byte aligned) are re-laid into aligned planes per row: a byte permutation
+        uint8_t *planes = nullptr;
+        TRY(m->alloc(&planes, (size_t)rows * q6k_plane_row_bytes(cols / 256)));
+        launch_q6k_planes((const uint8_t *)p, (size_t)rows, cols, planes, m->stream);
+        CU(cudaGetLastError());
+        CU(cudaStreamSynchronize(m->stream));
+        m->release(p);
+        *out = KMatDev{planes, 14, rows, cols, 1};
+        return BRRR_OK;
+    }
+    *out = KMatDev{(const uint8_t *)p, (int)t, rows, cols, 0};
     return BRRR_OK;
 }
 
@@ -182,26 +198,27 @@ int qenqueue_step(brrr_qwen *m, bool want, float *trace_dev, int *nlaunch) {
     int n = 0;
     CU(launch_qw_embed(m->embd.p, d, m->st, m->x, false, s)); n++;
     if (trace_dev) CU(cudaMemcpyAsync(trace_dev, m->x, d * sizeof(float), cudaMemcpyDeviceToDevice, s));
+    // layer 0 has no down kernel before it: its attention norm + Q8_K is a launch of its own
+    CU(launch_qw_norm_quant(m->x, m->L[0].attn_norm, c.rms_eps, d, nullptr, m->xq, m->xs, m->xsum, pdl, s)); n++;
     for (int il = 0; il < c.n_layer; il++) {
         QLayer &ly = m->L[il];
-        CU(launch_qw_norm_quant(m->x, ly.attn_norm, c.rms_eps, d, nullptr, m->xq, m->xs, m->xsum, pdl, s)); n++;
         KMatDev qkv[3] = {ly.wq, ly.wk, ly.wv};
         float *qkv_out[3] = {m->q, m->k, m->v};
-        CU(launch_qw_matvec(qkv, qkv_out, 3, false, m->xq, m->xs, m->xsum, pdl, s)); n++;
+        CU(launch_qw_matvec(qkv, qkv_out, 3, false, m->xq, m->xs, m->xsum, pdl, s, ly.kc, ly.vc, nkv, m->st)); n++;
         CU(launch_qw_qknorm_rope(m->q, m->k, m->v, ly.q_norm, ly.k_norm, m->rope, c.rms_eps, nh, nkv, m->st, 0, ly.kc, ly.vc, pdl, s)); n++;
-        CU(launch_qw_attn(m->q, ly.kc, ly.vc, nh, nkv, m->st, 0, m->ao, pdl, s)); n++;
-        CU(launch_qw_quant(m->ao, nh * hd, m->aq, m->as, m->asum, pdl, s)); n++;
+        CU(launch_qw_attn(m->q, ly.kc, ly.vc, nh, nkv, m->st, 0, m->aq, m->as, m->asum, pdl, s)); n++;
         float *xo[1] = {m->x};
         CU(launch_qw_matvec(&ly.wo, xo, 1, true, m->aq, m->as, m->asum, pdl, s)); n++;
-        CU(launch_qw_norm_quant(m->x, ly.ffn_norm, c.rms_eps, d, m->xn, m->xq, m->xs, m->xsum, pdl, s)); n++;
-        CU(launch_ffn_in(m->xn, nullptr, 0.0f, d, ly.ginp, nullptr, c.n_expert, topk, m->rlogits, m->top, m->wts, &m->st->router_done, m->st, pdl, s)); n++;
+        // router: FFN norm (12 slices) and the Q8_K image of the normalised token in its prologue
+        CU(launch_ffn_in(m->x, ly.ffn_norm, c.rms_eps, d, ly.ginp, nullptr, c.n_expert, topk, m->rlogits, m->top, m->wts, &m->st->router_done, m->st,
+                         pdl, s, 1, nullptr, 1, m->xq, m->xs, m->xsum)); n++;
         CU(launch_qw_gate_up(ly.gate, ly.up, m->top, topk, ff, m->xq, m->xs, m->xsum, m->hbuf, pdl, s)); n++;
-        CU(launch_qw_quant(m->hbuf, topk * ff, m->hq, m->hs, m->hsum, pdl, s)); n++;
-        CU(launch_qw_down(ly.down, m->top, m->wts, topk, d, ff, m->hq, m->hs, m->hsum, m->x, pdl, s)); n++;
+        const bool last = il == c.n_layer - 1;
+        const float *nw = last ? (want ? m->out_norm : nullptr) : m->L[il + 1].attn_norm;
+        CU(launch_qw_down(ly.down, m->top, m->wts, topk, d, ff, m->hbuf, m->x, m->down_counter, nw, c.rms_eps, m->xq, m->xs, m->xsum, pdl, s)); n++;
         if (trace_dev) CU(cudaMemcpyAsync(trace_dev + (size_t)(il + 1) * d, m->x, d * sizeof(float), cudaMemcpyDeviceToDevice, s));
     }
     if (want) {
-        CU(launch_qw_norm_quant(m->x, m->out_norm, c.rms_eps, d, nullptr, m->xq, m->xs, m->xsum, pdl, s)); n++;
         CU(launch_qw_head(m->head, m->xq, m->xs, m->xsum, m->logits, m->st, pdl, s)); n++;
         launch_finish_token(m->st, s); n++;
     }
@@ -286,6 +303,8 @@ int qbuild(brrr_qwen *m, const QSource &src) {
     TRY(m->alloc(&m->xq, d)); TRY(m->alloc(&m->aq, nh * hd)); TRY(m->alloc(&m->hq, (size_t)topk * ff));
     TRY(m->alloc(&m->xsum, d / 32)); TRY(m->alloc(&m->asum, nh * hd / 32)); TRY(m->alloc(&m->hsum, (size_t)topk * ff / 32));
     TRY(m->alloc(&m->top, 8)); TRY(m->alloc(&m->st, 1));
+    TRY(m->alloc(&m->down_counter, 1));
+    CU(cudaMemsetAsync(m->down_counter, 0, sizeof(unsigned int), m->stream));
     CU(cudaMemsetAsync(m->st, 0, sizeof(DevState), m->stream));
     CU(cudaMemsetAsync(m->x, 0, d * 4, m->stream));
     CU(cudaMallocHost(&m->h_in, 16));
@@ -406,15 +425,15 @@ extern "C" uint64_t brrr_qwen_bytes_per_step(const brrr_qwen *m, uint32_t pos) {
     if (!m) return 0;
     const brrr_qwen_cfg &c = m->cfg;
     const uint64_t d = c.n_embd, nkv = c.n_head_kv, hd = c.head_dim, ne = c.n_expert, k = c.n_expert_used, ff = c.n_ff_exp;
+    auto rb = [](const KMatDev &w) { return (uint64_t)kq_gguf_row_bytes(w.type, w.cols); };      // GGUF density, whatever the device layout
     uint64_t total = 0;
     for (const QLayer &ly : m->L) {
-        total += (uint64_t)ly.wq.rows * ly.wq.bpr() + (uint64_t)ly.wk.rows * ly.wk.bpr() + (uint64_t)ly.wv.rows * ly.wv.bpr() +
-                 (uint64_t)ly.wo.rows * ly.wo.bpr();
-        total += k * ff * (ly.gate.bpr() + ly.up.bpr()) + k * d * ly.down.bpr();
+        total += (uint64_t)ly.wq.rows * rb(ly.wq) + (uint64_t)ly.wk.rows * rb(ly.wk) + (uint64_t)ly.wv.rows * rb(ly.wv) + (uint64_t)ly.wo.rows * rb(ly.wo);
+        total += k * ff * (rb(ly.gate) + rb(ly.up)) + k * d * rb(ly.down);
         total += ne * d * 4 + 2 * d * 4 + 2 * hd * 4;
         total += ((uint64_t)pos + 1) * nkv * hd * 4 * 2;
     }
-    total += (uint64_t)m->head.rows * m->head.bpr() + d * 4 + m->embd.bpr();
+    total += (uint64_t)m->head.rows * rb(m->head) + d * 4 + rb(m->embd);
     return total;
 }
 

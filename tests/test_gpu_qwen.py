@@ -64,7 +64,7 @@ def test_qwen_tokens_logits_hidden_bit_exact(brrr, orc, shape):
     first = eng.prefill(prompt)
     toks = eng.decode(first, len(prompt), n)
     assert [first] + [int(t) for t in toks[:-1]] == want
-    assert eng.launches_per_step(True) == 1 + 11 * cfg.n_layer + 3
+    assert eng.launches_per_step(True) == 2 + 7 * cfg.n_layer + 2      # embed, first norm; seven per layer; head, finish
     assert eng.bytes_per_step(10) > 0
     eng.close()
 
