@@ -83,6 +83,10 @@ SIGNATURES = {
     "brrr_qwen_stream": (_P, [_P]),
     "brrr_qwen_launches_per_step": (_I, [_P, _I]),
     "brrr_qwen_bytes_per_step": (C.c_uint64, [_P, C.c_uint32]),
+    "brrr_qwen_chat_prompt": (_I, [_P, C.c_char_p, _P, C.c_size_t, C.POINTER(C.c_size_t)]),
+    "brrr_qwen_generate": (_I, [_P, _P, _P, C.c_size_t, C.c_uint32, _P, _P, _P, C.c_size_t, _P]),
+    "brrr_qwen_serve_parse": (_I, [C.c_char_p, C.POINTER(C.c_uint32), C.c_char_p, C.c_size_t]),
+    "brrr_qwen_cli_main": (_I, [_I, _P]),
     "brrr_quant_q8": (_I, [_P, _I, _P, _P, _P]),
     "brrr_quant_q8k": (_I, [_P, _I, _P, _P, _P, _P]),
     "brrr_q4k_matvec": (_I, [_P, _I, _I, _P, _P, _P, _P, _P, _P]),

@@ -23,6 +23,7 @@ OBJ = os.path.join(HERE, "_obj")
 LIB = os.path.join(HERE, "libbrrr.so")
 HOOKS_LIB = os.path.join(HERE, "libbrrr_hooks.so")
 EXE = os.path.join(HERE, "brrr_engine")
+EXE_QWEN = os.path.join(HERE, "brrr_engine_qwen")
 
 SOURCES = ["kernels_small.cu", "kernels_q8.cu", "kernels_mx.cu", "kernels_router.cu", "kernels_attn.cu", "kernels_ep.cu", "kernels_tile.cu", "kernels_mxt.cu", "kernels_kq.cu", "kernels_qwen.cu", "qwen_model.cu",
            "model.cu", "capi_stage.cu", "capi_noalloc.cu", "host_text.cpp"]
@@ -78,11 +79,12 @@ def build(force=False, verbose=False, defines=(), out=LIB):
     if r.returncode != 0:
         raise RuntimeError(f"link failed:\n{r.stdout}\n{r.stderr}")
     if out == LIB:
-        # the command-line front end (reference binary's arguments and protocol), linked against the library
-        cmd = ["g++", "-O2", "-o", EXE, os.path.join(CSRC, "engine_main.cpp"), "-L" + HERE, "-lbrrr", "-Wl,-rpath,$ORIGIN"]
-        r = subprocess.run(cmd, capture_output=True, text=True)
-        if r.returncode != 0:
-            raise RuntimeError(f"link of brrr_engine failed:\n{r.stdout}\n{r.stderr}")
+        # the command-line front ends (the reference binaries' arguments and protocols), linked against the library
+        for exe, main_src in ((EXE, "engine_main.cpp"), (EXE_QWEN, "engine_qwen_main.cpp")):
+            cmd = ["g++", "-O2", "-o", exe, os.path.join(CSRC, main_src), "-L" + HERE, "-lbrrr", "-Wl,-rpath,$ORIGIN"]
+            r = subprocess.run(cmd, capture_output=True, text=True)
+            if r.returncode != 0:
+                raise RuntimeError(f"link of {os.path.basename(exe)} failed:\n{r.stdout}\n{r.stderr}")
     return out
 
 

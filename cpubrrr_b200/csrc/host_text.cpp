@@ -324,6 +324,86 @@ extern "C" int brrr_serve_parse(const char *line, float *temp, uint64_t *seed, u
     return 1;
 }
 
+// ---------------------------------------------------------------- qwen3moe: ChatML prompt, generate, serve line (engine_qwen2.rs:622-683)
+// Prompt ids: <|im_start|> "system\nYou are a helpful assistant." <|im_end|> <|im_start|> "\nuser\n" + text
+// <|im_end|> <|im_start|> "\nassistant\n"; text pieces go through the greedy longest-match encoder with a
+// 48-byte window (engine_qwen2.rs:500-505); the special tokens are looked up by their literal spelling.
+extern "C" int brrr_qwen_chat_prompt(const brrr_tokenizer *t, const char *user_text, uint32_t *out, size_t cap, size_t *n_out) {
+    if (!t || !user_text || !n_out) return BRRR_ERR_ARG;
+    uint32_t im_start = 0, im_end = 0;
+    if (brrr_tokenizer_special(t, "<|im_start|>", &im_start) != BRRR_OK || brrr_tokenizer_special(t, "<|im_end|>", &im_end) != BRRR_OK) return BRRR_ERR_IO;
+    std::vector<uint32_t> ids;
+    auto enc = [&](const std::string &s) -> int {
+        size_t n = 0;
+        int st = brrr_tokenizer_encode(t, s.data(), s.size(), 48, nullptr, 0, &n);
+        if (st != BRRR_OK) return st;
+        size_t at = ids.size();
+        ids.resize(at + n);
+        return brrr_tokenizer_encode(t, s.data(), s.size(), 48, ids.data() + at, n, &n);
+    };
+    int st;
+    ids.push_back(im_start);
+    if ((st = enc("system\nYou are a helpful assistant.")) != BRRR_OK) return st;
+    ids.push_back(im_end);
+    ids.push_back(im_start);
+    if ((st = enc(std::string("\nuser\n") + user_text)) != BRRR_OK) return st;
+    ids.push_back(im_end);
+    ids.push_back(im_start);
+    if ((st = enc("\nassistant\n")) != BRRR_OK) return st;
+    *n_out = ids.size();
+    if (out) {
+        if (ids.size() > cap) return BRRR_ERR_RANGE;
+        memcpy(out, ids.data(), ids.size() * 4);
+    }
+    return BRRR_OK;
+}
+
+// Token-by-token prefill, then greedy decode until <|im_end|>, a token id beyond the vocabulary file,
+// ngen tokens or the context limit (engine_qwen2.rs:632-650).  Decoding runs on the device in bursts.
+extern "C" int brrr_qwen_generate(brrr_qwen *m, const brrr_tokenizer *t, const uint32_t *ids, size_t n_ids, uint32_t ngen,
+                                  void (*emit)(const char *, uint32_t, void *), void *emit_arg, uint32_t *out_ids, size_t out_cap,
+                                  brrr_gen_stats *stats) {
+    if (!m || !t || !ids || n_ids == 0) return BRRR_ERR_ARG;
+    if (n_ids >= BRRR_MAXSEQ) return BRRR_ERR_RANGE;
+    uint32_t im_end = 0;
+    if (brrr_tokenizer_special(t, "<|im_end|>", &im_end) != BRRR_OK) return BRRR_ERR_IO;
+    const uint32_t ntok = brrr_tokenizer_size(t);
+    auto t0 = std::chrono::steady_clock::now();
+    uint32_t next = 0;
+    int st;
+    for (size_t i = 0; i < n_ids; i++)
+        if ((st = brrr_qwen_forward(m, ids[i], (uint32_t)i, i + 1 == n_ids, &next)) != BRRR_OK) return st;
+    auto t1 = std::chrono::steady_clock::now();
+    size_t pos = n_ids;
+    uint32_t n = 0;
+    auto stop = [&](uint32_t tok) { return tok == im_end || tok >= ntok; };
+    std::vector<uint32_t> burst(32);
+    while (n < ngen && !stop(next) && pos + 1 < BRRR_MAXSEQ) {
+        uint32_t want = ngen - n < 32 ? ngen - n : 32;
+        if (pos + want >= BRRR_MAXSEQ) want = (uint32_t)(BRRR_MAXSEQ - 1 - pos);
+        if (want == 0) break;
+        if ((st = brrr_qwen_decode(m, next, (uint32_t)pos, want, burst.data())) != BRRR_OK) return st;
+        for (uint32_t used = 0; used < want; used++) {
+            if (out_ids && n < out_cap) out_ids[n] = next;
+            if (emit) {
+                const char *b; uint32_t l;
+                if (brrr_tokenizer_token(t, next, &b, &l) == BRRR_OK) emit(b, l, emit_arg);
+            }
+            n++; pos++;
+            next = burst[used];
+            if (n >= ngen || stop(next) || pos + 1 >= BRRR_MAXSEQ) break;      // steps the device ran beyond this one are discarded
+        }
+    }
+    auto t2 = std::chrono::steady_clock::now();
+    if (stats) {
+        stats->prefill_tokens = (uint32_t)n_ids;
+        stats->decode_tokens = n;
+        stats->prefill_seconds = std::chrono::duration<double>(t1 - t0).count();
+        stats->decode_seconds = std::chrono::duration<double>(t2 - t1).count();
+    }
+    return BRRR_OK;
+}
+
 static void emit_stdout(const char *b, uint32_t l, void *) {
     fwrite(b, 1, l, stdout);
     fflush(stdout);
@@ -380,6 +460,102 @@ extern "C" int brrr_cli_main(int argc, char **argv) {
         rc = run(prompt, ngen ? ngen : 96, 0, false) == BRRR_OK ? 0 : 1;
     }
     brrr_model_close(m);
+    brrr_tokenizer_close(tok);
+    return rc;
+}
+
+// One request line of the qwen3moe serve loop (engine_qwen2.rs:664-673): the line is trimmed; if it
+// splits into four tab-separated fields and the third is a count, that is ngen and the fourth is the
+// prompt with every "\\n" and "\\t" turned into a SPACE (temperature and seed are accepted and ignored:
+// this engine is greedy only); otherwise the whole line is the prompt.  Returns 1 / 0, -1 for an empty line.
+extern "C" int brrr_qwen_serve_parse(const char *line, uint32_t *ngen, char *prompt, size_t prompt_cap) {
+    if (!line || !prompt || prompt_cap == 0) return -1;
+    std::string s(line);
+    auto ws = [](char c) { return c == ' ' || c == '\t' || c == '\n' || c == '\r' || c == '\f' || c == '\v'; };
+    while (!s.empty() && ws(s.back())) s.pop_back();
+    size_t b = 0;
+    while (b < s.size() && ws(s[b])) b++;
+    s = s.substr(b);
+    if (s.empty()) return -1;
+    size_t p1 = s.find('\t'), p2 = p1 == std::string::npos ? p1 : s.find('\t', p1 + 1), p3 = p2 == std::string::npos ? p2 : s.find('\t', p2 + 1);
+    if (p3 != std::string::npos) {
+        std::string f2 = s.substr(p2 + 1, p3 - p2 - 1);
+        size_t i = !f2.empty() && f2[0] == '+' ? 1 : 0;
+        bool num = i < f2.size();
+        unsigned long long v = 0;
+        for (size_t k = i; k < f2.size() && num; k++) {
+            if (f2[k] < '0' || f2[k] > '9') num = false;
+            else if ((v = v * 10 + (unsigned)(f2[k] - '0')) > (1ull << 40)) v = 1ull << 40;
+        }
+        if (num) {
+            std::string f3 = s.substr(p3 + 1), un;
+            for (size_t k = 0; k < f3.size(); k++) {
+                if (f3[k] == '\\' && k + 1 < f3.size() && (f3[k + 1] == 'n' || f3[k + 1] == 't')) { un.push_back(' '); k++; }
+                else un.push_back(f3[k]);
+            }
+            if (ngen) *ngen = (uint32_t)(v > BRRR_MAXSEQ ? BRRR_MAXSEQ : v);
+            snprintf(prompt, prompt_cap, "%s", un.c_str());
+            return 1;
+        }
+    }
+    snprintf(prompt, prompt_cap, "%s", s.c_str());
+    return 0;
+}
+
+// The qwen3moe reference binary's command line (engine_qwen2.rs:486-489, 622-683):
+// <data-dir> <blob> [prompt|--serve] [ngen]; default ngen 64 (256 when serving).
+extern "C" int brrr_qwen_cli_main(int argc, char **argv) {
+    if (argc < 3) { fprintf(stderr, "usage: %s <data-dir> <blob> [prompt|--serve] [ngen]\n", argv[0]); return 2; }
+    const char *dir = argv[1], *blob = argv[2];
+    std::string prompt = argc > 3 ? argv[3] : "Write a haiku about CPUs.";
+    const bool serve = prompt == "--serve";
+    uint32_t ngen_default = serve ? 256 : 64;
+    if (argc > 4) { char *end = nullptr; unsigned long v = strtoul(argv[4], &end, 10); if (end && *end == 0 && argv[4][0]) ngen_default = (uint32_t)v; }
+    brrr_tokenizer *tok = nullptr;
+    if (brrr_tokenizer_open(dir, &tok) != BRRR_OK) { fprintf(stderr, "cannot read %s/tokens.bin\n", dir); return 1; }
+    fprintf(stderr, "loading blob...\n");
+    brrr_qwen *m = nullptr;
+    int st = brrr_qwen_open(dir, blob, 0, &m);
+    if (st != BRRR_OK) { fprintf(stderr, "model open failed: %s (%s)\n", brrr_strerror(st), brrr_last_cuda_error()); return 1; }
+    auto run = [&](const std::string &text, uint32_t ngen, brrr_gen_stats *gs) -> int {
+        size_t n = 0;
+        int s2 = brrr_qwen_chat_prompt(tok, text.c_str(), nullptr, 0, &n);
+        if (s2 != BRRR_OK) { fprintf(stderr, "prompt not encodable\n"); return s2; }
+        std::vector<uint32_t> ids(n);
+        brrr_qwen_chat_prompt(tok, text.c_str(), ids.data(), n, &n);
+        fprintf(stderr, "prompt: %zu tokens\n", n);
+        s2 = brrr_qwen_generate(m, tok, ids.data(), n, ngen, emit_stdout, nullptr, nullptr, 0, gs);
+        if (s2 != BRRR_OK) fprintf(stderr, "generate failed: %s (%s)\n", brrr_strerror(s2), brrr_last_cuda_error());
+        return s2;
+    };
+    int rc = 0;
+    if (serve) {
+        fprintf(stderr, "[READY]\n");
+        char *line = nullptr;
+        size_t cap = 0;
+        ssize_t got;
+        std::vector<char> ptext;
+        while ((got = getline(&line, &cap, stdin)) >= 0) {
+            uint32_t ngen = 0;
+            ptext.assign((size_t)got + 2, 0);
+            int form = brrr_qwen_serve_parse(line, &ngen, ptext.data(), ptext.size());
+            if (form < 0) continue;
+            brrr_gen_stats gs{};
+            if (run(ptext.data(), form == 1 ? ngen : ngen_default, &gs) != BRRR_OK) { rc = 1; break; }
+            // the reference prints prefill_tok=0 here (engine_qwen2.rs:677)
+            printf("\n[STATS] prefill_tok=0 prefill_s=%.3f decode_tok=%u decode_s=%.3f tok_s=%.1f\n[DONE]\n", gs.prefill_seconds, gs.decode_tokens,
+                   gs.decode_seconds, gs.decode_seconds > 0 ? gs.decode_tokens / gs.decode_seconds : 0.0);
+            fflush(stdout);
+        }
+        free(line);
+    } else {
+        brrr_gen_stats gs{};
+        rc = run(prompt, ngen_default, &gs) == BRRR_OK ? 0 : 1;
+        if (rc == 0)
+            printf("\n---\ndecode: %u tokens in %.2fs = %.1f tok/s\n", gs.decode_tokens, gs.decode_seconds,
+                   gs.decode_seconds > 0 ? gs.decode_tokens / gs.decode_seconds : 0.0);
+    }
+    brrr_qwen_close(m);
     brrr_tokenizer_close(tok);
     return rc;
 }

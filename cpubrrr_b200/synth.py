@@ -225,7 +225,7 @@ def write_gguf(path, cfg, seed, tokens=None, arch="gpt-oss", ktypes=None):
     kv_u32(f"{arch}.vocab_size", cfg.n_vocab)
     kv_u32(f"{arch}.context_length", 4096)
     if tokens is None:
-        tokens = default_tokens(cfg.n_vocab)
+        tokens = default_tokens(cfg.n_vocab, arch)
     arr = struct.pack("<IQ", 8, len(tokens)) + b"".join(_gguf_str(t) for t in tokens)
     kv.append(_gguf_str("tokenizer.ggml.tokens") + struct.pack("<I", 9) + arr)
 
@@ -257,26 +257,30 @@ def _byte_spelling():
     return table
 
 
-def raw_tokens(n_vocab):
+_SPECIALS = {"gpt-oss": (b"<|start|>", b"<|end|>", b"<|message|>", b"<|return|>"),
+             "qwen3moe": (b"<|endoftext|>", b"<|im_start|>", b"<|im_end|>", b"<|fim_pad|>")}
+
+
+def raw_tokens(n_vocab, arch="gpt-oss"):
     """Toy vocabulary as the raw byte strings tokens.bin holds: the 256 single bytes, then short
-    words "w0", "w1", ...; the last four entries are special tokens (spelled with '<|', which the
-    engine's lookup skips)."""
+    words "w0", "w1", ...; the last four entries are special tokens of the architecture's chat
+    format (spelled with '<|', which the engine's lookup skips)."""
     toks = [bytes([b]) for b in range(256)]
     i = 0
     while len(toks) < n_vocab - 4:
         toks.append(f"w{i}".encode())
         i += 1
-    for s in (b"<|start|>", b"<|end|>", b"<|message|>", b"<|return|>"):
+    for s in _SPECIALS[arch]:
         if len(toks) < n_vocab:
             toks.append(s)
     return toks[:n_vocab]
 
 
-def default_tokens(n_vocab):
+def default_tokens(n_vocab, arch="gpt-oss"):
     """The toy vocabulary in its GGUF spelling (UTF-8 of the byte-level characters; special tokens
     literal)."""
     sp = _byte_spelling()
-    return [t if t.startswith(b"<|") else "".join(sp[b] for b in t).encode("utf-8") for t in raw_tokens(n_vocab)]
+    return [t if t.startswith(b"<|") else "".join(sp[b] for b in t).encode("utf-8") for t in raw_tokens(n_vocab, arch)]
 
 
 def write_tokens_bin(path, toks):

@@ -236,6 +236,26 @@ void *brrr_qwen_stream(brrr_qwen *m);
 int brrr_qwen_launches_per_step(const brrr_qwen *m, int want_logits);
 uint64_t brrr_qwen_bytes_per_step(const brrr_qwen *m, uint32_t pos);
 
+/* ChatML prompt ids of the qwen3moe engine: im_start "system\nYou are a helpful assistant." im_end im_start
+ * "\nuser\n" + text im_end im_start "\nassistant\n", text pieces through brrr_tokenizer_encode with a 48-byte
+ * window, the two special tokens looked up by spelling (BRRR_ERR_IO when the vocabulary lacks them).
+ * Replaces the prompt builder of generate (src/bin/engine_qwen2.rs:627-631, 500-505). */
+int brrr_qwen_chat_prompt(const brrr_tokenizer *t, const char *user_text, uint32_t *out, size_t cap, size_t *n_out);
+/* Token-by-token prefill, then greedy decode until <|im_end|>, an id beyond the vocabulary file, ngen tokens
+ * or the context limit; emit (nullable) gets the bytes of every produced token, out_ids (nullable) the ids.
+ * Replaces generate (src/bin/engine_qwen2.rs:626-650). */
+int brrr_qwen_generate(brrr_qwen *m, const brrr_tokenizer *t, const uint32_t *ids, size_t n_ids, uint32_t ngen,
+                       void (*emit)(const char *, uint32_t, void *), void *emit_arg, uint32_t *out_ids, size_t out_cap,
+                       brrr_gen_stats *stats);
+/* One request line of the qwen3moe serve loop: trimmed; `temp \t seed \t ngen \t prompt` (returns 1: ngen taken,
+ * "\n" and "\t" escapes of the prompt become spaces, temp and seed ignored - the engine is greedy only) or a
+ * bare prompt (returns 0); -1 for an empty line (src/bin/engine_qwen2.rs:659-673). */
+int brrr_qwen_serve_parse(const char *line, uint32_t *ngen, char *prompt, size_t prompt_cap);
+/* main() of the qwen3moe engine binary: <data-dir> <blob> [prompt|--serve] [ngen] (default 64, 256 when
+ * serving); [READY] on stderr, streamed tokens, "[STATS] prefill_tok=0 ..." and "[DONE]" on stdout
+ * (src/bin/engine_qwen2.rs:486-489, 622-683). */
+int brrr_qwen_cli_main(int argc, char **argv);
+
 /* ---------------------------------------------------------------- stage-level entry points
  * Device pointers in, device pointers out.  They launch the same kernels the forward pass uses. */
 

@@ -121,3 +121,52 @@ def serve_parse(line):
                 out.append(ch)
         return True, max(temp, 0.0), seed, min(max(ngen, 1), 4096), "".join(out)
     return False, 0.0, 0, 0, pline
+
+
+# ---- qwen3moe host layer (src/bin/engine_qwen2.rs:493-507, 622-683) ---------------------------------
+
+def special_ids(toks):
+    """Literal spelling -> id of the tokens that start with '<|' (the reference's `spm` map; the last one wins)."""
+    return {t: i for i, t in enumerate(toks) if t.startswith(b"<|")}
+
+
+def qwen_chat_prompt(toks, user_text):
+    """ChatML prompt ids; text pieces use the 48-byte encode window (engine_qwen2.rs:500-505, 627-631)."""
+    lookup, spm = make_lookup(toks), special_ids(toks)
+    im_start, im_end = spm[b"<|im_start|>"], spm[b"<|im_end|>"]
+    ids = [im_start] + encode(lookup, "system\nYou are a helpful assistant.", 48) + [im_end]
+    ids += [im_start] + encode(lookup, "\nuser\n" + user_text, 48) + [im_end]
+    ids += [im_start] + encode(lookup, "\nassistant\n", 48)
+    return ids
+
+
+def qwen_serve_parse(line):
+    """(is_tsv, ngen or None, prompt) of one request line, None for an empty one (engine_qwen2.rs:659-673):
+    temp and seed fields are not even parsed; "\\n" and "\\t" in the prompt become spaces."""
+    ptext = line.strip()
+    if not ptext:
+        return None
+    parts = ptext.split("\t", 3)
+    if len(parts) == 4:
+        f = parts[2]
+        digits = f[1:] if f.startswith("+") else f
+        if digits.isascii() and digits.isdigit():
+            return True, min(int(digits), 4096), parts[3].replace("\\n", " ").replace("\\t", " ")
+    return False, None, ptext
+
+
+def qwen_generate(run, toks, ids, ngen):
+    """Greedy generation as the reference's generate closure: token-by-token prefill, stop on <|im_end|>
+    or an id beyond the vocabulary file; returns the produced ids."""
+    im_end, ntok = special_ids(toks)[b"<|im_end|>"], len(toks)
+    nxt = 0
+    for i, t in enumerate(ids):
+        nxt = run(t, i, True)
+    pos, out = len(ids), []
+    for _ in range(ngen):
+        if nxt == im_end or nxt >= ntok:
+            break
+        out.append(nxt)
+        nxt = run(nxt, pos, True)
+        pos += 1
+    return out

@@ -81,7 +81,7 @@ def make_data_dir(out_dir, cfg, seed, case, arch="gpt-oss", ktypes=None):
         assert os.path.isdir(gold), f"no reference checkout and no committed data directory for case {case}"
         for f in ("config.txt", "manifest.txt"):
             shutil.copy(os.path.join(gold, f), os.path.join(out_dir, f))
-        S.write_tokens_bin(os.path.join(out_dir, "tokens.bin"), S.raw_tokens(cfg.n_vocab))
+        S.write_tokens_bin(os.path.join(out_dir, "tokens.bin"), S.raw_tokens(cfg.n_vocab, arch))
         assert _sha(os.path.join(out_dir, "tokens.bin")) == open(os.path.join(gold, "tokens.sha256")).read().strip()
     # the manifest must describe the blob that was just written
     rows = open(os.path.join(out_dir, "manifest.txt")).read().split("\n")

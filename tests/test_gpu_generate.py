@@ -114,3 +114,83 @@ def test_engine_binary_serve_protocol(brrr, orc, tmp_path):
         body, stats = chunk.rsplit("\n[STATS] ", 1)
         assert f"prefill_tok={len(ids)} " in stats and f"decode_tok={len(want)} " in stats
         assert body.encode("utf-8", "replace") == b"".join(toks[t] for t in want).decode("utf-8", "replace").encode("utf-8", "replace")
+
+
+# ---- qwen3moe: ChatML generate, the engine binary, and the reference's own HTTP front end -----------
+
+def test_qwen_generate_and_binary_serve_protocol(brrr, orc, tmp_path):
+    """brrr_qwen_generate and `brrr_engine_qwen <data-dir> <blob> --serve` on a synthetic qwen3moe data
+    directory whose vocabulary holds the ChatML special tokens: prompt ids, produced ids, streamed text and
+    the [STATS] / [DONE] lines equal what the oracle generates (src/bin/engine_qwen2.rs:622-683: greedy
+    only, stop on <|im_end|>, prefill_tok=0 in the stats line, escapes of a TSV prompt become spaces)."""
+    import refdata
+    from oracle import oracle_host as H
+    cfg, d, blob = refdata.case_data_dir(str(tmp_path / "q"), "qwen_d256", 41)
+    toks = H.load_tokens(os.path.join(d, "tokens.bin"))
+    om = orc.QwenModel.open(d, blob)
+    L = brrr.lib()
+    tok = C.c_void_p()
+    assert L.brrr_tokenizer_open(d.encode(), C.byref(tok)) == 0
+    eng = brrr.QwenEngine.open(d, blob)
+    for text, ngen in (("w1 w2 w3", 40), ("Write a haiku about CPUs.", 33)):
+        n = C.c_size_t()
+        assert L.brrr_qwen_chat_prompt(tok, text.encode(), None, 0, C.byref(n)) == 0
+        ids = np.zeros(n.value, np.uint32)
+        assert L.brrr_qwen_chat_prompt(tok, text.encode(), ids.ctypes.data, n.value, C.byref(n)) == 0
+        assert ids.tolist() == H.qwen_chat_prompt(toks, text)
+        want = H.qwen_generate(om.run, toks, ids.tolist(), ngen)
+        out = np.zeros(ngen + 1, np.uint32)
+        st = Stats()
+        assert L.brrr_qwen_generate(eng._h, tok, ids.ctypes.data, ids.size, ngen, None, None, out.ctypes.data, out.size, C.byref(st)) == 0
+        assert [int(t) for t in out[:st.decode_tokens]] == want and st.prefill_tokens == ids.size
+    eng.close()
+    L.brrr_tokenizer_close(tok)
+    exe = os.path.join(os.path.dirname(brrr.__file__), "brrr_engine_qwen")
+    req = "w1 w2 w3\n0.8\t7\t5\tw3 w4\\nw5\n"
+    r = subprocess.run([exe, d, blob, "--serve", "24"], input=req.encode(), capture_output=True, timeout=300)
+    assert r.returncode == 0, r.stderr.decode()
+    assert b"[READY]" in r.stderr
+    out = r.stdout.decode("utf-8", "replace")
+    assert out.count("[DONE]") == 2 and out.count("[STATS]") == 2
+    first, second = out.split("[DONE]\n")[:2]
+    for text, ngen, chunk in (("w1 w2 w3", 24, first), ("w3 w4 w5", 5, second)):
+        want = H.qwen_generate(om.run, toks, H.qwen_chat_prompt(toks, text), ngen)
+        body, stats = chunk.rsplit("\n[STATS] ", 1)
+        assert "prefill_tok=0 " in stats and f"decode_tok={len(want)} " in stats
+        assert body.encode("utf-8", "replace") == b"".join(toks[t] for t in want).decode("utf-8", "replace").encode("utf-8", "replace")
+    om.close()
+
+
+def test_reference_openai_server_drives_the_engine_binaries(brrr, orc, tmp_path):
+    """The reference's own HTTP front end (scripts/openai_server.py, class Engine, lines 34-90) spawns an
+    engine binary with `<data-dir> <blob> --serve` and talks to it over the pipe.  Here it is imported
+    unmodified from the reference checkout (skipped where there is none), pointed at brrr_engine and
+    brrr_engine_qwen, and its request() must return the text and the [STATS] fields the oracle predicts."""
+    import importlib.util
+    import refdata
+    from oracle import oracle_host as H
+    src = os.path.join(refdata.REF, "scripts", "openai_server.py")
+    if not os.path.exists(src):
+        pytest.skip("reference checkout not present")
+    spec = importlib.util.spec_from_file_location("ref_openai_server", src)
+    mod = importlib.util.module_from_spec(spec)
+    spec.loader.exec_module(mod)                       # defines Engine; starts nothing (no engines found under its ROOT)
+    bindir = os.path.dirname(brrr.__file__)
+    for case, seed, exe, qwen in (("gptoss_serve", 37, "brrr_engine", False), ("qwen_d256", 41, "brrr_engine_qwen", True)):
+        cfg, d, blob = refdata.case_data_dir(str(tmp_path / case), case, seed)
+        toks = H.load_tokens(os.path.join(d, "tokens.bin"))
+        om = (orc.QwenModel if qwen else orc.Model).open(d, blob)
+        eng = mod.Engine({"id": "test/" + case, "bin": os.path.join(bindir, exe), "data": d})
+        with eng.lock:
+            eng.ensure()
+            got = []
+            stats = eng.request("w3 w4\nw5", 6, 0.0, got.append)
+        eng.proc.stdin.close()
+        eng.proc.wait(timeout=60)
+        if qwen:
+            want = H.qwen_generate(om.run, toks, H.qwen_chat_prompt(toks, "w3 w4 w5"), 6)
+        else:
+            want = oracle_generate(orc, om, H.chat_prompt(H.make_lookup(toks), "w3 w4\nw5"), 6)
+        assert "".join(got) == b"".join(toks[t] for t in want).decode("utf-8", "replace")
+        assert int(stats["decode_tok"]) == len(want) and stats["tok_s"] >= 0
+        om.close()

@@ -135,3 +135,58 @@ def test_chat_prompt_ids(L, orc, tokdir):
     assert [int(v) for v in out] == H.chat_prompt(lookup, text)
     assert L.brrr_chat_prompt(h, text.encode(), out.ctypes.data, 3, C.byref(n)) == 5
     L.brrr_tokenizer_close(h)
+
+
+# ---- qwen3moe host layer ----------------------------------------------------------------------------
+
+@pytest.fixture(scope="module")
+def qtokdir(tmp_path_factory):
+    """tokens.bin of the qwen toy vocabulary (ChatML special tokens at the end) with a few long pieces."""
+    d = tmp_path_factory.mktemp("qtok")
+    toks = S.raw_tokens(700, "qwen3moe")
+    toks[300] = b"You are a helpful assistant."
+    toks[301] = b"\nuser\n"
+    toks[302] = b"y" * 45                # inside the 48-byte window of this engine, beyond the 32 of the other
+    toks[303] = b"z" * 50                # beyond it
+    S.write_tokens_bin(str(d / "tokens.bin"), toks)
+    return str(d)
+
+
+def test_qwen_chat_prompt_matches_reference_restatement(L, qtokdir):
+    from oracle import oracle_host as H
+    toks = H.load_tokens(os.path.join(qtokdir, "tokens.bin"))
+    h = _open(L, qtokdir)
+    for text in ["Write a haiku about CPUs.", "y" * 45 + " and " + "z" * 50, "", "tabs\tand\nnewlines w12 w13"]:
+        n = C.c_size_t()
+        assert L.brrr_qwen_chat_prompt(h, text.encode(), None, 0, C.byref(n)) == 0
+        ids = np.zeros(n.value, np.uint32)
+        assert L.brrr_qwen_chat_prompt(h, text.encode(), ids.ctypes.data, n.value, C.byref(n)) == 0
+        want = H.qwen_chat_prompt(toks, text)
+        assert ids.tolist() == want
+        assert ids[0] == len(toks) - 3 and want.count(len(toks) - 2) == 2          # im_start first, two im_end
+    assert 302 in H.qwen_chat_prompt(toks, "y" * 45)                                  # the 45-byte piece is found in one step
+    L.brrr_tokenizer_close(h)
+
+
+def test_qwen_chat_prompt_needs_the_chatml_tokens(L, tokdir):
+    h = _open(L, tokdir)                 # the gpt-oss toy vocabulary has no <|im_start|>
+    n = C.c_size_t()
+    assert L.brrr_qwen_chat_prompt(h, b"hi", None, 0, C.byref(n)) == 2
+    L.brrr_tokenizer_close(h)
+
+
+def test_qwen_serve_parse(L):
+    from oracle import oracle_host as H
+    lines = ["  hello there  \n", "\n", "   ", "0.7\t5\t12\tline one\\nline two\\tend\n", "x\ty\t7\tnot validated\n", "0\t1\tseven\ta b\n",
+             "0\t1\t+9\tplus\n", "a\tb\tc\n", "0\t1\t99999\tbig\n", "0\t1\t3\ttabs\tin\tprompt\\\\n\n"]
+    for line in lines:
+        ngen = C.c_uint32(0)
+        buf = C.create_string_buffer(256)
+        form = L.brrr_qwen_serve_parse(line.encode(), C.byref(ngen), buf, 256)
+        want = H.qwen_serve_parse(line)
+        if want is None:
+            assert form == -1
+            continue
+        assert form == int(want[0]) and buf.value.decode() == want[2], line
+        if want[0]:
+            assert ngen.value == want[1]
