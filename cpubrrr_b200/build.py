@@ -25,7 +25,7 @@ HOOKS_LIB = os.path.join(HERE, "libbrrr_hooks.so")
 EXE = os.path.join(HERE, "brrr_engine")
 EXE_QWEN = os.path.join(HERE, "brrr_engine_qwen")
 
-SOURCES = ["kernels_small.cu", "kernels_q8.cu", "kernels_mx.cu", "kernels_router.cu", "kernels_attn.cu", "kernels_ep.cu", "kernels_tile.cu", "kernels_mxt.cu", "kernels_kq.cu", "kernels_qwen.cu", "qwen_model.cu",
+SOURCES = ["kernels_small.cu", "kernels_q8.cu", "kernels_mx.cu", "kernels_router.cu", "kernels_attn.cu", "kernels_ep.cu", "kernels_tile.cu", "kernels_rows.cu", "kernels_mxt.cu", "kernels_kq.cu", "kernels_qwen.cu", "qwen_model.cu",
            "model.cu", "capi_stage.cu", "capi_noalloc.cu", "host_text.cpp"]
 
 NVCC_FLAGS = [

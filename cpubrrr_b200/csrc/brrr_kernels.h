@@ -8,7 +8,15 @@ namespace brrr {
 
 // ---- elementwise / small stages (kernels_small.cu)
 void launch_quant_q8(const float *x, int n, int8_t *q, float *s, cudaStream_t st);
-cudaError_t launch_rmsnorm_quant(const float *x, const float *w, float eps, int n, float *xn, int8_t *q, float *s, bool pdl, cudaStream_t st);
+// rows > 1: one CTA per row; rows are n apart in x / xn / q and n / 32 apart in s
+cudaError_t launch_rmsnorm_quant(const float *x, const float *w, float eps, int n, float *xn, int8_t *q, float *s, bool pdl, cudaStream_t st,
+                                 int rows = 1);
+// ---- token rows (kernels_rows.cu): y[t][r] (+)= row r of m . activation t (+ bias), t < ntok <= 16
+cudaError_t launch_q8_rows(Q8Dev m, const int8_t *xq, const float *xs, int ntok, const float *bias, float *y, int ldy, int epi, bool pdl,
+                           cudaStream_t st);
+// RoPE of every row's k and the cache append of k and v (row t: position row_pos[t] of sequence row_seq[t])
+cudaError_t launch_kv_append_rows(const float *qkv, int ldq, int nh, int nkv, float *kc, float *vc, size_t seq_stride, const float *rope,
+                                  const int *row_pos, const int *row_seq, int rows, bool pdl, cudaStream_t st);
 void launch_embed(const uint16_t *embd, int d, const DevState *state, float *x, cudaStream_t st);
 void launch_embed_tok(const uint16_t *embd, int d, uint32_t tok, float *x, cudaStream_t st);
 // ntok rows from token ids in device memory: x[t] = embedding of toks[t]
@@ -182,7 +190,9 @@ cudaError_t launch_router_hint(const float *x_in, const float *norm_w, float eps
 // else pos_val.  window = 0 means full attention.
 cudaError_t launch_attn_decode(const float *qkv, float *kc, float *vc, const float *rope, const float *sinks, int nh, int nkv,
                                const DevState *state, int pos_val, int window, float *ao, int8_t *aq, float *as,
-                               DevState *err_state, bool pdl, cudaStream_t st, int pos_off = 0);
+                               DevState *err_state, bool pdl, cudaStream_t st, int pos_off = 0, const int *row_pos = nullptr,
+                               const int *row_seq = nullptr, size_t seq_stride = 0, int ldq = 0, int rows = 1);
+// row_pos != nullptr: `rows` tokens in one launch (grid.y), see AttnArgs in kernels_attn.cu; the rows' k / v must be in the cache already
 // pos_off is added to the position read from state (ignored with pos_val)
 
 }  // namespace brrr

@@ -36,6 +36,13 @@ struct AttnArgs {
     int8_t *aq;
     float *as;
     DevState *err_state;
+    // token rows (grid.y = rows; nullptr: one token): row t attends at position row_pos[t] of sequence
+    // row_seq[t] (caches seq_stride floats apart); its q | k | v are ldq floats after the previous row's,
+    // its outputs nh * 64 values after it.  The cached positions may then have been written by the kernel
+    // just before this one (earlier rows of the same sequence), so they are fetched after the dependency wait.
+    const int *row_pos, *row_seq;
+    size_t seq_stride;
+    int ldq;
 };
 
 #ifndef AT_SCORE_UNROLL
@@ -57,10 +64,20 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(AttnArgs a) {
     const int group = a.nh / a.nkv, kvh = h / group;
     uint32_t *err = a.err_state ? &a.err_state->err : nullptr;
     Waiter waiter(err);
+    const bool rows = a.row_pos != nullptr;
+    if (rows) {
+        const int t = blockIdx.y;
+        a.qkv += (size_t)t * a.ldq;
+        a.kc += (size_t)a.row_seq[t] * a.seq_stride;
+        a.vc += (size_t)a.row_seq[t] * a.seq_stride;
+        a.ao += (size_t)t * a.nh * HD;
+        a.aq += (size_t)t * a.nh * HD;
+        a.as += (size_t)t * a.nh * 2;
+    }
 
     // The position is an input of this step (written before the graph launch or by the previous
     // step's last kernel), never by the immediate predecessor, so it may be read before the wait.
-    const int pos = a.state ? (int)a.state->pos + a.pos_off : a.pos_val;
+    const int pos = rows ? a.row_pos[blockIdx.y] : (a.state ? (int)a.state->pos + a.pos_off : a.pos_val);
     const int start = a.window > 0 ? max(pos - (a.window - 1), 0) : 0;
     const int n = pos - start + 1;                  // keys including the current one
     const int ncached = n - 1;                      // keys that come from the cache
@@ -81,7 +98,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(AttnArgs a) {
     }
     __syncwarp();
     // one lane per copy (K and V of the first tiles): their address translations overlap
-    if (tid < 2 * min(AT_SLOTS, ntiles)) {
+    if (!rows && tid < 2 * min(AT_SLOTS, ntiles)) {
         if (tid & 1) issue(vbase, vtiles, vbar, tid >> 1);
         else issue(kbase, ktiles, kbar, tid >> 1);
     }
@@ -95,6 +112,10 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(AttnArgs a) {
     BRRR_GT_GO(a.err_state, 190);
     pdl_trigger();
     waiter.poison_if_failed();
+    if (rows && tid < 2 * min(AT_SLOTS, ntiles)) {
+        if (tid & 1) issue(vbase, vtiles, vbar, tid >> 1);
+        else issue(kbase, ktiles, kbar, tid >> 1);
+    }
 
     // ---- RoPE (NeoX halves, table holds cos*mscale / sin*mscale) on q and k; v passes through
     if (tid < 64) {
@@ -110,7 +131,7 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(AttnArgs a) {
     }
     __syncthreads();
     // the first head of each KV group appends this position to the cache
-    if (h % group == 0 && tid < 128) {
+    if (!rows && h % group == 0 && tid < 128) {        // (token rows: kv_append_rows_kernel has done it for every row)
         size_t o = ((size_t)kvh * BRRR_MAXSEQ + pos) * HD + (tid & 63);
         if (tid < 64) a.kc[o] = kcur[tid]; else a.vc[o] = vcur[tid - 64];
     }
@@ -215,14 +236,15 @@ static size_t attn_smem() { return AT_TILE_BYTES * AT_SLOTS * 2 + (size_t)BRRR_M
 
 cudaError_t launch_attn_decode(const float *qkv, float *kc, float *vc, const float *rope, const float *sinks, int nh, int nkv,
                                const DevState *state, int pos_val, int window, float *ao, int8_t *aq, float *as,
-                               DevState *err_state, bool pdl, cudaStream_t st, int pos_off) {
-    AttnArgs a{qkv, kc, vc, rope, sinks, nh, nkv, state, pos_val, window, pos_off, ao, aq, as, err_state};
+                               DevState *err_state, bool pdl, cudaStream_t st, int pos_off, const int *row_pos, const int *row_seq, size_t seq_stride,
+                               int ldq, int rows) {
+    AttnArgs a{qkv, kc, vc, rope, sinks, nh, nkv, state, pos_val, window, pos_off, ao, aq, as, err_state, row_pos, row_seq, seq_stride, ldq};
     static unsigned long long configured = 0;      // one bit per device
     {
         cudaError_t e = smem_optin(attn_decode_kernel, (int)attn_smem(), configured);
         if (e != cudaSuccess) return e;
     }
-    return launch_k(attn_decode_kernel, dim3(nh), dim3(AT_THREADS), attn_smem(), st, pdl, a);
+    return launch_k(attn_decode_kernel, dim3(nh, row_pos ? rows : 1), dim3(AT_THREADS), attn_smem(), st, pdl, a);
 }
 
 }  // namespace brrr

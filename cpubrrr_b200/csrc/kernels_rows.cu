@@ -1,0 +1,161 @@
+// Token rows: the dense half of a layer for up to 16 tokens at once (prompt tiles and batched decode
+// over independent sequences; forward_tile_worker, src/bin/engine_gpt2.rs:1011-1250, keeps the
+// per-token arithmetic and shares each weight pass among the tokens of a tile).  Every value is
+// computed by the same operation sequence as in the one-token kernels, so results are bit-identical
+// to the token-serial schedule.
+//
+//   rmsnorm_quant (grid = rows)      one CTA per row, the one-token kernel with row offsets (kernels_small.cu)
+//   q8_rows_kernel                   Q8 matrix x the Q8 activations of all rows: the CTA's weights go into
+//                                    registers once (before the dependency wait), the rows' activations into
+//                                    shared memory once, then one chain walk per row
+//   kv_append_rows_kernel            RoPE of every row's k and the cache append of k and v, before any row attends
+//   attn_decode_kernel (grid.y = rows, kernels_attn.cu)
+#include "brrr_kernels.h"
+#include "brrr_block.cuh"
+#include "brrr_tma.cuh"
+
+namespace brrr {
+
+namespace {
+
+constexpr int QR_THREADS = 128;
+
+struct Q8RowsArgs {
+    Q8Dev m;
+    const int8_t *xq;       // [rows][cols]
+    const float *xs;        // [rows][cols / 32]
+    const float *bias;
+    float *y;               // [rows][ldy]
+    int ntok, ldy;
+};
+
+// NP > 0: block pairs per matrix row, weights resident in registers.  NP == 0: any shape, weights read
+// from global memory for every token row (small test shapes).
+template <int EPI, int NP>
+__global__ void __launch_bounds__(QR_THREADS) q8_rows_kernel(Q8RowsArgs a) {
+    extern __shared__ __align__(16) unsigned char rsm[];
+    const int np = NP > 0 ? NP : a.m.cols / 64, nb = np * 2;
+    const int tid = threadIdx.x, rl = tid >> 3, c8 = tid & 7, p = c8 >> 2;
+    const int u = blockIdx.x, row = u * 16 + rl;
+    const uint8_t *unit0 = a.m.data + q8_unit_off(u, 0, np);
+    const int2 *wp = reinterpret_cast<const int2 *>(unit0 + rl * 64 + c8 * 8);
+    const float *sp = reinterpret_cast<const float *>(unit0 + Q8_UNIT_SCALES + rl * 8 + p * 4);
+    int2 w[NP > 0 ? NP : 1];
+    float s[NP > 0 ? NP : 1];
+    if (NP > 0) {
+#pragma unroll
+        for (int i = 0; i < (NP > 0 ? NP : 1); i++) {
+            w[i] = __ldg(wp + (size_t)i * (Q8_UNIT / 8));
+            s[i] = __ldg(sp + (size_t)i * (Q8_UNIT / 4));
+        }
+    }
+    const bool out = c8 == 0 && row < a.m.rows;
+    float bias_pre = 0.0f;
+    if (out && (EPI == Q8_EPI_BIAS || EPI == Q8_EPI_RESID_BIAS)) bias_pre = a.bias[row];
+    pdl_wait();
+    pdl_trigger();
+    // the activation images of all rows: [row][np * 8] int2 then [row][nb] floats
+    int2 *xp = reinterpret_cast<int2 *>(rsm);
+    float *xsc = reinterpret_cast<float *>(xp + (size_t)a.ntok * np * 8);
+    const int nidx = np * 8;
+    for (int i = tid; i < a.ntok * nidx; i += QR_THREADS) {
+        const int t = i / nidx, idx = i % nidx;
+        const int *xw = reinterpret_cast<const int *>(a.xq + (size_t)t * a.m.cols + (idx >> 2) * 32);
+        xp[i] = make_int2(xw[idx & 3], xw[4 + (idx & 3)]);
+    }
+    for (int i = tid; i < a.ntok * nb; i += QR_THREADS) xsc[i] = a.xs[i];
+    __syncthreads();
+    for (int t = 0; t < a.ntok; t++) {
+        const int2 *xpt = xp + (size_t)t * nidx + c8;
+        const float *xst = xsc + (size_t)t * nb + p;
+        float acc = 0.0f;
+        if (NP > 0) {
+#pragma unroll
+            for (int i = 0; i < (NP > 0 ? NP : 1); i++) {
+                const int2 xv = xpt[i * 8];
+                const int d = __dp4a(w[i].y, xv.y, __dp4a(w[i].x, xv.x, 0));
+                acc = __fmaf_rn((float)d, __fmul_rn(s[i], xst[i * 2]), acc);
+            }
+        } else {
+            for (int i = 0; i < np; i++) {
+                const int2 wv = __ldg(wp + (size_t)i * (Q8_UNIT / 8));
+                const float sv = __ldg(sp + (size_t)i * (Q8_UNIT / 4));
+                const int2 xv = xpt[i * 8];
+                const int d = __dp4a(wv.y, xv.y, __dp4a(wv.x, xv.x, 0));
+                acc = __fmaf_rn((float)d, __fmul_rn(sv, xst[i * 2]), acc);
+            }
+        }
+        float r = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 4));      // acc_even + acc_odd per lane, then (l0+l1)+(l2+l3)
+        r = brrr_hsum4(r);
+        if (out) {
+            float *yp = a.y + (size_t)t * a.ldy + row;
+            if (EPI == Q8_EPI_PLAIN) *yp = r;
+            else if (EPI == Q8_EPI_BIAS) *yp = __fadd_rn(r, bias_pre);
+            else *yp = __fadd_rn(*yp, __fadd_rn(r, bias_pre));                // x += dot + bias
+        }
+    }
+}
+
+template <int NP>
+cudaError_t q8_rows_launch(const Q8RowsArgs &a, int epi, unsigned grid, size_t smem, bool pdl, cudaStream_t st) {
+    static unsigned long long configured[3] = {0, 0, 0};
+    cudaError_t e;
+    switch (epi) {
+    case Q8_EPI_PLAIN:
+        if ((e = smem_optin(q8_rows_kernel<Q8_EPI_PLAIN, NP>, 160 * 1024, configured[0])) != cudaSuccess) return e;
+        return launch_k(q8_rows_kernel<Q8_EPI_PLAIN, NP>, dim3(grid), dim3(QR_THREADS), smem, st, pdl, a);
+    case Q8_EPI_BIAS:
+        if ((e = smem_optin(q8_rows_kernel<Q8_EPI_BIAS, NP>, 160 * 1024, configured[1])) != cudaSuccess) return e;
+        return launch_k(q8_rows_kernel<Q8_EPI_BIAS, NP>, dim3(grid), dim3(QR_THREADS), smem, st, pdl, a);
+    case Q8_EPI_RESID_BIAS:
+        if ((e = smem_optin(q8_rows_kernel<Q8_EPI_RESID_BIAS, NP>, 160 * 1024, configured[2])) != cudaSuccess) return e;
+        return launch_k(q8_rows_kernel<Q8_EPI_RESID_BIAS, NP>, dim3(grid), dim3(QR_THREADS), smem, st, pdl, a);
+    }
+    return cudaErrorInvalidValue;
+}
+
+// RoPE of k (NeoX halves, the same operations as attn_decode_kernel) and the cache append of k and v for every row.
+struct KvRowsArgs {
+    const float *qkv;        // [rows][ldq]: q | k | v of every row, bias added, not rotated
+    int ldq, nh, nkv;
+    float *kc, *vc;          // [sequence][nkv][MAXSEQ][64]
+    size_t seq_stride;       // floats between two sequences' caches
+    const float *rope;
+    const int *row_pos, *row_seq;
+};
+
+__global__ void __launch_bounds__(64) kv_append_rows_kernel(KvRowsArgs a) {
+    const int kvh = blockIdx.x, t = blockIdx.y, tid = threadIdx.x, i = tid & 31;
+    const int pos = a.row_pos[t];
+    const float c = a.rope[((size_t)pos * 32 + i) * 2], s = a.rope[((size_t)pos * 32 + i) * 2 + 1];
+    pdl_wait();
+    pdl_trigger();
+    const float *k = a.qkv + (size_t)t * a.ldq + (size_t)(a.nh + kvh) * 64, *v = k + (size_t)a.nkv * 64;
+    const size_t o = (size_t)a.row_seq[t] * a.seq_stride + ((size_t)kvh * BRRR_MAXSEQ + pos) * 64;
+    const float x0 = k[i], x1 = k[32 + i];
+    if (tid < 32) a.kc[o + i] = __fsub_rn(__fmul_rn(x0, c), __fmul_rn(x1, s));
+    else a.kc[o + 32 + i] = __fadd_rn(__fmul_rn(x1, c), __fmul_rn(x0, s));
+    a.vc[o + tid] = v[tid];
+}
+
+}  // namespace
+
+// y[t][r] (+)= row r of m . activation t (+ bias) for t < ntok <= 16.  epi: Q8_EPI_PLAIN / BIAS / RESID_BIAS.
+cudaError_t launch_q8_rows(Q8Dev m, const int8_t *xq, const float *xs, int ntok, const float *bias, float *y, int ldy, int epi, bool pdl,
+                           cudaStream_t st) {
+    if (ntok < 1 || ntok > 16 || m.cols % 64) return cudaErrorInvalidValue;
+    Q8RowsArgs a{m, xq, xs, bias, y, ntok, ldy};
+    const int np = m.cols / 64, urows = q8_urows(m.rows);
+    const size_t smem = (size_t)ntok * np * 72;
+    if (np == 45) return q8_rows_launch<45>(a, epi, (unsigned)urows, smem, pdl, st);
+    if (np == 64) return q8_rows_launch<64>(a, epi, (unsigned)urows, smem, pdl, st);
+    return q8_rows_launch<0>(a, epi, (unsigned)urows, smem, pdl, st);
+}
+
+cudaError_t launch_kv_append_rows(const float *qkv, int ldq, int nh, int nkv, float *kc, float *vc, size_t seq_stride, const float *rope,
+                                  const int *row_pos, const int *row_seq, int rows, bool pdl, cudaStream_t st) {
+    KvRowsArgs a{qkv, ldq, nh, nkv, kc, vc, seq_stride, rope, row_pos, row_seq};
+    return launch_k(kv_append_rows_kernel, dim3(nkv, rows), dim3(64), 0, st, pdl, a);
+}
+
+}  // namespace brrr

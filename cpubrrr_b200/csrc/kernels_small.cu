@@ -31,6 +31,11 @@ __global__ void __launch_bounds__(512) rmsnorm_quant_kernel(const float *__restr
     extern __shared__ __align__(16) float sm[];      // n floats of x, then n floats of norm weights
     __shared__ float inv_sh;
     float *wn = sm + n;
+    // one CTA per row (token): rows are n floats apart in x and xn, n quants and n / 32 scales apart in q and s
+    x += (size_t)blockIdx.x * n;
+    if (xn) xn += (size_t)blockIdx.x * n;
+    if (q) q += (size_t)blockIdx.x * n;
+    if (s) s += (size_t)blockIdx.x * (n / 32);
     stage_vec4(w, wn, n, threadIdx.x, blockDim.x);   // static: fetched before the wait
     float4 wreg[4];
     norm_prefetch<4>(w, n, wreg, threadIdx.x, blockDim.x);
@@ -43,8 +48,9 @@ __global__ void __launch_bounds__(512) rmsnorm_quant_kernel(const float *__restr
     }
 }
 
-cudaError_t launch_rmsnorm_quant(const float *x, const float *w, float eps, int n, float *xn, int8_t *q, float *s, bool pdl, cudaStream_t st) {
-    return launch_k(rmsnorm_quant_kernel, dim3(1), dim3(512), (size_t)n * 2 * sizeof(float), st, pdl, x, w, eps, n, xn, q, s);
+cudaError_t launch_rmsnorm_quant(const float *x, const float *w, float eps, int n, float *xn, int8_t *q, float *s, bool pdl, cudaStream_t st,
+                                 int rows) {
+    return launch_k(rmsnorm_quant_kernel, dim3(rows), dim3(512), (size_t)n * 2 * sizeof(float), st, pdl, x, w, eps, n, xn, q, s);
 }
 
 // ---------------------------------------------------------------- embedding gather

@@ -151,11 +151,21 @@ struct brrr_model {
     float *tl_xs = nullptr, *tl_hs = nullptr, *tl_logits = nullptr, *tl_wts = nullptr, *tl_gu = nullptr, *tl_part = nullptr;
     int32_t *tl_top = nullptr;
     int *tl_cnt = nullptr, *tl_list = nullptr;
-    float *tl_x = nullptr, *tl_xn = nullptr;     // prompt tiles: residual and normalised residual of up to 16 tokens
-    uint32_t *tl_toks = nullptr;                 // token ids of the tile being replayed
-    uint32_t *h_tile = nullptr;                  // pinned: one 20-word slot per tile of a call
-    cudaGraphExec_t g_tile = nullptr;            // a full 16-token tile without the head
-    bool tile_graph_failed = false;
+    // token rows (prompt tiles, batched decode): up to 16 rows walk the layers together
+    float *tl_x = nullptr, *tl_xn = nullptr;     // residual and normalised residual of the rows
+    float *tl_qkv = nullptr, *tl_ao = nullptr, *tl_ns = nullptr, *tl_as = nullptr;
+    int8_t *tl_nq = nullptr, *tl_aq = nullptr;
+    uint32_t *tl_toks = nullptr;                 // per row: token id, position, sequence (device; filled from a pinned slot)
+    int *tl_pos = nullptr, *tl_seq = nullptr;
+    uint32_t *h_tile = nullptr;                  // pinned: one 64-word slot per tile in flight
+    uint32_t h_tile_next = 0;
+    cudaGraphExec_t g_rows[2][17] = {};          // [prompt tiles on the model's own cache | batched sequences][rows]: layers without the head
+    bool rows_graph_failed = false;
+    // batched decode over independent sequences: one KV cache per sequence and layer
+    int nseq = 0;
+    std::vector<float *> kcb, vcb;               // per layer: [nseq][nkv][MAXSEQ][64]
+    float *bt_logits = nullptr;                  // [16][n_vocab]
+    unsigned long long *bt_best = nullptr;       // [16] running argmax per row
     bool tile_prefill = false;                   // run_tile on 16-token tiles (brrr_model_set_tile_prefill / BRRR_TILE_PREFILL=1); default: token-serial, which is faster today
     unsigned int *tl_counter = nullptr;
     std::vector<void *> allocs;
@@ -753,7 +763,7 @@ extern "C" void brrr_model_close(brrr_model *m) {
     for (void *p : m->allocs) cudaFree(p);
     if (m->h_in) cudaFreeHost(m->h_in);
     if (m->h_tile) cudaFreeHost(m->h_tile);
-    if (m->g_tile) cudaGraphExecDestroy(m->g_tile);
+    for (auto &gs : m->g_rows) for (cudaGraphExec_t g : gs) if (g) cudaGraphExecDestroy(g);
     if (m->h_out) cudaFreeHost(m->h_out);
     if (m->stream) cudaStreamDestroy(m->stream);
     delete m;
@@ -845,48 +855,76 @@ extern "C" int brrr_forward(brrr_model *m, uint32_t tok, uint32_t pos, int want,
 
 static int moe_tile_enqueue(brrr_model *m, int il, const float *d_xn, float *d_x, int ntok);
 
-// One tile of up to 16 prompt tokens (forward_tile_worker, src/bin/engine_gpt2.rs:1011-1250): the
-// tokens walk the layers together.  Attention is causal inside the tile, so q/k/v, attention and the
-// output projection run token by token (each token's K and V are in the cache before the next token
-// attends); the MoE block, where the weight bytes are, runs once per layer for the whole tile on the
-// tensor-core tile kernels (kernels_tile.cu), streaming each routed expert once for all its tokens.
-// Every value is bit-identical to the token-serial schedule.
-// graph_mode: the replayable form of a full tile without the head: token ids come from m->tl_toks,
-// the tile's first position from the device state (attention adds the token's offset), and the
-// per-token kernels are chained by programmatic dependent launch.
-static int forward_tile_16(brrr_model *m, const uint32_t *toks, int n, uint32_t pos0, bool want, bool graph_mode) {
+// Up to 16 token rows walk the layers together (forward_tile_worker, src/bin/engine_gpt2.rs:1011-1250:
+// every stage gains a token dimension, weight row outer, tokens inner).  A row is (token, position,
+// sequence): consecutive positions of one sequence for a prompt tile, one position each of several
+// sequences for batched decode.  Per layer: norm + Q8 of every row, q|k|v for all rows from one pass over
+// the weights, RoPE + cache append of every row's k / v, attention of all rows in one launch (causal
+// inside a tile: a row sees the rows before it through the cache), o-proj for all rows, FFN norm, and
+// the MoE block on the tensor-core tile kernels.  Every value is bit-identical to the token-serial
+// schedule.  Everything is read from device arrays (tl_toks, tl_pos, tl_seq), so the enqueue is
+// captured once per row count and replayed.
+static int rows_alloc(brrr_model *m) {
+    if (m->tl_x) return BRRR_OK;
     const brrr_cfg &c = m->cfg;
-    const int d = c.n_embd, nh = c.n_head, nkv = c.n_head_kv;
+    const int d = c.n_embd, nb = d / 32, qkv_rows = (c.n_head + 2 * c.n_head_kv) * c.head_dim, ao = c.n_head * c.head_dim;
+    TRY(m->alloc(&m->tl_x, (size_t)16 * d)); TRY(m->alloc(&m->tl_xn, (size_t)16 * d));
+    TRY(m->alloc(&m->tl_qkv, (size_t)16 * qkv_rows)); TRY(m->alloc(&m->tl_ao, (size_t)16 * ao));
+    TRY(m->alloc(&m->tl_nq, (size_t)16 * d)); TRY(m->alloc(&m->tl_ns, (size_t)16 * nb));
+    TRY(m->alloc(&m->tl_aq, (size_t)16 * ao)); TRY(m->alloc(&m->tl_as, (size_t)16 * (ao / 32)));
+    TRY(m->alloc(&m->tl_toks, 16)); TRY(m->alloc(&m->tl_pos, 16)); TRY(m->alloc(&m->tl_seq, 16));
+    CU(cudaMallocHost(&m->h_tile, (size_t)64 * 64 * sizeof(uint32_t)));
+    return BRRR_OK;
+}
+
+static int enqueue_rows(brrr_model *m, int n, bool batch, bool pdl) {
+    const brrr_cfg &c = m->cfg;
+    const int d = c.n_embd, nh = c.n_head, nkv = c.n_head_kv, qkv_rows = (nh + 2 * nkv) * c.head_dim;
     cudaStream_t s = m->stream;
-    const bool pdl = graph_mode && m->use_pdl;
-    if (graph_mode) launch_embed_tile(m->tok_embd, d, m->tl_toks, n, m->tl_x, s);
-    else for (int t = 0; t < n; t++) launch_embed_tok(m->tok_embd, d, toks[t], m->tl_x + (size_t)t * d, s);
+    launch_embed_tile(m->tok_embd, d, m->tl_toks, n, m->tl_x, s);
     for (int il = 0; il < c.n_layer; il++) {
         Layer &ly = m->L[il];
         int window = ((il + 1) % 2 != 0) ? c.sliding_window : 0;
         if (window >= BRRR_MAXSEQ) window = 0;
-        for (int t = 0; t < n; t++) {
-            float *x = m->tl_x + (size_t)t * d;
-            // the first kernel after a plain launch takes the full dependency
-            CUL(launch_q8_stream(ly.wqkv, x, ly.attn_norm, c.rms_eps, nullptr, nullptr, ly.bqkv, m->qkv, Q8_EPI_BIAS, m->st, pdl && t > 0, s));
-            CUL(launch_attn_decode(m->qkv, ly.kc, ly.vc, m->rope, ly.sinks, nh, nkv, graph_mode ? m->st : nullptr, (int)pos0 + t, window, m->ao, m->aq, m->as,
-                                   m->st, pdl, s, t));
-            CUL(launch_q8_stream(ly.wo, nullptr, nullptr, 0.0f, m->aq, m->as, ly.bo, x, Q8_EPI_RESID_BIAS, m->st, pdl, s));
-            CUL(launch_rmsnorm_quant(x, ly.ffn_norm, c.rms_eps, d, m->tl_xn + (size_t)t * d, m->xq, m->xs, pdl, s));
-        }
+        float *kc = batch ? m->kcb[il] : ly.kc, *vc = batch ? m->vcb[il] : ly.vc;
+        const size_t seq_stride = batch ? (size_t)nkv * BRRR_MAXSEQ * c.head_dim : 0;
+        // the first kernel after a plain launch takes the full dependency
+        CUL(launch_rmsnorm_quant(m->tl_x, ly.attn_norm, c.rms_eps, d, nullptr, m->tl_nq, m->tl_ns, false, s, n));
+        CUL(launch_q8_rows(ly.wqkv, m->tl_nq, m->tl_ns, n, ly.bqkv, m->tl_qkv, qkv_rows, Q8_EPI_BIAS, pdl, s));
+        CUL(launch_kv_append_rows(m->tl_qkv, qkv_rows, nh, nkv, kc, vc, seq_stride, m->rope, m->tl_pos, m->tl_seq, n, pdl, s));
+        CUL(launch_attn_decode(m->tl_qkv, kc, vc, m->rope, ly.sinks, nh, nkv, nullptr, 0, window, m->tl_ao, m->tl_aq, m->tl_as, m->st, pdl, s, 0,
+                               m->tl_pos, m->tl_seq, seq_stride, qkv_rows, n));
+        CUL(launch_q8_rows(ly.wo, m->tl_aq, m->tl_as, n, ly.bo, m->tl_x, d, Q8_EPI_RESID_BIAS, pdl, s));
+        CUL(launch_rmsnorm_quant(m->tl_x, ly.ffn_norm, c.rms_eps, d, m->tl_xn, m->tl_nq, m->tl_ns, pdl, s, n));
         TRY(moe_tile_enqueue(m, il, m->tl_xn, m->tl_x, n));
     }
-    if (graph_mode) return BRRR_OK;
-    // leave the engine as the serial schedule would after the tile's last token
-    CU(cudaMemcpyAsync(m->x, m->tl_x + (size_t)(n - 1) * d, (size_t)d * sizeof(float), cudaMemcpyDeviceToDevice, s));
-    m->h_in[0] = toks[n - 1]; m->h_in[1] = pos0 + (uint32_t)n - 1;
-    CU(cudaMemcpyAsync(m->st, m->h_in, 8, cudaMemcpyHostToDevice, s));
-    if (want) {
-        CUL(launch_rmsnorm_quant(m->x, m->out_norm, c.rms_eps, d, nullptr, m->xq, m->xs, false, s));
-        CUL(launch_q8_head(m->head, m->xq, m->xs, m->logits, m->st, false, s));
-        launch_finish_token(m->st, s);
-    }
     CU(cudaGetLastError());
+    return BRRR_OK;
+}
+
+// Run the layers for the n rows described by (toks, pos, seq) (host arrays): the descriptors go through a
+// pinned slot of their own to the device arrays, then the captured enqueue is replayed (captured at the
+// first use of each row count; a direct run comes first so that every kernel has its attributes set).
+static int rows_run(brrr_model *m, int n, const uint32_t *toks, const uint32_t *pos, const uint32_t *seq, bool batch) {
+    TRY(rows_alloc(m));
+    uint32_t *h = m->h_tile + (size_t)(m->h_tile_next++ % 64) * 64;
+    if (m->h_tile_next % 64 == 0) CU(cudaStreamSynchronize(m->stream));        // the ring of pinned slots wraps: nothing may still be reading them
+    for (int t = 0; t < n; t++) { h[t] = toks[t]; h[16 + t] = pos[t]; h[32 + t] = seq ? seq[t] : 0u; }
+    CU(cudaMemcpyAsync(m->tl_toks, h, (size_t)n * 4, cudaMemcpyHostToDevice, m->stream));
+    CU(cudaMemcpyAsync(m->tl_pos, h + 16, (size_t)n * 4, cudaMemcpyHostToDevice, m->stream));
+    CU(cudaMemcpyAsync(m->tl_seq, h + 32, (size_t)n * 4, cudaMemcpyHostToDevice, m->stream));
+    cudaGraphExec_t &g = m->g_rows[batch ? 1 : 0][n];
+    if (g) { CU(cudaGraphLaunch(g, m->stream)); return BRRR_OK; }
+    TRY(enqueue_rows(m, n, batch, false));
+    if (!m->rows_graph_failed) {
+        CU(cudaStreamSynchronize(m->stream));
+        cudaGraph_t gr = nullptr;
+        CU(cudaStreamBeginCapture(m->stream, cudaStreamCaptureModeThreadLocal));
+        int st = enqueue_rows(m, n, batch, m->use_pdl);
+        cudaError_t e = cudaStreamEndCapture(m->stream, &gr);
+        if (!(st == BRRR_OK && e == cudaSuccess && cudaGraphInstantiate(&g, gr, 0) == cudaSuccess)) { g = nullptr; m->rows_graph_failed = true; (void)cudaGetLastError(); }
+        if (gr) cudaGraphDestroy(gr);
+    }
     return BRRR_OK;
 }
 
@@ -895,14 +933,10 @@ extern "C" int brrr_forward_tile(brrr_model *m, const uint32_t *toks, uint32_t n
     if (pos0 + n > BRRR_MAXSEQ) return BRRR_ERR_RANGE;
     for (uint32_t i = 0; i < n; i++) if (toks[i] >= (uint32_t)m->cfg.n_vocab) return BRRR_ERR_RANGE;
     CU(cudaSetDevice(m->device));
-    // Both schedules give the same bits.  The tile schedule amortises only the MoE block so far (the
-    // dense projections still run per token); it is opt-in.  Expert-parallel ranks stay serial.
+    // Both schedules give the same bits.  Expert-parallel ranks stay token-serial.
     const bool serial = m->ep || !m->tile_prefill;
-    const int d = m->cfg.n_embd;
-    if (!serial && !m->tl_x) {
-        TRY(m->alloc(&m->tl_x, (size_t)16 * d)); TRY(m->alloc(&m->tl_xn, (size_t)16 * d)); TRY(m->alloc(&m->tl_toks, 16));
-        CU(cudaMallocHost(&m->h_tile, (size_t)(BRRR_MAXSEQ / 16) * 20 * sizeof(uint32_t)));
-    }
+    const brrr_cfg &c = m->cfg;
+    const int d = c.n_embd;
     bool tiled_last = false;
     for (uint32_t i0 = 0; i0 < n; i0 += 16) {
         const uint32_t cnt = n - i0 < 16 ? n - i0 : 16;
@@ -914,32 +948,22 @@ extern "C" int brrr_forward_tile(brrr_model *m, const uint32_t *toks, uint32_t n
             }
             continue;
         }
-        if (cnt == 16 && !(want && last) && m->g_tile) {
-            // a full tile without the head: replay the captured tile step.  Host words of the tile
-            // (16 token ids; state before = {-, pos0}; state after = {last token, last position}) sit in
-            // their own pinned slot, so nothing is overwritten before the stream has read it.
-            uint32_t *h = m->h_tile + (size_t)(i0 / 16) * 20;
-            for (int t = 0; t < 16; t++) h[t] = toks[i0 + t];
-            h[16] = toks[i0]; h[17] = pos0 + i0; h[18] = toks[i0 + 15]; h[19] = pos0 + i0 + 15;
-            CU(cudaMemcpyAsync(m->tl_toks, h, 64, cudaMemcpyHostToDevice, m->stream));
-            CU(cudaMemcpyAsync(m->st, h + 16, 8, cudaMemcpyHostToDevice, m->stream));
-            CU(cudaGraphLaunch(m->g_tile, m->stream));
-            CU(cudaMemcpyAsync(m->x, m->tl_x + (size_t)15 * d, (size_t)d * sizeof(float), cudaMemcpyDeviceToDevice, m->stream));
-            CU(cudaMemcpyAsync(m->st, h + 18, 8, cudaMemcpyHostToDevice, m->stream));
-        } else {
-            TRY(forward_tile_16(m, toks + i0, (int)cnt, pos0 + i0, want && last, false));
-            if (cnt == 16 && !m->g_tile && !m->tile_graph_failed) {
-                // every kernel of the tile step has now run once directly (attributes set, scratch
-                // allocated): capture the replayable form for the tiles that follow
-                CU(cudaStreamSynchronize(m->stream));
-                cudaGraph_t g = nullptr;
-                CU(cudaStreamBeginCapture(m->stream, cudaStreamCaptureModeThreadLocal));
-                int st = forward_tile_16(m, nullptr, 16, 0, false, true);
-                cudaError_t e = cudaStreamEndCapture(m->stream, &g);
-                if (st == BRRR_OK && e == cudaSuccess && cudaGraphInstantiate(&m->g_tile, g, 0) == cudaSuccess) { }
-                else { m->g_tile = nullptr; m->tile_graph_failed = true; (void)cudaGetLastError(); }
-                if (g) cudaGraphDestroy(g);
+        uint32_t pos[16];
+        for (uint32_t t = 0; t < cnt; t++) pos[t] = pos0 + i0 + t;
+        TRY(rows_run(m, (int)cnt, toks + i0, pos, nullptr, false));
+        if (last) {
+            // leave the engine as the serial schedule would after the tile's last token
+            cudaStream_t s = m->stream;
+            CU(cudaMemcpyAsync(m->x, m->tl_x + (size_t)(cnt - 1) * d, (size_t)d * sizeof(float), cudaMemcpyDeviceToDevice, s));
+            m->h_in[0] = toks[n - 1]; m->h_in[1] = pos0 + n - 1;
+            CU(cudaMemcpyAsync(m->st, m->h_in, 8, cudaMemcpyHostToDevice, s));
+            if (want) {
+                CUL(launch_rmsnorm_quant(m->x, m->out_norm, c.rms_eps, d, nullptr, m->xq, m->xs, false, s));
+                CUL(launch_q8_head(m->head, m->xq, m->xs, m->logits, m->st, false, s));
+                launch_finish_token(m->st, s);
             }
+            CU(cudaGetLastError());
+            // (h_in is host-pageable-safe here: the stream is synchronised below before it is reused)
         }
         tiled_last = last;
     }
