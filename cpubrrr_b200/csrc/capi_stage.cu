@@ -102,7 +102,7 @@ extern "C" int brrr_mx_matvec(const brrr_mxmat *w, int row0, int nrows, const in
 
 extern "C" int brrr_mx_matmul_tile(const brrr_mxmat *w, int row0, int nrows, const int8_t *d_xq, const float *d_xs, int ntok, float *d_y, int ldy,
                                    void *stream) {
-    if (!w || !d_xq || !d_xs || !d_y || row0 < 0 || nrows <= 0 || row0 + nrows > w->m.rows || ntok < 1 || ntok > 16 || ldy < nrows) return BRRR_ERR_ARG;
+    if (!w || !d_xq || !d_xs || !d_y || row0 < 0 || nrows <= 0 || row0 + nrows > w->m.rows || ntok < 1 || ntok > BRRR_TILE_MAX || ldy < nrows) return BRRR_ERR_ARG;
     if (((uintptr_t)d_xq & 3)) return BRRR_ERR_ARG;
     if (launch_mx_tile(w->m, row0, nrows, d_xq, d_xs, ntok, d_y, ldy, nullptr, (cudaStream_t)stream) != cudaSuccess) return BRRR_ERR_CUDA;
     return check_launch();

@@ -1,23 +1,21 @@
 // Token-tile MXFP4 matmul on the 5th-generation tensor cores (tcgen05.mma kind::i8, accumulators in
 // tensor memory): the batched counterpart of the per-token expert matvec, for prefill tiles and
-// batched decode.  One pass over the weights serves up to 16 tokens, as the reference's tile path
-// does on the CPU (src/bin/engine_gpt2.rs:1005-1010, TILE = 16), and every output equals the
+// batched decode.  One pass over the weights serves up to 64 tokens, as the reference's tile path
+// does on the CPU for 16 (src/bin/engine_gpt2.rs:1005-1010, TILE = 16), and every output equals the
 // per-token result bit for bit.
 //
 // Arithmetic.  A row's value is four lane chains, each fma(float(t_lane(b)), 2^(e_b-128) * xs[b], acc)
 // over the 32-blocks b, with t_lane(b) the exact int32 sum of the lane's 8 products.  The integer
-// sums of 128 rows x 16 tokens x 4 lanes of one block are one 128 x 64 x 32 int8 matrix product:
+// sums of 128 rows x NT tokens x 4 lanes of one block are one 128 x 4 NT x 32 int8 matrix product:
 //   A[row][k]           = the row's 32 codes decoded to signed bytes (k = 8*lane + i),
 //   B[token*4+lane][k]  = the token's activation byte k if k belongs to `lane`, else 0,
 // issued twice, once with the positive and once with the negative decode table (their sum is the
-// signed value), accumulating in the same 128 x 64 int32 tile of tensor memory.  The four epilogue
+// signed value), accumulating in the same 128 x 4 NT int32 tile of tensor memory.  The four worker
 // warps read their 32 lanes of tensor memory (tcgen05.ld) and run the float chains, one thread per
-// row with 64 accumulators.
+// row with 4 NT accumulators.  NT = 4 entries per CTA for tiles of up to 16 tokens, 8 beyond.
 //
-// This version is serialised per block pair inside a CTA (decode -> MMA -> epilogue; several CTAs
-// per SM overlap each other, and the next pair's operands are fetched one pair ahead); operands are
-// written to shared memory by the threads themselves in the canonical K-major no-swizzle layout
-// (8-row x 16-byte core matrices).
+// Operands are written to shared memory by the threads themselves in the canonical K-major
+// no-swizzle layout (8-row x 16-byte core matrices).
 #include "brrr_kernels.h"
 #include "brrr_block.cuh"
 #include "brrr_tma.cuh"
@@ -28,11 +26,14 @@ namespace brrr {
 namespace {
 
 constexpr int TL_ROWS = 128;           // rows per CTA = MMA M
-constexpr int TL_N = 64;               // MMA N: 16 tokens x 4 chain lanes
-constexpr int TL_MAXTOK = 16;
+
+constexpr int TL_MAXTOK = 64;           // entries per expert and launch (one per token of the tile at most)
 constexpr int TL_A_BYTES = TL_ROWS * 32;       // one decoded A tile (128 rows x 32 k bytes)
-constexpr int TL_B_BYTES = TL_N * 32;
-constexpr uint32_t TL_TMEM_COLS = 128;         // two 64-column accumulator tiles (the two blocks of a pair)
+
+constexpr int TL_THREADS = 224;        // four worker warps, the producer warp, two issuer warps
+constexpr int TL_DEPTH = 5;            // weight ring: block pairs in flight per CTA
+constexpr int TL_SLOT = 9 * MX_UNIT;   // one pair of a 128-row tile: up to 9 units of 16 rows
+constexpr int TL_CPL = (TL_SLOT / 16 + 31) / 32;   // 16-byte pieces per producer lane and pair
 
 // shared-memory matrix descriptor: K-major, no swizzle; core matrix = 8 rows x 16 bytes, 128 bytes
 // apart along M/N (stride byte offset), `lbo` bytes apart along K (leading byte offset)
@@ -45,14 +46,12 @@ __device__ __forceinline__ uint64_t tl_smem_desc(const void *p, uint32_t lbo) {
     return d;
 }
 
-// instruction descriptor, kind::i8: D = s32, A = B = signed 8-bit, both K-major, N = 64, M = 128
-constexpr uint32_t TL_IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((TL_N >> 3) << 17) | ((TL_ROWS >> 4) << 24);
-
-__device__ __forceinline__ void tl_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t accumulate) {
+// kind::i8 product; instruction descriptor: D = s32, A = B = signed 8-bit, both K-major, N / 8 at bit 17, M / 16 at bit 24
+__device__ __forceinline__ void tl_mma(uint32_t tmem_d, uint64_t desc_a, uint64_t desc_b, uint32_t accumulate, uint32_t idesc) {
     asm volatile(
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
         "tcgen05.mma.cta_group::1.kind::i8 [%0], %1, %2, %3, {%5, %5, %5, %5}, p;\n\t}"
-        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(TL_IDESC), "r"(accumulate), "r"(0u)
+        ::"r"(tmem_d), "l"(desc_a), "l"(desc_b), "r"(idesc), "r"(accumulate), "r"(0u)
         : "memory");
 }
 __device__ __forceinline__ void tl_commit(uint64_t *bar) {
@@ -71,171 +70,256 @@ __device__ __forceinline__ void tl_ld16(uint32_t taddr, int (&r)[16]) {
 }
 __device__ __forceinline__ void tl_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// One launch serves blockIdx.y = expert (or a single matrix).  Each expert has a list of up to 16
+// One launch serves blockIdx.y = (expert or the single matrix, chunk of entries).  Each expert has a list of up to 64
 // entries; entry i multiplies the activation row entry / src_div and writes output row entry.
 struct TileArgs {
     MxDev w;
     int row0, nrows;         // rows [row0, row0 + nrows) of each expert's matrix
     int rows_per_expert;     // matrix row of (expert e, row r) = e * rows_per_expert + r
     const int *cnt;          // [experts] entries per expert; nullptr: one matrix, entries 0 .. ntok - 1
-    const int *list;         // [experts][16]
+    const int *list;         // [experts][TL_MAXTOK]
     int src_div;
     const int8_t *xq;        // [activation rows][blocks * 32]
     const float *xs;         // [activation rows][blocks]
     int ntok;
+    int chunks;              // CTAs per expert along blockIdx.y: ceil(most entries an expert can have / entries per CTA)
     const float *bias;       // nullable: [experts][rows_per_expert], added to every output
     float *y;                // element [entry][col0 + row - row0], rows ldy apart
     int ldy, col0;
     DevState *state;
 };
 
-__global__ void __launch_bounds__(128) mx_tile_kernel(TileArgs a) {
-    __shared__ __align__(128) unsigned char a_tiles[4][TL_A_BYTES];     // [block of the pair][P, N]
-    __shared__ __align__(128) unsigned char b_tiles[2][TL_B_BYTES];
-    __shared__ float tbl[256];
-    __shared__ float xs_pair[2][TL_MAXTOK];
-    __shared__ __align__(8) uint64_t bar;
-    __shared__ uint32_t tmem_base_sh;
-    __shared__ int ent[TL_MAXTOK];
-    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+// One CTA = 128 rows of one expert against one chunk of up to NT of its entries (NT = 4 or 8, MMA N = 4 NT; an
+// expert with more entries is served by several CTAs, which re-read its rows from L2).
+//
+// Roles.  A tcgen05.mma or a bulk copy costs its issuing thread on the order of a hundred cycles, so the
+// asynchronous work is spread: warp 4 is the producer (every lane copies 16-byte pieces of the pairs' weight
+// units into a ring TL_DEPTH pairs deep),
+// one thread each of warps 5 and 6 issues the two products of one block of every pair as soon as the
+// workers have staged the operands.  Warps 0-3 are the workers, one
+// thread per row: stage(q) decodes the row's 64 codes of pair q from the ring into half (q & 1) of the
+// operand tiles, chains(p) reads the pair's accumulators from tensor memory and runs the float chains.
+// A worker runs stage(p + 1) before chains(p), so the tensor core works on pair p + 1 meanwhile.
+//
+// Barriers (all waits bounded).  full[slot], 32 arrivals: the producer lanes' copies of the pair have landed;
+// empty[slot], 128 arrivals: the workers have read it.  staged[half], 128 arrivals: the
+// half's operands are written and, because a worker stages pair p + 2 only after chains(p), the half's
+// accumulators have been read.  done[half], 2 arrivals: the issuers' tcgen05.commit of the pair; workers wait for it before they read
+// the accumulators and before they overwrite the half's operands two pairs later.
+template <int NT>
+__global__ void __launch_bounds__(TL_THREADS, 3) mx_tile_kernel(TileArgs a) {
+    constexpr int N = 4 * NT;                                    // columns per block: NT tokens x 4 chain lanes
+    constexpr uint32_t TMEM_COLS = 4 * N;                        // two halves x two blocks x N columns (64 or 128)
+    constexpr uint32_t IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((TL_ROWS >> 4) << 24);
+    extern __shared__ __align__(128) unsigned char tsm[];
     const int nb = a.w.blocks, np = nb / 2;
-    const int e = blockIdx.y;
-    const int n_ent = a.cnt ? a.cnt[e] : a.ntok;
-    if (n_ent == 0) return;                      // no token routed to this expert (before anything is allocated)
-    if (tid < TL_MAXTOK) ent[tid] = tid < n_ent ? (a.list ? a.list[e * TL_MAXTOK + tid] : tid) : 0;
-    uint32_t *err = a.state ? &a.state->err : nullptr;
-    Waiter waiter(err);
-    const uint32_t P_LO = 0x04030200u, P_HI = 0x0D090705u, N_LO = 0xFDFEFF00u, N_HI = 0xF4F8FAFCu;
-
-    mx_fill_scale_table(tbl, tid, 128);
-    for (int i = tid; i < 2 * TL_B_BYTES / 16; i += 128) reinterpret_cast<uint4 *>(&b_tiles[0][0])[i] = make_uint4(0, 0, 0, 0);
-    if (tid == 0) { mbar_init(&bar, 1); mbar_fence_init(); }
+    unsigned char (*a_tiles)[TL_A_BYTES] = reinterpret_cast<unsigned char (*)[TL_A_BYTES]>(tsm);           // [half][block of the pair][P, N]
+    unsigned char (*b_tiles)[N * 32] = reinterpret_cast<unsigned char (*)[N * 32]>(tsm + 8 * TL_A_BYTES);  // [half][block of the pair]
+    unsigned char *ring = tsm + 8 * TL_A_BYTES + 4 * N * 32;                                               // [TL_DEPTH][8 units]
+    float *xs_sm = reinterpret_cast<float *>(ring + TL_DEPTH * TL_SLOT);                                   // [NT][nb] activation block scales
+    __shared__ float tbl[256];
+    __shared__ __align__(8) uint64_t full[TL_DEPTH], empty[TL_DEPTH], staged[2], done[2];
+    __shared__ uint32_t tmem_base_sh;
+    __shared__ int ent[NT];
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int e = blockIdx.y / a.chunks, chunk = blockIdx.y % a.chunks;
+    const int n_ent = min((a.cnt ? a.cnt[e] : a.ntok) - chunk * NT, NT);
+    if (n_ent <= 0) return;                      // nothing routed here (before anything is allocated)
+    if (tid < NT) ent[tid] = tid < n_ent ? (a.list ? a.list[e * TL_MAXTOK + chunk * NT + tid] : chunk * NT + tid) : 0;
+    mx_fill_scale_table(tbl, tid, TL_THREADS);
+    for (int i = tid; i < 4 * N * 32 / 16; i += TL_THREADS) reinterpret_cast<uint4 *>(&b_tiles[0][0])[i] = make_uint4(0, 0, 0, 0);   // rows of absent tokens stay zero
+    if (tid == 0) {
+        for (int i = 0; i < TL_DEPTH; i++) { mbar_init(&full[i], 32); mbar_init(&empty[i], 128); }
+        mbar_init(&staged[0], 128); mbar_init(&staged[1], 128);
+        mbar_init(&done[0], 2); mbar_init(&done[1], 2);
+        mbar_fence_init();
+    }
     if (warp == 0) {
-        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_sh)), "r"(TL_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_sh)), "r"(TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     tl_fence_before();
     __syncthreads();
     tl_fence_after();
     const uint32_t tmem_base = tmem_base_sh;
+    uint32_t *err = a.state ? &a.state->err : nullptr;
+    Waiter waiter(err);
+    // the tile's live rows lie in up to nine units of 16 rows (a row window may start anywhere); only those are copied
+    const int row_base = e * a.rows_per_expert + a.row0 + blockIdx.x * TL_ROWS;
+    const int live_rows = min(TL_ROWS, a.nrows - (int)blockIdx.x * TL_ROWS);
+    const int n_units = ((row_base & 15) + live_rows + 15) >> 4;
 
-    // this thread's row: weights of (row, all four lanes) for a block pair are 32 contiguous bytes
-    const int row_local = blockIdx.x * TL_ROWS + tid;
-    const bool row_live = row_local < a.nrows;
-    const int row = e * a.rows_per_expert + a.row0 + (row_live ? row_local : a.nrows - 1);   // out-of-range rows reread the last row, never stored
-    const unsigned char *wrow = a.w.data + mx_unit_off(row >> 4, 0, np) + (row & 15) * 32;
-    const unsigned char *erow = a.w.data + mx_unit_off(row >> 4, 0, np) + MX_UNIT_EXPS + (row & 15) * 2;
-    // A element (row m, byte k) lives at (k / 16) * 2048 + (m / 8) * 128 + (m % 8) * 16 + k % 16
-    const uint32_t a_off = (uint32_t)((tid >> 3) * 128 + (tid & 7) * 16);
-    // B row n = token * 4 + lane holds the 8 activation bytes of `lane` at k = 8 * lane .. + 7
-    const int bt = (tid & 63) >> 2, bl = tid & 3, bblk = tid >> 6;          // threads 0..63: first block of the pair, 64..127: second
-    const uint32_t b_off = (uint32_t)((bl >> 1) * (TL_N * 16) + ((tid & 63) >> 3) * 128 + ((tid & 63) & 7) * 16 + (bl & 1) * 8);
-
-    float acc[TL_N];
+    if (warp == 4) {
+        // ---------------- producer: 16-byte asynchronous copies, one arrival per lane on the slot's barrier
+        const int lane = tid & 31;
+        const int n_chunks = n_units * (MX_UNIT / 16);
+        const unsigned char *wbase = a.w.data + mx_unit_off(row_base >> 4, 0, np);
+        uint32_t src_off[TL_CPL], dst_off[TL_CPL];          // this lane's chunks of a pair: unit g, 16-byte piece o
 #pragma unroll
-    for (int i = 0; i < TL_N; i++) acc[i] = 0.0f;
-
-    // operands of a block pair are fetched one pair ahead, so their global-memory latency hides
-    // behind the tensor-core work and the epilogue of the current pair
-    const size_t srow = (size_t)(ent[bt] / a.src_div);
-    const bool b_live = bt < n_ent;
-    auto fetch_b = [&](int p, uint32_t &lo, uint32_t &hi, float &sc) {
-        const int b = 2 * p + bblk;
-        const uint32_t *xw = reinterpret_cast<const uint32_t *>(a.xq + (srow * nb + b) * 32);
-        lo = b_live ? xw[bl] : 0u; hi = b_live ? xw[4 + bl] : 0u;
-        sc = (b_live && bl == 0) ? a.xs[srow * nb + b] : 0.0f;
-    };
-    uint4 w0 = *reinterpret_cast<const uint4 *>(wrow), w1 = *reinterpret_cast<const uint4 *>(wrow + 16);
-    uint32_t e2 = *reinterpret_cast<const unsigned short *>(erow);
-    uint32_t xlo, xhi;
-    float xsc;
-    fetch_b(0, xlo, xhi, xsc);
-
-    for (int p = 0; p < np; p++) {
-        // ---- decode this row's two blocks into the four A tiles
-        const uint32_t wl[4][2] = {{w0.x, w0.y}, {w0.z, w0.w}, {w1.x, w1.y}, {w1.z, w1.w}};
-        const uint32_t e2c = e2;
+        for (int i = 0; i < TL_CPL; i++) {
+            const int c = lane + 32 * i, g = c / (MX_UNIT / 16), o = (c - g * (MX_UNIT / 16)) * 16;
+            src_off[i] = (uint32_t)g * (uint32_t)np * MX_UNIT + o;
+            dst_off[i] = (uint32_t)(g * MX_UNIT + o);
+        }
+        auto load = [&](int q, int slot) {
+            const unsigned char *src = wbase + (size_t)q * MX_UNIT;
+            unsigned char *dst = ring + slot * TL_SLOT;
 #pragma unroll
-        for (int j = 0; j < 4; j++) {
+            for (int i = 0; i < TL_CPL; i++)
+                if (lane + 32 * i < n_chunks)
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst + dst_off[i])), "l"(src + src_off[i]) : "memory");
+            asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&full[slot])) : "memory");
+        };
+        const int pre = min(TL_DEPTH, np);
+        for (int q = 0; q < pre; q++) load(q, q);
+        int slot = 0;
+        uint32_t par = 0;
+        for (int p = 0; p + TL_DEPTH < np; p++) {
+            waiter.wait(&empty[slot], par);                              // every worker has read pair p out of the slot
+            load(p + TL_DEPTH, slot);
+            if (++slot == TL_DEPTH) { slot = 0; par ^= 1u; }
+        }
+        asm volatile("cp.async.wait_all;" ::: "memory");
+    } else if (tid == 160 || tid == 192) {
+        // ---------------- issuers: block k of every pair (two threads in two warps, so the products of a pair issue side by side)
+        const int k = tid == 160 ? 0 : 1;
+        uint64_t da[2][2], db[2];
 #pragma unroll
-            for (int k = 0; k < 2; k++) {
-                const uint32_t w = wl[j][k], wx = w ^ 0x88888888u;
-                const uint32_t off = (uint32_t)((j >> 1) * 2048) + a_off + (j & 1) * 8;
-                *reinterpret_cast<uint2 *>(&a_tiles[2 * k][off]) = make_uint2(brrr_prmt(P_LO, P_HI, w), brrr_prmt(P_LO, P_HI, w >> 16));
-                *reinterpret_cast<uint2 *>(&a_tiles[2 * k + 1][off]) = make_uint2(brrr_prmt(N_LO, N_HI, wx), brrr_prmt(N_LO, N_HI, wx >> 16));
+        for (int h = 0; h < 2; h++) {
+            da[h][0] = tl_smem_desc(&a_tiles[4 * h + 2 * k][0], 2048);
+            da[h][1] = tl_smem_desc(&a_tiles[4 * h + 2 * k + 1][0], 2048);
+            db[h] = tl_smem_desc(&b_tiles[2 * h + k][0], N * 16);
+        }
+        for (int p = 0; p < np; p++) {
+            const int h = p & 1;
+            waiter.wait(&staged[h], (uint32_t)(p >> 1) & 1u);
+            tl_fence_after();
+            const uint32_t dcol = tmem_base + (uint32_t)((2 * h + k) * N);
+            if (h == 0) { tl_mma(dcol, da[0][0], db[0], 0u, IDESC); tl_mma(dcol, da[0][1], db[0], 1u, IDESC); }
+            else        { tl_mma(dcol, da[1][0], db[1], 0u, IDESC); tl_mma(dcol, da[1][1], db[1], 1u, IDESC); }
+            tl_commit(&done[h]);
+        }
+    } else if (tid < 128) {
+        // ---------------- workers
+        const uint32_t P_LO = 0x04030200u, P_HI = 0x0D090705u, N_LO = 0xFDFEFF00u, N_HI = 0xF4F8FAFCu;
+        const int row_local = blockIdx.x * TL_ROWS + tid;
+        const bool row_live = tid < live_rows;
+        // this row in a ring slot: its unit, there its 32 code bytes of the pair and its two exponent bytes
+        const int urow = (row_base & 15) + tid;
+        const unsigned char *my_unit = ring + (urow >> 4) * MX_UNIT;
+        const uint32_t w_off = (uint32_t)(urow & 15) * 32, e_off = MX_UNIT_EXPS + (uint32_t)(urow & 15) * 2;
+        // A element (row m, byte k) lives at (k / 16) * 2048 + (m / 8) * 128 + (m % 8) * 16 + k % 16
+        const uint32_t a_off = (uint32_t)((tid >> 3) * 128 + (tid & 7) * 16);
+        // B row n = token * 4 + lane holds the 8 activation bytes of `lane` at k = 8 * lane .. + 7; threads 0 .. N - 1 serve
+        // the first block of the pair, 64 .. 64 + N - 1 the second
+        const int n_row = tid & 63, bt = n_row >> 2, bl = tid & 3, bblk = tid >> 6;
+        const bool b_live = n_row < N && bt < n_ent;
+        const uint32_t b_off = (uint32_t)((bl >> 1) * (N * 16) + (n_row >> 3) * 128 + (n_row & 7) * 16 + (bl & 1) * 8);
+        // its activation words come straight from global memory (L2), one pair ahead
+        const int8_t *my_x = a.xq + (size_t)(ent[b_live ? bt : 0] / a.src_div) * nb * 32 + bblk * 32 + 4 * bl;
+        uint32_t xlo = 0, xhi = 0;
+        if (b_live) { xlo = *reinterpret_cast<const uint32_t *>(my_x); xhi = *reinterpret_cast<const uint32_t *>(my_x + 16); }
+        for (int i = tid; i < n_ent * nb; i += 128) xs_sm[i] = a.xs[(size_t)(ent[i / nb] / a.src_div) * nb + i % nb];
+        asm volatile("bar.sync 1, 128;" ::: "memory");             // the workers' own barrier: xs_sm is complete
+
+        int f_slot = 0;
+        uint32_t f_par = 0;
+        // operands of pair q -> half (q & 1) of the tiles; returns the row's two exponent bytes
+        auto stage = [&](int q) -> uint32_t {
+            const int h = q & 1;
+            waiter.wait(&full[f_slot], f_par);
+            const unsigned char *u = my_unit + f_slot * TL_SLOT;
+            const int q_slot = f_slot;
+            if (++f_slot == TL_DEPTH) { f_slot = 0; f_par ^= 1u; }
+            const uint4 w0 = *reinterpret_cast<const uint4 *>(u + w_off), w1 = *reinterpret_cast<const uint4 *>(u + w_off + 16);
+            const uint32_t e2 = *reinterpret_cast<const unsigned short *>(u + e_off);
+            mbar_arrive(&empty[q_slot]);
+            const uint32_t wl[4][2] = {{w0.x, w0.y}, {w0.z, w0.w}, {w1.x, w1.y}, {w1.z, w1.w}};
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+#pragma unroll
+                for (int k = 0; k < 2; k++) {
+                    const uint32_t w = wl[j][k], wx = w ^ 0x88888888u;
+                    const uint32_t off = (uint32_t)((j >> 1) * 2048) + a_off + (j & 1) * 8;
+                    *reinterpret_cast<uint2 *>(&a_tiles[4 * h + 2 * k][off]) = make_uint2(brrr_prmt(P_LO, P_HI, w), brrr_prmt(P_LO, P_HI, w >> 16));
+                    *reinterpret_cast<uint2 *>(&a_tiles[4 * h + 2 * k + 1][off]) = make_uint2(brrr_prmt(N_LO, N_HI, wx), brrr_prmt(N_LO, N_HI, wx >> 16));
+                }
             }
-        }
-        // ---- activations of the pair's two blocks into the B tiles (rows of absent tokens stay zero)
-        {
-            const int2 iv = mx_interleave(xlo, xhi);
-            *reinterpret_cast<uint2 *>(&b_tiles[bblk][b_off]) = make_uint2((uint32_t)iv.x, (uint32_t)iv.y);
-            if (bl == 0) xs_pair[bblk][bt] = xsc;
-        }
-        fence_proxy_async();               // generic-proxy writes above -> visible to the tensor core's reads
-        __syncthreads();
-        // ---- two blocks x two tables, one accumulator tile per block
-        if (tid == 0) {
+            if (b_live) {
+                const int2 iv = mx_interleave(xlo, xhi);
+                *reinterpret_cast<uint2 *>(&b_tiles[2 * h + bblk][b_off]) = make_uint2((uint32_t)iv.x, (uint32_t)iv.y);
+                if (q + 1 < np) {
+                    xlo = *reinterpret_cast<const uint32_t *>(my_x + (size_t)(q + 1) * 64);
+                    xhi = *reinterpret_cast<const uint32_t *>(my_x + (size_t)(q + 1) * 64 + 16);
+                }
+            }
+            fence_proxy_async();               // generic-proxy writes above -> visible to the tensor core's reads
+            tl_fence_before();                 // and this thread's reads of the half's accumulators are done
+            mbar_arrive(&staged[h]);
+            return e2;
+        };
+        float acc[N];
+#pragma unroll
+        for (int i = 0; i < N; i++) acc[i] = 0.0f;
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+        // float chains of pair p: thread = row (tensor-memory lane), N columns per block
+        auto chains = [&](int p, uint32_t e2c) {
+            const int h = p & 1;
+            waiter.wait(&done[h], (uint32_t)(p >> 1) & 1u);
             tl_fence_after();
 #pragma unroll
             for (int k = 0; k < 2; k++) {
-                const uint64_t db = tl_smem_desc(&b_tiles[k][0], TL_N * 16);
-                tl_mma(tmem_base + k * TL_N, tl_smem_desc(&a_tiles[2 * k][0], 2048), db, 0u);
-                tl_mma(tmem_base + k * TL_N, tl_smem_desc(&a_tiles[2 * k + 1][0], 2048), db, 1u);
-            }
-            tl_commit(&bar);
-        }
-        if (p + 1 < np) {                  // next pair's operands
-            w0 = *reinterpret_cast<const uint4 *>(wrow + (size_t)(p + 1) * MX_UNIT);
-            w1 = *reinterpret_cast<const uint4 *>(wrow + (size_t)(p + 1) * MX_UNIT + 16);
-            e2 = *reinterpret_cast<const unsigned short *>(erow + (size_t)(p + 1) * MX_UNIT);
-            fetch_b(p + 1, xlo, xhi, xsc);
-        }
-        waiter.wait(&bar, (uint32_t)p & 1u);
-        tl_fence_after();
-        // ---- float chains: thread = row (tensor-memory lane), 64 columns per block
-        const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+                int d[N / 16][16];
 #pragma unroll
-        for (int k = 0; k < 2; k++) {
-            const float esc = tbl[k ? e2c >> 8 : e2c & 0xFFu];
-            int d[4][16];
+                for (int c = 0; c < N / 16; c++) tl_ld16(lane_addr + (uint32_t)((2 * h + k) * N + 16 * c), d[c]);
+                tl_wait_ld();
+                const float esc = tbl[k ? e2c >> 8 : e2c & 0xFFu];
 #pragma unroll
-            for (int c = 0; c < 4; c++) tl_ld16(lane_addr + k * TL_N + 16 * c, d[c]);
-            tl_wait_ld();
+                for (int t = 0; t < NT; t++) {
+                    const float sxs = __fmul_rn(esc, xs_sm[t * nb + 2 * p + k]);
 #pragma unroll
-            for (int c = 0; c < 4; c++) {
-#pragma unroll
-                for (int t = 0; t < 4; t++) {
-                    const float s = __fmul_rn(esc, xs_pair[k][4 * c + t]);
-#pragma unroll
-                    for (int l = 0; l < 4; l++) acc[16 * c + 4 * t + l] = __fmaf_rn((float)d[c][4 * t + l], s, acc[16 * c + 4 * t + l]);
+                    for (int l = 0; l < 4; l++) acc[4 * t + l] = __fmaf_rn((float)d[t / 4][4 * (t % 4) + l], sxs, acc[4 * t + l]);
                 }
             }
+        };
+        uint32_t e2c = stage(0);
+        for (int p = 0; p < np; p++) {
+            uint32_t e2n = 0;
+            if (p + 1 < np) e2n = stage(p + 1);      // the tensor core runs pair p + 1 ...
+            chains(p, e2c);                          // ... beside the chains of pair p
+            e2c = e2n;
         }
-        tl_fence_before();
-        __syncthreads();                   // tiles and accumulators are free for the next pair
-    }
-    if (row_live) {
-        const float bias = a.bias ? a.bias[(size_t)e * a.rows_per_expert + a.row0 + row_local] : 0.0f;
+        if (row_live) {
+            const float bias = a.bias ? a.bias[(size_t)e * a.rows_per_expert + a.row0 + row_local] : 0.0f;
 #pragma unroll
-        for (int t = 0; t < TL_MAXTOK; t++)
-            if (t < n_ent) {
-                float v = __fadd_rn(__fadd_rn(acc[4 * t], acc[4 * t + 1]), __fadd_rn(acc[4 * t + 2], acc[4 * t + 3]));
-                if (a.bias) v = __fadd_rn(v, bias);
-                a.y[(size_t)ent[t] * a.ldy + a.col0 + row_local] = v;
-            }
+            for (int t = 0; t < NT; t++)
+                if (t < n_ent) {
+                    float v = __fadd_rn(__fadd_rn(acc[4 * t], acc[4 * t + 1]), __fadd_rn(acc[4 * t + 2], acc[4 * t + 3]));
+                    if (a.bias) v = __fadd_rn(v, bias);
+                    a.y[(size_t)ent[t] * a.ldy + a.col0 + row_local] = v;
+                }
+        }
     }
-    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TL_TMEM_COLS) : "memory");
+    tl_fence_before();
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
 }
 
-// Per expert, the (token, slot) pairs routed to it, in ascending order: entry = token * topk + slot.
-__global__ void tile_route_kernel(const int32_t *__restrict__ top, int ntok, int topk, int ne, int *__restrict__ cnt, int *__restrict__ list) {
-    const int e = blockIdx.x * blockDim.x + threadIdx.x;
-    if (e >= ne) return;
-    int c = 0;
-    for (int t = 0; t < ntok; t++)
+// Per expert, the (token, slot) pairs routed to it, in ascending order: entry = token * topk + slot.  One CTA per
+// expert, thread = token (a token routes to an expert at most once, so the order is the token order).
+__global__ void __launch_bounds__(TL_MAXTOK) tile_route_kernel(const int32_t *__restrict__ top, int ntok, int topk, int *__restrict__ cnt, int *__restrict__ list) {
+    __shared__ int first_warp;
+    const int e = blockIdx.x, t = threadIdx.x;
+    int slot = -1;
+    if (t < ntok)
         for (int s = 0; s < topk; s++)
-            if (top[t * 8 + s] == e && c < TL_MAXTOK) list[e * TL_MAXTOK + c++] = t * topk + s;
-    cnt[e] = c;
+            if (top[t * 8 + s] == e) { slot = s; break; }
+    const unsigned m = __ballot_sync(0xffffffffu, slot >= 0);
+    if (t == 31) first_warp = __popc(m);
+    __syncthreads();
+    const int before = __popc(m & ((1u << (t & 31)) - 1u)) + (t >= 32 ? first_warp : 0);
+    if (slot >= 0) list[e * TL_MAXTOK + before] = t * topk + slot;
+    if (t == TL_MAXTOK - 1) cnt[e] = before + (slot >= 0 ? 1 : 0);
 }
 
 // x[t] += w[t][k] * part[t * topk + k], k ascending (part already holds the bias): the fold of
@@ -248,28 +332,44 @@ __global__ void tile_combine_kernel(const float *__restrict__ part, const float 
     x[(size_t)t * d + r] = s;
 }
 
+size_t tl_smem(int nt, int nb) { return 8 * TL_A_BYTES + 4 * (size_t)(4 * nt) * 32 + (size_t)TL_DEPTH * TL_SLOT + (size_t)nt * nb * 4; }
+
+// Block pairs need an even block count.  Entries per CTA: 4 while no expert can have more than 16 entries, else 8.
+cudaError_t tl_launch(TileArgs a, int tiles, int experts, int max_entries, cudaStream_t st) {
+    if ((a.w.blocks & 1) || a.w.blocks < 2 || max_entries < 1 || max_entries > TL_MAXTOK) return cudaErrorInvalidValue;
+    const int nt = max_entries <= 16 ? 4 : 8;
+    const size_t smem = tl_smem(nt, a.w.blocks);
+    if (smem > 200 * 1024) return cudaErrorInvalidValue;
+    static unsigned long long configured4 = 0, configured8 = 0;      // one bit per device
+    cudaError_t ce = nt == 4 ? smem_optin(mx_tile_kernel<4>, 200 * 1024, configured4) : smem_optin(mx_tile_kernel<8>, 200 * 1024, configured8);
+    if (ce != cudaSuccess) return ce;
+    a.chunks = (max_entries + nt - 1) / nt;
+    const dim3 grid(tiles, experts * a.chunks);
+    if (nt == 4) mx_tile_kernel<4><<<grid, TL_THREADS, smem, st>>>(a);
+    else mx_tile_kernel<8><<<grid, TL_THREADS, smem, st>>>(a);
+    return cudaGetLastError();
+}
+
 }  // namespace
 
 cudaError_t launch_mx_tile(MxDev w, int row0, int nrows, const int8_t *xq, const float *xs, int ntok, float *y, int ldy, DevState *state,
                            cudaStream_t st) {
     TileArgs a{};
     a.w = w; a.row0 = row0; a.nrows = nrows; a.src_div = 1; a.xq = xq; a.xs = xs; a.ntok = ntok; a.y = y; a.ldy = ldy; a.state = state;
-    mx_tile_kernel<<<dim3((nrows + TL_ROWS - 1) / TL_ROWS, 1), 128, 0, st>>>(a);
-    return cudaGetLastError();
+    return tl_launch(a, (nrows + TL_ROWS - 1) / TL_ROWS, 1, ntok, st);
 }
 
 // All experts of one matrix kind against their routed entries (see TileArgs).
-cudaError_t launch_mx_tile_experts(MxDev w, int ne, int rows_per_expert, const int *cnt, const int *list, int src_div, const int8_t *xq,
+cudaError_t launch_mx_tile_experts(MxDev w, int ne, int rows_per_expert, const int *cnt, const int *list, int max_entries, int src_div, const int8_t *xq,
                                    const float *xs, const float *bias, float *y, int ldy, int col0, DevState *state, cudaStream_t st) {
     TileArgs a{};
     a.w = w; a.row0 = 0; a.nrows = rows_per_expert; a.rows_per_expert = rows_per_expert; a.cnt = cnt; a.list = list; a.src_div = src_div;
     a.xq = xq; a.xs = xs; a.bias = bias; a.y = y; a.ldy = ldy; a.col0 = col0; a.state = state;
-    mx_tile_kernel<<<dim3((rows_per_expert + TL_ROWS - 1) / TL_ROWS, ne), 128, 0, st>>>(a);
-    return cudaGetLastError();
+    return tl_launch(a, (rows_per_expert + TL_ROWS - 1) / TL_ROWS, ne, max_entries, st);
 }
 
 void launch_tile_route(const int32_t *top, int ntok, int topk, int ne, int *cnt, int *list, cudaStream_t st) {
-    tile_route_kernel<<<(ne + 63) / 64, 64, 0, st>>>(top, ntok, topk, ne, cnt, list);
+    tile_route_kernel<<<ne, TL_MAXTOK, 0, st>>>(top, ntok, topk, cnt, list);
 }
 
 void launch_tile_combine(const float *part, const float *wts, int topk, int d, int ntok, float *x, cudaStream_t st) {

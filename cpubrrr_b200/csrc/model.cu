@@ -151,7 +151,7 @@ struct brrr_model {
     float *tl_xs = nullptr, *tl_hs = nullptr, *tl_logits = nullptr, *tl_wts = nullptr, *tl_gu = nullptr, *tl_part = nullptr;
     int32_t *tl_top = nullptr;
     int *tl_cnt = nullptr, *tl_list = nullptr;
-    // token rows (prompt tiles, batched decode): up to 16 rows walk the layers together
+    // token rows (prompt tiles, batched decode): up to BRRR_TILE_MAX rows walk the layers together
     float *tl_x = nullptr, *tl_xn = nullptr;     // residual and normalised residual of the rows
     float *tl_qkv = nullptr, *tl_ao = nullptr, *tl_ns = nullptr, *tl_as = nullptr;
     int8_t *tl_nq = nullptr, *tl_aq = nullptr;
@@ -159,14 +159,15 @@ struct brrr_model {
     int *tl_pos = nullptr, *tl_seq = nullptr;
     uint32_t *h_tile = nullptr;                  // pinned: one 64-word slot per tile in flight
     uint32_t h_tile_next = 0;
-    cudaGraphExec_t g_rows[2][17] = {};          // [prompt tiles on the model's own cache | batched sequences][rows]: layers without the head
+    cudaGraphExec_t g_rows[2][BRRR_TILE_MAX + 1] = {};          // [prompt tiles on the model's own cache | batched sequences][rows]: layers without the head
     bool rows_graph_failed = false;
     // batched decode over independent sequences: one KV cache per sequence and layer
     int nseq = 0;
     std::vector<float *> kcb, vcb;               // per layer: [nseq][nkv][MAXSEQ][64]
     float *bt_logits = nullptr;                  // [16][n_vocab]
     unsigned long long *bt_best = nullptr;       // [16] running argmax per row
-    bool tile_prefill = false;                   // run_tile on 16-token tiles (brrr_model_set_tile_prefill / BRRR_TILE_PREFILL=1); default: token-serial, which is faster today
+    int tile_rows = BRRR_TILE_MAX;               // tokens per prompt tile (BRRR_TILE_ROWS=n, 2..64): any size gives the same bits
+    bool tile_prefill = true;                    // run_tile on 16-token tiles (brrr_model_set_tile_prefill / BRRR_TILE_PREFILL=0 switch to token-serial; same bits)
     unsigned int *tl_counter = nullptr;
     std::vector<void *> allocs;
 
@@ -479,7 +480,8 @@ int build_model(brrr_model *m, const Source &src) {
         m->use_mxt = d % 64 == 0 && nb % 2 == 0 && topk <= 8 && free_b > experts * 2.2 + rest;
         if (const char *e = getenv("BRRR_NOMXT")) if (e[0] && e[0] != '0') m->use_mxt = false;
         if (const char *e = getenv("BRRR_NOFUSEDFOLD")) if (e[0] && e[0] != '0') m->fused_fold = false;
-        if (const char *e = getenv("BRRR_TILE_PREFILL")) if (e[0] && e[0] != '0') m->tile_prefill = true;
+        if (const char *e = getenv("BRRR_TILE_PREFILL")) m->tile_prefill = e[0] && e[0] != '0';
+        if (const char *e = getenv("BRRR_TILE_ROWS")) { const int v = atoi(e); if (v >= 2 && v <= BRRR_TILE_MAX) m->tile_rows = v; }
     }
     for (int il = 0; il < c.n_layer; il++) {
         Layer &ly = m->L[il];
@@ -864,22 +866,25 @@ static int moe_tile_enqueue(brrr_model *m, int il, const float *d_xn, float *d_x
 // the MoE block on the tensor-core tile kernels.  Every value is bit-identical to the token-serial
 // schedule.  Everything is read from device arrays (tl_toks, tl_pos, tl_seq), so the enqueue is
 // captured once per row count and replayed.
+constexpr int ROWS_SLOTS = 64;          // pinned descriptor slots of rows_run
+
 static int rows_alloc(brrr_model *m) {
     if (m->tl_x) return BRRR_OK;
     const brrr_cfg &c = m->cfg;
     const int d = c.n_embd, nb = d / 32, qkv_rows = (c.n_head + 2 * c.n_head_kv) * c.head_dim, ao = c.n_head * c.head_dim;
-    TRY(m->alloc(&m->tl_x, (size_t)16 * d)); TRY(m->alloc(&m->tl_xn, (size_t)16 * d));
-    TRY(m->alloc(&m->tl_qkv, (size_t)16 * qkv_rows)); TRY(m->alloc(&m->tl_ao, (size_t)16 * ao));
-    TRY(m->alloc(&m->tl_nq, (size_t)16 * d)); TRY(m->alloc(&m->tl_ns, (size_t)16 * nb));
-    TRY(m->alloc(&m->tl_aq, (size_t)16 * ao)); TRY(m->alloc(&m->tl_as, (size_t)16 * (ao / 32)));
-    TRY(m->alloc(&m->tl_toks, 16)); TRY(m->alloc(&m->tl_pos, 16)); TRY(m->alloc(&m->tl_seq, 16));
-    CU(cudaMallocHost(&m->h_tile, (size_t)64 * 64 * sizeof(uint32_t)));
+    const size_t R = BRRR_TILE_MAX;
+    TRY(m->alloc(&m->tl_x, R * d)); TRY(m->alloc(&m->tl_xn, R * d));
+    TRY(m->alloc(&m->tl_qkv, R * qkv_rows)); TRY(m->alloc(&m->tl_ao, R * ao));
+    TRY(m->alloc(&m->tl_nq, R * d)); TRY(m->alloc(&m->tl_ns, R * nb));
+    TRY(m->alloc(&m->tl_aq, R * ao)); TRY(m->alloc(&m->tl_as, R * (ao / 32)));
+    TRY(m->alloc(&m->tl_toks, R)); TRY(m->alloc(&m->tl_pos, R)); TRY(m->alloc(&m->tl_seq, R));
+    CU(cudaMallocHost(&m->h_tile, (size_t)ROWS_SLOTS * 3 * R * sizeof(uint32_t)));
     return BRRR_OK;
 }
 
 static int enqueue_rows(brrr_model *m, int n, bool batch, bool pdl) {
     const brrr_cfg &c = m->cfg;
-    const int d = c.n_embd, nh = c.n_head, nkv = c.n_head_kv, qkv_rows = (nh + 2 * nkv) * c.head_dim;
+    const int d = c.n_embd, nh = c.n_head, nkv = c.n_head_kv, qkv_rows = (nh + 2 * nkv) * c.head_dim, ao = nh * c.head_dim;
     cudaStream_t s = m->stream;
     launch_embed_tile(m->tok_embd, d, m->tl_toks, n, m->tl_x, s);
     for (int il = 0; il < c.n_layer; il++) {
@@ -890,11 +895,16 @@ static int enqueue_rows(brrr_model *m, int n, bool batch, bool pdl) {
         const size_t seq_stride = batch ? (size_t)nkv * BRRR_MAXSEQ * c.head_dim : 0;
         // the first kernel after a plain launch takes the full dependency
         CUL(launch_rmsnorm_quant(m->tl_x, ly.attn_norm, c.rms_eps, d, nullptr, m->tl_nq, m->tl_ns, false, s, n));
-        CUL(launch_q8_rows(ly.wqkv, m->tl_nq, m->tl_ns, n, ly.bqkv, m->tl_qkv, qkv_rows, Q8_EPI_BIAS, pdl, s));
+        // the projections take up to 16 rows per pass over the weights (later passes of a tile find them in L2)
+        for (int r0 = 0; r0 < n; r0 += 16)
+            CUL(launch_q8_rows(ly.wqkv, m->tl_nq + (size_t)r0 * d, m->tl_ns + (size_t)r0 * (d / 32), std::min(16, n - r0), ly.bqkv, m->tl_qkv + (size_t)r0 * qkv_rows,
+                               qkv_rows, Q8_EPI_BIAS, pdl, s));
         CUL(launch_kv_append_rows(m->tl_qkv, qkv_rows, nh, nkv, kc, vc, seq_stride, m->rope, m->tl_pos, m->tl_seq, n, pdl, s));
         CUL(launch_attn_decode(m->tl_qkv, kc, vc, m->rope, ly.sinks, nh, nkv, nullptr, 0, window, m->tl_ao, m->tl_aq, m->tl_as, m->st, pdl, s, 0,
                                m->tl_pos, m->tl_seq, seq_stride, qkv_rows, n));
-        CUL(launch_q8_rows(ly.wo, m->tl_aq, m->tl_as, n, ly.bo, m->tl_x, d, Q8_EPI_RESID_BIAS, pdl, s));
+        for (int r0 = 0; r0 < n; r0 += 16)
+            CUL(launch_q8_rows(ly.wo, m->tl_aq + (size_t)r0 * ao, m->tl_as + (size_t)r0 * (ao / 32), std::min(16, n - r0), ly.bo, m->tl_x + (size_t)r0 * d, d,
+                               Q8_EPI_RESID_BIAS, pdl, s));
         CUL(launch_rmsnorm_quant(m->tl_x, ly.ffn_norm, c.rms_eps, d, m->tl_xn, m->tl_nq, m->tl_ns, pdl, s, n));
         TRY(moe_tile_enqueue(m, il, m->tl_xn, m->tl_x, n));
     }
@@ -907,12 +917,13 @@ static int enqueue_rows(brrr_model *m, int n, bool batch, bool pdl) {
 // first use of each row count; a direct run comes first so that every kernel has its attributes set).
 static int rows_run(brrr_model *m, int n, const uint32_t *toks, const uint32_t *pos, const uint32_t *seq, bool batch) {
     TRY(rows_alloc(m));
-    uint32_t *h = m->h_tile + (size_t)(m->h_tile_next++ % 64) * 64;
-    if (m->h_tile_next % 64 == 0) CU(cudaStreamSynchronize(m->stream));        // the ring of pinned slots wraps: nothing may still be reading them
-    for (int t = 0; t < n; t++) { h[t] = toks[t]; h[16 + t] = pos[t]; h[32 + t] = seq ? seq[t] : 0u; }
+    const int R = BRRR_TILE_MAX;
+    uint32_t *h = m->h_tile + (size_t)(m->h_tile_next++ % ROWS_SLOTS) * 3 * R;
+    if (m->h_tile_next % ROWS_SLOTS == 0) CU(cudaStreamSynchronize(m->stream));        // the ring of pinned slots wraps: nothing may still be reading them
+    for (int t = 0; t < n; t++) { h[t] = toks[t]; h[R + t] = pos[t]; h[2 * R + t] = seq ? seq[t] : 0u; }
     CU(cudaMemcpyAsync(m->tl_toks, h, (size_t)n * 4, cudaMemcpyHostToDevice, m->stream));
-    CU(cudaMemcpyAsync(m->tl_pos, h + 16, (size_t)n * 4, cudaMemcpyHostToDevice, m->stream));
-    CU(cudaMemcpyAsync(m->tl_seq, h + 32, (size_t)n * 4, cudaMemcpyHostToDevice, m->stream));
+    CU(cudaMemcpyAsync(m->tl_pos, h + R, (size_t)n * 4, cudaMemcpyHostToDevice, m->stream));
+    CU(cudaMemcpyAsync(m->tl_seq, h + 2 * R, (size_t)n * 4, cudaMemcpyHostToDevice, m->stream));
     cudaGraphExec_t &g = m->g_rows[batch ? 1 : 0][n];
     if (g) { CU(cudaGraphLaunch(g, m->stream)); return BRRR_OK; }
     TRY(enqueue_rows(m, n, batch, false));
@@ -938,8 +949,9 @@ extern "C" int brrr_forward_tile(brrr_model *m, const uint32_t *toks, uint32_t n
     const brrr_cfg &c = m->cfg;
     const int d = c.n_embd;
     bool tiled_last = false;
-    for (uint32_t i0 = 0; i0 < n; i0 += 16) {
-        const uint32_t cnt = n - i0 < 16 ? n - i0 : 16;
+    const uint32_t T = (uint32_t)m->tile_rows;
+    for (uint32_t i0 = 0; i0 < n; i0 += T) {
+        const uint32_t cnt = n - i0 < T ? n - i0 : T;
         const bool last = i0 + cnt == n;
         if (serial || cnt == 1) {
             for (uint32_t i = i0; i < i0 + cnt; i++) {
@@ -948,7 +960,7 @@ extern "C" int brrr_forward_tile(brrr_model *m, const uint32_t *toks, uint32_t n
             }
             continue;
         }
-        uint32_t pos[16];
+        uint32_t pos[BRRR_TILE_MAX];
         for (uint32_t t = 0; t < cnt; t++) pos[t] = pos0 + i0 + t;
         TRY(rows_run(m, (int)cnt, toks + i0, pos, nullptr, false));
         if (last) {
@@ -1108,38 +1120,38 @@ extern "C" int brrr_moe_ffn_step_tc(brrr_model *m, int il, const float *d_xn, fl
 
 extern "C" int brrr_model_uses_tensor_experts(const brrr_model *m) { return m && m->use_mxt ? 1 : 0; }
 
-// MoE FFN of one layer for a tile of up to 16 normalised tokens: per-token router (one launch),
+// MoE FFN of one layer for a tile of up to BRRR_TILE_MAX (64) normalised tokens: per-token router (one launch),
 // routing lists per expert, then three grouped tensor-core matmuls (gate, up, down) that read every
 // needed expert matrix once for all its tokens, SwiGLU + Q8 per (token, slot), and the fold in slot
 // order.  Bit-identical to brrr_moe_ffn_step applied to the tokens one by one.
 // Enqueue only (no synchronisation): the tile's MoE step on m->stream.
 static int moe_tile_enqueue(brrr_model *m, int il, const float *d_xn, float *d_x, int ntok) {
     const brrr_cfg &c = m->cfg;
-    const int d = c.n_embd, nb = d / 32, topk = c.n_expert_used, ne = c.n_expert, np_ = 16 * topk;
+    const int d = c.n_embd, nb = d / 32, topk = c.n_expert_used, ne = c.n_expert, R = BRRR_TILE_MAX, np_ = R * topk;
     if (!m->tl_xq) {
-        TRY(m->alloc(&m->tl_xq, (size_t)16 * d)); TRY(m->alloc(&m->tl_xs, (size_t)16 * nb));
-        TRY(m->alloc(&m->tl_logits, (size_t)16 * ne)); TRY(m->alloc(&m->tl_top, 16 * 8)); TRY(m->alloc(&m->tl_wts, 16 * 8));
-        TRY(m->alloc(&m->tl_counter, 16)); TRY(m->alloc(&m->tl_cnt, ne)); TRY(m->alloc(&m->tl_list, (size_t)ne * 16));
+        TRY(m->alloc(&m->tl_xq, (size_t)R * d)); TRY(m->alloc(&m->tl_xs, (size_t)R * nb));
+        TRY(m->alloc(&m->tl_logits, (size_t)R * ne)); TRY(m->alloc(&m->tl_top, R * 8)); TRY(m->alloc(&m->tl_wts, R * 8));
+        TRY(m->alloc(&m->tl_counter, R)); TRY(m->alloc(&m->tl_cnt, ne)); TRY(m->alloc(&m->tl_list, (size_t)ne * R));
         TRY(m->alloc(&m->tl_gu, (size_t)np_ * 2 * d)); TRY(m->alloc(&m->tl_hq, (size_t)np_ * d)); TRY(m->alloc(&m->tl_hs, (size_t)np_ * nb));
         TRY(m->alloc(&m->tl_part, (size_t)np_ * d));
-        CU(cudaMemsetAsync(m->tl_counter, 0, 16 * sizeof(unsigned int), m->stream));
+        CU(cudaMemsetAsync(m->tl_counter, 0, R * sizeof(unsigned int), m->stream));
     }
     Layer &ly = m->L[il];
     cudaStream_t s = m->stream;
     launch_quant_q8(d_xn, ntok * d, m->tl_xq, m->tl_xs, s);
     CUL(launch_ffn_in(d_xn, nullptr, c.rms_eps, d, ly.ginp, ly.ginp_b, ne, topk, m->tl_logits, m->tl_top, m->tl_wts, m->tl_counter, m->st, false, s, ntok));
     launch_tile_route(m->tl_top, ntok, topk, ne, m->tl_cnt, m->tl_list, s);
-    CUL(launch_mx_tile_experts(ly.gate, ne, d, m->tl_cnt, m->tl_list, topk, m->tl_xq, m->tl_xs, ly.gate_b, m->tl_gu, 2 * d, 0, m->st, s));
-    CUL(launch_mx_tile_experts(ly.up, ne, d, m->tl_cnt, m->tl_list, topk, m->tl_xq, m->tl_xs, ly.up_b, m->tl_gu, 2 * d, d, m->st, s));
+    CUL(launch_mx_tile_experts(ly.gate, ne, d, m->tl_cnt, m->tl_list, ntok, topk, m->tl_xq, m->tl_xs, ly.gate_b, m->tl_gu, 2 * d, 0, m->st, s));
+    CUL(launch_mx_tile_experts(ly.up, ne, d, m->tl_cnt, m->tl_list, ntok, topk, m->tl_xq, m->tl_xs, ly.up_b, m->tl_gu, 2 * d, d, m->st, s));
     launch_swiglu_quant(m->tl_gu, ntok * topk, d, m->tl_hq, m->tl_hs, s);
-    CUL(launch_mx_tile_experts(ly.down, ne, d, m->tl_cnt, m->tl_list, 1, m->tl_hq, m->tl_hs, ly.down_b, m->tl_part, d, 0, m->st, s));
+    CUL(launch_mx_tile_experts(ly.down, ne, d, m->tl_cnt, m->tl_list, ntok, 1, m->tl_hq, m->tl_hs, ly.down_b, m->tl_part, d, 0, m->st, s));
     launch_tile_combine(m->tl_part, m->tl_wts, topk, d, ntok, d_x, s);
     CU(cudaGetLastError());
     return BRRR_OK;
 }
 
 extern "C" int brrr_moe_ffn_tile(brrr_model *m, int il, const float *d_xn, float *d_x, int ntok, int32_t *d_top, float *d_wts) {
-    if (!m || !d_xn || !d_x || il < 0 || il >= m->cfg.n_layer || ntok < 1 || ntok > 16) return BRRR_ERR_ARG;
+    if (!m || !d_xn || !d_x || il < 0 || il >= m->cfg.n_layer || ntok < 1 || ntok > BRRR_TILE_MAX) return BRRR_ERR_ARG;
     if (m->ep) return BRRR_ERR_STATE;
     CU(cudaSetDevice(m->device));
     const int topk = m->cfg.n_expert_used;

@@ -33,6 +33,8 @@ enum {
 };
 
 #define BRRR_MAXSEQ 4096     /* src/bin/engine_gpt2.rs:16 */
+#define BRRR_TILE_MAX 64     /* most token rows one pass over the layers takes (the reference's TILE is 16, src/bin/engine_gpt2.rs:19;
+                              * every row's result is independent of the tile size) */
 
 /* Model hyper-parameters: the keys of the data directory's config.txt
  * (scripts/setup_model.sh:71-89, parsed at src/bin/engine_gpt2.rs:58-80). */
@@ -76,11 +78,12 @@ int brrr_forward(brrr_model *m, uint32_t tok, uint32_t pos, int want_logits, uin
  * the reference guarantees for run_tile (src/bin/engine_gpt2.rs:1004-1010, 1387-1393). */
 int brrr_forward_tile(brrr_model *m, const uint32_t *toks, uint32_t n, uint32_t pos0, int want_logits, uint32_t *out_tok);
 
-/* Schedule of brrr_forward_tile.  on = 0 (default): one graph launch per token.  on != 0: tiles of 16
- * tokens walk the layers together as in forward_tile_worker (src/bin/engine_gpt2.rs:1011-1250, TILE = 16):
- * q/k/v, attention and the output projection per token, the MoE block once per layer and tile on the
- * tensor-core tile kernels.  Same bits either way; the environment variable BRRR_TILE_PREFILL=1
- * sets the initial value.  Ignored by expert-parallel ranks (always token-serial). */
+/* Schedule of brrr_forward_tile.  on != 0 (default): tiles of up to BRRR_TILE_MAX tokens walk the layers
+ * together as in forward_tile_worker (src/bin/engine_gpt2.rs:1011-1250, where TILE = 16): q/k/v and the
+ * output projection once per 16 rows, attention for all rows in one launch, the MoE block once per layer
+ * and tile on the tensor-core tile kernels.  on = 0: one graph launch per token.  Same bits either way;
+ * the environment variables BRRR_TILE_PREFILL=0/1 and BRRR_TILE_ROWS=n (2..BRRR_TILE_MAX) set the initial
+ * values.  Ignored by expert-parallel ranks (always token-serial). */
 int brrr_model_set_tile_prefill(brrr_model *m, int on);
 
 /* n greedy decode steps starting from `first_tok` at position `pos`, the token id staying on the
@@ -319,7 +322,7 @@ void brrr_mxmat_free(brrr_mxmat *m);
  * (src/bin/engine_gpt2.rs:193-228). */
 int brrr_mx_matvec(const brrr_mxmat *w, int row0, int nrows, const int8_t *d_xq, const float *d_xs, float *d_y, int32_t *d_blockdots, void *stream);
 
-/* The same product for a tile of up to 16 tokens in one pass over the weights, on the tcgen05
+/* The same product for a tile of up to BRRR_TILE_MAX tokens in one pass over the weights, on the tcgen05
  * tensor cores (int8 MMA into tensor memory, float chains in the epilogue): d_y[t * ldy + i] = row
  * (row0 + i) . activation t, each value bit-identical to brrr_mx_matvec on token t alone.
  * d_xq [ntok][blocks * 32] int8, d_xs [ntok][blocks].  Replaces the expert products of the tile
@@ -374,7 +377,7 @@ int brrr_moe_ffn_step_tc(brrr_model *m, int il, const float *d_xn, float *d_x, i
 /* 1 when the decode step of this model runs its expert matvecs on the tensor cores. */
 int brrr_model_uses_tensor_experts(const brrr_model *m);
 
-/* The same MoE FFN for a tile of 1..16 normalised tokens (d_xn [ntok][n_embd], d_x [ntok][n_embd]
+/* The same MoE FFN for a tile of 1..BRRR_TILE_MAX normalised tokens (d_xn [ntok][n_embd], d_x [ntok][n_embd]
  * residuals, d_top / d_wts nullable [ntok][n_expert_used]): per-token router, then gate / up /
  * down as grouped tensor-core matmuls (tcgen05) that read each selected expert once for all the
  * tokens routed to it.  Bit-identical to brrr_moe_ffn_step applied token by token.  Replaces the MoE

@@ -290,19 +290,22 @@ def test_speculation_can_be_disabled(brrr, orc, monkeypatch):
 
 
 def test_prompt_tiles_match_serial(brrr):
-    """With the tile schedule switched on, run_tile walks tiles of 16 tokens through the layers together
-    (MoE block on the tensor-core tile kernels); the reference guarantees its batched prefill is bit-identical to the token-serial
+    """run_tile walks tiles of tokens through the layers together (MoE block on the tensor-core tile
+    kernels); the reference guarantees its batched prefill is bit-identical to the token-serial
     schedule (src/bin/engine_gpt2.rs:1005-1010).  Checked on the last token's hidden state and logits,
-    on the returned token, and on a decode run that reads the KV cache the tiles wrote.  37 tokens =
-    two full tiles and a ragged one; a 1-token call takes the serial path."""
+    on the returned token, and on a decode run that reads the KV cache the tiles wrote, for tiles of 64
+    (the default: 150 tokens = two full tiles and a ragged one of 22) and of 16 (the reference's TILE);
+    a 1-token call takes the serial path."""
     cfg = brrr.make_cfg(256, 3, 8, 2, 8, 4, 1024, sliding_window=8)
     eng = brrr.Engine.synth(cfg, 11)
-    prompt = [int(t) for t in S.synth_prompt(11, 37, 1000)]
+    prompt = [int(t) for t in S.synth_prompt(11, 150, 1000)]
     tok_s = 0
+    eng.set_tile_prefill(False)
     for i, t in enumerate(prompt):
         tok_s = eng.run(t, i, i == len(prompt) - 1)
     h_s, l_s = eng.hidden(), eng.logits()
     dec_s = eng.decode(tok_s, len(prompt), 24)
+    assert eng.run_tile(prompt, 0, True) == tok_s                  # the serial schedule through run_tile
     eng.set_tile_prefill(True)
     tok_t = eng.run_tile(prompt, 0, True)
     h_t, l_t = eng.hidden(), eng.logits()
@@ -314,4 +317,13 @@ def test_prompt_tiles_match_serial(brrr):
     eng.run_tile(prompt[:-1], 0, False)
     assert eng.run(prompt[-1], len(prompt) - 1, True) == tok_s
     assert eng.run_tile(prompt[:1], 0, True) == eng.run(prompt[0], 0, True)
+    eng.close()
+    import os
+    os.environ["BRRR_TILE_ROWS"] = "16"
+    try:
+        eng = brrr.Engine.synth(cfg, 11)
+    finally:
+        del os.environ["BRRR_TILE_ROWS"]
+    assert eng.run_tile(prompt, 0, True) == tok_s
+    assert np.array_equal(bits(eng.hidden()), bits(h_s)) and np.array_equal(bits(eng.logits()), bits(l_s))
     eng.close()
