@@ -293,6 +293,73 @@ def run_moe_tile(args):
     eng.close()
 
 
+def run_batched(args):
+    """--workload batched: greedy decode of b = 1, 4, 16, 64 independent sequences (one KV cache each, 32-token
+    prompts) through Engine.batch_step, one pass per step for all rows of the batch.  One step = one pass
+    = b tokens; the clock is the host's around the calls (each returns the rows' tokens to host memory).  The
+    first 16 tokens of four sequences are checked against the one-sequence engine."""
+    import numpy as np
+    import torch
+    import cpubrrr_b200 as B
+    from cpubrrr_b200 import synth as S
+    torch.cuda.set_device(0)
+    eng = B.Engine.synth(B.gptoss_20b_cfg() if args.layers == 24 else B.make_cfg(2880, args.layers, 64, 8, 32, 4, args.vocab), SEED)
+    vmax = 199999 if args.vocab > 199999 else args.vocab - 1
+    plen, nb = 32, 64
+    prompts = [[int(t) for t in S.synth_prompt(SEED + 100 + i, plen, vmax)] for i in range(nb)]
+    # the checker: four sequences on the one-sequence engine (token-serial schedule)
+    ncheck, want = 16, []
+    eng.set_tile_prefill(False)
+    for s in range(4):
+        tok = 0
+        for i, t in enumerate(prompts[s]):
+            tok = eng.run(t, i, i == plen - 1)
+        w = [tok]
+        for k in range(1, ncheck):
+            tok = eng.run(tok, plen + k - 1, True)
+            w.append(tok)
+        want.append(w)
+    # serial decode rate of one sequence, for scale
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    eng.decode(want[0][-1], plen + ncheck - 1, 64)
+    serial_tok_s = 64 / (time.perf_counter() - t0)
+    eng.batch_open(nb)
+    rows, same = [], True
+    steps = max(args.steps, ncheck)
+    for b in (1, 4, 16, 64):
+        for s in range(b):
+            eng.batch_prefill(s, prompts[s][:-1])
+        toks = [prompts[s][-1] for s in range(b)]
+        pos = [plen - 1] * b
+        seqs = list(range(b))
+        got = [[] for _ in range(b)]
+        for k in range(max(args.warmup, 3)):                     # warm-up passes (captures the graph of this row count)
+            out = eng.batch_step(toks, [p + k for p in pos], seqs) if k == 0 else eng.batch_step([int(t) for t in out], [p + k for p in pos], seqs)
+            for s in range(b):
+                got[s].append(int(out[s]))
+        w = max(args.warmup, 3)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        for k in range(w, w + steps):
+            out = eng.batch_step([int(t) for t in out], [p + k for p in pos], seqs)
+            for s in range(b):
+                got[s].append(int(out[s]))
+        dt = time.perf_counter() - t0
+        for s in range(min(b, 4)):
+            same = same and got[s][:ncheck] == want[s]
+        rows.append({"batch": b, "tok_s": b * steps / dt, "ms_per_pass": 1000 * dt / steps, "per_sequence_tok_s": steps / dt})
+    best = rows[-1]
+    print(json.dumps({"metric": "batched decode tok/s (gpt-oss-20b shape, independent sequences)", "value": best["tok_s"], "unit": "tok/s", "n_gpus": 1,
+                      "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": best["ms_per_pass"], "higher_is_better": True, "scaling": "weak",
+                      "vs_baseline": None, "dtype": "int8xfp4->int32 (tcgen05 kind::i8), int8 dp4a, f32", "data": "synthetic",
+                      "config": {"workload": "gpt-oss-20b batched greedy decode, 32-token prompts, b = 1/4/16/64 sequences, wall clock through Engine.batch_step",
+                                 "l2": "inputs larger than L2 (every pass streams the dense layers, the routed experts and the vocabulary projection)"},
+                      "batches": rows, "one_sequence_decode_tok_s": serial_tok_s,
+                      "parity": {"sequences_checked": 4, "tokens_each": ncheck, "identical_to_one_sequence_engine": bool(same)}}), flush=True)
+    eng.close()
+
+
 def run_prefill(args):
     """--workload prefill: one 2048-token prompt through Engine.run_tile (tiles of 64 tokens: q/k/v and o-proj
     per 16 rows, attention for all rows in one launch, the MoE block per tile on the tcgen05 tile kernels)
@@ -355,13 +422,15 @@ def main():
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline / parity leg")
     ap.add_argument("--no-stages", action="store_true", help="skip the per-kernel-class timing")
     ap.add_argument("--no-ep", action="store_true", help="N > 1: skip the expert-parallel gpt-oss-120b leg")
-    ap.add_argument("--workload", default="gptoss20b", choices=["gptoss20b", "gptoss120b", "qwen3-30b-a3b", "moe-tile", "prefill"],
+    ap.add_argument("--workload", default="gptoss20b", choices=["gptoss20b", "gptoss120b", "qwen3-30b-a3b", "moe-tile", "prefill", "batched"],
                     help="gptoss20b is the benchmark workload; gptoss120b is the expert-parallel configuration; qwen3-30b-a3b measures the reference's second engine")
     ap.add_argument("--parallel", default="replicas", choices=["replicas", "ep"],
                     help="N > 1: independent replicas (weak scaling, default) or one sequence with the experts sharded over the ranks (strong scaling)")
     ap.add_argument("--layers", type=int, default=24, help="profiling aid: fewer layers (not the benchmark workload)")
     ap.add_argument("--vocab", type=int, default=201088, help="profiling aid: smaller vocabulary (not the benchmark workload)")
     args = ap.parse_args()
+    if args.workload == "batched":
+        return run_batched(args)
     if args.workload == "moe-tile":
         run_moe_tile(args)
         return

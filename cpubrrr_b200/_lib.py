@@ -38,6 +38,10 @@ SIGNATURES = {
     "brrr_forward": (_I, [_P, C.c_uint32, C.c_uint32, _I, C.POINTER(C.c_uint32)]),
     "brrr_forward_tile": (_I, [_P, _P, C.c_uint32, C.c_uint32, _I, C.POINTER(C.c_uint32)]),
     "brrr_model_set_tile_prefill": (_I, [_P, _I]),
+    "brrr_batch_open": (_I, [_P, _I]),
+    "brrr_batch_prefill": (_I, [_P, C.c_uint32, _P, C.c_uint32, C.c_uint32]),
+    "brrr_batch_step": (_I, [_P, _I, _P, _P, _P, _P]),
+    "brrr_batch_step_logits": (_I, [_P, _I, _P, _P, _P, _P, _P]),
     "brrr_decode": (_I, [_P, C.c_uint32, C.c_uint32, C.c_uint32, _P]),
     "brrr_decode_enqueue": (_I, [_P, C.c_uint32, C.c_uint32, C.c_uint32]),
     "brrr_decode_wait": (_I, [_P, C.c_uint32, _P]),

@@ -9,6 +9,9 @@
 #include <stdint.h>
 
 #define BRRR_MAXSEQ 4096
+#ifndef BRRR_TILE_MAX
+#define BRRR_TILE_MAX 64      // token rows per pass over the layers (same value as in the public header)
+#endif
 
 // ---------------------------------------------------------------- scalar helpers
 __device__ __forceinline__ float brrr_expf_dev(float x) {

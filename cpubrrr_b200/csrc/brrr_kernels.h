@@ -20,6 +20,7 @@ cudaError_t launch_kv_append_rows(const float *qkv, int ldq, int nh, int nkv, fl
 void launch_embed(const uint16_t *embd, int d, const DevState *state, float *x, cudaStream_t st);
 void launch_embed_tok(const uint16_t *embd, int d, uint32_t tok, float *x, cudaStream_t st);
 // ntok rows from token ids in device memory: x[t] = embedding of toks[t]
+void launch_rows_argmax(const float *logits, int n_vocab, int rows, uint32_t *out, cudaStream_t st);   // out[t] = first index of the largest logit of row t
 void launch_embed_tile(const uint16_t *embd, int d, const uint32_t *toks_dev, int ntok, float *x, cudaStream_t st);
 void launch_swiglu_quant(const float *gu, int topk, int d, int8_t *hq, float *hs, cudaStream_t st);
 void launch_finish_token(DevState *state, cudaStream_t st);

@@ -1,13 +1,13 @@
-// Token rows: the dense half of a layer for up to 16 tokens at once (prompt tiles and batched decode
+// Token rows: the dense half of a layer for up to 64 tokens at once (prompt tiles and batched decode
 // over independent sequences; forward_tile_worker, src/bin/engine_gpt2.rs:1011-1250, keeps the
 // per-token arithmetic and shares each weight pass among the tokens of a tile).  Every value is
 // computed by the same operation sequence as in the one-token kernels, so results are bit-identical
 // to the token-serial schedule.
 //
 //   rmsnorm_quant (grid = rows)      one CTA per row, the one-token kernel with row offsets (kernels_small.cu)
-//   q8_rows_kernel                   Q8 matrix x the Q8 activations of all rows: the CTA's weights go into
-//                                    registers once (before the dependency wait), the rows' activations into
-//                                    shared memory once, then one chain walk per row
+//   q8_rows_kernel                   Q8 matrix x the Q8 activations of the rows: a CTA = 16 matrix rows x 8 token rows;
+//                                    its weights go into registers once (before the dependency wait), the rows'
+//                                    activations into shared memory, then one chain walk per four token rows
 //   kv_append_rows_kernel            RoPE of every row's k and the cache append of k and v, before any row attends
 //   attn_decode_kernel (grid.y = rows, kernels_attn.cu)
 #include "brrr_kernels.h"
@@ -19,6 +19,7 @@ namespace brrr {
 namespace {
 
 constexpr int QR_THREADS = 128;
+constexpr int QR_TPC = 8;               // token rows per CTA (blockIdx.y walks the groups)
 
 struct Q8RowsArgs {
     Q8Dev m;
@@ -54,62 +55,79 @@ __global__ void __launch_bounds__(QR_THREADS) q8_rows_kernel(Q8RowsArgs a) {
     if (out && (EPI == Q8_EPI_BIAS || EPI == Q8_EPI_RESID_BIAS)) bias_pre = a.bias[row];
     pdl_wait();
     pdl_trigger();
-    // the activation images of all rows: [row][np * 8] int2 then [row][nb] floats
+    // the activation images of this CTA's token rows: [row][np * 8] int2 then [row][nb] floats
+    const int t_first = blockIdx.y * QR_TPC, ntok = min(QR_TPC, a.ntok - t_first);
     int2 *xp = reinterpret_cast<int2 *>(rsm);
-    float *xsc = reinterpret_cast<float *>(xp + (size_t)a.ntok * np * 8);
+    float *xsc = reinterpret_cast<float *>(xp + (size_t)QR_TPC * np * 8);
     const int nidx = np * 8;
-    for (int i = tid; i < a.ntok * nidx; i += QR_THREADS) {
+    for (int i = tid; i < ntok * nidx; i += QR_THREADS) {
         const int t = i / nidx, idx = i % nidx;
-        const int *xw = reinterpret_cast<const int *>(a.xq + (size_t)t * a.m.cols + (idx >> 2) * 32);
+        const int *xw = reinterpret_cast<const int *>(a.xq + (size_t)(t_first + t) * a.m.cols + (idx >> 2) * 32);
         xp[i] = make_int2(xw[idx & 3], xw[4 + (idx & 3)]);
     }
-    for (int i = tid; i < a.ntok * nb; i += QR_THREADS) xsc[i] = a.xs[i];
+    for (int i = tid; i < ntok * nb; i += QR_THREADS) xsc[i] = a.xs[(size_t)t_first * nb + i];
     __syncthreads();
-    for (int t = 0; t < a.ntok; t++) {
-        const int2 *xpt = xp + (size_t)t * nidx + c8;
-        const float *xst = xsc + (size_t)t * nb + p;
-        float acc = 0.0f;
+    // four token rows per walk over the weights: their chains are independent, so their instructions interleave
+    for (int t0 = 0; t0 < ntok; t0 += 4) {
+        const int2 *xpt[4];
+        const float *xst[4];
+        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+#pragma unroll
+        for (int g = 0; g < 4; g++) {
+            const int t = min(t0 + g, ntok - 1);                 // rows past the end repeat the last one (never stored)
+            xpt[g] = xp + (size_t)t * nidx + c8;
+            xst[g] = xsc + (size_t)t * nb + p;
+        }
         if (NP > 0) {
 #pragma unroll
             for (int i = 0; i < (NP > 0 ? NP : 1); i++) {
-                const int2 xv = xpt[i * 8];
-                const int d = __dp4a(w[i].y, xv.y, __dp4a(w[i].x, xv.x, 0));
-                acc = __fmaf_rn((float)d, __fmul_rn(s[i], xst[i * 2]), acc);
+#pragma unroll
+                for (int g = 0; g < 4; g++) {
+                    const int2 xv = xpt[g][i * 8];
+                    const int d = __dp4a(w[i].y, xv.y, __dp4a(w[i].x, xv.x, 0));
+                    acc[g] = __fmaf_rn((float)d, __fmul_rn(s[i], xst[g][i * 2]), acc[g]);
+                }
             }
         } else {
             for (int i = 0; i < np; i++) {
                 const int2 wv = __ldg(wp + (size_t)i * (Q8_UNIT / 8));
                 const float sv = __ldg(sp + (size_t)i * (Q8_UNIT / 4));
-                const int2 xv = xpt[i * 8];
-                const int d = __dp4a(wv.y, xv.y, __dp4a(wv.x, xv.x, 0));
-                acc = __fmaf_rn((float)d, __fmul_rn(sv, xst[i * 2]), acc);
+#pragma unroll
+                for (int g = 0; g < 4; g++) {
+                    const int2 xv = xpt[g][i * 8];
+                    const int d = __dp4a(wv.y, xv.y, __dp4a(wv.x, xv.x, 0));
+                    acc[g] = __fmaf_rn((float)d, __fmul_rn(sv, xst[g][i * 2]), acc[g]);
+                }
             }
         }
-        float r = __fadd_rn(acc, __shfl_xor_sync(0xffffffffu, acc, 4));      // acc_even + acc_odd per lane, then (l0+l1)+(l2+l3)
-        r = brrr_hsum4(r);
-        if (out) {
-            float *yp = a.y + (size_t)t * a.ldy + row;
-            if (EPI == Q8_EPI_PLAIN) *yp = r;
-            else if (EPI == Q8_EPI_BIAS) *yp = __fadd_rn(r, bias_pre);
-            else *yp = __fadd_rn(*yp, __fadd_rn(r, bias_pre));                // x += dot + bias
+#pragma unroll
+        for (int g = 0; g < 4; g++) {
+            float r = __fadd_rn(acc[g], __shfl_xor_sync(0xffffffffu, acc[g], 4));      // acc_even + acc_odd per lane, then (l0+l1)+(l2+l3)
+            r = brrr_hsum4(r);
+            if (out && t0 + g < ntok) {
+                float *yp = a.y + (size_t)(t_first + t0 + g) * a.ldy + row;
+                if (EPI == Q8_EPI_PLAIN) *yp = r;
+                else if (EPI == Q8_EPI_BIAS) *yp = __fadd_rn(r, bias_pre);
+                else *yp = __fadd_rn(*yp, __fadd_rn(r, bias_pre));                // x += dot + bias
+            }
         }
     }
 }
 
 template <int NP>
-cudaError_t q8_rows_launch(const Q8RowsArgs &a, int epi, unsigned grid, size_t smem, bool pdl, cudaStream_t st) {
+cudaError_t q8_rows_launch(const Q8RowsArgs &a, int epi, dim3 grid, size_t smem, bool pdl, cudaStream_t st) {
     static unsigned long long configured[3] = {0, 0, 0};
     cudaError_t e;
     switch (epi) {
     case Q8_EPI_PLAIN:
         if ((e = smem_optin(q8_rows_kernel<Q8_EPI_PLAIN, NP>, 160 * 1024, configured[0])) != cudaSuccess) return e;
-        return launch_k(q8_rows_kernel<Q8_EPI_PLAIN, NP>, dim3(grid), dim3(QR_THREADS), smem, st, pdl, a);
+        return launch_k(q8_rows_kernel<Q8_EPI_PLAIN, NP>, grid, dim3(QR_THREADS), smem, st, pdl, a);
     case Q8_EPI_BIAS:
         if ((e = smem_optin(q8_rows_kernel<Q8_EPI_BIAS, NP>, 160 * 1024, configured[1])) != cudaSuccess) return e;
-        return launch_k(q8_rows_kernel<Q8_EPI_BIAS, NP>, dim3(grid), dim3(QR_THREADS), smem, st, pdl, a);
+        return launch_k(q8_rows_kernel<Q8_EPI_BIAS, NP>, grid, dim3(QR_THREADS), smem, st, pdl, a);
     case Q8_EPI_RESID_BIAS:
         if ((e = smem_optin(q8_rows_kernel<Q8_EPI_RESID_BIAS, NP>, 160 * 1024, configured[2])) != cudaSuccess) return e;
-        return launch_k(q8_rows_kernel<Q8_EPI_RESID_BIAS, NP>, dim3(grid), dim3(QR_THREADS), smem, st, pdl, a);
+        return launch_k(q8_rows_kernel<Q8_EPI_RESID_BIAS, NP>, grid, dim3(QR_THREADS), smem, st, pdl, a);
     }
     return cudaErrorInvalidValue;
 }
@@ -138,18 +156,46 @@ __global__ void __launch_bounds__(64) kv_append_rows_kernel(KvRowsArgs a) {
     a.vc[o + tid] = v[tid];
 }
 
+// Index of the largest logit of every row, the lowest index among equals: the same 64-bit key (ordered float bits,
+// inverted index) the one-token head folds with atomicMax.  One CTA per row.
+__global__ void __launch_bounds__(1024) rows_argmax_kernel(const float *__restrict__ logits, int n_vocab, uint32_t *__restrict__ out) {
+    __shared__ unsigned long long wbest[32];
+    const float *row = logits + (size_t)blockIdx.x * n_vocab;
+    unsigned long long best = 0ull;
+    for (int i = threadIdx.x; i < n_vocab; i += 1024) {
+        const unsigned long long key = ((unsigned long long)float_orderable(row[i]) << 32) | (0xFFFFFFFFu - (uint32_t)i);
+        best = key > best ? key : best;
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const unsigned long long other = __shfl_xor_sync(0xffffffffu, best, o);
+        best = other > best ? other : best;
+    }
+    if ((threadIdx.x & 31) == 0) wbest[threadIdx.x >> 5] = best;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 32; w++) best = wbest[w] > best ? wbest[w] : best;
+        out[blockIdx.x] = 0xFFFFFFFFu - (uint32_t)(best & 0xFFFFFFFFull);
+    }
+}
+
 }  // namespace
 
-// y[t][r] (+)= row r of m . activation t (+ bias) for t < ntok <= 16.  epi: Q8_EPI_PLAIN / BIAS / RESID_BIAS.
+void launch_rows_argmax(const float *logits, int n_vocab, int rows, uint32_t *out, cudaStream_t st) {
+    rows_argmax_kernel<<<rows, 1024, 0, st>>>(logits, n_vocab, out);
+}
+
+// y[t][r] (+)= row r of m . activation t (+ bias) for t < ntok <= 64.  epi: Q8_EPI_PLAIN / BIAS / RESID_BIAS.
 cudaError_t launch_q8_rows(Q8Dev m, const int8_t *xq, const float *xs, int ntok, const float *bias, float *y, int ldy, int epi, bool pdl,
                            cudaStream_t st) {
-    if (ntok < 1 || ntok > 16 || m.cols % 64) return cudaErrorInvalidValue;
+    if (ntok < 1 || ntok > BRRR_TILE_MAX || m.cols % 64) return cudaErrorInvalidValue;
     Q8RowsArgs a{m, xq, xs, bias, y, ntok, ldy};
     const int np = m.cols / 64, urows = q8_urows(m.rows);
-    const size_t smem = (size_t)ntok * np * 72;
-    if (np == 45) return q8_rows_launch<45>(a, epi, (unsigned)urows, smem, pdl, st);
-    if (np == 64) return q8_rows_launch<64>(a, epi, (unsigned)urows, smem, pdl, st);
-    return q8_rows_launch<0>(a, epi, (unsigned)urows, smem, pdl, st);
+    const size_t smem = (size_t)QR_TPC * np * 72;
+    const dim3 grid((unsigned)urows, (unsigned)((ntok + QR_TPC - 1) / QR_TPC));
+    if (np == 45) return q8_rows_launch<45>(a, epi, grid, smem, pdl, st);
+    if (np == 64) return q8_rows_launch<64>(a, epi, grid, smem, pdl, st);
+    return q8_rows_launch<0>(a, epi, grid, smem, pdl, st);
 }
 
 cudaError_t launch_kv_append_rows(const float *qkv, int ldq, int nh, int nkv, float *kc, float *vc, size_t seq_stride, const float *rope,

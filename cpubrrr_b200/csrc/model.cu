@@ -164,8 +164,8 @@ struct brrr_model {
     // batched decode over independent sequences: one KV cache per sequence and layer
     int nseq = 0;
     std::vector<float *> kcb, vcb;               // per layer: [nseq][nkv][MAXSEQ][64]
-    float *bt_logits = nullptr;                  // [16][n_vocab]
-    unsigned long long *bt_best = nullptr;       // [16] running argmax per row
+    float *bt_logits = nullptr;                  // [BRRR_TILE_MAX][n_vocab]
+    uint32_t *bt_tok = nullptr;                  // [BRRR_TILE_MAX] argmax per row
     int tile_rows = BRRR_TILE_MAX;               // tokens per prompt tile (BRRR_TILE_ROWS=n, 2..64): any size gives the same bits
     bool tile_prefill = true;                    // run_tile on 16-token tiles (brrr_model_set_tile_prefill / BRRR_TILE_PREFILL=0 switch to token-serial; same bits)
     unsigned int *tl_counter = nullptr;
@@ -884,7 +884,7 @@ static int rows_alloc(brrr_model *m) {
 
 static int enqueue_rows(brrr_model *m, int n, bool batch, bool pdl) {
     const brrr_cfg &c = m->cfg;
-    const int d = c.n_embd, nh = c.n_head, nkv = c.n_head_kv, qkv_rows = (nh + 2 * nkv) * c.head_dim, ao = nh * c.head_dim;
+    const int d = c.n_embd, nh = c.n_head, nkv = c.n_head_kv, qkv_rows = (nh + 2 * nkv) * c.head_dim;
     cudaStream_t s = m->stream;
     launch_embed_tile(m->tok_embd, d, m->tl_toks, n, m->tl_x, s);
     for (int il = 0; il < c.n_layer; il++) {
@@ -895,16 +895,11 @@ static int enqueue_rows(brrr_model *m, int n, bool batch, bool pdl) {
         const size_t seq_stride = batch ? (size_t)nkv * BRRR_MAXSEQ * c.head_dim : 0;
         // the first kernel after a plain launch takes the full dependency
         CUL(launch_rmsnorm_quant(m->tl_x, ly.attn_norm, c.rms_eps, d, nullptr, m->tl_nq, m->tl_ns, false, s, n));
-        // the projections take up to 16 rows per pass over the weights (later passes of a tile find them in L2)
-        for (int r0 = 0; r0 < n; r0 += 16)
-            CUL(launch_q8_rows(ly.wqkv, m->tl_nq + (size_t)r0 * d, m->tl_ns + (size_t)r0 * (d / 32), std::min(16, n - r0), ly.bqkv, m->tl_qkv + (size_t)r0 * qkv_rows,
-                               qkv_rows, Q8_EPI_BIAS, pdl, s));
+        CUL(launch_q8_rows(ly.wqkv, m->tl_nq, m->tl_ns, n, ly.bqkv, m->tl_qkv, qkv_rows, Q8_EPI_BIAS, pdl, s));
         CUL(launch_kv_append_rows(m->tl_qkv, qkv_rows, nh, nkv, kc, vc, seq_stride, m->rope, m->tl_pos, m->tl_seq, n, pdl, s));
         CUL(launch_attn_decode(m->tl_qkv, kc, vc, m->rope, ly.sinks, nh, nkv, nullptr, 0, window, m->tl_ao, m->tl_aq, m->tl_as, m->st, pdl, s, 0,
                                m->tl_pos, m->tl_seq, seq_stride, qkv_rows, n));
-        for (int r0 = 0; r0 < n; r0 += 16)
-            CUL(launch_q8_rows(ly.wo, m->tl_aq + (size_t)r0 * ao, m->tl_as + (size_t)r0 * (ao / 32), std::min(16, n - r0), ly.bo, m->tl_x + (size_t)r0 * d, d,
-                               Q8_EPI_RESID_BIAS, pdl, s));
+        CUL(launch_q8_rows(ly.wo, m->tl_aq, m->tl_as, n, ly.bo, m->tl_x, d, Q8_EPI_RESID_BIAS, pdl, s));
         CUL(launch_rmsnorm_quant(m->tl_x, ly.ffn_norm, c.rms_eps, d, m->tl_xn, m->tl_nq, m->tl_ns, pdl, s, n));
         TRY(moe_tile_enqueue(m, il, m->tl_xn, m->tl_x, n));
     }
@@ -984,6 +979,75 @@ extern "C" int brrr_forward_tile(brrr_model *m, const uint32_t *toks, uint32_t n
         CU(cudaStreamSynchronize(m->stream));
         if (m->h_out[6] != 0) { snprintf(g_cuda_err, sizeof g_cuda_err, "device wait timed out (code %u)", m->h_out[6]); return BRRR_ERR_STATE; }
         if (want && out_tok) *out_tok = m->h_out[0];
+    }
+    return BRRR_OK;
+}
+
+// ---- batched decode over independent sequences: one KV cache per sequence, rows = (token, position, sequence)
+extern "C" int brrr_batch_open(brrr_model *m, int nseq) {
+    if (!m || nseq < 1 || nseq > BRRR_BATCH_MAX) return BRRR_ERR_ARG;
+    if (m->ep || m->nseq) return BRRR_ERR_STATE;
+    CU(cudaSetDevice(m->device));
+    const brrr_cfg &c = m->cfg;
+    const size_t per_seq = (size_t)c.n_head_kv * BRRR_MAXSEQ * c.head_dim;
+    m->kcb.assign(c.n_layer, nullptr); m->vcb.assign(c.n_layer, nullptr);
+    for (int il = 0; il < c.n_layer; il++) { TRY(m->alloc(&m->kcb[il], per_seq * nseq)); TRY(m->alloc(&m->vcb[il], per_seq * nseq)); }
+    TRY(m->alloc(&m->bt_logits, (size_t)BRRR_TILE_MAX * c.n_vocab));
+    TRY(m->alloc(&m->bt_tok, BRRR_TILE_MAX));
+    TRY(rows_alloc(m));
+    m->nseq = nseq;
+    return BRRR_OK;
+}
+
+static int batch_check(brrr_model *m, int n, const uint32_t *toks, const uint32_t *pos, const uint32_t *seq) {
+    if (!m || !toks || !pos || !seq || n < 1 || n > BRRR_TILE_MAX) return BRRR_ERR_ARG;
+    if (!m->nseq) return BRRR_ERR_STATE;
+    for (int t = 0; t < n; t++)
+        if (toks[t] >= (uint32_t)m->cfg.n_vocab || pos[t] >= BRRR_MAXSEQ || seq[t] >= (uint32_t)m->nseq) return BRRR_ERR_RANGE;
+    return BRRR_OK;
+}
+
+// The layers for n rows on the sequences' caches; with out_toks, the vocabulary projection and argmax of every row.
+static int batch_rows(brrr_model *m, int n, const uint32_t *toks, const uint32_t *pos, const uint32_t *seq, uint32_t *out_toks, float *out_logits) {
+    TRY(batch_check(m, n, toks, pos, seq));
+    CU(cudaSetDevice(m->device));
+    const brrr_cfg &c = m->cfg;
+    cudaStream_t s = m->stream;
+    TRY(rows_run(m, n, toks, pos, seq, true));
+    if (out_toks || out_logits) {
+        CUL(launch_rmsnorm_quant(m->tl_x, m->out_norm, c.rms_eps, c.n_embd, nullptr, m->tl_nq, m->tl_ns, false, s, n));
+        CUL(launch_q8_rows(m->head, m->tl_nq, m->tl_ns, n, nullptr, m->bt_logits, c.n_vocab, Q8_EPI_PLAIN, false, s));
+        launch_rows_argmax(m->bt_logits, c.n_vocab, n, m->bt_tok, s);
+        CU(cudaGetLastError());
+        CU(cudaMemcpyAsync(m->h_out + 8, m->bt_tok, (size_t)n * 4, cudaMemcpyDeviceToHost, s));
+        if (out_logits) CU(cudaMemcpyAsync(out_logits, m->bt_logits, (size_t)n * c.n_vocab * sizeof(float), cudaMemcpyDeviceToHost, s));
+    }
+    CU(cudaMemcpyAsync(m->h_out, m->st, 32, cudaMemcpyDeviceToHost, s));
+    CU(cudaStreamSynchronize(s));
+    if (m->h_out[6] != 0) { snprintf(g_cuda_err, sizeof g_cuda_err, "device wait timed out (code %u)", m->h_out[6]); return BRRR_ERR_STATE; }
+    if (out_toks) for (int t = 0; t < n; t++) out_toks[t] = m->h_out[8 + t];
+    return BRRR_OK;
+}
+
+extern "C" int brrr_batch_step(brrr_model *m, int n, const uint32_t *toks, const uint32_t *pos, const uint32_t *seq, uint32_t *out_toks) {
+    if (!out_toks) return BRRR_ERR_ARG;
+    return batch_rows(m, n, toks, pos, seq, out_toks, nullptr);
+}
+
+extern "C" int brrr_batch_step_logits(brrr_model *m, int n, const uint32_t *toks, const uint32_t *pos, const uint32_t *seq, uint32_t *out_toks, float *out_logits) {
+    if (!out_toks || !out_logits) return BRRR_ERR_ARG;
+    return batch_rows(m, n, toks, pos, seq, out_toks, out_logits);
+}
+
+extern "C" int brrr_batch_prefill(brrr_model *m, uint32_t seq, const uint32_t *toks, uint32_t n, uint32_t pos0) {
+    if (!m || !toks || n == 0) return BRRR_ERR_ARG;
+    if (!m->nseq) return BRRR_ERR_STATE;
+    if (pos0 + n > BRRR_MAXSEQ || seq >= (uint32_t)m->nseq) return BRRR_ERR_RANGE;
+    uint32_t pos[BRRR_TILE_MAX], sq[BRRR_TILE_MAX];
+    for (uint32_t i0 = 0; i0 < n; i0 += BRRR_TILE_MAX) {
+        const uint32_t cnt = n - i0 < BRRR_TILE_MAX ? n - i0 : BRRR_TILE_MAX;
+        for (uint32_t t = 0; t < cnt; t++) { pos[t] = pos0 + i0 + t; sq[t] = seq; }
+        TRY(batch_rows(m, (int)cnt, toks + i0, pos, sq, nullptr, nullptr));
     }
     return BRRR_OK;
 }

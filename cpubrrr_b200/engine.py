@@ -73,6 +73,29 @@ class Engine:
         check(lib().brrr_forward_tile(self._h, t.ctypes.data, t.size, int(pos0), int(bool(want)), C.byref(out)), "brrr_forward_tile")
         return int(out.value)
 
+    # ---- batched decode over independent sequences (one KV cache each)
+    def batch_open(self, nseq):
+        check(lib().brrr_batch_open(self._h, int(nseq)), "brrr_batch_open")
+
+    def batch_prefill(self, seq, ids, pos0=0):
+        t = np.ascontiguousarray(ids, dtype=np.uint32)
+        check(lib().brrr_batch_prefill(self._h, int(seq), t.ctypes.data, t.size, int(pos0)), "brrr_batch_prefill")
+
+    def batch_step(self, toks, pos, seq, logits=False):
+        """One pass for the rows (toks[i], pos[i], seq[i]); returns the greedy next token of every row
+        (and the rows' logits with logits=True)."""
+        t = np.ascontiguousarray(toks, dtype=np.uint32)
+        p = np.ascontiguousarray(pos, dtype=np.uint32)
+        s = np.ascontiguousarray(seq, dtype=np.uint32)
+        assert t.size == p.size == s.size
+        out = np.empty(t.size, np.uint32)
+        if logits:
+            lg = np.empty((t.size, self.cfg.n_vocab), np.float32)
+            check(lib().brrr_batch_step_logits(self._h, t.size, t.ctypes.data, p.ctypes.data, s.ctypes.data, out.ctypes.data, lg.ctypes.data), "brrr_batch_step_logits")
+            return out, lg
+        check(lib().brrr_batch_step(self._h, t.size, t.ctypes.data, p.ctypes.data, s.ctypes.data, out.ctypes.data), "brrr_batch_step")
+        return out
+
     def decode(self, first_tok, pos, n):
         out = np.empty(n, np.uint32)
         check(lib().brrr_decode(self._h, int(first_tok), int(pos), int(n), out.ctypes.data), "brrr_decode")

@@ -33,8 +33,10 @@ enum {
 };
 
 #define BRRR_MAXSEQ 4096     /* src/bin/engine_gpt2.rs:16 */
+#ifndef BRRR_TILE_MAX
 #define BRRR_TILE_MAX 64     /* most token rows one pass over the layers takes (the reference's TILE is 16, src/bin/engine_gpt2.rs:19;
                               * every row's result is independent of the tile size) */
+#endif
 
 /* Model hyper-parameters: the keys of the data directory's config.txt
  * (scripts/setup_model.sh:71-89, parsed at src/bin/engine_gpt2.rs:58-80). */
@@ -85,6 +87,25 @@ int brrr_forward_tile(brrr_model *m, const uint32_t *toks, uint32_t n, uint32_t 
  * the environment variables BRRR_TILE_PREFILL=0/1 and BRRR_TILE_ROWS=n (2..BRRR_TILE_MAX) set the initial
  * values.  Ignored by expert-parallel ranks (always token-serial). */
 int brrr_model_set_tile_prefill(brrr_model *m, int on);
+
+/* Batched decode over independent sequences.  The reference decodes one sequence; its tile path
+ * (forward_tile_worker, src/bin/engine_gpt2.rs:1011-1250) already walks several token rows through a
+ * layer together and groups them by routed expert (the `subs` / `active` lists, :1160-1172).  Here a
+ * row is (token, position, sequence): every sequence has its own KV cache, the dense projections and
+ * the vocabulary projection read their weights once per 8 rows, each selected expert is read once
+ * for all the rows routed to it.  Every row's result is bit-identical to brrr_forward on that
+ * sequence alone.
+ *   brrr_batch_open     allocates nseq (1..BRRR_BATCH_MAX) caches; once per model, not with expert-parallel ranks
+ *   brrr_batch_prefill  feeds n prompt tokens of one sequence from position pos0 (tiles, no logits)
+ *   brrr_batch_step     n rows (1..BRRR_TILE_MAX) in one pass; out_toks[i] = greedy next token of row i.
+ *                       A row attends over its sequence's cache up to pos[i] - 1 plus itself; rows of one
+ *                       sequence must carry ascending positions
+ *   brrr_batch_step_logits  the same, and the rows' logits [n][n_vocab] to host memory */
+#define BRRR_BATCH_MAX 64
+int brrr_batch_open(brrr_model *m, int nseq);
+int brrr_batch_prefill(brrr_model *m, uint32_t seq, const uint32_t *toks, uint32_t n, uint32_t pos0);
+int brrr_batch_step(brrr_model *m, int n, const uint32_t *toks, const uint32_t *pos, const uint32_t *seq, uint32_t *out_toks);
+int brrr_batch_step_logits(brrr_model *m, int n, const uint32_t *toks, const uint32_t *pos, const uint32_t *seq, uint32_t *out_toks, float *out_logits);
 
 /* n greedy decode steps starting from `first_tok` at position `pos`, the token id staying on the
  * device between steps (one graph launch per step, no host round trip); out_toks[i] is the token
