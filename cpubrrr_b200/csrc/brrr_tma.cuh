@@ -42,6 +42,17 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
     return ok != 0;
 }
 
+// the same with a suspend-time hint: the warp sleeps in hardware until the phase completes or about `ns`
+// nanoseconds have passed, so a thread that waits long issues few instructions while it waits
+__device__ __forceinline__ bool mbar_try_wait_hint(uint64_t *bar, uint32_t parity, uint32_t ns) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2, %3;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok)
+                 : "r"(smem_u32(bar)), "r"(parity), "r"(ns)
+                 : "memory");
+    return ok != 0;
+}
+
 // non-blocking probe: cheap when the phase has already completed
 __device__ __forceinline__ bool mbar_test_wait(uint64_t *bar, uint32_t parity) {
     uint32_t ok;
@@ -73,6 +84,20 @@ struct Waiter {
         do {
             for (int i = 0; i < 128; i++)
                 if (mbar_try_wait(bar, parity)) return true;
+        } while (clock64() - t0 < WAIT_CYCLES);
+        dead = true;
+        if (err) atomicCAS(err, (uint32_t)DEV_ERR_NONE, (uint32_t)DEV_ERR_COPY_TIMEOUT);
+        return false;
+    }
+    // The same bounded wait with hardware suspension between probes (see mbar_try_wait_hint): for roles that
+    // spend most of their time waiting beside busy warps (producers, issuing threads) and must still wake at once.
+    __device__ __forceinline__ bool wait_suspended(uint64_t *bar, uint32_t parity) {
+        if (dead) return false;
+        if (mbar_test_wait(bar, parity)) return true;
+        const long long t0 = clock64();
+        do {
+            for (int i = 0; i < 16; i++)
+                if (mbar_try_wait_hint(bar, parity, 4000u)) return true;
         } while (clock64() - t0 < WAIT_CYCLES);
         dead = true;
         if (err) atomicCAS(err, (uint32_t)DEV_ERR_NONE, (uint32_t)DEV_ERR_COPY_TIMEOUT);

@@ -9,7 +9,7 @@
 // The serial sums are one thread each (64 output dims + 1 denominator).
 //
 // The cache is laid out [kv head][position][64] so the window of one head is one contiguous
-// range; it is brought into shared memory in tiles of 128 positions by bulk asynchronous copies
+// range; it is brought into shared memory in tiles of 128 positions (32 for token rows) by bulk asynchronous copies
 // issued before the kernel waits on its predecessor (the cached positions are older than this
 // token).  The current position's k and v never come from the cache: every head recomputes them.
 #include "brrr_kernels.h"
@@ -20,9 +20,9 @@ namespace brrr {
 
 constexpr int HD = 64;
 constexpr int AT_THREADS = 256;
-constexpr int AT_TILE = 128;                       // positions per tile
+constexpr int AT_TILE_ONE = 128;                   // positions per tile: one token per launch (one CTA per SM streams its head's window)
+constexpr int AT_TILE_ROWS = 32;                   // token rows: many (head, row) CTAs share an SM, so each holds less
 constexpr int AT_SLOTS = 2;                        // ring depth per tensor
-constexpr size_t AT_TILE_BYTES = (size_t)AT_TILE * HD * sizeof(float);
 
 struct AttnArgs {
     const float *qkv;
@@ -50,7 +50,9 @@ struct AttnArgs {
 #endif
 constexpr int kScoreUnroll = AT_SCORE_UNROLL;      // keys of the score loop in flight per thread group (their shuffle chains overlap)
 
+template <int AT_TILE>
 __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(AttnArgs a) {
+    constexpr size_t AT_TILE_BYTES = (size_t)AT_TILE * HD * sizeof(float);
     extern __shared__ __align__(128) unsigned char smraw[];
     float *ktiles = reinterpret_cast<float *>(smraw);                                   // [AT_SLOTS][128][64]
     float *vtiles = reinterpret_cast<float *>(smraw + AT_TILE_BYTES * AT_SLOTS);
@@ -232,19 +234,22 @@ __global__ void __launch_bounds__(AT_THREADS) attn_decode_kernel(AttnArgs a) {
     BRRR_GT_END(a.err_state, 191);
 }
 
-static size_t attn_smem() { return AT_TILE_BYTES * AT_SLOTS * 2 + (size_t)BRRR_MAXSEQ * 4 + AT_SLOTS * 2 * 8; }
+static size_t attn_smem(int tile) { return (size_t)tile * HD * sizeof(float) * AT_SLOTS * 2 + (size_t)BRRR_MAXSEQ * 4 + AT_SLOTS * 2 * 8; }
 
 cudaError_t launch_attn_decode(const float *qkv, float *kc, float *vc, const float *rope, const float *sinks, int nh, int nkv,
                                const DevState *state, int pos_val, int window, float *ao, int8_t *aq, float *as,
                                DevState *err_state, bool pdl, cudaStream_t st, int pos_off, const int *row_pos, const int *row_seq, size_t seq_stride,
                                int ldq, int rows) {
     AttnArgs a{qkv, kc, vc, rope, sinks, nh, nkv, state, pos_val, window, pos_off, ao, aq, as, err_state, row_pos, row_seq, seq_stride, ldq};
-    static unsigned long long configured = 0;      // one bit per device
-    {
-        cudaError_t e = smem_optin(attn_decode_kernel, (int)attn_smem(), configured);
+    static unsigned long long configured = 0, configured_rows = 0;      // one bit per device
+    if (row_pos) {
+        cudaError_t e = smem_optin(attn_decode_kernel<AT_TILE_ROWS>, (int)attn_smem(AT_TILE_ROWS), configured_rows);
         if (e != cudaSuccess) return e;
+        return launch_k(attn_decode_kernel<AT_TILE_ROWS>, dim3(nh, rows), dim3(AT_THREADS), attn_smem(AT_TILE_ROWS), st, pdl, a);
     }
-    return launch_k(attn_decode_kernel, dim3(nh, row_pos ? rows : 1), dim3(AT_THREADS), attn_smem(), st, pdl, a);
+    cudaError_t e = smem_optin(attn_decode_kernel<AT_TILE_ONE>, (int)attn_smem(AT_TILE_ONE), configured);
+    if (e != cudaSuccess) return e;
+    return launch_k(attn_decode_kernel<AT_TILE_ONE>, dim3(nh, 1), dim3(AT_THREADS), attn_smem(AT_TILE_ONE), st, pdl, a);
 }
 
 }  // namespace brrr

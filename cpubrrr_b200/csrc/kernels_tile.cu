@@ -175,7 +175,7 @@ __global__ void __launch_bounds__(TL_THREADS, 3) mx_tile_kernel(TileArgs a) {
         int slot = 0;
         uint32_t par = 0;
         for (int p = 0; p + TL_DEPTH < np; p++) {
-            waiter.wait(&empty[slot], par);                              // every worker has read pair p out of the slot
+            waiter.wait_suspended(&empty[slot], par);                              // every worker has read pair p out of the slot
             load(p + TL_DEPTH, slot);
             if (++slot == TL_DEPTH) { slot = 0; par ^= 1u; }
         }
@@ -192,7 +192,7 @@ __global__ void __launch_bounds__(TL_THREADS, 3) mx_tile_kernel(TileArgs a) {
         }
         for (int p = 0; p < np; p++) {
             const int h = p & 1;
-            waiter.wait(&staged[h], (uint32_t)(p >> 1) & 1u);
+            waiter.wait_suspended(&staged[h], (uint32_t)(p >> 1) & 1u);
             tl_fence_after();
             const uint32_t dcol = tmem_base + (uint32_t)((2 * h + k) * N);
             if (h == 0) { tl_mma(dcol, da[0][0], db[0], 0u, IDESC); tl_mma(dcol, da[0][1], db[0], 1u, IDESC); }
@@ -227,7 +227,7 @@ __global__ void __launch_bounds__(TL_THREADS, 3) mx_tile_kernel(TileArgs a) {
         // operands of pair q -> half (q & 1) of the tiles; returns the row's two exponent bytes
         auto stage = [&](int q) -> uint32_t {
             const int h = q & 1;
-            waiter.wait(&full[f_slot], f_par);
+            waiter.wait_suspended(&full[f_slot], f_par);
             const unsigned char *u = my_unit + f_slot * TL_SLOT;
             const int q_slot = f_slot;
             if (++f_slot == TL_DEPTH) { f_slot = 0; f_par ^= 1u; }
@@ -265,7 +265,7 @@ __global__ void __launch_bounds__(TL_THREADS, 3) mx_tile_kernel(TileArgs a) {
         // float chains of pair p: thread = row (tensor-memory lane), N columns per block
         auto chains = [&](int p, uint32_t e2c) {
             const int h = p & 1;
-            waiter.wait(&done[h], (uint32_t)(p >> 1) & 1u);
+            waiter.wait_suspended(&done[h], (uint32_t)(p >> 1) & 1u);
             tl_fence_after();
 #pragma unroll
             for (int k = 0; k < 2; k++) {
