@@ -374,6 +374,18 @@ def run_prefill(args):
     eng = B.Engine.synth(B.gptoss_20b_cfg() if args.layers == 24 else B.make_cfg(2880, args.layers, 64, 8, 32, 4, args.vocab), SEED)
     n = 2048
     prompt = [int(t) for t in S.synth_prompt(SEED, n, 199999 if args.vocab > 199999 else args.vocab - 1)]
+    if args.profile_range:
+        # for a profiler started with --profile-from-start off: two tiles untimed, then one tile inside the range
+        tr = int(os.environ.get("BRRR_TILE_ROWS", "64"))
+        eng.run_tile(prompt[:2 * tr], 0, False)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.start()
+        eng.run_tile(prompt[2 * tr:3 * tr], 2 * tr, False)
+        torch.cuda.synchronize()
+        torch.cuda.profiler.stop()
+        print(json.dumps({"profile_range": "one prompt tile", "tile_rows": tr, "layers": eng.cfg.n_layer}), flush=True)
+        eng.close()
+        return
     sample = 256
     # serial sample (also the checker)
     tile_rows = int(os.environ.get("BRRR_TILE_ROWS", "64"))
@@ -421,6 +433,9 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu", action="store_true", help="skip the CPU baseline / parity leg")
     ap.add_argument("--no-stages", action="store_true", help="skip the per-kernel-class timing")
+    ap.add_argument("--profile-range", action="store_true",
+                    help="for ncu --profile-from-start off: cudaProfilerStart/Stop around the K timed decode steps (decode workloads), or around "
+                         "one prompt tile after two untimed ones (--workload prefill, which then exits)")
     ap.add_argument("--no-ep", action="store_true", help="N > 1: skip the expert-parallel gpt-oss-120b leg")
     ap.add_argument("--workload", default="gptoss20b", choices=["gptoss20b", "gptoss120b", "qwen3-30b-a3b", "moe-tile", "prefill", "batched"],
                     help="gptoss20b is the benchmark workload; gptoss120b is the expert-parallel configuration; qwen3-30b-a3b measures the reference's second engine")
@@ -518,10 +533,16 @@ def main():
         barrier()
         if sampler:
             sampler.start()
+        if args.profile_range:
+            torch.cuda.synchronize()
+            torch.cuda.profiler.start()          # for ncu --profile-from-start off: exactly the K timed steps
         e0.record(stream)
         eng.decode_enqueue(first, PROMPT_LEN, K)
         toks = eng.decode_wait(K)
         e1.record(stream)
+        if args.profile_range:
+            torch.cuda.synchronize()
+            torch.cuda.profiler.stop()
         barrier()
         ms = reduce_max(e0.elapsed_time(e1))
         redos = (eng.spec_redos() if hasattr(eng, "spec_redos") else 0) - redos0
