@@ -101,6 +101,7 @@ SIGNATURES = {
     "brrr_q8mat_export": (_I, [_P, _P, _P, _P]),
     "brrr_q8mat_free": (None, [_P]),
     "brrr_q8_matvec": (_I, [_P, _P, _P, _P, _P]),
+    "brrr_q8_matmul_rows": (_I, [_P, _P, _P, _I, _P, _I, _I, _P]),
     "brrr_mxmat_from_gguf": (_I, [_P, _I, _I, C.POINTER(_P), _P]),
     "brrr_mxmat_free": (None, [_P]),
     "brrr_mx_matvec": (_I, [_P, _I, _I, _P, _P, _P, _P, _P]),

@@ -13,7 +13,7 @@ cudaError_t launch_rmsnorm_quant(const float *x, const float *w, float eps, int 
                                  int rows = 1);
 // ---- token rows (kernels_rows.cu): y[t][r] (+)= row r of m . activation t (+ bias), t < ntok <= 16
 cudaError_t launch_q8_rows(Q8Dev m, const int8_t *xq, const float *xs, int ntok, const float *bias, float *y, int ldy, int epi, bool pdl,
-                           cudaStream_t st);
+                           cudaStream_t st, DevState *state = nullptr, int engine = -1);
 // RoPE of every row's k and the cache append of k and v (row t: position row_pos[t] of sequence row_seq[t])
 cudaError_t launch_kv_append_rows(const float *qkv, int ldq, int nh, int nkv, float *kc, float *vc, size_t seq_stride, const float *rope,
                                   const int *row_pos, const int *row_seq, int rows, bool pdl, cudaStream_t st);
@@ -153,6 +153,8 @@ cudaError_t launch_mx_tile(MxDev w, int row0, int nrows, const int8_t *xq, const
 // entry i reads activation row entry / src_div and writes y[entry * ldy + col0 + row] (+ bias[e][row])
 cudaError_t launch_mx_tile_experts(MxDev w, int ne, int rows_per_expert, const int *cnt, const int *list, int max_entries, int src_div, const int8_t *xq,
                                    const float *xs, const float *bias, float *y, int ldy, int col0, DevState *state, cudaStream_t st);
+cudaError_t launch_q8_tile(Q8Dev m, const int8_t *xq, const float *xs, int ntok, const float *bias, float *y, int ldy, int epi, DevState *state,
+                           bool pdl, cudaStream_t st);          // Q8 matrix x token rows on kind::i8 (kernels_tile.cu)
 void launch_tile_route(const int32_t *top, int ntok, int topk, int ne, int *cnt, int *list, cudaStream_t st);
 void launch_tile_combine(const float *part, const float *wts, int topk, int d, int ntok, float *x, cudaStream_t st);
 

@@ -78,6 +78,14 @@ extern "C" int brrr_q8_matvec(const brrr_q8mat *w, const int8_t *d_xq, const flo
     return check_launch();
 }
 
+extern "C" int brrr_q8_matmul_rows(const brrr_q8mat *w, const int8_t *d_xq, const float *d_xs, int ntok, float *d_y, int ldy, int tensor_cores,
+                                   void *stream) {
+    if (!w || !d_xq || !d_xs || !d_y || ntok < 1 || ntok > BRRR_TILE_MAX || ldy < w->m.rows) return BRRR_ERR_ARG;
+    if (launch_q8_rows(w->m, d_xq, d_xs, ntok, nullptr, d_y, ldy, Q8_EPI_PLAIN, false, (cudaStream_t)stream, nullptr, tensor_cores ? 1 : 0) != cudaSuccess)
+        return BRRR_ERR_CUDA;
+    return check_launch();
+}
+
 extern "C" int brrr_mxmat_from_gguf(const uint8_t *d_raw, int rows, int blocks, brrr_mxmat **out, void *stream) {
     if (!d_raw || !out || rows <= 0 || rows % 16 || blocks <= 0 || blocks % 2) return BRRR_ERR_ARG;
     brrr_mxmat *x = new brrr_mxmat();

@@ -10,6 +10,7 @@
 //                                    activations into shared memory, then one chain walk per four token rows
 //   kv_append_rows_kernel            RoPE of every row's k and the cache append of k and v, before any row attends
 //   attn_decode_kernel (grid.y = rows, kernels_attn.cu)
+#include <cstdlib>
 #include "brrr_kernels.h"
 #include "brrr_block.cuh"
 #include "brrr_tma.cuh"
@@ -186,9 +187,15 @@ void launch_rows_argmax(const float *logits, int n_vocab, int rows, uint32_t *ou
 }
 
 // y[t][r] (+)= row r of m . activation t (+ bias) for t < ntok <= 64.  epi: Q8_EPI_PLAIN / BIAS / RESID_BIAS.
+// engine: 0 = integer units (the default: measured faster at every tile size so far), 1 = tensor cores (launch_q8_tile,
+// kernels_tile.cu), -1 = the environment variable BRRR_Q8_TILE=1 selects the tensor cores for tiles of at least 32 rows of
+// the layer projections.  Same bits either way.
 cudaError_t launch_q8_rows(Q8Dev m, const int8_t *xq, const float *xs, int ntok, const float *bias, float *y, int ldy, int epi, bool pdl,
-                           cudaStream_t st) {
+                           cudaStream_t st, DevState *state, int engine) {
     if (ntok < 1 || ntok > BRRR_TILE_MAX || m.cols % 64) return cudaErrorInvalidValue;
+    static const bool env_tile = [] { const char *e = getenv("BRRR_Q8_TILE"); return e && e[0] && e[0] != '0'; }();
+    const bool tile = engine == 1 || (engine < 0 && env_tile && ntok >= 32 && m.rows <= 16384);
+    if (tile) return launch_q8_tile(m, xq, xs, ntok, bias, y, ldy, epi, state, pdl, st);
     Q8RowsArgs a{m, xq, xs, bias, y, ntok, ldy};
     const int np = m.cols / 64, urows = q8_urows(m.rows);
     const size_t smem = (size_t)QR_TPC * np * 72;

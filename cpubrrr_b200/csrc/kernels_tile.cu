@@ -305,6 +305,206 @@ __global__ void __launch_bounds__(TL_THREADS, 3) mx_tile_kernel(TileArgs a) {
     if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
 }
 
+// ---------------------------------------------------------------- Q8 matrix x token rows (dense projections of a tile)
+// The Q8 row dot (dot_q8_i8, src/bin/engine_gpt2.rs:169-191) is 2 block parities x 4 lanes of chains,
+// chain (p, j) accumulating fma(float(t_j(b)), w_scale[b] * xs[b], acc) over the blocks b of parity p, t_j(b) the
+// exact integer dot of the lane's 8 weights with its 8 activation bytes; the row is (e0 + e1) + (e2 + e3) with
+// e_j = acc[0][j] + acc[1][j].  The weights are int8 already, so the producer warp copies the 16-byte pieces of a
+// unit straight to their place in the K-major operand tile and no thread decodes anything: one product per block
+// (128 rows x 16 columns x 32), workers = entry staging + chains.  One CTA = 128 matrix rows x up to 4 token rows.
+constexpr int QT_DEPTH = 4;
+constexpr int QT_STAGE = 2 * TL_A_BYTES + TL_ROWS * 8;      // two operand tiles (the pair's blocks) + [128 rows][2] f32 block scales
+
+struct Q8TileArgs {
+    Q8Dev m;
+    const int8_t *xq;       // [token rows][cols]
+    const float *xs;        // [token rows][cols / 32]
+    const float *bias;
+    float *y;               // [token rows][ldy]
+    int ntok, ldy;
+    DevState *state;
+};
+
+template <int EPI, int NT>
+__global__ void __maxnreg__(96) q8_tile_kernel(Q8TileArgs a) {      // 96 registers: three CTAs of 7 warps (TL_THREADS) per SM
+    constexpr int N = 4 * NT;
+    constexpr uint32_t IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((TL_ROWS >> 4) << 24);
+    constexpr uint32_t TMEM_COLS = 4 * N;
+    extern __shared__ __align__(128) unsigned char tsm[];
+    const int np = a.m.cols / 64, nb = np * 2;
+    unsigned char *ring = tsm;                                                                                  // [QT_DEPTH][QT_STAGE]
+    unsigned char (*b_tiles)[N * 32] = reinterpret_cast<unsigned char (*)[N * 32]>(tsm + QT_DEPTH * QT_STAGE);  // [half][block of the pair]
+    float *xs_sm = reinterpret_cast<float *>(tsm + QT_DEPTH * QT_STAGE + 4 * N * 32);                           // [NT][nb]
+    __shared__ __align__(8) uint64_t full[QT_DEPTH], empty[QT_DEPTH], staged[2], done[2];
+    __shared__ uint32_t tmem_base_sh;
+    const int tid = threadIdx.x, warp = tid >> 5;
+    const int t_first = blockIdx.y * NT, n_ent = min(a.ntok - t_first, NT);
+    for (int i = tid; i < 4 * N * 32 / 16; i += TL_THREADS) reinterpret_cast<uint4 *>(&b_tiles[0][0])[i] = make_uint4(0, 0, 0, 0);   // rows of absent tokens stay zero
+    if (tid == 0) {
+        for (int i = 0; i < QT_DEPTH; i++) { mbar_init(&full[i], 32); mbar_init(&empty[i], 130); }
+        mbar_init(&staged[0], 128); mbar_init(&staged[1], 128);
+        mbar_init(&done[0], 2); mbar_init(&done[1], 2);
+        mbar_fence_init();
+    }
+    if (warp == 0) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_sh)), "r"(TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tl_fence_before();
+    __syncthreads();
+    tl_fence_after();
+    const uint32_t tmem_base = tmem_base_sh;
+    uint32_t *err = a.state ? &a.state->err : nullptr;
+    Waiter waiter(err);
+    const int urow0 = blockIdx.x * (TL_ROWS / 16);
+    const int n_units = min(TL_ROWS / 16, q8_urows(a.m.rows) - urow0);
+
+    if (warp == 4) {
+        // ---------------- producer: the weights are static, so the ring fills before the dependency wait
+        const int lane = tid & 31;
+        const unsigned char *wbase = a.m.data + q8_unit_off(urow0, 0, np);
+        const uint32_t unit_stride = (uint32_t)np * Q8_UNIT;
+        // this lane's pieces of a pair, offsets recomputed per copy (the producer has time; registers are the workers')
+        auto load = [&](int q, int slot) {
+            const unsigned char *src = wbase + (size_t)q * Q8_UNIT;
+            unsigned char *dst = ring + slot * QT_STAGE;
+#pragma unroll 4
+            for (int i = 0; i < 16; i++) {                       // operand pieces: (unit g, row rl, block p, half kh) -> tile p, K half kh, row m
+                const int idx = lane + 32 * i, kh = idx & 1, pp = (idx >> 1) & 1, rl = (idx >> 2) & 15, g = idx >> 6, m = g * 16 + rl;
+                if (g < n_units)
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst + pp * TL_A_BYTES + kh * 2048 + (m >> 3) * 128 + (m & 7) * 16)),
+                                 "l"(src + g * unit_stride + rl * 64 + pp * 32 + kh * 16) : "memory");
+            }
+#pragma unroll
+            for (int i = 0; i < 2; i++) {                        // block scales: 128 bytes per unit
+                const int idx = lane + 32 * i, g = idx >> 3, part = idx & 7;
+                if (g < n_units)
+                    asm volatile("cp.async.cg.shared.global [%0], [%1], 16;" ::"r"(smem_u32(dst + 2 * TL_A_BYTES + g * 128 + part * 16)),
+                                 "l"(src + g * unit_stride + Q8_UNIT_SCALES + part * 16) : "memory");
+            }
+            asm volatile("cp.async.mbarrier.arrive.noinc.shared::cta.b64 [%0];" ::"r"(smem_u32(&full[slot])) : "memory");
+        };
+        const int pre = min(QT_DEPTH, np);
+        for (int q = 0; q < pre; q++) load(q, q);
+        pdl_wait();
+        pdl_trigger();
+        int slot = 0;
+        uint32_t par = 0;
+        for (int p = 0; p + QT_DEPTH < np; p++) {
+            waiter.wait_suspended(&empty[slot], par);                    // the products of pair p are complete and its scales read
+            load(p + QT_DEPTH, slot);
+            if (++slot == QT_DEPTH) { slot = 0; par ^= 1u; }
+        }
+        asm volatile("cp.async.wait_all;" ::: "memory");
+    } else if (tid == 160 || tid == 192) {
+        // ---------------- issuers: block k of every pair
+        pdl_wait();
+        pdl_trigger();
+        const int k = tid == 160 ? 0 : 1;
+        const uint64_t da0 = tl_smem_desc(ring + k * TL_A_BYTES, 2048);
+        const uint64_t db[2] = {tl_smem_desc(&b_tiles[k][0], N * 16), tl_smem_desc(&b_tiles[2 + k][0], N * 16)};
+        int slot = 0;
+        for (int p = 0; p < np; p++) {
+            const int h = p & 1;
+            waiter.wait_suspended(&staged[h], (uint32_t)(p >> 1) & 1u);    // every worker has seen the pair's weights land and staged its entries
+            tl_fence_after();
+            tl_mma(tmem_base + (uint32_t)((2 * h + k) * N), da0 + (uint64_t)(slot * (QT_STAGE / 16)), h ? db[1] : db[0], 0u, IDESC);
+            tl_commit(&done[h]);
+            tl_commit(&empty[slot]);
+            if (++slot == QT_DEPTH) slot = 0;
+        }
+    } else if (tid < 128) {
+        // ---------------- workers: thread = matrix row of the tile
+        pdl_wait();
+        pdl_trigger();
+        const int row = blockIdx.x * TL_ROWS + tid;
+        const bool row_live = row < a.m.rows;
+        const int n_row = tid & 63, bt = n_row >> 2, bl = tid & 3, bblk = tid >> 6;
+        const bool b_live = n_row < N && bt < n_ent;
+        // B row n = token * 4 + lane: the lane's 8 activation bytes (positions 4 lane .. + 3 and 16 + 4 lane .. + 3, the order of the unit) at k = 8 lane .. + 7
+        const uint32_t b_off = (uint32_t)((bl >> 1) * (N * 16) + (n_row >> 3) * 128 + (n_row & 7) * 16 + (bl & 1) * 8);
+        const int8_t *my_x = a.xq + (size_t)(t_first + (b_live ? bt : 0)) * a.m.cols + bblk * 32 + 4 * bl;
+        uint32_t xlo = 0, xhi = 0;
+        if (b_live) { xlo = *reinterpret_cast<const uint32_t *>(my_x); xhi = *reinterpret_cast<const uint32_t *>(my_x + 16); }
+        for (int i = tid; i < n_ent * nb; i += 128) xs_sm[i] = a.xs[(size_t)t_first * nb + i];
+        float bias_pre = 0.0f;
+        if (row_live && (EPI == Q8_EPI_BIAS || EPI == Q8_EPI_RESID_BIAS)) bias_pre = a.bias[row];
+        asm volatile("bar.sync 1, 128;" ::: "memory");             // the workers' own barrier: xs_sm is complete
+        int f_slot = 0;
+        uint32_t f_par = 0;
+        auto stage = [&](int q) -> float2 {
+            const int h = q & 1;
+            waiter.wait_suspended(&full[f_slot], f_par);
+            const float2 sc = *reinterpret_cast<const float2 *>(ring + f_slot * QT_STAGE + 2 * TL_A_BYTES + tid * 8);
+            const int q_slot = f_slot;
+            if (++f_slot == QT_DEPTH) { f_slot = 0; f_par ^= 1u; }
+            if (b_live) {
+                *reinterpret_cast<uint2 *>(&b_tiles[2 * h + bblk][b_off]) = make_uint2(xlo, xhi);
+                if (q + 1 < np) {
+                    xlo = *reinterpret_cast<const uint32_t *>(my_x + (size_t)(q + 1) * 64);
+                    xhi = *reinterpret_cast<const uint32_t *>(my_x + (size_t)(q + 1) * 64 + 16);
+                }
+            }
+            fence_proxy_async();               // generic-proxy writes (these, and the producer's copies seen through full[]) -> the tensor core's reads
+            tl_fence_before();                 // this thread's reads of the half's accumulators are done
+            mbar_arrive(&staged[h]);
+            mbar_arrive(&empty[q_slot]);
+            return sc;
+        };
+        float acc[2][N];
+#pragma unroll
+        for (int i = 0; i < N; i++) { acc[0][i] = 0.0f; acc[1][i] = 0.0f; }
+        const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
+        auto chains = [&](int p, float2 sc) {
+            const int h = p & 1;
+            waiter.wait_suspended(&done[h], (uint32_t)(p >> 1) & 1u);
+            tl_fence_after();
+#pragma unroll
+            for (int k = 0; k < 2; k++) {
+                const float ws = k ? sc.y : sc.x;
+#pragma unroll
+                for (int c = 0; c < N / 16; c++) {             // 16 columns = four token rows at a time (registers)
+                    int d[16];
+                    tl_ld16(lane_addr + (uint32_t)((2 * h + k) * N + 16 * c), d);
+                    tl_wait_ld();
+#pragma unroll
+                    for (int t = 0; t < 4; t++) {
+                        const float sxs = __fmul_rn(ws, xs_sm[(4 * c + t) * nb + 2 * p + k]);
+#pragma unroll
+                        for (int l = 0; l < 4; l++) acc[k][16 * c + 4 * t + l] = __fmaf_rn((float)d[4 * t + l], sxs, acc[k][16 * c + 4 * t + l]);
+                    }
+                }
+            }
+        };
+        float2 scc = stage(0);
+        for (int p = 0; p < np; p++) {
+            float2 scn = make_float2(0.0f, 0.0f);
+            if (p + 1 < np) scn = stage(p + 1);
+            chains(p, scc);
+            scc = scn;
+        }
+        if (row_live) {
+#pragma unroll
+            for (int t = 0; t < NT; t++)
+                if (t < n_ent) {
+                    const float e0 = __fadd_rn(acc[0][4 * t], acc[1][4 * t]), e1 = __fadd_rn(acc[0][4 * t + 1], acc[1][4 * t + 1]);
+                    const float e2 = __fadd_rn(acc[0][4 * t + 2], acc[1][4 * t + 2]), e3 = __fadd_rn(acc[0][4 * t + 3], acc[1][4 * t + 3]);
+                    const float r = __fadd_rn(__fadd_rn(e0, e1), __fadd_rn(e2, e3));
+                    float *yp = a.y + (size_t)(t_first + t) * a.ldy + row;
+                    if (EPI == Q8_EPI_PLAIN) *yp = r;
+                    else if (EPI == Q8_EPI_BIAS) *yp = __fadd_rn(r, bias_pre);
+                    else *yp = __fadd_rn(*yp, __fadd_rn(r, bias_pre));                // x += dot + bias
+                }
+        }
+    } else {
+        pdl_wait();
+        pdl_trigger();
+    }
+    tl_fence_before();
+    __syncthreads();
+    if (warp == 0) asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(TMEM_COLS) : "memory");
+}
+
 // Per expert, the (token, slot) pairs routed to it, in ascending order: entry = token * topk + slot.  One CTA per
 // expert, thread = token (a token routes to an expert at most once, so the order is the token order).
 __global__ void __launch_bounds__(TL_MAXTOK) tile_route_kernel(const int32_t *__restrict__ top, int ntok, int topk, int *__restrict__ cnt, int *__restrict__ list) {
@@ -350,7 +550,33 @@ cudaError_t tl_launch(TileArgs a, int tiles, int experts, int max_entries, cudaS
     return cudaGetLastError();
 }
 
+template <int EPI, int NT>
+cudaError_t q8_tile_launch(const Q8TileArgs &a, bool pdl, cudaStream_t st) {
+    static unsigned long long configured = 0;      // one bit per device
+    cudaError_t e = smem_optin(q8_tile_kernel<EPI, NT>, 100 * 1024, configured);
+    if (e != cudaSuccess) return e;
+    const size_t smem = (size_t)QT_DEPTH * QT_STAGE + 4 * (4 * NT) * 32 + (size_t)NT * (a.m.cols / 32) * 4;
+    if (smem > 100 * 1024) return cudaErrorInvalidValue;
+    const dim3 grid((unsigned)((a.m.rows + TL_ROWS - 1) / TL_ROWS), (unsigned)((a.ntok + NT - 1) / NT));
+    return launch_k(q8_tile_kernel<EPI, NT>, grid, dim3(TL_THREADS), smem, st, pdl, a);
+}
+
 }  // namespace
+
+// y[t][r] (+)= row r of m . activation t (+ bias) on the tensor cores, t < ntok <= 64: bit-identical to the
+// integer-unit kernels (kernels_q8.cu, kernels_rows.cu).  Four token rows per CTA up to 4 rows, eight beyond.
+cudaError_t launch_q8_tile(Q8Dev m, const int8_t *xq, const float *xs, int ntok, const float *bias, float *y, int ldy, int epi, DevState *state,
+                           bool pdl, cudaStream_t st) {
+    if (ntok < 1 || ntok > BRRR_TILE_MAX || m.cols % 64 || m.cols < 64) return cudaErrorInvalidValue;
+    Q8TileArgs a{m, xq, xs, bias, y, ntok, ldy, state};
+    const bool wide = ntok > 4;
+    switch (epi) {
+    case Q8_EPI_PLAIN: return wide ? q8_tile_launch<Q8_EPI_PLAIN, 8>(a, pdl, st) : q8_tile_launch<Q8_EPI_PLAIN, 4>(a, pdl, st);
+    case Q8_EPI_BIAS: return wide ? q8_tile_launch<Q8_EPI_BIAS, 8>(a, pdl, st) : q8_tile_launch<Q8_EPI_BIAS, 4>(a, pdl, st);
+    case Q8_EPI_RESID_BIAS: return wide ? q8_tile_launch<Q8_EPI_RESID_BIAS, 8>(a, pdl, st) : q8_tile_launch<Q8_EPI_RESID_BIAS, 4>(a, pdl, st);
+    }
+    return cudaErrorInvalidValue;
+}
 
 cudaError_t launch_mx_tile(MxDev w, int row0, int nrows, const int8_t *xq, const float *xs, int ntok, float *y, int ldy, DevState *state,
                            cudaStream_t st) {

@@ -895,11 +895,11 @@ static int enqueue_rows(brrr_model *m, int n, bool batch, bool pdl) {
         const size_t seq_stride = batch ? (size_t)nkv * BRRR_MAXSEQ * c.head_dim : 0;
         // the first kernel after a plain launch takes the full dependency
         CUL(launch_rmsnorm_quant(m->tl_x, ly.attn_norm, c.rms_eps, d, nullptr, m->tl_nq, m->tl_ns, false, s, n));
-        CUL(launch_q8_rows(ly.wqkv, m->tl_nq, m->tl_ns, n, ly.bqkv, m->tl_qkv, qkv_rows, Q8_EPI_BIAS, pdl, s));
+        CUL(launch_q8_rows(ly.wqkv, m->tl_nq, m->tl_ns, n, ly.bqkv, m->tl_qkv, qkv_rows, Q8_EPI_BIAS, pdl, s, m->st));
         CUL(launch_kv_append_rows(m->tl_qkv, qkv_rows, nh, nkv, kc, vc, seq_stride, m->rope, m->tl_pos, m->tl_seq, n, pdl, s));
         CUL(launch_attn_decode(m->tl_qkv, kc, vc, m->rope, ly.sinks, nh, nkv, nullptr, 0, window, m->tl_ao, m->tl_aq, m->tl_as, m->st, pdl, s, 0,
                                m->tl_pos, m->tl_seq, seq_stride, qkv_rows, n));
-        CUL(launch_q8_rows(ly.wo, m->tl_aq, m->tl_as, n, ly.bo, m->tl_x, d, Q8_EPI_RESID_BIAS, pdl, s));
+        CUL(launch_q8_rows(ly.wo, m->tl_aq, m->tl_as, n, ly.bo, m->tl_x, d, Q8_EPI_RESID_BIAS, pdl, s, m->st));
         CUL(launch_rmsnorm_quant(m->tl_x, ly.ffn_norm, c.rms_eps, d, m->tl_xn, m->tl_nq, m->tl_ns, pdl, s, n));
         TRY(moe_tile_enqueue(m, il, m->tl_xn, m->tl_x, n));
     }
@@ -1016,7 +1016,7 @@ static int batch_rows(brrr_model *m, int n, const uint32_t *toks, const uint32_t
     TRY(rows_run(m, n, toks, pos, seq, true));
     if (out_toks || out_logits) {
         CUL(launch_rmsnorm_quant(m->tl_x, m->out_norm, c.rms_eps, c.n_embd, nullptr, m->tl_nq, m->tl_ns, false, s, n));
-        CUL(launch_q8_rows(m->head, m->tl_nq, m->tl_ns, n, nullptr, m->bt_logits, c.n_vocab, Q8_EPI_PLAIN, false, s));
+        CUL(launch_q8_rows(m->head, m->tl_nq, m->tl_ns, n, nullptr, m->bt_logits, c.n_vocab, Q8_EPI_PLAIN, false, s, m->st));
         launch_rows_argmax(m->bt_logits, c.n_vocab, n, m->bt_tok, s);
         CU(cudaGetLastError());
         CU(cudaMemcpyAsync(m->h_out + 8, m->bt_tok, (size_t)n * 4, cudaMemcpyDeviceToHost, s));

@@ -333,6 +333,11 @@ int brrr_q8mat_export(const brrr_q8mat *m, int8_t *d_q, float *d_s, void *stream
 void brrr_q8mat_free(brrr_q8mat *m);
 /* y[r] = row r . Q8 activation.  Replaces dot_q8_i8 / Q8Mat::dot (src/bin/engine_gpt2.rs:165-191, 495-500). */
 int brrr_q8_matvec(const brrr_q8mat *w, const int8_t *d_xq, const float *d_xs, float *d_y, void *stream);
+/* The same product for 1..BRRR_TILE_MAX token rows in one pass over the weights: d_y[t * ldy + r] = row r . activation t
+ * (d_xq [ntok][cols], d_xs [ntok][cols / 32]), every value bit-identical to brrr_q8_matvec on row t alone.  tensor_cores = 0:
+ * integer units (dp4a; what the prompt tiles and batched decode run), 1: tcgen05 kind::i8 products with the int8 weights copied
+ * straight into operand layout.  Replaces the q/k/v and o-proj loops of the tile path (src/bin/engine_gpt2.rs:1034-1118). */
+int brrr_q8_matmul_rows(const brrr_q8mat *w, const int8_t *d_xq, const float *d_xs, int ntok, float *d_y, int ldy, int tensor_cores, void *stream);
 
 /* GGUF MXFP4 rows (17-byte blocks, device) -> engine layout.  Replaces repack_mx
  * (src/bin/engine_gpt2.rs:439-461). rows % 16 == 0, blocks % 2 == 0. */

@@ -86,6 +86,37 @@ def test_q8_pack_and_matvec(L, orc, dev, rows, cols):
     L.brrr_q8mat_free(h)
 
 
+@pytest.mark.parametrize("rows,cols,ntok", [(64, 64, 1), (96, 2880, 5), (36, 4096, 16), (1028, 128, 9), (5120, 2880, 64), (2880, 4096, 33)])
+def test_q8_matmul_rows_equal_oracle_on_both_engines(L, orc, dev, rows, cols, ntok):
+    """Q8 matrix x token rows (the q/k/v and o-proj products of a tile) on the integer units and on the tcgen05
+    kind::i8 tensor-core kernel: every output equals the oracle's one-row dot bit for bit; nothing is written
+    beyond the matrix rows (ldy > rows), ragged row tiles and chunks included."""
+    import torch
+    wb = S.synth_bf16(rows + ntok, 1, S.T["WQ"], rows * cols)
+    h = C.c_void_p()
+    dw = to_dev(wb, dev)
+    ok(L.brrr_q8mat_from_bf16(P(dw), rows, cols, C.byref(h), None))
+    q, s = orc.q8_from_bf16(wb, rows, cols)
+    xq = np.empty((ntok, cols), np.int8); xs = np.empty((ntok, cols // 32), np.float32)
+    want = np.empty((ntok, rows), np.float32)
+    for t in range(ntok):
+        x = S.synth_input(200 + t, cols) * np.float32(0.25 + t)
+        if t == 2:
+            x[:96] = 0.0
+        xq[t], xs[t] = orc.quant_q8(x)
+        want[t] = orc.q8_matvec(q, s, xq[t], xs[t])
+    dxq, dxs = to_dev(xq, dev), to_dev(xs, dev)
+    ldy = rows + 5
+    for tensor_cores in (0, 1):
+        dy = torch.full((ntok, ldy), 3.0, dtype=torch.float32, device=dev)
+        ok(L.brrr_q8_matmul_rows(h, P(dxq), P(dxs), ntok, P(dy), ldy, tensor_cores, None))
+        torch.cuda.synchronize()
+        got = dy.cpu().numpy()
+        assert np.array_equal(bits(got[:, :rows]), bits(want)), f"engine {tensor_cores}"
+        assert np.all(got[:, rows:] == 3.0)
+    L.brrr_q8mat_free(h)
+
+
 @pytest.mark.parametrize("rows,blocks", [(16, 2), (64, 90), (208, 4), (2880, 90), (48, 26)])
 def test_mx_pack_and_matvec_int_exact(L, orc, dev, rows, blocks):
     """int32 lane accumulators of every (row, block) equal the oracle's; f32 row results too."""
