@@ -191,6 +191,9 @@ cudaError_t launch_router_hint(const float *x_in, const float *norm_w, float eps
 // ---- attention (kernels_attn.cu)
 // KV cache layout [n_head_kv][BRRR_MAXSEQ][64].  pos is read from state when state != nullptr,
 // else pos_val.  window = 0 means full attention.
+cudaError_t launch_attn_rows(const float *qkv, int ldq, const float *kc, const float *vc, size_t seq_stride, const float *rope, const float *sinks,
+                             int nh, int nkv, int window, const int *row_pos, const int *row_seq, int rows, float *ao, int8_t *aq, float *as,
+                             DevState *err_state, bool pdl, cudaStream_t st);       // rows of one sequence share their K / V tiles (prompt tiles)
 cudaError_t launch_attn_decode(const float *qkv, float *kc, float *vc, const float *rope, const float *sinks, int nh, int nkv,
                                const DevState *state, int pos_val, int window, float *ao, int8_t *aq, float *as,
                                DevState *err_state, bool pdl, cudaStream_t st, int pos_off = 0, const int *row_pos = nullptr,

@@ -166,6 +166,7 @@ struct brrr_model {
     std::vector<float *> kcb, vcb;               // per layer: [nseq][nkv][MAXSEQ][64]
     float *bt_logits = nullptr;                  // [BRRR_TILE_MAX][n_vocab]
     uint32_t *bt_tok = nullptr;                  // [BRRR_TILE_MAX] argmax per row
+    bool no_attn_rows = false;                   // BRRR_NO_ATTN_ROWS=1: prompt tiles use the per-(head, row) attention kernel (same bits)
     int tile_rows = BRRR_TILE_MAX;               // tokens per prompt tile (BRRR_TILE_ROWS=n, 2..64): any size gives the same bits
     bool tile_prefill = true;                    // run_tile on 16-token tiles (brrr_model_set_tile_prefill / BRRR_TILE_PREFILL=0 switch to token-serial; same bits)
     unsigned int *tl_counter = nullptr;
@@ -481,6 +482,7 @@ int build_model(brrr_model *m, const Source &src) {
         if (const char *e = getenv("BRRR_NOMXT")) if (e[0] && e[0] != '0') m->use_mxt = false;
         if (const char *e = getenv("BRRR_NOFUSEDFOLD")) if (e[0] && e[0] != '0') m->fused_fold = false;
         if (const char *e = getenv("BRRR_TILE_PREFILL")) m->tile_prefill = e[0] && e[0] != '0';
+        if (const char *e = getenv("BRRR_NO_ATTN_ROWS")) m->no_attn_rows = e[0] && e[0] != '0';
         if (const char *e = getenv("BRRR_TILE_ROWS")) { const int v = atoi(e); if (v >= 2 && v <= BRRR_TILE_MAX) m->tile_rows = v; }
     }
     for (int il = 0; il < c.n_layer; il++) {
@@ -897,8 +899,14 @@ static int enqueue_rows(brrr_model *m, int n, bool batch, bool pdl) {
         CUL(launch_rmsnorm_quant(m->tl_x, ly.attn_norm, c.rms_eps, d, nullptr, m->tl_nq, m->tl_ns, false, s, n));
         CUL(launch_q8_rows(ly.wqkv, m->tl_nq, m->tl_ns, n, ly.bqkv, m->tl_qkv, qkv_rows, Q8_EPI_BIAS, pdl, s, m->st));
         CUL(launch_kv_append_rows(m->tl_qkv, qkv_rows, nh, nkv, kc, vc, seq_stride, m->rope, m->tl_pos, m->tl_seq, n, pdl, s));
-        CUL(launch_attn_decode(m->tl_qkv, kc, vc, m->rope, ly.sinks, nh, nkv, nullptr, 0, window, m->tl_ao, m->tl_aq, m->tl_as, m->st, pdl, s, 0,
-                               m->tl_pos, m->tl_seq, seq_stride, qkv_rows, n));
+        // prompt tiles (rows of one sequence, ascending positions) share their K / V tiles; rows of different sequences cannot
+        const int group = nh / nkv;
+        if (!batch && !m->no_attn_rows && group <= 32 && (group & (group - 1)) == 0)
+            CUL(launch_attn_rows(m->tl_qkv, qkv_rows, kc, vc, seq_stride, m->rope, ly.sinks, nh, nkv, window, m->tl_pos, m->tl_seq, n, m->tl_ao, m->tl_aq,
+                                 m->tl_as, m->st, pdl, s));
+        else
+            CUL(launch_attn_decode(m->tl_qkv, kc, vc, m->rope, ly.sinks, nh, nkv, nullptr, 0, window, m->tl_ao, m->tl_aq, m->tl_as, m->st, pdl, s, 0,
+                                   m->tl_pos, m->tl_seq, seq_stride, qkv_rows, n));
         CUL(launch_q8_rows(ly.wo, m->tl_aq, m->tl_as, n, ly.bo, m->tl_x, d, Q8_EPI_RESID_BIAS, pdl, s, m->st));
         CUL(launch_rmsnorm_quant(m->tl_x, ly.ffn_norm, c.rms_eps, d, m->tl_xn, m->tl_nq, m->tl_ns, pdl, s, n));
         TRY(moe_tile_enqueue(m, il, m->tl_xn, m->tl_x, n));
