@@ -159,7 +159,7 @@ struct brrr_model {
     int *tl_pos = nullptr, *tl_seq = nullptr;
     uint32_t *h_tile = nullptr;                  // pinned: one 64-word slot per tile in flight
     uint32_t h_tile_next = 0;
-    cudaGraphExec_t g_rows[2][BRRR_TILE_MAX + 1] = {};          // [prompt tiles on the model's own cache | batched sequences][rows]: layers without the head
+    cudaGraphExec_t g_rows[3][BRRR_TILE_MAX + 1] = {};          // [ROWS_PROMPT | ROWS_BATCH | ROWS_BATCH_PROMPT][rows]: layers without the head
     bool rows_graph_failed = false;
     // batched decode over independent sequences: one KV cache per sequence and layer
     int nseq = 0;
@@ -869,6 +869,9 @@ static int moe_tile_enqueue(brrr_model *m, int il, const float *d_xn, float *d_x
 // schedule.  Everything is read from device arrays (tl_toks, tl_pos, tl_seq), so the enqueue is
 // captured once per row count and replayed.
 constexpr int ROWS_SLOTS = 64;          // pinned descriptor slots of rows_run
+// what the rows of a pass are: a prompt tile on the model's own cache, rows of any sequences of a batch, or a prompt tile of one
+// sequence of a batch (rows of one sequence with ascending positions share their K / V tiles in attention)
+enum { ROWS_PROMPT = 0, ROWS_BATCH = 1, ROWS_BATCH_PROMPT = 2 };
 
 static int rows_alloc(brrr_model *m) {
     if (m->tl_x) return BRRR_OK;
@@ -884,7 +887,8 @@ static int rows_alloc(brrr_model *m) {
     return BRRR_OK;
 }
 
-static int enqueue_rows(brrr_model *m, int n, bool batch, bool pdl) {
+static int enqueue_rows(brrr_model *m, int n, int kind, bool pdl) {
+    const bool batch = kind != ROWS_PROMPT, one_sequence = kind != ROWS_BATCH;
     const brrr_cfg &c = m->cfg;
     const int d = c.n_embd, nh = c.n_head, nkv = c.n_head_kv, qkv_rows = (nh + 2 * nkv) * c.head_dim;
     cudaStream_t s = m->stream;
@@ -901,7 +905,7 @@ static int enqueue_rows(brrr_model *m, int n, bool batch, bool pdl) {
         CUL(launch_kv_append_rows(m->tl_qkv, qkv_rows, nh, nkv, kc, vc, seq_stride, m->rope, m->tl_pos, m->tl_seq, n, pdl, s));
         // prompt tiles (rows of one sequence, ascending positions) share their K / V tiles; rows of different sequences cannot
         const int group = nh / nkv;
-        if (!batch && !m->no_attn_rows && group <= 32 && (group & (group - 1)) == 0)
+        if (one_sequence && !m->no_attn_rows && group <= 32 && (group & (group - 1)) == 0)
             CUL(launch_attn_rows(m->tl_qkv, qkv_rows, kc, vc, seq_stride, m->rope, ly.sinks, nh, nkv, window, m->tl_pos, m->tl_seq, n, m->tl_ao, m->tl_aq,
                                  m->tl_as, m->st, pdl, s));
         else
@@ -918,7 +922,7 @@ static int enqueue_rows(brrr_model *m, int n, bool batch, bool pdl) {
 // Run the layers for the n rows described by (toks, pos, seq) (host arrays): the descriptors go through a
 // pinned slot of their own to the device arrays, then the captured enqueue is replayed (captured at the
 // first use of each row count; a direct run comes first so that every kernel has its attributes set).
-static int rows_run(brrr_model *m, int n, const uint32_t *toks, const uint32_t *pos, const uint32_t *seq, bool batch) {
+static int rows_run(brrr_model *m, int n, const uint32_t *toks, const uint32_t *pos, const uint32_t *seq, int kind) {
     TRY(rows_alloc(m));
     const int R = BRRR_TILE_MAX;
     uint32_t *h = m->h_tile + (size_t)(m->h_tile_next++ % ROWS_SLOTS) * 3 * R;
@@ -927,14 +931,14 @@ static int rows_run(brrr_model *m, int n, const uint32_t *toks, const uint32_t *
     CU(cudaMemcpyAsync(m->tl_toks, h, (size_t)n * 4, cudaMemcpyHostToDevice, m->stream));
     CU(cudaMemcpyAsync(m->tl_pos, h + R, (size_t)n * 4, cudaMemcpyHostToDevice, m->stream));
     CU(cudaMemcpyAsync(m->tl_seq, h + 2 * R, (size_t)n * 4, cudaMemcpyHostToDevice, m->stream));
-    cudaGraphExec_t &g = m->g_rows[batch ? 1 : 0][n];
+    cudaGraphExec_t &g = m->g_rows[kind][n];
     if (g) { CU(cudaGraphLaunch(g, m->stream)); return BRRR_OK; }
-    TRY(enqueue_rows(m, n, batch, false));
+    TRY(enqueue_rows(m, n, kind, false));
     if (!m->rows_graph_failed) {
         CU(cudaStreamSynchronize(m->stream));
         cudaGraph_t gr = nullptr;
         CU(cudaStreamBeginCapture(m->stream, cudaStreamCaptureModeThreadLocal));
-        int st = enqueue_rows(m, n, batch, m->use_pdl);
+        int st = enqueue_rows(m, n, kind, m->use_pdl);
         cudaError_t e = cudaStreamEndCapture(m->stream, &gr);
         if (!(st == BRRR_OK && e == cudaSuccess && cudaGraphInstantiate(&g, gr, 0) == cudaSuccess)) { g = nullptr; m->rows_graph_failed = true; (void)cudaGetLastError(); }
         if (gr) cudaGraphDestroy(gr);
@@ -965,7 +969,7 @@ extern "C" int brrr_forward_tile(brrr_model *m, const uint32_t *toks, uint32_t n
         }
         uint32_t pos[BRRR_TILE_MAX];
         for (uint32_t t = 0; t < cnt; t++) pos[t] = pos0 + i0 + t;
-        TRY(rows_run(m, (int)cnt, toks + i0, pos, nullptr, false));
+        TRY(rows_run(m, (int)cnt, toks + i0, pos, nullptr, ROWS_PROMPT));
         if (last) {
             // leave the engine as the serial schedule would after the tile's last token
             cudaStream_t s = m->stream;
@@ -1016,12 +1020,13 @@ static int batch_check(brrr_model *m, int n, const uint32_t *toks, const uint32_
 }
 
 // The layers for n rows on the sequences' caches; with out_toks, the vocabulary projection and argmax of every row.
-static int batch_rows(brrr_model *m, int n, const uint32_t *toks, const uint32_t *pos, const uint32_t *seq, uint32_t *out_toks, float *out_logits) {
+static int batch_rows(brrr_model *m, int n, const uint32_t *toks, const uint32_t *pos, const uint32_t *seq, uint32_t *out_toks, float *out_logits,
+                      int kind = ROWS_BATCH) {
     TRY(batch_check(m, n, toks, pos, seq));
     CU(cudaSetDevice(m->device));
     const brrr_cfg &c = m->cfg;
     cudaStream_t s = m->stream;
-    TRY(rows_run(m, n, toks, pos, seq, true));
+    TRY(rows_run(m, n, toks, pos, seq, kind));
     if (out_toks || out_logits) {
         CUL(launch_rmsnorm_quant(m->tl_x, m->out_norm, c.rms_eps, c.n_embd, nullptr, m->tl_nq, m->tl_ns, false, s, n));
         CUL(launch_q8_rows(m->head, m->tl_nq, m->tl_ns, n, nullptr, m->bt_logits, c.n_vocab, Q8_EPI_PLAIN, false, s, m->st));
@@ -1055,7 +1060,7 @@ extern "C" int brrr_batch_prefill(brrr_model *m, uint32_t seq, const uint32_t *t
     for (uint32_t i0 = 0; i0 < n; i0 += BRRR_TILE_MAX) {
         const uint32_t cnt = n - i0 < BRRR_TILE_MAX ? n - i0 : BRRR_TILE_MAX;
         for (uint32_t t = 0; t < cnt; t++) { pos[t] = pos0 + i0 + t; sq[t] = seq; }
-        TRY(batch_rows(m, (int)cnt, toks + i0, pos, sq, nullptr, nullptr));
+        TRY(batch_rows(m, (int)cnt, toks + i0, pos, sq, nullptr, nullptr, cnt > 1 ? ROWS_BATCH_PROMPT : ROWS_BATCH));
     }
     return BRRR_OK;
 }
