@@ -30,7 +30,12 @@ constexpr int TL_ROWS = 128;           // rows per CTA = MMA M
 constexpr int TL_MAXTOK = 64;           // entries per expert and launch (one per token of the tile at most)
 constexpr int TL_A_BYTES = TL_ROWS * 32;       // one decoded A tile (128 rows x 32 k bytes)
 
-constexpr int TL_THREADS = 224;        // four worker warps, the producer warp, two issuer warps
+constexpr int TL_THREADS = 224;        // four worker warps, the producer warp, two issuer warps (q8_tile_kernel)
+// mx_tile_kernel: one or two issuing threads, ring depth and CTAs per SM.  Measured on the 2048-token prefill (tok/s): 2 issuers /
+// depth 5 / 3 CTAs 3956; 1 issuer 3973; depth 3 3969; 1 issuer + depth 3 + 4 CTAs per SM (80 registers, spills) 3648.
+constexpr int MT_ISSUERS = 2;
+constexpr int MT_CTAS = 3;
+constexpr int MT_THREADS = 160 + 32 * MT_ISSUERS;   // four worker warps, the producer warp, the issuer warp(s)
 constexpr int TL_DEPTH = 5;            // weight ring: block pairs in flight per CTA
 constexpr int TL_SLOT = 9 * MX_UNIT;   // one pair of a 128-row tile: up to 9 units of 16 rows
 constexpr int TL_CPL = (TL_SLOT / 16 + 31) / 32;   // 16-byte pieces per producer lane and pair
@@ -107,7 +112,7 @@ struct TileArgs {
 // accumulators have been read.  done[half], 2 arrivals: the issuers' tcgen05.commit of the pair; workers wait for it before they read
 // the accumulators and before they overwrite the half's operands two pairs later.
 template <int NT>
-__global__ void __launch_bounds__(TL_THREADS, 3) mx_tile_kernel(TileArgs a) {
+__global__ void __launch_bounds__(MT_THREADS, MT_CTAS) mx_tile_kernel(TileArgs a) {
     constexpr int N = 4 * NT;                                    // columns per block: NT tokens x 4 chain lanes
     constexpr uint32_t TMEM_COLS = 4 * N;                        // two halves x two blocks x N columns (64 or 128)
     constexpr uint32_t IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((TL_ROWS >> 4) << 24);
@@ -126,12 +131,12 @@ __global__ void __launch_bounds__(TL_THREADS, 3) mx_tile_kernel(TileArgs a) {
     const int n_ent = min((a.cnt ? a.cnt[e] : a.ntok) - chunk * NT, NT);
     if (n_ent <= 0) return;                      // nothing routed here (before anything is allocated)
     if (tid < NT) ent[tid] = tid < n_ent ? (a.list ? a.list[e * TL_MAXTOK + chunk * NT + tid] : chunk * NT + tid) : 0;
-    mx_fill_scale_table(tbl, tid, TL_THREADS);
-    for (int i = tid; i < 4 * N * 32 / 16; i += TL_THREADS) reinterpret_cast<uint4 *>(&b_tiles[0][0])[i] = make_uint4(0, 0, 0, 0);   // rows of absent tokens stay zero
+    mx_fill_scale_table(tbl, tid, MT_THREADS);
+    for (int i = tid; i < 4 * N * 32 / 16; i += MT_THREADS) reinterpret_cast<uint4 *>(&b_tiles[0][0])[i] = make_uint4(0, 0, 0, 0);   // rows of absent tokens stay zero
     if (tid == 0) {
         for (int i = 0; i < TL_DEPTH; i++) { mbar_init(&full[i], 32); mbar_init(&empty[i], 128); }
         mbar_init(&staged[0], 128); mbar_init(&staged[1], 128);
-        mbar_init(&done[0], 2); mbar_init(&done[1], 2);
+        mbar_init(&done[0], MT_ISSUERS); mbar_init(&done[1], MT_ISSUERS);
         mbar_fence_init();
     }
     if (warp == 0) {
@@ -180,23 +185,28 @@ __global__ void __launch_bounds__(TL_THREADS, 3) mx_tile_kernel(TileArgs a) {
             if (++slot == TL_DEPTH) { slot = 0; par ^= 1u; }
         }
         asm volatile("cp.async.wait_all;" ::: "memory");
-    } else if (tid == 160 || tid == 192) {
-        // ---------------- issuers: block k of every pair (two threads in two warps, so the products of a pair issue side by side)
-        const int k = tid == 160 ? 0 : 1;
-        uint64_t da[2][2], db[2];
+    } else if (tid == 160 || (MT_ISSUERS == 2 && tid == 192)) {
+        // ---------------- issuer(s): with two, block k of every pair each (two threads in two warps issue side by side); with one, both blocks
+        const int k0 = tid == 160 ? 0 : 1, k1 = MT_ISSUERS == 2 ? k0 + 1 : 2;
+        uint64_t da[2][4], db[2][2];
 #pragma unroll
         for (int h = 0; h < 2; h++) {
-            da[h][0] = tl_smem_desc(&a_tiles[4 * h + 2 * k][0], 2048);
-            da[h][1] = tl_smem_desc(&a_tiles[4 * h + 2 * k + 1][0], 2048);
-            db[h] = tl_smem_desc(&b_tiles[2 * h + k][0], N * 16);
+#pragma unroll
+            for (int i = 0; i < 4; i++) da[h][i] = tl_smem_desc(&a_tiles[4 * h + i][0], 2048);
+            db[h][0] = tl_smem_desc(&b_tiles[2 * h][0], N * 16);
+            db[h][1] = tl_smem_desc(&b_tiles[2 * h + 1][0], N * 16);
         }
         for (int p = 0; p < np; p++) {
             const int h = p & 1;
             waiter.wait_suspended(&staged[h], (uint32_t)(p >> 1) & 1u);
             tl_fence_after();
-            const uint32_t dcol = tmem_base + (uint32_t)((2 * h + k) * N);
-            if (h == 0) { tl_mma(dcol, da[0][0], db[0], 0u, IDESC); tl_mma(dcol, da[0][1], db[0], 1u, IDESC); }
-            else        { tl_mma(dcol, da[1][0], db[1], 0u, IDESC); tl_mma(dcol, da[1][1], db[1], 1u, IDESC); }
+#pragma unroll
+            for (int k = 0; k < 2; k++)
+                if (k >= k0 && k < k1) {
+                    const uint32_t dcol = tmem_base + (uint32_t)((2 * h + k) * N);
+                    if (h == 0) { tl_mma(dcol, da[0][2 * k], db[0][k], 0u, IDESC); tl_mma(dcol, da[0][2 * k + 1], db[0][k], 1u, IDESC); }
+                    else        { tl_mma(dcol, da[1][2 * k], db[1][k], 0u, IDESC); tl_mma(dcol, da[1][2 * k + 1], db[1][k], 1u, IDESC); }
+                }
             tl_commit(&done[h]);
         }
     } else if (tid < 128) {
@@ -545,8 +555,8 @@ cudaError_t tl_launch(TileArgs a, int tiles, int experts, int max_entries, cudaS
     if (ce != cudaSuccess) return ce;
     a.chunks = (max_entries + nt - 1) / nt;
     const dim3 grid(tiles, experts * a.chunks);
-    if (nt == 4) mx_tile_kernel<4><<<grid, TL_THREADS, smem, st>>>(a);
-    else mx_tile_kernel<8><<<grid, TL_THREADS, smem, st>>>(a);
+    if (nt == 4) mx_tile_kernel<4><<<grid, MT_THREADS, smem, st>>>(a);
+    else mx_tile_kernel<8><<<grid, MT_THREADS, smem, st>>>(a);
     return cudaGetLastError();
 }
 
