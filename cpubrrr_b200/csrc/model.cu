@@ -146,7 +146,7 @@ struct brrr_model {
     EpCtx epc{};
     void *ep_buf = nullptr;
     std::vector<void *> ep_peers;
-    // scratch of the token-tile MoE step (allocated at first use): 16 tokens x top-k entries
+    // scratch of the token-tile MoE step (allocated at first use): BRRR_TILE_MAX tokens x top-k entries
     int8_t *tl_xq = nullptr, *tl_hq = nullptr;
     float *tl_xs = nullptr, *tl_hs = nullptr, *tl_logits = nullptr, *tl_wts = nullptr, *tl_gu = nullptr, *tl_part = nullptr;
     int32_t *tl_top = nullptr;
@@ -168,7 +168,7 @@ struct brrr_model {
     uint32_t *bt_tok = nullptr;                  // [BRRR_TILE_MAX] argmax per row
     bool no_attn_rows = false;                   // BRRR_NO_ATTN_ROWS=1: prompt tiles use the per-(head, row) attention kernel (same bits)
     int tile_rows = BRRR_TILE_MAX;               // tokens per prompt tile (BRRR_TILE_ROWS=n, 2..64): any size gives the same bits
-    bool tile_prefill = true;                    // run_tile on 16-token tiles (brrr_model_set_tile_prefill / BRRR_TILE_PREFILL=0 switch to token-serial; same bits)
+    bool tile_prefill = true;                    // run_tile on token tiles (brrr_model_set_tile_prefill / BRRR_TILE_PREFILL=0 switch to token-serial; same bits)
     unsigned int *tl_counter = nullptr;
     std::vector<void *> allocs;
 
@@ -859,7 +859,7 @@ extern "C" int brrr_forward(brrr_model *m, uint32_t tok, uint32_t pos, int want,
 
 static int moe_tile_enqueue(brrr_model *m, int il, const float *d_xn, float *d_x, int ntok);
 
-// Up to 16 token rows walk the layers together (forward_tile_worker, src/bin/engine_gpt2.rs:1011-1250:
+// Up to BRRR_TILE_MAX token rows walk the layers together (forward_tile_worker, src/bin/engine_gpt2.rs:1011-1250:
 // every stage gains a token dimension, weight row outer, tokens inner).  A row is (token, position,
 // sequence): consecutive positions of one sequence for a prompt tile, one position each of several
 // sequences for batched decode.  Per layer: norm + Q8 of every row, q|k|v for all rows from one pass over
