@@ -3,7 +3,7 @@ preparation scripts.
 
 A data directory is what scripts/setup_model.sh of the reference leaves beside a GGUF blob:
 config.txt, manifest.txt, tokens.bin (plus index.json).  When a checkout of the reference is
-present (BRRR_REFERENCE_DIR, default /root/reference) `make_data_dir` runs, unmodified,
+present (environment variable BRRR_REFERENCE_DIR, else the default location below) `make_data_dir` runs, unmodified,
   * scripts/gguf_index.py <blob>            -> index.json
   * scripts/dump_tokenizer.py <blob> <dir>  -> tokens.bin
   * the inline generator of scripts/setup_model.sh (the `python3 -c "..."` command after
