@@ -73,6 +73,22 @@ __device__ __forceinline__ void tl_ld16(uint32_t taddr, int (&r)[16]) {
                  : "r"(taddr)
                  : "memory");
 }
+// packed pairs of floats for fma.rn.f32x2
+__device__ __forceinline__ unsigned long long tl_pack2(float lo, float hi) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(__float_as_uint(lo)), "r"(__float_as_uint(hi)));
+    return r;
+}
+__device__ __forceinline__ void tl_unpack2(unsigned long long v, float &lo, float &hi) {
+    uint32_t a, b;
+    asm("mov.b64 {%0, %1}, %2;" : "=r"(a), "=r"(b) : "l"(v));
+    lo = __uint_as_float(a); hi = __uint_as_float(b);
+}
+__device__ __forceinline__ unsigned long long tl_fma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+    unsigned long long r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
 __device__ __forceinline__ void tl_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // One launch serves blockIdx.y = (expert or the single matrix, chunk of entries).  Each expert has a list of up to 64
@@ -245,14 +261,18 @@ __global__ void __launch_bounds__(MT_THREADS, MT_CTAS) mx_tile_kernel(TileArgs a
             const uint32_t e2 = *reinterpret_cast<const unsigned short *>(u + e_off);
             mbar_arrive(&empty[q_slot]);
             const uint32_t wl[4][2] = {{w0.x, w0.y}, {w0.z, w0.w}, {w1.x, w1.y}, {w1.z, w1.w}};
+            // lanes (0, 1) and (2, 3) of a row are neighbours in the tile: one 16-byte store per (K half, block, table); a warp's
+            // stores then cover 512 contiguous bytes (no bank conflict)
 #pragma unroll
-            for (int j = 0; j < 4; j++) {
+            for (int jh = 0; jh < 2; jh++) {
 #pragma unroll
                 for (int k = 0; k < 2; k++) {
-                    const uint32_t w = wl[j][k], wx = w ^ 0x88888888u;
-                    const uint32_t off = (uint32_t)((j >> 1) * 2048) + a_off + (j & 1) * 8;
-                    *reinterpret_cast<uint2 *>(&a_tiles[4 * h + 2 * k][off]) = make_uint2(brrr_prmt(P_LO, P_HI, w), brrr_prmt(P_LO, P_HI, w >> 16));
-                    *reinterpret_cast<uint2 *>(&a_tiles[4 * h + 2 * k + 1][off]) = make_uint2(brrr_prmt(N_LO, N_HI, wx), brrr_prmt(N_LO, N_HI, wx >> 16));
+                    const uint32_t wa = wl[2 * jh][k], wb = wl[2 * jh + 1][k], wax = wa ^ 0x88888888u, wbx = wb ^ 0x88888888u;
+                    const uint32_t off = (uint32_t)(jh * 2048) + a_off;
+                    *reinterpret_cast<uint4 *>(&a_tiles[4 * h + 2 * k][off]) =
+                        make_uint4(brrr_prmt(P_LO, P_HI, wa), brrr_prmt(P_LO, P_HI, wa >> 16), brrr_prmt(P_LO, P_HI, wb), brrr_prmt(P_LO, P_HI, wb >> 16));
+                    *reinterpret_cast<uint4 *>(&a_tiles[4 * h + 2 * k + 1][off]) =
+                        make_uint4(brrr_prmt(N_LO, N_HI, wax), brrr_prmt(N_LO, N_HI, wax >> 16), brrr_prmt(N_LO, N_HI, wbx), brrr_prmt(N_LO, N_HI, wbx >> 16));
                 }
             }
             if (b_live) {
@@ -268,9 +288,11 @@ __global__ void __launch_bounds__(MT_THREADS, MT_CTAS) mx_tile_kernel(TileArgs a
             mbar_arrive(&staged[h]);
             return e2;
         };
-        float acc[N];
+        // the chains of lanes (0, 1) and (2, 3) of an entry share an instruction (fma.rn.f32x2: two independent
+        // round-to-nearest fused multiply-adds)
+        unsigned long long acc2[N / 2];
 #pragma unroll
-        for (int i = 0; i < N; i++) acc[i] = 0.0f;
+        for (int i = 0; i < N / 2; i++) acc2[i] = 0ull;
         const uint32_t lane_addr = tmem_base + ((uint32_t)(warp * 32) << 16);
         // float chains of pair p: thread = row (tensor-memory lane), N columns per block
         auto chains = [&](int p, uint32_t e2c) {
@@ -287,8 +309,10 @@ __global__ void __launch_bounds__(MT_THREADS, MT_CTAS) mx_tile_kernel(TileArgs a
 #pragma unroll
                 for (int t = 0; t < NT; t++) {
                     const float sxs = __fmul_rn(esc, xs_sm[t * nb + 2 * p + k]);
+                    const unsigned long long s2 = tl_pack2(sxs, sxs);
 #pragma unroll
-                    for (int l = 0; l < 4; l++) acc[4 * t + l] = __fmaf_rn((float)d[t / 4][4 * (t % 4) + l], sxs, acc[4 * t + l]);
+                    for (int l = 0; l < 2; l++)
+                        acc2[2 * t + l] = tl_fma2(tl_pack2((float)d[t / 4][4 * (t % 4) + 2 * l], (float)d[t / 4][4 * (t % 4) + 2 * l + 1]), s2, acc2[2 * t + l]);
                 }
             }
         };
@@ -304,7 +328,10 @@ __global__ void __launch_bounds__(MT_THREADS, MT_CTAS) mx_tile_kernel(TileArgs a
 #pragma unroll
             for (int t = 0; t < NT; t++)
                 if (t < n_ent) {
-                    float v = __fadd_rn(__fadd_rn(acc[4 * t], acc[4 * t + 1]), __fadd_rn(acc[4 * t + 2], acc[4 * t + 3]));
+                    float a0, a1, a2, a3;
+                    tl_unpack2(acc2[2 * t], a0, a1);
+                    tl_unpack2(acc2[2 * t + 1], a2, a3);
+                    float v = __fadd_rn(__fadd_rn(a0, a1), __fadd_rn(a2, a3));
                     if (a.bias) v = __fadd_rn(v, bias);
                     a.y[(size_t)ent[t] * a.ldy + a.col0 + row_local] = v;
                 }
