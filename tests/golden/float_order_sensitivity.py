@@ -1,7 +1,7 @@
 """TEST INFRASTRUCTURE - how much does the fixed float order matter for the parity bar?
 
 Builds the CPU oracle twice from the sources under oracle/: with its own flags (every sum in the reference's
-order, fused multiply-adds only where written) and with `-ffast-math` (the compiler may re-associate sums into
+order, fused multiply-adds only where written) and with `-fassociative-math -ffp-contract=fast` (the compiler may re-associate sums into
 vector lanes and contract multiply-adds: a stand-in for kernels that keep the integer block dots exact but do
 not keep the float order).  Both run the gpt-oss-20b workload of bench.py (seeded synthetic weights, 73-token
 prompt, 128 greedy steps from position 73) on the CPU.  The relaxed build is teacher-forced with the strict
