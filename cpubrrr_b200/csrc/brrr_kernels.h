@@ -145,11 +145,11 @@ cudaError_t launch_down_t(MxtDev down, const float *down_b, const int32_t *top, 
                           bool pdl, cudaStream_t st, const EpCtx *ep = nullptr, int layer = 0);
 
 // ---- token-tile matmul on tcgen05 tensor cores (kernels_tile.cu): y[t][r] = row (row0 + r) . activation t,
-// t < ntok <= 64, every value bit-identical to launch_mx_gemv on token t alone
+// t < ntok <= BRRR_TILE_MAX, every value bit-identical to launch_mx_gemv on token t alone
 cudaError_t launch_mx_tile(MxDev w, int row0, int nrows, const int8_t *xq, const float *xs, int ntok, float *y, int ldy, DevState *state,
                            cudaStream_t st);
 
-// every expert of one matrix kind against the (token, slot) entries routed to it (cnt[e], list[e][64], at most max_entries per expert);
+// every expert of one matrix kind against the (token, slot) entries routed to it (cnt[e], list[e][BRRR_TILE_MAX], at most max_entries per expert);
 // entry i reads activation row entry / src_div and writes y[entry * ldy + col0 + row] (+ bias[e][row])
 cudaError_t launch_mx_tile_experts(MxDev w, int ne, int rows_per_expert, const int *cnt, const int *list, int max_entries, int src_div, const int8_t *xq,
                                    const float *xs, const float *bias, float *y, int ldy, int col0, DevState *state, cudaStream_t st);

@@ -1,4 +1,4 @@
-// Token rows: the dense half of a layer for up to 64 tokens at once (prompt tiles and batched decode
+// Token rows: the dense half of a layer for up to 256 tokens at once (prompt tiles and batched decode
 // over independent sequences; forward_tile_worker, src/bin/engine_gpt2.rs:1011-1250, keeps the
 // per-token arithmetic and shares each weight pass among the tokens of a tile).  Every value is
 // computed by the same operation sequence as in the one-token kernels, so results are bit-identical
@@ -186,7 +186,7 @@ void launch_rows_argmax(const float *logits, int n_vocab, int rows, uint32_t *ou
     rows_argmax_kernel<<<rows, 1024, 0, st>>>(logits, n_vocab, out);
 }
 
-// y[t][r] (+)= row r of m . activation t (+ bias) for t < ntok <= 64.  epi: Q8_EPI_PLAIN / BIAS / RESID_BIAS.
+// y[t][r] (+)= row r of m . activation t (+ bias) for t < ntok <= BRRR_TILE_MAX.  epi: Q8_EPI_PLAIN / BIAS / RESID_BIAS.
 // engine: 0 = integer units (the default: measured faster at every tile size so far), 1 = tensor cores (launch_q8_tile,
 // kernels_tile.cu), -1 = the environment variable BRRR_Q8_TILE=1 selects the tensor cores for tiles of at least 32 rows of
 // the layer projections.  Same bits either way.

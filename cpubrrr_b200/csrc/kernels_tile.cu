@@ -1,6 +1,6 @@
 // Token-tile MXFP4 matmul on the 5th-generation tensor cores (tcgen05.mma kind::i8, accumulators in
 // tensor memory): the batched counterpart of the per-token expert matvec, for prefill tiles and
-// batched decode.  One pass over the weights serves up to 64 tokens, as the reference's tile path
+// batched decode.  One pass over the weights serves up to 256 tokens, as the reference's tile path
 // does on the CPU for 16 (src/bin/engine_gpt2.rs:1005-1010, TILE = 16), and every output equals the
 // per-token result bit for bit.
 //
@@ -27,7 +27,7 @@ namespace {
 
 constexpr int TL_ROWS = 128;           // rows per CTA = MMA M
 
-constexpr int TL_MAXTOK = 64;           // entries per expert and launch (one per token of the tile at most)
+constexpr int TL_MAXTOK = BRRR_TILE_MAX; // entries per expert and launch (one per token of the tile at most)
 constexpr int TL_A_BYTES = TL_ROWS * 32;       // one decoded A tile (128 rows x 32 k bytes)
 
 constexpr int TL_THREADS = 224;        // four worker warps, the producer warp, two issuer warps (q8_tile_kernel)
@@ -91,7 +91,7 @@ __device__ __forceinline__ unsigned long long tl_fma2(unsigned long long a, unsi
 }
 __device__ __forceinline__ void tl_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// One launch serves blockIdx.y = (expert or the single matrix, chunk of entries).  Each expert has a list of up to 64
+// One launch serves blockIdx.y = (expert or the single matrix, chunk of entries).  Each expert has a list of up to 256
 // entries; entry i multiplies the activation row entry / src_div and writes output row entry.
 struct TileArgs {
     MxDev w;
@@ -545,16 +545,17 @@ __global__ void __maxnreg__(96) q8_tile_kernel(Q8TileArgs a) {      // 96 regist
 // Per expert, the (token, slot) pairs routed to it, in ascending order: entry = token * topk + slot.  One CTA per
 // expert, thread = token (a token routes to an expert at most once, so the order is the token order).
 __global__ void __launch_bounds__(TL_MAXTOK) tile_route_kernel(const int32_t *__restrict__ top, int ntok, int topk, int *__restrict__ cnt, int *__restrict__ list) {
-    __shared__ int first_warp;
+    __shared__ int warp_cnt[TL_MAXTOK / 32];
     const int e = blockIdx.x, t = threadIdx.x;
     int slot = -1;
     if (t < ntok)
         for (int s = 0; s < topk; s++)
             if (top[t * 8 + s] == e) { slot = s; break; }
     const unsigned m = __ballot_sync(0xffffffffu, slot >= 0);
-    if (t == 31) first_warp = __popc(m);
+    if ((t & 31) == 0) warp_cnt[t >> 5] = __popc(m);
     __syncthreads();
-    const int before = __popc(m & ((1u << (t & 31)) - 1u)) + (t >= 32 ? first_warp : 0);
+    int before = __popc(m & ((1u << (t & 31)) - 1u));
+    for (int w = 0; w < (t >> 5); w++) before += warp_cnt[w];
     if (slot >= 0) list[e * TL_MAXTOK + before] = t * topk + slot;
     if (t == TL_MAXTOK - 1) cnt[e] = before + (slot >= 0 ? 1 : 0);
 }
@@ -600,7 +601,7 @@ cudaError_t q8_tile_launch(const Q8TileArgs &a, bool pdl, cudaStream_t st) {
 
 }  // namespace
 
-// y[t][r] (+)= row r of m . activation t (+ bias) on the tensor cores, t < ntok <= 64: bit-identical to the
+// y[t][r] (+)= row r of m . activation t (+ bias) on the tensor cores, t < ntok <= BRRR_TILE_MAX: bit-identical to the
 // integer-unit kernels (kernels_q8.cu, kernels_rows.cu).  Four token rows per CTA up to 4 rows, eight beyond.
 cudaError_t launch_q8_tile(Q8Dev m, const int8_t *xq, const float *xs, int ntok, const float *bias, float *y, int ldy, int epi, DevState *state,
                            bool pdl, cudaStream_t st) {

@@ -167,7 +167,7 @@ struct brrr_model {
     float *bt_logits = nullptr;                  // [BRRR_TILE_MAX][n_vocab]
     uint32_t *bt_tok = nullptr;                  // [BRRR_TILE_MAX] argmax per row
     bool no_attn_rows = false;                   // BRRR_NO_ATTN_ROWS=1: prompt tiles use the per-(head, row) attention kernel (same bits)
-    int tile_rows = BRRR_TILE_MAX;               // tokens per prompt tile (BRRR_TILE_ROWS=n, 2..64): any size gives the same bits
+    int tile_rows = BRRR_TILE_MAX;               // tokens per prompt tile (BRRR_TILE_ROWS=n, 2..BRRR_TILE_MAX): any size gives the same bits
     bool tile_prefill = true;                    // run_tile on token tiles (brrr_model_set_tile_prefill / BRRR_TILE_PREFILL=0 switch to token-serial; same bits)
     unsigned int *tl_counter = nullptr;
     std::vector<void *> allocs;
@@ -1030,7 +1030,7 @@ static int batch_rows(brrr_model *m, int n, const uint32_t *toks, const uint32_t
     if (out_toks || out_logits) {
         CUL(launch_rmsnorm_quant(m->tl_x, m->out_norm, c.rms_eps, c.n_embd, nullptr, m->tl_nq, m->tl_ns, false, s, n));
         // from 8 rows on the vocabulary projection runs on the tensor cores (measured: 3726 against 3564 tok/s at 64 rows, 1790 against
-        // 1754 at 16; BRRR_HEAD_TILE_MIN=n moves the threshold, 65 = never); same bits either way
+        // 1754 at 16; BRRR_HEAD_TILE_MIN=n moves the threshold, above BRRR_TILE_MAX = never); same bits either way
         static const int head_tile_min = [] { const char *e = getenv("BRRR_HEAD_TILE_MIN"); const int v = e ? atoi(e) : 0; return v >= 1 ? v : 8; }();
         CUL(launch_q8_rows(m->head, m->tl_nq, m->tl_ns, n, nullptr, m->bt_logits, c.n_vocab, Q8_EPI_PLAIN, false, s, m->st, n >= head_tile_min ? 1 : 0));
         launch_rows_argmax(m->bt_logits, c.n_vocab, n, m->bt_tok, s);
