@@ -22,6 +22,28 @@ namespace {
 constexpr int QR_THREADS = 128;
 constexpr int QR_TPC = 8;               // token rows per CTA (blockIdx.y walks the groups)
 
+// packed pairs of floats (mul / fma .rn.f32x2)
+__device__ __forceinline__ unsigned long long qr_pack2(float lo, float hi) {
+    unsigned long long r;
+    asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "r"(__float_as_uint(lo)), "r"(__float_as_uint(hi)));
+    return r;
+}
+__device__ __forceinline__ void qr_unpack2(unsigned long long v, float &lo, float &hi) {
+    uint32_t a, b;
+    asm("mov.b64 {%0, %1}, %2;" : "=r"(a), "=r"(b) : "l"(v));
+    lo = __uint_as_float(a); hi = __uint_as_float(b);
+}
+__device__ __forceinline__ unsigned long long qr_mul2(unsigned long long a, unsigned long long b) {
+    unsigned long long r;
+    asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+    return r;
+}
+__device__ __forceinline__ unsigned long long qr_fma2(unsigned long long a, unsigned long long b, unsigned long long c) {
+    unsigned long long r;
+    asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+    return r;
+}
+
 struct Q8RowsArgs {
     Q8Dev m;
     const int8_t *xq;       // [rows][cols]
@@ -66,41 +88,36 @@ __global__ void __launch_bounds__(QR_THREADS) q8_rows_kernel(Q8RowsArgs a) {
         const int *xw = reinterpret_cast<const int *>(a.xq + (size_t)(t_first + t) * a.m.cols + (idx >> 2) * 32);
         xp[i] = make_int2(xw[idx & 3], xw[4 + (idx & 3)]);
     }
-    for (int i = tid; i < ntok * nb; i += QR_THREADS) xsc[i] = a.xs[(size_t)t_first * nb + i];
+    // block scales transposed to [block][token row]: two neighbouring rows' scales are one 8-byte read
+    for (int i = tid; i < ntok * nb; i += QR_THREADS) xsc[(i % nb) * QR_TPC + i / nb] = a.xs[(size_t)t_first * nb + i];
     __syncthreads();
-    // four token rows per walk over the weights: their chains are independent, so their instructions interleave
+    // four token rows per walk over the weights: their chains are independent, so their instructions interleave, and
+    // rows (0, 1) and (2, 3) share the float instructions (mul / fma .f32x2: two independent round-to-nearest operations)
     for (int t0 = 0; t0 < ntok; t0 += 4) {
         const int2 *xpt[4];
-        const float *xst[4];
-        float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+        unsigned long long acc2[2] = {0ull, 0ull};
 #pragma unroll
-        for (int g = 0; g < 4; g++) {
-            const int t = min(t0 + g, ntok - 1);                 // rows past the end repeat the last one (never stored)
-            xpt[g] = xp + (size_t)t * nidx + c8;
-            xst[g] = xsc + (size_t)t * nb + p;
-        }
+        for (int g = 0; g < 4; g++) xpt[g] = xp + (size_t)min(t0 + g, ntok - 1) * nidx + c8;      // rows past the end repeat the last one (never stored)
+        const float *xst = xsc + (size_t)p * QR_TPC + t0;          // scales of rows t0 .. t0 + 3 for block 2 i + p at + 2 i * QR_TPC (rows past the end: stale, never stored)
+        auto step = [&](int2 wv, float sv, int i) {
+            const unsigned long long s2 = qr_pack2(sv, sv);
+#pragma unroll
+            for (int h = 0; h < 2; h++) {
+                const int2 xa = xpt[2 * h][i * 8], xb = xpt[2 * h + 1][i * 8];
+                const int da = __dp4a(wv.y, xa.y, __dp4a(wv.x, xa.x, 0)), db = __dp4a(wv.y, xb.y, __dp4a(wv.x, xb.x, 0));
+                const unsigned long long sx2 = qr_mul2(s2, *reinterpret_cast<const unsigned long long *>(xst + (size_t)2 * i * QR_TPC + 2 * h));
+                acc2[h] = qr_fma2(qr_pack2((float)da, (float)db), sx2, acc2[h]);
+            }
+        };
         if (NP > 0) {
 #pragma unroll
-            for (int i = 0; i < (NP > 0 ? NP : 1); i++) {
-#pragma unroll
-                for (int g = 0; g < 4; g++) {
-                    const int2 xv = xpt[g][i * 8];
-                    const int d = __dp4a(w[i].y, xv.y, __dp4a(w[i].x, xv.x, 0));
-                    acc[g] = __fmaf_rn((float)d, __fmul_rn(s[i], xst[g][i * 2]), acc[g]);
-                }
-            }
+            for (int i = 0; i < (NP > 0 ? NP : 1); i++) step(w[i], s[i], i);
         } else {
-            for (int i = 0; i < np; i++) {
-                const int2 wv = __ldg(wp + (size_t)i * (Q8_UNIT / 8));
-                const float sv = __ldg(sp + (size_t)i * (Q8_UNIT / 4));
-#pragma unroll
-                for (int g = 0; g < 4; g++) {
-                    const int2 xv = xpt[g][i * 8];
-                    const int d = __dp4a(wv.y, xv.y, __dp4a(wv.x, xv.x, 0));
-                    acc[g] = __fmaf_rn((float)d, __fmul_rn(sv, xst[g][i * 2]), acc[g]);
-                }
-            }
+            for (int i = 0; i < np; i++) step(__ldg(wp + (size_t)i * (Q8_UNIT / 8)), __ldg(sp + (size_t)i * (Q8_UNIT / 4)), i);
         }
+        float acc[4];
+        qr_unpack2(acc2[0], acc[0], acc[1]);
+        qr_unpack2(acc2[1], acc[2], acc[3]);
 #pragma unroll
         for (int g = 0; g < 4; g++) {
             float r = __fadd_rn(acc[g], __shfl_xor_sync(0xffffffffu, acc[g], 4));      // acc_even + acc_odd per lane, then (l0+l1)+(l2+l3)
