@@ -12,10 +12,11 @@
 // issued twice, once with the positive and once with the negative decode table (their sum is the
 // signed value), accumulating in the same 128 x 4 NT int32 tile of tensor memory.  The four worker
 // warps read their 32 lanes of tensor memory (tcgen05.ld) and run the float chains, one thread per
-// row with 4 NT accumulators.  NT = 4 entries per CTA for tiles of up to 16 tokens, 8 beyond.
+// row with 4 NT accumulators.  NT = 4 entries per CTA for tiles of up to 16 tokens, 8 up to 64, 16 beyond.
 //
 // Operands are written to shared memory by the threads themselves in the canonical K-major
 // no-swizzle layout (8-row x 16-byte core matrices).
+#include <cstdlib>
 #include "brrr_kernels.h"
 #include "brrr_block.cuh"
 #include "brrr_tma.cuh"
@@ -35,6 +36,8 @@ constexpr int TL_THREADS = 224;        // four worker warps, the producer warp, 
 // depth 5 / 3 CTAs 3956; 1 issuer 3973; depth 3 3969; 1 issuer + depth 3 + 4 CTAs per SM (80 registers, spills) 3648.
 constexpr int MT_ISSUERS = 2;
 constexpr int MT_CTAS = 3;
+constexpr int MT_NT16_FROM = 65;         // tile size from which a CTA takes 16 entries (128 registers, 2 CTAs per SM: one decode of the weights serves
+                                         // twice the entries; 256-row prefill 5864 against 5469 tok/s); BRRR_TILE_NT16_FROM=n moves it
 constexpr int MT_THREADS = 160 + 32 * MT_ISSUERS;   // four worker warps, the producer warp, the issuer warp(s)
 constexpr int TL_DEPTH = 5;            // weight ring: block pairs in flight per CTA
 constexpr int TL_SLOT = 9 * MX_UNIT;   // one pair of a 128-row tile: up to 9 units of 16 rows
@@ -110,7 +113,7 @@ struct TileArgs {
     DevState *state;
 };
 
-// One CTA = 128 rows of one expert against one chunk of up to NT of its entries (NT = 4 or 8, MMA N = 4 NT; an
+// One CTA = 128 rows of one expert against one chunk of up to NT of its entries (NT = 4, 8 or 16, MMA N = 4 NT; an
 // expert with more entries is served by several CTAs, which re-read its rows from L2).
 //
 // Roles.  A tcgen05.mma or a bulk copy costs its issuing thread on the order of a hundred cycles, so the
@@ -128,7 +131,7 @@ struct TileArgs {
 // accumulators have been read.  done[half], 2 arrivals: the issuers' tcgen05.commit of the pair; workers wait for it before they read
 // the accumulators and before they overwrite the half's operands two pairs later.
 template <int NT>
-__global__ void __launch_bounds__(MT_THREADS, MT_CTAS) mx_tile_kernel(TileArgs a) {
+__global__ void __launch_bounds__(MT_THREADS, NT == 16 ? 2 : MT_CTAS) mx_tile_kernel(TileArgs a) {
     constexpr int N = 4 * NT;                                    // columns per block: NT tokens x 4 chain lanes
     constexpr uint32_t TMEM_COLS = 4 * N;                        // two halves x two blocks x N columns (64 or 128)
     constexpr uint32_t IDESC = (2u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(N >> 3) << 17) | ((TL_ROWS >> 4) << 24);
@@ -301,18 +304,23 @@ __global__ void __launch_bounds__(MT_THREADS, MT_CTAS) mx_tile_kernel(TileArgs a
             tl_fence_after();
 #pragma unroll
             for (int k = 0; k < 2; k++) {
-                int d[N / 16][16];
-#pragma unroll
-                for (int c = 0; c < N / 16; c++) tl_ld16(lane_addr + (uint32_t)((2 * h + k) * N + 16 * c), d[c]);
-                tl_wait_ld();
                 const float esc = tbl[k ? e2c >> 8 : e2c & 0xFFu];
+                constexpr int G = N > 32 ? 32 : N;                // columns per tensor-memory read round (registers)
 #pragma unroll
-                for (int t = 0; t < NT; t++) {
-                    const float sxs = __fmul_rn(esc, xs_sm[t * nb + 2 * p + k]);
-                    const unsigned long long s2 = tl_pack2(sxs, sxs);
+                for (int c0 = 0; c0 < N; c0 += G) {
+                    int d[G / 16][16];
 #pragma unroll
-                    for (int l = 0; l < 2; l++)
-                        acc2[2 * t + l] = tl_fma2(tl_pack2((float)d[t / 4][4 * (t % 4) + 2 * l], (float)d[t / 4][4 * (t % 4) + 2 * l + 1]), s2, acc2[2 * t + l]);
+                    for (int c = 0; c < G / 16; c++) tl_ld16(lane_addr + (uint32_t)((2 * h + k) * N + c0 + 16 * c), d[c]);
+                    tl_wait_ld();
+#pragma unroll
+                    for (int tt = 0; tt < G / 4; tt++) {
+                        const int t = c0 / 4 + tt;
+                        const float sxs = __fmul_rn(esc, xs_sm[t * nb + 2 * p + k]);
+                        const unsigned long long s2 = tl_pack2(sxs, sxs);
+#pragma unroll
+                        for (int l = 0; l < 2; l++)
+                            acc2[2 * t + l] = tl_fma2(tl_pack2((float)d[tt / 4][4 * (tt % 4) + 2 * l], (float)d[tt / 4][4 * (tt % 4) + 2 * l + 1]), s2, acc2[2 * t + l]);
+                    }
                 }
             }
         };
@@ -572,19 +580,22 @@ __global__ void tile_combine_kernel(const float *__restrict__ part, const float 
 
 size_t tl_smem(int nt, int nb) { return 8 * TL_A_BYTES + 4 * (size_t)(4 * nt) * 32 + (size_t)TL_DEPTH * TL_SLOT + (size_t)nt * nb * 4; }
 
-// Block pairs need an even block count.  Entries per CTA: 4 while no expert can have more than 16 entries, else 8.
+// Block pairs need an even block count.  Entries per CTA: 4 while no expert can have more than 16 entries, 8 up to 64, else 16.
 cudaError_t tl_launch(TileArgs a, int tiles, int experts, int max_entries, cudaStream_t st) {
     if ((a.w.blocks & 1) || a.w.blocks < 2 || max_entries < 1 || max_entries > TL_MAXTOK) return cudaErrorInvalidValue;
-    const int nt = max_entries <= 16 ? 4 : 8;
+    static const int wide_from = [] { const char *e = getenv("BRRR_TILE_NT16_FROM"); const int v = e ? atoi(e) : 0; return v >= 1 ? v : MT_NT16_FROM; }();
+    const int nt = max_entries <= 16 ? 4 : max_entries < wide_from ? 8 : 16;
     const size_t smem = tl_smem(nt, a.w.blocks);
     if (smem > 200 * 1024) return cudaErrorInvalidValue;
-    static unsigned long long configured4 = 0, configured8 = 0;      // one bit per device
-    cudaError_t ce = nt == 4 ? smem_optin(mx_tile_kernel<4>, 200 * 1024, configured4) : smem_optin(mx_tile_kernel<8>, 200 * 1024, configured8);
+    static unsigned long long configured4 = 0, configured8 = 0, configured16 = 0;      // one bit per device
+    cudaError_t ce = nt == 4 ? smem_optin(mx_tile_kernel<4>, 200 * 1024, configured4)
+                   : nt == 8 ? smem_optin(mx_tile_kernel<8>, 200 * 1024, configured8) : smem_optin(mx_tile_kernel<16>, 200 * 1024, configured16);
     if (ce != cudaSuccess) return ce;
     a.chunks = (max_entries + nt - 1) / nt;
     const dim3 grid(tiles, experts * a.chunks);
     if (nt == 4) mx_tile_kernel<4><<<grid, MT_THREADS, smem, st>>>(a);
-    else mx_tile_kernel<8><<<grid, MT_THREADS, smem, st>>>(a);
+    else if (nt == 8) mx_tile_kernel<8><<<grid, MT_THREADS, smem, st>>>(a);
+    else mx_tile_kernel<16><<<grid, MT_THREADS, smem, st>>>(a);
     return cudaGetLastError();
 }
 
