@@ -361,7 +361,7 @@ def run_batched(args):
 
 
 def run_prefill(args):
-    """--workload prefill: one 2048-token prompt through Engine.run_tile (tiles of 256 tokens: q/k/v and o-proj
+    """--workload prefill: one 2048-token prompt through Engine.run_tile (tiles of 512 tokens: q/k/v and o-proj
     per 16 rows, attention for all rows in one launch, the MoE block per tile on the tcgen05 tile kernels)
     against the token-serial schedule on a 256-token sample of the same prompt (its first 256 positions, where
     attention is cheapest: the comparison favours the serial schedule).  One step = one prompt token.  The tile
@@ -376,7 +376,7 @@ def run_prefill(args):
     prompt = [int(t) for t in S.synth_prompt(SEED, n, 199999 if args.vocab > 199999 else args.vocab - 1)]
     if args.profile_range:
         # for a profiler started with --profile-from-start off: two tiles untimed, then one tile inside the range
-        tr = int(os.environ.get("BRRR_TILE_ROWS", "256"))
+        tr = int(os.environ.get("BRRR_TILE_ROWS", "512"))
         eng.run_tile(prompt[:2 * tr], 0, False)
         torch.cuda.synchronize()
         torch.cuda.profiler.start()
@@ -388,7 +388,7 @@ def run_prefill(args):
         return
     sample = 256
     # serial sample (also the checker)
-    tile_rows = int(os.environ.get("BRRR_TILE_ROWS", "256"))
+    tile_rows = int(os.environ.get("BRRR_TILE_ROWS", "512"))
     eng.set_tile_prefill(True)
     eng.run_tile(prompt[:2 * tile_rows], 0, False)            # warm-up of both paths (graphs of the tile sizes in use)
     eng.run_tile(prompt[:sample % tile_rows or tile_rows], 0, False)

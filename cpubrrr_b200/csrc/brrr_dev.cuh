@@ -10,7 +10,7 @@
 
 #define BRRR_MAXSEQ 4096
 #ifndef BRRR_TILE_MAX
-#define BRRR_TILE_MAX 256     // token rows per pass over the layers (same value as in the public header)
+#define BRRR_TILE_MAX 512     // token rows per pass over the layers (same value as in the public header)
 #endif
 
 // ---------------------------------------------------------------- scalar helpers

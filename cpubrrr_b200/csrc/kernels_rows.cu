@@ -1,4 +1,4 @@
-// Token rows: the dense half of a layer for up to 256 tokens at once (prompt tiles and batched decode
+// Token rows: the dense half of a layer for up to 512 tokens at once (prompt tiles and batched decode
 // over independent sequences; forward_tile_worker, src/bin/engine_gpt2.rs:1011-1250, keeps the
 // per-token arithmetic and shares each weight pass among the tokens of a tile).  Every value is
 // computed by the same operation sequence as in the one-token kernels, so results are bit-identical

@@ -1,6 +1,6 @@
 // Token-tile MXFP4 matmul on the 5th-generation tensor cores (tcgen05.mma kind::i8, accumulators in
 // tensor memory): the batched counterpart of the per-token expert matvec, for prefill tiles and
-// batched decode.  One pass over the weights serves up to 256 tokens, as the reference's tile path
+// batched decode.  One pass over the weights serves up to 512 tokens, as the reference's tile path
 // does on the CPU for 16 (src/bin/engine_gpt2.rs:1005-1010, TILE = 16), and every output equals the
 // per-token result bit for bit.
 //
@@ -94,7 +94,7 @@ __device__ __forceinline__ unsigned long long tl_fma2(unsigned long long a, unsi
 }
 __device__ __forceinline__ void tl_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// One launch serves blockIdx.y = (expert or the single matrix, chunk of entries).  Each expert has a list of up to 256
+// One launch serves blockIdx.y = (expert or the single matrix, chunk of entries).  Each expert has a list of up to 512
 // entries; entry i multiplies the activation row entry / src_div and writes output row entry.
 struct TileArgs {
     MxDev w;

@@ -64,7 +64,7 @@ class Engine:
         return int(out.value)
 
     def set_tile_prefill(self, on):
-        """run_tile on token tiles of up to 256 rows (True, default) or one graph launch per token (False); same results."""
+        """run_tile on token tiles of up to 512 rows (True, default) or one graph launch per token (False); same results."""
         check(lib().brrr_model_set_tile_prefill(self._h, int(bool(on))), "brrr_model_set_tile_prefill")
 
     def run_tile(self, toks, pos0, want=True):

@@ -34,7 +34,7 @@ enum {
 
 #define BRRR_MAXSEQ 4096     /* src/bin/engine_gpt2.rs:16 */
 #ifndef BRRR_TILE_MAX
-#define BRRR_TILE_MAX 256    /* most token rows one pass over the layers takes (the reference's TILE is 16, src/bin/engine_gpt2.rs:19;
+#define BRRR_TILE_MAX 512    /* most token rows one pass over the layers takes (the reference's TILE is 16, src/bin/engine_gpt2.rs:19;
                               * every row's result is independent of the tile size) */
 #endif
 

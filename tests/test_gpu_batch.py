@@ -102,14 +102,14 @@ def test_batch_bad_args(brrr):
     eng = brrr.Engine.synth(cfg, 23)
     L = brrr.lib()
     # statuses: 1 = BRRR_ERR_ARG, 5 = BRRR_ERR_RANGE, 6 = BRRR_ERR_STATE
-    one = np.zeros(300, np.uint32)
-    out = np.zeros(300, np.uint32)
+    one = np.zeros(600, np.uint32)
+    out = np.zeros(600, np.uint32)
     p = one.ctypes.data
     assert L.brrr_batch_step(eng._h, 1, p, p, p, out.ctypes.data) == 6      # before brrr_batch_open
     assert L.brrr_batch_open(eng._h, 0) == 1 and L.brrr_batch_open(eng._h, 65) == 1
     assert L.brrr_batch_open(eng._h, 2) == 0
     assert L.brrr_batch_open(eng._h, 2) == 6
-    assert L.brrr_batch_step(eng._h, 257, p, p, p, out.ctypes.data) == 1
+    assert L.brrr_batch_step(eng._h, 513, p, p, p, out.ctypes.data) == 1
     assert L.brrr_batch_step(eng._h, 0, p, p, p, out.ctypes.data) == 1
     bad = np.array([2], np.uint32)
     assert L.brrr_batch_step(eng._h, 1, p, p, bad.ctypes.data, out.ctypes.data) == 5     # sequence 2 of 2

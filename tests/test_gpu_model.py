@@ -293,12 +293,12 @@ def test_prompt_tiles_match_serial(brrr):
     """run_tile walks tiles of tokens through the layers together (MoE block on the tensor-core tile
     kernels); the reference guarantees its batched prefill is bit-identical to the token-serial
     schedule (src/bin/engine_gpt2.rs:1005-1010).  Checked on the last token's hidden state and logits,
-    on the returned token, and on a decode run that reads the KV cache the tiles wrote, for tiles of 256
-    (the default: 600 tokens = two full tiles and a ragged one of 88) and of 16 (the reference's TILE);
+    on the returned token, and on a decode run that reads the KV cache the tiles wrote, for tiles of 512
+    (the default: 1100 tokens = two full tiles and a ragged one of 76) and of 16 (the reference's TILE);
     a 1-token call takes the serial path."""
     cfg = brrr.make_cfg(256, 3, 8, 2, 8, 4, 1024, sliding_window=8)
     eng = brrr.Engine.synth(cfg, 11)
-    prompt = [int(t) for t in S.synth_prompt(11, 600, 1000)]
+    prompt = [int(t) for t in S.synth_prompt(11, 1100, 1000)]
     tok_s = 0
     eng.set_tile_prefill(False)
     for i, t in enumerate(prompt):

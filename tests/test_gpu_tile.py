@@ -1,6 +1,6 @@
 """Token-tile MXFP4 matmul on the tcgen05 tensor cores (brrr_mx_matmul_tile) against the CPU oracle:
 every output must equal the per-token expert matvec bit for bit (0 ulp), for any number of tokens
-in the tile (1..256: four entries per CTA up to 16 tokens, eight beyond), ragged row counts and row
+in the tile (1..512: four entries per CTA up to 16 tokens, eight up to 64, sixteen beyond), ragged row counts and row
 windows."""
 import ctypes as C
 
@@ -53,7 +53,7 @@ def _case(L, orc, dev, rows, blocks, ntok, row0=0, nrows=None, wide_exponents=Fa
 
 
 @pytest.mark.parametrize("rows,blocks,ntok", [(128, 2, 16), (128, 4, 1), (256, 90, 16), (16, 2, 3), (208, 6, 5), (2880, 90, 16), (5760, 90, 7),
-                                               (256, 6, 17), (2880, 90, 64), (208, 10, 41), (256, 6, 200), (128, 4, 256)])
+                                               (256, 6, 17), (2880, 90, 64), (208, 10, 41), (256, 6, 200), (128, 4, 512)])
 def test_tile_equals_per_token_matvec(L, orc, dev, rows, blocks, ntok):
     _case(L, orc, dev, rows, blocks, ntok)
 
@@ -69,14 +69,14 @@ def test_tile_bad_args(L, dev):
     raw = to_dev(S.synth_mxfp4(1, 0, S.T["UP"], 16 * 2), dev)
     h = C.c_void_p()
     assert L.brrr_mxmat_from_gguf(P(raw), 16, 2, C.byref(h), None) == 0
-    assert L.brrr_mx_matmul_tile(h, 0, 16, P(t), P(t), 257, P(t), 16, None) == 1
+    assert L.brrr_mx_matmul_tile(h, 0, 16, P(t), P(t), 513, P(t), 16, None) == 1
     assert L.brrr_mx_matmul_tile(h, 0, 16, P(t), P(t), 0, P(t), 16, None) == 1
     assert L.brrr_mx_matmul_tile(h, 8, 16, P(t), P(t), 1, P(t), 16, None) == 1
     assert L.brrr_mx_matmul_tile(h, 0, 16, P(t), P(t), 1, P(t), 8, None) == 1
     L.brrr_mxmat_free(h)
 
 
-@pytest.mark.parametrize("ntok", [1, 5, 16, 17, 40, 64, 130, 256])
+@pytest.mark.parametrize("ntok", [1, 5, 16, 17, 40, 64, 130, 512])
 def test_moe_ffn_tile_equals_token_by_token(brrr, dev, ntok):
     """The grouped tensor-core MoE step on a tile of tokens against the per-token step (itself
     bit-identical to the oracle): routing, weights and residual outputs, at the gpt-oss-20b layer
