@@ -294,7 +294,7 @@ def run_moe_tile(args):
 
 
 def run_batched(args):
-    """--workload batched: greedy decode of b = 1, 4, 16, 64 independent sequences (one KV cache each, 32-token
+    """--workload batched: greedy decode of b = 1, 4, 16, 64, 256 independent sequences (one KV cache each, 32-token
     prompts) through Engine.batch_step, one pass per step for all rows of the batch.  One step = one pass
     = b tokens; the clock is the host's around the calls (each returns the rows' tokens to host memory).  The
     first 16 tokens of four sequences are checked against the one-sequence engine."""
@@ -305,7 +305,7 @@ def run_batched(args):
     torch.cuda.set_device(0)
     eng = B.Engine.synth(B.gptoss_20b_cfg() if args.layers == 24 else B.make_cfg(2880, args.layers, 64, 8, 32, 4, args.vocab), SEED)
     vmax = 199999 if args.vocab > 199999 else args.vocab - 1
-    plen, nb = 32, 64
+    plen, nb = 32, 256
     prompts = [[int(t) for t in S.synth_prompt(SEED + 100 + i, plen, vmax)] for i in range(nb)]
     # the checker: four sequences on the one-sequence engine (token-serial schedule)
     ncheck, want = 16, []
@@ -327,7 +327,7 @@ def run_batched(args):
     eng.batch_open(nb)
     rows, same = [], True
     steps = max(args.steps, ncheck)
-    for b in (1, 4, 16, 64):
+    for b in (1, 4, 16, 64, 256):
         for s in range(b):
             eng.batch_prefill(s, prompts[s][:-1])
         toks = [prompts[s][-1] for s in range(b)]
@@ -349,11 +349,11 @@ def run_batched(args):
         for s in range(min(b, 4)):
             same = same and got[s][:ncheck] == want[s]
         rows.append({"batch": b, "tok_s": b * steps / dt, "ms_per_pass": 1000 * dt / steps, "per_sequence_tok_s": steps / dt})
-    best = rows[-1]
+    best = max(rows, key=lambda r: r["tok_s"])
     print(json.dumps({"metric": "batched decode tok/s (gpt-oss-20b shape, independent sequences)", "value": best["tok_s"], "unit": "tok/s", "n_gpus": 1,
                       "steps": steps, "warmup": max(args.warmup, 3), "ms_per_step": best["ms_per_pass"], "higher_is_better": True, "scaling": "weak",
                       "vs_baseline": None, "dtype": "int8xfp4->int32 (tcgen05 kind::i8), int8 dp4a, f32", "data": "synthetic",
-                      "config": {"workload": "gpt-oss-20b batched greedy decode, 32-token prompts, b = 1/4/16/64 sequences, wall clock through Engine.batch_step",
+                      "config": {"workload": "gpt-oss-20b batched greedy decode, 32-token prompts, b = 1/4/16/64/256 sequences (one 403 MB KV cache each), wall clock through Engine.batch_step",
                                  "l2": "inputs larger than L2 (every pass streams the dense layers, the routed experts and the vocabulary projection)"},
                       "batches": rows, "one_sequence_decode_tok_s": serial_tok_s,
                       "parity": {"sequences_checked": 4, "tokens_each": ncheck, "identical_to_one_sequence_engine": bool(same)}}), flush=True)

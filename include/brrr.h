@@ -101,7 +101,7 @@ int brrr_model_set_tile_prefill(brrr_model *m, int on);
  *                       A row attends over its sequence's cache up to pos[i] - 1 plus itself; rows of one
  *                       sequence must carry ascending positions
  *   brrr_batch_step_logits  the same, and the rows' logits [n][n_vocab] to host memory */
-#define BRRR_BATCH_MAX 64
+#define BRRR_BATCH_MAX 256
 int brrr_batch_open(brrr_model *m, int nseq);
 int brrr_batch_prefill(brrr_model *m, uint32_t seq, const uint32_t *toks, uint32_t n, uint32_t pos0);
 int brrr_batch_step(brrr_model *m, int n, const uint32_t *toks, const uint32_t *pos, const uint32_t *seq, uint32_t *out_toks);

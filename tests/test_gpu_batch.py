@@ -106,7 +106,7 @@ def test_batch_bad_args(brrr):
     out = np.zeros(600, np.uint32)
     p = one.ctypes.data
     assert L.brrr_batch_step(eng._h, 1, p, p, p, out.ctypes.data) == 6      # before brrr_batch_open
-    assert L.brrr_batch_open(eng._h, 0) == 1 and L.brrr_batch_open(eng._h, 65) == 1
+    assert L.brrr_batch_open(eng._h, 0) == 1 and L.brrr_batch_open(eng._h, 257) == 1
     assert L.brrr_batch_open(eng._h, 2) == 0
     assert L.brrr_batch_open(eng._h, 2) == 6
     assert L.brrr_batch_step(eng._h, 513, p, p, p, out.ctypes.data) == 1
