@@ -55,3 +55,24 @@ def test_no_cpu_fallback_when_library_missing(monkeypatch, brrr):
     import pytest
     with pytest.raises(_lib.BrrrError):
         _lib.lib()
+
+
+def test_limits_agree_between_header_and_device_code(brrr):
+    """BRRR_MAXSEQ and BRRR_TILE_MAX are defined for hosts (include/brrr.h) and for the kernels (csrc/brrr_dev.cuh):
+    the two must carry the same values, and the argument checks that need no GPU must follow them."""
+    pub = open(os.path.join(ROOT, "include", "brrr.h")).read()
+    dev = open(os.path.join(ROOT, "cpubrrr_b200", "csrc", "brrr_dev.cuh")).read()
+    for name in ("BRRR_MAXSEQ", "BRRR_TILE_MAX"):
+        a = re.search(r"#define\s+%s\s+(\d+)" % name, pub).group(1)
+        b = re.search(r"#define\s+%s\s+(\d+)" % name, dev).group(1)
+        assert a == b, (name, a, b)
+    tile_max = int(re.search(r"#define\s+BRRR_TILE_MAX\s+(\d+)", pub).group(1))
+    batch_max = int(re.search(r"#define\s+BRRR_BATCH_MAX\s+(\d+)", pub).group(1))
+    L = brrr.lib()
+    p = ctypes.c_void_p(16)
+    # no model handle: argument errors come before anything touches the device
+    assert L.brrr_batch_open(None, 1) == 1
+    assert L.brrr_batch_step(None, 1, p, p, p, p) == 1
+    assert L.brrr_q8_matmul_rows(None, p, p, 1, p, 16, 0, None) == 1
+    assert L.brrr_mx_matmul_tile(None, 0, 16, p, p, tile_max + 1, p, 16, None) == 1
+    assert batch_max <= tile_max
